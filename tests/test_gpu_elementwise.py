@@ -1,0 +1,119 @@
+"""Memory-bound sm_100a kernels vs the plain PyTorch fp32 statements in ops/reference.py."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    assert err <= tol * (b.abs().max().item() + 1e-6), f"err {err}, ref scale {b.abs().max().item()}"
+
+
+def _grads(fn, inputs, seed=0):
+    torch.manual_seed(seed)
+    outs = fn(*inputs)
+    outs = outs if isinstance(outs, tuple) else (outs,)
+    gs = [torch.randn_like(o.float()).to(o.dtype) for o in outs]
+    grads = torch.autograd.grad(outs, [i for i in inputs if i.requires_grad], gs, allow_unused=True)
+    return outs, grads
+
+
+@pytest.mark.parametrize("T,D", [(64, 256), (1000, 4096), (33, 2048), (7, 64), (129, 8192)])
+def test_rmsnorm_and_add(T, D):
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    torch.manual_seed(0)
+    x = torch.randn(T, D, device="cuda").bfloat16().requires_grad_()
+    r = torch.randn(T, D, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16().requires_grad_()
+    o1, g1 = _grads(lambda a, b: ops.rms_norm(a, b, 1e-6), [x, w])
+    o2, g2 = _grads(lambda a, b: ref.rms_norm(a.float(), b.float(), 1e-6), [x, w])
+    _close(o1[0], o2[0]); _close(g1[0], g2[0]); _close(g1[1], g2[1], 3e-2)
+    o1, g1 = _grads(lambda a, b, c: ops.add_rms_norm(a, b, c, 1e-6), [x, r, w])
+    o2, g2 = _grads(lambda a, b, c: ref.add_rms_norm(a, b, c, 1e-6), [x, r, w])
+    for a, b in zip(o1 + tuple(g1), o2 + tuple(g2)):
+        _close(a, b, 3e-2)
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,d", [(128, 4, 2, 64), (300, 32, 8, 128), (17, 2, 1, 256)])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_qk_norm_rope(T, Hq, Hkv, d, with_norm):
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    torch.manual_seed(0)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * d, device="cuda").bfloat16().requires_grad_()
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_() if with_norm else None
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_() if with_norm else None
+    cos, sin = ops.rope_tables(torch.arange(T, device="cuda"), d, 1e6)
+
+    def run(fn):
+        q = qkv[:, :Hq * d].view(T, Hq, d)
+        k = qkv[:, Hq * d:(Hq + Hkv) * d].view(T, Hkv, d)
+        return fn(q, k, qw, kw, cos, sin, 1e-6)
+    ins = [qkv] + ([qw, kw] if with_norm else [])
+    o1, g1 = _grads(lambda *a: run(ops.qk_norm_rope), ins)
+    o2, g2 = _grads(lambda *a: run(ref.qk_norm_rope), ins)
+    for a, b in zip(o1 + tuple(g1), o2 + tuple(g2)):
+        _close(a, b, 3e-2)
+
+
+@pytest.mark.parametrize("T,F", [(256, 768), (1000, 12288), (3, 64)])
+def test_swiglu(T, F):
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    torch.manual_seed(0)
+    gu = torch.randn(T, 2 * F, device="cuda").bfloat16().requires_grad_()
+    o1, g1 = _grads(lambda a: ops.swiglu(a[:, :F], a[:, F:]), [gu])
+    o2, g2 = _grads(lambda a: ref.swiglu(a[:, :F], a[:, F:]), [gu])
+    _close(o1[0], o2[0]); _close(g1[0], g2[0])
+
+
+@pytest.mark.parametrize("T,D,V,chunks", [(256, 128, 1000, 1), (500, 256, 32000, 3), (128, 64, 151936, 1)])
+def test_linear_cross_entropy(T, D, V, chunks):
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    torch.manual_seed(0)
+    h = torch.randn(T, D, device="cuda").bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(V, D, device="cuda")).bfloat16().requires_grad_()
+    y = torch.randint(0, V, (T,), device="cuda")
+    y[::7] = -100
+    l1 = ops.linear_cross_entropy_sum(h, w, y, chunks)
+    g1 = torch.autograd.grad(l1 / 100.0, [h, w])
+    check_status("ce")
+    l2 = ref.linear_cross_entropy_sum(h.float(), w.float(), y, chunks)
+    g2 = torch.autograd.grad(l2 / 100.0, [h, w])
+    assert abs(l1.item() - l2.item()) / abs(l2.item()) < 5e-3
+    _close(g1[0], g2[0], 3e-2); _close(g1[1], g2[1], 3e-2)
+    lg = (h.float() @ w.float().t()).bfloat16().requires_grad_()
+    l3 = ops.cross_entropy_sum(lg, y)
+    (g3,) = torch.autograd.grad(l3, [lg])
+    l4 = ref.cross_entropy_sum(lg.float(), y)
+    (g4,) = torch.autograd.grad(l4, [lg])
+    assert abs(l3.item() - l4.item()) / abs(l4.item()) < 5e-3
+    _close(g3, g4, 3e-2)
+
+
+def test_adamw_and_sqnorm():
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    torch.manual_seed(0)
+    n = 1_000_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").bfloat16()
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    p16 = p.bfloat16()
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    coef = torch.tensor([0.5], device="cuda")
+    for step in (1, 2, 3):
+        ops.adamw_step_(p, g, m, v, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step, p_lowp=p16, clip_coef=coef)
+        ref.adamw_step_(pr, g, mr, vr, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step, grad_scale=0.5)
+    assert (p - pr).abs().max().item() < 1e-4
+    assert torch.equal(p16, p.bfloat16())
+    a, b = torch.randn(300_001, device="cuda").bfloat16(), torch.randn(77, device="cuda")
+    s1 = ops.sq_norm([a, b])
+    s2 = a.float().pow(2).sum() + b.pow(2).sum()
+    assert abs(s1.item() - s2.item()) / s2.item() < 1e-4
+    assert torch.equal(ops.sq_norm([a, b]), s1)

@@ -1,0 +1,111 @@
+"""tcgen05 GEMM vs a plain fp32 PyTorch product, all operand layouts, edge shapes, grouped forms."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(out, ref, tol=2e-2):
+    out, ref = out.float(), ref.float()
+    err = (out - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max err {err} vs scale {scale}"
+
+
+SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (200, 136, 72), (1024, 4096, 1024), (64, 64, 64), (136, 520, 200),
+          (2048, 128, 512)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("layout", ["tn", "nn", "tt"])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_layouts(M, N, K, layout, out_dtype):
+    from torchllmtuner_b200.ops import gemm
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    torch.manual_seed(0)
+    dev = "cuda"
+    A = torch.randn(M, K, device=dev).bfloat16()
+    B = torch.randn(N, K, device=dev).bfloat16()
+    ref = A.float() @ B.float().t()
+    if layout == "tn":
+        out = gemm(A, B, out_dtype=out_dtype)
+    elif layout == "nn":   # B stored [K, N]
+        out = gemm(A, B.t().contiguous(), b_mn=True, out_dtype=out_dtype)
+    else:                  # A stored [K, M], B stored [K, N]
+        out = gemm(A.t().contiguous(), B.t().contiguous(), a_mn=True, b_mn=True, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    check_status("gemm")
+    _close(out, ref)
+
+
+def test_gemm_accumulate_and_strided_out():
+    from torchllmtuner_b200.ops import gemm
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    torch.manual_seed(1)
+    M, N, K = 256, 384, 512
+    A = torch.randn(K, M, device="cuda").bfloat16()
+    B = torch.randn(K, N, device="cuda").bfloat16()
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    ref = acc + A.float().t() @ B.float()
+    gemm(A, B, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    check_status("gemm")
+    _close(acc, ref)
+    big = torch.zeros(M, 2 * N, device="cuda", dtype=torch.bfloat16)
+    gemm(A, B, a_mn=True, b_mn=True, out=big[:, N:])
+    check_status("gemm")
+    _close(big[:, N:], A.float().t() @ B.float())
+    assert big[:, :N].abs().max().item() == 0
+
+
+def test_gemm_determinism():
+    from torchllmtuner_b200.ops import gemm
+    A = torch.randn(512, 1024, device="cuda").bfloat16()
+    B = torch.randn(768, 1024, device="cuda").bfloat16()
+    assert torch.equal(gemm(A, B), gemm(A, B))
+
+
+def _segments(counts):
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + -(-c // 128) * 128)
+    return offs
+
+
+@pytest.mark.parametrize("counts", [[128, 256, 0, 130, 5], [700, 1, 0, 0, 300, 128]])
+def test_grouped_gemm_and_wgrad(counts):
+    from torchllmtuner_b200.ops.cuda_ext import check_status, load
+    ext = load()
+    torch.manual_seed(2)
+    G, K, N = len(counts), 256, 384
+    offs = _segments(counts)
+    rows = offs[-1]
+    x = torch.zeros(rows, K, device="cuda", dtype=torch.bfloat16)
+    for g, c in enumerate(counts):
+        x[offs[g]:offs[g] + c] = torch.randn(c, K, device="cuda").bfloat16()
+    w = torch.randn(G, N, K, device="cuda").bfloat16() * 0.1
+    seg = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    y = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    ext.grouped_gemm(x, w, y, seg, False)
+    check_status("grouped_gemm")
+    for g, c in enumerate(counts):
+        if c:
+            _close(y[offs[g]:offs[g] + c], x[offs[g]:offs[g] + c].float() @ w[g].float().t())
+    # dgrad form: y2 = dy @ w  (w stored [G, N, K] read as [G, K'=N, N'=K])
+    dy = torch.zeros(rows, N, device="cuda", dtype=torch.bfloat16)
+    for g, c in enumerate(counts):
+        dy[offs[g]:offs[g] + c] = torch.randn(c, N, device="cuda").bfloat16()
+    dx = torch.empty(rows, K, device="cuda", dtype=torch.bfloat16)
+    ext.grouped_gemm(dy, w, dx, seg, True)
+    check_status("grouped_dgrad")
+    for g, c in enumerate(counts):
+        if c:
+            _close(dx[offs[g]:offs[g] + c], dy[offs[g]:offs[g] + c].float() @ w[g].float())
+    dw = torch.empty(G, N, K, device="cuda", dtype=torch.float32)
+    ext.grouped_wgrad(dy, x, dw, seg, False)
+    check_status("grouped_wgrad")
+    for g, c in enumerate(counts):
+        ref = dy[offs[g]:offs[g] + c].float().t() @ x[offs[g]:offs[g] + c].float()
+        if c:
+            _close(dw[g], ref)
+        else:
+            assert dw[g].abs().max().item() == 0

@@ -1,0 +1,809 @@
+// Variable-length causal GQA flash attention for sm_100a on tcgen05 / TMEM, forward and backward.
+// (reference call sites: llmtuner/models/qwen/qwen3/model.py:270-283 through the HF attention interface, and
+//  llmtuner/kernel/ops/varlen_attention.py:60-85; the reference builds a dense [B,1,T,T] mask for packed rows
+//  (llmtuner/models/common/attention.py:14-62) where this kernel masks from per-tile document bounds.)
+//
+// Layout: q [Tq, Hq, HD], k/v [Tk, Hkv, HD], bf16, heads packed (head stride HD), arbitrary token stride.
+// Work is described by tile tables built on the host from cu_seqlens (int32 [n][8]):
+//   q tile : {q0, nq, kbeg, klen, diag0}        rows q0..q0+nq of one document; its keys are rows kbeg..kbeg+klen;
+//                                               row i of the tile sees keys [0, min(klen, diag0 + i)) when causal.
+//   k tile : {k0, nk, kk0, qbeg, qlen, off, klen} keys k0..k0+nk (index kk0.. inside the document); the document's
+//                                               queries are rows qbeg..qbeg+qlen; query r sees key x iff x <= r + off.
+// Forward: one CTA per (q tile, head): S = Q K^T into TMEM, softmax in registers (row per thread, lazy rescale of
+// the TMEM-resident O), P through shared memory, O += P V.  Backward: a dK/dV kernel per (k tile, kv head) that
+// loops over the query heads of the group and the q tiles, and a dQ kernel per (q tile, head); both recompute
+// S and dP so that no atomics are needed.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace llmt {
+
+constexpr int kAttnThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 16-column slice `ks` of a K-major tile stored as 64-column halves of [128 rows][128 B].
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int ks) {
+  return umma_desc_sw128(base + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+}
+// 16-row slice `ks` of the same physical tile read as an MN-major operand (rows = reduction index).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int ks) {
+  return umma_desc_sw128(base + ks * 2048, 16384, 1024);
+}
+// Store 32 consecutive bf16 (packed in 16 words) of row `row`, columns [col0, col0+32) into a swizzled K-major tile.
+__device__ __forceinline__ void store_row32_swz(uint8_t* tile, int row, int col0, const uint32_t* w) {
+  uint8_t* base = tile + (col0 >> 6) * 16384 + row * 128;
+  const int chunk0 = (col0 & 63) >> 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 v = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+    *reinterpret_cast<uint4*>(base + (((chunk0 + c) ^ (row & 7)) << 4)) = v;
+  }
+}
+
+template <int HD>
+struct AttnSmem {
+  static constexpr int kTile = 128 * HD * 2;   // Q / K / V / dO tile, 128 rows
+  static constexpr int kP = 128 * 128 * 2;     // P / dS tile
+};
+
+// =========================================================================================== forward
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
+                const int* __restrict__ tiles, int Hq, int Hkv, int Tq, int64_t o_stride, float scale_log2, int causal,
+                int* status) {
+  using SM = AttnSmem<HD>;
+  constexpr int NH = HD / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + SM::kTile;       // 2 stages
+  uint8_t* sV = sK + 2 * SM::kTile;   // 2 stages
+  uint8_t* sP = sV + 2 * SM::kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + SM::kP);
+  uint64_t* q_full = bars;
+  uint64_t* kfull = bars + 1;
+  uint64_t* kempty = bars + 3;
+  uint64_t* vfull = bars + 5;
+  uint64_t* vempty = bars + 7;
+  uint64_t* sfull = bars + 9;
+  uint64_t* sempty = bars + 11;
+  uint64_t* pfull = bars + 13;
+  uint64_t* pvdone = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_idx = blockIdx.x / Hq;
+  const int h = blockIdx.x % Hq;
+  const int hk = h / (Hq / Hkv);
+  const int* tl = tiles + tile_idx * 8;
+  const int q0 = tl[0], nq = tl[1], kbeg = tl[2], klen = tl[3], diag0 = tl[4];
+  const int kmax = causal ? min(klen, diag0 + nq - 1) : klen;
+  const int n_kv = (kmax + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1);
+      mbar_init(&vfull[s], 1); mbar_init(&vempty[s], 1);
+      mbar_init(&sfull[s], 1); mbar_init(&sempty[s], 128);
+    }
+    mbar_init(pfull, 128);
+    mbar_init(pvdone, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tO = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_arrive_expect_tx(q_full, SM::kTile);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) tma_load_3d(sQ + hf * 16384, &tmQ, q_full, hf * 64, h, q0);
+      int armed[4] = {-1, -1, -1, -1};  // last armed parity of kfull[0], kfull[1], vfull[0], vfull[1]
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&kempty[s], ph ^ 1, abort_flag, status, 1100 + s)) break;
+        mbar_arrive_expect_tx(&kfull[s], SM::kTile);
+        armed[s] = (int)ph;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sK + s * SM::kTile + hf * 16384, &tmK, &kfull[s], hf * 64, hk, kbeg + j * 128);
+        if (!mbar_wait_bounded(&vempty[s], ph ^ 1, abort_flag, status, 1110 + s)) break;
+        mbar_arrive_expect_tx(&vfull[s], SM::kTile);
+        armed[2 + s] = (int)ph;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sV + s * SM::kTile + hf * 16384, &tmV, &vfull[s], hf * 64, hk, kbeg + j * 128);
+      }
+      if (*abort_flag) {
+        // wait (bounded) for copies in flight before shared memory is released
+        for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(q_full, 0)) break;
+        for (int x = 0; x < 4; ++x) {
+          if (armed[x] < 0) continue;
+          uint64_t* b = (x < 2) ? &kfull[x] : &vfull[x - 2];
+          for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(b, (uint32_t)armed[x])) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idS = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idPV = umma_idesc_bf16(128, HD, false, true);
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, status, 1200);
+      auto issue_S = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&kfull[s], ph, abort_flag, status, 1210 + s)) return false;
+        if (!mbar_wait_bounded(&sempty[s], ph ^ 1, abort_flag, status, 1220 + s)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_bf16_ss(tS + s * 128, desc_kmajor(aQ, ks), desc_kmajor(aK + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+        umma_commit(&sfull[s]);
+        umma_commit(&kempty[s]);
+        return true;
+      };
+      if (ok) ok = issue_S(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        if (j + 1 < n_kv) { if (!issue_S(j + 1)) break; }
+        if (!mbar_wait_bounded(pfull, j & 1, abort_flag, status, 1230)) break;
+        if (!mbar_wait_bounded(&vfull[s], (j >> 1) & 1, abort_flag, status, 1240 + s)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tO, desc_kmajor(aP, ks), desc_mnmajor(aV + s * SM::kTile, ks), idPV, (j | ks) ? 1u : 0u);
+        umma_commit(&vempty[s]);
+        umma_commit(pvdone);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    const int row_limit = causal ? min(klen, diag0 + row) : klen;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait_bounded(&sfull[s], (j >> 1) & 1, abort_flag, status, 1300 + s)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tS + lane_off + s * 128;
+      const int kbase = j * 128;
+      const bool need_mask = kbase + 128 > (causal ? min(klen, diag0) : klen);
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(ts + c * 32, r);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i < row_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      mx *= scale_log2;
+      const float m_new = fmaxf(m_used, mx);
+      const bool need = m_new > m_used + 8.f;  // lazy rescale: only when the running max moved by more than 2^8
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = need ? ((m_used == -INFINITY) ? 0.f : ex2(m_used - m_new)) : 1.f;
+        if (need) { l *= alpha; m_used = m_new; }
+        if (j > 0) {
+          if (!mbar_wait_bounded(pvdone, (j - 1) & 1, abort_flag, status, 1310)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + lane_off + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tO + lane_off + c * 32, r);
+          }
+          tmem_wait_st();
+        }
+      }
+      if (j > 0) {
+        if (!mbar_wait_bounded(pvdone, (j - 1) & 1, abort_flag, status, 1320)) { ok = false; break; }
+      }
+      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32], w[16];
+        tmem_ld_32x32(ts + c * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2(__uint_as_float(r[i]) * scale_log2 - m_safe);
+          float p1 = ex2(__uint_as_float(r[i + 1]) * scale_log2 - m_safe);
+          if (need_mask) {
+            if (kbase + c * 32 + i >= row_limit) p0 = 0.f;
+            if (kbase + c * 32 + i + 1 >= row_limit) p1 = 0.f;
+          }
+          rs += p0 + p1;
+          w[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        store_row32_swz(sP, row, c * 32, w);
+      }
+      l += rs;
+      tc_fence_before();
+      mbar_arrive(&sempty[s]);
+      fence_proxy_async_smem();
+      mbar_arrive(pfull);
+    }
+    // ---- finalize
+    if (ok && n_kv > 0) ok = mbar_wait_bounded(pvdone, (n_kv - 1) & 1, abort_flag, status, 1330);
+    if (ok) {
+      tc_fence_after();
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = O + (int64_t)(q0 + row) * o_stride + (int64_t)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        if (n_kv > 0) {
+          tmem_ld_32x32(tO + lane_off + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row < nq) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            reinterpret_cast<uint4*>(orow + c * 32)[v] = o;
+          }
+        }
+      }
+      if (row < nq) lse[(int64_t)h * Tq + q0 + row] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// =========================================================================================== backward: delta
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t o_stride, const __nv_bfloat16* __restrict__ d_o,
+                                  int64_t do_stride, float* __restrict__ delta, int T, int H, int HD) {
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (int64_t)T * H) return;
+  const int t = (int)(item / H), h = (int)(item % H), lane = threadIdx.x & 31;
+  const __nv_bfloat16* po = o + (int64_t)t * o_stride + (int64_t)h * HD;
+  const __nv_bfloat16* pd = d_o + (int64_t)t * do_stride + (int64_t)h * HD;
+  float s = 0.f;
+  for (int c = lane * 2; c < HD; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + c));
+    s += a.x * b.x + a.y * b.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[(int64_t)h * T + t] = s;
+}
+
+// =========================================================================================== backward: dK, dV
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
+                    __nv_bfloat16* __restrict__ dV, const int* __restrict__ tiles, int Hq, int Hkv, int Tq, int64_t dk_stride,
+                    int64_t dv_stride, float scale, int causal, int* status) {
+  using SM = AttnSmem<HD>;
+  constexpr int NH = HD / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + SM::kTile;
+  uint8_t* sQ = sV + SM::kTile;
+  uint8_t* sdO = sQ + SM::kTile;
+  uint8_t* sPT = sdO + SM::kTile;
+  uint8_t* sdST = sPT + SM::kP;
+  float* s_lse = reinterpret_cast<float*>(sdST + SM::kP);  // [2][128]
+  float* s_delta = s_lse + 256;                            // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 256);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* s_full = bars + 3;
+  uint64_t* p_full = bars + 4;
+  uint64_t* acc_done = bars + 5;
+  uint64_t* stat_ready = bars + 6;  // lse / delta of the current q tile staged by the 128 compute threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_idx = blockIdx.x / Hkv;
+  const int hk = blockIdx.x % Hkv;
+  const int g = Hq / Hkv;
+  const int* tl = tiles + tile_idx * 8;
+  const int k0 = tl[0], nk = tl[1], kk0 = tl[2], qbeg = tl[3], qlen = tl[4], off = tl[5], klen = tl[6];
+  int qs = 0;
+  if (causal) { qs = kk0 - off; if (qs < 0) qs = 0; qs &= ~127; }
+  const int n_qt = (qlen > qs) ? (qlen - qs + 127) / 128 : 0;
+  const int n_it = n_qt * g;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1);
+    mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(acc_done, 1); mbar_init(stat_ready, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tST = tmem_base, tDPT = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 256 + HD;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+      mbar_arrive_expect_tx(kv_full, 2 * SM::kTile);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        tma_load_3d(sK + hf * 16384, &tmK, kv_full, hf * 64, hk, k0);
+        tma_load_3d(sV + hf * 16384, &tmV, kv_full, hf * 64, hk, k0);
+      }
+      int it_issued = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int h = hk * g + it / n_qt;
+        const int qrow = qbeg + qs + (it % n_qt) * 128;
+        if (!mbar_wait_bounded(qdo_empty, (it & 1) ^ 1, abort_flag, status, 2100)) break;
+        mbar_arrive_expect_tx(qdo_full, 2 * SM::kTile);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) {
+          tma_load_3d(sQ + hf * 16384, &tmQ, qdo_full, hf * 64, h, qrow);
+          tma_load_3d(sdO + hf * 16384, &tmdO, qdo_full, hf * 64, h, qrow);
+        }
+        it_issued = it + 1;
+      }
+      if (*abort_flag) {
+        for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(kv_full, 0)) break;
+        if (it_issued > 0)
+          for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(qdo_full, (it_issued - 1) & 1)) break;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idS = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idAcc = umma_idesc_bf16(128, HD, false, true);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aPT = smem_u32(sPT),
+                     adST = smem_u32(sdST);
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, status, 2200);
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (!mbar_wait_bounded(qdo_full, it & 1, abort_flag, status, 2210)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) umma_bf16_ss(tST, desc_kmajor(aK, ks), desc_kmajor(aQ, ks), idS, ks ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) umma_bf16_ss(tDPT, desc_kmajor(aV, ks), desc_kmajor(adO, ks), idS, ks ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(p_full, it & 1, abort_flag, status, 2220)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_ss(tDV, desc_kmajor(aPT, ks), desc_mnmajor(adO, ks), idAcc, (it | ks) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) umma_bf16_ss(tDK, desc_kmajor(adST, ks), desc_mnmajor(aQ, ks), idAcc, (it | ks) ? 1u : 0u);
+        umma_commit(qdo_empty);
+        umma_commit(acc_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // key row inside the tile
+    const int tid = threadIdx.x - 64;     // 0..127
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const int key_idx = kk0 + row;
+    const bool key_ok = (row < nk) && (key_idx < klen);
+    const float scale_log2 = scale * kLog2e;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int h = hk * g + it / n_qt;
+      const int qi0 = qs + (it % n_qt) * 128;  // first query index (inside the document) of this q tile
+      {
+        const int qi = qi0 + tid;
+        const bool v = qi < qlen;
+        s_lse[(it & 1) * 128 + tid] = v ? lse[(int64_t)h * Tq + qbeg + qi] * kLog2e : INFINITY;
+        s_delta[(it & 1) * 128 + tid] = v ? delta[(int64_t)h * Tq + qbeg + qi] : 0.f;
+      }
+      mbar_arrive(stat_ready);
+      if (!mbar_wait_bounded(stat_ready, it & 1, abort_flag, status, 2330)) { ok = false; break; }
+      if (!mbar_wait_bounded(s_full, it & 1, abort_flag, status, 2300)) { ok = false; break; }
+      tc_fence_after();
+      if (it > 0) {
+        if (!mbar_wait_bounded(acc_done, (it - 1) & 1, abort_flag, status, 2310)) { ok = false; break; }
+      }
+      const float* pl = s_lse + (it & 1) * 128;
+      const float* pd = s_delta + (it & 1) * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32], wp[16], wd[16];
+        tmem_ld_32x32(tST + lane_off + c * 32, rs);
+        tmem_ld_32x32(tDPT + lane_off + c * 32, rd);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int qc = c * 32 + i + e;
+            const int qi = qi0 + qc;
+            const bool vis = key_ok && (qi < qlen) && (!causal || key_idx <= qi + off);
+            const float pv = vis ? ex2(__uint_as_float(rs[i + e]) * scale_log2 - pl[qc]) : 0.f;
+            p[e] = pv;
+            ds[e] = pv * (__uint_as_float(rd[i + e]) - pd[qc]);
+          }
+          wp[i >> 1] = pack_bf16x2(p[0], p[1]);
+          wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
+        store_row32_swz(sPT, row, c * 32, wp);
+        store_row32_swz(sdST, row, c * 32, wd);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+    }
+    if (ok && n_it > 0) ok = mbar_wait_bounded(acc_done, (n_it - 1) & 1, abort_flag, status, 2320);
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* kr = dK + (int64_t)(k0 + row) * dk_stride + (int64_t)hk * HD;
+      __nv_bfloat16* vr = dV + (int64_t)(k0 + row) * dv_stride + (int64_t)hk * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t rk[32], rv[32];
+        if (n_it > 0) {
+          tmem_ld_32x32(tDK + lane_off + c * 32, rk);
+          tmem_ld_32x32(tDV + lane_off + c * 32, rv);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { rk[i] = 0u; rv[i] = 0u; }
+        }
+        if (row < nk) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 a, b;
+            a.x = pack_bf16x2(__uint_as_float(rk[8 * v]) * scale, __uint_as_float(rk[8 * v + 1]) * scale);
+            a.y = pack_bf16x2(__uint_as_float(rk[8 * v + 2]) * scale, __uint_as_float(rk[8 * v + 3]) * scale);
+            a.z = pack_bf16x2(__uint_as_float(rk[8 * v + 4]) * scale, __uint_as_float(rk[8 * v + 5]) * scale);
+            a.w = pack_bf16x2(__uint_as_float(rk[8 * v + 6]) * scale, __uint_as_float(rk[8 * v + 7]) * scale);
+            b.x = pack_bf16x2(__uint_as_float(rv[8 * v]), __uint_as_float(rv[8 * v + 1]));
+            b.y = pack_bf16x2(__uint_as_float(rv[8 * v + 2]), __uint_as_float(rv[8 * v + 3]));
+            b.z = pack_bf16x2(__uint_as_float(rv[8 * v + 4]), __uint_as_float(rv[8 * v + 5]));
+            b.w = pack_bf16x2(__uint_as_float(rv[8 * v + 6]), __uint_as_float(rv[8 * v + 7]));
+            reinterpret_cast<uint4*>(kr + c * 32)[v] = a;
+            reinterpret_cast<uint4*>(vr + c * 32)[v] = b;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// =========================================================================================== backward: dQ
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
+                   const int* __restrict__ tiles, int Hq, int Hkv, int Tq, int64_t dq_stride, float scale, int causal,
+                   int* status) {
+  using SM = AttnSmem<HD>;
+  constexpr int NH = HD / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + SM::kTile;
+  uint8_t* sK = sdO + SM::kTile;      // 2 stages
+  uint8_t* sV = sK + 2 * SM::kTile;   // 2 stages
+  uint8_t* sdS = sV + 2 * SM::kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + SM::kP);
+  uint64_t* qdo_full = bars;
+  uint64_t* kfull = bars + 1;
+  uint64_t* kempty = bars + 3;
+  uint64_t* vfull = bars + 5;
+  uint64_t* vempty = bars + 7;
+  uint64_t* s_full = bars + 9;
+  uint64_t* ds_full = bars + 10;
+  uint64_t* dq_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_idx = blockIdx.x / Hq;
+  const int h = blockIdx.x % Hq;
+  const int hk = h / (Hq / Hkv);
+  const int* tl = tiles + tile_idx * 8;
+  const int q0 = tl[0], nq = tl[1], kbeg = tl[2], klen = tl[3], diag0 = tl[4];
+  const int kmax = causal ? min(klen, diag0 + nq - 1) : klen;
+  const int n_kv = (kmax + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1); mbar_init(&vfull[s], 1); mbar_init(&vempty[s], 1);
+    }
+    mbar_init(s_full, 1); mbar_init(ds_full, 128); mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+      mbar_arrive_expect_tx(qdo_full, 2 * SM::kTile);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        tma_load_3d(sQ + hf * 16384, &tmQ, qdo_full, hf * 64, h, q0);
+        tma_load_3d(sdO + hf * 16384, &tmdO, qdo_full, hf * 64, h, q0);
+      }
+      int armed[4] = {-1, -1, -1, -1};
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&kempty[s], ph ^ 1, abort_flag, status, 3100 + s)) break;
+        mbar_arrive_expect_tx(&kfull[s], SM::kTile);
+        armed[s] = (int)ph;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sK + s * SM::kTile + hf * 16384, &tmK, &kfull[s], hf * 64, hk, kbeg + j * 128);
+        if (!mbar_wait_bounded(&vempty[s], ph ^ 1, abort_flag, status, 3110 + s)) break;
+        mbar_arrive_expect_tx(&vfull[s], SM::kTile);
+        armed[2 + s] = (int)ph;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sV + s * SM::kTile + hf * 16384, &tmV, &vfull[s], hf * 64, hk, kbeg + j * 128);
+      }
+      if (*abort_flag) {
+        for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(qdo_full, 0)) break;
+        for (int x = 0; x < 4; ++x) {
+          if (armed[x] < 0) continue;
+          uint64_t* b = (x < 2) ? &kfull[x] : &vfull[x - 2];
+          for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(b, (uint32_t)armed[x])) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idS = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idDQ = umma_idesc_bf16(128, HD, false, true);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), adS = smem_u32(sdS);
+      bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, status, 3200);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_bounded(&kfull[s], ph, abort_flag, status, 3210 + s)) break;
+        if (!mbar_wait_bounded(&vfull[s], ph, abort_flag, status, 3220 + s)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_bf16_ss(tS, desc_kmajor(aQ, ks), desc_kmajor(aK + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_bf16_ss(tDP, desc_kmajor(adO, ks), desc_kmajor(aV + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+        umma_commit(s_full);
+        umma_commit(&vempty[s]);
+        if (!mbar_wait_bounded(ds_full, j & 1, abort_flag, status, 3230)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tDQ, desc_kmajor(adS, ks), desc_mnmajor(aK + s * SM::kTile, ks), idDQ, (j | ks) ? 1u : 0u);
+        umma_commit(&kempty[s]);
+        umma_commit(dq_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const bool row_ok = row < nq;
+    const float scale_log2 = scale * kLog2e;
+    const float lse2 = row_ok ? lse[(int64_t)h * Tq + q0 + row] * kLog2e : INFINITY;
+    const float dl = row_ok ? delta[(int64_t)h * Tq + q0 + row] : 0.f;
+    const int row_limit = row_ok ? (causal ? min(klen, diag0 + row) : klen) : 0;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (!mbar_wait_bounded(s_full, j & 1, abort_flag, status, 3300)) { ok = false; break; }
+      tc_fence_after();
+      if (j > 0) {
+        if (!mbar_wait_bounded(dq_done, (j - 1) & 1, abort_flag, status, 3310)) { ok = false; break; }
+      }
+      const int kbase = j * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32], wd[16];
+        tmem_ld_32x32(tS + lane_off + c * 32, rs);
+        tmem_ld_32x32(tDP + lane_off + c * 32, rd);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const bool vis = kbase + c * 32 + i + e < row_limit;
+            const float p = vis ? ex2(__uint_as_float(rs[i + e]) * scale_log2 - lse2) : 0.f;
+            ds[e] = p * (__uint_as_float(rd[i + e]) - dl);
+          }
+          wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
+        store_row32_swz(sdS, row, c * 32, wd);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(ds_full);
+    }
+    if (ok && n_kv > 0) ok = mbar_wait_bounded(dq_done, (n_kv - 1) & 1, abort_flag, status, 3320);
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* qr = dQ + (int64_t)(q0 + row) * dq_stride + (int64_t)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        if (n_kv > 0) {
+          tmem_ld_32x32(tDQ + lane_off + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v]) * scale, __uint_as_float(r[8 * v + 1]) * scale);
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * scale, __uint_as_float(r[8 * v + 3]) * scale);
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * scale, __uint_as_float(r[8 * v + 5]) * scale);
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * scale, __uint_as_float(r[8 * v + 7]) * scale);
+            reinterpret_cast<uint4*>(qr + c * 32)[v] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ------------------------------------------------------------------------------------------- host
+int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                   const uint32_t* box);
+
+// [T, H, HD] tensor with token stride `tok_stride` elements -> 3-D map {HD, H, T}, box {64, 1, 128}.
+static int make_thd_map(CUtensorMap* m, const void* p, int T, int H, int HD, int64_t tok_stride) {
+  uint64_t dims[3] = {(uint64_t)HD, (uint64_t)H, (uint64_t)T};
+  uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)tok_stride * 2};
+  uint32_t box[3] = {64, 1, 128};
+  return make_tmap_bf16(m, p, 3, dims, str, box);
+}
+
+template <typename K>
+static int set_smem(K kern, int bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace llmt
+
+using namespace llmt;
+
+extern "C" int llmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* tiles, int num_tiles,
+                             int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                             int64_t o_stride, float scale, int causal, int* status, cudaStream_t st) {
+  if (num_tiles <= 0 || Hq <= 0) return 0;
+  if ((HD != 64 && HD != 128) || Hq % Hkv || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (o_stride & 7)) return -10;
+  CUtensorMap tq, tk, tv;
+  if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride) ||
+      make_thd_map(&tv, v, Tk, Hkv, HD, v_stride))
+    return -11;
+  const int smem = 5 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 256;
+  const float sl2 = scale * kLog2e;
+  if (HD == 128) {
+    static bool cfg = false;
+    if (!cfg) { if (set_smem(attn_fwd_kernel<128>, smem)) return -2; cfg = true; }
+    attn_fwd_kernel<128><<<num_tiles * Hq, kAttnThreads, smem, st>>>(tq, tk, tv, (__nv_bfloat16*)o, lse, tiles, Hq, Hkv, Tq,
+                                                                     o_stride, sl2, causal, status);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { if (set_smem(attn_fwd_kernel<64>, smem)) return -2; cfg = true; }
+    attn_fwd_kernel<64><<<num_tiles * Hq, kAttnThreads, smem, st>>>(tq, tk, tv, (__nv_bfloat16*)o, lse, tiles, Hq, Hkv, Tq,
+                                                                    o_stride, sl2, causal, status);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                             float* delta, void* dq, void* dk, void* dv, const int* q_tiles, int num_q_tiles,
+                             const int* k_tiles, int num_k_tiles, int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride,
+                             int64_t k_stride, int64_t v_stride, int64_t o_stride, int64_t do_stride, int64_t dq_stride,
+                             int64_t dk_stride, int64_t dv_stride, float scale, int causal, int* status, cudaStream_t st) {
+  if (Hq <= 0 || Tq <= 0) return 0;
+  if ((HD != 64 && HD != 128) || Hq % Hkv || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (do_stride & 7) ||
+      (dq_stride & 7) || (dk_stride & 7) || (dv_stride & 7))
+    return -10;
+  {
+    const int64_t items = (int64_t)Tq * Hq;
+    attn_delta_kernel<<<(int)((items + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, o_stride, (const __nv_bfloat16*)dout,
+                                                              do_stride, delta, Tq, Hq, HD);
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride) ||
+      make_thd_map(&tv, v, Tk, Hkv, HD, v_stride) || make_thd_map(&tdo, dout, Tq, Hq, HD, do_stride))
+    return -11;
+  const int smem_kv = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 2048 + 1024 + 256;
+  const int smem_q = 6 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 256;
+  if (HD == 128) {
+    static bool cfg = false;
+    if (!cfg) {
+      if (set_smem(attn_bwd_dkv_kernel<128>, smem_kv) || set_smem(attn_bwd_dq_kernel<128>, smem_q)) return -2;
+      cfg = true;
+    }
+    if (num_k_tiles > 0)
+      attn_bwd_dkv_kernel<128><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
+          tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
+          causal, status);
+    if (num_q_tiles > 0)
+      attn_bwd_dq_kernel<128><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
+                                                                              q_tiles, Hq, Hkv, Tq, dq_stride, scale, causal,
+                                                                              status);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      if (set_smem(attn_bwd_dkv_kernel<64>, smem_kv) || set_smem(attn_bwd_dq_kernel<64>, smem_q)) return -2;
+      cfg = true;
+    }
+    if (num_k_tiles > 0)
+      attn_bwd_dkv_kernel<64><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
+          tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
+          causal, status);
+    if (num_q_tiles > 0)
+      attn_bwd_dq_kernel<64><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
+                                                                             q_tiles, Hq, Hkv, Tq, dq_stride, scale, causal,
+                                                                             status);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,329 @@
+// Python bindings: thin tensor -> pointer adapters over the C entry points in kernels.h. All checks that can be
+// done on the host (dtype, device, contiguity, alignment) are done here so the kernels can assume them.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+}
+inline void check_rc(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+
+Tensor& status_word() {
+  static Tensor s;
+  if (!s.defined()) s = torch::zeros({8}, torch::dtype(torch::kInt32).device(torch::kCUDA));
+  return s;
+}
+inline int* status_ptr() { return status_word().data_ptr<int>(); }
+
+// Row-major 2-D view description of a tensor whose last dim is contiguous.
+struct Mat {
+  const void* ptr;
+  int64_t rows, cols, ld;
+};
+inline Mat as_mat(const Tensor& t, const char* name) {
+  check_bf16(t, name);
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, name, " must be 2-D with a contiguous last dim");
+  return Mat{t.data_ptr(), t.size(0), t.size(1), t.stride(0)};
+}
+
+// out[M,N] (+)= op(a) * op(b); layouts as in llmt_gemm_bf16. a_mn / b_mn say that the stored matrix is [K][M] / [K][N].
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, bool accumulate, int64_t max_ctas) {
+  c10::cuda::CUDAGuard guard(a.device());
+  const Mat A = as_mat(a, "a"), B = as_mat(b, "b");
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1, "out must be 2-D CUDA with contiguous last dim");
+  const bool f32 = out.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || out.scalar_type() == at::kBFloat16, "out must be float32 or bfloat16");
+  const int64_t M = a_mn ? A.cols : A.rows, K = a_mn ? A.rows : A.cols;
+  const int64_t N = b_mn ? B.cols : B.rows, Kb = b_mn ? B.rows : B.cols;
+  TORCH_CHECK(K == Kb, "inner dimensions differ: ", K, " vs ", Kb);
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N, "out has the wrong shape");
+  check_rc(llmt_gemm_bf16(A.ptr, B.ptr, out.data_ptr(), (int)M, (int)N, (int)K, A.ld, B.ld, out.stride(0), a_mn, b_mn, f32,
+                          accumulate, status_ptr(), (int)max_ctas, cur_stream()),
+           "llmt_gemm_bf16");
+}
+
+void grouped_gemm(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& seg_offsets, bool b_mn) {
+  c10::cuda::CUDAGuard guard(a.device());
+  const Mat A = as_mat(a, "a");
+  check_bf16(b, "b");
+  check_bf16(out, "out");
+  TORCH_CHECK(b.dim() == 3 && b.is_contiguous(), "b must be contiguous [G, N, K] or [G, K, N]");
+  TORCH_CHECK(seg_offsets.is_cuda() && seg_offsets.scalar_type() == at::kInt && seg_offsets.is_contiguous());
+  const int G = (int)b.size(0);
+  TORCH_CHECK(seg_offsets.numel() == G + 1);
+  const int64_t N = b_mn ? b.size(2) : b.size(1), K = b_mn ? b.size(1) : b.size(2);
+  TORCH_CHECK(A.cols == K && out.size(0) == A.rows && out.size(1) == N && out.stride(1) == 1);
+  check_rc(llmt_grouped_gemm_bf16(A.ptr, b.data_ptr(), out.data_ptr(), seg_offsets.data_ptr<int>(), G, (int)A.rows, (int)N,
+                                  (int)K, A.ld, out.stride(0), b_mn, 0, status_ptr(), cur_stream()),
+           "llmt_grouped_gemm_bf16");
+}
+
+// out[G, M, N] (+)= a_g^T b_g ; a [rows, M], b [rows, N]
+void grouped_wgrad(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& seg_offsets, bool accumulate) {
+  c10::cuda::CUDAGuard guard(a.device());
+  const Mat A = as_mat(a, "a"), B = as_mat(b, "b");
+  TORCH_CHECK(out.dim() == 3 && out.is_contiguous() && out.is_cuda());
+  const bool f32 = out.scalar_type() == at::kFloat;
+  const int G = (int)out.size(0);
+  TORCH_CHECK(seg_offsets.numel() == G + 1 && A.rows == B.rows && out.size(1) == A.cols && out.size(2) == B.cols);
+  check_rc(llmt_grouped_wgrad_bf16(A.ptr, B.ptr, out.data_ptr(), seg_offsets.data_ptr<int>(), G, (int)A.rows, (int)A.cols,
+                                   (int)B.cols, A.ld, B.ld, f32, accumulate, status_ptr(), cur_stream()),
+           "llmt_grouped_wgrad_bf16");
+}
+
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& res, const Tensor& w, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  const int64_t D = x.size(-1), T = x.numel() / D;
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({T}, x.options().dtype(torch::kFloat));
+  Tensor s;
+  const void* rp = nullptr;
+  void* sp = nullptr;
+  if (res.has_value()) {
+    check_bf16(*res, "res");
+    TORCH_CHECK(res->is_contiguous() && res->numel() == x.numel());
+    s = torch::empty_like(x);
+    rp = res->data_ptr();
+    sp = s.data_ptr();
+  }
+  check_rc(llmt_rmsnorm_fwd(x.data_ptr(), rp, w.data_ptr(), y.data_ptr(), sp, rstd.data_ptr<float>(), (int)T, (int)D,
+                            (float)eps, cur_stream()),
+           "llmt_rmsnorm_fwd");
+  if (res.has_value()) return {y, rstd, s};
+  return {y, rstd};
+}
+
+// Returns (dx, dw fp32 [D]). `x` is the tensor that was normalised (the sum when a residual was added).
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                const c10::optional<Tensor>& dres) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_bf16(dy, "dy");
+  check_bf16(x, "x");
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous());
+  const int64_t D = x.size(-1), T = x.numel() / D;
+  Tensor dx = torch::empty_like(x);
+  Tensor dw = torch::empty({D}, x.options().dtype(torch::kFloat));
+  Tensor part = torch::empty({llmt_rmsnorm_bwd_partials((int)T), D}, x.options().dtype(torch::kFloat));
+  const void* dr = nullptr;
+  if (dres.has_value()) {
+    check_bf16(*dres, "dres");
+    TORCH_CHECK(dres->is_contiguous());
+    dr = dres->data_ptr();
+  }
+  check_rc(llmt_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(),
+                            part.data_ptr<float>(), dw.data_ptr<float>(), nullptr, 0, (int)T, (int)D, cur_stream()),
+           "llmt_rmsnorm_bwd");
+  return {dx, dw};
+}
+
+// x [T, H, HD] with arbitrary token stride (stride(1) == HD, stride(2) == 1). w may be undefined (no norm).
+std::vector<Tensor> qk_norm_rope_fwd(const Tensor& x, const c10::optional<Tensor>& w, const Tensor& cosb, const Tensor& sinb,
+                                     double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "x must be [T, H, HD] with packed heads");
+  TORCH_CHECK(cosb.scalar_type() == at::kFloat && sinb.scalar_type() == at::kFloat && cosb.is_contiguous() && sinb.is_contiguous());
+  const int T = (int)x.size(0), H = (int)x.size(1), HD = (int)x.size(2);
+  TORCH_CHECK(cosb.size(0) == T && cosb.size(1) == HD / 2);
+  Tensor y = torch::empty({T, H, HD}, x.options());
+  Tensor rstd = torch::empty({(int64_t)T * H}, x.options().dtype(torch::kFloat));
+  const void* wp = w.has_value() ? w->data_ptr() : nullptr;
+  check_rc(llmt_qk_norm_rope_fwd(x.data_ptr(), x.stride(0), wp, cosb.data_ptr<float>(), sinb.data_ptr<float>(), y.data_ptr(),
+                                 y.stride(0), rstd.data_ptr<float>(), T, H, HD, (float)eps, cur_stream()),
+           "llmt_qk_norm_rope_fwd");
+  return {y, rstd};
+}
+
+std::vector<Tensor> qk_norm_rope_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& w, const Tensor& cosb,
+                                     const Tensor& sinb, const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_bf16(dy, "dy");
+  TORCH_CHECK(dy.dim() == 3 && dy.stride(2) == 1 && dy.stride(1) == dy.size(2));
+  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2));
+  const int T = (int)x.size(0), H = (int)x.size(1), HD = (int)x.size(2);
+  Tensor dx = torch::empty({T, H, HD}, x.options());
+  Tensor dw, part;
+  const void* wp = nullptr;
+  float *pp = nullptr, *dwp = nullptr;
+  if (w.has_value()) {
+    wp = w->data_ptr();
+    dw = torch::empty({HD}, x.options().dtype(torch::kFloat));
+    part = torch::empty({llmt_qk_norm_rope_bwd_partials(T, H), HD}, x.options().dtype(torch::kFloat));
+    pp = part.data_ptr<float>();
+    dwp = dw.data_ptr<float>();
+  }
+  check_rc(llmt_qk_norm_rope_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), wp, cosb.data_ptr<float>(),
+                                 sinb.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(), dx.stride(0), pp, dwp, nullptr,
+                                 0, T, H, HD, cur_stream()),
+           "llmt_qk_norm_rope_bwd");
+  if (w.has_value()) return {dx, dw};
+  return {dx};
+}
+
+inline int64_t row_stride_2d(const Tensor& t) {
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, "expected a 2-D tensor with a contiguous last dim");
+  return t.stride(0);
+}
+
+Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
+  c10::cuda::CUDAGuard guard(gate.device());
+  check_bf16(gate, "gate");
+  check_bf16(up, "up");
+  TORCH_CHECK(row_stride_2d(gate) == row_stride_2d(up) && gate.sizes() == up.sizes());
+  Tensor out = torch::empty({gate.size(0), gate.size(1)}, gate.options());
+  check_rc(llmt_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.size(0), (int)gate.size(1), gate.stride(0),
+                           out.stride(0), cur_stream()),
+           "llmt_swiglu_fwd");
+  return out;
+}
+
+// dgate/dup are written into `dgate_out` / `dup_out` (same row stride), which lets them be the two halves of one buffer.
+void swiglu_bwd(const Tensor& dout, const Tensor& gate, const Tensor& up, Tensor& dgate_out, Tensor& dup_out) {
+  c10::cuda::CUDAGuard guard(gate.device());
+  check_bf16(dout, "dout");
+  TORCH_CHECK(row_stride_2d(gate) == row_stride_2d(up) && row_stride_2d(dgate_out) == row_stride_2d(dup_out));
+  check_rc(llmt_swiglu_bwd(dout.data_ptr(), gate.data_ptr(), up.data_ptr(), dgate_out.data_ptr(), dup_out.data_ptr(),
+                           gate.size(0), (int)gate.size(1), gate.stride(0), row_stride_2d(dout), dgate_out.stride(0),
+                           cur_stream()),
+           "llmt_swiglu_bwd");
+}
+
+// In place: logits become d(sum CE)/d(logits) * grad_scale. Returns (row_loss fp32 [rows], row_lse fp32 [rows]).
+std::vector<Tensor> ce_fwd_bwd(Tensor& logits, const Tensor& labels, double grad_scale, const c10::optional<Tensor>& scale_t,
+                               int64_t ignore_index, bool write_grad) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_bf16(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0));
+  const int rows = (int)logits.size(0), V = (int)logits.size(1);
+  Tensor loss = torch::empty({rows}, logits.options().dtype(torch::kFloat));
+  Tensor lse = torch::empty({rows}, logits.options().dtype(torch::kFloat));
+  const float* sp = scale_t.has_value() ? scale_t->data_ptr<float>() : nullptr;
+  check_rc(llmt_ce_fwd_bwd(logits.data_ptr(), labels.data_ptr<int64_t>(), loss.data_ptr<float>(), lse.data_ptr<float>(), rows,
+                           V, logits.stride(0), sp, (float)grad_scale, (int)ignore_index, write_grad, cur_stream()),
+           "llmt_ce_fwd_bwd");
+  return {loss, lse};
+}
+
+void adamw(Tensor& p32, const c10::optional<Tensor>& p16, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1,
+           double b2, double eps, double wd, int64_t step, const c10::optional<Tensor>& clip_coef, double grad_scale,
+           bool decoupled) {
+  c10::cuda::CUDAGuard guard(p32.device());
+  TORCH_CHECK(p32.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(p32.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous());
+  const int64_t n = p32.numel();
+  TORCH_CHECK(g.numel() == n && m.numel() == n && v.numel() == n);
+  const bool gb = g.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(gb || g.scalar_type() == at::kFloat, "grad must be bf16 or fp32");
+  void* p16p = nullptr;
+  if (p16.has_value()) {
+    check_bf16(*p16, "p16");
+    TORCH_CHECK(p16->is_contiguous() && p16->numel() == n);
+    p16p = p16->data_ptr();
+  }
+  const float* cc = clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr;
+  check_rc(llmt_adamw(p32.data_ptr<float>(), p16p, g.data_ptr(), gb, m.data_ptr<float>(), v.data_ptr<float>(), n, (float)lr,
+                      (float)b1, (float)b2, (float)eps, (float)wd, (int)step, cc, (float)grad_scale, decoupled, cur_stream()),
+           "llmt_adamw");
+}
+
+// out[0] (+)= sum(x^2), deterministic. scratch: fp32 >= sqnorm_scratch_floats().
+void sqnorm(const Tensor& x, Tensor& scratch, Tensor& out, bool accumulate) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && scratch.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat);
+  TORCH_CHECK(scratch.numel() >= llmt_sqnorm_scratch_floats());
+  const bool b = x.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(b || x.scalar_type() == at::kFloat);
+  check_rc(llmt_sqnorm(x.data_ptr(), b, x.numel(), scratch.data_ptr<float>(), out.data_ptr<float>(), accumulate, cur_stream()),
+           "llmt_sqnorm");
+}
+int64_t sqnorm_scratch_floats() { return llmt_sqnorm_scratch_floats(); }
+
+void clip_coef(const Tensor& total_sq, double max_norm, Tensor& coef, Tensor& norm_out, Tensor& finite) {
+  c10::cuda::CUDAGuard guard(total_sq.device());
+  check_rc(llmt_clip_coef(total_sq.data_ptr<float>(), (float)max_norm, coef.data_ptr<float>(), norm_out.data_ptr<float>(),
+                          finite.data_ptr<int>(), cur_stream()),
+           "llmt_clip_coef");
+}
+
+std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tiles, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16(q, "q"); check_bf16(k, "k"); check_bf16(v, "v");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3);
+  TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == q.size(2) && k.stride(2) == 1 && k.stride(1) == k.size(2) &&
+              v.stride(2) == 1 && v.stride(1) == v.size(2), "q/k/v need packed heads [T, H, HD]");
+  TORCH_CHECK(tiles.is_cuda() && tiles.scalar_type() == at::kInt && tiles.is_contiguous() && tiles.size(1) == 8);
+  const int Tq = (int)q.size(0), Hq = (int)q.size(1), HD = (int)q.size(2), Tk = (int)k.size(0), Hkv = (int)k.size(1);
+  Tensor o = torch::empty({Tq, Hq, HD}, q.options());
+  Tensor lse = torch::empty({Hq, Tq}, q.options().dtype(torch::kFloat));
+  check_rc(llmt_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), tiles.data_ptr<int>(),
+                         (int)tiles.size(0), Tq, Tk, Hq, Hkv, HD, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
+                         (float)scale, causal, status_ptr(), cur_stream()),
+           "llmt_attn_fwd");
+  return {o, lse};
+}
+
+std::vector<Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& dout,
+                             const Tensor& lse, const Tensor& q_tiles, const Tensor& k_tiles, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16(dout, "dout");
+  TORCH_CHECK(dout.dim() == 3 && dout.stride(2) == 1 && dout.stride(1) == dout.size(2) && o.is_contiguous());
+  const int Tq = (int)q.size(0), Hq = (int)q.size(1), HD = (int)q.size(2), Tk = (int)k.size(0), Hkv = (int)k.size(1);
+  Tensor dq = torch::empty({Tq, Hq, HD}, q.options());
+  Tensor dk = torch::empty({Tk, Hkv, HD}, k.options());
+  Tensor dv = torch::empty({Tk, Hkv, HD}, v.options());
+  Tensor delta = torch::empty({Hq, Tq}, q.options().dtype(torch::kFloat));
+  check_rc(llmt_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(),
+                         delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), q_tiles.data_ptr<int>(),
+                         (int)q_tiles.size(0), k_tiles.data_ptr<int>(), (int)k_tiles.size(0), Tq, Tk, Hq, Hkv, HD, q.stride(0),
+                         k.stride(0), v.stride(0), o.stride(0), dout.stride(0), dq.stride(0), dk.stride(0), dv.stride(0),
+                         (float)scale, causal, status_ptr(), cur_stream()),
+           "llmt_attn_bwd");
+  return {dq, dk, dv};
+}
+
+// Reads the status word (synchronises the current stream) and clears it. Returns {code, site, block, extra}.
+std::vector<int64_t> read_status(bool clear) {
+  Tensor h = status_word().cpu();
+  std::vector<int64_t> r{h[0].item<int64_t>(), h[1].item<int64_t>(), h[2].item<int64_t>(), h[3].item<int64_t>()};
+  if (clear && r[0] != 0) status_word().zero_();
+  return r;
+}
+Tensor status_tensor() { return status_word(); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn"), py::arg("b_mn"),
+        py::arg("accumulate") = false, py::arg("max_ctas") = 0);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("grouped_wgrad", &grouped_wgrad);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
+  m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("adamw", &adamw);
+  m.def("sqnorm", &sqnorm);
+  m.def("sqnorm_scratch_floats", &sqnorm_scratch_floats);
+  m.def("clip_coef", &clip_coef);
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
+  m.def("read_status", &read_status, py::arg("clear") = true);
+  m.def("status_tensor", &status_tensor);
+}

@@ -1,0 +1,615 @@
+// Memory-bound training kernels for sm_100a: RMSNorm (with residual add) fwd/bwd, per-head QK-norm + RoPE
+// fwd/bwd, SwiGLU fwd/bwd, row-wise cross-entropy with in-place gradient, fused AdamW on flat shards,
+// deterministic squared-norm. bf16 storage, fp32 math, 16-byte vector accesses.
+// (reference call sites: llmtuner/models/qwen/ops.py:80-131,503; llmtuner/components/loss.py:35-70;
+//  llmtuner/components/optimizer/optimizer.py:62-106; llmtuner/accelerator/collectives.py:290-558)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace llmt {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(b[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm
+// y = (x [+ res]) * rsqrt(mean((x+res)^2) + eps) * w ; optionally writes s = x + res (the new residual stream).
+template <int NV>  // each thread owns NV groups of 8 columns: col = (v * kRowThreads + tid) * 8
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                  const __nv_bfloat16* __restrict__ res,
+                                                                  const __nv_bfloat16* __restrict__ w,
+                                                                  __nv_bfloat16* __restrict__ y,
+                                                                  __nv_bfloat16* __restrict__ sum_out,
+                                                                  float* __restrict__ rstd, int T, int D, float eps) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    float v[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * kRowThreads + threadIdx.x) * 8;
+      if (col < D) {
+        load8(x + (int64_t)row * D + col, v[i]);
+        if (res != nullptr) {
+          float r[8];
+          load8(res + (int64_t)row * D + col, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] + r[j]));
+          if (sum_out != nullptr) store8(sum_out + (int64_t)row * D + col, v[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float r = rsqrtf(ss / (float)D + eps);
+    if (threadIdx.x == 0 && rstd != nullptr) rstd[row] = r;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * kRowThreads + threadIdx.x) * 8;
+      if (col < D) {
+        float wv[8], o[8];
+        load8(w + col, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * wv[j];
+        store8(y + (int64_t)row * D + col, o);
+      }
+    }
+  }
+}
+
+// dx = r * (g - x * r^2 * mean(g * x)) [+ dres], g = dy * w ; dw partial per block = sum_rows dy * x * r.
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                  const __nv_bfloat16* __restrict__ x,
+                                                                  const __nv_bfloat16* __restrict__ w,
+                                                                  const float* __restrict__ rstd,
+                                                                  const __nv_bfloat16* __restrict__ dres,
+                                                                  __nv_bfloat16* __restrict__ dx,
+                                                                  float* __restrict__ dw_partial, int T, int D) {
+  __shared__ float red[32];
+  float dw[NV][8];
+  float wv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (i * kRowThreads + threadIdx.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dw[i][j] = 0.f; wv[i][j] = 0.f; }
+    if (col < D) load8(w + col, wv[i]);
+  }
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    float xv[NV][8], g[NV][8];
+    const float r = rstd[row];
+    float c = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * kRowThreads + threadIdx.x) * 8;
+      if (col < D) {
+        float d[8];
+        load8(x + (int64_t)row * D + col, xv[i]);
+        load8(dy + (int64_t)row * D + col, d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          g[i][j] = d[j] * wv[i][j];
+          c += g[i][j] * xv[i][j];
+          dw[i][j] += d[j] * xv[i][j] * r;
+        }
+      }
+    }
+    c = block_sum(c, red);
+    const float k = r * r * r * c / (float)D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * kRowThreads + threadIdx.x) * 8;
+      if (col < D) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = r * g[i][j] - xv[i][j] * k;
+        if (dres != nullptr) {
+          float e[8];
+          load8(dres + (int64_t)row * D + col, e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        store8(dx + (int64_t)row * D + col, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (i * kRowThreads + threadIdx.x) * 8;
+    if (col < D) {
+      float* p = dw_partial + (int64_t)blockIdx.x * D + col;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) p[j] = dw[i][j];
+    }
+  }
+}
+
+// out[c] (+)= sum_p partial[p][c]
+__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out_f32,
+                              __nv_bfloat16* __restrict__ out_bf16, int P, int D, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += partial[(int64_t)p * D + c];
+  if (out_f32 != nullptr) out_f32[c] = accumulate ? out_f32[c] + s : s;
+  if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16_rn(accumulate ? __bfloat162float(out_bf16[c]) + s : s);
+}
+
+// ------------------------------------------------------------------------------------------ QK-norm + RoPE
+// One warp per (token, head). x rows are `stride` elements apart per token and HD per head. HD = 64 * P.
+// Forward: n = x * rsqrt(mean x^2 + eps) * w (skipped when w == nullptr), then half rotation with cos/sin [T, HD/2].
+template <int P>
+__global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t tok_stride,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               const float* __restrict__ cosb,
+                                                               const float* __restrict__ sinb,
+                                                               __nv_bfloat16* __restrict__ y, int64_t y_tok_stride,
+                                                               float* __restrict__ rstd, int T, int H, float eps) {
+  constexpr int HD = 64 * P;
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (int64_t)T * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD;
+  float a[2 * P], b[2 * P];  // a: first half elements, b: partner elements in the second half
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    const int c = (i * 32 + lane) * 2;
+    const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + c));
+    const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + HD / 2 + c));
+    a[2 * i] = fa.x; a[2 * i + 1] = fa.y; b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
+    ss += fa.x * fa.x + fa.y * fa.y + fb.x * fb.x + fb.y * fb.y;
+  }
+  float r = 1.f;
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    r = rsqrtf(ss / (float)HD + eps);
+    if (lane == 0 && rstd != nullptr) rstd[item] = r;
+  }
+  __nv_bfloat16* py = y + (int64_t)t * y_tok_stride + (int64_t)h * HD;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    const int c = (i * 32 + lane) * 2;
+    float wa0 = 1.f, wa1 = 1.f, wb0 = 1.f, wb1 = 1.f;
+    if (w != nullptr) {
+      const float2 fwa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + c));
+      const float2 fwb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + HD / 2 + c));
+      wa0 = fwa.x; wa1 = fwa.y; wb0 = fwb.x; wb1 = fwb.y;
+    }
+    const float2 cs = *reinterpret_cast<const float2*>(cosb + (int64_t)t * (HD / 2) + c);
+    const float2 sn = *reinterpret_cast<const float2*>(sinb + (int64_t)t * (HD / 2) + c);
+    const float n1x = a[2 * i] * r * wa0, n1y = a[2 * i + 1] * r * wa1;
+    const float n2x = b[2 * i] * r * wb0, n2y = b[2 * i + 1] * r * wb1;
+    *reinterpret_cast<__nv_bfloat162*>(py + c) = __floats2bfloat162_rn(n1x * cs.x - n2x * sn.x, n1y * cs.y - n2y * sn.y);
+    *reinterpret_cast<__nv_bfloat162*>(py + HD / 2 + c) = __floats2bfloat162_rn(n2x * cs.x + n1x * sn.x, n2y * cs.y + n1y * sn.y);
+  }
+}
+
+// Backward: un-rotate dy (rotation by -angle), then RMSNorm backward per head. dw partial is accumulated per block
+// in shared memory over its (token, head) items and written to dw_partial[blockIdx.x][HD].
+template <int P>
+__global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, int64_t dy_tok_stride,
+                                                               const __nv_bfloat16* __restrict__ x, int64_t tok_stride,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               const float* __restrict__ cosb,
+                                                               const float* __restrict__ sinb,
+                                                               const float* __restrict__ rstd,
+                                                               __nv_bfloat16* __restrict__ dx, int64_t dx_tok_stride,
+                                                               float* __restrict__ dw_partial, int T, int H) {
+  constexpr int HD = 64 * P;
+  __shared__ float sdw[HD];
+  for (int i = threadIdx.x; i < HD; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  float dwa[2 * P], dwb[2 * P];
+#pragma unroll
+  for (int i = 0; i < 2 * P; ++i) { dwa[i] = 0.f; dwb[i] = 0.f; }
+  for (int64_t item = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); item < (int64_t)T * H; item += (int64_t)gridDim.x * wpb) {
+    const int t = (int)(item / H), h = (int)(item % H);
+    const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD;
+    const __nv_bfloat16* pd = dy + (int64_t)t * dy_tok_stride + (int64_t)h * HD;
+    __nv_bfloat16* po = dx + (int64_t)t * dx_tok_stride + (int64_t)h * HD;
+    float xa[2 * P], xb[2 * P], ga[2 * P], gb[2 * P];
+    const float r = (w != nullptr) ? rstd[item] : 1.f;
+    float c = 0.f;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const int col = (i * 32 + lane) * 2;
+      const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + col));
+      const float2 d2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + HD / 2 + col));
+      const float2 cs = *reinterpret_cast<const float2*>(cosb + (int64_t)t * (HD / 2) + col);
+      const float2 sn = *reinterpret_cast<const float2*>(sinb + (int64_t)t * (HD / 2) + col);
+      // y1 = n1 c - n2 s ; y2 = n2 c + n1 s  =>  dn1 = d1 c + d2 s ; dn2 = d2 c - d1 s
+      float dn1x = d1.x * cs.x + d2.x * sn.x, dn1y = d1.y * cs.y + d2.y * sn.y;
+      float dn2x = d2.x * cs.x - d1.x * sn.x, dn2y = d2.y * cs.y - d1.y * sn.y;
+      if (w != nullptr) {
+        const float2 fxa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + col));
+        const float2 fxb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + HD / 2 + col));
+        const float2 fwa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + col));
+        const float2 fwb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + HD / 2 + col));
+        xa[2 * i] = fxa.x; xa[2 * i + 1] = fxa.y; xb[2 * i] = fxb.x; xb[2 * i + 1] = fxb.y;
+        dwa[2 * i] += dn1x * fxa.x * r; dwa[2 * i + 1] += dn1y * fxa.y * r;
+        dwb[2 * i] += dn2x * fxb.x * r; dwb[2 * i + 1] += dn2y * fxb.y * r;
+        dn1x *= fwa.x; dn1y *= fwa.y; dn2x *= fwb.x; dn2y *= fwb.y;
+        c += dn1x * fxa.x + dn1y * fxa.y + dn2x * fxb.x + dn2y * fxb.y;
+      }
+      ga[2 * i] = dn1x; ga[2 * i + 1] = dn1y; gb[2 * i] = dn2x; gb[2 * i + 1] = dn2y;
+    }
+    float k = 0.f;
+    if (w != nullptr) {
+      c = warp_sum(c);
+      k = r * r * r * c / (float)HD;
+    }
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const int col = (i * 32 + lane) * 2;
+      float o1x = ga[2 * i], o1y = ga[2 * i + 1], o2x = gb[2 * i], o2y = gb[2 * i + 1];
+      if (w != nullptr) {
+        o1x = r * o1x - xa[2 * i] * k; o1y = r * o1y - xa[2 * i + 1] * k;
+        o2x = r * o2x - xb[2 * i] * k; o2y = r * o2y - xb[2 * i + 1] * k;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(po + col) = __floats2bfloat162_rn(o1x, o1y);
+      *reinterpret_cast<__nv_bfloat162*>(po + HD / 2 + col) = __floats2bfloat162_rn(o2x, o2y);
+    }
+  }
+  if (w != nullptr && dw_partial != nullptr) {
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const int col = (i * 32 + lane) * 2;
+      atomicAdd(&sdw[col], dwa[2 * i]);
+      atomicAdd(&sdw[col + 1], dwa[2 * i + 1]);
+      atomicAdd(&sdw[HD / 2 + col], dwb[2 * i]);
+      atomicAdd(&sdw[HD / 2 + col + 1], dwb[2 * i + 1]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) dw_partial[(int64_t)blockIdx.x * HD + i] = sdw[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ SwiGLU
+// Rows of `gate` and `up` may be strided (views into one [T, 2F] buffer); out/dgate/dup likewise.
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                  __nv_bfloat16* __restrict__ out, int64_t T, int F, int64_t ld_in, int64_t ld_out) {
+  const int64_t nvec = T * (F / 8);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / (F / 8);
+    const int col = (int)(i % (F / 8)) * 8;
+    float g[8], u[8], o[8];
+    load8(gate + row * ld_in + col, g);
+    load8(up + row * ld_in + col, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(out + row * ld_out + col, o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gate,
+                                  const __nv_bfloat16* __restrict__ up, __nv_bfloat16* __restrict__ dgate,
+                                  __nv_bfloat16* __restrict__ dup, int64_t T, int F, int64_t ld_in, int64_t ld_dout,
+                                  int64_t ld_dg) {
+  const int64_t nvec = T * (F / 8);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / (F / 8);
+    const int col = (int)(i % (F / 8)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gate + row * ld_in + col, g);
+    load8(up + row * ld_in + col, u);
+    load8(dout + row * ld_dout + col, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * s;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * (s + silu * (1.f - s));
+    }
+    store8(dgate + row * ld_dg + col, dg);
+    store8(dup + row * ld_dg + col, du);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ cross-entropy
+// One CTA per row of bf16 logits [rows, V] (row stride ld). Pass 1: online max / sum-exp. Pass 2: overwrite the
+// logits with d(loss_sum)/d(logit) * grad_scale = (softmax - onehot) * grad_scale. Rows whose label is
+// ignore_index get zero gradient and no loss. Row losses go to `row_loss` (fp32); the caller sums them
+// (deterministic), lse goes to `row_lse` when given.
+__global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ labels,
+                                                         float* __restrict__ row_loss, float* __restrict__ row_lse,
+                                                         int V, int64_t ld, const float* __restrict__ grad_scale_ptr,
+                                                         float grad_scale, int ignore_index, int write_grad) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  __nv_bfloat16* p = logits + row * ld;
+  const int64_t label = labels[row];
+  const bool valid = (label != ignore_index) && label >= 0 && label < V;
+  float m = -INFINITY, s = 0.f;
+  const int nvec = V / 8;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float f[8];
+    load8(p + i * 8, f);
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    const float nm = fmaxf(m, lm);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
+    s = s * __expf(m - nm) + acc;
+    m = nm;
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    const float f = __bfloat162float(p[i]);
+    const float nm = fmaxf(m, f);
+    s = s * __expf(m - nm) + __expf(f - nm);
+    m = nm;
+  }
+  const float gm = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum(s, red);
+  const float lse = gm + logf(gs);
+  if (threadIdx.x == 0) {
+    if (row_lse != nullptr) row_lse[row] = lse;
+    row_loss[row] = valid ? (lse - __bfloat162float(p[label])) : 0.f;
+  }
+  if (!write_grad) return;
+  __syncthreads();  // the label logit was read above before anyone overwrites it
+  const float gsc = valid ? grad_scale * (grad_scale_ptr != nullptr ? *grad_scale_ptr : 1.f) : 0.f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float f[8];
+    load8(p + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float g = __expf(f[j] - lse);
+      if (i * 8 + j == label) g -= 1.f;
+      f[j] = g * gsc;
+    }
+    store8(p + i * 8, f);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    float g = __expf(__bfloat162float(p[i]) - lse);
+    if (i == label) g -= 1.f;
+    p[i] = __float2bfloat16_rn(g * gsc);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ AdamW on a flat shard
+// p32: fp32 master, m/v: fp32 moments, g: bf16 or fp32 gradient, p16: bf16 working copy (optional).
+// clip_coef (device, optional) multiplies the gradient: it is min(1, max_norm / (norm + 1e-6)) computed on the device.
+template <typename GT>
+__global__ void adamw_kernel(float* __restrict__ p32, __nv_bfloat16* __restrict__ p16, const GT* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v, int64_t n, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ clip_coef,
+                             float grad_scale, int decoupled) {
+  const float gs = grad_scale * (clip_coef != nullptr ? *clip_coef : 1.f);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float gr;
+    if constexpr (sizeof(GT) == 2) gr = __bfloat162float(g[i]) * gs;
+    else gr = g[i] * gs;
+    float p = p32[i];
+    if (!decoupled) gr += wd * p;
+    const float mi = b1 * m[i] + (1.f - b1) * gr;
+    const float vi = b2 * v[i] + (1.f - b2) * gr * gr;
+    m[i] = mi;
+    v[i] = vi;
+    if (decoupled) p *= (1.f - lr * wd);
+    p -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    p32[i] = p;
+    if (p16 != nullptr) p16[i] = __float2bfloat16_rn(p);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ squared norm
+// Deterministic two-stage sum of squares: stage 1 writes one partial per block into `scratch`, stage 2 (one
+// block) adds them in index order into out[0] (accumulating when `accumulate`).
+template <typename T>
+__global__ void __launch_bounds__(256) sqnorm_partial_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ scratch) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float f;
+    if constexpr (sizeof(T) == 2) f = __bfloat162float(x[i]);
+    else f = x[i];
+    s += f * f;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) scratch[blockIdx.x] = s;
+}
+__global__ void __launch_bounds__(256) sqnorm_final_kernel(const float* __restrict__ scratch, int nparts,
+                                                           float* __restrict__ out, int accumulate) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += scratch[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + s : s;
+}
+// clip_coef[0] = min(1, max_norm / (sqrt(total_sq[0]) + 1e-6)); norm_out[0] = sqrt(total_sq[0]); finite[0] = isfinite
+__global__ void clip_coef_kernel(const float* __restrict__ total_sq, float max_norm, float* __restrict__ clip_coef,
+                                 float* __restrict__ norm_out, int* __restrict__ finite) {
+  const float n = sqrtf(total_sq[0]);
+  norm_out[0] = n;
+  clip_coef[0] = fminf(1.f, max_norm / (n + 1e-6f));
+  if (finite != nullptr) finite[0] = isfinite(n) ? 1 : 0;
+}
+
+static inline int grid_for(int64_t n, int threads, int per_sm = 8) {
+  int64_t b = (n + threads - 1) / threads;
+  const int64_t cap = (int64_t)148 * per_sm;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace llmt
+
+using namespace llmt;
+
+#define LLMT_CHECK_LAUNCH() return (cudaGetLastError() == cudaSuccess) ? 0 : -3
+
+extern "C" int llmt_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd, int T,
+                                int D, float eps, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D % 8 || D > 8 * kRowThreads * 4) return -10;
+  const int nv = (D + 8 * kRowThreads - 1) / (8 * kRowThreads);
+  const int grid = T < 148 * 8 ? T : 148 * 8;
+  auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)res; auto W = (const __nv_bfloat16*)w;
+  auto Y = (__nv_bfloat16*)y; auto S = (__nv_bfloat16*)sum_out;
+  if (nv == 1) rmsnorm_fwd_kernel<1><<<grid, kRowThreads, 0, st>>>(X, R, W, Y, S, rstd, T, D, eps);
+  else if (nv == 2) rmsnorm_fwd_kernel<2><<<grid, kRowThreads, 0, st>>>(X, R, W, Y, S, rstd, T, D, eps);
+  else rmsnorm_fwd_kernel<4><<<grid, kRowThreads, 0, st>>>(X, R, W, Y, S, rstd, T, D, eps);
+  LLMT_CHECK_LAUNCH();
+}
+
+// dw_partial: fp32 scratch of llmt_rmsnorm_bwd_partials(T) * D floats.
+extern "C" int llmt_rmsnorm_bwd_partials(int T) { return T < 148 * 2 ? (T < 1 ? 1 : T) : 148 * 2; }
+extern "C" int llmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                                float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, int T, int D,
+                                cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D % 8 || D > 8 * kRowThreads * 4) return -10;
+  const int nv = (D + 8 * kRowThreads - 1) / (8 * kRowThreads);
+  const int grid = llmt_rmsnorm_bwd_partials(T);
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
+  auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
+  if (nv == 1) rmsnorm_bwd_kernel<1><<<grid, kRowThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_partial, T, D);
+  else if (nv == 2) rmsnorm_bwd_kernel<2><<<grid, kRowThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_partial, T, D);
+  else rmsnorm_bwd_kernel<4><<<grid, kRowThreads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_partial, T, D);
+  colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, dw_f32, (__nv_bfloat16*)dw_bf16, grid, D, accumulate);
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_qk_norm_rope_fwd(const void* x, int64_t tok_stride, const void* w, const float* cosb, const float* sinb,
+                                     void* y, int64_t y_tok_stride, float* rstd, int T, int H, int HD, float eps,
+                                     cudaStream_t st) {
+  if (T <= 0 || H <= 0) return 0;
+  const int64_t items = (int64_t)T * H;
+  const int grid = (int)((items + 7) / 8);
+  auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w; auto Y = (__nv_bfloat16*)y;
+  if (HD == 64) qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, st>>>(X, tok_stride, W, cosb, sinb, Y, y_tok_stride, rstd, T, H, eps);
+  else if (HD == 128) qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, st>>>(X, tok_stride, W, cosb, sinb, Y, y_tok_stride, rstd, T, H, eps);
+  else if (HD == 256) qk_norm_rope_fwd_kernel<4><<<grid, 256, 0, st>>>(X, tok_stride, W, cosb, sinb, Y, y_tok_stride, rstd, T, H, eps);
+  else return -10;
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_qk_norm_rope_bwd_partials(int T, int H) {
+  const int64_t items = (int64_t)T * H;
+  const int64_t b = (items + 7) / 8;
+  return (int)(b < 1 ? 1 : (b > 148 * 4 ? 148 * 4 : b));
+}
+extern "C" int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, const void* x, int64_t tok_stride, const void* w,
+                                     const float* cosb, const float* sinb, const float* rstd, void* dx,
+                                     int64_t dx_tok_stride, float* dw_partial, float* dw_f32, void* dw_bf16,
+                                     int accumulate, int T, int H, int HD, cudaStream_t st) {
+  if (T <= 0 || H <= 0) return 0;
+  const int grid = llmt_qk_norm_rope_bwd_partials(T, H);
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
+  auto DX = (__nv_bfloat16*)dx;
+  if (HD == 64) qk_norm_rope_bwd_kernel<1><<<grid, 256, 0, st>>>(DY, dy_tok_stride, X, tok_stride, W, cosb, sinb, rstd, DX, dx_tok_stride, dw_partial, T, H);
+  else if (HD == 128) qk_norm_rope_bwd_kernel<2><<<grid, 256, 0, st>>>(DY, dy_tok_stride, X, tok_stride, W, cosb, sinb, rstd, DX, dx_tok_stride, dw_partial, T, H);
+  else if (HD == 256) qk_norm_rope_bwd_kernel<4><<<grid, 256, 0, st>>>(DY, dy_tok_stride, X, tok_stride, W, cosb, sinb, rstd, DX, dx_tok_stride, dw_partial, T, H);
+  else return -10;
+  if (w != nullptr && dw_partial != nullptr)
+    colsum_kernel<<<(HD + 255) / 256, 256, 0, st>>>(dw_partial, dw_f32, (__nv_bfloat16*)dw_bf16, grid, HD, accumulate);
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t T, int F, int64_t ld_in, int64_t ld_out,
+                               cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8 || ld_in % 8 || ld_out % 8) return -10;
+  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up,
+                                                                 (__nv_bfloat16*)out, T, F, ld_in, ld_out);
+  LLMT_CHECK_LAUNCH();
+}
+extern "C" int llmt_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int64_t T, int F,
+                               int64_t ld_in, int64_t ld_dout, int64_t ld_dg, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8 || ld_in % 8 || ld_dout % 8 || ld_dg % 8) return -10;
+  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)gate,
+                                                                 (const __nv_bfloat16*)up, (__nv_bfloat16*)dgate,
+                                                                 (__nv_bfloat16*)dup, T, F, ld_in, ld_dout, ld_dg);
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_ce_fwd_bwd(void* logits, const int64_t* labels, float* row_loss, float* row_lse, int rows, int V,
+                               int64_t ld, const float* grad_scale_ptr, float grad_scale, int ignore_index, int write_grad,
+                               cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (ld % 8) return -10;
+  ce_fwd_bwd_kernel<<<rows, 512, 0, st>>>((__nv_bfloat16*)logits, labels, row_loss, row_lse, V, ld, grad_scale_ptr,
+                                          grad_scale, ignore_index, write_grad);
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_adamw(float* p32, void* p16, const void* g, int g_is_bf16, float* m, float* v, int64_t n, float lr,
+                          float b1, float b2, float eps, float wd, int step, const float* clip_coef, float grad_scale,
+                          int decoupled, cudaStream_t st) {
+  if (n <= 0) return 0;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  const int grid = grid_for(n, 256);
+  if (g_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p32, (__nv_bfloat16*)p16, (const __nv_bfloat16*)g, m, v, n, lr, b1, b2,
+                                                       eps, wd, bc1, bc2, clip_coef, grad_scale, decoupled);
+  else
+    adamw_kernel<float><<<grid, 256, 0, st>>>(p32, (__nv_bfloat16*)p16, (const float*)g, m, v, n, lr, b1, b2, eps, wd, bc1,
+                                               bc2, clip_coef, grad_scale, decoupled);
+  LLMT_CHECK_LAUNCH();
+}
+
+// scratch must hold llmt_sqnorm_scratch_floats() floats.
+extern "C" int llmt_sqnorm_scratch_floats() { return 148 * 8; }
+extern "C" int llmt_sqnorm(const void* x, int is_bf16, int64_t n, float* scratch, float* out, int accumulate,
+                           cudaStream_t st) {
+  if (n <= 0) {
+    if (!accumulate) cudaMemsetAsync(out, 0, sizeof(float), st);
+    return 0;
+  }
+  const int grid = grid_for(n, 256);
+  if (is_bf16) sqnorm_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, n, scratch);
+  else sqnorm_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)x, n, scratch);
+  sqnorm_final_kernel<<<1, 256, 0, st>>>(scratch, grid, out, accumulate);
+  LLMT_CHECK_LAUNCH();
+}
+extern "C" int llmt_clip_coef(const float* total_sq, float max_norm, float* clip_coef, float* norm_out, int* finite,
+                              cudaStream_t st) {
+  clip_coef_kernel<<<1, 1, 0, st>>>(total_sq, max_norm, clip_coef, norm_out, finite);
+  LLMT_CHECK_LAUNCH();
+}

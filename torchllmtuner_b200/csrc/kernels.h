@@ -1,0 +1,62 @@
+// C entry points of the sm_100a kernel library. Every function enqueues work on `stream` and returns 0 on a
+// successful launch, a negative code for a rejected argument or a failed launch. Device-side failures
+// (bounded waits that expired, capacity overflow) are reported through the `status` word, see common.cuh.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- GEMM family (gemm.cu) ----
+int llmt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                   int a_mn, int b_mn, int out_f32, int accumulate, int* status, int max_ctas, cudaStream_t stream);
+int llmt_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* seg_offsets, int num_groups, int M_padded,
+                           int N, int K, int64_t lda, int64_t ldc, int b_mn, int out_f32, int* status,
+                           cudaStream_t stream);
+int llmt_grouped_wgrad_bf16(const void* A, const void* B, void* C, const int* seg_offsets, int num_groups,
+                            int rows_padded, int M, int N, int64_t lda, int64_t ldb, int out_f32, int accumulate,
+                            int* status, cudaStream_t stream);
+
+// ---- memory-bound kernels (elementwise.cu) ----
+int llmt_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd, int T, int D,
+                     float eps, cudaStream_t st);
+int llmt_rmsnorm_bwd_partials(int T);
+int llmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                     float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, int T, int D, cudaStream_t st);
+int llmt_qk_norm_rope_fwd(const void* x, int64_t tok_stride, const void* w, const float* cosb, const float* sinb, void* y,
+                          int64_t y_tok_stride, float* rstd, int T, int H, int HD, float eps, cudaStream_t st);
+int llmt_qk_norm_rope_bwd_partials(int T, int H);
+int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, const void* x, int64_t tok_stride, const void* w,
+                          const float* cosb, const float* sinb, const float* rstd, void* dx, int64_t dx_tok_stride,
+                          float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, int T, int H, int HD,
+                          cudaStream_t st);
+int llmt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t T, int F, int64_t ld_in, int64_t ld_out,
+                    cudaStream_t st);
+int llmt_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int64_t T, int F,
+                    int64_t ld_in, int64_t ld_dout, int64_t ld_dg, cudaStream_t st);
+int llmt_ce_fwd_bwd(void* logits, const int64_t* labels, float* row_loss, float* row_lse, int rows, int V, int64_t ld,
+                    const float* grad_scale_ptr, float grad_scale, int ignore_index, int write_grad, cudaStream_t st);
+int llmt_adamw(float* p32, void* p16, const void* g, int g_is_bf16, float* m, float* v, int64_t n, float lr, float b1,
+               float b2, float eps, float wd, int step, const float* clip_coef, float grad_scale, int decoupled,
+               cudaStream_t st);
+int llmt_sqnorm_scratch_floats();
+int llmt_sqnorm(const void* x, int is_bf16, int64_t n, float* scratch, float* out, int accumulate, cudaStream_t st);
+int llmt_clip_coef(const float* total_sq, float max_norm, float* clip_coef, float* norm_out, int* finite, cudaStream_t st);
+
+// ---- attention (attention.cu) ----
+// q [Tq, Hq, HD], k/v [Tk, Hkv, HD] bf16 with token strides in elements; varlen via cu_seqlens (device int32).
+// tiles: device int32 [num_tiles][4] = {q_row_begin, q_row_end, k_row_begin, k_causal_end_for_first_row}; see attention.cu.
+int llmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* tiles, int num_tiles,
+                  int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                  int64_t o_stride, float scale, int causal, int* status, cudaStream_t st);
+int llmt_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                  float* delta, void* dq, void* dk, void* dv, const int* q_tiles, int num_q_tiles, const int* k_tiles,
+                  int num_k_tiles, int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride,
+                  int64_t v_stride, int64_t o_stride, int64_t do_stride, int64_t dq_stride, int64_t dk_stride,
+                  int64_t dv_stride, float scale, int causal, int* status, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,311 @@
+"""Autograd-aware hot ops. CUDA tensors run the hand-written sm_100a kernels (`csrc/*.cu`); CPU tensors run the
+plain PyTorch statements in `reference.py`, which are also the numerical oracle of the kernel tests.
+There is no library fallback on CUDA: if the extension cannot be loaded the call raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import reference as ref
+from .attn_meta import AttnMeta
+from .cuda_ext import load as _ext
+
+IGNORE_INDEX = ref.IGNORE_INDEX
+
+
+def _use_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def _c(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _2d(t: torch.Tensor) -> torch.Tensor:
+    t = t.reshape(-1, t.shape[-1])
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+# ----------------------------------------------------------------------------------------------- GEMM
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=False, max_ctas=0):
+    """out[M,N] (+)= op(a) @ op(b)^T-style product on the tcgen05 kernel.
+    a_mn=False: a is [M,K]; a_mn=True: a is stored [K,M]. b_mn=False: b is [N,K]; b_mn=True: b is stored [K,N]."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+    _ext().gemm(a, b, out, a_mn, b_mn, accumulate, max_ctas)
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = _2d(x)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        return gemm(x2, w).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _2d(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape)                      # dy [M,N] @ W [N,K]
+        if ctx.needs_input_grad[1]:
+            main = getattr(w, "main_grad", None)
+            if main is not None:                                                   # accumulate straight into the owner's buffer
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=getattr(w, "main_grad_initialized", False))
+                w.main_grad_initialized = True
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)        # dy^T [N,M] @ x [M,K]
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if _use_cuda(x) and x.dtype == torch.bfloat16:
+        return _Linear.apply(x, w)
+    return ref.linear(x, w)
+
+
+# ----------------------------------------------------------------------------------------------- RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        xc = _c(x)
+        y, rstd = _ext().rmsnorm_fwd(xc, None, w, eps)
+        ctx.save_for_backward(xc, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dx, dw = _ext().rmsnorm_bwd(_c(dy), x, w, rstd, None)
+        return dx, dw.to(w.dtype), None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, res, w, eps):
+        y, rstd, s = _ext().rmsnorm_fwd(_c(x), _c(res), w, eps)
+        ctx.save_for_backward(s, w, rstd)
+        return y, s
+
+    @staticmethod
+    def backward(ctx, dy, ds):
+        s, w, rstd = ctx.saved_tensors
+        dsum, dw = _ext().rmsnorm_bwd(_c(dy), s, w, rstd, _c(ds) if ds is not None else None)
+        return dsum, dsum, dw.to(w.dtype), None
+
+
+def rms_norm(x, weight, eps: float):
+    if _use_cuda(x) and x.dtype == torch.bfloat16:
+        return _RMSNorm.apply(x, weight, eps)
+    return ref.rms_norm(x, weight, eps)
+
+
+def add_rms_norm(x, residual, weight, eps: float):
+    """Returns (rms_norm(x + residual), x + residual) with one pass over the data."""
+    if _use_cuda(x) and x.dtype == torch.bfloat16:
+        return _AddRMSNorm.apply(x, residual, weight, eps)
+    return ref.add_rms_norm(x, residual, weight, eps)
+
+
+# ----------------------------------------------------------------------------------------------- QK-norm + RoPE
+rope_tables = ref.rope_tables
+
+
+class _QKNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, cos, sin, eps):
+        y, rstd = _ext().qk_norm_rope_fwd(x, w, cos, sin, eps)
+        ctx.save_for_backward(x, w if w is not None else torch.empty(0), cos, sin, rstd)
+        ctx.has_w = w is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, cos, sin, rstd = ctx.saved_tensors
+        if dy.stride(2) != 1 or dy.stride(1) != dy.shape[2]:
+            dy = dy.contiguous()
+        out = _ext().qk_norm_rope_bwd(dy, x, w if ctx.has_w else None, cos, sin, rstd)
+        return out[0], (out[1].to(w.dtype) if ctx.has_w else None), None, None, None
+
+
+def qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps: float):
+    """q [T,Hq,d], k [T,Hkv,d] (views with packed heads are fine); cos/sin fp32 [T,d/2]."""
+    if _use_cuda(q) and q.dtype == torch.bfloat16:
+        return _QKNormRope.apply(q, q_weight, cos, sin, eps), _QKNormRope.apply(k, k_weight, cos, sin, eps)
+    return ref.qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps)
+
+
+# ----------------------------------------------------------------------------------------------- SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        g2, u2 = _2d(gate), _2d(up)
+        if g2.stride(0) != u2.stride(0):
+            g2, u2 = g2.contiguous(), u2.contiguous()
+        ctx.save_for_backward(g2, u2)
+        ctx.shape = gate.shape
+        return _ext().swiglu_fwd(g2, u2).reshape(gate.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        g2, u2 = ctx.saved_tensors
+        d2 = _2d(dout)
+        both = torch.empty(g2.shape[0], 2 * g2.shape[1], dtype=g2.dtype, device=g2.device)
+        dg, du = both[:, :g2.shape[1]], both[:, g2.shape[1]:]
+        _ext().swiglu_bwd(d2, g2, u2, dg, du)
+        return dg.reshape(ctx.shape), du.reshape(ctx.shape)
+
+
+def swiglu(gate, up):
+    if _use_cuda(gate) and gate.dtype == torch.bfloat16:
+        return _SwiGLU.apply(gate, up)
+    return ref.swiglu(gate, up)
+
+
+# ----------------------------------------------------------------------------------------------- attention
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, meta: AttnMeta, scale):
+        o, lse = _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta, ctx.scale = meta, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        if do.stride(2) != 1 or do.stride(1) != do.shape[2]:
+            do = do.contiguous()
+        dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, ctx.meta.q_tiles, ctx.meta.k_tiles, ctx.scale, ctx.meta.causal)
+        return dq, dk, dv, None, None
+
+
+def attention(q, k, v, meta: AttnMeta, scale: float | None = None):
+    """Packed-row GQA attention; documents and masks come from `meta`. q [Tq,Hq,d], k/v [Tk,Hkv,d] -> [Tq,Hq,d]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if _use_cuda(q) and q.dtype == torch.bfloat16:
+        if meta.q_tiles is None:
+            raise ValueError("AttnMeta was built without device tables; pass device= to AttnMeta.build")
+        return _Attention.apply(q, k, v, meta, scale)
+    out, _ = ref.attention(q, k, v, meta.cu_q, meta.causal, scale, k_cu_seqlens=meta.cu_k, q_offsets=meta.q_offsets)
+    return out
+
+
+def attention_with_lse(q, k, v, meta: AttnMeta, scale: float | None = None):
+    """Forward only, returns (out, lse [Hq, Tq]); used by context-parallel merges."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if _use_cuda(q) and q.dtype == torch.bfloat16:
+        o, lse = _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
+        return o, lse
+    return ref.attention(q, k, v, meta.cu_q, meta.causal, scale, k_cu_seqlens=meta.cu_k, q_offsets=meta.q_offsets)
+
+
+# ----------------------------------------------------------------------------------------------- cross-entropy
+class _LinearCrossEntropy(torch.autograd.Function):
+    """loss_sum = sum_t CE(h_t W^T, y_t), computed chunk by chunk; logits of a chunk are overwritten in place by their
+    gradient, from which dh and dW are accumulated, so that the full [T, V] logits never exist
+    (reference: llmtuner/components/loss.py:246-316)."""
+
+    @staticmethod
+    def forward(ctx, h, w, targets, num_chunks):
+        ext = _ext()
+        T, D = h.shape
+        n = max(1, int(num_chunks))
+        step = -(-T // n)
+        step = -(-step // 128) * 128
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dh = torch.empty_like(h) if need_dh else None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device) if need_dw else None
+        loss = torch.zeros((), dtype=torch.float32, device=h.device)
+        first = True
+        for s in range(0, T, step):
+            hc = h[s:s + step]
+            logits = gemm(hc, w)                                                   # [c, V] bf16
+            row_loss, _ = ext.ce_fwd_bwd(logits, targets[s:s + step].contiguous(), 1.0, None, IGNORE_INDEX,
+                                         need_dh or need_dw)
+            loss += row_loss.sum()
+            if need_dh:
+                gemm(logits, w, b_mn=True, out=dh[s:s + step])                     # dlogits [c,V] @ W [V,D]
+            if need_dw:
+                gemm(logits, hc, a_mn=True, b_mn=True, out=dw, accumulate=not first)  # dlogits^T @ h
+            first = False
+        ctx.save_for_backward(dh if dh is not None else torch.empty(0), dw if dw is not None else torch.empty(0))
+        ctx.flags = (need_dh, need_dw, w.dtype)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw = ctx.saved_tensors
+        need_dh, need_dw, wdt = ctx.flags
+        return ((dh * g.to(dh.dtype)) if need_dh else None, ((dw * g).to(wdt)) if need_dw else None, None, None)
+
+
+def linear_cross_entropy_sum(h, w, targets, num_chunks: int = 1):
+    if _use_cuda(h) and h.dtype == torch.bfloat16:
+        return _LinearCrossEntropy.apply(_2d(h), w, targets.reshape(-1), num_chunks)
+    return ref.linear_cross_entropy_sum(h.reshape(-1, h.shape[-1]), w, targets.reshape(-1), num_chunks)
+
+
+class _CrossEntropySum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets):
+        work = logits.clone()
+        row_loss, _ = _ext().ce_fwd_bwd(work, targets.contiguous(), 1.0, None, IGNORE_INDEX, True)
+        ctx.save_for_backward(work)
+        return row_loss.sum()
+
+    @staticmethod
+    def backward(ctx, g):
+        (d,) = ctx.saved_tensors
+        return d * g.to(d.dtype), None
+
+
+def cross_entropy_sum(logits, targets):
+    if _use_cuda(logits) and logits.dtype == torch.bfloat16:
+        return _CrossEntropySum.apply(_2d(logits), targets.reshape(-1))
+    return ref.cross_entropy_sum(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1))
+
+
+# ----------------------------------------------------------------------------------------------- optimizer pieces
+def adamw_step_(p_master, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+                p_lowp=None, decoupled=True, clip_coef=None):
+    if p_master.is_cuda:
+        _ext().adamw(p_master, p_lowp, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, clip_coef,
+                     grad_scale, decoupled)
+        return
+    gs = grad_scale * (float(clip_coef) if clip_coef is not None else 1.0)
+    ref.adamw_step_(p_master, grad, exp_avg, exp_avg_sq, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                    weight_decay=weight_decay, step=step, grad_scale=gs, p_lowp=p_lowp, decoupled=decoupled)
+
+
+_scratch: dict = {}
+
+
+def sq_norm(tensors, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Deterministic sum of squares over a list of tensors, fp32, on the tensors' device (no host sync)."""
+    tensors = [t for t in tensors if t is not None and t.numel()]
+    if not tensors:
+        return torch.zeros((), dtype=torch.float32) if out is None else out.zero_()
+    dev = tensors[0].device
+    if dev.type != "cuda":
+        v = ref.sq_norm(tensors)
+        return v if out is None else out.copy_(v)
+    ext = _ext()
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    if key not in _scratch:
+        _scratch[key] = torch.empty(ext.sqnorm_scratch_floats(), dtype=torch.float32, device=dev)
+    acc = torch.zeros(1, dtype=torch.float32, device=dev) if out is None else out.reshape(1)
+    for i, t in enumerate(tensors):
+        t = t if t.is_contiguous() else t.contiguous()
+        if t.dtype not in (torch.float32, torch.bfloat16):
+            t = t.float()
+        ext.sqnorm(t, _scratch[key], acc, i > 0)
+    return acc.reshape(())

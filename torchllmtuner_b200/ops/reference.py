@@ -1,0 +1,201 @@
+"""Plain PyTorch fp32-math statements of every hot op.
+
+These are the CPU path and the numerical oracle for the sm_100a kernels: each CUDA kernel test
+compares against the function of the same name here (reference for the op set:
+llmtuner/kernel/cpu/basic.py:1-96, llmtuner/models/qwen/ops.py:80-131,503,
+llmtuner/components/loss.py:35-70). Everything is differentiable through autograd.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+IGNORE_INDEX = -100
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return F.linear(x, w)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * weight.float()).to(x.dtype)
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+    """(norm(x + residual), x + residual): the residual stream stays in the input dtype."""
+    s = (x.float() + residual.float()).to(x.dtype)
+    return rms_norm(s, weight, eps), s
+
+
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float, dtype=torch.float32):
+    """cos/sin of shape [T, head_dim/2] for half-rotation RoPE."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim))
+    ang = positions.float()[:, None] * inv[None, :]
+    return ang.cos().to(dtype), ang.sin().to(dtype)
+
+
+def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    # x [T, H, d] fp32; cos/sin [T, d/2]; half rotation: (x1, x2) -> (x1 c - x2 s, x2 c + x1 s)
+    d2 = x.shape[-1] // 2
+    x1, x2 = x[..., :d2], x[..., d2:]
+    c, s = cos.float()[:, None, :], sin.float()[:, None, :]
+    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1)
+
+
+def qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps: float):
+    """Per-head RMSNorm over head_dim (skipped when the weight is None) followed by half-rotation RoPE.
+    q [T, Hq, d], k [T, Hkv, d]."""
+    def one(x, w):
+        xf = x.float()
+        if w is not None:
+            xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        return _rope(xf, cos, sin).to(x.dtype)
+    return one(q, q_weight), one(k, k_weight)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    g = gate.float()
+    return (g * torch.sigmoid(g) * up.float()).to(gate.dtype)
+
+
+def attention(q, k, v, cu_seqlens=None, causal: bool = True, scale: float | None = None,
+              k_cu_seqlens=None, q_offsets=None):
+    """Variable-length GQA attention over packed rows.
+
+    q [Tq, Hq, d], k/v [Tk, Hkv, d]. `cu_seqlens` (int32 [n+1]) cuts the rows into documents; a query
+    only sees keys of its own document (block-causal when `causal`). `k_cu_seqlens` gives separate key
+    cuts (default: same as q) and `q_offsets[i]` is the position of document i's first query inside
+    that document's keys (default: keys and queries end together), which is what context-parallel
+    shards need. Returns (out [Tq, Hq, d], lse [Hq, Tq] fp32).
+    """
+    Tq, Hq, d = q.shape
+    Hkv = k.shape[1]
+    g = Hq // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if cu_seqlens is None:
+        cu_seqlens = torch.tensor([0, Tq], dtype=torch.int32)
+    cq = cu_seqlens.tolist()
+    ck = cq if k_cu_seqlens is None else k_cu_seqlens.tolist()
+    out = torch.zeros_like(q)
+    lse = torch.full((Hq, Tq), float("-inf"), dtype=torch.float32, device=q.device)
+    for i in range(len(cq) - 1):
+        qs, qe, ks, ke = cq[i], cq[i + 1], ck[i], ck[i + 1]
+        if qe == qs:
+            continue
+        qi = q[qs:qe].float().transpose(0, 1)                        # [Hq, lq, d]
+        ki = k[ks:ke].float().transpose(0, 1).repeat_interleave(g, 0)
+        vi = v[ks:ke].float().transpose(0, 1).repeat_interleave(g, 0)
+        s = torch.matmul(qi, ki.transpose(1, 2)) * scale              # [Hq, lq, lk]
+        lq, lk = qe - qs, ke - ks
+        if causal:
+            off = (lk - lq) if q_offsets is None else int(q_offsets[i])
+            qpos = torch.arange(lq, device=q.device)[:, None] + off
+            kpos = torch.arange(lk, device=q.device)[None, :]
+            s = s.masked_fill(kpos > qpos, float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l.unsqueeze(-1))
+        p = torch.nan_to_num(p, nan=0.0)
+        out[qs:qe] = torch.matmul(p, vi).transpose(0, 1).to(q.dtype)
+        lse[:, qs:qe] = l
+    return out, lse
+
+
+def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Sum (not mean) of token cross-entropies in fp32; targets == IGNORE_INDEX are skipped."""
+    return F.cross_entropy(logits.float(), targets, ignore_index=IGNORE_INDEX, reduction="sum")
+
+
+def linear_cross_entropy_sum(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, num_chunks: int = 1):
+    """Head projection + summed CE without ever holding more than one chunk of logits."""
+    total = h.new_zeros((), dtype=torch.float32)
+    n = max(1, num_chunks)
+    step = -(-h.shape[0] // n)
+    for s in range(0, h.shape[0], step):
+        total = total + cross_entropy_sum(F.linear(h[s:s + step], w), targets[s:s + step])
+    return total
+
+
+def router_scores(logits: torch.Tensor, score_fn: str) -> torch.Tensor:
+    lf = logits.float()
+    if score_fn == "softmax":
+        return torch.softmax(lf, dim=-1)
+    if score_fn == "sigmoid":
+        return torch.sigmoid(lf)
+    if score_fn == "sqrtsoftplus":
+        return torch.sqrt(F.softplus(lf))
+    raise ValueError(score_fn)
+
+
+def router_topk(logits, bias, top_k: int, score_fn: str = "softmax", renorm: bool = True, route_scale: float = 1.0):
+    """scores = f(logits); selection on scores (+bias, which never enters the weights); weights are the
+    selected scores, optionally renormalised. Returns (weights [T,k] fp32, indices [T,k] int64,
+    counts [E] fp32)."""
+    scores = router_scores(logits, score_fn)
+    sel = scores if bias is None else scores + bias.float()[None, :]
+    idx = torch.topk(sel, top_k, dim=-1, sorted=True).indices
+    w = scores.gather(-1, idx)
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    w = w * route_scale
+    counts = torch.zeros(logits.shape[-1], dtype=torch.float32, device=logits.device)
+    counts.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=logits.device))
+    return w, idx, counts
+
+
+def moe_permute(x: torch.Tensor, indices: torch.Tensor, num_experts: int):
+    """Sort the T*k token copies by expert (stable). Returns (rows [T*k, D], order [T*k] int64 =
+    flat copy index of each sorted row, tokens_per_expert [E] int64)."""
+    flat = indices.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    rows = x.index_select(0, order // indices.shape[1])
+    counts = torch.bincount(flat, minlength=num_experts)
+    return rows, order, counts
+
+
+def moe_unpermute_combine(y: torch.Tensor, order: torch.Tensor, weights: torch.Tensor, num_tokens: int):
+    """out[t] = sum_j weights[t, j] * y[row of copy (t, j)], accumulated in fp32."""
+    k = weights.shape[1]
+    w_sorted = weights.reshape(-1).index_select(0, order).float()
+    out = torch.zeros(num_tokens, y.shape[1], dtype=torch.float32, device=y.device)
+    out.index_add_(0, order // k, y.float() * w_sorted[:, None])
+    return out.to(y.dtype)
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """Rows of `x` are grouped by expert (counts[e] consecutive rows each); y_e = x_e @ w[e].T with
+    w [E, N, K]."""
+    outs, s = [], 0
+    for e, c in enumerate(counts.tolist()):
+        outs.append(F.linear(x[s:s + c], w[e]))
+        s += c
+    return torch.cat(outs, 0) if outs else x.new_zeros(0, w.shape[1])
+
+
+def adamw_step_(p_master, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+                p_lowp=None, decoupled: bool = True):
+    """One AdamW (or Adam when not `decoupled`) update on fp32 master weights; writes the low-precision
+    copy when given."""
+    g = grad.float() * grad_scale
+    if not decoupled and weight_decay:
+        g = g + weight_decay * p_master
+    exp_avg.mul_(beta1).add_(g, alpha=1 - beta1)
+    exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
+    if decoupled and weight_decay:
+        p_master.mul_(1 - lr * weight_decay)
+    denom = (exp_avg_sq / bc2).sqrt_().add_(eps)
+    p_master.addcdiv_(exp_avg, denom, value=-lr / bc1)
+    if p_lowp is not None:
+        p_lowp.copy_(p_master)
+
+
+def sq_norm(tensors) -> torch.Tensor:
+    acc = None
+    for t in tensors:
+        v = t.float().pow(2).sum()
+        acc = v if acc is None else acc + v
+    return acc if acc is not None else torch.zeros(())
