@@ -1,0 +1,199 @@
+"""Headline benchmark: training tokens/s of Qwen3-8B (FSDP over N GPUs of one node, bf16, sequence 8192, one sequence per
+GPU and step, full activation checkpointing, synthetic uniform-random tokens, random-init weights).
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+Two timed regions, both CUDA-event timed on the launching stream between barrier + synchronize, max over ranks:
+  value : K optimizer steps with the step's inputs already resident on the device and no host read of the result
+  e2e   : K optimizer steps through `Trainer.train_step()`: every step copies its inputs from pinned host memory to the
+          device and reads the step's loss / grad-norm back to the host
+Rank 0 prints one JSON line. `--impl reference` reports why the reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read only)."""
+
+    def __init__(self, gpu_index: int):
+        self.path = f"/tmp/llmt_clocks_{os.getpid()}.csv"
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1])); mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        os.unlink(self.path)
+        if not sm:
+            return {}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args) -> int:
+    why = ("reference not runnable offline: pip install --no-deps succeeded, but `import llmtuner` needs colorama and grain "
+           "(not in the wheelhouse) and torch>=2.12 APIs (fully_shard(dp_mesh_dims=...), DCP DefaultStager); box has torch 2.11")
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def build_config(args, world: int):
+    from torchllmtuner_b200 import LLMTunerConfig
+    cfg = LLMTunerConfig()
+    flat = dict(model_name_or_path=args.model, initialization_device="meta", global_batch_size=world * args.micro_batch,
+                max_seq_len=args.seq, steps=10 ** 6, activation_checkpoint_mode=args.ac, chunked_loss_num_chunks=args.loss_chunks,
+                seed=0, dump_folder="/tmp/llmt_bench", data_parallel_shard_size=world, log_freq=10 ** 6, gc_freq=10 ** 6,
+                fsdp_implementation=args.fsdp_impl, deterministic=False)
+    cfg.apply_flat(flat)
+    if args.layers:
+        cfg.model.arch_overrides = dict(cfg.model.arch_overrides, num_hidden_layers=args.layers)
+    return cfg
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "stock"])
+    ap.add_argument("--model", default="qwen3_8b")
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--ac", default="full")
+    ap.add_argument("--loss-chunks", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline metric)")
+    ap.add_argument("--fsdp-impl", default="native", choices=["native", "custom"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.impl == "stock":
+        from baseline.stock_arm import run_stock
+        return run_stock(args)
+
+    import torch
+    import torch.distributed as dist
+    from torchllmtuner_b200 import Trainer
+    from torchllmtuner_b200.ops.cuda_ext import check_status, load
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N > 1"
+    warm = max(3, args.warmup)
+    cfg = build_config(args, world)
+    tr = Trainer(cfg)
+    dev = tr.env.device
+    ext = load()
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, k: int) -> float:
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident inputs for the kernel-only region
+    def device_batch():
+        b = next(tr.data_iterator)
+        return [{k: (v.to(dev) if isinstance(v, torch.Tensor) and k != "cu_seqlens" else v) for k, v in b.items()}]
+
+    for _ in range(warm):
+        tr.train_step()
+    check_status("bench warm-up")
+    pre = [device_batch() for _ in range(args.steps)]
+    it = iter(pre)
+    sampler = ClockSampler(tr.env.local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    n0 = ext.launch_count()
+    ms_dev = timed(lambda: tr.train_step(batches=next(it), read_stats=False), args.steps)
+    launches = ext.launch_count() - n0
+    clocks = sampler.stop() if sampler else {}
+    # ---- end to end: pinned host -> device copy of every step's inputs, loss read back every step
+    h2d = d2h = 0
+    probe = next(tr.data_iterator)
+    h2d = sum(v.numel() * v.element_size() for k, v in probe.items() if isinstance(v, torch.Tensor) and k != "cu_seqlens")
+    d2h = 3 * 4
+    results = []
+    ms_e2e = timed(lambda: results.append(tr.train_step()), args.steps)
+    check_status("bench")
+    tokens_per_step = world * args.micro_batch * args.seq
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    fpt = tr.model.flops_per_token(args.seq)
+    mem = torch.cuda.max_memory_allocated() / 2 ** 30
+    out = {"metric": "training tokens/sec/box (device-timed, max over ranks), Qwen3-8B FSDP bf16 seq 8192", "value": value,
+           "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_dev / args.steps,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+           "config": {"model": args.model + (f"[layers={args.layers}]" if args.layers else ""), "global_batch": world * args.micro_batch,
+                      "seq_len": args.seq, "parallelism": f"fsdp{world}", "activation_checkpointing": args.ac,
+                      "loss": f"chunked x{args.loss_chunks}", "l2": "inputs (16 GB of weights per step) larger than the 126 MB L2",
+                      "fsdp_implementation": args.fsdp_impl},
+           "clocks": clocks, "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d,
+                                      "d2h_bytes_per_step": d2h},
+           "gpu_launches": int(launches), "mfu_nominal_pct": 100 * value / world * fpt / 2.25e15,
+           "tflops_per_gpu": value / world * fpt / 1e12, "final_loss": results[-1].loss if results else None,
+           "peak_mem_gib": mem, "impl": "ours"}
+    tr.close()
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,59 @@
+"""End-to-end CPU slice: tiny Qwen3 dense trains through the public Trainer API and the loss falls."""
+import torch
+
+from torchllmtuner_b200 import LLMTunerConfig, Trainer
+
+
+def tiny_config(**flat):
+    cfg = LLMTunerConfig()
+    base = dict(model_name_or_path="qwen3", vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=2, global_batch_size=4, max_seq_len=32, steps=8,
+                learning_rate=3e-3, seed=0, dump_folder="/tmp/llmt_test_out")
+    base.update(flat)
+    cfg.apply_flat(base)
+    return cfg
+
+
+def run(cfg, repeat_batch=True):
+    """Uniform random tokens carry no signal, so the tests replay the first global batch every step."""
+    tr = Trainer(cfg)
+    losses = []
+    try:
+        for _ in range(cfg.training.steps):
+            if repeat_batch:
+                tr.dataloader.cursor = 0
+            losses.append(tr.train_step().loss)
+    finally:
+        tr.close()
+    return losses
+
+
+def test_dense_loss_decreases():
+    losses = run(tiny_config())
+    assert losses[-1] < losses[0] - 0.05, losses
+    assert all(torch.isfinite(torch.tensor(losses)))
+
+
+def test_full_ac_matches_no_ac():
+    a = run(tiny_config(steps=3))
+    b = run(tiny_config(steps=3, activation_checkpoint_mode="full"))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5, (a, b)
+
+
+def test_chunked_loss_matches_logits_loss():
+    a = run(tiny_config(steps=3))
+    b = run(tiny_config(steps=3, chunked_loss_num_chunks=3))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-4, (a, b)
+
+
+def test_grad_accumulation_matches_one_batch():
+    a = run(tiny_config(steps=3))
+    b = run(tiny_config(steps=3, gradient_accumulation_steps=2))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-4, (a, b)
+
+
+def test_moe_trains():
+    cfg = tiny_config(model_name_or_path="qwen3_moe", steps=6)
+    cfg.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, router_bias_update_coeff=1e-3)
+    losses = run(cfg)
+    assert losses[-1] < losses[0], losses

@@ -1,0 +1,151 @@
+"""Optimizer container, gradient clipping and EMA over sharded units
+(reference: llmtuner/components/optimizer/optimizer.py:142-608, ema.py:43-410,
+llmtuner/accelerator/collectives.py:290-558, llmtuner/trainer/runtime/gradients.py:321-372)."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ... import ops
+from ...errors import ConfigError
+from .sharded import ShardedAdamW
+
+
+class OptimizersContainer:
+    """Fan-out over one optimizer per model part. Exposes `step`, `zero_grad`, and flat state for checkpoints."""
+
+    def __init__(self, optimizers):
+        self.optimizers = list(optimizers)
+
+    def step(self, clip_coef=None) -> None:
+        for o in self.optimizers:
+            o.step(clip_coef)
+
+    def zero_grad(self) -> None:
+        for o in self.optimizers:
+            o.zero_grad()
+
+    @property
+    def param_groups(self):
+        return [g for o in self.optimizers for g in o.param_groups]
+
+
+def build_optimizers(runtimes, opt_cfg) -> OptimizersContainer:
+    outs = []
+    for rt in runtimes:
+        t = opt_cfg.optimizer_type
+        if t in ("Adam", "AdamW", "AdamWSwap"):
+            outs.append(ShardedAdamW(rt.units, lr=opt_cfg.learning_rate, betas=opt_cfg.betas, eps=opt_cfg.eps,
+                                     weight_decay=opt_cfg.weight_decay, decoupled=t != "Adam",
+                                     param_group_rules=opt_cfg.param_groups,
+                                     host_moments=(t == "AdamWSwap" or opt_cfg.state_residency == "host"),
+                                     swap_slice_bytes=opt_cfg.swap_max_device_bytes or (1 << 28)))
+        elif t == "DistMuon":
+            from .muon import DistMuon
+            outs.append(DistMuon(rt, lr=opt_cfg.learning_rate, weight_decay=opt_cfg.weight_decay, betas=opt_cfg.betas,
+                                 eps=opt_cfg.eps, param_group_rules=opt_cfg.param_groups))
+        else:
+            raise ConfigError(f"unknown optimizer_type {t!r}")
+    return OptimizersContainer(outs)
+
+
+class GradientClipper:
+    """L2 norm over every unit's gradient shard, combined across the groups that hold disjoint shards, then a clip
+    coefficient that lives on the device. Dense shards are summed over `dp_shard_cp` (and `tp` for TP-sharded
+    parameters), expert shards over `efsdp` x `ep`."""
+
+    def __init__(self, runtimes, topo, max_norm: float, device):
+        self.runtimes, self.topo, self.max_norm = list(runtimes), topo, max_norm
+        self.device = torch.device(device)
+        f = dict(dtype=torch.float32, device=self.device)
+        self.total = torch.zeros(2, **f)       # [dense_sq, expert_sq]
+        self.coef = torch.ones(1, **f)
+        self.norm = torch.zeros(1, **f)
+        self.finite = torch.ones(1, dtype=torch.int32, device=self.device)
+
+    def _reduce(self, x: torch.Tensor, name: str) -> None:
+        g = self.topo.get_group(name)
+        if g is not None:
+            dist.all_reduce(x, group=g)
+
+    @torch.no_grad()
+    def __call__(self) -> torch.Tensor:
+        dense, expert, tp_rep = [], [], []
+        for rt in self.runtimes:
+            for u in rt.units:
+                if u.has_grad:
+                    (expert if u.is_expert else dense).append(u.grad_shard)
+        sq_d = ops.sq_norm(dense).reshape(1) if dense else torch.zeros(1, dtype=torch.float32, device=self.device)
+        sq_e = ops.sq_norm(expert).reshape(1) if expert else torch.zeros(1, dtype=torch.float32, device=self.device)
+        sq_d, sq_e = sq_d.to(self.device), sq_e.to(self.device)
+        if self.topo.size("dp_shard_cp") > 1:
+            self._reduce(sq_d, "dp_shard_cp")
+        if self.topo.tp > 1:
+            # TP-replicated parameters (norms, router) are counted tp times after this sum; their weight in the
+            # total is negligible and the reference's split into replicated/sharded groups is applied by
+            # `tp_replicated_correction` when exactness is requested.
+            self._reduce(sq_d, "tp")
+        if self.topo.ep > 1:
+            self._reduce(sq_e, "efsdp")
+            self._reduce(sq_e, "ep")
+        elif self.topo.size("dp_shard_cp") > 1:
+            self._reduce(sq_e, "dp_shard_cp")
+        total = (sq_d + sq_e).reshape(1)
+        if self.device.type == "cuda":
+            from ...ops.cuda_ext import load
+            load().clip_coef(total, self.max_norm, self.coef, self.norm, self.finite)
+        else:
+            n = torch.sqrt(total)
+            self.norm.copy_(n)
+            self.coef.copy_(torch.clamp(self.max_norm / (n + 1e-6), max=1.0))
+            self.finite.fill_(int(bool(torch.isfinite(n))))
+        return self.norm
+
+
+class EMA:
+    """Exponential moving average of the fp32 master shards: avg.lerp_(param, 1 - decay) with
+    decay = 2^(-1 / (half_life_fraction * num_updates)) unless given (reference: ema.py:152-410)."""
+
+    def __init__(self, runtimes, cfg, total_steps: int):
+        self.cfg = cfg
+        self.units = [u for rt in runtimes for u in rt.units]
+        n_updates = max(1, (total_steps - cfg.start_step) // cfg.update_every_n_steps)
+        self.decay = cfg.decay if cfg.decay is not None else 2.0 ** (-1.0 / max(1e-9, cfg.half_life_fraction * n_updates))
+        self.ema_params = {u.name: u.master.detach().clone() for u in self.units}
+        self.num_updates = 0
+
+    @torch.no_grad()
+    def step(self, step: int) -> None:
+        c = self.cfg
+        if step < c.start_step or (step - c.start_step) % c.update_every_n_steps:
+            return
+        self.num_updates += 1
+        d = self.decay
+        if c.step_bias:
+            d = min(d, (1 + self.num_updates) / (c.step_bias + self.num_updates))
+        avgs = [self.ema_params[u.name] for u in self.units]
+        torch._foreach_lerp_(avgs, [u.master for u in self.units], 1.0 - d)
+
+    def reset(self) -> None:
+        for u in self.units:
+            self.ema_params[u.name].copy_(u.master)
+        self.num_updates = 0
+
+    def state_dict(self):
+        return {"ema_params": self.ema_params, "num_updates": self.num_updates}
+
+    def load_state_dict(self, sd):
+        for k, v in sd["ema_params"].items():
+            self.ema_params[k].copy_(v)
+        self.num_updates = int(sd.get("num_updates", 0))
+
+
+def check_finite(clipper: GradientClipper, loss_value: float | None = None) -> None:
+    """Host-side verdict, read once at the end of the step: the kernels already skipped the update when the
+    coefficient was not finite, so raising here is equivalent to raising before the update."""
+    from ...errors import LLMTunerError
+    if int(clipper.finite.item()) == 0 or (loss_value is not None and not math.isfinite(loss_value)):
+        raise LLMTunerError(f"non-finite gradient norm or loss (norm={float(clipper.norm.item())}, loss={loss_value}); "
+                            "the optimizer update was skipped on every rank")

@@ -1,0 +1,116 @@
+"""Optimizers over the flat shards of `parallel.fsdp.FlatUnit`s
+(reference: llmtuner/components/optimizer/optimizer.py:62-608, adamw_swap.py:71-650).
+
+`ShardedAdamW` runs one fused kernel per unit on (fp32 master, fp32 moments, gradient shard) and rewrites the
+low-precision shard that the next all-gather (or the peers' loads) reads. The clip coefficient stays on the device:
+the kernel multiplies the gradient by it and skips the update when it is not finite, so no host round trip sits
+between backward and the optimizer. Regex parameter groups (first match wins) are honoured per parameter by
+cutting the unit into runs of equal hyper-parameters. `state_residency="host"` keeps the moments in pinned host
+memory and streams them through the device in bounded slices (AdamWSwap).
+"""
+from __future__ import annotations
+
+import re
+
+import torch
+
+from ... import ops
+
+
+class ShardedAdamW:
+    def __init__(self, units, *, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
+                 decoupled: bool = True, param_group_rules=None, host_moments: bool = False, swap_slice_bytes: int = 1 << 28):
+        self.units = list(units)
+        self.defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        self.decoupled = decoupled
+        self.host_moments = host_moments
+        self.swap_slice = max(1 << 20, swap_slice_bytes) // 4
+        self.rules = [(re.compile(r.pattern), dict(r.optimizer_kwargs)) for r in (param_group_rules or [])]
+        self.param_groups = [dict(self.defaults, name=".*", param_names=[])]
+        for pat, kw in self.rules:
+            g = dict(self.defaults, name=pat.pattern, param_names=[])
+            g.update({("lr" if k == "learning_rate" else k): v for k, v in kw.items()})
+            self.param_groups.append(g)
+        self.step_count = 0
+        self.state: dict[str, dict[str, torch.Tensor]] = {}
+        self._runs: dict[str, list[tuple[int, int, int]]] = {}
+        for u in self.units:
+            dev = "cpu" if host_moments else u.master.device
+            kw = dict(dtype=torch.float32, device=dev)
+            m, v = torch.zeros(u.shard_numel, **kw), torch.zeros(u.shard_numel, **kw)
+            if host_moments and torch.cuda.is_available():
+                m, v = m.pin_memory(), v.pin_memory()
+            self.state[u.name] = {"exp_avg": m, "exp_avg_sq": v}
+            self._runs[u.name] = self._build_runs(u)
+
+    def _group_index(self, fqn: str) -> int:
+        for i, (pat, _) in enumerate(self.rules):
+            if pat.search(fqn):
+                return i + 1
+        return 0
+
+    def _build_runs(self, u):
+        """[(shard_lo, shard_hi, group_index)] covering the shard, merged where neighbours share a group."""
+        runs: list[list[int]] = []
+        pos = 0
+        for fqn, _shape, lo, hi, shard_lo in u.shard_slices():
+            gi = self._group_index(fqn)
+            self.param_groups[gi]["param_names"].append(fqn)
+            if shard_lo > pos:
+                runs.append([pos, shard_lo, runs[-1][2] if runs else gi])
+            n = hi - lo
+            if runs and runs[-1][2] == gi and runs[-1][1] == shard_lo:
+                runs[-1][1] = shard_lo + n
+            else:
+                runs.append([shard_lo, shard_lo + n, gi])
+            pos = shard_lo + n
+        if pos < u.shard_numel:
+            if runs:
+                runs[-1][1] = u.shard_numel
+            else:
+                runs.append([0, u.shard_numel, 0])
+        return [tuple(r) for r in runs]
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for u in self.units:
+            u.has_grad = False
+
+    @torch.no_grad()
+    def step(self, clip_coef: torch.Tensor | None = None) -> None:
+        self.step_count += 1
+        for u in self.units:
+            if not u.has_grad:
+                continue
+            st = self.state[u.name]
+            lowp = u.shard_lowp if u.separate_master else None
+            for lo, hi, gi in self._runs[u.name]:
+                g = self.param_groups[gi]
+                kw = dict(lr=g["lr"], beta1=g["betas"][0], beta2=g["betas"][1], eps=g["eps"], weight_decay=g["weight_decay"],
+                          step=self.step_count, decoupled=self.decoupled, clip_coef=clip_coef)
+                if not self.host_moments:
+                    ops.adamw_step_(u.master[lo:hi], u.grad_shard[lo:hi], st["exp_avg"][lo:hi], st["exp_avg_sq"][lo:hi],
+                                    p_lowp=None if lowp is None else lowp[lo:hi], **kw)
+                else:
+                    for a in range(lo, hi, self.swap_slice):
+                        b = min(hi, a + self.swap_slice)
+                        m = st["exp_avg"][a:b].to(u.master.device, non_blocking=True)
+                        v = st["exp_avg_sq"][a:b].to(u.master.device, non_blocking=True)
+                        ops.adamw_step_(u.master[a:b], u.grad_shard[a:b], m, v, p_lowp=None if lowp is None else lowp[a:b], **kw)
+                        st["exp_avg"][a:b].copy_(m, non_blocking=True)
+                        st["exp_avg_sq"][a:b].copy_(v, non_blocking=True)
+
+    # ------------------------------------------------------------------ checkpoint state keyed by parameter FQN
+    def state_dict_shards(self):
+        """{unit_name: {"master", "exp_avg", "exp_avg_sq"}} flat shard tensors plus the step counter."""
+        return {"step": self.step_count,
+                "units": {u.name: {"master": u.master, **self.state[u.name]} for u in self.units}}
+
+    def load_state_dict_shards(self, sd) -> None:
+        self.step_count = int(sd["step"])
+        for u in self.units:
+            src = sd["units"][u.name]
+            u.master.copy_(src["master"])
+            if u.separate_master:
+                u.shard_lowp.copy_(u.master)
+            for k in ("exp_avg", "exp_avg_sq"):
+                self.state[u.name][k].copy_(src[k])

@@ -16,7 +16,12 @@ inline void check_bf16(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
   TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
 }
-inline void check_rc(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+// Number of kernels of this library launched so far (the caller-side count; each binding adds what it enqueues).
+static int64_t g_launches = 0;
+inline void check_rc(int rc, const char* what, int launches = 1) {
+  TORCH_CHECK(rc == 0, what, " failed with code ", rc);
+  g_launches += launches;
+}
 
 Tensor& status_word() {
   static Tensor s;
@@ -125,7 +130,7 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   }
   check_rc(llmt_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(),
                             part.data_ptr<float>(), dw.data_ptr<float>(), nullptr, 0, (int)T, (int)D, cur_stream()),
-           "llmt_rmsnorm_bwd");
+           "llmt_rmsnorm_bwd", 2);
   return {dx, dw};
 }
 
@@ -168,7 +173,7 @@ std::vector<Tensor> qk_norm_rope_bwd(const Tensor& dy, const Tensor& x, const c1
   check_rc(llmt_qk_norm_rope_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), wp, cosb.data_ptr<float>(),
                                  sinb.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(), dx.stride(0), pp, dwp, nullptr,
                                  0, T, H, HD, cur_stream()),
-           "llmt_qk_norm_rope_bwd");
+           "llmt_qk_norm_rope_bwd", w.has_value() ? 2 : 1);
   if (w.has_value()) return {dx, dw};
   return {dx};
 }
@@ -248,7 +253,7 @@ void sqnorm(const Tensor& x, Tensor& scratch, Tensor& out, bool accumulate) {
   const bool b = x.scalar_type() == at::kBFloat16;
   TORCH_CHECK(b || x.scalar_type() == at::kFloat);
   check_rc(llmt_sqnorm(x.data_ptr(), b, x.numel(), scratch.data_ptr<float>(), out.data_ptr<float>(), accumulate, cur_stream()),
-           "llmt_sqnorm");
+           "llmt_sqnorm", 2);
 }
 int64_t sqnorm_scratch_floats() { return llmt_sqnorm_scratch_floats(); }
 
@@ -291,7 +296,7 @@ std::vector<Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, 
                          (int)q_tiles.size(0), k_tiles.data_ptr<int>(), (int)k_tiles.size(0), Tq, Tk, Hq, Hkv, HD, q.stride(0),
                          k.stride(0), v.stride(0), o.stride(0), dout.stride(0), dq.stride(0), dk.stride(0), dv.stride(0),
                          (float)scale, causal, status_ptr(), cur_stream()),
-           "llmt_attn_bwd");
+           "llmt_attn_bwd", 3);
   return {dq, dk, dv};
 }
 
@@ -303,6 +308,7 @@ std::vector<int64_t> read_status(bool clear) {
   return r;
 }
 Tensor status_tensor() { return status_word(); }
+int64_t launch_count() { return g_launches; }
 
 }  // namespace
 
@@ -326,4 +332,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_bwd", &attn_bwd);
   m.def("read_status", &read_status, py::arg("clear") = true);
   m.def("status_tensor", &status_tensor);
+  m.def("launch_count", &launch_count);
 }

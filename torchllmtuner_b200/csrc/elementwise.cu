@@ -421,6 +421,7 @@ __global__ void adamw_kernel(float* __restrict__ p32, __nv_bfloat16* __restrict_
                              float eps, float wd, float bc1, float bc2, const float* __restrict__ clip_coef,
                              float grad_scale, int decoupled) {
   const float gs = grad_scale * (clip_coef != nullptr ? *clip_coef : 1.f);
+  if (!isfinite(gs)) return;  // non-finite gradient norm: leave parameters and moments untouched
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     float gr;
     if constexpr (sizeof(GT) == 2) gr = __bfloat162float(g[i]) * gs;
@@ -467,7 +468,7 @@ __global__ void clip_coef_kernel(const float* __restrict__ total_sq, float max_n
                                  float* __restrict__ norm_out, int* __restrict__ finite) {
   const float n = sqrtf(total_sq[0]);
   norm_out[0] = n;
-  clip_coef[0] = fminf(1.f, max_norm / (n + 1e-6f));
+  clip_coef[0] = isfinite(n) ? fminf(1.f, max_norm / (n + 1e-6f)) : NAN;
   if (finite != nullptr) finite[0] = isfinite(n) ? 1 : 0;
 }
 

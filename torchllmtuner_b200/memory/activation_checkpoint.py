@@ -1,0 +1,51 @@
+"""Activation checkpointing modes (reference: llmtuner/memory/activation_checkpoint.py:80-656).
+
+  none           keep every activation
+  full           keep only each block's input; the block forward is replayed in backward
+  selective      every `save_every_nth_block`-th block keeps its activations, the others recompute
+  memory_budget  the fraction of blocks that recompute is chosen from `memory_budget` (0 = all recompute, 1 = none)
+  region         per-block choice from module-name patterns: blocks matching `recompute_regions` recompute
+Expert-parallel token exchanges are never replayed: the dispatcher caches the received rows of the forward pass
+for the recompute (the role of the reference's MUST_SAVE policy for all_to_all, activation_checkpoint.py:278-300).
+"""
+from __future__ import annotations
+
+import re
+
+
+def apply_ac(model, training_config) -> None:
+    mode = training_config.activation_checkpoint_mode
+    n_layers = len(model.model.layers) if hasattr(model, "model") and hasattr(model.model, "layers") else 0
+    if mode in ("none", "full"):
+        model.activation_checkpoint = mode
+        return
+    if mode == "selective":
+        model.activation_checkpoint = "selective"
+        model.ac_save_every = max(1, training_config.selective_ac.save_every_nth_block)
+        return
+    if mode == "memory_budget":
+        b = training_config.memory_budget_ac.memory_budget
+        if b >= 1.0:
+            model.activation_checkpoint = "none"
+        elif b <= 0.0:
+            model.activation_checkpoint = "full"
+        else:
+            model.activation_checkpoint = "selective"
+            model.ac_save_every = max(2, round(1.0 / b))
+        return
+    if mode == "region":
+        rc = training_config.region_ac
+        save = [re.compile(p) for p in rc.save_regions]
+        rec = [re.compile(p) for p in rc.recompute_regions]
+        recompute_all = not save
+        sel = []
+        for i in range(n_layers):
+            name = f"model.layers.{i}"
+            r = any(p.search(name) for p in rec) or (recompute_all and not rec)
+            if any(p.search(name) for p in save):
+                r = False
+            sel.append(r)
+        model.activation_checkpoint = "full" if all(sel) else ("none" if not any(sel) else "selective")
+        model.ac_block_mask = sel
+        return
+    raise ValueError(mode)

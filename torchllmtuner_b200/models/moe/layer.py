@@ -1,0 +1,94 @@
+"""Sparse MoE block with aux-loss-free bias balancing (reference: llmtuner/models/common/moe/layer.py:88-309,
+bias_update.py:36-291, auxiliary_loss.py:31-168).
+
+Persistent fp32 buffers `expert_bias_E` and `tokens_per_expert_E`. Once per optimizer step the token counts are
+all-reduced over the data ranks and `bias += delta - mean(delta)` with `delta = coeff * sign(mean(counts) - counts)`.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .experts import GroupedExperts, RoutedExperts
+from .routing import QuantileBalancedTopKRouter, TokenChoiceTopKRouter
+
+
+class MoE(nn.Module):
+    def __init__(self, hidden: int, num_experts: int, top_k: int, moe_inter: int, *, shared_inter: int = 0,
+                 score_fn: str = "softmax", norm_topk_prob: bool = True, route_scale: float = 1.0,
+                 bias_update_coeff: float = 0.0, aux_loss_coef: float = 0.0, quantile_balancing: bool = False,
+                 fixed_router: bool = False, experts_implementation: str = "native", dtype=None, device=None,
+                 shared_mlp_factory=None):
+        super().__init__()
+        rcls = QuantileBalancedTopKRouter if quantile_balancing else TokenChoiceTopKRouter
+        self.router = rcls(hidden, num_experts, top_k, score_fn, norm_topk_prob, route_scale, fixed=fixed_router, dtype=dtype,
+                           device=device)
+        self.routed = RoutedExperts(GroupedExperts(num_experts, hidden, moe_inter, dtype=dtype, device=device,
+                                                   implementation=experts_implementation))
+        self.shared_experts = shared_mlp_factory(shared_inter) if (shared_inter and shared_mlp_factory) else None
+        self.num_experts, self.top_k = num_experts, top_k
+        self.bias_update_coeff, self.aux_loss_coef = bias_update_coeff, aux_loss_coef
+        self.register_buffer("expert_bias_E", torch.zeros(num_experts, dtype=torch.float32, device=device), persistent=True)
+        self.register_buffer("tokens_per_expert_E", torch.zeros(num_experts, dtype=torch.float32, device=device), persistent=True)
+        self.aux_loss: torch.Tensor | None = None
+        self.dispatch_timer = None
+
+    @property
+    def gate(self):          # HF-style name of the router projection
+        return self.router.gate
+
+    @property
+    def experts(self):
+        return self.routed.experts
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        bias = self.expert_bias_E if self.bias_update_coeff > 0 else None
+        w, idx, counts, scores = self.router(x2, bias)
+        if self.training and torch.is_grad_enabled():
+            with torch.no_grad():
+                self.tokens_per_expert_E.add_(counts)
+        if self.aux_loss_coef > 0 and self.training:
+            # DeepSeek-V3 style micro-batch balance loss: E * sum_e f_e * P_e
+            T = x2.shape[0]
+            f = counts / max(1, T * self.top_k) * self.num_experts
+            p = scores.mean(0)
+            self.aux_loss = self.aux_loss_coef * (f.detach() * p).sum()
+        out = self.routed(x2, w, idx)
+        if self.shared_experts is not None:
+            out = out + self.shared_experts(x2)
+        return out.reshape(shape)
+
+    @torch.no_grad()
+    def update_expert_bias(self, reduce_fn=None) -> None:
+        """`reduce_fn(counts)` all-reduces the counts over the data ranks (identity on one rank)."""
+        counts = self.tokens_per_expert_E
+        if reduce_fn is not None:
+            counts = reduce_fn(counts)
+        if self.bias_update_coeff > 0:
+            delta = self.bias_update_coeff * torch.sign(counts.mean() - counts)
+            self.expert_bias_E.add_(delta - delta.mean())
+        self.tokens_per_expert_E.zero_()
+
+
+def moe_blocks(model: nn.Module):
+    return [m for m in model.modules() if isinstance(m, MoE)]
+
+
+def collect_aux_loss(model: nn.Module):
+    total = None
+    for m in moe_blocks(model):
+        if m.aux_loss is not None:
+            total = m.aux_loss if total is None else total + m.aux_loss
+            m.aux_loss = None
+    return total
+
+
+def routing_load_metrics(model: nn.Module) -> dict[str, float]:
+    out = {}
+    for i, m in enumerate(moe_blocks(model)):
+        c = m.tokens_per_expert_E
+        if c.sum() > 0:
+            out[f"moe/layer{i}/max_over_mean"] = float(c.max() / c.mean().clamp_min(1e-9))
+    return out

@@ -1,0 +1,125 @@
+"""Token-choice top-k routers (reference: llmtuner/models/common/moe/routing.py:31-345,
+llmtuner/models/qwen/routing.py:20-78).
+
+scores = f(fp32 logits) with f in {softmax, sigmoid, sqrtsoftplus}; the load-balancing bias enters the selection only,
+never the combine weights; optional node-limited groups; renormalisation with +1e-20; `route_scale`; a fixed
+round-robin router for debugging; a quantile-balanced variant that shifts logits by running per-expert quantiles.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ... import ops
+from ...ops import reference as ref
+
+
+class RouterGateLinear(nn.Module):
+    """Router projection with fp32 output (reference: llmtuner/models/common/linear.py:104-183)."""
+
+    def __init__(self, hidden: int, num_experts: int, dtype=None, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(num_experts, hidden, dtype=dtype, device=device))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            return _RouterGate.apply(x, self.weight)
+        return torch.mm(x.float(), self.weight.float().t())
+
+
+class _RouterGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return ops.gemm(x, w, out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, dl):
+        x, w = ctx.saved_tensors
+        d16 = dl.to(torch.bfloat16)
+        dx = ops.gemm(d16, w, b_mn=True)
+        dw = ops.gemm(d16, x, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw
+
+
+class TokenChoiceTopKRouter(nn.Module):
+    def __init__(self, hidden: int, num_experts: int, top_k: int, score_fn: str = "softmax", norm_topk_prob: bool = True,
+                 route_scale: float = 1.0, num_groups: int = 1, topk_groups: int = 1, fixed: bool = False, dtype=None,
+                 device=None):
+        super().__init__()
+        self.gate = RouterGateLinear(hidden, num_experts, dtype=dtype, device=device)
+        self.num_experts, self.top_k, self.score_fn = num_experts, top_k, score_fn
+        self.norm_topk_prob, self.route_scale = norm_topk_prob, route_scale
+        self.num_groups, self.topk_groups, self.fixed = num_groups, topk_groups, fixed
+
+    @property
+    def weight(self):
+        return self.gate.weight
+
+    def forward(self, x: torch.Tensor, expert_bias: torch.Tensor | None = None):
+        """x [T, D] -> (weights [T,k] fp32, indices [T,k] int64, counts [E] fp32, scores [T,E] fp32)."""
+        logits = self.gate(x)
+        scores = ref.router_scores(logits, self.score_fn)
+        if self.fixed:
+            T = x.shape[0]
+            idx = (torch.arange(T, device=x.device)[:, None] * self.top_k + torch.arange(self.top_k, device=x.device)[None, :]) % self.num_experts
+        else:
+            sel = scores if expert_bias is None else scores + expert_bias.float()[None, :]
+            if self.num_groups > 1:
+                T = sel.shape[0]
+                grp = sel.view(T, self.num_groups, -1)
+                gscore = grp.topk(min(2, grp.shape[-1]), dim=-1).values.sum(-1) if expert_bias is not None else grp.amax(-1)
+                keep = gscore.topk(self.topk_groups, dim=-1).indices
+                mask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, keep, True)
+                sel = grp.masked_fill(~mask[..., None], float("-inf")).view(T, -1)
+            idx = torch.topk(sel.detach(), self.top_k, dim=-1, sorted=True).indices
+        w = scores.gather(-1, idx)
+        if self.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        w = w * self.route_scale
+        counts = torch.zeros(self.num_experts, dtype=torch.float32, device=x.device)
+        counts.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x.device))
+        return w, idx, counts, scores
+
+
+class QuantileBalancer(nn.Module):
+    """Running per-expert logit quantiles from a 1000-bin histogram (reference: routing.py:491)."""
+
+    def __init__(self, num_experts: int, top_k: int, bins: int = 1000, lo: float = -20.0, hi: float = 20.0, momentum: float = 0.9):
+        super().__init__()
+        self.bins, self.lo, self.hi, self.momentum = bins, lo, hi, momentum
+        self.target = 1.0 - top_k / num_experts
+        self.register_buffer("threshold_E", torch.zeros(num_experts, dtype=torch.float32))
+
+    @torch.no_grad()
+    def update(self, logits: torch.Tensor) -> None:
+        E = logits.shape[1]
+        width = (self.hi - self.lo) / self.bins
+        b = ((logits.float() - self.lo) / width).clamp_(0, self.bins - 1).long()
+        hist = torch.zeros(E, self.bins, device=logits.device)
+        hist.scatter_add_(1, b.t().contiguous(), torch.ones_like(b.t(), dtype=torch.float32))
+        cdf = hist.cumsum(1) / max(1, logits.shape[0])
+        q = (cdf < self.target).sum(1).float() * width + self.lo
+        self.threshold_E.mul_(self.momentum).add_(q, alpha=1 - self.momentum)
+
+
+class QuantileBalancedTopKRouter(TokenChoiceTopKRouter):
+    """Selection on logits shifted by each expert's running quantile, so every expert fires at about the same rate."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.balancer = QuantileBalancer(self.num_experts, self.top_k)
+
+    def forward(self, x, expert_bias=None):
+        logits = self.gate(x)
+        if self.training:
+            self.balancer.update(logits.detach())
+        scores = ref.router_scores(logits, self.score_fn)
+        sel = logits.detach().float() - self.balancer.threshold_E[None, :]
+        idx = torch.topk(sel, self.top_k, dim=-1, sorted=True).indices
+        w = scores.gather(-1, idx)
+        if self.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        counts = torch.zeros(self.num_experts, dtype=torch.float32, device=x.device)
+        counts.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x.device))
+        return w * self.route_scale, idx, counts, scores

@@ -1,0 +1,93 @@
+"""Model registry (reference: llmtuner/models/registry.py:17-305).
+
+`register_model(name, builder, ...)`, `get_model_spec`, `build_registered_model`. Built-ins: `qwen3` (dense alias),
+`qwen3_moe`, `qwen3_8b`, `qwen3_30b_a3b`, and the capability-surface families `qwen3_5`, `qwen3_5_moe`,
+`qwen3_5_moe_text`, `deepseek_v4`, `kimi_linear`, `kimi_k3` which are registered behind the same contracts.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Callable
+
+from ..errors import ConfigError
+
+
+@dataclass
+class ModelSpec:
+    name: str
+    builder: Callable
+    state_format: str = "native"            # name of the ModelStateFormat used for HF import/export
+    supports: frozenset[str] = field(default_factory=lambda: frozenset({"fsdp", "tp", "ep", "cp", "pp", "ac"}))
+    description: str = ""
+
+
+_MODELS: dict[str, ModelSpec] = {}
+
+
+def register_model(name: str, builder: Callable, *, state_format: str = "native", supports=None, description: str = "",
+                   replace: bool = False) -> ModelSpec:
+    if name in _MODELS and not replace:
+        raise ConfigError(f"model {name!r} is already registered")
+    spec = ModelSpec(name, builder, state_format, frozenset(supports) if supports is not None else ModelSpec.__dataclass_fields__["supports"].default_factory(), description)
+    _MODELS[name] = spec
+    return spec
+
+
+def registered_models() -> list[str]:
+    _ensure_builtins()
+    return sorted(_MODELS)
+
+
+def get_model_spec(name: str) -> ModelSpec:
+    _ensure_builtins()
+    if name not in _MODELS:
+        raise ConfigError(f"unknown model {name!r}; registered: {sorted(_MODELS)}")
+    return _MODELS[name]
+
+
+def resolve_state_format(name: str):
+    from .state import get_state_format
+    return get_state_format(get_model_spec(name).state_format)
+
+
+def build_registered_model(model_config, dtype=None, device=None):
+    """`model_name_or_path` is a registry key or a Hugging Face folder whose config.json names the architecture."""
+    _ensure_builtins()
+    key = model_config.model_name_or_path
+    overrides = {}
+    if key not in _MODELS and os.path.isdir(key):
+        with open(os.path.join(key, "config.json")) as f:
+            hf = json.load(f)
+        mt = hf.get("model_type", "")
+        key = {"qwen3": "qwen3_moe", "qwen3_moe": "qwen3_moe"}.get(mt)
+        if key is None:
+            raise ConfigError(f"Hugging Face model_type {mt!r} has no registered model")
+        overrides = {k: v for k, v in hf.items() if not isinstance(v, (dict,))}
+        overrides["num_experts"] = hf.get("num_experts", 0) or 0
+    spec = get_model_spec(key)
+    return spec.builder(model_config, dtype=dtype, device=device, **overrides)
+
+
+_loaded = False
+
+
+def _ensure_builtins() -> None:
+    global _loaded
+    if _loaded:
+        return
+    _loaded = True
+    from . import qwen3
+    reg = lambda n, b, **kw: register_model(n, b, replace=True, **kw)  # noqa: E731
+    reg("qwen3_moe", qwen3.build_qwen3, state_format="qwen3", description="Qwen3 dense / MoE decoder")
+    reg("qwen3", qwen3.build_qwen3, state_format="qwen3", description="dense Qwen3 (alias of qwen3_moe without experts)")
+    reg("qwen3_8b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_8B, **kw}),
+        state_format="qwen3", description="Qwen3-8B architecture")
+    reg("qwen3_30b_a3b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_30B_A3B, **kw}),
+        state_format="qwen3", description="Qwen3-30B-A3B architecture")
+    try:
+        from . import families
+        families.register_all(reg)
+    except ImportError:
+        pass

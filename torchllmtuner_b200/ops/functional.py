@@ -282,6 +282,8 @@ def adamw_step_(p_master, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, w
                      grad_scale, decoupled)
         return
     gs = grad_scale * (float(clip_coef) if clip_coef is not None else 1.0)
+    if not math.isfinite(gs):
+        return          # non-finite gradient norm: leave parameters and moments untouched
     ref.adamw_step_(p_master, grad, exp_avg, exp_avg_sq, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
                     weight_decay=weight_decay, step=step, grad_scale=gs, p_lowp=p_lowp, decoupled=decoupled)
 

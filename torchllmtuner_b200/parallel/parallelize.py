@@ -1,0 +1,60 @@
+"""`parallelize_model`: validate, resolve plans (metadata only), then apply the stages in the fixed order
+TP -> EP -> CP -> AC -> activation swap -> compile -> FSDP (reference: llmtuner/parallel/parallelize.py:54-314)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..accelerator.collectives import synchronize_local_errors
+from .compatibility import check_compatibility
+from .stages import STAGE_ORDER
+
+
+@dataclass
+class ParallelAssembly:
+    model: torch.nn.Module
+    topo: object
+    fsdp: object = None
+    tp_plan: dict = field(default_factory=dict)
+    ep_plan: dict = field(default_factory=dict)
+    cp_driver: object = None
+    stages_applied: list[str] = field(default_factory=list)
+
+
+def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None) -> ParallelAssembly:
+    arch = getattr(model, "config", None)
+    check_compatibility(config, topo, arch)
+    if hasattr(model, "validate_parallel"):
+        model.validate_parallel(tp=topo.tp, cp_ulysses=topo.cp_ulysses, ep=topo.ep)
+    asm = ParallelAssembly(model, topo)
+    t = config.training
+    for stage in STAGE_ORDER:
+        with synchronize_local_errors(f"parallelize:{stage}"):
+            if stage == "tp" and topo.tp > 1:
+                from .tensor_parallel import apply_tp
+                asm.tp_plan = apply_tp(model, topo, config.parallel.tp_config)
+            elif stage == "ep" and getattr(arch, "num_experts", 0) > 0 and topo.ep > 1:
+                from .expert_parallel import apply_ep
+                asm.ep_plan = apply_ep(model, topo, config.parallel.ep_config)
+            elif stage == "cp" and topo.cp > 1:
+                from .context_parallel import apply_cp
+                asm.cp_driver = apply_cp(model, topo, config.parallel.cp_config)
+            elif stage == "ac":
+                from ..memory.activation_checkpoint import apply_ac
+                apply_ac(model, t)
+            elif stage == "activation_swap" and t.activation_swap:
+                from ..memory.activation_swap import apply_activation_swap
+                apply_activation_swap(model, t)
+            elif stage == "compile" and t.compile:
+                from .graph_capture import apply_compile
+                apply_compile(model, t.compile_config)
+            elif stage == "fsdp":
+                from .fsdp import apply_fsdp
+                asm.fsdp = apply_fsdp(model, topo, config.parallel.fsdp_config, device=device, param_dtype=param_dtype,
+                                      ac_mode=getattr(model, "activation_checkpoint", "none"),
+                                      ac_save_every=getattr(model, "ac_save_every", 2), init_fn=init_fn)
+            else:
+                continue
+        asm.stages_applied.append(stage)
+    return asm

@@ -1,0 +1,62 @@
+"""Assembly of the training runtime from a config (reference: llmtuner/trainer/runtime/assembly.py:86-642)."""
+from __future__ import annotations
+
+import torch
+
+from ...components.loss import LossFunctions
+from ...components.optimizer import EMA, GradientClipper, build_lr_scheduler, build_optimizers
+from ...models.registry import build_registered_model
+from ...parallel.parallelize import parallelize_model
+from ...memory.materialization import materialize_meta_model
+from .engine import TrainingEngine
+
+
+def build_model(config, env):
+    """Build on the meta device when asked (large models) or on CPU (tests, reference comparisons)."""
+    dev = "meta" if config.model.initialization_device == "meta" else ("cpu" if config.model.initialization_device == "cpu" else env.device)
+    with torch.device(dev):
+        model = build_registered_model(config.model, dtype=env.param_dtype, device=None)
+    if dev != "meta":
+        model.initialize_parameters(seed=config.training.seed)
+    return model
+
+
+def make_init_fn(model, seed: int):
+    """Per-parameter initialiser used while the flat units materialise meta parameters in place."""
+    std = getattr(model.config, "initializer_range", 0.02)
+
+    def init(fqn: str, p: torch.Tensor) -> None:
+        if fqn.endswith("norm.weight") or "layernorm" in fqn:
+            p.fill_(1.0)
+        else:
+            g = torch.Generator(device=p.device).manual_seed((seed * 1000003 + (abs(hash(fqn)) % 1000003)) % (2 ** 63))
+            p.normal_(0.0, std, generator=g)
+    return init
+
+
+def prepare_parallel_model(config, env):
+    model = build_model(config, env)
+    init_fn = make_init_fn(model, config.training.seed) if config.model.initialization_device == "meta" else None
+    asm = parallelize_model(model, config, env.topo, device=env.device, param_dtype=env.param_dtype, init_fn=init_fn)
+    materialize_meta_model(model, env.device)
+    for m in model.modules():          # persistent fp32 buffers stay fp32 on the compute device
+        for name, buf in list(m._buffers.items()):
+            if buf is not None and buf.device != env.device:
+                m._buffers[name] = buf.to(env.device)
+    return model, asm
+
+
+def build_loss_functions(config, env, asm) -> LossFunctions:
+    return LossFunctions(num_chunks=config.training.chunked_loss_num_chunks)
+
+
+def build_optimizer_stack(config, env, asm):
+    optimizers = build_optimizers([asm.fsdp], config.optimizer)
+    lr = build_lr_scheduler(optimizers, config.optimizer.lr_scheduler_config, config.training.steps)
+    ema = EMA([asm.fsdp], config.training.ema_config, config.training.steps) if config.training.ema_config is not None else None
+    clipper = GradientClipper([asm.fsdp], env.topo, config.training.max_norm, env.device)
+    return optimizers, lr, ema, clipper
+
+
+def create_training_engine(config, env, model, asm, loss_fns, optimizers, lr, ema, clipper) -> TrainingEngine:
+    return TrainingEngine(model, asm, loss_fns, optimizers, lr, ema, clipper, env.topo, env.device)

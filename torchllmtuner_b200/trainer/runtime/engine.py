@@ -1,0 +1,95 @@
+"""Training engine: one forward/backward per micro-batch and the optimizer step
+(reference: llmtuner/trainer/runtime/engine.py:52-494, gradients.py:50-372)."""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ...components.loss import LossFunctions
+from ...components.optimizer import check_finite
+from ...models.moe import collect_aux_loss, moe_blocks
+
+
+class TrainingEngine:
+    def __init__(self, model, assembly, loss_fns: LossFunctions, optimizers, lr_schedulers, ema, clipper, topo, device):
+        self.model, self.asm, self.loss_fns = model, assembly, loss_fns
+        self.optimizers, self.lr_schedulers, self.ema, self.clipper = optimizers, lr_schedulers, ema, clipper
+        self.topo, self.device = topo, device
+        self.rt = assembly.fsdp
+        self.step_loss = torch.zeros((), dtype=torch.float32, device=device)
+
+    # ------------------------------------------------------------------ step phases
+    def begin_step(self) -> None:
+        self.step_loss.zero_()
+        self.model.train()
+
+    def parallel_dims(self) -> dict | None:
+        t = self.topo
+        if t.cp == 1 and t.tp == 1:
+            return None
+        lb = getattr(self.asm.cp_driver, "load_balancer", None)
+        return {"cp": t.cp, "cp_rank": t.coord("cp"), "tp": t.tp, "tp_rank": t.coord("tp"), "load_balancer": lb}
+
+    def forward_backward(self, batch: dict, global_valid_tokens: torch.Tensor, is_last_microbatch: bool = True) -> torch.Tensor:
+        """Returns the un-normalised loss sum of this micro-batch (device scalar, detached)."""
+        m = self.model
+        self.rt.is_last_microbatch = is_last_microbatch
+        inputs = m.prepare_inputs(batch, self.device, self.parallel_dims())
+        ctx = m.build_context(inputs["positions"], inputs["attn_meta"], self.asm.cp_driver)
+        if self.asm.cp_driver is not None:
+            self.asm.cp_driver.begin_microbatch(inputs)
+        self.rt.before_forward()
+        if self.loss_fns.chunked:
+            h = m(inputs["tokens"], ctx, skip_lm_head=True)
+            loss_sum = self.loss_fns.from_hidden(h, m.lm_head.weight, inputs["targets"])
+        else:
+            logits = m(inputs["tokens"], ctx)
+            loss_sum = self.loss_fns.from_logits(logits, inputs["targets"])
+        loss = loss_sum / global_valid_tokens
+        aux = collect_aux_loss(m)
+        if aux is not None:
+            loss = loss + aux
+        loss.backward()
+        self.rt.finish_backward()
+        self.step_loss += loss_sum.detach()
+        return loss_sum.detach()
+
+    @torch.no_grad()
+    def evaluate(self, batch: dict) -> tuple[torch.Tensor, int]:
+        m = self.model
+        was = m.training
+        m.eval()
+        inputs = m.prepare_inputs(batch, self.device, self.parallel_dims())
+        ctx = m.build_context(inputs["positions"], inputs["attn_meta"], self.asm.cp_driver)
+        self.rt.before_forward()
+        h = m(inputs["tokens"], ctx, skip_lm_head=True)
+        loss = self.loss_fns.from_hidden(h, m.lm_head.weight, inputs["targets"]) if self.loss_fns.chunked else \
+            self.loss_fns.from_logits(m.lm_head(h), inputs["targets"])
+        m.train(was)
+        return loss, int((inputs["targets"] != -100).sum())
+
+    def _update_moe_bias(self) -> None:
+        blocks = moe_blocks(self.model)
+        if not blocks:
+            return
+        group = self.topo.get_group("loss") if self.topo.ep > 1 else self.topo.get_group("dp_cp")
+        counts = torch.stack([b.tokens_per_expert_E for b in blocks])
+        if group is not None:
+            dist.all_reduce(counts, group=group)
+        for b, c in zip(blocks, counts):
+            b.tokens_per_expert_E.copy_(c)
+            b.update_expert_bias()
+
+    def optimizer_step(self, step: int) -> torch.Tensor:
+        self.rt.wait_reductions()
+        norm = self.clipper()
+        self._update_moe_bias()
+        self.optimizers.step(self.clipper.coef)
+        self.rt.post_optimizer()
+        self.lr_schedulers.step()
+        if self.ema is not None:
+            self.ema.step(step)
+        return norm
+
+    def finish_step(self, step: int, loss_value: float | None = None) -> None:
+        check_finite(self.clipper, loss_value)
