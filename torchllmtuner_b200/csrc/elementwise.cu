@@ -176,8 +176,10 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
 }
 
 // ------------------------------------------------------------------------------------------ QK-norm + RoPE
-// One warp per (token, head). x rows are `stride` elements apart per token and HD per head. HD = 64 * P.
-// Forward: n = x * rsqrt(mean x^2 + eps) * w (skipped when w == nullptr), then half rotation with cos/sin [T, HD/2].
+// One warp per (token, head). Token rows are `tok_stride` elements apart, heads are packed (HD apart). HD = 64 * P.
+// Lane l owns columns {j * 32 + l : j < P} of the first half and their partners (+ HD/2) in the second half.
+// Forward: n = x * rsqrt(mean x^2 + eps) * w (skipped when w == nullptr), then half rotation with cos/sin [T, HD/2]:
+//   y1 = n1 cos - n2 sin ; y2 = n2 cos + n1 sin.
 template <int P>
 __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t tok_stride,
                                                                const __nv_bfloat16* __restrict__ w,
@@ -186,20 +188,20 @@ __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const __nv_bfloat
                                                                __nv_bfloat16* __restrict__ y, int64_t y_tok_stride,
                                                                float* __restrict__ rstd, int T, int H, float eps) {
   constexpr int HD = 64 * P;
+  constexpr int HALF = HD / 2;
   const int lane = threadIdx.x & 31;
   const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= (int64_t)T * H) return;
   const int t = (int)(item / H), h = (int)(item % H);
   const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD;
-  float a[2 * P], b[2 * P];  // a: first half elements, b: partner elements in the second half
+  float a[P], b[P];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < P; ++i) {
-    const int c = (i * 32 + lane) * 2;
-    const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + c));
-    const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + HD / 2 + c));
-    a[2 * i] = fa.x; a[2 * i + 1] = fa.y; b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
-    ss += fa.x * fa.x + fa.y * fa.y + fb.x * fb.x + fb.y * fb.y;
+  for (int j = 0; j < P; ++j) {
+    const int c = j * 32 + lane;
+    a[j] = __bfloat162float(px[c]);
+    b[j] = __bfloat162float(px[HALF + c]);
+    ss += a[j] * a[j] + b[j] * b[j];
   }
   float r = 1.f;
   if (w != nullptr) {
@@ -209,25 +211,19 @@ __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const __nv_bfloat
   }
   __nv_bfloat16* py = y + (int64_t)t * y_tok_stride + (int64_t)h * HD;
 #pragma unroll
-  for (int i = 0; i < P; ++i) {
-    const int c = (i * 32 + lane) * 2;
-    float wa0 = 1.f, wa1 = 1.f, wb0 = 1.f, wb1 = 1.f;
-    if (w != nullptr) {
-      const float2 fwa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + c));
-      const float2 fwb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + HD / 2 + c));
-      wa0 = fwa.x; wa1 = fwa.y; wb0 = fwb.x; wb1 = fwb.y;
-    }
-    const float2 cs = *reinterpret_cast<const float2*>(cosb + (int64_t)t * (HD / 2) + c);
-    const float2 sn = *reinterpret_cast<const float2*>(sinb + (int64_t)t * (HD / 2) + c);
-    const float n1x = a[2 * i] * r * wa0, n1y = a[2 * i + 1] * r * wa1;
-    const float n2x = b[2 * i] * r * wb0, n2y = b[2 * i + 1] * r * wb1;
-    *reinterpret_cast<__nv_bfloat162*>(py + c) = __floats2bfloat162_rn(n1x * cs.x - n2x * sn.x, n1y * cs.y - n2y * sn.y);
-    *reinterpret_cast<__nv_bfloat162*>(py + HD / 2 + c) = __floats2bfloat162_rn(n2x * cs.x + n1x * sn.x, n2y * cs.y + n1y * sn.y);
+  for (int j = 0; j < P; ++j) {
+    const int c = j * 32 + lane;
+    float wa = 1.f, wb = 1.f;
+    if (w != nullptr) { wa = __bfloat162float(w[c]); wb = __bfloat162float(w[HALF + c]); }
+    const float cs = cosb[(int64_t)t * HALF + c], sn = sinb[(int64_t)t * HALF + c];
+    const float n1 = a[j] * r * wa, n2 = b[j] * r * wb;
+    py[c] = __float2bfloat16_rn(n1 * cs - n2 * sn);
+    py[HALF + c] = __float2bfloat16_rn(n2 * cs + n1 * sn);
   }
 }
 
-// Backward: un-rotate dy (rotation by -angle), then RMSNorm backward per head. dw partial is accumulated per block
-// in shared memory over its (token, head) items and written to dw_partial[blockIdx.x][HD].
+// Backward: un-rotate dy (dn1 = d1 cos + d2 sin ; dn2 = d2 cos - d1 sin), then RMSNorm backward per head.
+// The weight gradient is accumulated per block in shared memory and written to dw_partial[blockIdx.x][HD].
 template <int P>
 __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, int64_t dy_tok_stride,
                                                                const __nv_bfloat16* __restrict__ x, int64_t tok_stride,
@@ -238,70 +234,63 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
                                                                __nv_bfloat16* __restrict__ dx, int64_t dx_tok_stride,
                                                                float* __restrict__ dw_partial, int T, int H) {
   constexpr int HD = 64 * P;
+  constexpr int HALF = HD / 2;
   __shared__ float sdw[HD];
   for (int i = threadIdx.x; i < HD; i += blockDim.x) sdw[i] = 0.f;
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
-  float dwa[2 * P], dwb[2 * P];
+  float dwa[P], dwb[P];
 #pragma unroll
-  for (int i = 0; i < 2 * P; ++i) { dwa[i] = 0.f; dwb[i] = 0.f; }
+  for (int j = 0; j < P; ++j) { dwa[j] = 0.f; dwb[j] = 0.f; }
   for (int64_t item = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); item < (int64_t)T * H; item += (int64_t)gridDim.x * wpb) {
     const int t = (int)(item / H), h = (int)(item % H);
     const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD;
     const __nv_bfloat16* pd = dy + (int64_t)t * dy_tok_stride + (int64_t)h * HD;
     __nv_bfloat16* po = dx + (int64_t)t * dx_tok_stride + (int64_t)h * HD;
-    float xa[2 * P], xb[2 * P], ga[2 * P], gb[2 * P];
+    float xa[P], xb[P], ga[P], gb[P];
     const float r = (w != nullptr) ? rstd[item] : 1.f;
-    float c = 0.f;
+    float c_acc = 0.f;
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-      const int col = (i * 32 + lane) * 2;
-      const float2 d1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + col));
-      const float2 d2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + HD / 2 + col));
-      const float2 cs = *reinterpret_cast<const float2*>(cosb + (int64_t)t * (HD / 2) + col);
-      const float2 sn = *reinterpret_cast<const float2*>(sinb + (int64_t)t * (HD / 2) + col);
-      // y1 = n1 c - n2 s ; y2 = n2 c + n1 s  =>  dn1 = d1 c + d2 s ; dn2 = d2 c - d1 s
-      float dn1x = d1.x * cs.x + d2.x * sn.x, dn1y = d1.y * cs.y + d2.y * sn.y;
-      float dn2x = d2.x * cs.x - d1.x * sn.x, dn2y = d2.y * cs.y - d1.y * sn.y;
+    for (int j = 0; j < P; ++j) {
+      const int c = j * 32 + lane;
+      const float d1 = __bfloat162float(pd[c]), d2 = __bfloat162float(pd[HALF + c]);
+      const float cs = cosb[(int64_t)t * HALF + c], sn = sinb[(int64_t)t * HALF + c];
+      float dn1 = d1 * cs + d2 * sn;
+      float dn2 = d2 * cs - d1 * sn;
+      xa[j] = 0.f; xb[j] = 0.f;
       if (w != nullptr) {
-        const float2 fxa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + col));
-        const float2 fxb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(px + HD / 2 + col));
-        const float2 fwa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + col));
-        const float2 fwb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + HD / 2 + col));
-        xa[2 * i] = fxa.x; xa[2 * i + 1] = fxa.y; xb[2 * i] = fxb.x; xb[2 * i + 1] = fxb.y;
-        dwa[2 * i] += dn1x * fxa.x * r; dwa[2 * i + 1] += dn1y * fxa.y * r;
-        dwb[2 * i] += dn2x * fxb.x * r; dwb[2 * i + 1] += dn2y * fxb.y * r;
-        dn1x *= fwa.x; dn1y *= fwa.y; dn2x *= fwb.x; dn2y *= fwb.y;
-        c += dn1x * fxa.x + dn1y * fxa.y + dn2x * fxb.x + dn2y * fxb.y;
+        xa[j] = __bfloat162float(px[c]);
+        xb[j] = __bfloat162float(px[HALF + c]);
+        dwa[j] += dn1 * xa[j] * r;
+        dwb[j] += dn2 * xb[j] * r;
+        dn1 *= __bfloat162float(w[c]);
+        dn2 *= __bfloat162float(w[HALF + c]);
+        c_acc += dn1 * xa[j] + dn2 * xb[j];
       }
-      ga[2 * i] = dn1x; ga[2 * i + 1] = dn1y; gb[2 * i] = dn2x; gb[2 * i + 1] = dn2y;
+      ga[j] = dn1;
+      gb[j] = dn2;
     }
     float k = 0.f;
     if (w != nullptr) {
-      c = warp_sum(c);
-      k = r * r * r * c / (float)HD;
+      c_acc = warp_sum(c_acc);
+      k = r * r * r * c_acc / (float)HD;
     }
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-      const int col = (i * 32 + lane) * 2;
-      float o1x = ga[2 * i], o1y = ga[2 * i + 1], o2x = gb[2 * i], o2y = gb[2 * i + 1];
-      if (w != nullptr) {
-        o1x = r * o1x - xa[2 * i] * k; o1y = r * o1y - xa[2 * i + 1] * k;
-        o2x = r * o2x - xb[2 * i] * k; o2y = r * o2y - xb[2 * i + 1] * k;
-      }
-      *reinterpret_cast<__nv_bfloat162*>(po + col) = __floats2bfloat162_rn(o1x, o1y);
-      *reinterpret_cast<__nv_bfloat162*>(po + HD / 2 + col) = __floats2bfloat162_rn(o2x, o2y);
+    for (int j = 0; j < P; ++j) {
+      const int c = j * 32 + lane;
+      float o1 = ga[j], o2 = gb[j];
+      if (w != nullptr) { o1 = r * o1 - xa[j] * k; o2 = r * o2 - xb[j] * k; }
+      po[c] = __float2bfloat16_rn(o1);
+      po[HALF + c] = __float2bfloat16_rn(o2);
     }
   }
   if (w != nullptr && dw_partial != nullptr) {
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-      const int col = (i * 32 + lane) * 2;
-      atomicAdd(&sdw[col], dwa[2 * i]);
-      atomicAdd(&sdw[col + 1], dwa[2 * i + 1]);
-      atomicAdd(&sdw[HD / 2 + col], dwb[2 * i]);
-      atomicAdd(&sdw[HD / 2 + col + 1], dwb[2 * i + 1]);
+    for (int j = 0; j < P; ++j) {
+      const int c = j * 32 + lane;
+      atomicAdd(&sdw[c], dwa[j]);
+      atomicAdd(&sdw[HALF + c], dwb[j]);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < HD; i += blockDim.x) dw_partial[(int64_t)blockIdx.x * HD + i] = sdw[i];

@@ -52,9 +52,10 @@ class FlatUnit:
         self.slots: list[ParamSlot] = []
         off = 0
         for fqn, p in named_params:
-            n = p.numel()
+            shape = getattr(p, "_meta_shape", p.shape)
+            n = shape.numel()
             self.params.append(p)
-            self.slots.append(ParamSlot(fqn, p.shape, n, off))
+            self.slots.append(ParamSlot(fqn, shape, n, off))
             off += -(-n // 8) * 8      # 16-byte aligned starts so every matrix is a legal TMA base
         self.numel = off
         quantum = world * ALIGN
@@ -174,7 +175,7 @@ class FSDPRuntime:
             bufs.append(torch.zeros(unit.padded, dtype=dtype, device=self.device))
         return bufs
 
-    def finalize(self, init_fn=None, source_state: dict | None = None) -> None:
+    def finalize(self, init_fn=None, needs_init: set | None = None) -> None:
         """Bind gather/gradient buffers and establish the shards. Parameters that still hold real data (model
         built on CPU/GPU) are copied in; meta parameters are initialised by `init_fn(fqn, param)` inside the bound
         full buffer, unit by unit, so the peak is one unit."""
@@ -188,7 +189,8 @@ class FSDPRuntime:
             else:
                 pool = self._pool(self._slot_bufs, u, 2, u.param_dtype)
                 full = pool[self._unit_slot(u)]
-            old = [(p, None if p.is_meta else p.detach().clone()) for p in u.params]
+            needs_init = needs_init or set()
+            old = [(p, None if id(p) in needs_init else p.detach().clone()) for p in u.params]
             u.bind_full(full)
             u.persistent = persistent
             with torch.no_grad():
@@ -435,6 +437,24 @@ class _CheckpointedBlock(torch.autograd.Function):
         return xd.grad, None, None, None, None
 
 
+def _materialize_meta_params(model: nn.Module, device, dtype) -> set[int]:
+    """Replace every meta parameter by an empty parameter on `device` (same object for tied weights) so that the
+    units can bind views with `.data =`. Returns the ids of the new parameters: they still need initial values."""
+    fresh: dict[int, nn.Parameter] = {}
+    for mod in model.modules():
+        for name, p in list(mod._parameters.items()):
+            if p is None or not p.is_meta:
+                continue
+            if id(p) not in fresh:
+                q = nn.Parameter(torch.empty(0, dtype=dtype, device=device), requires_grad=p.requires_grad)
+                for k, v in p.__dict__.items():
+                    setattr(q, k, v)
+                q._meta_shape = p.shape
+                fresh[id(p)] = q
+            mod._parameters[name] = fresh[id(p)]
+    return {id(q) for q in fresh.values()}
+
+
 # ---------------------------------------------------------------------------------------------- stage entry
 def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_mode="none", ac_save_every=2,
                init_fn=None) -> FSDPRuntime:
@@ -445,6 +465,7 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
     structure = getattr(model, "decoder_structure", None)
     if structure is None:
         raise ConfigError(f"{type(model).__name__} exposes no decoder_structure; cannot place FSDP units")
+    needs_init = _materialize_meta_params(model, device, param_dtype)
     bound = BoundDecoder(structure, model)
     rt = FSDPRuntime(model, topo, fsdp_config, device=device, param_dtype=param_dtype, ac_mode=ac_mode,
                      ac_save_every=ac_save_every)
@@ -482,7 +503,7 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
     if rest:
         named_units["rest"] = rt.add_unit("rest", rest)
     rt.named_units = {k: v for k, v in named_units.items() if v is not None}
-    rt.finalize(init_fn=init_fn)
+    rt.finalize(init_fn=init_fn, needs_init=needs_init)
     model.block_runner = rt.run_block
     model.fsdp_runtime = rt
     return rt
