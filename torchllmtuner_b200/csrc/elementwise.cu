@@ -405,25 +405,60 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(__nv_bfloat16* __restri
 // p32: fp32 master, m/v: fp32 moments, g: bf16 or fp32 gradient, p16: bf16 working copy (optional).
 // clip_coef (device, optional) multiplies the gradient: it is min(1, max_norm / (norm + 1e-6)) computed on the device.
 template <typename GT>
-__global__ void adamw_kernel(float* __restrict__ p32, __nv_bfloat16* __restrict__ p16, const GT* __restrict__ g,
-                             float* __restrict__ m, float* __restrict__ v, int64_t n, float lr, float b1, float b2,
-                             float eps, float wd, float bc1, float bc2, const float* __restrict__ clip_coef,
-                             float grad_scale, int decoupled) {
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p32, __nv_bfloat16* __restrict__ p16, const GT* __restrict__ g,
+                                                    float* __restrict__ m, float* __restrict__ v, int64_t n, float lr, float b1,
+                                                    float b2, float eps, float wd, float bc1, float bc2,
+                                                    const float* __restrict__ clip_coef, float grad_scale, int decoupled) {
   const float gs = grad_scale * (clip_coef != nullptr ? *clip_coef : 1.f);
   if (!isfinite(gs)) return;  // non-finite gradient norm: leave parameters and moments untouched
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float gr;
-    if constexpr (sizeof(GT) == 2) gr = __bfloat162float(g[i]) * gs;
-    else gr = g[i] * gs;
-    float p = p32[i];
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = decoupled ? (1.f - lr * wd) : 1.f;
+  auto update = [&](float& p, float& mi, float& vi, float gr) {
+    gr *= gs;
     if (!decoupled) gr += wd * p;
-    const float mi = b1 * m[i] + (1.f - b1) * gr;
-    const float vi = b2 * v[i] + (1.f - b2) * gr * gr;
-    m[i] = mi;
-    v[i] = vi;
-    if (decoupled) p *= (1.f - lr * wd);
-    p -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-    p32[i] = p;
+    mi = b1 * mi + (1.f - b1) * gr;
+    vi = b2 * vi + (1.f - b2) * gr * gr;
+    p = p * decay - lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+  };
+  // 4 elements per thread per iteration, 16-byte accesses when every base pointer allows it
+  const bool vec = ((reinterpret_cast<uintptr_t>(p32) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(g) & (sizeof(GT) * 4 - 1)) == 0 &&
+                   (p16 == nullptr || (reinterpret_cast<uintptr_t>(p16) & 7) == 0);
+  const int64_t n4 = vec ? n / 4 : 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 p = reinterpret_cast<float4*>(p32)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float gr[4];
+    if constexpr (sizeof(GT) == 2) {
+      const uint2 u = reinterpret_cast<const uint2*>(g)[i];
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+      gr[0] = a.x; gr[1] = a.y; gr[2] = b.x; gr[3] = b.y;
+    } else {
+      const float4 u = reinterpret_cast<const float4*>(g)[i];
+      gr[0] = u.x; gr[1] = u.y; gr[2] = u.z; gr[3] = u.w;
+    }
+    update(p.x, mm.x, vv.x, gr[0]);
+    update(p.y, mm.y, vv.y, gr[1]);
+    update(p.z, mm.z, vv.z, gr[2]);
+    update(p.w, mm.w, vv.w, gr[3]);
+    reinterpret_cast<float4*>(p32)[i] = p;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (p16 != nullptr) {
+      uint2 o;
+      o.x = pack_bf16x2(p.x, p.y);
+      o.y = pack_bf16x2(p.z, p.w);
+      reinterpret_cast<uint2*>(p16)[i] = o;
+    }
+  }
+  for (int64_t i = n4 * 4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float gr;
+    if constexpr (sizeof(GT) == 2) gr = __bfloat162float(g[i]);
+    else gr = g[i];
+    float p = p32[i], mi = m[i], vi = v[i];
+    update(p, mi, vi, gr);
+    p32[i] = p; m[i] = mi; v[i] = vi;
     if (p16 != nullptr) p16[i] = __float2bfloat16_rn(p);
   }
 }
@@ -574,7 +609,7 @@ extern "C" int llmt_adamw(float* p32, void* p16, const void* g, int g_is_bf16, f
                           int decoupled, cudaStream_t st) {
   if (n <= 0) return 0;
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
-  const int grid = grid_for(n, 256);
+  const int grid = grid_for((n + 3) / 4, 256, 16);
   if (g_is_bf16)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p32, (__nv_bfloat16*)p16, (const __nv_bfloat16*)g, m, v, n, lr, b1, b2,
                                                        eps, wd, bc1, bc2, clip_coef, grad_scale, decoupled);

@@ -94,6 +94,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   };
 
+  // Tile order inside one M x N problem: super-rows of kGroupM m-tiles are swept column by column, so the CTAs that
+  // run concurrently cover a near-square patch (A and B tiles are both reused out of L2).
+  constexpr int kGroupM = 16;
+  auto tile_mn = [&](int tt, int& m0, int& n0) {
+    const int per_group = kGroupM * num_n;
+    const int grp_i = tt / per_group;
+    const int first_m = grp_i * kGroupM;
+    const int gm = (num_m - first_m < kGroupM) ? (num_m - first_m) : kGroupM;
+    const int r = tt - grp_i * per_group;
+    m0 = (first_m + r % gm) * BM;
+    n0 = (r / gm) * BN;
+  };
+
   auto group_of_row = [&](int row) -> int {
     // segments are few (<= a few hundred); linear scan by one thread per tile is negligible
     int g = 0;
@@ -111,9 +124,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t armed = 0, armed_parity = 0;  // per-stage bookkeeping for the abort drain
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int tt = t % tiles_per_group;
-        const int m0 = (tt % num_m) * BM;
-        const int n0 = (tt / num_m) * BN;
+        int m0, n0;
+        tile_mn(t % tiles_per_group, m0, n0);
         int g = 0;
         if constexpr (GROUPED) g = group_of_row(m0);
         int k_begin;
@@ -203,9 +215,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const int tt = t % tiles_per_group;
-      const int m0 = (tt % num_m) * BM;
-      const int n0 = (tt / num_m) * BN;
+      int m0, n0;
+      tile_mn(t % tiles_per_group, m0, n0);
       const int row_limit = M;  // MODE 1: padded rows are written too (their inputs are zero)
       int k_begin;
       const bool empty_k = kb_range(t, k_begin) == 0;  // MODE 2 segment without rows: the product is zero

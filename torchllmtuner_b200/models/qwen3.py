@@ -11,6 +11,7 @@ structure come from `AttnMeta` (cu_seqlens), never from a dense mask.
 from __future__ import annotations
 
 import math
+import zlib
 from dataclasses import dataclass, field
 
 import torch
@@ -194,7 +195,7 @@ class Qwen3ForCausalLM(nn.Module):
                 p.fill_(1.0)
             else:
                 if seed is not None:
-                    gen = torch.Generator(device=p.device).manual_seed(seed + (hash(name) % 100003))
+                    gen = torch.Generator(device=p.device).manual_seed(seed * 1000003 + zlib.crc32(name.encode()))
                 p.normal_(0.0, std, generator=gen)
         for m in self.modules():
             if isinstance(m, MoE):

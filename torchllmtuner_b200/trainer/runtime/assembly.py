@@ -1,6 +1,8 @@
 """Assembly of the training runtime from a config (reference: llmtuner/trainer/runtime/assembly.py:86-642)."""
 from __future__ import annotations
 
+import zlib
+
 import torch
 
 from ...components.loss import LossFunctions
@@ -29,7 +31,7 @@ def make_init_fn(model, seed: int):
         if fqn.endswith("norm.weight") or "layernorm" in fqn:
             p.fill_(1.0)
         else:
-            g = torch.Generator(device=p.device).manual_seed((seed * 1000003 + (abs(hash(fqn)) % 1000003)) % (2 ** 63))
+            g = torch.Generator(device=p.device).manual_seed(seed * 1000003 + zlib.crc32(fqn.encode()))
             p.normal_(0.0, std, generator=g)
     return init
 
