@@ -41,8 +41,22 @@ inline Mat as_mat(const Tensor& t, const char* name) {
   return Mat{t.data_ptr(), t.size(0), t.size(1), t.stride(0)};
 }
 
+// A slice of a peer-memory collective handed to a kernel's comm warps (see csrc/comm.cuh). Pointers are raw device
+// addresses (peers' symmetric buffers are not torch tensors on this rank).
+struct PySideJob {
+  int64_t kind = 0;                 // 0 none, 1 copy, 2 reduce
+  std::vector<int64_t> src;         // device addresses
+  int64_t dst = 0;
+  int64_t n = 0;                    // copy: bytes; reduce: elements
+  bool accumulate = false;
+  int64_t wait_flags = 0;           // device address of the local flag array, 0 = no wait
+  int64_t n_wait = 0;
+  int64_t wait_value = 0;
+};
+
 // out[M,N] (+)= op(a) * op(b); layouts as in llmt_gemm_bf16. a_mn / b_mn say that the stored matrix is [K][M] / [K][N].
-void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, bool accumulate, int64_t max_ctas) {
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, bool accumulate, int64_t max_ctas,
+          const c10::optional<PySideJob>& side) {
   c10::cuda::CUDAGuard guard(a.device());
   const Mat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1, "out must be 2-D CUDA with contiguous last dim");
@@ -52,9 +66,43 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, b
   const int64_t N = b_mn ? B.cols : B.rows, Kb = b_mn ? B.rows : B.cols;
   TORCH_CHECK(K == Kb, "inner dimensions differ: ", K, " vs ", Kb);
   TORCH_CHECK(out.size(0) == M && out.size(1) == N, "out has the wrong shape");
+  if (side.has_value() && side->kind != 0) {
+    const void* src[8] = {nullptr};
+    TORCH_CHECK(side->src.size() >= 1 && side->src.size() <= 8, "side job needs 1..8 sources");
+    for (size_t i = 0; i < side->src.size(); ++i) src[i] = reinterpret_cast<const void*>(side->src[i]);
+    check_rc(llmt_gemm_bf16_fused(A.ptr, B.ptr, out.data_ptr(), (int)M, (int)N, (int)K, A.ld, B.ld, out.stride(0), a_mn, b_mn, f32,
+                                  accumulate, (int)side->kind, (int)side->src.size(), src, reinterpret_cast<void*>(side->dst),
+                                  (long long)side->n, side->accumulate, reinterpret_cast<const uint32_t*>(side->wait_flags),
+                                  (int)side->n_wait, (uint32_t)side->wait_value, status_ptr(), cur_stream()),
+             "llmt_gemm_bf16_fused");
+    return;
+  }
   check_rc(llmt_gemm_bf16(A.ptr, B.ptr, out.data_ptr(), (int)M, (int)N, (int)K, A.ld, B.ld, out.stride(0), a_mn, b_mn, f32,
                           accumulate, status_ptr(), (int)max_ctas, cur_stream()),
            "llmt_gemm_bf16");
+}
+
+void side_job(const PySideJob& j, int64_t ctas) {
+  const void* src[8] = {nullptr};
+  TORCH_CHECK(j.src.size() >= 1 && j.src.size() <= 8, "side job needs 1..8 sources");
+  for (size_t i = 0; i < j.src.size(); ++i) src[i] = reinterpret_cast<const void*>(j.src[i]);
+  check_rc(llmt_side_job((int)j.kind, (int)j.src.size(), src, reinterpret_cast<void*>(j.dst), (long long)j.n, j.accumulate,
+                         reinterpret_cast<const uint32_t*>(j.wait_flags), (int)j.n_wait, (uint32_t)j.wait_value, (int)ctas,
+                         status_ptr(), cur_stream()),
+           "llmt_side_job");
+}
+
+void signal_peers(const std::vector<int64_t>& peer_flag_ptrs, int64_t slot, int64_t value) {
+  uint32_t* p[8] = {nullptr};
+  TORCH_CHECK(peer_flag_ptrs.size() >= 1 && peer_flag_ptrs.size() <= 8);
+  for (size_t i = 0; i < peer_flag_ptrs.size(); ++i) p[i] = reinterpret_cast<uint32_t*>(peer_flag_ptrs[i]);
+  check_rc(llmt_signal_peers(p, (int)peer_flag_ptrs.size(), (int)slot, (uint32_t)value, cur_stream()), "llmt_signal_peers");
+}
+
+void wait_flags(int64_t flags_ptr, int64_t n, int64_t value, int64_t site) {
+  check_rc(llmt_wait_flags(reinterpret_cast<const uint32_t*>(flags_ptr), (int)n, (uint32_t)value, (int)site, status_ptr(),
+                           cur_stream()),
+           "llmt_wait_flags");
 }
 
 void grouped_gemm(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& seg_offsets, bool b_mn) {
@@ -313,8 +361,21 @@ int64_t launch_count() { return g_launches; }
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::class_<PySideJob>(m, "SideJob")
+      .def(py::init<>())
+      .def_readwrite("kind", &PySideJob::kind)
+      .def_readwrite("src", &PySideJob::src)
+      .def_readwrite("dst", &PySideJob::dst)
+      .def_readwrite("n", &PySideJob::n)
+      .def_readwrite("accumulate", &PySideJob::accumulate)
+      .def_readwrite("wait_flags", &PySideJob::wait_flags)
+      .def_readwrite("n_wait", &PySideJob::n_wait)
+      .def_readwrite("wait_value", &PySideJob::wait_value);
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn"), py::arg("b_mn"),
-        py::arg("accumulate") = false, py::arg("max_ctas") = 0);
+        py::arg("accumulate") = false, py::arg("max_ctas") = 0, py::arg("side") = py::none());
+  m.def("side_job", &side_job);
+  m.def("signal_peers", &signal_peers);
+  m.def("wait_flags", &wait_flags);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

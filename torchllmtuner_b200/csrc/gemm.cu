@@ -10,14 +10,15 @@
 //
 // CTA = 6 warps: warp 0 issues TMA, warp 1 owns TMEM and issues MMAs, warps 2-5 drain the accumulator.
 // The accumulator is double buffered in TMEM so the epilogue of tile i overlaps the MMAs of tile i+1.
-#include "common.cuh"
+#include "comm.cuh"
 #include "kernels.h"
 
 namespace llmt {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;                       // TMA warp, MMA warp, 4 epilogue warps
+constexpr int kGemmThreadsComm = 192 + kCommThreads;   // plus the comm warps that carry a SideJob
 
 template <int BN>
 struct GemmCfg {
@@ -35,9 +36,9 @@ struct GroupedArgs {
 };
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreadsComm, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    void* __restrict__ Cptr, int M, int N, int K, int64_t ldc, GroupedArgs grp, int* status) {
+                    void* __restrict__ Cptr, int M, int N, int K, int64_t ldc, GroupedArgs grp, SideJob side, int* status) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -209,6 +210,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ comm warps (only launched with a SideJob)
+    run_side_job(side, (long long)blockIdx.x * kCommThreads + (threadIdx.x - 192), (long long)gridDim.x * kCommThreads, status);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
@@ -352,7 +356,7 @@ int sm_count() {
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, int MODE>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int64_t ldc, GroupedArgs grp,
-                  int* status, int max_ctas, cudaStream_t stream) {
+                  int* status, int max_ctas, cudaStream_t stream, const SideJob* side = nullptr) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OUT_F32, ACCUM, MODE>;
   static bool configured = false;
@@ -364,17 +368,22 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid < 1) return 0;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, grp, status);
+  SideJob none{};
+  const bool with_side = side != nullptr && side->kind != kSideNone;
+  if (with_side && max_ctas <= 0) grid = sm_count();   // every SM carries comm warps, even past the last tile
+  kern<<<grid, with_side ? kGemmThreadsComm : kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, grp,
+                                                                                     with_side ? *side : none, status);
   return (cudaGetLastError() == cudaSuccess) ? 0 : -3;
 }
 
 template <int BN>
 static int dispatch_plain(bool a_mn, bool b_mn, bool out_f32, bool accum, const CUtensorMap& ta, const CUtensorMap& tb,
-                          void* C, int M, int N, int K, int64_t ldc, int* status, int max_ctas, cudaStream_t s) {
+                          void* C, int M, int N, int K, int64_t ldc, int* status, int max_ctas, cudaStream_t s,
+                          const SideJob* side) {
   GroupedArgs grp{nullptr, 0};
 #define LLMT_CASE(AM, BMN, F32, ACC)                                                            \
   if (a_mn == AM && b_mn == BMN && out_f32 == F32 && accum == ACC)                              \
-    return launch<BN, AM, BMN, F32, ACC, 0>(ta, tb, C, M, N, K, ldc, grp, status, max_ctas, s);
+    return launch<BN, AM, BMN, F32, ACC, 0>(ta, tb, C, M, N, K, ldc, grp, status, max_ctas, s, side);
   LLMT_CASE(false, false, false, false)
   LLMT_CASE(false, false, true, false)
   LLMT_CASE(false, true, false, false)
@@ -395,9 +404,8 @@ using namespace llmt;
 //   a_mn == 0: A stored [M][K] (row stride lda elements); a_mn == 1: A stored [K][M].
 //   b_mn == 0: B stored [N][K] (row stride ldb);          b_mn == 1: B stored [K][N].
 // Requirements: base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
-extern "C" int llmt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                              int64_t ldc, int a_mn, int b_mn, int out_f32, int accumulate, int* status, int max_ctas,
-                              cudaStream_t stream) {
+static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_mn,
+                     int b_mn, int out_f32, int accumulate, int* status, int max_ctas, cudaStream_t stream, const SideJob* side) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -10;
   const bool bn256 = N > 128;
@@ -415,8 +423,34 @@ extern "C" int llmt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     str[0] = (uint64_t)ldb * 2;
     if (make_tmap_bf16(&tb, B, 2, dims, str, box)) return -12;
   }
-  if (bn256) return dispatch_plain<256>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream);
-  return dispatch_plain<128>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream);
+  if (bn256) return dispatch_plain<256>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream, side);
+  return dispatch_plain<128>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream, side);
+}
+
+extern "C" int llmt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                              int64_t ldc, int a_mn, int b_mn, int out_f32, int accumulate, int* status, int max_ctas,
+                              cudaStream_t stream) {
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, accumulate, status, max_ctas, stream, nullptr);
+}
+
+// Same product, with a slice of a peer-memory collective carried by the comm warps of every CTA (see comm.cuh).
+extern "C" int llmt_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                    int64_t ldc, int a_mn, int b_mn, int out_f32, int accumulate, int job_kind, int job_nsrc,
+                                    const void* const* job_src, void* job_dst, long long job_n, int job_accumulate,
+                                    const uint32_t* wait_flags, int n_wait, uint32_t wait_value, int* status,
+                                    cudaStream_t stream) {
+  SideJob j{};
+  j.kind = job_kind;
+  j.nsrc = job_nsrc;
+  for (int i = 0; i < kMaxPeers; ++i) j.src[i] = (i < job_nsrc) ? job_src[i] : nullptr;
+  j.dst = job_dst;
+  j.n = job_n;
+  j.accumulate = job_accumulate;
+  j.wait_flags = wait_flags;
+  j.n_wait = n_wait;
+  j.wait_value = wait_value;
+  if (job_kind != kSideNone && (job_nsrc < 1 || job_nsrc > kMaxPeers)) return -10;
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, accumulate, status, 0, stream, &j);
 }
 
 // Grouped forward/dgrad: rows of A (and C) are cut into `num_groups` segments at seg_offsets (device int32,

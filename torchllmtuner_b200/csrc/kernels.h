@@ -12,6 +12,10 @@ extern "C" {
 // ---- GEMM family (gemm.cu) ----
 int llmt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                    int a_mn, int b_mn, int out_f32, int accumulate, int* status, int max_ctas, cudaStream_t stream);
+int llmt_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                         int a_mn, int b_mn, int out_f32, int accumulate, int job_kind, int job_nsrc,
+                         const void* const* job_src, void* job_dst, long long job_n, int job_accumulate,
+                         const uint32_t* wait_flags, int n_wait, uint32_t wait_value, int* status, cudaStream_t stream);
 int llmt_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* seg_offsets, int num_groups, int M_padded,
                            int N, int K, int64_t lda, int64_t ldc, int b_mn, int out_f32, int* status,
                            cudaStream_t stream);
@@ -44,6 +48,12 @@ int llmt_adamw(float* p32, void* p16, const void* g, int g_is_bf16, float* m, fl
 int llmt_sqnorm_scratch_floats();
 int llmt_sqnorm(const void* x, int is_bf16, int64_t n, float* scratch, float* out, int accumulate, cudaStream_t st);
 int llmt_clip_coef(const float* total_sq, float max_norm, float* clip_coef, float* norm_out, int* finite, cudaStream_t st);
+
+// ---- peer-memory communication (comm.cu) ----
+int llmt_side_job(int kind, int nsrc, const void* const* src, void* dst, long long n, int accumulate,
+                  const uint32_t* wait_flags, int n_wait, uint32_t wait_value, int ctas, int* status, cudaStream_t st);
+int llmt_signal_peers(uint32_t* const* peer_flags, int npeers, int slot, uint32_t value, cudaStream_t st);
+int llmt_wait_flags(const uint32_t* flags, int n, uint32_t value, int site, int* status, cudaStream_t st);
 
 // ---- attention (attention.cu) ----
 // q [Tq, Hq, HD], k/v [Tk, Hkv, HD] bf16 with token strides in elements; varlen via cu_seqlens (device int32).

@@ -15,6 +15,11 @@ from .cuda_ext import load as _ext
 IGNORE_INDEX = ref.IGNORE_INDEX
 
 
+def _comm_queue():
+    from ..parallel import symm
+    return symm._ACTIVE
+
+
 def _use_cuda(t: torch.Tensor) -> bool:
     return t.is_cuda
 
@@ -36,6 +41,17 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=F
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+    q = _comm_queue()
+    if q:                                   # a pending peer-memory collective rides on this kernel's comm warps
+        K = a.shape[0] if a_mn else a.shape[1]
+        s, callbacks = q.take(2.0 * M * N * K)
+        if s is not None:
+            ext = _ext()
+            from ..parallel.symm import make_side_job
+            ext.gemm(a, b, out, a_mn, b_mn, accumulate, 0, make_side_job(ext, s))
+            for cb in callbacks:
+                cb()
+            return out
     _ext().gemm(a, b, out, a_mn, b_mn, accumulate, max_ctas)
     return out
 

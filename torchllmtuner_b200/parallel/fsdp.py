@@ -233,7 +233,7 @@ class FSDPRuntime:
                     prev.gathered = False
                 self._slot_owner[key] = u
             if self.fused is not None and self.fused.supports(u):
-                self.fused.all_gather(u)
+                self.fused.all_gather(u)       # queued; carried by the GEMMs launched from here on
             else:
                 if self.comm_stream is not None:
                     self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -242,6 +242,8 @@ class FSDPRuntime:
                     if self.comm_stream is not None:
                         u.gather_event = self.comm_stream.record_event()
             u.gathered = True
+        if wait and self.fused is not None and self.fused.supports(u):
+            self.fused.wait_gather(u)          # finish what no GEMM carried
         if wait and u.gather_event is not None:
             torch.cuda.current_stream().wait_event(u.gather_event)
             u.gather_event = None
@@ -297,6 +299,10 @@ class FSDPRuntime:
 
     def before_block_backward(self, i: int) -> None:
         """The gradient slot about to be written may still be read by an earlier reduce-scatter."""
+        if self.fused is not None:
+            for u in self._units(i):
+                if self.fused.supports(u):
+                    self.fused.before_grad_write(u)
         if self.comm_stream is None:
             return
         for u in self._units(i):
@@ -319,6 +325,8 @@ class FSDPRuntime:
 
     def wait_reductions(self) -> None:
         """Make the compute stream see every reduce-scattered gradient (called before clipping / the optimizer)."""
+        if self.fused is not None:
+            self.fused.flush_all()
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         if self.replicate_group is not None and self.is_last_microbatch:
@@ -328,6 +336,8 @@ class FSDPRuntime:
 
     def post_optimizer(self) -> None:
         """After the optimizer rewrote the shards: zero gradient state, refresh persistent full copies."""
+        if self.fused is not None:
+            self.fused.step_barrier()
         for u in self.units:
             u.has_grad = False
             for p in u.params:
@@ -504,6 +514,8 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
         named_units["rest"] = rt.add_unit("rest", rest)
     rt.named_units = {k: v for k, v in named_units.items() if v is not None}
     rt.finalize(init_fn=init_fn, needs_init=needs_init)
+    from .symm import enable_fused_fsdp
+    enable_fused_fsdp(rt)
     model.block_runner = rt.run_block
     model.fsdp_runtime = rt
     return rt
