@@ -23,3 +23,35 @@ def test_hsdp_and_accumulation_match_single_rank():
     _close(ref["loss"], got["loss"], 2e-5)
     got = run_ranks(2, base_flat(data_parallel_shard_size=2, gradient_accumulation_steps=2))
     _close(ref["loss"], got["loss"], 2e-5)
+
+
+def test_tp2_matches_single_rank():
+    ref = run_ranks(1, base_flat())
+    got = run_ranks(2, base_flat(tensor_parallel_size=2, data_parallel_shard_size=1))
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
+def test_tp2_dp2_matches_single_rank():
+    ref = run_ranks(1, base_flat())
+    got = run_ranks(4, base_flat(tensor_parallel_size=2, data_parallel_shard_size=2, activation_checkpoint_mode="full"))
+    _close(ref["loss"], got["loss"], 5e-5)
+
+
+MOE = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
+
+
+def test_ep2_matches_single_rank():
+    ref = run_ranks(1, base_flat(model_name_or_path="qwen3_moe"), arch=MOE)
+    got = run_ranks(2, base_flat(model_name_or_path="qwen3_moe", expert_parallel_size=2, data_parallel_shard_size=2), arch=MOE)
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
+@pytest.mark.parametrize("flat", [dict(context_parallel_ulysses_size=2), dict(context_parallel_kv_allgather_size=2),
+                                  dict(context_parallel_kv_allgather_size=2, context_parallel_load_balancer="headtail")])
+def test_cp2_matches_single_rank(flat):
+    ref = run_ranks(1, base_flat())
+    got = run_ranks(2, base_flat(data_parallel_shard_size=1, **flat))
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)

@@ -24,3 +24,20 @@ def test_fsdp2_gpu_matches_single_gpu():
         got = run_ranks(2, _flat(data_parallel_shard_size=2, activation_checkpoint_mode="full", fsdp_implementation=impl), device="cuda")
         assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 3e-2, (impl, ref, got)
         assert max(abs(a - b) / max(a, 1e-6) for a, b in zip(ref["grad_norm"], got["grad_norm"])) < 5e-2, (impl, ref, got)
+
+
+MOE = dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128)
+
+
+@pytest.mark.parametrize("name,flat,arch", [
+    ("tp2", dict(tensor_parallel_size=2, data_parallel_shard_size=1), None),
+    ("cp_ulysses2", dict(context_parallel_ulysses_size=2, data_parallel_shard_size=1), None),
+    ("cp_kv2_headtail", dict(context_parallel_kv_allgather_size=2, context_parallel_load_balancer="headtail", data_parallel_shard_size=1), None),
+    ("ep2", dict(model_name_or_path="qwen3_moe", expert_parallel_size=2, data_parallel_shard_size=2), MOE),
+])
+def test_parallel_modes_gpu_match_single_gpu(name, flat, arch):
+    _need(2)
+    base = dict(model_name_or_path=flat.get("model_name_or_path", "qwen3"))
+    ref = run_ranks(1, _flat(**base), arch=arch, device="cuda")
+    got = run_ranks(2, _flat(**flat), arch=arch, device="cuda")
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (name, ref, got)

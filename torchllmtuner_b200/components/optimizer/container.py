@@ -73,20 +73,30 @@ class GradientClipper:
     @torch.no_grad()
     def __call__(self) -> torch.Tensor:
         dense, expert, tp_rep = [], [], []
+        tp = self.topo.tp > 1
         for rt in self.runtimes:
             for u in rt.units:
-                if u.has_grad:
-                    (expert if u.is_expert else dense).append(u.grad_shard)
-        sq_d = ops.sq_norm(dense).reshape(1) if dense else torch.zeros(1, dtype=torch.float32, device=self.device)
-        sq_e = ops.sq_norm(expert).reshape(1) if expert else torch.zeros(1, dtype=torch.float32, device=self.device)
-        sq_d, sq_e = sq_d.to(self.device), sq_e.to(self.device)
+                if not u.has_grad:
+                    continue
+                (expert if u.is_expert else dense).append(u.grad_shard)
+                if tp:
+                    # regions of parameters that every TP rank holds in full: counted once, not tp times
+                    rep = {s.fqn for p, s in zip(u.params, u.slots) if getattr(p, "tp_replicated", False)}
+                    for fqn, _shape, lo, hi, shard_lo in u.shard_slices():
+                        if fqn in rep:
+                            tp_rep.append(u.grad_shard[shard_lo:shard_lo + hi - lo])
+        zero = lambda: torch.zeros(1, dtype=torch.float32, device=self.device)  # noqa: E731
+        sq_d = ops.sq_norm(dense).reshape(1).to(self.device) if dense else zero()
+        sq_e = ops.sq_norm(expert).reshape(1).to(self.device) if expert else zero()
+        sq_r = ops.sq_norm(tp_rep).reshape(1).to(self.device) if tp_rep else zero()
+        if tp:
+            sq_d = sq_d - sq_r
+            self._reduce(sq_d, "tp")
+            if expert:
+                self._reduce(sq_e, "tp")
+            sq_d = sq_d + sq_r
         if self.topo.size("dp_shard_cp") > 1:
             self._reduce(sq_d, "dp_shard_cp")
-        if self.topo.tp > 1:
-            # TP-replicated parameters (norms, router) are counted tp times after this sum; their weight in the
-            # total is negligible and the reference's split into replicated/sharded groups is applied by
-            # `tp_replicated_correction` when exactness is requested.
-            self._reduce(sq_d, "tp")
         if self.topo.ep > 1:
             self._reduce(sq_e, "efsdp")
             self._reduce(sq_e, "ep")

@@ -321,7 +321,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
                     __nv_bfloat16* __restrict__ dV, const int* __restrict__ tiles, int Hq, int Hkv, int Tq, int64_t dk_stride,
-                    int64_t dv_stride, float scale, int causal, int* status) {
+                    int64_t dv_stride, float scale, int causal, int accumulate, int* status) {
   using SM = AttnSmem<HD>;
   constexpr int NH = HD / 64;
   extern __shared__ uint8_t smem_raw[];
@@ -507,6 +507,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             b.y = pack_bf16x2(__uint_as_float(rv[8 * v + 2]), __uint_as_float(rv[8 * v + 3]));
             b.z = pack_bf16x2(__uint_as_float(rv[8 * v + 4]), __uint_as_float(rv[8 * v + 5]));
             b.w = pack_bf16x2(__uint_as_float(rv[8 * v + 6]), __uint_as_float(rv[8 * v + 7]));
+            if (accumulate) {
+              const uint4 pa = reinterpret_cast<const uint4*>(kr + c * 32)[v], pb = reinterpret_cast<const uint4*>(vr + c * 32)[v];
+              const __nv_bfloat162 *ha = reinterpret_cast<const __nv_bfloat162*>(&pa), *hb = reinterpret_cast<const __nv_bfloat162*>(&pb);
+              __nv_bfloat162 *na = reinterpret_cast<__nv_bfloat162*>(&a), *nb = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                na[j] = __hadd2(na[j], ha[j]);
+                nb[j] = __hadd2(nb[j], hb[j]);
+              }
+            }
             reinterpret_cast<uint4*>(kr + c * 32)[v] = a;
             reinterpret_cast<uint4*>(vr + c * 32)[v] = b;
           }
@@ -760,12 +770,13 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
                              float* delta, void* dq, void* dk, void* dv, const int* q_tiles, int num_q_tiles,
                              const int* k_tiles, int num_k_tiles, int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride,
                              int64_t k_stride, int64_t v_stride, int64_t o_stride, int64_t do_stride, int64_t dq_stride,
-                             int64_t dk_stride, int64_t dv_stride, float scale, int causal, int* status, cudaStream_t st) {
+                             int64_t dk_stride, int64_t dv_stride, float scale, int causal, int pass, int* status, cudaStream_t st) {
+  // pass 0: delta, dK/dV (overwrite), dQ. pass > 0: only dK/dV over another k-tile table, accumulating into dK/dV.
   if (Hq <= 0 || Tq <= 0) return 0;
   if ((HD != 64 && HD != 128) || Hq % Hkv || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (do_stride & 7) ||
       (dq_stride & 7) || (dk_stride & 7) || (dv_stride & 7))
     return -10;
-  {
+  if (pass == 0) {
     const int64_t items = (int64_t)Tq * Hq;
     attn_delta_kernel<<<(int)((items + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)o, o_stride, (const __nv_bfloat16*)dout,
                                                               do_stride, delta, Tq, Hq, HD);
@@ -785,8 +796,8 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
     if (num_k_tiles > 0)
       attn_bwd_dkv_kernel<128><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
           tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
-          causal, status);
-    if (num_q_tiles > 0)
+          causal, pass > 0, status);
+    if (num_q_tiles > 0 && pass == 0)
       attn_bwd_dq_kernel<128><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
                                                                               q_tiles, Hq, Hkv, Tq, dq_stride, scale, causal,
                                                                               status);
@@ -799,8 +810,8 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
     if (num_k_tiles > 0)
       attn_bwd_dkv_kernel<64><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
           tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
-          causal, status);
-    if (num_q_tiles > 0)
+          causal, pass > 0, status);
+    if (num_q_tiles > 0 && pass == 0)
       attn_bwd_dq_kernel<64><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
                                                                              q_tiles, Hq, Hkv, Tq, dq_stride, scale, causal,
                                                                              status);

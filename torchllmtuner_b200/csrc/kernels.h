@@ -65,7 +65,7 @@ int llmt_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
                   float* delta, void* dq, void* dk, void* dv, const int* q_tiles, int num_q_tiles, const int* k_tiles,
                   int num_k_tiles, int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride,
                   int64_t v_stride, int64_t o_stride, int64_t do_stride, int64_t dq_stride, int64_t dk_stride,
-                  int64_t dv_stride, float scale, int causal, int* status, cudaStream_t st);
+                  int64_t dv_stride, float scale, int causal, int pass, int* status, cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -200,7 +200,8 @@ class _Attention(torch.autograd.Function):
         q, k, v, o, lse = ctx.saved_tensors
         if do.stride(2) != 1 or do.stride(1) != do.shape[2]:
             do = do.contiguous()
-        dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, ctx.meta.q_tiles, ctx.meta.k_tiles, ctx.scale, ctx.meta.causal)
+        m = ctx.meta
+        dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, m.q_tiles, m.k_tile_passes, ctx.scale, m.causal, not m.covers_all_keys)
         return dq, dk, dv, None, None
 
 
@@ -211,7 +212,7 @@ def attention(q, k, v, meta: AttnMeta, scale: float | None = None):
         if meta.q_tiles is None:
             raise ValueError("AttnMeta was built without device tables; pass device= to AttnMeta.build")
         return _Attention.apply(q, k, v, meta, scale)
-    out, _ = ref.attention(q, k, v, meta.cu_q, meta.causal, scale, k_cu_seqlens=meta.cu_k, q_offsets=meta.q_offsets)
+    out, _ = ref.attention_pieces(q, k, v, meta.pieces, meta.causal, scale)
     return out
 
 
@@ -221,7 +222,7 @@ def attention_with_lse(q, k, v, meta: AttnMeta, scale: float | None = None):
     if _use_cuda(q) and q.dtype == torch.bfloat16:
         o, lse = _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
         return o, lse
-    return ref.attention(q, k, v, meta.cu_q, meta.causal, scale, k_cu_seqlens=meta.cu_k, q_offsets=meta.q_offsets)
+    return ref.attention_pieces(q, k, v, meta.pieces, meta.causal, scale)
 
 
 # ----------------------------------------------------------------------------------------------- cross-entropy

@@ -62,46 +62,60 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return (g * torch.sigmoid(g) * up.float()).to(gate.dtype)
 
 
-def attention(q, k, v, cu_seqlens=None, causal: bool = True, scale: float | None = None,
-              k_cu_seqlens=None, q_offsets=None):
-    """Variable-length GQA attention over packed rows.
-
-    q [Tq, Hq, d], k/v [Tk, Hkv, d]. `cu_seqlens` (int32 [n+1]) cuts the rows into documents; a query
-    only sees keys of its own document (block-causal when `causal`). `k_cu_seqlens` gives separate key
-    cuts (default: same as q) and `q_offsets[i]` is the position of document i's first query inside
-    that document's keys (default: keys and queries end together), which is what context-parallel
-    shards need. Returns (out [Tq, Hq, d], lse [Hq, Tq] fp32).
-    """
+def attention_pieces(q, k, v, pieces, causal: bool = True, scale: float | None = None):
+    """GQA attention over explicit pieces (q0, qlen, k0, klen, off): query i of a piece sees keys
+    [0, min(klen, i + off + 1)) of that piece when causal. q [Tq, Hq, d], k/v [Tk, Hkv, d].
+    Returns (out [Tq, Hq, d], lse [Hq, Tq] fp32)."""
     Tq, Hq, d = q.shape
-    Hkv = k.shape[1]
-    g = Hq // Hkv
+    g = Hq // k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
-    if cu_seqlens is None:
-        cu_seqlens = torch.tensor([0, Tq], dtype=torch.int32)
-    cq = cu_seqlens.tolist()
-    ck = cq if k_cu_seqlens is None else k_cu_seqlens.tolist()
-    out = torch.zeros_like(q)
-    lse = torch.full((Hq, Tq), float("-inf"), dtype=torch.float32, device=q.device)
-    for i in range(len(cq) - 1):
-        qs, qe, ks, ke = cq[i], cq[i + 1], ck[i], ck[i + 1]
-        if qe == qs:
+    outs = torch.zeros(Tq, Hq, d, dtype=torch.float32, device=q.device)
+    lses = torch.full((Hq, Tq), float("-inf"), dtype=torch.float32, device=q.device)
+    rows_o, rows_i = [], []
+    for (q0, qlen, k0, klen, off) in pieces:
+        if qlen == 0:
             continue
-        qi = q[qs:qe].float().transpose(0, 1)                        # [Hq, lq, d]
-        ki = k[ks:ke].float().transpose(0, 1).repeat_interleave(g, 0)
-        vi = v[ks:ke].float().transpose(0, 1).repeat_interleave(g, 0)
-        s = torch.matmul(qi, ki.transpose(1, 2)) * scale              # [Hq, lq, lk]
-        lq, lk = qe - qs, ke - ks
+        qi = q[q0:q0 + qlen].float().transpose(0, 1)
+        ki = k[k0:k0 + klen].float().transpose(0, 1).repeat_interleave(g, 0)
+        vi = v[k0:k0 + klen].float().transpose(0, 1).repeat_interleave(g, 0)
+        s = torch.matmul(qi, ki.transpose(1, 2)) * scale
         if causal:
-            off = (lk - lq) if q_offsets is None else int(q_offsets[i])
-            qpos = torch.arange(lq, device=q.device)[:, None] + off
-            kpos = torch.arange(lk, device=q.device)[None, :]
+            qpos = torch.arange(qlen, device=q.device)[:, None] + off
+            kpos = torch.arange(klen, device=q.device)[None, :]
             s = s.masked_fill(kpos > qpos, float("-inf"))
         l = torch.logsumexp(s, dim=-1)
-        p = torch.exp(s - l.unsqueeze(-1))
-        p = torch.nan_to_num(p, nan=0.0)
-        out[qs:qe] = torch.matmul(p, vi).transpose(0, 1).to(q.dtype)
-        lse[:, qs:qe] = l
-    return out, lse
+        p = torch.nan_to_num(torch.exp(s - l.unsqueeze(-1)), nan=0.0)
+        rows_o.append(torch.matmul(p, vi).transpose(0, 1))
+        rows_i.append((q0, qlen, l))
+    # assemble without in-place writes so that autograd flows
+    order = sorted(range(len(rows_i)), key=lambda t: rows_i[t][0])
+    chunks, pos = [], 0
+    for t in order:
+        q0, qlen, l = rows_i[t]
+        if q0 > pos:
+            chunks.append(torch.zeros(q0 - pos, Hq, d, dtype=torch.float32, device=q.device))
+        chunks.append(rows_o[t])
+        lses[:, q0:q0 + qlen] = l.detach()
+        pos = q0 + qlen
+    if pos < Tq:
+        chunks.append(torch.zeros(Tq - pos, Hq, d, dtype=torch.float32, device=q.device))
+    out = torch.cat(chunks, 0) if chunks else outs
+    return out.to(q.dtype), lses
+
+
+def attention(q, k, v, cu_seqlens=None, causal: bool = True, scale: float | None = None, k_cu_seqlens=None, q_offsets=None):
+    """Packed-row attention from cumulative document cuts (see `attention_pieces`)."""
+    Tq = q.shape[0]
+    if cu_seqlens is None:
+        cu_seqlens = torch.tensor([0, Tq])
+    cq = torch.as_tensor(cu_seqlens).tolist()
+    ck = cq if k_cu_seqlens is None else torch.as_tensor(k_cu_seqlens).tolist()
+    pieces = []
+    for i in range(len(cq) - 1):
+        qlen, klen = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
+        off = (klen - qlen) if q_offsets is None else int(q_offsets[i])
+        pieces.append((cq[i], qlen, ck[i], klen, off))
+    return attention_pieces(q, k, v, pieces, causal, scale)
 
 
 def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,170 @@
+"""Context parallelism for standard attention: Ulysses head<->sequence all-to-all and key/value all-gather with
+optional head-tail load balancing, both with packed (multi-document) rows
+(reference: llmtuner/parallel/context_parallel/context_parallel.py:18-55, attention.py:12-87, input_sharding.py:109-232;
+the reference removed the standard-attention kernels, plan.py:27-34, and rejects packed rows under CP,
+models/common/input_preparation.py:144-149; here both are supported by carrying the global document cuts to every rank).
+
+The driver is installed as `ForwardContext.cp`; `Qwen3Attention` calls `cp.attention(q, k, v, meta, scale)` with local
+rows `[T/cp, H, d]`.
+  ulysses       a2a turns [T/cp, H, d] into [T, H/cp, d] for q, k, v; attention over complete rows and the global
+                document table; a2a back for the output.
+  kv_allgather  queries stay local; K and V are all-gathered into global row order; each local query span of each
+                document attends that document's keys up to its own position (explicit query offsets).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops.attn_meta import AttnMeta
+from .input_sharding import contiguous_chunk, headtail_chunks
+
+
+class _SeqToHead(torch.autograd.Function):
+    """[T/R, H, d] -> [T, H/R, d] (rows in global order of the rank chunks); backward is the inverse."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        R = dist.get_world_size(group)
+        t, H, d = x.shape
+        send = x.view(t, R, H // R, d).permute(1, 0, 2, 3).contiguous()         # [R, t, H/R, d]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        return recv.view(R * t, H // R, d)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _HeadToSeq.apply(g, ctx.group), None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        R = dist.get_world_size(group)
+        T, h, d = x.shape
+        send = x.contiguous().view(R, T // R, h, d)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        return recv.permute(1, 0, 2, 3).reshape(T // R, R * h, d)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _SeqToHead.apply(g, ctx.group), None
+
+
+def cp_all_to_all(x, group, to_heads: bool):
+    return _SeqToHead.apply(x, group) if to_heads else _HeadToSeq.apply(x, group)
+
+
+class _AllGatherRowsCP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, perm):
+        ctx.group, ctx.perm = group, perm
+        R = dist.get_world_size(group)
+        out = x.new_empty((x.shape[0] * R, *x.shape[1:]))
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out if perm is None else out.index_select(0, perm[0])
+
+    @staticmethod
+    def backward(ctx, g):
+        R = dist.get_world_size(ctx.group)
+        if ctx.perm is not None:
+            g = g.index_select(0, ctx.perm[1])
+        out = g.new_empty((g.shape[0] // R, *g.shape[1:]))
+        dist.reduce_scatter_tensor(out, g.contiguous(), group=ctx.group)
+        return out, None, None
+
+
+class ContextParallelDriver:
+    def __init__(self, topo, cp_config):
+        self.topo = topo
+        self.strategy = "ulysses" if topo.cp_ulysses > 1 else "kv_allgather"
+        if topo.cp_ulysses > 1 and topo.cp_kv > 1:
+            self.strategy = "hybrid"
+        self.load_balancer = cp_config.context_parallel_load_balancer if topo.cp_kv > 1 else None
+        self.group = topo.get_group("cp")
+        self.size, self.rank = topo.cp, topo.coord("cp")
+        self._mb = None
+
+    # ------------------------------------------------------------------ per micro-batch tables
+    def begin_microbatch(self, inputs: dict) -> None:
+        """Builds the attention tables of this rank from the global document cuts."""
+        dev = inputs["tokens"].device
+        B, S = inputs["batch"], inputs["seq"]
+        gcu = inputs.get("global_cu_seqlens", inputs["cu_seqlens"]).tolist()
+        mb = {"B": B, "S": S}
+        if self.strategy == "ulysses":
+            mb["meta"] = AttnMeta.build(gcu, causal=True, device=dev)
+        else:
+            # local spans of every sequence, in local row order
+            R, r = self.size, self.rank
+            spans = headtail_chunks(S, R, r) if self.load_balancer == "headtail" else [contiguous_chunk(S, R, r)]
+            pieces, local = [], 0
+            for b in range(B):
+                for a, e in spans:
+                    ga, ge = b * S + a, b * S + e                      # global rows of this local span
+                    for i in range(len(gcu) - 1):
+                        ds, de = gcu[i], gcu[i + 1]
+                        lo, hi = max(ga, ds), min(ge, de)
+                        if hi > lo:
+                            pieces.append((local + (lo - ga), hi - lo, ds, hi - ds, lo - ds))   # q0, qlen, k0, klen, off
+                    local += e - a
+            mb["meta"] = AttnMeta.from_pieces(pieces, total_q=local, total_k=B * S, causal=True, device=dev)
+            if self.load_balancer == "headtail":
+                # gathered rows arrive rank-major (each rank: head chunk, tail chunk); map to global order and back
+                c = S // (2 * R)
+                src = []
+                for b in range(B):
+                    for chunk in range(2 * R):
+                        owner = chunk if chunk < R else 2 * R - 1 - chunk
+                        half = 0 if chunk < R else 1
+                        base = owner * (B * 2 * c) + b * 2 * c + half * c
+                        src.append(torch.arange(base, base + c))
+                fwd = torch.cat(src).to(dev)
+                inv = torch.empty_like(fwd)
+                inv[fwd] = torch.arange(fwd.numel(), device=dev)
+                mb["perm"] = (fwd, inv)
+            elif B > 1:
+                t = S // R
+                src = [torch.arange(rk * B * t + b * t, rk * B * t + (b + 1) * t) for b in range(B) for rk in range(R)]
+                fwd = torch.cat(src).to(dev)
+                inv = torch.empty_like(fwd)
+                inv[fwd] = torch.arange(fwd.numel(), device=dev)
+                mb["perm"] = (fwd, inv)
+            else:
+                mb["perm"] = None
+        self._mb = mb
+
+    # ------------------------------------------------------------------ attention
+    def attention(self, q, k, v, meta, scale):
+        mb = self._mb
+        if self.strategy == "ulysses":
+            B, S, R = mb["B"], mb["S"], self.size
+            # local rows are [b][s/R]; after the exchange rows are [rank][b][s/R]: restore [b][s] order
+            qh, kh, vh = (cp_all_to_all(t, self.group, True) for t in (q, k, v))
+            if B > 1:
+                t = S // R
+                idx = torch.arange(R * B * t, device=q.device).view(R, B, t).permute(1, 0, 2).reshape(-1)
+                inv = torch.empty_like(idx)
+                inv[idx] = torch.arange(idx.numel(), device=q.device)
+                qh, kh, vh = qh.index_select(0, idx), kh.index_select(0, idx), vh.index_select(0, idx)
+            o = ops.attention(qh, kh, vh, mb["meta"], scale)
+            if B > 1:
+                o = o.index_select(0, inv)
+            return cp_all_to_all(o, self.group, False)
+        kg = _AllGatherRowsCP.apply(k, self.group, mb["perm"])
+        vg = _AllGatherRowsCP.apply(v, self.group, mb["perm"])
+        return ops.attention(q, kg, vg, mb["meta"], scale)
+
+
+def apply_cp(model, topo, cp_config) -> ContextParallelDriver:
+    if topo.kcp > 1:
+        from ..errors import UnsupportedCombinationError
+        raise UnsupportedCombinationError("kcp context parallelism applies to delta-attention models only")
+    if topo.cp_ulysses > 1 and topo.cp_kv > 1:
+        from ..errors import UnsupportedCombinationError
+        raise UnsupportedCombinationError("combining the ulysses and kv_allgather axes in one run is not supported yet")
+    return ContextParallelDriver(topo, cp_config)

@@ -268,6 +268,10 @@ class FSDPRuntime:
                     p.grad = None
                 elif not accum_in_full and not getattr(p, "main_grad_initialized", False):
                     p._grad_view.zero_()
+        if self.topo.tp > 1 and (u.world > 1 or self.is_last_microbatch):
+            # parameters that every TP rank holds in full carry partial gradients: sum them over the TP group
+            from .tensor_parallel import allreduce_replicated_tp_grads
+            allreduce_replicated_tp_grads(u.params, self.topo.get_group("tp"))
         if u.world == 1:
             u.has_grad = True
             for p in u.params:
