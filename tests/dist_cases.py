@@ -17,19 +17,29 @@ def base_flat(**over):
 
 
 def train_case(flat: dict, arch: dict | None, out_path: str, steps: int = 3, repeat_batch: bool = True):
+    """Special keys in `flat` (removed before the config is built): `_load` resumes from the run folder first,
+    `_save_at` saves a full checkpoint after that many steps."""
     from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    flat = dict(flat)
+    do_load, save_at = flat.pop("_load", False), flat.pop("_save_at", None)
     cfg = LLMTunerConfig()
     cfg.apply_flat(flat)
     if arch:
         cfg.model.arch_overrides = arch
     tr = Trainer(cfg)
+    if do_load:
+        assert tr.checkpointer.load()
     losses, norms = [], []
-    for _ in range(steps):
+    for i in range(steps):
+        if save_at is not None and i == save_at:
+            tr.checkpointer.save(tr.progress.step, force=True)
         if repeat_batch:
             tr.dataloader.cursor = 0
         r = tr.train_step()
         losses.append(r.loss)
         norms.append(r.grad_norm)
+    if save_at is not None and save_at >= steps:
+        tr.checkpointer.save(tr.progress.step, force=True)
     if int(os.environ.get("RANK", "0")) == 0:
         with open(out_path, "w") as f:
             json.dump({"loss": losses, "grad_norm": norms}, f)

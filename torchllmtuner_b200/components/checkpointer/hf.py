@@ -1,0 +1,171 @@
+"""Hugging Face safetensors import / export (reference: llmtuner/components/checkpointer/model_state.py:30-283,
+hf/hf_storage.py:38-190, hf/hf_expert_storage.py:22-131).
+
+Import: every rank opens the indexed safetensors files lazily and copies exactly the element ranges its flat shards
+own (per-expert HF tensors are stitched into the packed native expert tensors on the fly).
+Export: every rank writes the HF tensors (or contiguous parts of them) it owns into its own
+`model-<rank>-of-<world>.safetensors`... which HF cannot read when a tensor is split, so instead the ranks hand their
+ranges to rank 0 tensor by tensor (point-to-point gathers of one parameter at a time), and rank 0 writes complete
+tensors into size-bounded shards, then publishes `model.safetensors.index.json` and `config.json` atomically by
+renaming a `.export-<id>` staging folder."""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+import uuid
+
+import torch
+import torch.distributed as dist
+
+from ...errors import ConfigError
+from ...models.state import get_state_format
+from .dcp_manager import iter_pieces
+
+_DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+
+
+def read_hf_weight_map(path: str) -> dict[str, str]:
+    idx = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(idx):
+        with open(idx) as f:
+            return json.load(f)["weight_map"]
+    single = os.path.join(path, "model.safetensors")
+    if os.path.exists(single):
+        from safetensors import safe_open
+        with safe_open(single, "pt") as f:
+            return {k: "model.safetensors" for k in f.keys()}
+    raise ConfigError(f"{path} holds neither model.safetensors.index.json nor model.safetensors")
+
+
+def _param_index(trainer):
+    out = {}
+    for u in trainer.asm.fsdp.units:
+        for p, s in zip(u.params, u.slots):
+            out[s.fqn.replace(".inner.", ".")] = (p, s)
+    return out
+
+
+def _full_shape(p, s):
+    shape = list(s.shape)
+    if getattr(p, "ep_sharded", False):
+        shape[0] = p.ep_full_experts
+    if hasattr(p, "tp_full_shape") and not getattr(p, "ep_sharded", False):
+        shape = list(p.tp_full_shape)
+    return shape
+
+
+def load_hf_checkpoint(trainer, path: str) -> None:
+    from safetensors import safe_open
+    fmt = get_state_format(getattr(trainer, "state_format", "qwen3"))
+    wmap = read_hf_weight_map(path)
+    handles: dict[str, object] = {}
+
+    def tensor(name):
+        fn = wmap.get(name)
+        if fn is None:
+            raise ConfigError(f"HF checkpoint {path} lacks tensor {name}")
+        if fn not in handles:
+            handles[fn] = safe_open(os.path.join(path, fn), "pt")
+        return handles[fn].get_tensor(name)
+
+    pidx = _param_index(trainer)
+    with torch.no_grad():
+        for fqn, tag, glo, ghi, u, slo in iter_pieces(trainer.asm.fsdp):
+            if tag:
+                raise ConfigError(f"HF import of {fqn}: parameters cut along a later dimension need tensor_parallel_size 1")
+            p, s = pidx[fqn]
+            for piece in fmt.to_hf(fqn, _full_shape(p, s)):
+                a, b = max(glo, piece.native_flat_lo), min(ghi, piece.native_flat_hi)
+                if b <= a:
+                    continue
+                src = tensor(piece.hf_name).reshape(-1)[a - piece.native_flat_lo:b - piece.native_flat_lo]
+                u.master[slo + (a - glo): slo + (b - glo)].copy_(src.float())
+        for u in trainer.asm.fsdp.units:
+            if u.separate_master:
+                u.shard_lowp.copy_(u.master)
+            if u.world > 1:
+                u.gathered = False
+                if getattr(u, "persistent", False):
+                    trainer.asm.fsdp.unshard(u)
+
+
+def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", max_shard_bytes: int = 5 << 30) -> None:
+    from safetensors.torch import save_file
+    rank, world = trainer.env.rank, trainer.env.world_size
+    fmt = get_state_format(getattr(trainer, "state_format", "qwen3"))
+    dt = _DT[export_dtype]
+    pidx = _param_index(trainer)
+    mine: dict[str, list] = {}
+    for fqn, tag, glo, ghi, u, slo in iter_pieces(trainer.asm.fsdp):
+        if tag:
+            raise ConfigError(f"HF export of {fqn}: parameters cut along a later dimension need tensor_parallel_size 1")
+        mine.setdefault(fqn, []).append((glo, ghi, u.master[slo:slo + ghi - glo]))
+    # which canonical FQNs exist anywhere, with their full shapes (identical on all ranks except expert slices)
+    table = {fqn: _full_shape(*pidx[fqn]) for fqn in pidx}
+    if world > 1:
+        tables = [None] * world
+        dist.all_gather_object(tables, table)
+        for t in tables:
+            table.update(t)
+    stage = f"{out_dir}.export-{uuid.uuid4().hex[:8]}" if rank == 0 else None
+    if rank == 0:
+        os.makedirs(stage, exist_ok=True)
+    shard, shard_bytes, shard_files, weight_map = {}, 0, [], {}
+
+    def flush():
+        nonlocal shard, shard_bytes
+        if shard:
+            name = f"model-{len(shard_files) + 1:05d}.safetensors"
+            save_file(shard, os.path.join(stage, name), metadata={"format": "pt"})
+            shard_files.append((name, list(shard)))
+            shard, shard_bytes = {}, 0
+
+    for fqn in sorted(table):
+        shape = table[fqn]
+        numel = 1
+        for x in shape:
+            numel *= x
+        parts = [(lo, hi, t.detach().to("cpu", torch.float32)) for lo, hi, t in mine.get(fqn, [])]
+        if world > 1:
+            gathered = [None] * world if rank == 0 else None
+            dist.gather_object(parts, gathered, dst=0)
+            parts = [x for g in gathered for x in g] if rank == 0 else []
+        if rank != 0:
+            continue
+        full = torch.zeros(numel, dtype=torch.float32)
+        seen = 0
+        for lo, hi, t in parts:
+            hi = min(hi, numel)
+            if hi > lo:
+                full[lo:hi] = t[:hi - lo]
+                seen += hi - lo
+        if seen < numel:
+            raise ConfigError(f"export of {fqn}: gathered {seen} of {numel} elements")
+        for piece in fmt.to_hf(fqn, shape):
+            t = full[piece.native_flat_lo:piece.native_flat_hi].to(dt)
+            pshape = shape[1:] if len(fmt.to_hf(fqn, shape)) > 1 else shape
+            t = t.view(*pshape).contiguous()
+            nbytes = t.numel() * t.element_size()
+            if shard_bytes + nbytes > max_shard_bytes:
+                flush()
+            shard[piece.hf_name] = t
+            shard_bytes += nbytes
+    if rank == 0:
+        flush()
+        total = len(shard_files)
+        for i, (name, keys) in enumerate(shard_files):
+            final = f"model-{i + 1:05d}-of-{total:05d}.safetensors"
+            os.replace(os.path.join(stage, name), os.path.join(stage, final))
+            for k in keys:
+                weight_map[k] = final
+        with open(os.path.join(stage, "config.json"), "w") as f:
+            json.dump(fmt.hf_config(trainer.model.config), f, indent=1)
+        with open(os.path.join(stage, "model.safetensors.index.json.tmp"), "w") as f:
+            json.dump({"metadata": {"format": "pt"}, "weight_map": weight_map}, f, indent=1)
+        os.replace(os.path.join(stage, "model.safetensors.index.json.tmp"), os.path.join(stage, "model.safetensors.index.json"))
+        if os.path.isdir(out_dir):
+            shutil.rmtree(out_dir)
+        os.replace(stage, out_dir)
+    if world > 1:
+        dist.barrier()
