@@ -81,3 +81,38 @@ def run_ranks(world: int, flat: dict, arch=None, steps: int = 3, device: str = "
         res = json.load(f)
     os.unlink(out)
     return res
+
+
+def _pp_worker(rank, world, port, flat, schedule, out_path, steps):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      LLMTUNER_DEVICE="cpu")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    torch.set_num_threads(1)
+    import torch.distributed as dist
+    from torchllmtuner_b200 import LLMTunerConfig
+    from torchllmtuner_b200.experiments.pipeline_parallel import PipelineTrainer
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(flat)
+    tr = PipelineTrainer(cfg, schedule, None)
+    losses = []
+    for _ in range(steps):
+        tr.loader.cursor = 0
+        losses.append(tr.train_step())
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump({"loss": losses}, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_pp(world, flat, schedule="1F1B", steps=3):
+    import tempfile
+
+    import torch.multiprocessing as mp
+    out = tempfile.mktemp(suffix=".json")
+    port = 20000 + (os.getpid() * 11 + world * 17 + len(schedule)) % 20000
+    mp.spawn(_pp_worker, args=(world, port, flat, schedule, out, steps), nprocs=world, join=True)
+    with open(out) as f:
+        res = json.load(f)
+    os.unlink(out)
+    return res

@@ -1,0 +1,88 @@
+"""Data pipeline: synthetic determinism and resume, text/SFT processing, packing, collating, cursor identity."""
+import json
+import os
+
+import pytest
+import torch
+
+from torchllmtuner_b200.components.tokenizer import WhitespaceTokenizer
+from torchllmtuner_b200.config import DataloaderConfig
+from torchllmtuner_b200.datasets import RandomTokenDataLoader, RandomTokenSource, build_dataloader
+from torchllmtuner_b200.datasets.contracts import IGNORE_INDEX, TextSequence
+from torchllmtuner_b200.datasets.packing import concat_then_split, first_fit
+from torchllmtuner_b200.datasets.processors import ChatProcessor
+
+
+def test_synthetic_same_seed_step_same_batch_and_dp_slices():
+    src = RandomTokenSource(1000, 8, 16, seed=3)
+    a, b = src.global_batch_at(5), src.global_batch_at(5)
+    assert torch.equal(a.input_ids, b.input_ids) and not torch.equal(a.input_ids, src.global_batch_at(6).input_ids)
+    l0, l1 = RandomTokenDataLoader(src, 0, 2, 4), RandomTokenDataLoader(src, 1, 2, 4)
+    b0, b1 = next(l0), next(l1)
+    assert torch.equal(torch.cat([b0["input"], b1["input"]]), src.global_batch_at(0).input_ids)
+    assert torch.equal(b0["labels"][:, :-1], b0["input"][:, 1:]) and (b0["labels"][:, -1] == IGNORE_INDEX).all()
+    sd = l0.state_dict()
+    nxt = next(l0)
+    l2 = RandomTokenDataLoader(src, 0, 2, 4)
+    l2.load_state_dict(sd)
+    assert torch.equal(next(l2)["input"], nxt["input"])
+    with pytest.raises(Exception):
+        RandomTokenDataLoader(src, 0, 4, 2).load_state_dict(sd)
+
+
+def _seq(n, base=0):
+    toks = list(range(base, base + n))
+    labels = toks[1:] + [IGNORE_INDEX]
+    return TextSequence(toks, labels, list(range(n)), [0] * n)
+
+
+def test_concat_then_split_positions_cuts_and_border_labels():
+    rows = list(concat_then_split([_seq(5), _seq(7, 100), _seq(3, 200)], seq_len=8, pad_id=0))
+    assert [len(r.tokens) for r in rows] == [8, 8]
+    assert rows[0].cuts == [0, 5, 8] and rows[0].positions == [0, 1, 2, 3, 4, 0, 1, 2]
+    assert rows[0].labels[4] == IGNORE_INDEX and rows[0].labels[7] == IGNORE_INDEX       # nothing predicted across borders
+    assert rows[1].cuts[-1] == 8 and rows[1].tokens[-1] == 0 and rows[1].labels[-1] == IGNORE_INDEX
+    capped = list(concat_then_split([_seq(2), _seq(2, 10), _seq(2, 20)], seq_len=8, max_num_documents=2))
+    assert len(capped) == 2 and capped[0].cuts[:3] == [0, 2, 4]
+
+
+def test_first_fit_never_splits_documents():
+    rows = list(first_fit([_seq(6), _seq(5, 100), _seq(2, 200), _seq(3, 300)], seq_len=8, num_bins=2))
+    for r in rows:
+        assert len(r.tokens) == 8
+    docs = sorted(c2 - c1 for r in rows for c1, c2 in zip(r.cuts[:-1], r.cuts[1:]))
+    assert {6, 5, 2, 3} <= set(docs)
+
+
+def test_sft_masks_the_prompt(tmp_path):
+    tok = WhitespaceTokenizer.from_texts(["what is two plus two", "four", "user assistant"])
+    seq = ChatProcessor(tok)({"prompt": "what is two plus two", "response": "four"})
+    sup = [t for t, l in zip(seq.tokens[1:], seq.labels[:-1]) if l != IGNORE_INDEX]
+    assert tok.stoi["four"] in sup and tok.stoi["what"] not in sup
+
+
+def test_text_loader_end_to_end_and_resume(tmp_path):
+    texts = [" ".join(f"w{(i * 7 + j) % 50}" for j in range(5 + i % 9)) for i in range(40)]
+    data = tmp_path / "corpus.jsonl"
+    data.write_text("\n".join(json.dumps({"text": t}) for t in texts))
+    tok = WhitespaceTokenizer.from_texts(texts)
+    vocab = tmp_path / "vocab.json"
+    tok.save(str(vocab))
+    cfg = DataloaderConfig(dataset="local_jsonl", dataset_path=str(data), tokenizer_path=str(vocab), tokenizer_backend="whitespace",
+                           num_prefetch_batches=0)
+    mk = lambda: build_dataloader(cfg, vocab_size=1000, global_batch=4, seq_len=32, seed=1, dp_rank=0, dp_degree=2, rows_per_rank=2)  # noqa: E731
+    a = mk()
+    b1, b2 = next(a), next(a)
+    assert b1["input"].shape == (2, 32) and b1["cu_seqlens"][0] == 0 and b1["cu_seqlens"][-1] == 64
+    assert (b1["positions"][0, :3] == torch.tensor([0, 1, 2])).all()
+    sd = a.state_dict()
+    b3 = next(a)
+    c = mk()
+    c.load_state_dict(sd)
+    assert torch.equal(next(c)["input"], b3["input"])
+    cfg2 = DataloaderConfig(dataset="local_jsonl", dataset_path=str(data), tokenizer_path=str(vocab), tokenizer_backend="whitespace",
+                            packing="first_fit", num_prefetch_batches=2)
+    d = build_dataloader(cfg2, vocab_size=1000, global_batch=4, seq_len=32, seed=1, dp_rank=0, dp_degree=2, rows_per_rank=2)
+    assert next(d)["input"].shape == (2, 32)
+    with pytest.raises(Exception):
+        d.load_state_dict(sd)          # different packing -> different corpus identity

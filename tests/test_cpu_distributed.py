@@ -55,3 +55,18 @@ def test_cp2_matches_single_rank(flat):
     got = run_ranks(2, base_flat(data_parallel_shard_size=1, **flat))
     _close(ref["loss"], got["loss"], 5e-5)
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
+@pytest.mark.parametrize("schedule", ["GPipe", "1F1B"])
+def test_pipeline_two_stages_match_single_rank(schedule):
+    from dist_cases import run_pp
+    ref = run_ranks(1, base_flat(num_hidden_layers=4))
+    got = run_pp(2, base_flat(num_hidden_layers=4, pipeline_parallel_size=2, data_parallel_shard_size=1), schedule)
+    _close(ref["loss"], got["loss"], 5e-5)
+
+
+def test_stage_split_rule():
+    from torchllmtuner_b200.experiments.pipeline_parallel import split_layers
+    assert split_layers(6, 2) == [(0, 3), (3, 6)]
+    assert split_layers(7, 2) == [(0, 4), (4, 7)]          # the remainder goes to the first stage
+    assert [b - a for a, b in split_layers(10, 4)] == [2, 3, 3, 2]

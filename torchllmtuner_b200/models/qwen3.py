@@ -181,6 +181,7 @@ class Qwen3ForCausalLM(nn.Module):
         self.activation_checkpoint = "none"     # set by the AC stage: none | full | selective
         self.ac_save_every = 2
         self.block_runner = None                # set by the FSDP stage to own gather/recompute/reduce per block
+        self.pp_first = self.pp_last = True     # pipeline stage position (both True without pipeline parallelism)
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
@@ -267,9 +268,14 @@ class Qwen3ForCausalLM(nn.Module):
         return layer(x, ctx)
 
     def forward(self, tokens: torch.Tensor, ctx: ForwardContext, skip_lm_head: bool = False) -> torch.Tensor:
-        x = self.model.embed_tokens(tokens)
-        for i, layer in enumerate(self.model.layers):
-            x = self.run_block(i, layer, x, ctx)
+        """`tokens` are ids on the first pipeline stage (or without pipeline parallelism) and the previous stage's hidden
+        rows otherwise; a stage that is not the last returns hidden rows."""
+        x = self.model.embed_tokens(tokens) if self.pp_first else tokens
+        layers = self.model.layers
+        for i, layer in enumerate(layers.values() if isinstance(layers, nn.ModuleDict) else layers):
+            x = self.run_block(getattr(layer, "layer_idx", i), layer, x, ctx)
+        if not self.pp_last:
+            return x
         h = self.model.norm(x)
         if skip_lm_head:
             return h

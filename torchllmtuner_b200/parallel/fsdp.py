@@ -499,7 +499,7 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
     else:
         named_units["embedding"] = rt.add_unit("embedding", named(bound.embedding))
     for key, block in bound.block_items():
-        i = int(key)
+        i = getattr(block, "layer_idx", int(key))
         units = []
         exp = [(n, p) for n, p in named(block) if getattr(p, "is_expert", False)]
         dense = [(n, p) for n, p in named(block) if not getattr(p, "is_expert", False)]
