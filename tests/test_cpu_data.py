@@ -86,3 +86,17 @@ def test_text_loader_end_to_end_and_resume(tmp_path):
     assert next(d)["input"].shape == (2, 32)
     with pytest.raises(Exception):
         d.load_state_dict(sd)          # different packing -> different corpus identity
+
+
+def test_multimodal_helpers():
+    from torchllmtuner_b200.datasets.multimodal import (build_mrope_positions, calculate_vision_tokens, insert_vision_placeholders,
+                                                        process_image, smart_resize)
+    h, w = smart_resize(500, 333, factor=28)
+    assert h % 28 == 0 and w % 28 == 0
+    patches, grid = process_image(torch.rand(3, 120, 90), patch=14, merge=2)
+    assert patches.shape == (grid[1] * grid[2], 3 * 14 * 14)
+    n = calculate_vision_tokens(grid)
+    ids = insert_vision_placeholders([5, 99, 6], 99, [grid])
+    assert ids.count(99) == n
+    pos = build_mrope_positions(ids, 99, [grid])
+    assert pos.shape == (3, len(ids)) and pos[0, 1] == pos[0, n] and pos[:, -1].max() == pos[:, -1].min()

@@ -1,4 +1,5 @@
 """End-to-end CPU slice: tiny Qwen3 dense trains through the public Trainer API and the loss falls."""
+import pytest
 import torch
 
 from torchllmtuner_b200 import LLMTunerConfig, Trainer
@@ -57,3 +58,40 @@ def test_moe_trains():
     cfg.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, router_bias_update_coeff=1e-3)
     losses = run(cfg)
     assert losses[-1] < losses[0], losses
+
+
+def test_muon_trains():
+    losses = run(tiny_config(steps=6, optimizer_type="DistMuon", learning_rate=2e-2))
+    assert losses[-1] < losses[0], losses
+
+
+def test_ema_and_wsd_schedule():
+    from torchllmtuner_b200.components.optimizer import wsd_factor
+    assert wsd_factor(0, warmup=4, total=20, decay_ratio=0.25) == 0.25
+    assert wsd_factor(10, warmup=4, total=20, decay_ratio=0.25) == 1.0
+    assert abs(wsd_factor(19, warmup=4, total=20, decay_ratio=0.25, decay_type="linear", min_lr_factor=0.1) - 0.1) < 0.2
+    cfg = tiny_config(steps=3, warmup_steps=2)
+    from torchllmtuner_b200.config import EMAConfig
+    cfg.training.ema_config = EMAConfig(decay=0.5)
+    tr = Trainer(cfg)
+    before = [tr.ema.ema_params[u.name].clone() for u in tr.asm.fsdp.units]
+    tr.train_step()
+    assert any(not torch.equal(b, tr.ema.ema_params[u.name]) for b, u in zip(before, tr.asm.fsdp.units))
+    assert tr.lr_schedulers.get_last_lr()[0] == cfg.optimizer.learning_rate      # warm-up finished after 2 steps
+    tr.close()
+
+
+@pytest.mark.parametrize("family", ["qwen3_5", "qwen3_5_moe", "kimi_linear", "kimi_k3", "deepseek_v4"])
+def test_other_families_train(family):
+    cfg = tiny_config(model_name_or_path=family, steps=4, max_seq_len=16, num_hidden_layers=4, hidden_size=64, num_attention_heads=2,
+                      num_key_value_heads=2, learning_rate=5e-3)
+    cfg.model.arch_overrides = dict(head_dim=64, qk_rope_dim=32, delta_heads=2, delta_head_dim=16)
+    losses = run(cfg)
+    assert losses[-1] < losses[0], (family, losses)
+
+
+def test_registry_lists_every_family():
+    from torchllmtuner_b200.models import registered_models
+    have = set(registered_models())
+    assert {"qwen3", "qwen3_moe", "qwen3_8b", "qwen3_30b_a3b", "qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "deepseek_v4",
+            "kimi_linear", "kimi_k3"} <= have
