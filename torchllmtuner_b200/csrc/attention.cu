@@ -54,31 +54,47 @@ struct AttnSmem {
 };
 
 // =========================================================================================== forward
+// Forward tiles: 128 query rows x 64 keys. K is double buffered, V single buffered, P goes through shared memory:
+// 96 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and the softmax of one overlaps the MMAs
+// of the other.
+constexpr int kFwdKV = 64;
+
+// 16-column slice `ks` of a K-major tile with `rows` rows stored as 64-column halves of [rows][128 B].
+__device__ __forceinline__ uint64_t desc_kmajor_rows(uint32_t base, int ks, int rows) {
+  return umma_desc_sw128(base + (ks >> 2) * (rows * 128) + (ks & 3) * 32, 16, 1024);
+}
+// 16-row slice `ks` of a tile with `rows` rows read as an MN-major operand (64-column blocks `rows * 128` B apart).
+__device__ __forceinline__ uint64_t desc_mnmajor_rows(uint32_t base, int ks, int rows) {
+  return umma_desc_sw128(base + ks * 2048, rows * 128, 1024);
+}
+
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
                 const int* __restrict__ tiles, int Hq, int Hkv, int Tq, int64_t o_stride, float scale_log2, int causal,
                 int* status) {
-  using SM = AttnSmem<HD>;
   constexpr int NH = HD / 64;
+  constexpr int kQBytes = 128 * HD * 2;
+  constexpr int kKVBytes = kFwdKV * HD * 2;
+  constexpr int kPBytes = 128 * kFwdKV * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + SM::kTile;       // 2 stages
-  uint8_t* sV = sK + 2 * SM::kTile;   // 2 stages
-  uint8_t* sP = sV + 2 * SM::kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + SM::kP);
+  uint8_t* sK = sQ + kQBytes;        // 2 stages
+  uint8_t* sV = sK + 2 * kKVBytes;   // 1 stage
+  uint8_t* sP = sV + kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
   uint64_t* q_full = bars;
   uint64_t* kfull = bars + 1;
   uint64_t* kempty = bars + 3;
   uint64_t* vfull = bars + 5;
-  uint64_t* vempty = bars + 7;
-  uint64_t* sfull = bars + 9;
-  uint64_t* sempty = bars + 11;
-  uint64_t* pfull = bars + 13;
-  uint64_t* pvdone = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* vempty = bars + 6;
+  uint64_t* sfull = bars + 7;
+  uint64_t* sempty = bars + 9;
+  uint64_t* pfull = bars + 11;
+  uint64_t* pvdone = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,65 +104,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int* tl = tiles + tile_idx * 8;
   const int q0 = tl[0], nq = tl[1], kbeg = tl[2], klen = tl[3], diag0 = tl[4];
   const int kmax = causal ? min(klen, diag0 + nq - 1) : klen;
-  const int n_kv = (kmax + 127) / 128;
+  const int n_kv = (kmax + kFwdKV - 1) / kFwdKV;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1);
-      mbar_init(&vfull[s], 1); mbar_init(&vempty[s], 1);
       mbar_init(&sfull[s], 1); mbar_init(&sempty[s], 128);
     }
+    mbar_init(vfull, 1); mbar_init(vempty, 1);
     mbar_init(pfull, 128);
     mbar_init(pvdone, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tO = tmem_base + 256;
+  const uint32_t tS = tmem_base, tO = tmem_base + 128;   // S: 2 buffers x 64 columns; O: HD columns
 
   if (warp == 0) {
     if (lane == 0 && n_kv > 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-      mbar_arrive_expect_tx(q_full, SM::kTile);
+      mbar_arrive_expect_tx(q_full, kQBytes);
 #pragma unroll
       for (int hf = 0; hf < NH; ++hf) tma_load_3d(sQ + hf * 16384, &tmQ, q_full, hf * 64, h, q0);
-      int armed[4] = {-1, -1, -1, -1};  // last armed parity of kfull[0], kfull[1], vfull[0], vfull[1]
+      int armed_k[2] = {-1, -1}, armed_v = -1;
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait_bounded(&kempty[s], ph ^ 1, abort_flag, status, 1100 + s)) break;
-        mbar_arrive_expect_tx(&kfull[s], SM::kTile);
-        armed[s] = (int)ph;
+        mbar_arrive_expect_tx(&kfull[s], kKVBytes);
+        armed_k[s] = (int)ph;
 #pragma unroll
-        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sK + s * SM::kTile + hf * 16384, &tmK, &kfull[s], hf * 64, hk, kbeg + j * 128);
-        if (!mbar_wait_bounded(&vempty[s], ph ^ 1, abort_flag, status, 1110 + s)) break;
-        mbar_arrive_expect_tx(&vfull[s], SM::kTile);
-        armed[2 + s] = (int)ph;
+        for (int hf = 0; hf < NH; ++hf)
+          tma_load_3d(sK + s * kKVBytes + hf * (kFwdKV * 128), &tmK, &kfull[s], hf * 64, hk, kbeg + j * kFwdKV);
+        if (!mbar_wait_bounded(vempty, (j & 1) ^ 1, abort_flag, status, 1110)) break;
+        mbar_arrive_expect_tx(vfull, kKVBytes);
+        armed_v = j & 1;
 #pragma unroll
-        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sV + s * SM::kTile + hf * 16384, &tmV, &vfull[s], hf * 64, hk, kbeg + j * 128);
+        for (int hf = 0; hf < NH; ++hf) tma_load_3d(sV + hf * (kFwdKV * 128), &tmV, vfull, hf * 64, hk, kbeg + j * kFwdKV);
       }
       if (*abort_flag) {
         // wait (bounded) for copies in flight before shared memory is released
         for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(q_full, 0)) break;
-        for (int x = 0; x < 4; ++x) {
-          if (armed[x] < 0) continue;
-          uint64_t* b = (x < 2) ? &kfull[x] : &vfull[x - 2];
-          for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(b, (uint32_t)armed[x])) break;
-        }
+        for (int x = 0; x < 2; ++x)
+          if (armed_k[x] >= 0)
+            for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(&kfull[x], (uint32_t)armed_k[x])) break;
+        if (armed_v >= 0)
+          for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(vfull, (uint32_t)armed_v)) break;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && n_kv > 0) {
-      constexpr uint32_t idS = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idS = umma_idesc_bf16(128, kFwdKV, false, false);
       constexpr uint32_t idPV = umma_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, status, 1200);
@@ -158,22 +175,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tS + s * 128, desc_kmajor(aQ, ks), desc_kmajor(aK + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tS + s * kFwdKV, desc_kmajor_rows(aQ, ks, 128), desc_kmajor_rows(aK + s * kKVBytes, ks, kFwdKV), idS, ks ? 1u : 0u);
         umma_commit(&sfull[s]);
         umma_commit(&kempty[s]);
         return true;
       };
       if (ok) ok = issue_S(0);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
         if (j + 1 < n_kv) { if (!issue_S(j + 1)) break; }
         if (!mbar_wait_bounded(pfull, j & 1, abort_flag, status, 1230)) break;
-        if (!mbar_wait_bounded(&vfull[s], (j >> 1) & 1, abort_flag, status, 1240 + s)) break;
+        if (!mbar_wait_bounded(vfull, j & 1, abort_flag, status, 1240)) break;
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tO, desc_kmajor(aP, ks), desc_mnmajor(aV + s * SM::kTile, ks), idPV, (j | ks) ? 1u : 0u);
-        umma_commit(&vempty[s]);
+        for (int ks = 0; ks < kFwdKV / 16; ++ks)
+          umma_bf16_ss(tO, desc_kmajor_rows(aP, ks, 128), desc_mnmajor_rows(aV, ks, kFwdKV), idPV, (j | ks) ? 1u : 0u);
+        umma_commit(vempty);
         umma_commit(pvdone);
       }
     }
@@ -189,22 +205,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int s = j & 1;
       if (!mbar_wait_bounded(&sfull[s], (j >> 1) & 1, abort_flag, status, 1300 + s)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t ts = tS + lane_off + s * 128;
-      const int kbase = j * 128;
-      const bool need_mask = kbase + 128 > (causal ? min(klen, diag0) : klen);
+      const uint32_t ts = tS + lane_off + s * kFwdKV;
+      const int kbase = j * kFwdKV;
+      const bool need_mask = kbase + kFwdKV > (causal ? min(klen, diag0) : klen);
+      // the whole S row of this tile (64 values) stays in registers between the max pass and the exp pass
+      uint32_t r[kFwdKV];
+      tmem_ld_32x32(ts, r);
+      tmem_ld_32x32(ts + 32, r + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sempty[s]);      // S buffer s may be overwritten by the MMA of tile j + 2
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i < row_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+        for (int i = 0; i < kFwdKV; ++i) if (kbase + i < row_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < kFwdKV; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
       mx *= scale_log2;
       const float m_new = fmaxf(m_used, mx);
@@ -217,12 +234,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(tO + lane_off + c * 32, r);
+            uint32_t o[32];
+            tmem_ld_32x32(tO + lane_off + c * 32, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tO + lane_off + c * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tO + lane_off + c * 32, o);
           }
           tmem_wait_st();
         }
@@ -232,15 +249,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], w[16];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < kFwdKV / 32; ++c) {
+        uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2(__uint_as_float(r[i]) * scale_log2 - m_safe);
-          float p1 = ex2(__uint_as_float(r[i + 1]) * scale_log2 - m_safe);
+          float p0 = ex2(__uint_as_float(r[c * 32 + i]) * scale_log2 - m_safe);
+          float p1 = ex2(__uint_as_float(r[c * 32 + i + 1]) * scale_log2 - m_safe);
           if (need_mask) {
             if (kbase + c * 32 + i >= row_limit) p0 = 0.f;
             if (kbase + c * 32 + i + 1 >= row_limit) p1 = 0.f;
@@ -252,7 +267,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       l += rs;
       tc_fence_before();
-      mbar_arrive(&sempty[s]);
       fence_proxy_async_smem();
       mbar_arrive(pfull);
     }
@@ -291,7 +305,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 256);
   }
 }
 
@@ -315,6 +329,11 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t o
 }
 
 // =========================================================================================== backward: dK, dV
+// One CTA per (128-key tile, kv head). It walks the query heads of the group and their 64-row q tiles. S^T and dP^T are
+// double buffered in TMEM, Q / dO and P^T / dS^T are double buffered in shared memory, so the MMAs of q tile i+1 run
+// while the 128 compute threads turn S^T, dP^T of tile i into P^T, dS^T; dV and dK accumulate in TMEM over the whole walk.
+constexpr int kBwdQ = 64;
+
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -322,27 +341,31 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
                     __nv_bfloat16* __restrict__ dV, const int* __restrict__ tiles, int Hq, int Hkv, int Tq, int64_t dk_stride,
                     int64_t dv_stride, float scale, int causal, int accumulate, int* status) {
-  using SM = AttnSmem<HD>;
   constexpr int NH = HD / 64;
+  constexpr int kKVBytes = 128 * HD * 2;
+  constexpr int kQBytes = kBwdQ * HD * 2;
+  constexpr int kPBytes = 128 * kBwdQ * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
-  uint8_t* sV = sK + SM::kTile;
-  uint8_t* sQ = sV + SM::kTile;
-  uint8_t* sdO = sQ + SM::kTile;
-  uint8_t* sPT = sdO + SM::kTile;
-  uint8_t* sdST = sPT + SM::kP;
-  float* s_lse = reinterpret_cast<float*>(sdST + SM::kP);  // [2][128]
-  float* s_delta = s_lse + 256;                            // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 256);
+  uint8_t* sV = sK + kKVBytes;
+  uint8_t* sQ = sV + kKVBytes;          // 2 stages
+  uint8_t* sdO = sQ + 2 * kQBytes;      // 2 stages
+  uint8_t* sPT = sdO + 2 * kQBytes;     // 2 buffers
+  uint8_t* sdST = sPT + 2 * kPBytes;    // 2 buffers
+  float* s_lse = reinterpret_cast<float*>(sdST + 2 * kPBytes);   // [2][64]
+  float* s_delta = s_lse + 2 * kBwdQ;                            // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * kBwdQ);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* s_full = bars + 3;
-  uint64_t* p_full = bars + 4;
-  uint64_t* acc_done = bars + 5;
-  uint64_t* stat_ready = bars + 6;  // lse / delta of the current q tile staged by the 128 compute threads
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* qdo_full = bars + 1;     // [2]
+  uint64_t* qdo_empty = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;       // [2]
+  uint64_t* s_empty = bars + 7;      // [2]
+  uint64_t* p_full = bars + 9;       // [2]
+  uint64_t* p_empty = bars + 11;     // [2]
+  uint64_t* acc_done = bars + 13;
+  uint64_t* stat_ready = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -352,13 +375,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int* tl = tiles + tile_idx * 8;
   const int k0 = tl[0], nk = tl[1], kk0 = tl[2], qbeg = tl[3], qlen = tl[4], off = tl[5], klen = tl[6];
   int qs = 0;
-  if (causal) { qs = kk0 - off; if (qs < 0) qs = 0; qs &= ~127; }
-  const int n_qt = (qlen > qs) ? (qlen - qs + 127) / 128 : 0;
+  if (causal) { qs = kk0 - off; if (qs < 0) qs = 0; qs &= ~(kBwdQ - 1); }
+  const int n_qt = (qlen > qs) ? (qlen - qs + kBwdQ - 1) / kBwdQ : 0;
   const int n_it = n_qt * g;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1);
-    mbar_init(s_full, 1); mbar_init(p_full, 128); mbar_init(acc_done, 1); mbar_init(stat_ready, 128);
+    mbar_init(kv_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1);
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128);
+      mbar_init(&p_full[b], 128); mbar_init(&p_empty[b], 1);
+    }
+    mbar_init(acc_done, 1); mbar_init(stat_ready, 128);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -367,60 +395,78 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tST = tmem_base, tDPT = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 256 + HD;
+  const uint32_t tST = tmem_base, tDPT = tmem_base + 2 * kBwdQ, tDV = tmem_base + 256, tDK = tmem_base + 256 + HD;
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
-      mbar_arrive_expect_tx(kv_full, 2 * SM::kTile);
+      mbar_arrive_expect_tx(kv_full, 2 * kKVBytes);
 #pragma unroll
       for (int hf = 0; hf < NH; ++hf) {
         tma_load_3d(sK + hf * 16384, &tmK, kv_full, hf * 64, hk, k0);
         tma_load_3d(sV + hf * 16384, &tmV, kv_full, hf * 64, hk, k0);
       }
-      int it_issued = 0;
+      int armed[2] = {-1, -1};
       for (int it = 0; it < n_it; ++it) {
+        const int b = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
         const int h = hk * g + it / n_qt;
-        const int qrow = qbeg + qs + (it % n_qt) * 128;
-        if (!mbar_wait_bounded(qdo_empty, (it & 1) ^ 1, abort_flag, status, 2100)) break;
-        mbar_arrive_expect_tx(qdo_full, 2 * SM::kTile);
+        const int qrow = qbeg + qs + (it % n_qt) * kBwdQ;
+        if (!mbar_wait_bounded(&qdo_empty[b], ph ^ 1, abort_flag, status, 2100 + b)) break;
+        mbar_arrive_expect_tx(&qdo_full[b], 2 * kQBytes);
+        armed[b] = (int)ph;
 #pragma unroll
         for (int hf = 0; hf < NH; ++hf) {
-          tma_load_3d(sQ + hf * 16384, &tmQ, qdo_full, hf * 64, h, qrow);
-          tma_load_3d(sdO + hf * 16384, &tmdO, qdo_full, hf * 64, h, qrow);
+          tma_load_3d(sQ + b * kQBytes + hf * (kBwdQ * 128), &tmQ, &qdo_full[b], hf * 64, h, qrow);
+          tma_load_3d(sdO + b * kQBytes + hf * (kBwdQ * 128), &tmdO, &qdo_full[b], hf * 64, h, qrow);
         }
-        it_issued = it + 1;
       }
       if (*abort_flag) {
         for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(kv_full, 0)) break;
-        if (it_issued > 0)
-          for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(qdo_full, (it_issued - 1) & 1)) break;
+        for (int b = 0; b < 2; ++b)
+          if (armed[b] >= 0)
+            for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(&qdo_full[b], (uint32_t)armed[b])) break;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && n_it > 0) {
-      constexpr uint32_t idS = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idS = umma_idesc_bf16(128, kBwdQ, false, false);
       constexpr uint32_t idAcc = umma_idesc_bf16(128, HD, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aPT = smem_u32(sPT),
                      adST = smem_u32(sdST);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, status, 2200);
+      auto issue_S = [&](int it) -> bool {
+        const int b = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&qdo_full[b], ph, abort_flag, status, 2210 + b)) return false;
+        if (!mbar_wait_bounded(&s_empty[b], ph ^ 1, abort_flag, status, 2215 + b)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_bf16_ss(tST + b * kBwdQ, desc_kmajor_rows(aK, ks, 128), desc_kmajor_rows(aQ + b * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_bf16_ss(tDPT + b * kBwdQ, desc_kmajor_rows(aV, ks, 128), desc_kmajor_rows(adO + b * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
+        umma_commit(&s_full[b]);
+        return true;
+      };
+      if (ok) ok = issue_S(0);
       for (int it = 0; it < n_it && ok; ++it) {
-        if (!mbar_wait_bounded(qdo_full, it & 1, abort_flag, status, 2210)) break;
+        const int b = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (it + 1 < n_it) { if (!issue_S(it + 1)) break; }
+        if (!mbar_wait_bounded(&p_full[b], ph, abort_flag, status, 2220 + b)) break;
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) umma_bf16_ss(tST, desc_kmajor(aK, ks), desc_kmajor(aQ, ks), idS, ks ? 1u : 0u);
+        for (int ks = 0; ks < kBwdQ / 16; ++ks)
+          umma_bf16_ss(tDV, desc_kmajor_rows(aPT + b * kPBytes, ks, 128), desc_mnmajor_rows(adO + b * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) umma_bf16_ss(tDPT, desc_kmajor(aV, ks), desc_kmajor(adO, ks), idS, ks ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait_bounded(p_full, it & 1, abort_flag, status, 2220)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16_ss(tDV, desc_kmajor(aPT, ks), desc_mnmajor(adO, ks), idAcc, (it | ks) ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_bf16_ss(tDK, desc_kmajor(adST, ks), desc_mnmajor(aQ, ks), idAcc, (it | ks) ? 1u : 0u);
-        umma_commit(qdo_empty);
-        umma_commit(acc_done);
+        for (int ks = 0; ks < kBwdQ / 16; ++ks)
+          umma_bf16_ss(tDK, desc_kmajor_rows(adST + b * kPBytes, ks, 128), desc_mnmajor_rows(aQ + b * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
+        umma_commit(&qdo_empty[b]);
+        umma_commit(&p_empty[b]);
+        if (it == n_it - 1) umma_commit(acc_done);
       }
     }
     __syncwarp();
@@ -434,29 +480,34 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float scale_log2 = scale * kLog2e;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
+      const int b = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
       const int h = hk * g + it / n_qt;
-      const int qi0 = qs + (it % n_qt) * 128;  // first query index (inside the document) of this q tile
-      {
+      const int qi0 = qs + (it % n_qt) * kBwdQ;  // first query index (inside the document) of this q tile
+      if (tid < kBwdQ) {
         const int qi = qi0 + tid;
         const bool v = qi < qlen;
-        s_lse[(it & 1) * 128 + tid] = v ? lse[(int64_t)h * Tq + qbeg + qi] * kLog2e : INFINITY;
-        s_delta[(it & 1) * 128 + tid] = v ? delta[(int64_t)h * Tq + qbeg + qi] : 0.f;
+        s_lse[b * kBwdQ + tid] = v ? lse[(int64_t)h * Tq + qbeg + qi] * kLog2e : INFINITY;
+        s_delta[b * kBwdQ + tid] = v ? delta[(int64_t)h * Tq + qbeg + qi] : 0.f;
       }
       mbar_arrive(stat_ready);
       if (!mbar_wait_bounded(stat_ready, it & 1, abort_flag, status, 2330)) { ok = false; break; }
-      if (!mbar_wait_bounded(s_full, it & 1, abort_flag, status, 2300)) { ok = false; break; }
+      if (!mbar_wait_bounded(&s_full[b], ph, abort_flag, status, 2300 + b)) { ok = false; break; }
       tc_fence_after();
-      if (it > 0) {
-        if (!mbar_wait_bounded(acc_done, (it - 1) & 1, abort_flag, status, 2310)) { ok = false; break; }
-      }
-      const float* pl = s_lse + (it & 1) * 128;
-      const float* pd = s_delta + (it & 1) * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rd[32], wp[16], wd[16];
-        tmem_ld_32x32(tST + lane_off + c * 32, rs);
-        tmem_ld_32x32(tDPT + lane_off + c * 32, rd);
-        tmem_wait_ld();
+      uint32_t rs[kBwdQ], rd[kBwdQ];
+      tmem_ld_32x32(tST + lane_off + b * kBwdQ, rs);
+      tmem_ld_32x32(tST + lane_off + b * kBwdQ + 32, rs + 32);
+      tmem_ld_32x32(tDPT + lane_off + b * kBwdQ, rd);
+      tmem_ld_32x32(tDPT + lane_off + b * kBwdQ + 32, rd + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_empty[b]);
+      if (!mbar_wait_bounded(&p_empty[b], ph ^ 1, abort_flag, status, 2310 + b)) { ok = false; break; }
+      const float* pl = s_lse + b * kBwdQ;
+      const float* pd = s_delta + b * kBwdQ;
+#pragma unroll
+      for (int c = 0; c < kBwdQ / 32; ++c) {
+        uint32_t wp[16], wd[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p[2], ds[2];
@@ -465,21 +516,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int qc = c * 32 + i + e;
             const int qi = qi0 + qc;
             const bool vis = key_ok && (qi < qlen) && (!causal || key_idx <= qi + off);
-            const float pv = vis ? ex2(__uint_as_float(rs[i + e]) * scale_log2 - pl[qc]) : 0.f;
+            const float pv = vis ? ex2(__uint_as_float(rs[qc]) * scale_log2 - pl[qc]) : 0.f;
             p[e] = pv;
-            ds[e] = pv * (__uint_as_float(rd[i + e]) - pd[qc]);
+            ds[e] = pv * (__uint_as_float(rd[qc]) - pd[qc]);
           }
           wp[i >> 1] = pack_bf16x2(p[0], p[1]);
           wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
         }
-        store_row32_swz(sPT, row, c * 32, wp);
-        store_row32_swz(sdST, row, c * 32, wd);
+        store_row32_swz(sPT + b * kPBytes, row, c * 32, wp);
+        store_row32_swz(sdST + b * kPBytes, row, c * 32, wd);
       }
-      tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[b]);
     }
-    if (ok && n_it > 0) ok = mbar_wait_bounded(acc_done, (n_it - 1) & 1, abort_flag, status, 2320);
+    if (ok && n_it > 0) ok = mbar_wait_bounded(acc_done, 0, abort_flag, status, 2320);
     if (ok) {
       tc_fence_after();
       __nv_bfloat16* kr = dK + (int64_t)(k0 + row) * dk_stride + (int64_t)hk * HD;
@@ -498,27 +548,27 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (row < nk) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            uint4 a, b;
+            uint4 a, bq;
             a.x = pack_bf16x2(__uint_as_float(rk[8 * v]) * scale, __uint_as_float(rk[8 * v + 1]) * scale);
             a.y = pack_bf16x2(__uint_as_float(rk[8 * v + 2]) * scale, __uint_as_float(rk[8 * v + 3]) * scale);
             a.z = pack_bf16x2(__uint_as_float(rk[8 * v + 4]) * scale, __uint_as_float(rk[8 * v + 5]) * scale);
             a.w = pack_bf16x2(__uint_as_float(rk[8 * v + 6]) * scale, __uint_as_float(rk[8 * v + 7]) * scale);
-            b.x = pack_bf16x2(__uint_as_float(rv[8 * v]), __uint_as_float(rv[8 * v + 1]));
-            b.y = pack_bf16x2(__uint_as_float(rv[8 * v + 2]), __uint_as_float(rv[8 * v + 3]));
-            b.z = pack_bf16x2(__uint_as_float(rv[8 * v + 4]), __uint_as_float(rv[8 * v + 5]));
-            b.w = pack_bf16x2(__uint_as_float(rv[8 * v + 6]), __uint_as_float(rv[8 * v + 7]));
+            bq.x = pack_bf16x2(__uint_as_float(rv[8 * v]), __uint_as_float(rv[8 * v + 1]));
+            bq.y = pack_bf16x2(__uint_as_float(rv[8 * v + 2]), __uint_as_float(rv[8 * v + 3]));
+            bq.z = pack_bf16x2(__uint_as_float(rv[8 * v + 4]), __uint_as_float(rv[8 * v + 5]));
+            bq.w = pack_bf16x2(__uint_as_float(rv[8 * v + 6]), __uint_as_float(rv[8 * v + 7]));
             if (accumulate) {
               const uint4 pa = reinterpret_cast<const uint4*>(kr + c * 32)[v], pb = reinterpret_cast<const uint4*>(vr + c * 32)[v];
               const __nv_bfloat162 *ha = reinterpret_cast<const __nv_bfloat162*>(&pa), *hb = reinterpret_cast<const __nv_bfloat162*>(&pb);
-              __nv_bfloat162 *na = reinterpret_cast<__nv_bfloat162*>(&a), *nb = reinterpret_cast<__nv_bfloat162*>(&b);
+              __nv_bfloat162 *na = reinterpret_cast<__nv_bfloat162*>(&a), *nb = reinterpret_cast<__nv_bfloat162*>(&bq);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                na[j] = __hadd2(na[j], ha[j]);
-                nb[j] = __hadd2(nb[j], hb[j]);
+              for (int jj = 0; jj < 4; ++jj) {
+                na[jj] = __hadd2(na[jj], ha[jj]);
+                nb[jj] = __hadd2(nb[jj], hb[jj]);
               }
             }
             reinterpret_cast<uint4*>(kr + c * 32)[v] = a;
-            reinterpret_cast<uint4*>(vr + c * 32)[v] = b;
+            reinterpret_cast<uint4*>(vr + c * 32)[v] = bq;
           }
         }
       }
@@ -724,11 +774,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                    const uint32_t* box);
 
-// [T, H, HD] tensor with token stride `tok_stride` elements -> 3-D map {HD, H, T}, box {64, 1, 128}.
-static int make_thd_map(CUtensorMap* m, const void* p, int T, int H, int HD, int64_t tok_stride) {
+// [T, H, HD] tensor with token stride `tok_stride` elements -> 3-D map {HD, H, T}, box {64, 1, rows}.
+static int make_thd_map(CUtensorMap* m, const void* p, int T, int H, int HD, int64_t tok_stride, uint32_t rows = 128) {
   uint64_t dims[3] = {(uint64_t)HD, (uint64_t)H, (uint64_t)T};
   uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)tok_stride * 2};
-  uint32_t box[3] = {64, 1, 128};
+  uint32_t box[3] = {64, 1, rows};
   return make_tmap_bf16(m, p, 3, dims, str, box);
 }
 
@@ -747,10 +797,10 @@ extern "C" int llmt_attn_fwd(const void* q, const void* k, const void* v, void* 
   if (num_tiles <= 0 || Hq <= 0) return 0;
   if ((HD != 64 && HD != 128) || Hq % Hkv || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (o_stride & 7)) return -10;
   CUtensorMap tq, tk, tv;
-  if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride) ||
-      make_thd_map(&tv, v, Tk, Hkv, HD, v_stride))
+  if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride, kFwdKV) ||
+      make_thd_map(&tv, v, Tk, Hkv, HD, v_stride, kFwdKV))
     return -11;
-  const int smem = 5 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 256;
+  const int smem = 128 * HD * 2 + 3 * kFwdKV * HD * 2 + 128 * kFwdKV * 2 + 1024 + 256;
   const float sl2 = scale * kLog2e;
   if (HD == 128) {
     static bool cfg = false;
@@ -785,7 +835,9 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
   if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride) ||
       make_thd_map(&tv, v, Tk, Hkv, HD, v_stride) || make_thd_map(&tdo, dout, Tq, Hq, HD, do_stride))
     return -11;
-  const int smem_kv = 4 * 128 * HD * 2 + 2 * 128 * 128 * 2 + 2048 + 1024 + 256;
+  CUtensorMap tq64, tdo64;   // 64-row boxes for the dK/dV kernel's q tiles
+  if (make_thd_map(&tq64, q, Tq, Hq, HD, q_stride, kBwdQ) || make_thd_map(&tdo64, dout, Tq, Hq, HD, do_stride, kBwdQ)) return -11;
+  const int smem_kv = 2 * 128 * HD * 2 + 4 * kBwdQ * HD * 2 + 4 * 128 * kBwdQ * 2 + 4 * kBwdQ * 4 + 1024 + 256;
   const int smem_q = 6 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 256;
   if (HD == 128) {
     static bool cfg = false;
@@ -795,7 +847,7 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
     }
     if (num_k_tiles > 0)
       attn_bwd_dkv_kernel<128><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
-          tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
+          tq64, tk, tv, tdo64, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
           causal, pass > 0, status);
     if (num_q_tiles > 0 && pass == 0)
       attn_bwd_dq_kernel<128><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
@@ -809,7 +861,7 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
     }
     if (num_k_tiles > 0)
       attn_bwd_dkv_kernel<64><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
-          tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
+          tq64, tk, tv, tdo64, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
           causal, pass > 0, status);
     if (num_q_tiles > 0 && pass == 0)
       attn_bwd_dq_kernel<64><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,

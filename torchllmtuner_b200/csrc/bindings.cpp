@@ -355,6 +355,62 @@ std::vector<Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   return {dq, dk, dv};
 }
 
+// ---- MoE
+std::vector<Tensor> router_topk(const Tensor& logits, const c10::optional<Tensor>& bias, int64_t k, int64_t score_fn, bool renorm,
+                                double route_scale) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous());
+  const int T = (int)logits.size(0), E = (int)logits.size(1);
+  Tensor w = torch::empty({T, k}, logits.options());
+  Tensor idx = torch::empty({T, k}, logits.options().dtype(torch::kLong));
+  Tensor counts = torch::zeros({E}, logits.options());
+  Tensor denom = torch::empty({T}, logits.options());
+  const float* bp = bias.has_value() ? bias->data_ptr<float>() : nullptr;
+  check_rc(llmt_router_topk(logits.data_ptr<float>(), bp, w.data_ptr<float>(), idx.data_ptr<int64_t>(), counts.data_ptr<float>(),
+                            denom.data_ptr<float>(), T, E, (int)k, (int)score_fn, renorm, (float)route_scale, cur_stream()),
+           "llmt_router_topk");
+  return {w, idx, counts, denom};
+}
+Tensor router_topk_bwd(const Tensor& logits, const Tensor& dw, const Tensor& idx, const Tensor& denom, int64_t score_fn, bool renorm,
+                       double route_scale) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor dl = torch::zeros_like(logits);
+  Tensor dwc = dw.contiguous();
+  check_rc(llmt_router_topk_bwd(logits.data_ptr<float>(), dwc.data_ptr<float>(), idx.data_ptr<int64_t>(), denom.data_ptr<float>(),
+                                dl.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)idx.size(1), (int)score_fn, renorm,
+                                (float)route_scale, cur_stream()),
+           "llmt_router_topk_bwd");
+  return dl;
+}
+// rows must be zero-initialised by the caller (padding rows stay zero)
+void permute_rows(const Tensor& x, const Tensor& dest, Tensor& rows, int64_t k) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check_bf16(x, "x"); check_bf16(rows, "rows");
+  TORCH_CHECK(x.is_contiguous() && rows.is_contiguous() && dest.scalar_type() == at::kLong && dest.is_contiguous());
+  check_rc(llmt_permute_rows(x.data_ptr(), dest.data_ptr<int64_t>(), rows.data_ptr(), dest.numel(), (int)k, (int)x.size(1), cur_stream()),
+           "llmt_permute_rows");
+}
+Tensor combine_rows(const Tensor& y, const Tensor& dest, const c10::optional<Tensor>& w, int64_t T, int64_t k) {
+  c10::cuda::CUDAGuard guard(y.device());
+  check_bf16(y, "y");
+  TORCH_CHECK(y.is_contiguous() && dest.is_contiguous());
+  Tensor out = torch::empty({T, y.size(1)}, y.options());
+  const float* wp = w.has_value() ? w->data_ptr<float>() : nullptr;
+  check_rc(llmt_combine_rows(y.data_ptr(), dest.data_ptr<int64_t>(), wp, out.data_ptr(), (int)T, (int)k, (int)y.size(1), cur_stream()),
+           "llmt_combine_rows");
+  return out;
+}
+std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& dest, const Tensor& w, int64_t k) {
+  c10::cuda::CUDAGuard guard(y.device());
+  Tensor dy = torch::zeros_like(y);
+  Tensor dw = torch::empty({dest.numel()}, y.options().dtype(torch::kFloat));
+  Tensor d = dout.contiguous();
+  check_rc(llmt_combine_bwd(d.data_ptr(), y.data_ptr(), dest.data_ptr<int64_t>(), w.data_ptr<float>(), dy.data_ptr(), dw.data_ptr<float>(),
+                            dest.numel(), (int)k, (int)y.size(1), cur_stream()),
+           "llmt_combine_bwd");
+  return {dy, dw};
+}
+
 // Reads the status word (synchronises the current stream) and clears it. Returns {code, site, block, extra}.
 std::vector<int64_t> read_status(bool clear) {
   Tensor h = status_word().cpu();
@@ -380,6 +436,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("wait_value", &PySideJob::wait_value);
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn"), py::arg("b_mn"),
         py::arg("accumulate") = false, py::arg("max_ctas") = 0, py::arg("side") = py::none());
+  m.def("router_topk", &router_topk);
+  m.def("router_topk_bwd", &router_topk_bwd);
+  m.def("permute_rows", &permute_rows);
+  m.def("combine_rows", &combine_rows);
+  m.def("combine_bwd", &combine_bwd);
   m.def("side_job", &side_job);
   m.def("signal_peers", &signal_peers);
   m.def("wait_flags", &wait_flags);

@@ -49,6 +49,16 @@ int llmt_sqnorm_scratch_floats();
 int llmt_sqnorm(const void* x, int is_bf16, int64_t n, float* scratch, float* out, int accumulate, cudaStream_t st);
 int llmt_clip_coef(const float* total_sq, float max_norm, float* clip_coef, float* norm_out, int* finite, cudaStream_t st);
 
+// ---- MoE routing and token movement (moe.cu) ----
+int llmt_router_topk(const float* logits, const float* bias, float* weights, int64_t* indices, float* counts, float* denom,
+                     int T, int E, int k, int score_fn, int renorm, float route_scale, cudaStream_t st);
+int llmt_router_topk_bwd(const float* logits, const float* dweights, const int64_t* indices, const float* denom, float* dlogits,
+                         int T, int E, int k, int score_fn, int renorm, float route_scale, cudaStream_t st);
+int llmt_permute_rows(const void* x, const int64_t* dest, void* rows, int64_t ncopies, int k, int D, cudaStream_t st);
+int llmt_combine_rows(const void* y, const int64_t* dest, const float* w, void* out, int T, int k, int D, cudaStream_t st);
+int llmt_combine_bwd(const void* dout, const void* y, const int64_t* dest, const float* w, void* dy, float* dw, int64_t ncopies,
+                     int k, int D, cudaStream_t st);
+
 // ---- peer-memory communication (comm.cu) ----
 int llmt_side_job(int kind, int nsrc, const void* const* src, void* dst, long long n, int accumulate,
                   const uint32_t* wait_flags, int n_wait, uint32_t wait_value, int ctas, int* status, cudaStream_t st);

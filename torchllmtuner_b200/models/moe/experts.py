@@ -75,6 +75,40 @@ def grouped_linear(x, w, seg_offsets, counts=None):
     return outs
 
 
+class _PermuteRows(torch.autograd.Function):
+    """rows[dest[c]] = x[c // k] into a zeroed padded buffer; backward sums the k copies of every token."""
+
+    @staticmethod
+    def forward(ctx, x, dest, cap, k):
+        rows = torch.zeros(cap, x.shape[1], dtype=x.dtype, device=x.device)
+        _ext().permute_rows(x.contiguous(), dest, rows, k)
+        ctx.save_for_backward(dest)
+        ctx.k, ctx.T = k, x.shape[0]
+        return rows
+
+    @staticmethod
+    def backward(ctx, g):
+        (dest,) = ctx.saved_tensors
+        return _ext().combine_rows(g.contiguous(), dest, None, ctx.T, ctx.k), None, None, None
+
+
+class _CombineRows(torch.autograd.Function):
+    """out[t] = sum_j w[t, j] * y[dest[t * k + j]] in fp32."""
+
+    @staticmethod
+    def forward(ctx, y, weights, dest, T, k):
+        w = weights.float().contiguous()
+        ctx.save_for_backward(y, w, dest)
+        ctx.k = k
+        return _ext().combine_rows(y.contiguous(), dest, w, T, k)
+
+    @staticmethod
+    def backward(ctx, g):
+        y, w, dest = ctx.saved_tensors
+        dy, dw = _ext().combine_bwd(g, y.contiguous(), dest, w.reshape(-1), ctx.k)
+        return dy, dw.view_as(w), None, None, None
+
+
 class GroupedExperts(nn.Module):
     def __init__(self, num_experts: int, hidden: int, inter: int, dtype=None, device=None, implementation: str = "native"):
         super().__init__()
@@ -115,12 +149,17 @@ class LocalTokenDispatcher:
         flat = indices.reshape(-1)
         dest, seg, counts = plan_segments(flat, self.num_experts)
         cap = padded_capacity(T * k, self.num_experts)
-        tok = torch.arange(T * k, device=x.device) // k
-        rows = x.new_zeros(cap, x.shape[1]).index_copy(0, dest, x.index_select(0, tok))
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:
+            rows = _PermuteRows.apply(x, dest, cap, k)
+        else:
+            tok = torch.arange(T * k, device=x.device) // k
+            rows = x.new_zeros(cap, x.shape[1]).index_copy(0, dest, x.index_select(0, tok))
         return rows, seg, {"dest": dest, "T": T, "k": k}
 
     def combine(self, y: torch.Tensor, weights: torch.Tensor, state) -> torch.Tensor:
         T, k = state["T"], state["k"]
+        if y.is_cuda and y.dtype == torch.bfloat16 and y.shape[1] % 8 == 0:
+            return _CombineRows.apply(y, weights, state["dest"], T, k)
         g = y.index_select(0, state["dest"]).view(T, k, -1)
         return (g.float() * weights.float().unsqueeze(-1)).sum(1).to(y.dtype)
 

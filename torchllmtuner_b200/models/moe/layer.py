@@ -31,6 +31,7 @@ class MoE(nn.Module):
         self.register_buffer("expert_bias_E", torch.zeros(num_experts, dtype=torch.float32, device=device), persistent=True)
         self.register_buffer("tokens_per_expert_E", torch.zeros(num_experts, dtype=torch.float32, device=device), persistent=True)
         self.aux_loss: torch.Tensor | None = None
+        self.router.need_scores = aux_loss_coef > 0      # the balance loss needs the full score matrix
         self.dispatch_timer = None
 
     @property

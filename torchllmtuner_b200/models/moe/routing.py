@@ -42,6 +42,27 @@ class _RouterGate(torch.autograd.Function):
         return dx, dw
 
 
+class _RouterTopK(torch.autograd.Function):
+    """Fused score / biased top-k / renormalise / histogram kernel with its hand-written backward."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, k, score_fn, renorm, route_scale):
+        from ...ops.cuda_ext import load
+        fn = 0 if score_fn == "softmax" else 1
+        w, idx, counts, denom = load().router_topk(logits.contiguous(), bias, k, fn, renorm, route_scale)
+        ctx.save_for_backward(logits, idx, denom)
+        ctx.cfg = (fn, renorm, route_scale)
+        ctx.mark_non_differentiable(idx, counts)
+        return w, idx, counts
+
+    @staticmethod
+    def backward(ctx, dw, _di, _dc):
+        from ...ops.cuda_ext import load
+        logits, idx, denom = ctx.saved_tensors
+        fn, renorm, scale = ctx.cfg
+        return load().router_topk_bwd(logits.contiguous(), dw.float(), idx, denom, fn, renorm, scale), None, None, None, None, None
+
+
 class TokenChoiceTopKRouter(nn.Module):
     def __init__(self, hidden: int, num_experts: int, top_k: int, score_fn: str = "softmax", norm_topk_prob: bool = True,
                  route_scale: float = 1.0, num_groups: int = 1, topk_groups: int = 1, fixed: bool = False, dtype=None,
@@ -59,6 +80,11 @@ class TokenChoiceTopKRouter(nn.Module):
     def forward(self, x: torch.Tensor, expert_bias: torch.Tensor | None = None):
         """x [T, D] -> (weights [T,k] fp32, indices [T,k] int64, counts [E] fp32, scores [T,E] fp32)."""
         logits = self.gate(x)
+        if (logits.is_cuda and not self.fixed and self.num_groups == 1 and self.score_fn in ("softmax", "sigmoid")
+                and self.num_experts <= 512 and self.top_k <= 16):
+            bias = expert_bias.float().contiguous() if expert_bias is not None else None
+            w, idx, counts = _RouterTopK.apply(logits, bias, self.top_k, self.score_fn, self.norm_topk_prob, self.route_scale)
+            return w, idx, counts, (ref.router_scores(logits, self.score_fn) if self.training and getattr(self, "need_scores", False) else None)
         scores = ref.router_scores(logits, self.score_fn)
         if self.fixed:
             T = x.shape[0]
