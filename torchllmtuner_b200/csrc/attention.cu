@@ -59,6 +59,14 @@ struct AttnSmem {
 // of the other.
 constexpr int kFwdKV = 64;
 
+// Optional timeline of CTA 0 (development aid): role r writes clock64() for step j, point p into g_attn_dbg[(j*8+p)*2+r].
+#ifdef LLMT_ATTN_TIMELINE
+__device__ long long g_attn_dbg[2 * 8 * 256];
+#define LLMT_TL(role, j, p) do { if (blockIdx.x == 0 && (j) < 256) g_attn_dbg[(((j) * 8) + (p)) * 2 + (role)] = clock64(); } while (0)
+#else
+#define LLMT_TL(role, j, p) do { } while (0)
+#endif
+
 // 16-column slice `ks` of a K-major tile with `rows` rows stored as 64-column halves of [rows][128 B].
 __device__ __forceinline__ uint64_t desc_kmajor_rows(uint32_t base, int ks, int rows) {
   return umma_desc_sw128(base + (ks >> 2) * (rows * 128) + (ks & 3) * 32, 16, 1024);
@@ -78,13 +86,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int kQBytes = 128 * HD * 2;
   constexpr int kKVBytes = kFwdKV * HD * 2;
   constexpr int kPBytes = 128 * kFwdKV * 2;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The launch asks for exactly the bytes used (two CTAs must fit in one SM), so the dynamic shared memory base has to be
+  // 1024-byte aligned already; the kernel refuses to run otherwise instead of overrunning its allocation.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(status, kStatusBadArgument, 1001, (int)(smem_u32(smem_raw) & 1023u));
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kQBytes;        // 2 stages
   uint8_t* sV = sK + 2 * kKVBytes;   // 1 stage
-  uint8_t* sP = sV + kKVBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+  uint8_t* sP = sV + kKVBytes;       // 2 buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
   uint64_t* q_full = bars;
   uint64_t* kfull = bars + 1;
   uint64_t* kempty = bars + 3;
@@ -92,9 +106,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* vempty = bars + 6;
   uint64_t* sfull = bars + 7;
   uint64_t* sempty = bars + 9;
-  uint64_t* pfull = bars + 11;
-  uint64_t* pvdone = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* pfull = bars + 11;    // [2]
+  uint64_t* pvdone = bars + 13;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,10 +125,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1);
       mbar_init(&sfull[s], 1); mbar_init(&sempty[s], 128);
+      mbar_init(&pfull[s], 128); mbar_init(&pvdone[s], 1);
     }
     mbar_init(vfull, 1); mbar_init(vempty, 1);
-    mbar_init(pfull, 128);
-    mbar_init(pvdone, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -135,15 +148,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int hf = 0; hf < NH; ++hf) tma_load_3d(sQ + hf * 16384, &tmQ, q_full, hf * 64, h, q0);
       int armed_k[2] = {-1, -1}, armed_v = -1;
-      for (int j = 0; j < n_kv; ++j) {
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait_bounded(&kempty[s], ph ^ 1, abort_flag, status, 1100 + s)) break;
+        if (!mbar_wait_bounded(&kempty[s], ph ^ 1, abort_flag, status, 1100 + s)) return false;
         mbar_arrive_expect_tx(&kfull[s], kKVBytes);
         armed_k[s] = (int)ph;
 #pragma unroll
         for (int hf = 0; hf < NH; ++hf)
           tma_load_3d(sK + s * kKVBytes + hf * (kFwdKV * 128), &tmK, &kfull[s], hf * 64, hk, kbeg + j * kFwdKV);
+        return true;
+      };
+      bool pok = load_k(0);
+      for (int j = 0; j < n_kv && pok; ++j) {
+        if (j + 1 < n_kv && !load_k(j + 1)) break;     // K runs one tile ahead of V: S(j+1) is issued before PV(j)
         if (!mbar_wait_bounded(vempty, (j & 1) ^ 1, abort_flag, status, 1110)) break;
         mbar_arrive_expect_tx(vfull, kKVBytes);
         armed_v = j & 1;
@@ -173,24 +191,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait_bounded(&kfull[s], ph, abort_flag, status, 1210 + s)) return false;
         if (!mbar_wait_bounded(&sempty[s], ph ^ 1, abort_flag, status, 1220 + s)) return false;
         tc_fence_after();
+        LLMT_TL(1, j - 1, 5);
+        {
+          // descriptors differ only in the start address field: build the two bases once and step the low word
+          const uint64_t dq0 = desc_kmajor_rows(aQ, 0, 128), dk0 = desc_kmajor_rows(aK + s * kKVBytes, 0, kFwdKV);
+          const uint32_t d_s = tS + s * kFwdKV;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tS + s * kFwdKV, desc_kmajor_rows(aQ, ks, 128), desc_kmajor_rows(aK + s * kKVBytes, ks, kFwdKV), idS, ks ? 1u : 0u);
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint64_t offq = (uint64_t)(((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4);
+            const uint64_t offk = (uint64_t)(((ks >> 2) * (kFwdKV * 128) + (ks & 3) * 32) >> 4);
+            umma_bf16_ss(d_s, dq0 + offq, dk0 + offk, idS, ks ? 1u : 0u);
+          }
+        }
+        LLMT_TL(1, j - 1, 6);
         umma_commit(&sfull[s]);
         umma_commit(&kempty[s]);
+        LLMT_TL(1, j - 1, 7);
         return true;
       };
       if (ok) ok = issue_S(0);
       for (int j = 0; j < n_kv && ok; ++j) {
+        LLMT_TL(1, j, 0);
         if (j + 1 < n_kv) { if (!issue_S(j + 1)) break; }
-        if (!mbar_wait_bounded(pfull, j & 1, abort_flag, status, 1230)) break;
+        LLMT_TL(1, j, 1);
+        const int pb = j & 1;
+        if (!mbar_wait_bounded(&pfull[pb], (j >> 1) & 1, abort_flag, status, 1230 + pb)) break;
+        LLMT_TL(1, j, 2);
         if (!mbar_wait_bounded(vfull, j & 1, abort_flag, status, 1240)) break;
         tc_fence_after();
+        LLMT_TL(1, j, 3);
 #pragma unroll
         for (int ks = 0; ks < kFwdKV / 16; ++ks)
-          umma_bf16_ss(tO, desc_kmajor_rows(aP, ks, 128), desc_mnmajor_rows(aV, ks, kFwdKV), idPV, (j | ks) ? 1u : 0u);
+          umma_bf16_ss(tO, desc_kmajor_rows(aP + pb * kPBytes, ks, 128), desc_mnmajor_rows(aV, ks, kFwdKV), idPV, (j | ks) ? 1u : 0u);
         umma_commit(vempty);
-        umma_commit(pvdone);
+        umma_commit(&pvdone[pb]);
+        LLMT_TL(1, j, 4);
       }
     }
     __syncwarp();
@@ -203,8 +238,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j & 1;
+      if (threadIdx.x == 64) LLMT_TL(0, j, 0);
       if (!mbar_wait_bounded(&sfull[s], (j >> 1) & 1, abort_flag, status, 1300 + s)) { ok = false; break; }
       tc_fence_after();
+      if (threadIdx.x == 64) LLMT_TL(0, j, 1);
       const uint32_t ts = tS + lane_off + s * kFwdKV;
       const int kbase = j * kFwdKV;
       const bool need_mask = kbase + kFwdKV > (causal ? min(klen, diag0) : klen);
@@ -215,14 +252,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sempty[s]);      // S buffer s may be overwritten by the MMA of tile j + 2
-      float mx = -INFINITY;
+      if (threadIdx.x == 64) LLMT_TL(0, j, 2);
+      // eight independent running maxima keep the dependency chains short
+      float mxs[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) mxs[q] = -INFINITY;
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < kFwdKV; ++i) if (kbase + i < row_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < kFwdKV; ++i) if (kbase + i < row_limit) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(r[i]));
       } else {
 #pragma unroll
-        for (int i = 0; i < kFwdKV; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < kFwdKV; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(r[i]));
       }
+      float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
       mx *= scale_log2;
       const float m_new = fmaxf(m_used, mx);
       const bool need = m_new > m_used + 8.f;  // lazy rescale: only when the running max moved by more than 2^8
@@ -230,7 +272,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float alpha = need ? ((m_used == -INFINITY) ? 0.f : ex2(m_used - m_new)) : 1.f;
         if (need) { l *= alpha; m_used = m_new; }
         if (j > 0) {
-          if (!mbar_wait_bounded(pvdone, (j - 1) & 1, abort_flag, status, 1310)) { ok = false; break; }
+          if (!mbar_wait_bounded(&pvdone[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, status, 1310)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
@@ -244,11 +286,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_wait_st();
         }
       }
-      if (j > 0) {
-        if (!mbar_wait_bounded(pvdone, (j - 1) & 1, abort_flag, status, 1320)) { ok = false; break; }
+      if (j > 1) {   // P buffer j & 1 was last read by the PV product of tile j - 2
+        if (!mbar_wait_bounded(&pvdone[j & 1], (((j >> 1) & 1) ^ 1), abort_flag, status, 1320)) { ok = false; break; }
       }
+      if (threadIdx.x == 64) LLMT_TL(0, j, 3);
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float rs = 0.f;
+      float rsum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < kFwdKV / 32; ++c) {
         uint32_t w[16];
@@ -260,18 +303,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (kbase + c * 32 + i >= row_limit) p0 = 0.f;
             if (kbase + c * 32 + i + 1 >= row_limit) p1 = 0.f;
           }
-          rs += p0 + p1;
+          rsum[(i >> 1) & 3] += p0 + p1;
           w[i >> 1] = pack_bf16x2(p0, p1);
         }
-        store_row32_swz(sP, row, c * 32, w);
+        store_row32_swz(sP + (j & 1) * kPBytes, row, c * 32, w);
       }
-      l += rs;
+      l += (rsum[0] + rsum[1]) + (rsum[2] + rsum[3]);
+      if (threadIdx.x == 64) LLMT_TL(0, j, 4);
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(pfull);
+      mbar_arrive(&pfull[j & 1]);
+      if (threadIdx.x == 64) LLMT_TL(0, j, 5);
     }
     // ---- finalize
-    if (ok && n_kv > 0) ok = mbar_wait_bounded(pvdone, (n_kv - 1) & 1, abort_flag, status, 1330);
+    if (ok && n_kv > 0) ok = mbar_wait_bounded(&pvdone[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, status, 1330);
     if (ok) {
       tc_fence_after();
       const float inv = (l > 0.f) ? 1.f / l : 0.f;
@@ -333,9 +378,10 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t o
 // double buffered in TMEM, Q / dO and P^T / dS^T are double buffered in shared memory, so the MMAs of q tile i+1 run
 // while the 128 compute threads turn S^T, dP^T of tile i into P^T, dS^T; dV and dK accumulate in TMEM over the whole walk.
 constexpr int kBwdQ = 64;
+constexpr int kBwdThreads = 64 + 256;   // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter, one per column half)
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
@@ -383,10 +429,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(kv_full, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1);
-      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 128);
-      mbar_init(&p_full[b], 128); mbar_init(&p_empty[b], 1);
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 256);
+      mbar_init(&p_full[b], 256); mbar_init(&p_empty[b], 1);
     }
-    mbar_init(acc_done, 1); mbar_init(stat_ready, 128);
+    mbar_init(acc_done, 1); mbar_init(stat_ready, 256);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -473,7 +519,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // key row inside the tile
-    const int tid = threadIdx.x - 64;     // 0..127
+    const int tid = threadIdx.x - 64;     // 0..255
+    const int half = tid >> 7;            // which 32 of the 64 query columns this thread handles
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int key_idx = kk0 + row;
     const bool key_ok = (row < nk) && (key_idx < klen);
@@ -494,19 +541,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!mbar_wait_bounded(stat_ready, it & 1, abort_flag, status, 2330)) { ok = false; break; }
       if (!mbar_wait_bounded(&s_full[b], ph, abort_flag, status, 2300 + b)) { ok = false; break; }
       tc_fence_after();
-      uint32_t rs[kBwdQ], rd[kBwdQ];
-      tmem_ld_32x32(tST + lane_off + b * kBwdQ, rs);
-      tmem_ld_32x32(tST + lane_off + b * kBwdQ + 32, rs + 32);
-      tmem_ld_32x32(tDPT + lane_off + b * kBwdQ, rd);
-      tmem_ld_32x32(tDPT + lane_off + b * kBwdQ + 32, rd + 32);
+      uint32_t rs[32], rd[32];
+      tmem_ld_32x32(tST + lane_off + b * kBwdQ + half * 32, rs);
+      tmem_ld_32x32(tDPT + lane_off + b * kBwdQ + half * 32, rd);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&s_empty[b]);
       if (!mbar_wait_bounded(&p_empty[b], ph ^ 1, abort_flag, status, 2310 + b)) { ok = false; break; }
       const float* pl = s_lse + b * kBwdQ;
       const float* pd = s_delta + b * kBwdQ;
-#pragma unroll
-      for (int c = 0; c < kBwdQ / 32; ++c) {
+      {
+        const int c = half;
         uint32_t wp[16], wd[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -516,9 +561,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int qc = c * 32 + i + e;
             const int qi = qi0 + qc;
             const bool vis = key_ok && (qi < qlen) && (!causal || key_idx <= qi + off);
-            const float pv = vis ? ex2(__uint_as_float(rs[qc]) * scale_log2 - pl[qc]) : 0.f;
+            const float pv = vis ? ex2(__uint_as_float(rs[i + e]) * scale_log2 - pl[qc]) : 0.f;
             p[e] = pv;
-            ds[e] = pv * (__uint_as_float(rd[qc]) - pd[qc]);
+            ds[e] = pv * (__uint_as_float(rd[i + e]) - pd[qc]);
           }
           wp[i >> 1] = pack_bf16x2(p[0], p[1]);
           wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
@@ -535,7 +580,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       __nv_bfloat16* kr = dK + (int64_t)(k0 + row) * dk_stride + (int64_t)hk * HD;
       __nv_bfloat16* vr = dV + (int64_t)(k0 + row) * dv_stride + (int64_t)hk * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t rk[32], rv[32];
         if (n_it > 0) {
           tmem_ld_32x32(tDK + lane_off + c * 32, rk);
@@ -581,7 +626,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 // =========================================================================================== backward: dQ
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
@@ -622,7 +667,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1); mbar_init(&vfull[s], 1); mbar_init(&vempty[s], 1);
     }
-    mbar_init(s_full, 1); mbar_init(ds_full, 128); mbar_init(dq_done, 1);
+    mbar_init(s_full, 1); mbar_init(ds_full, 256); mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -699,6 +744,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __syncwarp();
   } else {
     const int quarter = warp & 3;
+    const int half = (threadIdx.x - 64) >> 7;   // which 64 of the 128 key columns this thread handles
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const bool row_ok = row < nq;
@@ -715,7 +761,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       const int kbase = j * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t rs[32], rd[32], wd[16];
         tmem_ld_32x32(tS + lane_off + c * 32, rs);
         tmem_ld_32x32(tDP + lane_off + c * 32, rd);
@@ -742,7 +788,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       __nv_bfloat16* qr = dQ + (int64_t)(q0 + row) * dq_stride + (int64_t)h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t r[32];
         if (n_kv > 0) {
           tmem_ld_32x32(tDQ + lane_off + c * 32, r);
@@ -791,6 +837,12 @@ static int set_smem(K kern, int bytes) {
 
 using namespace llmt;
 
+#ifdef LLMT_ATTN_TIMELINE
+extern "C" int llmt_attn_timeline(long long* host_out, int n) {
+  return cudaMemcpyFromSymbol(host_out, g_attn_dbg, sizeof(long long) * (n < 4096 ? n : 4096)) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 extern "C" int llmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* tiles, int num_tiles,
                              int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
                              int64_t o_stride, float scale, int causal, int* status, cudaStream_t st) {
@@ -800,7 +852,7 @@ extern "C" int llmt_attn_fwd(const void* q, const void* k, const void* v, void* 
   if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride, kFwdKV) ||
       make_thd_map(&tv, v, Tk, Hkv, HD, v_stride, kFwdKV))
     return -11;
-  const int smem = 128 * HD * 2 + 3 * kFwdKV * HD * 2 + 128 * kFwdKV * 2 + 1024 + 256;
+  const int smem = 128 * HD * 2 + 3 * kFwdKV * HD * 2 + 2 * 128 * kFwdKV * 2 + 256;   // exact: no alignment slack, see the kernel
   const float sl2 = scale * kLog2e;
   if (HD == 128) {
     static bool cfg = false;
@@ -846,11 +898,11 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
       cfg = true;
     }
     if (num_k_tiles > 0)
-      attn_bwd_dkv_kernel<128><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
+      attn_bwd_dkv_kernel<128><<<num_k_tiles * Hkv, kBwdThreads, smem_kv, st>>>(
           tq64, tk, tv, tdo64, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
           causal, pass > 0, status);
     if (num_q_tiles > 0 && pass == 0)
-      attn_bwd_dq_kernel<128><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
+      attn_bwd_dq_kernel<128><<<num_q_tiles * Hq, kBwdThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
                                                                               q_tiles, Hq, Hkv, Tq, dq_stride, scale, causal,
                                                                               status);
   } else {
@@ -860,11 +912,11 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
       cfg = true;
     }
     if (num_k_tiles > 0)
-      attn_bwd_dkv_kernel<64><<<num_k_tiles * Hkv, kAttnThreads, smem_kv, st>>>(
+      attn_bwd_dkv_kernel<64><<<num_k_tiles * Hkv, kBwdThreads, smem_kv, st>>>(
           tq64, tk, tv, tdo64, lse, delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, k_tiles, Hq, Hkv, Tq, dk_stride, dv_stride, scale,
           causal, pass > 0, status);
     if (num_q_tiles > 0 && pass == 0)
-      attn_bwd_dq_kernel<64><<<num_q_tiles * Hq, kAttnThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
+      attn_bwd_dq_kernel<64><<<num_q_tiles * Hq, kBwdThreads, smem_q, st>>>(tq, tk, tv, tdo, lse, delta, (__nv_bfloat16*)dq,
                                                                              q_tiles, Hq, Hkv, Tq, dq_stride, scale, causal,
                                                                              status);
   }
