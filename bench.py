@@ -160,6 +160,8 @@ def main() -> int:
     n0 = ext.launch_count()
     ms_dev = timed(lambda: tr.train_step(batches=next(it), read_stats=False), args.steps)
     launches = ext.launch_count() - n0
+    fused = getattr(getattr(tr.asm, "fsdp", None), "fused", None)
+    qs = dict(fused.queue.stats) if fused is not None and fused.queue is not None else None
     clocks = sampler.stop() if sampler else {}
     # ---- end to end: pinned host -> device copy of every step's inputs, loss read back every step
     h2d = d2h = 0
@@ -185,7 +187,8 @@ def main() -> int:
                                       "d2h_bytes_per_step": d2h},
            "gpu_launches": int(launches), "mfu_nominal_pct": 100 * value / world * fpt / 2.25e15,
            "tflops_per_gpu": value / world * fpt / 1e12, "final_loss": results[-1].loss if results else None,
-           "peak_mem_gib": mem, "impl": "ours"}
+           "peak_mem_gib": mem, "impl": "ours",
+           "comm_fused_fraction": (qs["bytes_fused"] / max(1, qs["bytes_fused"] + qs["bytes_standalone"])) if qs else None}
     tr.close()
     if rank == 0:
         print(json.dumps(out))

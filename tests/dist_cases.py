@@ -42,7 +42,14 @@ def train_case(flat: dict, arch: dict | None, out_path: str, steps: int = 3, rep
         tr.checkpointer.save(tr.progress.step, force=True)
     if int(os.environ.get("RANK", "0")) == 0:
         with open(out_path, "w") as f:
-            json.dump({"loss": losses, "grad_norm": norms}, f)
+            extra = {}
+            try:
+                from torchllmtuner_b200.parallel import symm_tp
+                for c in symm_tp._COMMS.values():
+                    extra["tp_fused"] = dict(c.stats)
+            except Exception:
+                pass
+            json.dump({"loss": losses, "grad_norm": norms, **extra}, f)
     tr.close()
     import torch.distributed as dist
     if dist.is_initialized():

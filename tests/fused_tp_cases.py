@@ -1,0 +1,79 @@
+"""Workers for the fused tensor-parallel GEMM tests (one process per GPU, NCCL only for the reference collectives)."""
+import json
+import os
+import sys
+
+import torch
+
+
+def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    from torchllmtuner_b200.parallel.symm_tp import FusedTPComm, GatherLinears, LinearReduceScatter
+    T, D, N1, N2, Kl = 256 * world, 512, 384, 136, 320
+    comm = FusedTPComm(dist.group.WORLD, dev, T, D)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    res = {"ag": 0.0, "rs": 0.0, "ag_bwd": 0.0, "rs_bwd": 0.0}
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+    for it in range(iters):
+        xs = (torch.randn(T // world, D, generator=g, device=dev) * 0.5).bfloat16().requires_grad_()
+        w1 = (torch.randn(N1, D, generator=g, device=dev) * 0.05).bfloat16().requires_grad_()
+        w2 = (torch.randn(N2, D, generator=g, device=dev) * 0.05).bfloat16().requires_grad_()
+        # reference: NCCL gather + fp32 matmuls
+        full = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(full, xs.detach())
+        y1, y2 = GatherLinears.apply(comm, xs, w1, w2)
+        r1, r2 = full.float() @ w1.float().t(), full.float() @ w2.float().t()
+        res["ag"] = max(res["ag"], rel(y1, r1), rel(y2, r2))
+        d1 = (torch.randn(T, N1, generator=g, device=dev) * 0.1).bfloat16()
+        d2 = (torch.randn(T, N2, generator=g, device=dev) * 0.1).bfloat16()
+        torch.autograd.backward([y1, y2], [d1, d2])
+        dfull = d1.float() @ w1.float() + d2.float() @ w2.float()
+        dref = torch.empty(T // world, D, dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(dref, dfull)
+        res["ag_bwd"] = max(res["ag_bwd"], rel(xs.grad, dref), rel(w1.grad, d1.float().t() @ full.float()))
+        # row-parallel form
+        a = (torch.randn(T, Kl, generator=g, device=dev) * 0.5).bfloat16().requires_grad_()
+        w = (torch.randn(D, Kl, generator=g, device=dev) * 0.05).bfloat16().requires_grad_()
+        out = LinearReduceScatter.apply(comm, a, w)
+        pref = a.float() @ w.float().t()
+        oref = torch.empty(T // world, D, dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(oref, pref)
+        res["rs"] = max(res["rs"], rel(out, oref))
+        dy = (torch.randn(T // world, D, generator=g, device=dev) * 0.1).bfloat16()
+        out.backward(dy)
+        dyf = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(dyf, dy)
+        res["rs_bwd"] = max(res["rs_bwd"], rel(a.grad, dyf.float() @ w.float()), rel(w.grad, dyf.float().t() @ a.float()))
+        if it % 2 == rank % 2:          # skew the ranks so that flags, not luck, order the accesses
+            torch.cuda._sleep(20_000_000)
+    torch.cuda.synchronize()
+    check_status("fused tp test")
+    t = torch.tensor([res[k] for k in sorted(res)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump({**dict(zip(sorted(res), t.tolist())), "stats": comm.stats}, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_fused_tp(world: int, iters: int = 5) -> dict:
+    import tempfile
+
+    import torch.multiprocessing as mp
+    out = tempfile.mktemp(suffix=".json")
+    port = 21000 + (os.getpid() * 13 + world) % 20000
+    mp.spawn(_worker, args=(world, port, out, iters), nprocs=world, join=True)
+    with open(out) as f:
+        res = json.load(f)
+    os.unlink(out)
+    return res

@@ -41,3 +41,24 @@ def test_parallel_modes_gpu_match_single_gpu(name, flat, arch):
     ref = run_ranks(1, _flat(**base), arch=arch, device="cuda")
     got = run_ranks(2, _flat(**flat), arch=arch, device="cuda")
     assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (name, ref, got)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_tp_gemms_match_nccl_reference(world):
+    """all-gather -> GEMM and GEMM -> reduce-scatter over peer memory, forward and backward, with slot reuse."""
+    _need(world)
+    from fused_tp_cases import run_fused_tp
+    res = run_fused_tp(world)
+    for k in ("ag", "rs", "ag_bwd", "rs_bwd"):
+        assert res[k] < 2e-2, res
+    assert res["stats"]["ag_fused"] > 0 and res["stats"]["rs_fused"] > 0
+
+
+def test_tp2_model_uses_fused_collectives():
+    _need(2)
+    flat = _flat(tensor_parallel_size=2, data_parallel_shard_size=1)
+    flat["max_seq_len"] = 512
+    ref = run_ranks(1, dict(_flat(), max_seq_len=512), device="cuda")
+    got = run_ranks(2, flat, device="cuda")
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (ref, got)
+    assert got.get("tp_fused", {}).get("ag_fused", 0) > 0, got

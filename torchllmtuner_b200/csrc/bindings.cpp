@@ -77,9 +77,55 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, b
              "llmt_gemm_bf16_fused");
     return;
   }
-  check_rc(llmt_gemm_bf16(A.ptr, B.ptr, out.data_ptr(), (int)M, (int)N, (int)K, A.ld, B.ld, out.stride(0), a_mn, b_mn, f32,
-                          accumulate, status_ptr(), (int)max_ctas, cur_stream()),
-           "llmt_gemm_bf16");
+  const int rc = llmt_gemm_bf16(A.ptr, B.ptr, out.data_ptr(), (int)M, (int)N, (int)K, A.ld, B.ld, out.stride(0), a_mn, b_mn, f32,
+                                accumulate, status_ptr(), (int)max_ctas, cur_stream());
+  TORCH_CHECK(rc == 0, "llmt_gemm_bf16 failed with code ", rc, " (M=", M, " N=", N, " K=", K, " lda=", A.ld, " ldb=", B.ld,
+              " ldc=", out.stride(0), " a_mn=", a_mn, " b_mn=", b_mn, " a%16=", reinterpret_cast<uintptr_t>(A.ptr) % 16,
+              " b%16=", reinterpret_cast<uintptr_t>(B.ptr) % 16, ")");
+  g_launches += 1;
+}
+
+// GEMM fused with a tensor-parallel row collective over peer memory (csrc/comm.cuh). mode 1: `a` is the local gathered
+// matrix [M,K] that the kernel fills from `peer_src` (each rank's [M/world, K] chunk) while it multiplies; mode 2: `c` is
+// this rank's symmetric partial matrix [M,N], `out` [M/world, N] receives the reduced rows (+ residual).
+void gemm_tp(const Tensor& a, const Tensor& b, Tensor& c, bool b_mn, bool accumulate, int64_t mode, int64_t world, int64_t rank, int64_t epoch,
+             const std::vector<int64_t>& peer_src, int64_t flags, const std::vector<int64_t>& peer_flags, Tensor& counters,
+             const c10::optional<Tensor>& acc, const c10::optional<Tensor>& out, const c10::optional<Tensor>& residual) {
+  c10::cuda::CUDAGuard guard(a.device());
+  const Mat A = as_mat(a, "a"), B = as_mat(b, "b");
+  check_bf16(c, "c");
+  TORCH_CHECK(c.dim() == 2 && c.stride(1) == 1);
+  const int64_t M = A.rows, K = A.cols, N = b_mn ? B.cols : B.rows, Kb = b_mn ? B.rows : B.cols;
+  TORCH_CHECK(K == Kb && c.size(0) == M && c.size(1) == N, "gemm_tp: shapes do not match");
+  TORCH_CHECK(!accumulate || b_mn, "gemm_tp: accumulate is only built for the [K][N] layout of b");
+  TORCH_CHECK((int64_t)peer_src.size() == world && (int64_t)peer_flags.size() == world && world <= 8);
+  TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() >= 3 * world);
+  const void* ps[8] = {nullptr};
+  uint32_t* pf[8] = {nullptr};
+  for (int64_t i = 0; i < world; ++i) {
+    ps[i] = reinterpret_cast<const void*>(peer_src[i]);
+    pf[i] = reinterpret_cast<uint32_t*>(peer_flags[i]);
+  }
+  float* accp = nullptr;
+  void* outp = nullptr;
+  const void* resp = nullptr;
+  if (mode == 2) {
+    TORCH_CHECK(acc.has_value() && out.has_value(), "reduce-scatter form needs acc and out");
+    TORCH_CHECK(acc->scalar_type() == at::kFloat && acc->is_contiguous() && acc->numel() >= M / world * N);
+    check_bf16(*out, "out");
+    TORCH_CHECK(out->is_contiguous() && out->numel() == M / world * N);
+    accp = acc->data_ptr<float>();
+    outp = out->data_ptr();
+    if (residual.has_value()) {
+      check_bf16(*residual, "residual");
+      TORCH_CHECK(residual->is_contiguous() && residual->numel() == out->numel());
+      resp = residual->data_ptr();
+    }
+  }
+  check_rc(llmt_gemm_bf16_tp(A.ptr, B.ptr, c.data_ptr(), (int)M, (int)N, (int)K, A.ld, B.ld, c.stride(0), b_mn, accumulate, (int)mode, (int)world,
+                             (int)rank, (uint32_t)epoch, ps, reinterpret_cast<const uint32_t*>(flags), pf,
+                             reinterpret_cast<uint32_t*>(counters.data_ptr<int>()), accp, outp, resp, status_ptr(), cur_stream()),
+           "llmt_gemm_bf16_tp");
 }
 
 void side_job(const PySideJob& j, int64_t ctas) {
@@ -441,6 +487,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("permute_rows", &permute_rows);
   m.def("combine_rows", &combine_rows);
   m.def("combine_bwd", &combine_bwd);
+  m.def("gemm_tp", &gemm_tp, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("b_mn"), py::arg("accumulate"), py::arg("mode"), py::arg("world"),
+        py::arg("rank"), py::arg("epoch"), py::arg("peer_src"), py::arg("flags"), py::arg("peer_flags"), py::arg("counters"),
+        py::arg("acc") = py::none(), py::arg("out") = py::none(), py::arg("residual") = py::none());
   m.def("side_job", &side_job);
   m.def("signal_peers", &signal_peers);
   m.def("wait_flags", &wait_flags);

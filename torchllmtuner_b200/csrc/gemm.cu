@@ -38,7 +38,7 @@ struct GroupedArgs {
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, int MODE>
 __global__ void __launch_bounds__(kGemmThreadsComm, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    void* __restrict__ Cptr, int M, int N, int K, int64_t ldc, GroupedArgs grp, SideJob side, int* status) {
+                    void* __restrict__ Cptr, int M, int N, int K, int64_t ldc, GroupedArgs grp, SideJob side, TPFuse tp, int* status) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -49,6 +49,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* comm_word = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -98,7 +99,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // Tile order inside one M x N problem: super-rows of kGroupM m-tiles are swept column by column, so the CTAs that
   // run concurrently cover a near-square patch (A and B tiles are both reused out of L2).
   constexpr int kGroupM = 16;
+  // With a fused tensor-parallel collective (MODE 0 only) the rows are walked chunk by chunk instead: the all-gather
+  // form starts with this rank's own chunk, the reduce-scatter form ends with it.
+  const bool tp_on = (MODE == 0) && tp.mode != kTPNone;
+  const int tp_mpc = tp_on ? tp.chunk_rows / BM : 1;
+  const int tp_tpc = tp_mpc * num_n;
+  auto tp_chunk_of = [&](int tt) -> int { return (tp.rank + tt / tp_tpc + (tp.mode == kTPReduceScatter ? 1 : 0)) % tp.world; };
   auto tile_mn = [&](int tt, int& m0, int& n0) {
+    if (tp_on) {
+      const int w = tt % tp_tpc;
+      m0 = (tp_chunk_of(tt) * tp_mpc + w % tp_mpc) * BM;
+      n0 = (w / tp_mpc) * BN;
+      return;
+    }
     const int per_group = kGroupM * num_n;
     const int grp_i = tt / per_group;
     const int first_m = grp_i * kGroupM;
@@ -124,9 +137,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       uint32_t armed = 0, armed_parity = 0;  // per-stage bookkeeping for the abort drain
       bool ok = true;
+      int landed_chunk = -1;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m0, n0;
         tile_mn(t % tiles_per_group, m0, n0);
+        if (tp_on && tp.mode == kTPAllGather) {
+          const int c = tp_chunk_of(t);
+          if (c != landed_chunk) {
+            if (!tp_wait_landed(tp, c, abort_flag, status)) break;
+            landed_chunk = c;
+          }
+        }
         int g = 0;
         if constexpr (GROUPED) g = group_of_row(m0);
         int k_begin;
@@ -212,7 +233,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncwarp();
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ comm warps (only launched with a SideJob)
-    run_side_job(side, (long long)blockIdx.x * kCommThreads + (threadIdx.x - 192), (long long)gridDim.x * kCommThreads, status);
+    if (tp_on) {
+      if (tp.mode == kTPAllGather) tp_allgather_comm(tp, threadIdx.x - 192, comm_word, status);
+      else tp_reducescatter_comm(tp, threadIdx.x - 192, comm_word, status);
+    } else {
+      run_side_job(side, (long long)blockIdx.x * kCommThreads + (threadIdx.x - 192), (long long)gridDim.x * kCommThreads, status);
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
@@ -298,6 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_before();
       mbar_arrive(&tempty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (tp_on && tp.mode == kTPReduceScatter) tp_tile_done(tp, tp_chunk_of(t), (uint32_t)tp_tpc * 4u, lane);
     }
   }
 
@@ -330,6 +357,13 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
                    const uint32_t* box) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return -1;
+  // The encoder is a driver call and needs the primary context bound to the calling thread; a fresh thread (the
+  // autograd engine's) has none until its first runtime call.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t gdim[5], gstr[5];
   cuuint32_t bx[5], es[5];
   for (int i = 0; i < rank; ++i) {
@@ -356,7 +390,7 @@ int sm_count() {
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, int MODE>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int64_t ldc, GroupedArgs grp,
-                  int* status, int max_ctas, cudaStream_t stream, const SideJob* side = nullptr) {
+                  int* status, int max_ctas, cudaStream_t stream, const SideJob* side = nullptr, const TPFuse* tpf = nullptr) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OUT_F32, ACCUM, MODE>;
   static bool configured = false;
@@ -369,25 +403,28 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, 
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid < 1) return 0;
   SideJob none{};
-  const bool with_side = side != nullptr && side->kind != kSideNone;
+  TPFuse no_tp{};
+  const bool with_tp = tpf != nullptr && tpf->mode != kTPNone;
+  const bool with_side = (side != nullptr && side->kind != kSideNone) || with_tp;
   if (with_side && max_ctas <= 0) grid = sm_count();   // every SM carries comm warps, even past the last tile
-  kern<<<grid, with_side ? kGemmThreadsComm : kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, C, M, N, K, ldc, grp,
-                                                                                     with_side ? *side : none, status);
+  kern<<<grid, with_side ? kGemmThreadsComm : kGemmThreads, Cfg::kSmemBytes, stream>>>(
+      ta, tb, C, M, N, K, ldc, grp, (side != nullptr && !with_tp) ? *side : none, with_tp ? *tpf : no_tp, status);
   return (cudaGetLastError() == cudaSuccess) ? 0 : -3;
 }
 
 template <int BN>
 static int dispatch_plain(bool a_mn, bool b_mn, bool out_f32, bool accum, const CUtensorMap& ta, const CUtensorMap& tb,
                           void* C, int M, int N, int K, int64_t ldc, int* status, int max_ctas, cudaStream_t s,
-                          const SideJob* side) {
+                          const SideJob* side, const TPFuse* tpf = nullptr) {
   GroupedArgs grp{nullptr, 0};
 #define LLMT_CASE(AM, BMN, F32, ACC)                                                            \
   if (a_mn == AM && b_mn == BMN && out_f32 == F32 && accum == ACC)                              \
-    return launch<BN, AM, BMN, F32, ACC, 0>(ta, tb, C, M, N, K, ldc, grp, status, max_ctas, s, side);
+    return launch<BN, AM, BMN, F32, ACC, 0>(ta, tb, C, M, N, K, ldc, grp, status, max_ctas, s, side, tpf);
   LLMT_CASE(false, false, false, false)
   LLMT_CASE(false, false, true, false)
   LLMT_CASE(false, true, false, false)
   LLMT_CASE(false, true, true, false)
+  LLMT_CASE(false, true, false, true)
   LLMT_CASE(true, true, false, false)
   LLMT_CASE(true, true, true, false)
   LLMT_CASE(true, true, false, true)
@@ -405,7 +442,8 @@ using namespace llmt;
 //   b_mn == 0: B stored [N][K] (row stride ldb);          b_mn == 1: B stored [K][N].
 // Requirements: base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
 static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_mn,
-                     int b_mn, int out_f32, int accumulate, int* status, int max_ctas, cudaStream_t stream, const SideJob* side) {
+                     int b_mn, int out_f32, int accumulate, int* status, int max_ctas, cudaStream_t stream, const SideJob* side,
+                     const TPFuse* tpf = nullptr) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -10;
   const bool bn256 = N > 128;
@@ -417,14 +455,14 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
     if (!a_mn) { dims[0] = K; dims[1] = M; box[0] = 64; box[1] = BM; }
     else       { dims[0] = M; dims[1] = K; box[0] = 64; box[1] = BK; }
     str[0] = (uint64_t)lda * 2;
-    if (make_tmap_bf16(&ta, A, 2, dims, str, box)) return -11;
+    if (int rc = make_tmap_bf16(&ta, A, 2, dims, str, box)) return -1100 - rc;
     if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = 64; box[1] = bn; }
     else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = BK; }
     str[0] = (uint64_t)ldb * 2;
     if (make_tmap_bf16(&tb, B, 2, dims, str, box)) return -12;
   }
-  if (bn256) return dispatch_plain<256>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream, side);
-  return dispatch_plain<128>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream, side);
+  if (bn256) return dispatch_plain<256>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream, side, tpf);
+  return dispatch_plain<128>(a_mn, b_mn, out_f32, accumulate, ta, tb, C, M, N, K, ldc, status, max_ctas, stream, side, tpf);
 }
 
 extern "C" int llmt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
@@ -453,6 +491,31 @@ extern "C" int llmt_gemm_bf16_fused(const void* A, const void* B, void* C, int M
   return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, accumulate, status, 0, stream, &j);
 }
 
+// Tensor-parallel fused forms (see comm.cuh). mode 1: C[M,N] = gather(A) * B where `A` is the local gathered matrix
+// [M,K] that the comm warps fill from `peer_src` (every rank's chunk); mode 2: `C` is this rank's symmetric bf16 partial
+// matrix [M,N] (ldc == N), `out` [M/world, N] receives the reduced chunk (+ residual). A is row-major in both.
+// `accumulate` (only with b_mn) adds the product to what C already holds before the partial is published.
+extern "C" int llmt_gemm_bf16_tp(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                 int64_t ldc, int b_mn, int accumulate, int mode, int world, int rank, uint32_t epoch,
+                                 const void* const* peer_src, const uint32_t* flags, uint32_t* const* peer_flags,
+                                 uint32_t* counters, float* acc, void* out, const void* residual, int* status,
+                                 cudaStream_t stream) {
+  if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world || M % world) return -10;
+  const int chunk_rows = M / world;
+  if (chunk_rows % BM || (mode != kTPAllGather && mode != kTPReduceScatter)) return -10;
+  if (mode == kTPReduceScatter && (ldc != N || (N & 7))) return -10;
+  if (mode == kTPAllGather && lda != K) return -10;
+  TPFuse t{};
+  t.mode = mode; t.world = world; t.rank = rank; t.chunk_rows = chunk_rows; t.epoch = epoch;
+  for (int i = 0; i < world; ++i) { t.peer_src[i] = peer_src[i]; t.peer_flags[i] = peer_flags[i]; }
+  t.local_dst = const_cast<void*>(A);
+  t.chunk_bytes = (long long)chunk_rows * K * 2;
+  t.flags = flags; t.counters = counters;
+  t.acc = acc; t.out = reinterpret_cast<__nv_bfloat16*>(out); t.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  t.n_cols = N;
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, b_mn, 0, accumulate, status, 0, stream, nullptr, &t);
+}
+
 // Grouped forward/dgrad: rows of A (and C) are cut into `num_groups` segments at seg_offsets (device int32,
 // [G+1], multiples of 128, seg_offsets[G] == M_padded); segment g multiplies B[g].
 //   b_mn == 0: B stored [G][N][K];  b_mn == 1: B stored [G][K][N].
@@ -469,7 +532,7 @@ extern "C" int llmt_grouped_gemm_bf16(const void* A, const void* B, void* C, con
     uint32_t box[3];
     dims[0] = K; dims[1] = M_padded; box[0] = 64; box[1] = BM;
     str[0] = (uint64_t)lda * 2;
-    if (make_tmap_bf16(&ta, A, 2, dims, str, box)) return -11;
+    if (int rc = make_tmap_bf16(&ta, A, 2, dims, str, box)) return -1100 - rc;
     if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = 64; box[1] = bn; str[0] = (uint64_t)K * 2; }
     else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = BK; str[0] = (uint64_t)N * 2; }
     dims[2] = num_groups; box[2] = 1;
@@ -499,7 +562,7 @@ extern "C" int llmt_grouped_wgrad_bf16(const void* A, const void* B, void* C, co
     uint64_t dims[2], str[1];
     uint32_t box[2];
     dims[0] = M; dims[1] = rows_padded; box[0] = 64; box[1] = BK; str[0] = (uint64_t)lda * 2;
-    if (make_tmap_bf16(&ta, A, 2, dims, str, box)) return -11;
+    if (int rc = make_tmap_bf16(&ta, A, 2, dims, str, box)) return -1100 - rc;
     dims[0] = N; dims[1] = rows_padded; box[0] = 64; box[1] = BK; str[0] = (uint64_t)ldb * 2;
     if (make_tmap_bf16(&tb, B, 2, dims, str, box)) return -12;
   }

@@ -16,6 +16,10 @@ int llmt_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, in
                          int a_mn, int b_mn, int out_f32, int accumulate, int job_kind, int job_nsrc,
                          const void* const* job_src, void* job_dst, long long job_n, int job_accumulate,
                          const uint32_t* wait_flags, int n_wait, uint32_t wait_value, int* status, cudaStream_t stream);
+int llmt_gemm_bf16_tp(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                      int b_mn, int accumulate, int mode, int world, int rank, uint32_t epoch, const void* const* peer_src,
+                      const uint32_t* flags, uint32_t* const* peer_flags, uint32_t* counters, float* acc, void* out,
+                      const void* residual, int* status, cudaStream_t stream);
 int llmt_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* seg_offsets, int num_groups, int M_padded,
                            int N, int K, int64_t lda, int64_t ldc, int b_mn, int out_f32, int* status,
                            cudaStream_t stream);

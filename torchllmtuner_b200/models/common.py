@@ -53,7 +53,12 @@ class GatedMLP(nn.Module):
         self.up_proj = Linear(hidden, inter, dtype, device)
         self.down_proj = Linear(inter, hidden, dtype, device)
 
+    accepts_sharded_rows = True     # `x` may be a row-sharded handle whose `linears` gathers inside the first GEMM
+
     def forward(self, x):
+        if hasattr(x, "linears"):
+            g, u = x.linears(self.gate_proj.weight, self.up_proj.weight)
+            return self.down_proj(ops.swiglu(g, u))
         return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
 
 

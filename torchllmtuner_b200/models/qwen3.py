@@ -113,9 +113,15 @@ class Qwen3Attention(nn.Module):
         self.k_norm = RMSNorm(d, cfg.rms_norm_eps, dtype, device) if cfg.qk_norm else None
         self.scale = 1.0 / math.sqrt(d)
 
+    accepts_sharded_rows = True     # `x` may be a row-sharded handle whose `linears` gathers inside the first GEMM
+
     def project_qkv(self, x):
-        T = x.shape[0]
         d = self.head_dim
+        if hasattr(x, "linears") and not self.fused_qkv:
+            q, k, v = x.linears(self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
+            T = q.shape[0]
+            return q.view(T, -1, d), k.view(T, -1, d), v.view(T, -1, d)
+        T = x.shape[0]
         if self.fused_qkv:
             qkv = self.qkv_proj(x)
             nq, nk = self.num_heads * d, self.num_kv_heads * d

@@ -82,9 +82,9 @@ def _ensure_builtins() -> None:
     reg = lambda n, b, **kw: register_model(n, b, replace=True, **kw)  # noqa: E731
     reg("qwen3_moe", qwen3.build_qwen3, state_format="qwen3", description="Qwen3 dense / MoE decoder")
     reg("qwen3", qwen3.build_qwen3, state_format="qwen3", description="dense Qwen3 (alias of qwen3_moe without experts)")
-    reg("qwen3_8b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_8B, **kw}),
+    reg("qwen3_8b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_8B, **(mc.arch_overrides or {}), **kw}),
         state_format="qwen3", description="Qwen3-8B architecture")
-    reg("qwen3_30b_a3b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_30B_A3B, **kw}),
+    reg("qwen3_30b_a3b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_30B_A3B, **(mc.arch_overrides or {}), **kw}),
         state_format="qwen3", description="Qwen3-30B-A3B architecture")
     try:
         from . import families

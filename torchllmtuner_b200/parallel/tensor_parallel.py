@@ -127,7 +127,33 @@ class RowParallelLinear(ShardedLinear):
         self.group = group
 
     def forward(self, x):
+        if x.is_cuda and x.dim() == 2 and x.shape[0] % dist.get_world_size(self.group) == 0:
+            from .symm_tp import LinearReduceScatter
+            R = dist.get_world_size(self.group)
+            comm = _comm_for(self.group, x.shape[0] // R, self.weight.shape[0], x)
+            if comm is not None:
+                return LinearReduceScatter.apply(comm, x, self.weight)
         return reduce_scatter_along(super().forward(x), self.group)
+
+
+def _comm_for(group, chunk_rows: int, cols: int, like: torch.Tensor):
+    """Fused communicator of the group when a `[chunk_rows, cols]` bf16 chunk fits its arena (created on first use
+    with that shape), else None."""
+    if not like.is_cuda or like.dtype != torch.bfloat16:
+        return None
+    from .symm_tp import fused_tp_comm
+    return fused_tp_comm(group, torch.empty((chunk_rows, cols), dtype=like.dtype, device="meta"), like.device)
+
+
+class ShardedRows:
+    """Handle for `[T/R, D]` rows whose gather is deferred into the first column-parallel GEMM that consumes them."""
+
+    def __init__(self, comm, x_shard):
+        self.comm, self.x_shard = comm, x_shard
+
+    def linears(self, *weights):
+        from .symm_tp import GatherLinears
+        return GatherLinears.apply(self.comm, self.x_shard, *weights)
 
 
 class GatherSequenceFirst(nn.Module):
@@ -138,6 +164,10 @@ class GatherSequenceFirst(nn.Module):
         self.inner, self.group = inner, group
 
     def forward(self, x, *args, **kw):
+        if getattr(self.inner, "accepts_sharded_rows", False) and not getattr(self.inner, "fused_qkv", False) and x.dim() == 2:
+            comm = _comm_for(self.group, x.shape[0], x.shape[1], x)
+            if comm is not None:
+                return self.inner(ShardedRows(comm, x), *args, **kw)
         return self.inner(all_gather_along(x, self.group), *args, **kw)
 
     def __getattr__(self, name):
