@@ -83,14 +83,34 @@ def reference_arm(args) -> int:
 def build_config(args, world: int):
     from torchllmtuner_b200 import LLMTunerConfig
     cfg = LLMTunerConfig()
-    flat = dict(model_name_or_path=args.model, initialization_device="meta", global_batch_size=world * args.micro_batch,
+    dp = world // (args.tp * args.cp_ulysses * args.cp_kv)
+    gb = args.global_batch or dp * args.micro_batch * args.accum
+    flat = dict(model_name_or_path=args.model, initialization_device="meta", global_batch_size=gb,
                 max_seq_len=args.seq, steps=10 ** 6, activation_checkpoint_mode=args.ac, chunked_loss_num_chunks=args.loss_chunks,
-                seed=0, dump_folder="/tmp/llmt_bench", data_parallel_shard_size=world, log_freq=10 ** 6, gc_freq=10 ** 6,
-                fsdp_implementation=args.fsdp_impl, deterministic=False)
+                seed=0, dump_folder="/tmp/llmt_bench", data_parallel_shard_size=dp, log_freq=10 ** 6, gc_freq=10 ** 6,
+                fsdp_implementation=args.fsdp_impl, deterministic=False, gradient_accumulation_steps=args.accum)
+    if args.tp > 1:
+        flat["tensor_parallel_size"] = args.tp
+    if args.ep > 1:
+        flat["expert_parallel_size"] = args.ep
+    if args.cp_ulysses > 1:
+        flat["context_parallel_ulysses_size"] = args.cp_ulysses
+    if args.cp_kv > 1:
+        flat.update(context_parallel_kv_allgather_size=args.cp_kv, context_parallel_load_balancer="headtail")
     cfg.apply_flat(flat)
     if args.layers:
         cfg.model.arch_overrides = dict(cfg.model.arch_overrides, num_hidden_layers=args.layers)
     return cfg
+
+
+def _tp_stats():
+    try:
+        from torchllmtuner_b200.parallel import symm_tp
+        for c in symm_tp._COMMS.values():
+            return dict(c.stats)
+    except Exception:
+        pass
+    return None
 
 
 def main() -> int:
@@ -106,6 +126,12 @@ def main() -> int:
     ap.add_argument("--loss-chunks", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline metric)")
     ap.add_argument("--fsdp-impl", default="native", choices=["native", "custom"])
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (sequence parallel); the rest of the GPUs shard with FSDP")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (MoE models)")
+    ap.add_argument("--cp-ulysses", type=int, default=1)
+    ap.add_argument("--cp-kv", type=int, default=1)
+    ap.add_argument("--global-batch", type=int, default=0, help="sequences per step over the whole job (default: one per data-parallel rank)")
+    ap.add_argument("--accum", type=int, default=1, help="gradient accumulation steps")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -171,7 +197,10 @@ def main() -> int:
     results = []
     ms_e2e = timed(lambda: results.append(tr.train_step()), args.steps)
     check_status("bench")
-    tokens_per_step = world * args.micro_batch * args.seq
+    tokens_per_step = cfg.training.global_batch_size * args.seq
+    par = "+".join(p for p in (f"fsdp{tr.env.topo.dp_shard}" if tr.env.topo.dp_shard > 1 or world == 1 else "", f"tp{args.tp}" if args.tp > 1 else "",
+                               f"ep{args.ep}" if args.ep > 1 else "", f"cp_ulysses{args.cp_ulysses}" if args.cp_ulysses > 1 else "",
+                               f"cp_kv{args.cp_kv}" if args.cp_kv > 1 else "") if p)
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
     fpt = tr.model.flops_per_token(args.seq)
@@ -179,8 +208,8 @@ def main() -> int:
     out = {"metric": "training tokens/sec/box (device-timed, max over ranks), Qwen3-8B FSDP bf16 seq 8192", "value": value,
            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_dev / args.steps,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
-           "config": {"model": args.model + (f"[layers={args.layers}]" if args.layers else ""), "global_batch": world * args.micro_batch,
-                      "seq_len": args.seq, "parallelism": f"fsdp{world}", "activation_checkpointing": args.ac,
+           "config": {"model": args.model + (f"[layers={args.layers}]" if args.layers else ""), "global_batch": cfg.training.global_batch_size,
+                      "seq_len": args.seq, "parallelism": par, "activation_checkpointing": args.ac,
                       "loss": f"chunked x{args.loss_chunks}", "l2": "inputs (16 GB of weights per step) larger than the 126 MB L2",
                       "fsdp_implementation": args.fsdp_impl},
            "clocks": clocks, "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d,
@@ -188,6 +217,7 @@ def main() -> int:
            "gpu_launches": int(launches), "mfu_nominal_pct": 100 * value / world * fpt / 2.25e15,
            "tflops_per_gpu": value / world * fpt / 1e12, "final_loss": results[-1].loss if results else None,
            "peak_mem_gib": mem, "impl": "ours",
+           "tp_fused": _tp_stats(),
            "comm_fused_fraction": (qs["bytes_fused"] / max(1, qs["bytes_fused"] + qs["bytes_standalone"])) if qs else None}
     tr.close()
     if rank == 0:

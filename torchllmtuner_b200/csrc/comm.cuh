@@ -14,7 +14,7 @@
 namespace llmt {
 
 constexpr int kMaxPeers = 8;
-constexpr int kCommWarps = 4;
+constexpr int kCommWarps = 8;
 constexpr int kCommThreads = kCommWarps * 32;
 
 enum SideJobKind : int { kSideNone = 0, kSideCopy = 1, kSideReduce = 2 };
@@ -37,6 +37,28 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   return v;
 }
 
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Streaming copy out of (possibly peer) memory with `kCopyUnroll` 16-byte loads in flight per thread: over NVLink the
+// round trip is a few microseconds, so the bytes in flight across the comm warps must cover bandwidth x latency (~2 MB).
+constexpr int kCopyUnroll = 8;
+__device__ __forceinline__ void copy_stream16(const uint4* __restrict__ s, uint4* __restrict__ d, long long n16, long long tid,
+                                              long long nthreads) {
+  long long i = tid;
+  for (; i + (kCopyUnroll - 1) * nthreads < n16; i += kCopyUnroll * nthreads) {
+    uint4 v[kCopyUnroll];
+#pragma unroll
+    for (int u = 0; u < kCopyUnroll; ++u) v[u] = ld_stream16(s + i + u * nthreads);
+#pragma unroll
+    for (int u = 0; u < kCopyUnroll; ++u) d[i + u * nthreads] = v[u];
+  }
+  for (; i < n16; i += nthreads) d[i] = ld_stream16(s + i);
+}
+
 // Runs `job` cooperatively on `nthreads` threads (this thread is `tid`). Returns false when a flag wait expired.
 __device__ __forceinline__ bool run_side_job(const SideJob& job, long long tid, long long nthreads, int* status) {
   if (job.kind == kSideNone) return true;
@@ -46,16 +68,7 @@ __device__ __forceinline__ bool run_side_job(const SideJob& job, long long tid, 
       if (!flag_wait_bounded(job.wait_flags + f, job.wait_value, status, 5000 + f)) return false;
   }
   if (job.kind == kSideCopy) {
-    const long long n16 = job.n >> 4;
-    const uint4* s = reinterpret_cast<const uint4*>(job.src[0]);
-    uint4* d = reinterpret_cast<uint4*>(job.dst);
-    long long i = tid;
-    for (; i + 3 * nthreads < n16; i += 4 * nthreads) {   // four loads in flight per thread
-      const uint4 a = ld_peer16(s + i), b = ld_peer16(s + i + nthreads), c = ld_peer16(s + i + 2 * nthreads),
-                  e = ld_peer16(s + i + 3 * nthreads);
-      d[i] = a; d[i + nthreads] = b; d[i + 2 * nthreads] = c; d[i + 3 * nthreads] = e;
-    }
-    for (; i < n16; i += nthreads) d[i] = ld_peer16(s + i);
+    copy_stream16(reinterpret_cast<const uint4*>(job.src[0]), reinterpret_cast<uint4*>(job.dst), job.n >> 4, tid, nthreads);
   } else {
     const long long n8 = job.n >> 3;
     float* d = reinterpret_cast<float*>(job.dst);
@@ -127,11 +140,6 @@ struct TPFuse {
   int n_cols;                           // RS: N (row length of partial / acc / out)
 };
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void comm_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCommThreads) : "memory"); }
 
 // All comm-warp groups of the grid arrive once; the last one resets the counter and returns true.
@@ -168,13 +176,7 @@ __device__ __forceinline__ void tp_allgather_comm(const TPFuse& tp, int ctid, vo
     if (p != tp.rank && !comm_flag_wait(tp.flags + p, tp.epoch, status, 7000 + p, word, ctid)) return;
     const uint4* s = reinterpret_cast<const uint4*>(tp.peer_src[p]);
     uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(tp.local_dst) + (long long)p * tp.chunk_bytes);
-    long long i = tid;
-    for (; i + 3 * nthreads < n16; i += 4 * nthreads) {
-      const uint4 a = ld_stream16(s + i), b = ld_stream16(s + i + nthreads), c = ld_stream16(s + i + 2 * nthreads),
-                  e = ld_stream16(s + i + 3 * nthreads);
-      d[i] = a; d[i + nthreads] = b; d[i + 2 * nthreads] = c; d[i + 3 * nthreads] = e;
-    }
-    for (; i < n16; i += nthreads) d[i] = ld_stream16(s + i);
+    copy_stream16(s, d, n16, tid, nthreads);
     __threadfence();
     comm_bar_sync();
     if (ctid == 0 && grid_arrive_last(arrive + p, gridDim.x)) {
@@ -222,39 +224,62 @@ __device__ __forceinline__ void tp_reducescatter_comm(const TPFuse& tp, int ctid
     if (!comm_flag_wait(tp.flags + p, tp.epoch, status, 7200 + p, word, ctid)) return;
     const uint4* src = reinterpret_cast<const uint4*>(tp.peer_src[p]) + chunk_off16;
     const bool first = (s == 1), last = (s == tp.world);
-    for (long long i = tid; i < n8; i += nthreads) {
-      const uint4 v = ld_stream16(src + i);
-      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
-      float f[8];
+    constexpr int U = 4;   // peer loads and accumulator loads of U groups are all issued before the first use
+    for (long long i0 = tid; i0 < n8; i0 += U * nthreads) {
+      uint4 pv[U];
+      float4 a0[U], a1[U];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 x = __bfloat1622float2(b[j]);
-        f[2 * j] = x.x;
-        f[2 * j + 1] = x.y;
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < n8) pv[u] = ld_stream16(src + i);
       }
-      float4* a = reinterpret_cast<float4*>(tp.acc + i * 8);
       if (!first) {
-        const float4 a0 = a[0], a1 = a[1];
-        f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
-        f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
-      }
-      if (!last) {
-        a[0] = make_float4(f[0], f[1], f[2], f[3]);
-        a[1] = make_float4(f[4], f[5], f[6], f[7]);
-      } else {
-        if (tp.residual != nullptr) {
-          const uint4 r = reinterpret_cast<const uint4*>(tp.residual)[i];
-          const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 x = __bfloat1622float2(rb[j]);
-            f[2 * j] += x.x;
-            f[2 * j + 1] += x.y;
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nthreads;
+          if (i < n8) {
+            const float4* a = reinterpret_cast<const float4*>(tp.acc + i * 8);
+            a0[u] = __ldcs(a);
+            a1[u] = __ldcs(a + 1);
           }
         }
-        uint4 o;
-        o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]); o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-        reinterpret_cast<uint4*>(tp.out)[i] = o;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < n8) {
+          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&pv[u]);
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 x = __bfloat1622float2(b[j]);
+            f[2 * j] = x.x;
+            f[2 * j + 1] = x.y;
+          }
+          if (!first) {
+            f[0] += a0[u].x; f[1] += a0[u].y; f[2] += a0[u].z; f[3] += a0[u].w;
+            f[4] += a1[u].x; f[5] += a1[u].y; f[6] += a1[u].z; f[7] += a1[u].w;
+          }
+          if (!last) {
+            float4* a = reinterpret_cast<float4*>(tp.acc + i * 8);
+            __stcs(a, make_float4(f[0], f[1], f[2], f[3]));
+            __stcs(a + 1, make_float4(f[4], f[5], f[6], f[7]));
+          } else {
+            if (tp.residual != nullptr) {
+              const uint4 r = reinterpret_cast<const uint4*>(tp.residual)[i];
+              const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(rb[j]);
+                f[2 * j] += x.x;
+                f[2 * j + 1] += x.y;
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]); o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+            reinterpret_cast<uint4*>(tp.out)[i] = o;
+          }
+        }
       }
     }
     comm_bar_sync();

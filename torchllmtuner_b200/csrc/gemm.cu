@@ -106,10 +106,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tp_tpc = tp_mpc * num_n;
   auto tp_chunk_of = [&](int tt) -> int { return (tp.rank + tt / tp_tpc + (tp.mode == kTPReduceScatter ? 1 : 0)) % tp.world; };
   auto tile_mn = [&](int tt, int& m0, int& n0) {
-    if (tp_on) {
+    if (tp_on) {   // the same super-row sweep, inside one chunk
       const int w = tt % tp_tpc;
-      m0 = (tp_chunk_of(tt) * tp_mpc + w % tp_mpc) * BM;
-      n0 = (w / tp_mpc) * BN;
+      const int per_group = kGroupM * num_n;
+      const int grp_i = w / per_group;
+      const int first_m = grp_i * kGroupM;
+      const int gm = (tp_mpc - first_m < kGroupM) ? (tp_mpc - first_m) : kGroupM;
+      const int r = w - grp_i * per_group;
+      m0 = (tp_chunk_of(tt) * tp_mpc + first_m + r % gm) * BM;
+      n0 = (r / gm) * BN;
       return;
     }
     const int per_group = kGroupM * num_n;
