@@ -62,3 +62,14 @@ def test_tp2_model_uses_fused_collectives():
     got = run_ranks(2, flat, device="cuda")
     assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (ref, got)
     assert got.get("tp_fused", {}).get("ag_fused", 0) > 0, got
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_ep_dispatcher_matches_nccl_dispatcher(world):
+    """Device-side count exchange, P2P row pushes and pulls against the NCCL all-to-all dispatcher, values and gradients."""
+    _need(world)
+    from fused_ep_cases import run_fused_ep
+    res = run_fused_ep(world)
+    for k in ("out", "dx", "dw", "dparam"):
+        assert res[k] < 2e-2, res
+    assert res["stats"]["dispatches"] > 0 and res["stats"]["combines"] > 0

@@ -128,6 +128,101 @@ void gemm_tp(const Tensor& a, const Tensor& b, Tensor& c, bool b_mn, bool accumu
            "llmt_gemm_bf16_tp");
 }
 
+// ---- expert-parallel exchange over peer memory (csrc/ep_comm.cu). Peer buffers are raw device addresses.
+static void fill_ptrs(const std::vector<int64_t>& v, void** out) {
+  TORCH_CHECK(v.size() >= 1 && v.size() <= 8, "1..8 peers");
+  for (size_t i = 0; i < 8; ++i) out[i] = i < v.size() ? reinterpret_cast<void*>(v[i]) : nullptr;
+}
+inline void check_i32(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), n, " must be a contiguous CUDA int32 tensor");
+}
+
+// Returns (seg_offsets [E/R + 1], totals [E/R], send_off [E]) as int32 device tensors.
+std::vector<Tensor> ep_exchange(const Tensor& flat, int64_t E, int64_t me, const std::vector<int64_t>& tables,
+                                const std::vector<int64_t>& flags, int64_t epoch, int64_t cap) {
+  c10::cuda::CUDAGuard guard(flat.device());
+  TORCH_CHECK(flat.is_cuda() && flat.scalar_type() == at::kLong && flat.is_contiguous());
+  const int64_t R = (int64_t)tables.size();
+  void *tp[8], *fp[8];
+  fill_ptrs(tables, tp);
+  fill_ptrs(flags, fp);
+  auto o = torch::dtype(torch::kInt32).device(flat.device());
+  Tensor seg = torch::empty({E / R + 1}, o), tot = torch::empty({E / R}, o), off = torch::empty({E}, o);
+  check_rc(llmt_ep_exchange(flat.data_ptr<int64_t>(), flat.numel(), (int)E, (int)R, (int)me, tp, fp, (uint32_t)epoch, (int)cap,
+                            seg.data_ptr<int>(), tot.data_ptr<int>(), off.data_ptr<int>(), status_ptr(), cur_stream()),
+           "llmt_ep_exchange");
+  return {seg, tot, off};
+}
+
+// peers[drank[c]][drow[c]] = scale[c] * src[c / k]; returns dot[c] = <src[c / k], other[c]> when `other` is given.
+c10::optional<Tensor> ep_push_rows(const Tensor& src, const c10::optional<Tensor>& scale, const Tensor& drank, const Tensor& drow,
+                                   const std::vector<int64_t>& bufs, int64_t cap, int64_t k, const c10::optional<Tensor>& other) {
+  c10::cuda::CUDAGuard guard(src.device());
+  check_bf16(src, "src");
+  TORCH_CHECK(src.dim() == 2 && src.is_contiguous());
+  check_i32(drank, "drank");
+  check_i32(drow, "drow");
+  const int64_t n = drank.numel(), D = src.size(1);
+  TORCH_CHECK(drow.numel() == n && n == src.size(0) * k, "one destination per token copy");
+  void* bp[8];
+  fill_ptrs(bufs, bp);
+  const float* sp = nullptr;
+  if (scale.has_value()) {
+    TORCH_CHECK(scale->scalar_type() == at::kFloat && scale->is_contiguous() && scale->numel() == n);
+    sp = scale->data_ptr<float>();
+  }
+  c10::optional<Tensor> dot;
+  const void* op = nullptr;
+  float* dp = nullptr;
+  if (other.has_value()) {
+    check_bf16(*other, "other");
+    TORCH_CHECK(other->is_contiguous() && other->numel() == n * D);
+    dot = torch::empty({n}, torch::dtype(torch::kFloat32).device(src.device()));
+    op = other->data_ptr();
+    dp = dot->data_ptr<float>();
+  }
+  check_rc(llmt_ep_push_rows(src.data_ptr(), sp, drank.data_ptr<int>(), drow.data_ptr<int>(), bp, (int)bufs.size(), (int)cap, n, (int)k,
+                             (int)D, op, dp, status_ptr(), cur_stream()),
+           "llmt_ep_push_rows");
+  return dot;
+}
+
+// out[t] = sum_j w[t, j] * peers[drank][drow]; returns (out, raw rows [T*k, D] when keep).
+std::vector<Tensor> ep_pull_rows(const std::vector<int64_t>& bufs, const Tensor& drank, const Tensor& drow,
+                                 const c10::optional<Tensor>& w, int64_t cap, int64_t T, int64_t k, int64_t D, bool keep) {
+  c10::cuda::CUDAGuard guard(drank.device());
+  check_i32(drank, "drank");
+  check_i32(drow, "drow");
+  TORCH_CHECK(drank.numel() == T * k && drow.numel() == T * k);
+  void* bp[8];
+  fill_ptrs(bufs, bp);
+  auto o = torch::dtype(torch::kBFloat16).device(drank.device());
+  Tensor out = torch::empty({T, D}, o);
+  Tensor kp = keep ? torch::empty({T * k, D}, o) : Tensor();
+  const float* wp = nullptr;
+  if (w.has_value()) {
+    TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous() && w->numel() == T * k);
+    wp = w->data_ptr<float>();
+  }
+  check_rc(llmt_ep_pull_rows(bp, (int)bufs.size(), drank.data_ptr<int>(), drow.data_ptr<int>(), wp, out.data_ptr(),
+                             keep ? kp.data_ptr() : nullptr, (int)cap, (int)T, (int)k, (int)D, cur_stream()),
+           "llmt_ep_pull_rows");
+  if (keep) return {out, kp};
+  return {out};
+}
+
+// dst rows below seg_offsets[-1] = live rows of src (address), alignment padding zeroed when zero_pad.
+void ep_clone_rows(int64_t src, Tensor& dst, const Tensor& seg_offsets, const Tensor& totals, bool zero_pad) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  check_bf16(dst, "dst");
+  TORCH_CHECK(dst.dim() == 2 && dst.is_contiguous());
+  check_i32(seg_offsets, "seg_offsets");
+  check_i32(totals, "totals");
+  check_rc(llmt_ep_clone_rows(reinterpret_cast<const void*>(src), dst.data_ptr(), seg_offsets.data_ptr<int>(), totals.data_ptr<int>(),
+                              (int)totals.numel(), (int)dst.size(1), zero_pad, cur_stream()),
+           "llmt_ep_clone_rows");
+}
+
 void side_job(const PySideJob& j, int64_t ctas) {
   const void* src[8] = {nullptr};
   TORCH_CHECK(j.src.size() >= 1 && j.src.size() <= 8, "side job needs 1..8 sources");
@@ -490,6 +585,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tp", &gemm_tp, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("b_mn"), py::arg("accumulate"), py::arg("mode"), py::arg("world"),
         py::arg("rank"), py::arg("epoch"), py::arg("peer_src"), py::arg("flags"), py::arg("peer_flags"), py::arg("counters"),
         py::arg("acc") = py::none(), py::arg("out") = py::none(), py::arg("residual") = py::none());
+  m.def("ep_exchange", &ep_exchange);
+  m.def("ep_push_rows", &ep_push_rows);
+  m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("ep_clone_rows", &ep_clone_rows);
   m.def("side_job", &side_job);
   m.def("signal_peers", &signal_peers);
   m.def("wait_flags", &wait_flags);

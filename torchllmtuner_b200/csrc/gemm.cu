@@ -81,7 +81,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // MODE 2: one M x N product per segment, reduced over that segment's rows (the K dimension); C[g] is M x N.
   constexpr bool GROUPED = (MODE == 1);
   const int num_n = (N + BN - 1) / BN;
-  const int num_m = (M + BM - 1) / BM;  // MODE 1: M is the padded row total, a multiple of BM
+  // MODE 1: M is the capacity of the padded row buffer (a multiple of BM); only the tiles below the last segment's end
+  // hold rows, the rest of a statically sized buffer is skipped.
+  int num_m = (M + BM - 1) / BM;
+  if constexpr (MODE == 1) {
+    const int used = grp.seg_offsets[grp.num_groups] / BM;
+    num_m = used < num_m ? used : num_m;
+  }
   const int tiles_per_group = num_m * num_n;
   const int num_tiles = (MODE == 2) ? tiles_per_group * grp.num_groups : tiles_per_group;
   const int num_kb_plain = (K + BK - 1) / BK;

@@ -53,6 +53,16 @@ int llmt_sqnorm_scratch_floats();
 int llmt_sqnorm(const void* x, int is_bf16, int64_t n, float* scratch, float* out, int accumulate, cudaStream_t st);
 int llmt_clip_coef(const float* total_sq, float max_norm, float* clip_coef, float* norm_out, int* finite, cudaStream_t st);
 
+// ---- expert-parallel token exchange over peer memory (ep_comm.cu) ----
+int llmt_ep_exchange(const int64_t* flat, int64_t ncopies, int E, int R, int me, void* const* tables, void* const* flags,
+                     uint32_t epoch, int cap, int* seg_offsets, int* totals, int* send_off, int* status, cudaStream_t st);
+int llmt_ep_push_rows(const void* src, const float* scale, const int* drank, const int* drow, void* const* bufs, int R, int cap,
+                      int64_t ncopies, int k, int D, const void* other, float* dot_out, int* status, cudaStream_t st);
+int llmt_ep_pull_rows(void* const* bufs, int R, const int* drank, const int* drow, const float* w, void* out, void* keep, int cap,
+                      int T, int k, int D, cudaStream_t st);
+int llmt_ep_clone_rows(const void* src, void* dst, const int* seg_offsets, const int* totals, int G, int D, int zero_pad,
+                       cudaStream_t st);
+
 // ---- MoE routing and token movement (moe.cu) ----
 int llmt_router_topk(const float* logits, const float* bias, float* weights, int64_t* indices, float* counts, float* denom,
                      int T, int E, int k, int score_fn, int renorm, float route_scale, cudaStream_t st);

@@ -5,8 +5,8 @@
   selective      every `save_every_nth_block`-th block keeps its activations, the others recompute
   memory_budget  the fraction of blocks that recompute is chosen from `memory_budget` (0 = all recompute, 1 = none)
   region         per-block choice from module-name patterns: blocks matching `recompute_regions` recompute
-Expert-parallel token exchanges are never replayed: the dispatcher caches the received rows of the forward pass
-for the recompute (the role of the reference's MUST_SAVE policy for all_to_all, activation_checkpoint.py:278-300).
+Expert-parallel token exchanges are replayed with the block (the reference keeps all_to_all results under a MUST_SAVE
+policy, activation_checkpoint.py:278-300; here the exchange is a pair of peer-memory kernels and cheap to repeat).
 """
 from __future__ import annotations
 

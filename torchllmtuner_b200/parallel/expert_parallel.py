@@ -4,9 +4,9 @@ token_dispatch.py:319-678, domino_dispatch.py:36-390).
 `apply_ep` gives every MoE block the expert slice `[r*E/ep, (r+1)*E/ep)` of its rank and binds an all-to-all token
 dispatcher to the `ep` group. Dispatch: copies sorted by expert (stable), per-(rank, expert) counts exchanged, rows
 exchanged, received rows regrouped expert-major into zero-padded 128-row segments for the grouped GEMM; combine runs
-the inverse and accumulates score-weighted rows in fp32. Under activation recomputation the rows received in the
-first forward are reused, so expert traffic is never replayed. The `domino` dispatcher splits the tokens in two
-halves and overlaps the exchange of one half with the expert GEMMs of the other on a second stream.
+the inverse and accumulates score-weighted rows in fp32. The `domino` dispatcher splits the tokens in two halves and
+overlaps the exchange of one half with the expert GEMMs of the other on a second stream. On CUDA the default
+dispatcher is the peer-memory one of `parallel/symm_ep.py` (device-side counts, P2P row writes, no NCCL).
 """
 from __future__ import annotations
 
@@ -128,6 +128,11 @@ def convert_block(moe: MoE, topo, ep_config) -> None:
     ex.num_experts = n
     cls = DominoTokenDispatcher if ep_config.ep_token_dispatcher == "domino" else AllToAllTokenDispatcher
     moe.routed.dispatcher = cls(E, topo.get_group("ep"), ep, r)
+    if cls is AllToAllTokenDispatcher:
+        # 'alltoall' and 'fused': tokens move by P2P stores / loads over peer memory on CUDA bf16 (no NCCL, no host
+        # synchronisation); the NCCL dispatcher stays behind it for CPU runs and unsupported shapes.
+        from .symm_ep import PeerTokenDispatcher
+        moe.routed.dispatcher = PeerTokenDispatcher(E, topo.get_group("ep"), ep, r, fallback=moe.routed.dispatcher)
     if isinstance(moe.routed.dispatcher, DominoTokenDispatcher):
         d = moe.routed.dispatcher
         moe.routed.forward = lambda x, w, i, _d=d, _e=ex: _d.run(_e, x, w, i)
