@@ -205,7 +205,7 @@ def main() -> int:
     e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
     fpt = tr.model.flops_per_token(args.seq)
     mem = torch.cuda.max_memory_allocated() / 2 ** 30
-    out = {"metric": "training tokens/sec/box (device-timed, max over ranks), Qwen3-8B FSDP bf16 seq 8192", "value": value,
+    out = {"metric": f"training tokens/sec/box (device-timed, max over ranks), {args.model} {par} bf16 seq {args.seq}", "value": value,
            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_dev / args.steps,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
            "config": {"model": args.model + (f"[layers={args.layers}]" if args.layers else ""), "global_batch": cfg.training.global_batch_size,
