@@ -1,0 +1,142 @@
+"""Failure detection without a device fault: every failure is made on the host and observed by gloo ranks
+(model: the reference's coordination tests, tests/unit_tests/cpu/accelerator/test_collectives.py)."""
+import os
+import sys
+import tempfile
+
+import pytest
+import torch
+
+
+def _spawn(fn, world, *args):
+    import torch.multiprocessing as mp
+    out = tempfile.mkdtemp()
+    port = 23000 + (os.getpid() * 19 + hash(fn.__name__)) % 15000
+    mp.spawn(_entry, args=(world, port, fn.__name__, out, args), nprocs=world, join=True)
+    res = []
+    for r in range(world):
+        with open(os.path.join(out, f"{r}.txt")) as f:
+            res.append(f.read())
+    return res
+
+
+def _entry(rank, world, port, fn_name, out, args):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      LLMTUNER_DEVICE="cpu")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import datetime
+
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    torch.set_num_threads(1)
+    try:
+        verdict = globals()[fn_name](rank, world, *args)
+    except BaseException as e:  # noqa: BLE001
+        verdict = f"UNCAUGHT {type(e).__name__}: {e}"
+    with open(os.path.join(out, f"{rank}.txt"), "w") as f:
+        f.write(verdict)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------- cases (run in children)
+def _case_one_rank_raises(rank, world):
+    from torchllmtuner_b200.accelerator.collectives import CoordinatedError, synchronize_local_errors
+    try:
+        with synchronize_local_errors("load-shard"):
+            if rank == 1:
+                raise ValueError("disk error on rank 1")
+    except ValueError:
+        return "own"
+    except CoordinatedError as e:
+        return "peer:" + str(e)
+    return "none"
+
+
+def _case_all_ok(rank, world):
+    from torchllmtuner_b200.accelerator.collectives import synchronize_local_errors
+    with synchronize_local_errors("phase"):
+        pass
+    return "ok"
+
+
+def _case_nan_update_is_skipped_everywhere(rank, world):
+    """A non-finite gradient on one rank: the global norm is non-finite on every rank, no rank updates, all raise."""
+    from dist_cases import base_flat
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.errors import LLMTunerError
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(data_parallel_shard_size=world, dump_folder=tempfile.mkdtemp()))
+    tr = Trainer(cfg)
+    tr.train_step()
+    before = [u.master.clone() for u in tr.asm.fsdp.units]
+    if rank == 0:       # poison one gradient contribution on one rank through the loss scale
+        for p in tr.model.parameters():
+            p.register_hook(lambda g: g * float("nan"))
+            break
+    try:
+        tr.train_step()
+        verdict = "no-raise"
+    except LLMTunerError:
+        same = all(torch.equal(a, u.master) for a, u in zip(before, tr.asm.fsdp.units))
+        verdict = "raised,unchanged" if same else "raised,CHANGED"
+    tr.close()
+    return verdict
+
+
+def _case_checkpoint_publication_failure(rank, world, folder):
+    """The rank that publishes fails; every rank learns of it and the previous checkpoint stays the latest."""
+    from dist_cases import base_flat
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(data_parallel_shard_size=world, dump_folder=folder, enable=True, interval=1000, last_save_model_only=False))
+    tr = Trainer(cfg)
+    tr.train_step()
+    tr.checkpointer.save(tr.progress.step, force=True)
+    tr.checkpointer.wait()
+    first = tr.checkpointer.latest_step()
+    tr.train_step()
+    import torchllmtuner_b200.components.checkpointer.dcp_manager as dm
+    real = os.replace
+
+    def failing_replace(a, b):
+        if rank == 0 and "step-" in str(b):
+            raise OSError("injected publication failure")
+        return real(a, b)
+    dm.os.replace = failing_replace
+    try:
+        tr.checkpointer.save(tr.progress.step, force=True)
+        tr.checkpointer.wait()
+        verdict = "no-raise"
+    except Exception as e:  # noqa: BLE001
+        verdict = type(e).__name__
+    finally:
+        dm.os.replace = real
+    latest = tr.checkpointer.latest_step()
+    tr.close()
+    return f"{verdict},{first},{latest}"
+
+
+# ---------------------------------------------------------------------------------------------- tests
+def test_one_rank_raising_becomes_every_rank_raising():
+    res = _spawn(_case_one_rank_raises, 2)
+    assert res[1] == "own" and res[0].startswith("peer:") and "load-shard" in res[0], res
+
+
+def test_no_error_passes_through():
+    assert _spawn(_case_all_ok, 2) == ["ok", "ok"]
+
+
+def test_non_finite_gradient_skips_update_on_every_rank():
+    res = _spawn(_case_nan_update_is_skipped_everywhere, 2)
+    assert res == ["raised,unchanged", "raised,unchanged"], res
+
+
+def test_checkpoint_publication_failure_keeps_previous_checkpoint():
+    folder = tempfile.mkdtemp()
+    res = _spawn(_case_checkpoint_publication_failure, 2, folder)
+    for r in res:
+        assert r.count(",") == 2, res
+        verdict, first, latest = r.split(",")
+        assert verdict != "no-raise" and first == latest, res

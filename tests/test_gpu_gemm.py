@@ -109,3 +109,22 @@ def test_grouped_gemm_and_wgrad(counts):
             _close(dw[g], ref)
         else:
             assert dw[g].abs().max().item() == 0
+
+
+def test_bounded_wait_expires_into_status_word():
+    """A flag that nothing sets: the wait gives up after its poll limit, the kernel returns, the host reads the
+    status and the context stays usable."""
+    from torchllmtuner_b200.ops.cuda_ext import KernelStatusError, check_status, load
+    ext = load()
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ext.wait_flags(flags.data_ptr(), 4, 1, 9100, 1 << 14)
+    with pytest.raises(KernelStatusError) as e:
+        check_status("bounded wait test")
+    assert "9100" in str(e.value) or "910" in str(e.value)
+    # the status word was cleared by the read and the device still works
+    a = torch.randn(256, 128, device="cuda").bfloat16()
+    b = torch.randn(256, 128, device="cuda").bfloat16()
+    out = torch.empty(256, 256, device="cuda", dtype=torch.bfloat16)
+    ext.gemm(a, b, out, False, False, False, 0)
+    check_status("after recovery")
+    assert torch.allclose(out.float(), a.float() @ b.float().t(), atol=0.5, rtol=5e-2)

@@ -231,15 +231,22 @@ class DistributedCheckpointManager(CheckpointManager):
             self._async_future = (fut, tmp, final, step)
 
     def _publish(self, tmp: str, final: str, step: int) -> None:
+        """Atomic publication by rank 0 inside an error-coordination boundary: if the rename fails, every rank raises
+        and the previously published step stays the latest one."""
+        from ...accelerator.collectives import synchronize_local_errors
         if dist.is_initialized():
             dist.barrier()
-        if self.rank == 0:
-            if os.path.isdir(final):
-                shutil.rmtree(final)
-            os.replace(tmp, final)
-            self._purge_q.put(step)
-        if dist.is_initialized():
-            dist.barrier()
+        with synchronize_local_errors("checkpoint-publish"):
+            if self.rank == 0:
+                if os.path.isdir(final):
+                    shutil.rmtree(final)
+                os.replace(tmp, final)
+                self._purge_q.put(step)
+
+    def latest_step(self) -> int:
+        """Highest published step of this run folder, -1 when there is none."""
+        steps = self._existing_steps()
+        return max(steps) if steps else -1
 
     def maybe_wait_for_staging(self) -> None:
         pass        # staging copies are synchronised inside save()

@@ -240,9 +240,10 @@ void signal_peers(const std::vector<int64_t>& peer_flag_ptrs, int64_t slot, int6
   check_rc(llmt_signal_peers(p, (int)peer_flag_ptrs.size(), (int)slot, (uint32_t)value, cur_stream()), "llmt_signal_peers");
 }
 
-void wait_flags(int64_t flags_ptr, int64_t n, int64_t value, int64_t site) {
-  check_rc(llmt_wait_flags(reinterpret_cast<const uint32_t*>(flags_ptr), (int)n, (uint32_t)value, (int)site, status_ptr(),
-                           cur_stream()),
+// max_polls == 0: the library's default limit (seconds); tests pass a small limit to see a wait expire quickly.
+void wait_flags(int64_t flags_ptr, int64_t n, int64_t value, int64_t site, int64_t max_polls) {
+  check_rc(llmt_wait_flags(reinterpret_cast<const uint32_t*>(flags_ptr), (int)n, (uint32_t)value, (int)site, (uint32_t)max_polls,
+                           status_ptr(), cur_stream()),
            "llmt_wait_flags");
 }
 
@@ -591,7 +592,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_clone_rows", &ep_clone_rows);
   m.def("side_job", &side_job);
   m.def("signal_peers", &signal_peers);
-  m.def("wait_flags", &wait_flags);
+  m.def("wait_flags", &wait_flags, py::arg("flags_ptr"), py::arg("n"), py::arg("value"), py::arg("site"), py::arg("max_polls") = 0);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_wgrad", &grouped_wgrad);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

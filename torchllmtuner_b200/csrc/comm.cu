@@ -25,9 +25,9 @@ __global__ void signal_peers_kernel(PeerFlagPtrs flags, int npeers, int slot, ui
   }
 }
 
-__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t value, int* status, int site) {
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t value, int* status, int site, uint32_t max_polls) {
   const int i = threadIdx.x;
-  if (i < n) flag_wait_bounded(flags + i, value, status, site + i);
+  if (i < n) flag_wait_bounded(flags + i, value, status, site + i, max_polls);
 }
 
 }  // namespace llmt
@@ -67,8 +67,9 @@ extern "C" int llmt_signal_peers(uint32_t* const* peer_flags, int npeers, int sl
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int llmt_wait_flags(const uint32_t* flags, int n, uint32_t value, int site, int* status, cudaStream_t st) {
+extern "C" int llmt_wait_flags(const uint32_t* flags, int n, uint32_t value, int site, uint32_t max_polls, int* status,
+                               cudaStream_t st) {
   if (n < 1 || n > 32) return -10;
-  wait_flags_kernel<<<1, 32, 0, st>>>(flags, n, value, status, site);
+  wait_flags_kernel<<<1, 32, 0, st>>>(flags, n, value, status, site, max_polls ? max_polls : kMaxFlagPolls);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

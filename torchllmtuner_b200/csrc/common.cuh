@@ -117,8 +117,9 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 constexpr uint32_t kMaxFlagPolls = 1u << 24;
-__device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t expected, int* status, int site) {
-  for (uint32_t i = 0; i < kMaxFlagPolls; ++i) {
+__device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t expected, int* status, int site,
+                                                  uint32_t max_polls = kMaxFlagPolls) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
     if ((int32_t)(ld_acquire_sys(flag) - expected) >= 0) return true;
     __nanosleep(64);
   }

@@ -77,7 +77,8 @@ int llmt_combine_bwd(const void* dout, const void* y, const int64_t* dest, const
 int llmt_side_job(int kind, int nsrc, const void* const* src, void* dst, long long n, int accumulate,
                   const uint32_t* wait_flags, int n_wait, uint32_t wait_value, int ctas, int* status, cudaStream_t st);
 int llmt_signal_peers(uint32_t* const* peer_flags, int npeers, int slot, uint32_t value, cudaStream_t st);
-int llmt_wait_flags(const uint32_t* flags, int n, uint32_t value, int site, int* status, cudaStream_t st);
+int llmt_wait_flags(const uint32_t* flags, int n, uint32_t value, int site, uint32_t max_polls, int* status,
+                    cudaStream_t st);
 
 // ---- attention (attention.cu) ----
 // q [Tq, Hq, HD], k/v [Tk, Hkv, HD] bf16 with token strides in elements; varlen via cu_seqlens (device int32).
