@@ -123,7 +123,7 @@ def main() -> int:
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--ac", default="full")
-    ap.add_argument("--loss-chunks", type=int, default=8)
+    ap.add_argument("--loss-chunks", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline metric)")
     ap.add_argument("--fsdp-impl", default="native", choices=["native", "custom"])
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (sequence parallel); the rest of the GPUs shard with FSDP")
