@@ -47,7 +47,7 @@ def main() -> None:
     from .. import ops
     from .cuda_ext import check_status
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "attention", "attention_bwd", "rmsnorm", "swiglu", "ce"])
+    ap.add_argument("--op", required=True, choices=["gemm", "attention", "attention_bwd", "rmsnorm", "swiglu", "ce", "adamw", "qk_norm_rope", "grouped_gemm", "router"])
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--layout", default="tn", choices=["tn", "nn", "tt"])
     ap.add_argument("--seq", type=int, default=8192); ap.add_argument("--heads", type=int, default=32)
@@ -98,6 +98,37 @@ def main() -> None:
         lg = torch.randn(a.rows, a.cols, device=dev).bfloat16(); y = torch.randint(0, a.cols, (a.rows,), device=dev)
         ms = timeit(lambda: ops.cross_entropy_sum(lg, y), a.iters, a.warmup)
         out.update(shape=[a.rows, a.cols], ms=ms)
+    elif a.op == "adamw":
+        n = a.rows * a.cols
+        p32 = torch.randn(n, device=dev); p16 = p32.bfloat16(); g = torch.randn(n, device=dev).bfloat16()
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        ms = timeit(lambda: ops.adamw_step_(p32, g, m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1,
+                                            p_lowp=p16), a.iters, a.warmup)
+        gb = n * (4 * 3 * 2 + 2 + 2) / ms / 1e6          # p32, m, v read + written; bf16 grad read; bf16 param written
+        out.update(numel=n, ms=ms, gbs=gb, frac_of_peak=gb / pgb)
+    elif a.op == "qk_norm_rope":
+        S, H, Hk, d = a.seq, a.heads, a.kv_heads, a.head_dim
+        q = torch.randn(S, H, d, device=dev).bfloat16(); k = torch.randn(S, Hk, d, device=dev).bfloat16()
+        w = torch.ones(d, device=dev).bfloat16()
+        ang = torch.arange(S, device=dev, dtype=torch.float32)[:, None] * (1.0 / (1e6 ** (torch.arange(0, d, 2, device=dev) / d)))[None]
+        cos, sin = ang.cos(), ang.sin()
+        ms = timeit(lambda: ops.qk_norm_rope(q, k, w, w, cos, sin, 1e-6), a.iters, a.warmup)
+        gb = 2.0 * (q.numel() + k.numel()) * 2 / ms / 1e6
+        out.update(seq=S, heads=[H, Hk], ms=ms, gbs=gb, frac_of_peak=gb / pgb)
+    elif a.op == "grouped_gemm":
+        from ..models.moe.experts import grouped_linear
+        E, rows_per = a.heads, a.rows // a.heads // 128 * 128
+        x = torch.randn(E * rows_per, a.k, device=dev).bfloat16(); w = (torch.randn(E, a.n, a.k, device=dev) * 0.02).bfloat16()
+        seg = (torch.arange(E + 1, device=dev) * rows_per).to(torch.int32)
+        ms = timeit(lambda: grouped_linear(x, w, seg), a.iters, a.warmup)
+        tf = 2.0 * E * rows_per * a.n * a.k / ms / 1e9
+        out.update(experts=E, rows_per_expert=rows_per, n=a.n, k=a.k, ms=ms, tflops=tf, frac_of_peak=tf / ptf)
+    elif a.op == "router":
+        from .cuda_ext import load
+        logits = torch.randn(a.rows, a.cols, device=dev)
+        ext = load()
+        ms = timeit(lambda: ext.router_topk(logits, None, 8, 0, True, 1.0), a.iters, a.warmup)
+        out.update(shape=[a.rows, a.cols], k=8, ms=ms, gbs=logits.numel() * 4 / ms / 1e6)
     check_status(a.op)
     print(json.dumps(out))
 
