@@ -6,7 +6,7 @@ import sys
 import torch
 
 
-def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
+def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflow: bool = False):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch.distributed as dist
@@ -19,7 +19,7 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
     from torchllmtuner_b200.parallel.symm_ep import PeerTokenDispatcher
     E, k, T, D, F = 8 * world, 4, 384, 256, 128
     nccl = AllToAllTokenDispatcher(E, dist.group.WORLD, world, rank)
-    peer = PeerTokenDispatcher(E, dist.group.WORLD, world, rank, fallback=nccl)
+    peer = PeerTokenDispatcher(E, dist.group.WORLD, world, rank, fallback=nccl, capacity_factor=1.0 if overflow else 3.0)
     torch.manual_seed(7)
     experts = GroupedExperts(E // world, D, F, dtype=torch.bfloat16, device=dev)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -35,7 +35,9 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
         x0 = (torch.randn(T, D, generator=g, device=dev) * 0.5).bfloat16()
         scores = torch.rand(T, E, generator=g, device=dev)
         if it == 1:
-            scores[:, : E // 4] += 1.0           # unbalanced routing
+            scores[:, : E // 2] += 0.2           # unbalanced routing that still fits the receive buffers
+        if overflow:
+            scores[:, : E // world] += 10.0      # every copy goes to rank 0: its buffer must overflow
         w0, idx = scores.topk(k, dim=-1)
         w0 = (w0 / w0.sum(-1, keepdim=True)).float()
         dout = (torch.randn(T, D, generator=g, device=dev) * 0.1).bfloat16()
@@ -57,6 +59,26 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
         if it % 2 == rank % 2:
             torch.cuda._sleep(20_000_000)
     torch.cuda.synchronize()
+    if overflow:
+        from torchllmtuner_b200.errors import KernelStatusError
+        try:
+            check_status("fused ep overflow test")
+            seen = 0.0
+        except KernelStatusError as e:
+            seen = 1.0 if "capacity overflow" in str(e) else 0.0
+        # the context is still usable: a small GEMM runs and the status word is clean again
+        from torchllmtuner_b200.ops.functional import gemm
+        a = torch.randn(128, 64, device=dev).bfloat16()
+        gemm(a, a)
+        check_status("after overflow")
+        t = torch.tensor([seen], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            with open(out_path, "w") as f:
+                json.dump({"overflow_seen": float(t)}, f)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     check_status("fused ep test")
     t = torch.tensor([worst[k_] for k_ in sorted(worst)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -68,13 +90,13 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
     dist.destroy_process_group()
 
 
-def run_fused_ep(world: int, iters: int = 4) -> dict:
+def run_fused_ep(world: int, iters: int = 4, overflow: bool = False) -> dict:
     import tempfile
 
     import torch.multiprocessing as mp
     out = tempfile.mktemp(suffix=".json")
     port = 22000 + (os.getpid() * 17 + world) % 20000
-    mp.spawn(_worker, args=(world, port, out, iters), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, out, iters, overflow), nprocs=world, join=True)
     with open(out) as f:
         res = json.load(f)
     os.unlink(out)

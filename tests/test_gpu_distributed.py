@@ -73,3 +73,26 @@ def test_peer_ep_dispatcher_matches_nccl_dispatcher(world):
     for k in ("out", "dx", "dw", "dparam"):
         assert res[k] < 2e-2, res
     assert res["stats"]["dispatches"] > 0 and res["stats"]["combines"] > 0
+
+
+@pytest.mark.parametrize("name,flat,arch", [
+    ("tp2_fsdp2", dict(tensor_parallel_size=2, data_parallel_shard_size=2, activation_checkpoint_mode="full"), None),
+    ("ep2_fsdp4", dict(model_name_or_path="qwen3_moe", expert_parallel_size=2, data_parallel_shard_size=4, activation_checkpoint_mode="full"), MOE),
+    ("hsdp2x2", dict(data_parallel_replicate_size=2, data_parallel_shard_size=2), None),
+])
+def test_mixed_parallel_modes_on_four_gpus(name, flat, arch):
+    """Fused FSDP collectives together with fused TP / EP exchanges, each on its own sub-group arena."""
+    _need(4)
+    base = dict(model_name_or_path=flat.get("model_name_or_path", "qwen3"))
+    ref = run_ranks(1, _flat(**base), arch=arch, device="cuda")
+    got = run_ranks(4, _flat(**flat), arch=arch, device="cuda")
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (name, ref, got)
+
+
+def test_peer_ep_capacity_overflow_is_reported_not_written():
+    """All copies routed to one rank with a receive buffer sized for the average: rows that do not fit are dropped, the
+    status word says so, and the context stays usable."""
+    _need(2)
+    from fused_ep_cases import run_fused_ep
+    res = run_fused_ep(2, iters=1, overflow=True)
+    assert res["overflow_seen"] == 1.0, res
