@@ -1,0 +1,143 @@
+"""Config surface, topology arithmetic for every rank of 8 (no process group needed), closed-form helpers."""
+import json
+import math
+
+import pytest
+import torch
+
+from torchllmtuner_b200 import LLMTunerConfig
+from torchllmtuner_b200.config import build_parser
+from torchllmtuner_b200.errors import ConfigError, LLMTunerError, UnsupportedCombinationError
+from torchllmtuner_b200.parallel.topology import ParallelTopology, resolve_parallel_topology
+from torchllmtuner_b200.trainer.cli import parse_config
+
+
+# ------------------------------------------------------------------------------------------------ CLI / config
+def test_flat_flags_cover_the_thirteen_groups_without_collisions():
+    p = build_parser()
+    flags = {a.dest for a in p._actions}
+    for name in ("model_name_or_path", "data_parallel_shard_size", "tensor_parallel_size", "expert_parallel_size",
+                 "context_parallel_ulysses_size", "context_parallel_kv_allgather_size", "fsdp_reshard_after_forward",
+                 "enable_sequence_parallel", "context_parallel_load_balancer", "ep_token_dispatcher", "optimizer_type",
+                 "learning_rate", "warmup_steps", "global_batch_size", "max_seq_len", "activation_checkpoint_mode", "interval",
+                 "dataset", "log_freq", "enable_profiling"):
+        assert name in flags, name
+
+
+def test_cli_overrides_file_and_round_trips(tmp_path):
+    f = tmp_path / "run.yaml"
+    f.write_text("model_name_or_path: qwen3\nmax_seq_len: 128\nglobal_batch_size: 4\nlearning_rate: 1.0e-3\n")
+    cfg = parse_config(["--config", str(f), "--max_seq_len", "256"])
+    assert cfg.training.max_seq_len == 256 and cfg.training.global_batch_size == 4
+    assert cfg.optimizer.learning_rate == pytest.approx(1e-3)
+    j = tmp_path / "run.json"
+    j.write_text(json.dumps({"model_name_or_path": "qwen3", "steps": 7}))
+    assert parse_config(["--config", str(j)]).training.steps == 7
+
+
+@pytest.mark.parametrize("flat,err", [
+    (dict(ep_token_dispatcher="deepep"), ConfigError),
+    (dict(ep_token_dispatcher="nonsense"), ConfigError),
+    (dict(context_parallel_load_balancer="ptrr"), (ConfigError, UnsupportedCombinationError)),
+    (dict(global_batch_size=0), ConfigError),
+    (dict(interval=0), ConfigError),
+    (dict(qkv_projection="fused", tensor_parallel_size=2), (ConfigError, UnsupportedCombinationError)),
+])
+def test_invalid_values_and_combinations_raise_the_framework_classes(flat, err):
+    with pytest.raises(err) as e:
+        cfg = LLMTunerConfig()
+        cfg.apply_flat(flat)
+        cfg.__post_init__()
+    assert isinstance(e.value, LLMTunerError)
+
+
+# ------------------------------------------------------------------------------------------------ topology
+def _cfg(**flat):
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(flat)
+    return cfg.parallel
+
+
+def test_world_size_formula_and_derived_shard():
+    t = resolve_parallel_topology(_cfg(tensor_parallel_size=2, data_parallel_shard_size=-1), 8, 0)
+    assert (t.dp_shard, t.tp, t.world_size) == (4, 2, 8)
+    with pytest.raises(ConfigError):
+        resolve_parallel_topology(_cfg(tensor_parallel_size=3), 8, 0)
+    with pytest.raises(ConfigError):
+        resolve_parallel_topology(_cfg(data_parallel_shard_size=2, expert_parallel_size=4), 2, 0)   # (dp_shard*cp*tp) % ep
+
+
+def test_mesh_order_tp_innermost_for_every_rank_of_eight():
+    for rank in range(8):
+        t = resolve_parallel_topology(_cfg(data_parallel_replicate_size=2, data_parallel_shard_size=2, tensor_parallel_size=2), 8, rank)
+        c = t.coords(rank)
+        assert rank == (c["dp_replicate"] * 2 + c["dp_shard"]) * 2 + c["tp"]
+        assert t.group_ranks("tp", rank) == [rank - rank % 2, rank - rank % 2 + 1]          # TP ranks are adjacent
+        assert t.group_ranks("dp_shard", rank) == sorted({rank, rank ^ 2})
+        assert t.group_ranks("dp_replicate", rank) == sorted({rank, rank ^ 4})
+
+
+def test_sparse_view_ep_is_innermost_and_efsdp_is_the_rest():
+    for rank in range(8):
+        t = resolve_parallel_topology(_cfg(data_parallel_shard_size=8, expert_parallel_size=4), 8, rank)
+        assert t.efsdp == 2
+        assert t.group_ranks("ep", rank) == list(range(rank // 4 * 4, rank // 4 * 4 + 4))
+        assert t.group_ranks("efsdp", rank) == sorted({rank % 4, rank % 4 + 4})
+
+
+def test_groups_partition_the_world():
+    t = resolve_parallel_topology(_cfg(data_parallel_shard_size=2, context_parallel_ulysses_size=2, tensor_parallel_size=2), 8, 0)
+    for name in ("tp", "cp", "dp_shard"):
+        groups = t.all_groups(name)
+        assert sorted(r for g in groups for r in g) == list(range(8)), name
+
+
+# ------------------------------------------------------------------------------------------------ closed forms
+def test_stage_order_and_vocab_shards():
+    from torchllmtuner_b200.parallel.stages import STAGE_ORDER
+    from torchllmtuner_b200.utils.vocabulary import vocab_shard_bounds
+    assert list(STAGE_ORDER) == ["tp", "ep", "cp", "ac", "activation_swap", "compile", "fsdp"]
+    V, R = 151936, 8
+    cuts = [vocab_shard_bounds(V, R, r) for r in range(R)]
+    assert cuts[0][0] == 0 and cuts[-1][1] == V and all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
+    assert cuts[0][1] - cuts[0][0] == math.ceil(V / R) == 18992
+    assert vocab_shard_bounds(10, 4, 3) == (9, 10) and vocab_shard_bounds(5, 8, 7) == (5, 5)
+
+
+def test_flops_per_token_match_the_published_evaluations():
+    from torchllmtuner_b200.models.qwen3 import QWEN3_8B, QWEN3_30B_A3B, Qwen3Config
+    assert Qwen3Config(**QWEN3_8B).flops_per_token(8192) / 1e9 == pytest.approx(59.9, abs=0.1)
+    assert Qwen3Config(**QWEN3_8B).flops_per_token(131072) / 1e9 == pytest.approx(277.3, abs=0.2)
+    assert Qwen3Config(**QWEN3_30B_A3B).flops_per_token(4096) / 1e9 == pytest.approx(27.9, abs=0.1)
+
+
+def test_wsd_schedule_formula():
+    from torchllmtuner_b200.components.optimizer.lr_scheduler import wsd_factor
+    total, warm, ratio = 100, 10, 0.2
+    decay = int(total * ratio)
+    stable = total + 1 - warm - decay
+    kw = dict(warmup=warm, total=total, decay_ratio=ratio)
+    assert wsd_factor(0, decay_type="linear", **kw) == pytest.approx(1 / warm)
+    assert wsd_factor(warm - 1, decay_type="linear", **kw) == pytest.approx(1.0)
+    assert wsd_factor(50, decay_type="cosine", min_lr_factor=0.1, **kw) == pytest.approx(1.0)
+    step = warm + stable + 4
+    p = (step + 1 - warm - stable) / decay
+    assert wsd_factor(step, decay_type="linear", **kw) == pytest.approx(1 - p)
+    assert wsd_factor(step, decay_type="sqrt", **kw) == pytest.approx(1 - math.sqrt(p))
+    assert wsd_factor(step, decay_type="cosine", min_lr_factor=0.2, **kw) == pytest.approx(0.2 + 0.8 * 0.5 * (1 + math.cos(math.pi * p)))
+
+
+def test_seed_derivation_is_distinct_and_stable():
+    from torchllmtuner_b200.utils.seeding import derive_distinct_seed
+    seeds = {derive_distinct_seed(42, r) for r in range(64)}
+    assert len(seeds) == 64 and derive_distinct_seed(42, 3) == derive_distinct_seed(42, 3)
+
+
+def test_aux_loss_free_bias_update_rule():
+    from torchllmtuner_b200.models.moe.layer import MoE
+    moe = MoE(32, 4, 2, 16, bias_update_coeff=1e-3, dtype=torch.float32)
+    moe.tokens_per_expert_E.copy_(torch.tensor([10.0, 0.0, 5.0, 5.0]))
+    moe.update_expert_bias()
+    delta = 1e-3 * torch.sign(torch.tensor([5.0 - 10, 5.0 - 0, 0.0, 0.0]))
+    assert torch.allclose(moe.expert_bias_E, delta - delta.mean(), atol=1e-7)
+    assert float(moe.tokens_per_expert_E.sum()) == 0.0
