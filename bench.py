@@ -89,6 +89,8 @@ def build_config(args, world: int):
                 max_seq_len=args.seq, steps=10 ** 6, activation_checkpoint_mode=args.ac, chunked_loss_num_chunks=args.loss_chunks,
                 seed=0, dump_folder="/tmp/llmt_bench", data_parallel_shard_size=dp, log_freq=10 ** 6, gc_freq=10 ** 6,
                 fsdp_implementation=args.fsdp_impl, deterministic=False, gradient_accumulation_steps=args.accum)
+    if args.qkv == "fused":
+        flat["qkv_projection"] = "fused"
     if args.tp > 1:
         flat["tensor_parallel_size"] = args.tp
     if args.ep > 1:
@@ -126,6 +128,7 @@ def main() -> int:
     ap.add_argument("--loss-chunks", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline metric)")
     ap.add_argument("--fsdp-impl", default="native", choices=["native", "custom"])
+    ap.add_argument("--qkv", default="separate", choices=["separate", "fused"], help="q/k/v as three GEMMs or one")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (sequence parallel); the rest of the GPUs shard with FSDP")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (MoE models)")
     ap.add_argument("--cp-ulysses", type=int, default=1)

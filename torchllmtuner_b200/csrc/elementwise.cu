@@ -176,10 +176,31 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
 }
 
 // ------------------------------------------------------------------------------------------ QK-norm + RoPE
-// One warp per (token, head). Token rows are `tok_stride` elements apart, heads are packed (HD apart). HD = 64 * P.
-// Lane l owns columns {j * 32 + l : j < P} of the first half and their partners (+ HD/2) in the second half.
+// A group of G = 8 * P lanes per (token, head); HD = 64 * P, so a warp holds 32 / G items (HD 128: two items per warp).
+// Lane g of the group owns columns [4g, 4g + 4) of the first half and their rotation partners [HD/2 + 4g, ...): every
+// access is an 8-byte vector (bf16 x 4) or a 16-byte vector (cos / sin fp32 x 4). Token rows are `tok_stride` elements
+// apart, heads are packed (HD apart), all strides multiples of 4 elements.
 // Forward: n = x * rsqrt(mean x^2 + eps) * w (skipped when w == nullptr), then half rotation with cos/sin [T, HD/2]:
 //   y1 = n1 cos - n2 sin ; y2 = n2 cos + n1 sin.
+__device__ __forceinline__ void ld_bf16x4(const __nv_bfloat16* p, float* f) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, const float* f) {
+  uint2 v;
+  v.x = pack_bf16x2(f[0], f[1]);
+  v.y = pack_bf16x2(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+template <int G>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 template <int P>
 __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t tok_stride,
                                                                const __nv_bfloat16* __restrict__ w,
@@ -187,43 +208,49 @@ __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const __nv_bfloat
                                                                const float* __restrict__ sinb,
                                                                __nv_bfloat16* __restrict__ y, int64_t y_tok_stride,
                                                                float* __restrict__ rstd, int T, int H, float eps) {
-  constexpr int HD = 64 * P;
-  constexpr int HALF = HD / 2;
-  const int lane = threadIdx.x & 31;
-  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= (int64_t)T * H) return;
+  constexpr int HD = 64 * P, HALF = HD / 2, G = 8 * P, IPW = 32 / G;
+  const int lane = threadIdx.x & 31, g = lane % G;
+  const int64_t total = (int64_t)T * H;
+  int64_t item = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * IPW + lane / G;
+  const bool live = item < total;
+  if (!live) item = total - 1;                       // keep the whole warp in the shuffles
   const int t = (int)(item / H), h = (int)(item % H);
-  const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD;
-  float a[P], b[P];
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < P; ++j) {
-    const int c = j * 32 + lane;
-    a[j] = __bfloat162float(px[c]);
-    b[j] = __bfloat162float(px[HALF + c]);
-    ss += a[j] * a[j] + b[j] * b[j];
-  }
+  const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD + 4 * g;
+  float a[4], b[4];
+  ld_bf16x4(px, a);
+  ld_bf16x4(px + HALF, b);
   float r = 1.f;
+  float wa[4] = {1.f, 1.f, 1.f, 1.f}, wb[4] = {1.f, 1.f, 1.f, 1.f};
   if (w != nullptr) {
-    ss = warp_sum(ss);
-    r = rsqrtf(ss / (float)HD + eps);
-    if (lane == 0 && rstd != nullptr) rstd[item] = r;
-  }
-  __nv_bfloat16* py = y + (int64_t)t * y_tok_stride + (int64_t)h * HD;
+    float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < P; ++j) {
-    const int c = j * 32 + lane;
-    float wa = 1.f, wb = 1.f;
-    if (w != nullptr) { wa = __bfloat162float(w[c]); wb = __bfloat162float(w[HALF + c]); }
-    const float cs = cosb[(int64_t)t * HALF + c], sn = sinb[(int64_t)t * HALF + c];
-    const float n1 = a[j] * r * wa, n2 = b[j] * r * wb;
-    py[c] = __float2bfloat16_rn(n1 * cs - n2 * sn);
-    py[HALF + c] = __float2bfloat16_rn(n2 * cs + n1 * sn);
+    for (int j = 0; j < 4; ++j) ss += a[j] * a[j] + b[j] * b[j];
+    ss = group_sum<G>(ss);
+    r = rsqrtf(ss / (float)HD + eps);
+    if (g == 0 && live && rstd != nullptr) rstd[item] = r;
+    ld_bf16x4(w + 4 * g, wa);
+    ld_bf16x4(w + HALF + 4 * g, wb);
+  }
+  const float4 cs = *reinterpret_cast<const float4*>(cosb + (int64_t)t * HALF + 4 * g);
+  const float4 sn = *reinterpret_cast<const float4*>(sinb + (int64_t)t * HALF + 4 * g);
+  const float c4[4] = {cs.x, cs.y, cs.z, cs.w}, s4[4] = {sn.x, sn.y, sn.z, sn.w};
+  float o1[4], o2[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float n1 = a[j] * r * wa[j], n2 = b[j] * r * wb[j];
+    o1[j] = n1 * c4[j] - n2 * s4[j];
+    o2[j] = n2 * c4[j] + n1 * s4[j];
+  }
+  if (live) {
+    __nv_bfloat16* py = y + (int64_t)t * y_tok_stride + (int64_t)h * HD + 4 * g;
+    st_bf16x4(py, o1);
+    st_bf16x4(py + HALF, o2);
   }
 }
 
 // Backward: un-rotate dy (dn1 = d1 cos + d2 sin ; dn2 = d2 cos - d1 sin), then RMSNorm backward per head.
-// The weight gradient is accumulated per block in shared memory and written to dw_partial[blockIdx.x][HD].
+// The weight gradient is accumulated per lane over its items, then per block in shared memory and written to
+// dw_partial[blockIdx.x][HD].
 template <int P>
 __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, int64_t dy_tok_stride,
                                                                const __nv_bfloat16* __restrict__ x, int64_t tok_stride,
@@ -233,39 +260,51 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
                                                                const float* __restrict__ rstd,
                                                                __nv_bfloat16* __restrict__ dx, int64_t dx_tok_stride,
                                                                float* __restrict__ dw_partial, int T, int H) {
-  constexpr int HD = 64 * P;
-  constexpr int HALF = HD / 2;
+  constexpr int HD = 64 * P, HALF = HD / 2, G = 8 * P, IPW = 32 / G;
   __shared__ float sdw[HD];
   for (int i = threadIdx.x; i < HD; i += blockDim.x) sdw[i] = 0.f;
   __syncthreads();
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, g = lane % G;
   const int wpb = blockDim.x >> 5;
-  float dwa[P], dwb[P];
-#pragma unroll
-  for (int j = 0; j < P; ++j) { dwa[j] = 0.f; dwb[j] = 0.f; }
-  for (int64_t item = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); item < (int64_t)T * H; item += (int64_t)gridDim.x * wpb) {
+  const int64_t total = (int64_t)T * H;
+  float dwa[4] = {0.f, 0.f, 0.f, 0.f}, dwb[4] = {0.f, 0.f, 0.f, 0.f};
+  float wa[4] = {1.f, 1.f, 1.f, 1.f}, wb[4] = {1.f, 1.f, 1.f, 1.f};
+  if (w != nullptr) {
+    ld_bf16x4(w + 4 * g, wa);
+    ld_bf16x4(w + HALF + 4 * g, wb);
+  }
+  // every warp runs the same number of rounds so that the group shuffles stay converged
+  const int64_t warp_items = (int64_t)gridDim.x * wpb * IPW;
+  const int64_t rounds = (total + warp_items - 1) / warp_items;
+  for (int64_t rd = 0; rd < rounds; ++rd) {
+    int64_t item = rd * warp_items + ((int64_t)blockIdx.x * wpb + (threadIdx.x >> 5)) * IPW + lane / G;
+    const bool live = item < total;
+    if (!live) item = total - 1;
     const int t = (int)(item / H), h = (int)(item % H);
-    const __nv_bfloat16* px = x + (int64_t)t * tok_stride + (int64_t)h * HD;
-    const __nv_bfloat16* pd = dy + (int64_t)t * dy_tok_stride + (int64_t)h * HD;
-    __nv_bfloat16* po = dx + (int64_t)t * dx_tok_stride + (int64_t)h * HD;
-    float xa[P], xb[P], ga[P], gb[P];
+    const int64_t off = (int64_t)h * HD + 4 * g;
+    float d1[4], d2[4], xa[4] = {0.f, 0.f, 0.f, 0.f}, xb[4] = {0.f, 0.f, 0.f, 0.f};
+    ld_bf16x4(dy + (int64_t)t * dy_tok_stride + off, d1);
+    ld_bf16x4(dy + (int64_t)t * dy_tok_stride + off + HALF, d2);
+    const float4 cs = *reinterpret_cast<const float4*>(cosb + (int64_t)t * HALF + 4 * g);
+    const float4 sn = *reinterpret_cast<const float4*>(sinb + (int64_t)t * HALF + 4 * g);
+    const float c4[4] = {cs.x, cs.y, cs.z, cs.w}, s4[4] = {sn.x, sn.y, sn.z, sn.w};
     const float r = (w != nullptr) ? rstd[item] : 1.f;
-    float c_acc = 0.f;
+    if (w != nullptr) {
+      ld_bf16x4(x + (int64_t)t * tok_stride + off, xa);
+      ld_bf16x4(x + (int64_t)t * tok_stride + off + HALF, xb);
+    }
+    float ga[4], gb[4], c_acc = 0.f;
 #pragma unroll
-    for (int j = 0; j < P; ++j) {
-      const int c = j * 32 + lane;
-      const float d1 = __bfloat162float(pd[c]), d2 = __bfloat162float(pd[HALF + c]);
-      const float cs = cosb[(int64_t)t * HALF + c], sn = sinb[(int64_t)t * HALF + c];
-      float dn1 = d1 * cs + d2 * sn;
-      float dn2 = d2 * cs - d1 * sn;
-      xa[j] = 0.f; xb[j] = 0.f;
+    for (int j = 0; j < 4; ++j) {
+      float dn1 = d1[j] * c4[j] + d2[j] * s4[j];
+      float dn2 = d2[j] * c4[j] - d1[j] * s4[j];
       if (w != nullptr) {
-        xa[j] = __bfloat162float(px[c]);
-        xb[j] = __bfloat162float(px[HALF + c]);
-        dwa[j] += dn1 * xa[j] * r;
-        dwb[j] += dn2 * xb[j] * r;
-        dn1 *= __bfloat162float(w[c]);
-        dn2 *= __bfloat162float(w[HALF + c]);
+        if (live) {
+          dwa[j] += dn1 * xa[j] * r;
+          dwb[j] += dn2 * xb[j] * r;
+        }
+        dn1 *= wa[j];
+        dn2 *= wb[j];
         c_acc += dn1 * xa[j] + dn2 * xb[j];
       }
       ga[j] = dn1;
@@ -273,24 +312,25 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
     }
     float k = 0.f;
     if (w != nullptr) {
-      c_acc = warp_sum(c_acc);
+      c_acc = group_sum<G>(c_acc);
       k = r * r * r * c_acc / (float)HD;
     }
+    float o1[4], o2[4];
 #pragma unroll
-    for (int j = 0; j < P; ++j) {
-      const int c = j * 32 + lane;
-      float o1 = ga[j], o2 = gb[j];
-      if (w != nullptr) { o1 = r * o1 - xa[j] * k; o2 = r * o2 - xb[j] * k; }
-      po[c] = __float2bfloat16_rn(o1);
-      po[HALF + c] = __float2bfloat16_rn(o2);
+    for (int j = 0; j < 4; ++j) {
+      o1[j] = (w != nullptr) ? r * ga[j] - xa[j] * k : ga[j];
+      o2[j] = (w != nullptr) ? r * gb[j] - xb[j] * k : gb[j];
+    }
+    if (live) {
+      st_bf16x4(dx + (int64_t)t * dx_tok_stride + off, o1);
+      st_bf16x4(dx + (int64_t)t * dx_tok_stride + off + HALF, o2);
     }
   }
   if (w != nullptr && dw_partial != nullptr) {
 #pragma unroll
-    for (int j = 0; j < P; ++j) {
-      const int c = j * 32 + lane;
-      atomicAdd(&sdw[c], dwa[j]);
-      atomicAdd(&sdw[HALF + c], dwb[j]);
+    for (int j = 0; j < 4; ++j) {
+      atomicAdd(&sdw[4 * g + j], dwa[j]);
+      atomicAdd(&sdw[HALF + 4 * g + j], dwb[j]);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < HD; i += blockDim.x) dw_partial[(int64_t)blockIdx.x * HD + i] = sdw[i];
@@ -544,8 +584,10 @@ extern "C" int llmt_qk_norm_rope_fwd(const void* x, int64_t tok_stride, const vo
                                      void* y, int64_t y_tok_stride, float* rstd, int T, int H, int HD, float eps,
                                      cudaStream_t st) {
   if (T <= 0 || H <= 0) return 0;
+  if ((tok_stride & 3) || (y_tok_stride & 3) || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(y) & 7)) return -10;
   const int64_t items = (int64_t)T * H;
-  const int grid = (int)((items + 7) / 8);
+  const int ipw = HD == 64 ? 4 : (HD == 128 ? 2 : 1);          // items per warp
+  const int grid = (int)((items + 8 * ipw - 1) / (8 * ipw));
   auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w; auto Y = (__nv_bfloat16*)y;
   if (HD == 64) qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, st>>>(X, tok_stride, W, cosb, sinb, Y, y_tok_stride, rstd, T, H, eps);
   else if (HD == 128) qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, st>>>(X, tok_stride, W, cosb, sinb, Y, y_tok_stride, rstd, T, H, eps);
@@ -564,6 +606,9 @@ extern "C" int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, cons
                                      int64_t dx_tok_stride, float* dw_partial, float* dw_f32, void* dw_bf16,
                                      int accumulate, int T, int H, int HD, cudaStream_t st) {
   if (T <= 0 || H <= 0) return 0;
+  if ((tok_stride & 3) || (dy_tok_stride & 3) || (dx_tok_stride & 3) || (reinterpret_cast<uintptr_t>(x) & 7) ||
+      (reinterpret_cast<uintptr_t>(dy) & 7) || (reinterpret_cast<uintptr_t>(dx) & 7))
+    return -10;
   const int grid = llmt_qk_norm_rope_bwd_partials(T, H);
   auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
   auto DX = (__nv_bfloat16*)dx;

@@ -4,6 +4,8 @@ There is no library fallback on CUDA: if the extension cannot be loaded the call
 """
 from __future__ import annotations
 
+import os
+
 import math
 
 import torch
