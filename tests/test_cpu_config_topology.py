@@ -141,3 +141,32 @@ def test_aux_loss_free_bias_update_rule():
     delta = 1e-3 * torch.sign(torch.tensor([5.0 - 10, 5.0 - 0, 0.0, 0.0]))
     assert torch.allclose(moe.expert_bias_E, delta - delta.mean(), atol=1e-7)
     assert float(moe.tokens_per_expert_E.sum()) == 0.0
+
+
+def test_spmd_context_nesting_and_replay_snapshot():
+    from torchllmtuner_b200.accelerator import spmd
+    dense = resolve_parallel_topology(_cfg(tensor_parallel_size=2, data_parallel_shard_size=4), 8, 3)
+    sparse = resolve_parallel_topology(_cfg(data_parallel_shard_size=8, expert_parallel_size=4), 8, 3)
+    spmd.set_spmd_meshes(dense, sparse)
+    assert spmd.current_spmd_mesh() is dense and spmd.spmd_mesh_size("tp") == 2
+    with spmd.spmd_context(sparse):
+        assert spmd.current_spmd_mesh() is sparse and spmd.spmd_mesh_size("ep") == 4
+        snap = spmd.capture_spmd_context()
+    assert spmd.current_spmd_mesh() is dense
+    with spmd.restore_spmd_context(snap):
+        assert spmd.current_spmd_mesh() is sparse
+    assert spmd.current_spmd_mesh() is dense
+
+
+def test_kernel_argument_contracts_raise_config_errors():
+    from torchllmtuner_b200.ops import validation as v
+    q, k = torch.zeros(8, 4, 64), torch.zeros(8, 3, 64)
+    with pytest.raises(ConfigError):
+        v.validate_attention_inputs(q, k, k)
+    v.validate_attention_inputs(q, torch.zeros(8, 2, 64), torch.zeros(8, 2, 64))
+    with pytest.raises(ConfigError):
+        v.validate_rms_norm_inputs(torch.zeros(4, 16), torch.zeros(8))
+    with pytest.raises(ConfigError):
+        v.require_last_dim_contiguous(torch.zeros(8, 16).t(), "x")
+    with pytest.raises(ConfigError):
+        v.validate_router_inputs(torch.zeros(4, 8), 9)

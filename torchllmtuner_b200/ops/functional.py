@@ -11,6 +11,7 @@ import math
 import torch
 
 from . import reference as ref
+from .validation import validate_attention_inputs, validate_rms_norm_inputs
 from .attn_meta import AttnMeta
 from .cuda_ext import load as _ext
 
@@ -121,6 +122,7 @@ class _AddRMSNorm(torch.autograd.Function):
 
 
 def rms_norm(x, weight, eps: float):
+    validate_rms_norm_inputs(x, weight)
     if _use_cuda(x) and x.dtype == torch.bfloat16:
         return _RMSNorm.apply(x, weight, eps)
     return ref.rms_norm(x, weight, eps)
@@ -209,6 +211,7 @@ class _Attention(torch.autograd.Function):
 
 def attention(q, k, v, meta: AttnMeta, scale: float | None = None):
     """Packed-row GQA attention; documents and masks come from `meta`. q [Tq,Hq,d], k/v [Tk,Hkv,d] -> [Tq,Hq,d]."""
+    validate_attention_inputs(q, k, v)
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _use_cuda(q) and q.dtype == torch.bfloat16:
         if meta.q_tiles is None:

@@ -6,7 +6,7 @@ import torch
 import torch.distributed as dist
 
 from ...components.loss import LossFunctions
-from ...components.optimizer import check_finite
+from .gradients import check_step_condition
 from ...models.moe import collect_aux_loss, moe_blocks
 
 
@@ -92,4 +92,4 @@ class TrainingEngine:
         return norm
 
     def finish_step(self, step: int, loss_value: float | None = None) -> None:
-        check_finite(self.clipper, loss_value)
+        check_step_condition(self.clipper, loss_value)

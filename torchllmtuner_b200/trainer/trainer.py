@@ -6,13 +6,16 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..accelerator.collectives import agree_status, set_pg_timeouts
+from ..accelerator.collectives import set_pg_timeouts
 from ..components.metrics import MetricsProcessor
 from ..config import LLMTunerConfig, resolve_batch_size_per_rank
 from ..datasets import build_dataloader
 from ..datasets.contracts import DataloaderExhaustedError
 from ..utils import GarbageCollection, get_logger, set_log_ranks
 from ..utils.metric_loggers import build_metric_logger
+from .runtime.batch import fetch_batch, global_valid_tokens
+from .runtime.metrics import build_step_metrics
+from .runtime.reductions import TrainingReductionMeshes
 from .runtime.assembly import (build_loss_functions, build_optimizer_stack, create_training_engine, prepare_parallel_model)
 from .runtime.environment import build_runtime_environment
 from .runtime.observer import TrainingObserver
@@ -37,6 +40,7 @@ class Trainer:
         self.optimizers, self.lr_schedulers, self.ema, self.clipper = build_optimizer_stack(cfg, env, self.asm)
         self.engine = create_training_engine(cfg, env, self.model, self.asm, self.loss_fns, self.optimizers,
                                              self.lr_schedulers, self.ema, self.clipper)
+        self.reductions = TrainingReductionMeshes.from_topology(topo)
         self.dp_degree, self.dp_rank = topo.dp, topo.coord("dp")
         self.rows_per_rank = resolve_batch_size_per_rank(t.global_batch_size, self.dp_degree, t.gradient_accumulation_steps)
         arch = self.model.config
@@ -65,25 +69,7 @@ class Trainer:
     # ------------------------------------------------------------------ one optimizer step
     def fetch_batch(self):
         """Read one micro-batch; all data-parallel ranks agree on (ready / exhausted / error)."""
-        state, batch, err = 2, None, None
-        try:
-            batch = next(self.data_iterator)
-        except (StopIteration, DataloaderExhaustedError):
-            state = 1
-        except Exception as e:  # noqa: BLE001
-            state, err = 0, e
-        if dist.is_initialized() and self.env.world_size > 1:
-            dev = self.env.device if self.env.device.type == "cuda" else torch.device("cpu")
-            s = torch.tensor([state], dtype=torch.int32, device=dev)
-            dist.all_reduce(s, op=dist.ReduceOp.MIN)
-            agreed = int(s.item())
-        else:
-            agreed = state
-        if agreed == 0:
-            raise err if err is not None else RuntimeError("a peer rank failed while reading data")
-        if agreed == 1:
-            raise DataloaderExhaustedError("the data loader is exhausted on at least one rank")
-        return batch
+        return fetch_batch(self.data_iterator, self.env)
 
     def train_step(self, batches=None, read_stats: bool = True) -> StepResult | None:
         """One optimizer step. `batches` overrides the data loader (a list of trainer batches, which may already
@@ -93,11 +79,7 @@ class Trainer:
         eng.begin_step()
         if batches is None:
             batches = [self.fetch_batch() for _ in range(t.gradient_accumulation_steps)]
-        local_valid = sum(int(b["num_valid_tokens"]) for b in batches)
-        gv = torch.tensor([float(local_valid)], dtype=torch.float32, device=self.env.device)
-        if self.env.topo.dp > 1:
-            dist.all_reduce(gv, group=self.env.topo.get_group("dp"))
-        gv = gv.reshape(())
+        gv = global_valid_tokens(batches, self.env.device, self.reductions)
         self.checkpointer.maybe_wait_for_staging()
         for i, b in enumerate(batches):
             eng.forward_backward(b, gv, is_last_microbatch=(i == len(batches) - 1))
@@ -107,16 +89,7 @@ class Trainer:
             self.progress.step = step
             return None
         # one device->host read per step: [loss_sum, grad_norm, valid tokens]
-        stats = torch.stack([eng.step_loss, norm.reshape(()).to(torch.float32), gv])
-        group = self.env.topo.get_group("loss")
-        if group is not None:
-            red = stats[:1].clone()
-            dist.all_reduce(red, group=group)
-            if self.env.topo.tp > 1 or self.env.topo.cp > 1:
-                pass        # loss sums of sequence shards add up to the batch loss; token count stays the dp total
-            stats[0] = red[0]
-        loss_sum, gnorm, gtok = (float(x) for x in stats.tolist())
-        loss = loss_sum / max(1.0, gtok)
+        loss, gnorm, gtok = build_step_metrics(eng.step_loss, norm, gv, self.reductions)
         eng.finish_step(step, loss)
         self.progress.step = step
         self.progress.ntokens_seen += int(gtok)
