@@ -95,3 +95,9 @@ def test_registry_lists_every_family():
     have = set(registered_models())
     assert {"qwen3", "qwen3_moe", "qwen3_8b", "qwen3_30b_a3b", "qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "deepseek_v4",
             "kimi_linear", "kimi_k3"} <= have
+
+
+def test_fsdp_cpu_offload_keeps_moments_on_the_host_and_trains():
+    a = run(tiny_config(fsdp_cpu_offload=True, steps=3))
+    b = run(tiny_config(steps=3))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5

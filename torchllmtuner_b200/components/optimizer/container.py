@@ -32,7 +32,9 @@ class OptimizersContainer:
         return [g for o in self.optimizers for g in o.param_groups]
 
 
-def build_optimizers(runtimes, opt_cfg) -> OptimizersContainer:
+def build_optimizers(runtimes, opt_cfg, host_state: bool = False) -> OptimizersContainer:
+    """`host_state` (set by `fsdp_cpu_offload`) keeps the Adam moments in pinned host memory like AdamWSwap does: on a
+    180 GB device the optimizer state is the part worth offloading; parameters and gradients stay resident."""
     outs = []
     for rt in runtimes:
         t = opt_cfg.optimizer_type
@@ -40,7 +42,7 @@ def build_optimizers(runtimes, opt_cfg) -> OptimizersContainer:
             outs.append(ShardedAdamW(rt.units, lr=opt_cfg.learning_rate, betas=opt_cfg.betas, eps=opt_cfg.eps,
                                      weight_decay=opt_cfg.weight_decay, decoupled=t != "Adam",
                                      param_group_rules=opt_cfg.param_groups,
-                                     host_moments=(t == "AdamWSwap" or opt_cfg.state_residency == "host"),
+                                     host_moments=(t == "AdamWSwap" or opt_cfg.state_residency == "host" or host_state),
                                      swap_slice_bytes=opt_cfg.swap_max_device_bytes or (1 << 28)))
         elif t == "DistMuon":
             from .muon import DistMuon
