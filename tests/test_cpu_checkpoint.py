@@ -87,3 +87,22 @@ def test_resume_at_other_dp_and_ep_degree(tmp_path):
     # the 2-rank run trained 2 steps and saved before a third; resume on one rank and continue
     got = run_ranks(1, base_flat(_load=True, **ck), arch=MOE, steps=2)
     assert max(abs(a - b) for a, b in zip(ref["loss"][2:], got["loss"])) < 5e-5, (ref, got)
+
+
+def test_checkpoint_key_names(tmp_path):
+    """Keys follow the reference's flattened names: `model.<fqn>`, `optimizer.state.<fqn>.<moment>`, `ema.ema_params.<fqn>`,
+    plus lr scheduler, train state, data loader and RNG entries."""
+    import torch.distributed.checkpoint as dcp
+    folder = str(tmp_path / "run")
+    cfg = _cfg(folder)
+    tr = Trainer(cfg)
+    tr.train_step()
+    tr.checkpointer.save(1, force=True)
+    tr.checkpointer.wait()
+    tr.close()
+    keys = set(dcp.FileSystemReader(os.path.join(folder, "checkpoint", "step-1")).read_metadata().state_dict_metadata.keys())
+    assert any(k.startswith("model.model.layers.0.self_attn.q_proj.weight@") for k in keys), sorted(keys)[:20]
+    assert any(k.startswith("optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg@") for k in keys)
+    assert any(k.startswith("optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg_sq@") for k in keys)
+    for k in ("obj.lr_scheduler", "obj.train_state", "obj.format", "obj.optimizer.param_groups", "obj.dataloader.dp0", "obj.rng.rank0"):
+        assert k in keys, k
