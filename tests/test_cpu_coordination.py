@@ -36,6 +36,8 @@ def _entry(rank, world, port, fn_name, out, args):
         verdict = f"UNCAUGHT {type(e).__name__}: {e}"
     with open(os.path.join(out, f"{rank}.txt"), "w") as f:
         f.write(verdict)
+    if verdict.startswith("left") or verdict.startswith("timeout"):
+        os._exit(0)                      # a rank left on purpose: no farewell collectives
     dist.barrier()
     dist.destroy_process_group()
 
@@ -118,7 +120,35 @@ def _case_checkpoint_publication_failure(rank, world, folder):
     return f"{verdict},{first},{latest}"
 
 
+def _case_rank_leaves_between_steps(rank, world):
+    """Rank 1 leaves after a completed step with nothing in flight; rank 0's next collective ends with an error inside
+    the shortened process-group timeout instead of hanging."""
+    import datetime
+    import time
+
+    import torch.distributed as dist
+    from torchllmtuner_b200.accelerator.collectives import set_pg_timeouts
+    t = torch.ones(1)
+    dist.all_reduce(t)                                   # "step 1": both ranks take part
+    set_pg_timeouts(3, [])
+    if rank == 1:
+        return "left"
+    t0 = time.time()
+    try:
+        work = dist.all_reduce(t, async_op=True)
+        work.wait(datetime.timedelta(seconds=3))
+        return "no-error"
+    except Exception as e:  # noqa: BLE001
+        return f"timeout after {time.time() - t0:.1f}s: {type(e).__name__}"
+
+
 # ---------------------------------------------------------------------------------------------- tests
+def test_rank_leaving_between_steps_ends_the_next_collective_with_an_error():
+    res = _spawn(_case_rank_leaves_between_steps, 2)
+    assert res[1] == "left" and res[0].startswith("timeout after"), res
+    assert float(res[0].split()[2][:-2]) < 15.0, res
+
+
 def test_one_rank_raising_becomes_every_rank_raising():
     res = _spawn(_case_one_rank_raises, 2)
     assert res[1] == "own" and res[0].startswith("peer:") and "load-shard" in res[0], res
