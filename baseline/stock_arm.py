@@ -70,6 +70,10 @@ class Model(nn.Module):
 
 
 def run_stock(args) -> int:
+    if getattr(args, "tp", 1) > 1 or getattr(args, "ep", 1) > 1 or getattr(args, "cp_ulysses", 1) > 1 or getattr(args, "cp_kv", 1) > 1 \
+            or args.model != "qwen3_8b":
+        print(json.dumps({"impl": "stock", "unavailable": "the stock-PyTorch arm covers the dense FSDP configuration only"}))
+        return 0
     import torch.distributed as dist
     from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
