@@ -80,6 +80,8 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflo
         dist.destroy_process_group()
         return
     check_status("fused ep test")
+    ex = next(iter(__import__("torchllmtuner_b200.parallel.symm_ep", fromlist=["_EXCHANGES"])._EXCHANGES.values()))
+    assert ex.check_canaries(), "a kernel wrote past a buffer of the symmetric arena"
     t = torch.tensor([worst[k_] for k_ in sorted(worst)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:

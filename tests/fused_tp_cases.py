@@ -57,6 +57,7 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int):
             torch.cuda._sleep(20_000_000)
     torch.cuda.synchronize()
     check_status("fused tp test")
+    assert comm.check_canaries(), "a kernel wrote past a buffer of the symmetric arena"
     t = torch.tensor([res[k] for k in sorted(res)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
@@ -73,6 +74,56 @@ def run_fused_tp(world: int, iters: int = 5) -> dict:
     out = tempfile.mktemp(suffix=".json")
     port = 21000 + (os.getpid() * 13 + world) % 20000
     mp.spawn(_worker, args=(world, port, out, iters), nprocs=world, join=True)
+    with open(out) as f:
+        res = json.load(f)
+    os.unlink(out)
+    return res
+
+
+def _absent_peer_worker(rank: int, world: int, port: int, out_path: str):
+    """Rank 1 never publishes its chunk (it skips the launch on the host). Rank 0's bounded flag wait expires, the kernel
+    returns, the status word becomes an exception, and the error-coordination boundary raises on both ranks."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    from torchllmtuner_b200.accelerator.collectives import CoordinatedError, synchronize_local_errors
+    from torchllmtuner_b200.errors import KernelStatusError
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    from torchllmtuner_b200.parallel.symm_tp import AG, FusedTPComm
+    comm = FusedTPComm(dist.group.WORLD, dev, 256 * world, 256)
+    verdict = "none"
+    try:
+        with synchronize_local_errors("all-gather of step 7"):
+            if rank == 0:
+                # what ag_gemm does before its GEMM, with a short poll limit: wait for every rank's `ready` epoch
+                comm.ext.signal_peers([b + comm.off_flag[(AG, 0)] for b in comm.peer_base], comm.rank, 1)
+                comm.ext.wait_flags(comm.base + comm.off_flag[(AG, 0)], world, 1, 7400, 1 << 15)
+                check_status("all-gather wait")
+    except KernelStatusError as e:
+        verdict = "own:" + str(e)
+    except CoordinatedError as e:
+        verdict = "peer:" + str(e)
+    torch.cuda.synchronize()
+    ok = comm.check_canaries()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (verdict, ok))
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(gathered, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_absent_peer(world: int = 2):
+    import tempfile
+
+    import torch.multiprocessing as mp
+    out = tempfile.mktemp(suffix=".json")
+    port = 24000 + (os.getpid() * 23 + world) % 20000
+    mp.spawn(_absent_peer_worker, args=(world, port, out), nprocs=world, join=True)
     with open(out) as f:
         res = json.load(f)
     os.unlink(out)

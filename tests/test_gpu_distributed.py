@@ -96,3 +96,14 @@ def test_peer_ep_capacity_overflow_is_reported_not_written():
     from fused_ep_cases import run_fused_ep
     res = run_fused_ep(2, iters=1, overflow=True)
     assert res["overflow_seen"] == 1.0, res
+
+
+def test_peer_that_never_arrives_becomes_an_error_on_every_rank():
+    """Failure detection on the device without a fault: a host rank skips its launch, the waiting kernel gives up after
+    its poll limit, and both ranks raise through the error-coordination boundary; the symmetric arena is untouched."""
+    _need(2)
+    from fused_tp_cases import run_absent_peer
+    (v0, ok0), (v1, ok1) = run_absent_peer(2)
+    assert v0.startswith("own:") and "flag" in v0 and "7401" in v0, (v0, v1)
+    assert v1.startswith("peer:") and "all-gather of step 7" in v1, (v0, v1)
+    assert ok0 and ok1

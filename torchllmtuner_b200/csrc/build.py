@@ -76,11 +76,16 @@ def build(verbose: bool = False, force: bool = False) -> str:
     log: list[str] = []
     objs = []
 
+    # LLMT_DEBUG=1 in the environment builds every kernel with -DLLMT_DEBUG: device-side argument and bounds checks
+    # that report through the status word (the release build keeps only the checks that guard peer memory).
+    debug = os.environ.get("LLMT_DEBUG") == "1"
+    extra = ["-DLLMT_DEBUG"] if debug else []
+
     def compile_cu(src):
         path = os.path.join(HERE, src)
-        obj = os.path.join(BUILD, f"{os.path.splitext(src)[0]}.{_hash([path] + hdr)}.o")
+        obj = os.path.join(BUILD, f"{os.path.splitext(src)[0]}.{_hash([path] + hdr)}{'.dbg' if debug else ''}.o")
         if not os.path.exists(obj):
-            _run([_nvcc(), *NVCC_FLAGS, "-I", HERE, "-c", path, "-o", obj], log)
+            _run([_nvcc(), *NVCC_FLAGS, *extra, "-I", HERE, "-c", path, "-o", obj], log)
         return obj
 
     with ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as ex:

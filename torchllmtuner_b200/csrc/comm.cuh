@@ -62,6 +62,18 @@ __device__ __forceinline__ void copy_stream16(const uint4* __restrict__ s, uint4
 // Runs `job` cooperatively on `nthreads` threads (this thread is `tid`). Returns false when a flag wait expired.
 __device__ __forceinline__ bool run_side_job(const SideJob& job, long long tid, long long nthreads, int* status) {
   if (job.kind == kSideNone) return true;
+#ifdef LLMT_DEBUG
+  {  // debug build: argument contracts are checked on the device and reported through the status word, never by a trap
+    bool bad = (reinterpret_cast<uintptr_t>(job.dst) & 15) != 0 || job.n <= 0 || job.nsrc < 1 || job.nsrc > kMaxPeers;
+    bad = bad || (job.kind == kSideCopy && (job.n & 15)) || (job.kind == kSideReduce && (job.n & 7));
+    for (int p = 0; p < kMaxPeers; ++p)
+      if (p < job.nsrc && (job.src[p] == nullptr || (reinterpret_cast<uintptr_t>(job.src[p]) & 15))) bad = true;
+    if (bad) {
+      if (tid == 0) report_status(status, kStatusBadArgument, 5900, job.kind);
+      return false;
+    }
+  }
+#endif
   if (job.wait_flags != nullptr) {
     // every lane polls (loads of one address coalesce); bounded
     for (int f = 0; f < job.n_wait; ++f)

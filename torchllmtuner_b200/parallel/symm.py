@@ -148,6 +148,20 @@ def _align(n: int, a: int = 256) -> int:
     return -(-n // a) * a
 
 
+CANARY = 0x5AFEC0DE
+
+
+def write_canary(arena: torch.Tensor, nbytes: int = 256) -> None:
+    """Fill the last `nbytes` of a symmetric arena with a known pattern; nothing in the arena's layout uses them."""
+    arena[-nbytes:].view(torch.int32).fill_(CANARY - (1 << 32) if CANARY >= (1 << 31) else CANARY)
+
+
+def canary_intact(arena: torch.Tensor, nbytes: int = 256) -> bool:
+    """Host-side check (synchronises): False means some kernel, local or on a peer, wrote past a buffer of the arena."""
+    want = CANARY - (1 << 32) if CANARY >= (1 << 31) else CANARY
+    return bool((arena[-nbytes:].view(torch.int32) == want).all().item())
+
+
 class FusedFSDPComm:
     """Owner of the symmetric arena and of the gather / reduce protocols for the dense block units of one runtime."""
 
@@ -175,8 +189,9 @@ class FusedFSDPComm:
         self.flag_off = off
         self.n_flags = 4 * self.world                    # [slot][ready|done][src rank]
         off += _align(self.n_flags * 4)
-        self.arena = symm_mem.empty(off, dtype=torch.uint8, device=rt.device)
+        self.arena = symm_mem.empty(off + 256, dtype=torch.uint8, device=rt.device)
         self.arena.zero_()
+        write_canary(self.arena)
         self.hdl = symm_mem.rendezvous(self.arena, self.group)
         self.peer_base = [int(p) for p in self.hdl.buffer_ptrs]
         self.base = self.peer_base[self.rank]
@@ -243,6 +258,9 @@ class FusedFSDPComm:
 
     def flush_all(self) -> None:
         self.queue.flush(None)
+
+    def check_canaries(self) -> bool:
+        return canary_intact(self.arena)
 
     def step_barrier(self) -> None:
         """After the optimizer rewrote the shards: nobody may read them before everybody has finished writing."""

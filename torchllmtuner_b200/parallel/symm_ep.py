@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.moe.experts import SEG_ALIGN
+from .symm import canary_intact, write_canary
 
 BUF_X, BUF_Y, BUF_DY, BUF_DX = 0, 1, 2, 3
 
@@ -51,9 +52,10 @@ class PeerExchange:
         self.off_cflag = self.off_tab + tab_b
         base = self.off_cflag + flag_b
         self.off_flag = {(b, w): base + (2 * b + w) * flag_b for b in range(4) for w in (0, 1)}     # w: 0 ready, 1 free
-        total = base + 8 * flag_b
+        total = base + 8 * flag_b + 256
         self.arena = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.arena.zero_()
+        write_canary(self.arena)
         self.hdl = symm_mem.rendezvous(self.arena, group)
         self.peer_base = [int(p) for p in self.hdl.buffer_ptrs]
         self.base = self.peer_base[self.me]
@@ -62,6 +64,9 @@ class PeerExchange:
         self.stats = {"dispatches": 0, "combines": 0}
         torch.cuda.synchronize(device)
         self.hdl.barrier()
+
+    def check_canaries(self) -> bool:
+        return canary_intact(self.arena)
 
     def fits(self, copies: int, hidden: int, num_experts: int) -> bool:
         return copies <= self.max_copies and hidden == self.D and num_experts == self.E

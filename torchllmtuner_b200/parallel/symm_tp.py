@@ -19,6 +19,8 @@ import os
 import torch
 import torch.distributed as dist
 
+from .symm import canary_intact, write_canary
+
 AG, RS = 1, 2
 
 
@@ -47,9 +49,10 @@ class FusedTPComm:
         base = self.N_SLOTS * (chunk_b + part_b)
         self.off_flag = {(AG, i): base + i * flag_b for i in range(self.N_SLOTS)}
         self.off_flag.update({(RS, i): base + (self.N_SLOTS + i) * flag_b for i in range(self.N_SLOTS)})
-        total = base + 2 * self.N_SLOTS * flag_b
+        total = base + 2 * self.N_SLOTS * flag_b + 256
         self.arena = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.arena.zero_()
+        write_canary(self.arena)
         self.hdl = symm_mem.rendezvous(self.arena, group)
         self.peer_base = [int(p) for p in self.hdl.buffer_ptrs]
         self.base = self.peer_base[self.rank]
@@ -62,6 +65,9 @@ class FusedTPComm:
         self.hdl.barrier()
 
     # ------------------------------------------------------------------ helpers
+    def check_canaries(self) -> bool:
+        return canary_intact(self.arena)
+
     def fits(self, rows: int, cols: int) -> bool:
         return rows == self.rows and cols <= self.cols and cols % 8 == 0
 
