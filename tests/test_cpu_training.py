@@ -101,3 +101,15 @@ def test_fsdp_cpu_offload_keeps_moments_on_the_host_and_trains():
     a = run(tiny_config(fsdp_cpu_offload=True, steps=3))
     b = run(tiny_config(steps=3))
     assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
+
+
+def test_moe_dispatch_timers_report_percentiles():
+    cfg = tiny_config(model_name_or_path="qwen3_moe", measure_moe_dispatch=True, steps=2, log_freq=1)
+    cfg.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
+    tr = Trainer(cfg)
+    try:
+        tr.config.training.steps = 2
+        tr.train()
+        assert "moe/dispatch_p50(ms)" in tr.last_metrics and "moe/combine_p90(ms)" in tr.last_metrics, tr.last_metrics
+    finally:
+        tr.close()

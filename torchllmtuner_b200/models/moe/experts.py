@@ -173,6 +173,13 @@ class RoutedExperts(nn.Module):
         self.dispatcher = dispatcher or LocalTokenDispatcher(experts.num_experts)
 
     def forward(self, x, weights, indices):
-        rows, seg, state = self.dispatcher.dispatch(x, indices)
+        timer = getattr(self, "dispatch_timer", None)
+        if timer is None:
+            rows, seg, state = self.dispatcher.dispatch(x, indices)
+            y = self.experts(rows, seg)
+            return self.dispatcher.combine(y, weights, state)
+        with timer.span("dispatch"):
+            rows, seg, state = self.dispatcher.dispatch(x, indices)
         y = self.experts(rows, seg)
-        return self.dispatcher.combine(y, weights, state)
+        with timer.span("combine"):
+            return self.dispatcher.combine(y, weights, state)

@@ -50,3 +50,48 @@ class TrainingObserver:
         s = sorted(self.window)
         pick = lambda q: s[min(len(s) - 1, int(q * (len(s) - 1) + 0.5))]  # noqa: E731
         return {"steady/step_time_p50(s)": pick(0.5), "steady/step_time_p90(s)": pick(0.9)}
+
+
+class DispatchTimer:
+    """Device events around MoE token dispatch and combine (reference: llmtuner/trainer/runtime/training_observer.py:41-181).
+    The MoE blocks call `span(kind)`; `collect()` turns the finished pairs of a step into p50 / p90 milliseconds."""
+
+    def __init__(self, device):
+        self.cuda = torch.device(device).type == "cuda"
+        self.pending: dict[str, list] = {"dispatch": [], "combine": []}
+
+    class _Span:
+        def __init__(self, timer, kind):
+            self.timer, self.kind = timer, kind
+
+        def __enter__(self):
+            if self.timer.cuda:
+                self.a, self.b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self.a.record()
+            else:
+                self.t0 = time.perf_counter()
+            return self
+
+        def __exit__(self, *exc):
+            if self.timer.cuda:
+                self.b.record()
+                self.timer.pending[self.kind].append((self.a, self.b))
+            else:
+                self.timer.pending[self.kind].append((time.perf_counter() - self.t0) * 1e3)
+            return False
+
+    def span(self, kind: str):
+        return DispatchTimer._Span(self, kind)
+
+    def collect(self) -> dict[str, float]:
+        """Call after the step's device work has been synchronised (the observer's end_step does that)."""
+        out = {}
+        for kind, items in self.pending.items():
+            ms = sorted((a.elapsed_time(b) if self.cuda else a) for a, b in items) if self.cuda else sorted(items)
+            if ms:
+                pick = lambda q: ms[min(len(ms) - 1, int(q * (len(ms) - 1) + 0.5))]  # noqa: E731
+                out[f"moe/{kind}_p50(ms)"] = pick(0.5)
+                out[f"moe/{kind}_p90(ms)"] = pick(0.9)
+                out[f"moe/{kind}_total(ms)"] = float(sum(ms))
+            items.clear()
+        return out

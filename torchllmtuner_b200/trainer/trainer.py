@@ -13,6 +13,7 @@ from ..datasets import build_dataloader
 from ..datasets.contracts import DataloaderExhaustedError
 from ..utils import GarbageCollection, get_logger, set_log_ranks
 from ..utils.metric_loggers import build_metric_logger
+from ..utils.nvtx import nvtx_range
 from .runtime.batch import fetch_batch, global_valid_tokens
 from .runtime.metrics import build_step_metrics
 from .runtime.reductions import TrainingReductionMeshes
@@ -55,6 +56,16 @@ class Trainer:
                                         flops_per_token=self.model.flops_per_token(t.max_seq_len), num_params=self.num_params,
                                         logger=self.logger, sink=sink, device=env.device if env.device.type == "cuda" else None)
         self.observer = TrainingObserver(t.metrics_config, env.device, env.world_size)
+        self.dispatch_timer = None
+        if t.metrics_config.measure_moe_dispatch:
+            from ..models.moe import MoE
+            from .runtime.observer import DispatchTimer
+            self.dispatch_timer = DispatchTimer(env.device)
+            for m in self.model.modules():
+                if isinstance(m, MoE):
+                    m.dispatch_timer = m.routed.dispatch_timer = self.dispatch_timer
+        from ..utils import nvtx
+        nvtx.enable(bool(getattr(t.profiler_config, "enable_profiling", False)))
         from ..components.checkpointer import build_checkpointer
         self.checkpointer = build_checkpointer(cfg, self)
         from ..components.profiler import build_profiler
@@ -82,9 +93,11 @@ class Trainer:
         gv = global_valid_tokens(batches, self.env.device, self.reductions)
         self.checkpointer.maybe_wait_for_staging()
         for i, b in enumerate(batches):
-            eng.forward_backward(b, gv, is_last_microbatch=(i == len(batches) - 1))
+            with nvtx_range(f"forward_backward[{i}]"):
+                eng.forward_backward(b, gv, is_last_microbatch=(i == len(batches) - 1))
         step = self.progress.step + 1
-        norm = eng.optimizer_step(step)
+        with nvtx_range("optimizer_step"):
+            norm = eng.optimizer_step(step)
         if not read_stats:
             self.progress.step = step
             return None
@@ -126,8 +139,9 @@ class Trainer:
                     set_pg_timeouts(self.config.parallel.train_timeout_seconds, list(self.env.topo._groups.values()))
 
     def _report_completed_step(self, res: StepResult, global_tokens: int) -> None:
+        moe_times = self.dispatch_timer.collect() if self.dispatch_timer is not None else {}
         if self.metrics.should_log(res.step):
-            extra = self.observer.steady_state()
+            extra = {**self.observer.steady_state(), **moe_times}
             self.last_metrics = self.metrics.log(res.step, loss=res.loss, grad_norm=res.grad_norm, lr=res.lr,
                                                  global_tokens=global_tokens, step_seconds=res.step_seconds, extra=extra)
         self.checkpointer.save(res.step, last_step=(res.step == self.config.training.steps))
