@@ -37,3 +37,15 @@ def test_small_gemms_carry_nothing_and_flush_finishes_jobs():
     assert len(q.jobs) == 1 and q.jobs[0].tag == "b"
     q.flush(None)
     assert not q
+
+
+def test_canary_words_detect_a_write_past_the_last_buffer():
+    import torch
+    from torchllmtuner_b200.parallel.symm import canary_intact, write_canary
+    arena = torch.zeros(4096 + 256, dtype=torch.uint8)
+    write_canary(arena)
+    assert canary_intact(arena)
+    arena[:4096].fill_(7)                      # legal writes leave it intact
+    assert canary_intact(arena)
+    arena[4096 + 17] = 1                       # one byte past the buffers
+    assert not canary_intact(arena)

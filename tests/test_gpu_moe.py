@@ -56,3 +56,22 @@ def test_moe_block_cuda_matches_cpu_reference():
     for a, b in zip(gg, gc):
         if a is not None and b is not None:
             _close(a, b.to("cuda"), 6e-2)
+
+
+@pytest.mark.parametrize("n,E,R", [(1000, 8, 2), (32768, 128, 8), (4097, 64, 4), (5, 16, 2)])
+def test_ep_plan_matches_stable_sort(n, E, R):
+    """Destination rows of the peer-memory dispatcher: stable position inside each expert's run plus the run's start."""
+    from torchllmtuner_b200.ops.cuda_ext import load
+    ext = load()
+    g = torch.Generator(device="cuda").manual_seed(n + E)
+    flat = torch.randint(0, E, (n,), generator=g, device="cuda")
+    send_off = torch.randint(0, 1000, (E,), generator=g, device="cuda").to(torch.int32)
+    drank, drow = ext.ep_plan(flat, E, R, send_off)
+    counts = torch.bincount(flat, minlength=E)
+    start = counts.cumsum(0) - counts
+    order = torch.argsort(flat, stable=True)
+    rank = torch.empty_like(order)
+    rank[order] = torch.arange(n, device="cuda")
+    pos = rank - start[flat]
+    assert torch.equal(drow.long(), send_off.long()[flat] + pos)
+    assert torch.equal(drank.long(), flat // (E // R))

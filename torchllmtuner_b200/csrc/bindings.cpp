@@ -154,6 +154,19 @@ std::vector<Tensor> ep_exchange(const Tensor& flat, int64_t E, int64_t me, const
   return {seg, tot, off};
 }
 
+// (drank, drow) int32 [ncopies]: owner rank and row of every token copy (stable order inside each expert's run).
+std::vector<Tensor> ep_plan(const Tensor& flat, int64_t E, int64_t R, const Tensor& send_off) {
+  c10::cuda::CUDAGuard guard(flat.device());
+  TORCH_CHECK(flat.is_cuda() && flat.scalar_type() == at::kLong && flat.is_contiguous());
+  check_i32(send_off, "send_off");
+  auto o = torch::dtype(torch::kInt32).device(flat.device());
+  Tensor drank = torch::empty({flat.numel()}, o), drow = torch::empty({flat.numel()}, o);
+  check_rc(llmt_ep_plan(flat.data_ptr<int64_t>(), flat.numel(), (int)E, (int)R, send_off.data_ptr<int>(), drank.data_ptr<int>(),
+                        drow.data_ptr<int>(), cur_stream()),
+           "llmt_ep_plan");
+  return {drank, drow};
+}
+
 // peers[drank[c]][drow[c]] = scale[c] * src[c / k]; returns dot[c] = <src[c / k], other[c]> when `other` is given.
 c10::optional<Tensor> ep_push_rows(const Tensor& src, const c10::optional<Tensor>& scale, const Tensor& drank, const Tensor& drow,
                                    const std::vector<int64_t>& bufs, int64_t cap, int64_t k, const c10::optional<Tensor>& other) {
@@ -587,6 +600,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rank"), py::arg("epoch"), py::arg("peer_src"), py::arg("flags"), py::arg("peer_flags"), py::arg("counters"),
         py::arg("acc") = py::none(), py::arg("out") = py::none(), py::arg("residual") = py::none());
   m.def("ep_exchange", &ep_exchange);
+  m.def("ep_plan", &ep_plan);
   m.def("ep_push_rows", &ep_push_rows);
   m.def("ep_pull_rows", &ep_pull_rows);
   m.def("ep_clone_rows", &ep_clone_rows);

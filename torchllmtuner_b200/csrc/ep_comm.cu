@@ -81,6 +81,51 @@ __global__ void __launch_bounds__(1024) ep_exchange_kernel(const int64_t* __rest
   }
 }
 
+// Destination of every token copy, in one pass: pos = stable rank of copy c among this rank's copies of the same expert
+// (copies are numbered token-major, so the order is the one a stable sort by expert would give), then
+// drank[c] = expert / El and drow[c] = send_off[expert] + pos. One CTA of 1024 threads walks the copies in chunks of
+// 1024: lanes rank themselves inside their warp with match_any, a per-warp histogram and a scan over the 32 warps give
+// the offset of each warp inside the chunk, a running per-expert count carries over between chunks. E <= 256.
+constexpr int kEpPlanMaxExperts = 256;
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const int64_t* __restrict__ flat, int64_t ncopies, int E, int El,
+                                                       const int* __restrict__ send_off, int* __restrict__ drank,
+                                                       int* __restrict__ drow) {
+  __shared__ int run[kEpPlanMaxExperts];             // copies of each expert in earlier chunks
+  __shared__ int hist[32][kEpPlanMaxExperts];        // per warp: copies of each expert in this chunk, then exclusive scan over warps
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) run[e] = 0;
+  for (int64_t base = 0; base < ncopies; base += blockDim.x) {
+    for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) hist[i / E][i % E] = 0;
+    __syncthreads();
+    const int64_t c = base + threadIdx.x;
+    const bool live = c < ncopies;
+    int g = live ? (int)flat[c] : -1;
+    if (g < 0 || g >= E) g = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, g);
+    const int in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (g >= 0 && in_warp == 0) hist[warp][g] = __popc(peers);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {   // exclusive scan over the warps, seeded with the running count
+      int acc = run[e];
+      for (int w = 0; w < 32; ++w) {
+        const int n = hist[w][e];
+        hist[w][e] = acc;
+        acc += n;
+      }
+      run[e] = acc;
+    }
+    __syncthreads();
+    if (g >= 0) {
+      drank[c] = g / El;
+      drow[c] = send_off[g] + hist[warp][g] + in_warp;
+    } else if (live) {
+      drank[c] = 0;
+      drow[c] = -1;                                      // dropped by the push / pull kernels
+    }
+    __syncthreads();
+  }
+}
+
 // dst_peer[drank[c]][drow[c]] = scale[c] * src[c / k]; optional dot_out[c] = <src[c / k], other[c]>
 __global__ void __launch_bounds__(256) ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ scale,
                                                            const int* __restrict__ drank, const int* __restrict__ drow,
@@ -214,6 +259,14 @@ extern "C" int llmt_ep_exchange(const int64_t* flat, int64_t ncopies, int E, int
   if (R < 1 || R > kMaxPeers || E < R || E % R || E > kEpMaxExperts || me < 0 || me >= R || cap % 128) return -10;
   ep_exchange_kernel<<<1, 1024, 0, st>>>(flat, ncopies, E, R, me, make_peers(tables, R), make_peers(flags, R), epoch, cap,
                                          seg_offsets, totals, send_off, status);
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_ep_plan(const int64_t* flat, int64_t ncopies, int E, int R, const int* send_off, int* drank, int* drow,
+                            cudaStream_t st) {
+  if (ncopies <= 0) return 0;
+  if (R < 1 || E % R || E > kEpPlanMaxExperts) return -10;
+  ep_plan_kernel<<<1, 1024, 0, st>>>(flat, ncopies, E, E / R, send_off, drank, drow);
   LLMT_CHECK_LAUNCH();
 }
 

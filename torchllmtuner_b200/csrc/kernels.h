@@ -56,6 +56,7 @@ int llmt_clip_coef(const float* total_sq, float max_norm, float* clip_coef, floa
 // ---- expert-parallel token exchange over peer memory (ep_comm.cu) ----
 int llmt_ep_exchange(const int64_t* flat, int64_t ncopies, int E, int R, int me, void* const* tables, void* const* flags,
                      uint32_t epoch, int cap, int* seg_offsets, int* totals, int* send_off, int* status, cudaStream_t st);
+int llmt_ep_plan(const int64_t* flat, int64_t ncopies, int E, int R, const int* send_off, int* drank, int* drow, cudaStream_t st);
 int llmt_ep_push_rows(const void* src, const float* scale, const int* drank, const int* drow, void* const* bufs, int R, int cap,
                       int64_t ncopies, int k, int D, const void* other, float* dot_out, int* status, cudaStream_t st);
 int llmt_ep_pull_rows(void* const* bufs, int R, const int* drank, const int* drow, const float* w, void* out, void* keep, int cap,

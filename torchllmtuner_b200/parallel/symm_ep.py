@@ -94,14 +94,17 @@ class PeerExchange:
         self.count_epoch += 1
         seg, totals, send_off = self.ext.ep_exchange(flat, self.E, self.me, self._ptrs(self.off_tab), self._ptrs(self.off_cflag),
                                                      self.count_epoch, self.cap)
-        counts = torch.bincount(flat, minlength=self.E)
-        start = counts.cumsum(0) - counts
-        order = torch.argsort(flat, stable=True)
-        rank = torch.empty_like(order)
-        rank[order] = torch.arange(order.numel(), device=order.device)
-        pos = rank - start[flat]                                             # stable position inside this rank's run
-        drow = (send_off.long()[flat] + pos).to(torch.int32)
-        drank = (flat // self.El).to(torch.int32)
+        if self.E <= 256 and os.environ.get("LLMT_EP_FUSED_PLAN", "0") == "1":
+            drank, drow = self.ext.ep_plan(flat, self.E, self.R, send_off)
+        else:
+            counts = torch.bincount(flat, minlength=self.E)
+            start = counts.cumsum(0) - counts
+            order = torch.argsort(flat, stable=True)
+            rank = torch.empty_like(order)
+            rank[order] = torch.arange(order.numel(), device=order.device)
+            pos = rank - start[flat]                                         # stable position inside this rank's run
+            drow = (send_off.long()[flat] + pos).to(torch.int32)
+            drank = (flat // self.El).to(torch.int32)
         return {"seg": seg, "totals": totals, "drank": drank, "drow": drow, "T": indices.shape[0], "k": indices.shape[1]}
 
     def push(self, buf: int, src: torch.Tensor, plan, scale=None, other=None):
