@@ -526,18 +526,31 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool key_ok = (row < nk) && (key_idx < klen);
     const float scale_log2 = scale * kLog2e;
     bool ok = true;
+    // Row statistics (log-sum-exp, delta) of a query tile are fetched one iteration ahead: the global loads are issued
+    // at the top of iteration it-1, parked in registers while that iteration computes, and published at its end.
+    auto load_stats = [&](int it, float& l, float& d) {
+      const int h = hk * g + it / n_qt;
+      const int qi = qs + (it % n_qt) * kBwdQ + tid;
+      const bool v = qi < qlen;
+      l = v ? lse[(int64_t)h * Tq + qbeg + qi] * kLog2e : INFINITY;
+      d = v ? delta[(int64_t)h * Tq + qbeg + qi] : 0.f;
+    };
+    if (n_it > 0) {
+      if (tid < kBwdQ) {
+        float l, d;
+        load_stats(0, l, d);
+        s_lse[tid] = l;
+        s_delta[tid] = d;
+      }
+      mbar_arrive(stat_ready);
+    }
     for (int it = 0; it < n_it && ok; ++it) {
       const int b = it & 1;
       const uint32_t ph = (it >> 1) & 1;
-      const int h = hk * g + it / n_qt;
       const int qi0 = qs + (it % n_qt) * kBwdQ;  // first query index (inside the document) of this q tile
-      if (tid < kBwdQ) {
-        const int qi = qi0 + tid;
-        const bool v = qi < qlen;
-        s_lse[b * kBwdQ + tid] = v ? lse[(int64_t)h * Tq + qbeg + qi] * kLog2e : INFINITY;
-        s_delta[b * kBwdQ + tid] = v ? delta[(int64_t)h * Tq + qbeg + qi] : 0.f;
-      }
-      mbar_arrive(stat_ready);
+      float next_l = INFINITY, next_d = 0.f;
+      const bool have_next = it + 1 < n_it;
+      if (have_next && tid < kBwdQ) load_stats(it + 1, next_l, next_d);
       if (!mbar_wait_bounded(stat_ready, it & 1, abort_flag, status, 2330)) { ok = false; break; }
       if (!mbar_wait_bounded(&s_full[b], ph, abort_flag, status, 2300 + b)) { ok = false; break; }
       tc_fence_after();
@@ -573,6 +586,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       fence_proxy_async_smem();
       mbar_arrive(&p_full[b]);
+      if (have_next) {
+        // every thread has passed this iteration's stat_ready wait, so nobody still reads the other buffer
+        if (tid < kBwdQ) {
+          s_lse[(b ^ 1) * kBwdQ + tid] = next_l;
+          s_delta[(b ^ 1) * kBwdQ + tid] = next_d;
+        }
+        mbar_arrive(stat_ready);
+      }
     }
     if (ok && n_it > 0) ok = mbar_wait_bounded(acc_done, 0, abort_flag, status, 2320);
     if (ok) {
@@ -647,10 +668,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kempty = bars + 3;
   uint64_t* vfull = bars + 5;
   uint64_t* vempty = bars + 7;
-  uint64_t* s_full = bars + 9;
-  uint64_t* ds_full = bars + 10;
-  uint64_t* dq_done = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* s_full = bars + 9;       // [2]: S of key tile j lands in TMEM buffer j & 1
+  uint64_t* dp_full = bars + 11;
+  uint64_t* ds_full = bars + 12;
+  uint64_t* dq_done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -667,7 +689,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1); mbar_init(&vfull[s], 1); mbar_init(&vempty[s], 1);
     }
-    mbar_init(s_full, 1); mbar_init(ds_full, 256); mbar_init(dq_done, 1);
+    mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1); mbar_init(dp_full, 1); mbar_init(ds_full, 256); mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -676,7 +698,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+  // S is double buffered (columns 0..127 and 384..511) so that Q K^T of the next key tile is issued while the softmax
+  // warps still work on the current one; dP (128..255) and dQ (256..) are single.
+  const uint32_t tS0 = tmem_base, tS1 = tmem_base + 384, tDP = tmem_base + 128, tDQ = tmem_base + 256;
 
   if (warp == 0) {
     if (lane == 0 && n_kv > 0) {
@@ -718,22 +742,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t idDQ = umma_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), adS = smem_u32(sdS);
       bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, status, 3200);
-      for (int j = 0; j < n_kv && ok; ++j) {
+      auto issue_S = [&](int j) -> bool {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait_bounded(&kfull[s], ph, abort_flag, status, 3210 + s)) break;
-        if (!mbar_wait_bounded(&vfull[s], ph, abort_flag, status, 3220 + s)) break;
+        if (!mbar_wait_bounded(&kfull[s], (j >> 1) & 1, abort_flag, status, 3210 + s)) return false;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tS, desc_kmajor(aQ, ks), desc_kmajor(aK + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+          umma_bf16_ss(s ? tS1 : tS0, desc_kmajor(aQ, ks), desc_kmajor(aK + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      auto issue_dP = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait_bounded(&vfull[s], (j >> 1) & 1, abort_flag, status, 3220 + s)) return false;
+        tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
           umma_bf16_ss(tDP, desc_kmajor(adO, ks), desc_kmajor(aV + s * SM::kTile, ks), idS, ks ? 1u : 0u);
-        umma_commit(s_full);
+        umma_commit(dp_full);
         umma_commit(&vempty[s]);
+        return true;
+      };
+      if (ok) ok = issue_S(0) && issue_dP(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        // S of the next tile goes into the other TMEM buffer while the softmax warps are busy with tile j
+        if (j + 1 < n_kv) { if (!issue_S(j + 1)) break; }
         if (!mbar_wait_bounded(ds_full, j & 1, abort_flag, status, 3230)) break;
         tc_fence_after();
+        // dP of the next tile first (the softmax warps wait for it), then dQ of this tile
+        if (j + 1 < n_kv) { if (!issue_dP(j + 1)) break; }
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma_bf16_ss(tDQ, desc_kmajor(adS, ks), desc_mnmajor(aK + s * SM::kTile, ks), idDQ, (j | ks) ? 1u : 0u);
@@ -754,11 +792,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int row_limit = row_ok ? (causal ? min(klen, diag0 + row) : klen) : 0;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      if (!mbar_wait_bounded(s_full, j & 1, abort_flag, status, 3300)) { ok = false; break; }
+      if (!mbar_wait_bounded(&s_full[j & 1], (j >> 1) & 1, abort_flag, status, 3300)) { ok = false; break; }
+      if (!mbar_wait_bounded(dp_full, j & 1, abort_flag, status, 3305)) { ok = false; break; }
       tc_fence_after();
-      if (j > 0) {
-        if (!mbar_wait_bounded(dq_done, (j - 1) & 1, abort_flag, status, 3310)) { ok = false; break; }
-      }
+      const uint32_t tS = (j & 1) ? tS1 : tS0;
       const int kbase = j * 128;
 #pragma unroll 1
       for (int c = half * 2; c < half * 2 + 2; ++c) {
@@ -777,8 +814,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
           wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
         }
+        if (j > 0 && c == half * 2) {   // dQ of the previous tile still reads the dS buffer until its MMAs complete
+          if (!mbar_wait_bounded(dq_done, (j - 1) & 1, abort_flag, status, 3310)) { ok = false; break; }
+        }
         store_row32_swz(sdS, row, c * 32, wd);
       }
+      if (!ok) break;
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(ds_full);
