@@ -113,3 +113,22 @@ def test_moe_dispatch_timers_report_percentiles():
         assert "moe/dispatch_p50(ms)" in tr.last_metrics and "moe/combine_p90(ms)" in tr.last_metrics, tr.last_metrics
     finally:
         tr.close()
+
+
+def test_metric_names_and_profiler_trace_layout(tmp_path):
+    """The logged step carries the reference's metric names; the profiler writes
+    `<traces>/iteration_{step}/rank{rank}_trace.json.gz` on its schedule."""
+    import glob
+    import os
+    cfg = tiny_config(steps=4, log_freq=1, dump_folder=str(tmp_path), enable_profiling=True, profile_freq=2, profiler_active=1,
+                      profiler_warmup=1)
+    tr = Trainer(cfg)
+    try:
+        tr.train()
+        for k in ("loss_metrics/global_avg_loss", "loss_metrics/global_max_loss", "grad_norm", "lr", "throughput(tps)",
+                  "tps_per_device", "tflops", "mfu(%)", "time_metrics/end_to_end(s)"):
+            assert k in tr.last_metrics, (k, sorted(tr.last_metrics))
+    finally:
+        tr.close()
+    traces = glob.glob(os.path.join(str(tmp_path), "**", "iteration_*", "rank0_trace.json*"), recursive=True)
+    assert traces, list(os.walk(str(tmp_path)))[:5]
