@@ -132,3 +132,18 @@ def test_metric_names_and_profiler_trace_layout(tmp_path):
         tr.close()
     traces = glob.glob(os.path.join(str(tmp_path), "**", "iteration_*", "rank0_trace.json*"), recursive=True)
     assert traces, list(os.walk(str(tmp_path)))[:5]
+
+
+def test_cli_main_runs_a_tiny_job_and_seed_checkpoint(tmp_path, monkeypatch):
+    """`python -m torchllmtuner_b200 <flat flags>` end to end, then the seed-checkpoint mode of the same CLI."""
+    import os
+    from torchllmtuner_b200.trainer.cli import main
+    monkeypatch.setenv("LLMTUNER_DEVICE", "cpu")
+    flags = ["--model_name_or_path", "qwen3", "--vocab_size", "256", "--hidden_size", "64", "--intermediate_size", "128",
+             "--num_hidden_layers", "2", "--num_attention_heads", "4", "--num_key_value_heads", "2", "--global_batch_size", "2",
+             "--max_seq_len", "32", "--steps", "3", "--enable", "true", "--interval", "2", "--last_save_model_only", "false"]
+    assert main(flags + ["--dump_folder", str(tmp_path / "a")]) == 0
+    assert os.path.exists(tmp_path / "a" / "checkpoint" / "step-2" / ".metadata")
+    assert os.path.exists(tmp_path / "a" / "checkpoint" / "step-3" / ".metadata")          # the last step is always saved
+    assert main(flags + ["--dump_folder", str(tmp_path / "b"), "--create_seed_checkpoint", "true"]) == 0
+    assert os.path.exists(tmp_path / "b" / "checkpoint" / "step-0" / ".metadata")
