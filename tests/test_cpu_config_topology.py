@@ -170,3 +170,10 @@ def test_kernel_argument_contracts_raise_config_errors():
         v.require_last_dim_contiguous(torch.zeros(8, 16).t(), "x")
     with pytest.raises(ConfigError):
         v.validate_router_inputs(torch.zeros(4, 8), 9)
+
+
+def test_runtime_validator_reports_a_working_cpu_path(monkeypatch):
+    monkeypatch.setenv("LLMTUNER_DEVICE", "cpu")
+    from torchllmtuner_b200.utils.validate_runtime import collect
+    rep = collect()
+    assert "train_step_loss" in rep and rep["distributed"]["gloo"] and "extension" in rep
