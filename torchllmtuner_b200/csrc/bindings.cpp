@@ -386,26 +386,34 @@ inline int64_t row_stride_2d(const Tensor& t) {
   return t.stride(0);
 }
 
-Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
+static const int* limit_ptr(const c10::optional<Tensor>& row_limit) {
+  if (!row_limit.has_value()) return nullptr;
+  TORCH_CHECK(row_limit->is_cuda() && row_limit->scalar_type() == at::kInt && row_limit->numel() >= 1, "row_limit must be a CUDA int32 tensor");
+  return row_limit->data_ptr<int>();
+}
+
+// row_limit (optional int32 device scalar): rows at or beyond it are neither read nor written.
+Tensor swiglu_fwd(const Tensor& gate, const Tensor& up, const c10::optional<Tensor>& row_limit) {
   c10::cuda::CUDAGuard guard(gate.device());
   check_bf16(gate, "gate");
   check_bf16(up, "up");
   TORCH_CHECK(row_stride_2d(gate) == row_stride_2d(up) && gate.sizes() == up.sizes());
   Tensor out = torch::empty({gate.size(0), gate.size(1)}, gate.options());
   check_rc(llmt_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.size(0), (int)gate.size(1), gate.stride(0),
-                           out.stride(0), cur_stream()),
+                           out.stride(0), limit_ptr(row_limit), cur_stream()),
            "llmt_swiglu_fwd");
   return out;
 }
 
 // dgate/dup are written into `dgate_out` / `dup_out` (same row stride), which lets them be the two halves of one buffer.
-void swiglu_bwd(const Tensor& dout, const Tensor& gate, const Tensor& up, Tensor& dgate_out, Tensor& dup_out) {
+void swiglu_bwd(const Tensor& dout, const Tensor& gate, const Tensor& up, Tensor& dgate_out, Tensor& dup_out,
+                const c10::optional<Tensor>& row_limit) {
   c10::cuda::CUDAGuard guard(gate.device());
   check_bf16(dout, "dout");
   TORCH_CHECK(row_stride_2d(gate) == row_stride_2d(up) && row_stride_2d(dgate_out) == row_stride_2d(dup_out));
   check_rc(llmt_swiglu_bwd(dout.data_ptr(), gate.data_ptr(), up.data_ptr(), dgate_out.data_ptr(), dup_out.data_ptr(),
                            gate.size(0), (int)gate.size(1), gate.stride(0), row_stride_2d(dout), dgate_out.stride(0),
-                           cur_stream()),
+                           limit_ptr(row_limit), cur_stream()),
            "llmt_swiglu_bwd");
 }
 
@@ -613,8 +621,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
-  m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd, py::arg("gate"), py::arg("up"), py::arg("row_limit") = py::none());
+  m.def("swiglu_bwd", &swiglu_bwd, py::arg("dout"), py::arg("gate"), py::arg("up"), py::arg("dgate_out"), py::arg("dup_out"),
+        py::arg("row_limit") = py::none());
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
   m.def("adamw", &adamw);
   m.def("sqnorm", &sqnorm);

@@ -340,7 +340,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
 // ------------------------------------------------------------------------------------------ SwiGLU
 // Rows of `gate` and `up` may be strided (views into one [T, 2F] buffer); out/dgate/dup likewise.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
-                                  __nv_bfloat16* __restrict__ out, int64_t T, int F, int64_t ld_in, int64_t ld_out) {
+                                  __nv_bfloat16* __restrict__ out, int64_t T, int F, int64_t ld_in, int64_t ld_out,
+                                  const int* __restrict__ row_limit) {
+  // row_limit (optional, device memory): rows at or beyond *row_limit of a statically sized buffer hold nothing
+  if (row_limit != nullptr && *row_limit < T) T = *row_limit;
   const int64_t nvec = T * (F / 8);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / (F / 8);
@@ -356,7 +359,8 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const 
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gate,
                                   const __nv_bfloat16* __restrict__ up, __nv_bfloat16* __restrict__ dgate,
                                   __nv_bfloat16* __restrict__ dup, int64_t T, int F, int64_t ld_in, int64_t ld_dout,
-                                  int64_t ld_dg) {
+                                  int64_t ld_dg, const int* __restrict__ row_limit) {
+  if (row_limit != nullptr && *row_limit < T) T = *row_limit;
   const int64_t nvec = T * (F / 8);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / (F / 8);
@@ -622,20 +626,20 @@ extern "C" int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, cons
 }
 
 extern "C" int llmt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t T, int F, int64_t ld_in, int64_t ld_out,
-                               cudaStream_t st) {
+                               const int* row_limit, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8 || ld_in % 8 || ld_out % 8) return -10;
   swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up,
-                                                                 (__nv_bfloat16*)out, T, F, ld_in, ld_out);
+                                                                 (__nv_bfloat16*)out, T, F, ld_in, ld_out, row_limit);
   LLMT_CHECK_LAUNCH();
 }
 extern "C" int llmt_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int64_t T, int F,
-                               int64_t ld_in, int64_t ld_dout, int64_t ld_dg, cudaStream_t st) {
+                               int64_t ld_in, int64_t ld_dout, int64_t ld_dg, const int* row_limit, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8 || ld_in % 8 || ld_dout % 8 || ld_dg % 8) return -10;
   swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)gate,
                                                                  (const __nv_bfloat16*)up, (__nv_bfloat16*)dgate,
-                                                                 (__nv_bfloat16*)dup, T, F, ld_in, ld_dout, ld_dg);
+                                                                 (__nv_bfloat16*)dup, T, F, ld_in, ld_dout, ld_dg, row_limit);
   LLMT_CHECK_LAUNCH();
 }
 

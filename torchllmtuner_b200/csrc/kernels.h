@@ -41,9 +41,9 @@ int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, const void* x, 
                           float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, int T, int H, int HD,
                           cudaStream_t st);
 int llmt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t T, int F, int64_t ld_in, int64_t ld_out,
-                    cudaStream_t st);
+                    const int* row_limit, cudaStream_t st);
 int llmt_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int64_t T, int F,
-                    int64_t ld_in, int64_t ld_dout, int64_t ld_dg, cudaStream_t st);
+                    int64_t ld_in, int64_t ld_dout, int64_t ld_dg, const int* row_limit, cudaStream_t st);
 int llmt_ce_fwd_bwd(void* logits, const int64_t* labels, float* row_loss, float* row_lse, int rows, int V, int64_t ld,
                     const float* grad_scale_ptr, float grad_scale, int ignore_index, int write_grad, cudaStream_t st);
 int llmt_adamw(float* p32, void* p16, const void* g, int g_is_bf16, float* m, float* v, int64_t n, float lr, float b1,

@@ -134,7 +134,9 @@ class GroupedExperts(nn.Module):
             return out
         g = grouped_linear(rows, self.w1_EFD, seg_offsets)
         u = grouped_linear(rows, self.w3_EFD, seg_offsets)
-        return grouped_linear(ops.swiglu(g, u), self.w2_EDF, seg_offsets)
+        # rows past the last segment of a statically sized receive buffer hold nothing: the kernels skip them
+        limit = seg_offsets[-1:] if rows.is_cuda and seg_offsets.dtype == torch.int32 else None
+        return grouped_linear(ops.swiglu(g, u, limit), self.w2_EDF, seg_offsets)
 
 
 class LocalTokenDispatcher:

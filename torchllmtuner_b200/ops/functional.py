@@ -166,13 +166,13 @@ def qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps: float):
 # ----------------------------------------------------------------------------------------------- SwiGLU
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gate, up):
+    def forward(ctx, gate, up, row_limit):
         g2, u2 = _2d(gate), _2d(up)
         if g2.stride(0) != u2.stride(0):
             g2, u2 = g2.contiguous(), u2.contiguous()
         ctx.save_for_backward(g2, u2)
-        ctx.shape = gate.shape
-        return _ext().swiglu_fwd(g2, u2).reshape(gate.shape)
+        ctx.shape, ctx.row_limit = gate.shape, row_limit
+        return _ext().swiglu_fwd(g2, u2, row_limit).reshape(gate.shape)
 
     @staticmethod
     def backward(ctx, dout):
@@ -180,13 +180,15 @@ class _SwiGLU(torch.autograd.Function):
         d2 = _2d(dout)
         both = torch.empty(g2.shape[0], 2 * g2.shape[1], dtype=g2.dtype, device=g2.device)
         dg, du = both[:, :g2.shape[1]], both[:, g2.shape[1]:]
-        _ext().swiglu_bwd(d2, g2, u2, dg, du)
-        return dg.reshape(ctx.shape), du.reshape(ctx.shape)
+        _ext().swiglu_bwd(d2, g2, u2, dg, du, ctx.row_limit)
+        return dg.reshape(ctx.shape), du.reshape(ctx.shape), None
 
 
-def swiglu(gate, up):
+def swiglu(gate, up, row_limit=None):
+    """silu(gate) * up. `row_limit` (int32 device scalar) bounds the rows that are touched when the operands are
+    statically sized buffers whose live row count is only known on the device (expert-parallel receive buffers)."""
     if _use_cuda(gate) and gate.dtype == torch.bfloat16:
-        return _SwiGLU.apply(gate, up)
+        return _SwiGLU.apply(gate, up, row_limit)
     return ref.swiglu(gate, up)
 
 

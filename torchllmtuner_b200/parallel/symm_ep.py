@@ -34,7 +34,7 @@ def _align(n: int, a: int = 256) -> int:
 class PeerExchange:
     """Arena + flags of one EP group, sized for `max_copies` token copies per rank and rows of `hidden` bf16."""
 
-    def __init__(self, group, device, num_experts: int, max_copies: int, hidden: int, capacity_factor: float = 2.0):
+    def __init__(self, group, device, num_experts: int, max_copies: int, hidden: int, capacity_factor: float = 4.0):
         import torch.distributed._symmetric_memory as symm_mem
         from ..ops.cuda_ext import load
         self.ext = load()
@@ -94,7 +94,7 @@ class PeerExchange:
         self.count_epoch += 1
         seg, totals, send_off = self.ext.ep_exchange(flat, self.E, self.me, self._ptrs(self.off_tab), self._ptrs(self.off_cflag),
                                                      self.count_epoch, self.cap)
-        if self.E <= 256 and os.environ.get("LLMT_EP_FUSED_PLAN", "0") == "1":
+        if self.E <= 256 and os.environ.get("LLMT_EP_FUSED_PLAN", "1") == "1":
             drank, drow = self.ext.ep_plan(flat, self.E, self.R, send_off)
         else:
             counts = torch.bincount(flat, minlength=self.E)
@@ -182,7 +182,7 @@ class _PeerCombine(torch.autograd.Function):
 class PeerTokenDispatcher:
     """Drop-in for the all-to-all dispatcher (`dispatch` / `combine`) on CUDA bf16; falls back to `fallback` otherwise."""
 
-    def __init__(self, num_experts: int, group, ep_size: int, ep_rank: int, fallback, capacity_factor: float = 2.0):
+    def __init__(self, num_experts: int, group, ep_size: int, ep_rank: int, fallback, capacity_factor: float = 4.0):
         self.num_experts, self.group, self.ep_size, self.ep_rank = num_experts, group, ep_size, ep_rank
         self.local_experts = num_experts // ep_size
         self.fallback, self.capacity_factor = fallback, capacity_factor
