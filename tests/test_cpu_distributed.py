@@ -57,7 +57,7 @@ def test_cp2_matches_single_rank(flat):
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
 
 
-@pytest.mark.parametrize("schedule", ["GPipe", "1F1B"])
+@pytest.mark.parametrize("schedule", ["GPipe", "1F1B", "Interleaved1F1B"])
 def test_pipeline_two_stages_match_single_rank(schedule):
     from dist_cases import run_pp
     ref = run_ranks(1, base_flat(num_hidden_layers=4))
@@ -70,3 +70,42 @@ def test_stage_split_rule():
     assert split_layers(6, 2) == [(0, 3), (3, 6)]
     assert split_layers(7, 2) == [(0, 4), (4, 7)]          # the remainder goes to the first stage
     assert [b - a for a, b in split_layers(10, 4)] == [2, 3, 3, 2]
+
+
+def test_interleaved_schedule_orders_messages_consistently():
+    """Per direction of the pipeline, every rank's send order equals its neighbour's receive order, and a run with
+    asynchronous sends / blocking receives never waits on a message that was not sent (simulated, no processes)."""
+    from torchllmtuner_b200.experiments.pipeline_parallel.schedules import build_schedule, stages_per_rank
+    for name, pp, M in [("1f1b", 4, 8), ("interleaved1f1b", 2, 4), ("interleaved1f1b", 4, 8), ("interleaved1f1b", 3, 6)]:
+        V = stages_per_rank(name)
+        S = pp * V
+        acts = [build_schedule(name, r, pp, M) for r in range(pp)]
+        sends, recvs = {}, {}
+        for r in range(pp):
+            for kind, c, mb in acts[r]:
+                g = c * pp + r
+                if kind == "F":
+                    if g > 0:
+                        recvs.setdefault(((g - 1) % pp, r, "f"), []).append((g - 1, mb))
+                    if g < S - 1:
+                        sends.setdefault((r, (g + 1) % pp, "f"), []).append((g, mb))
+                else:
+                    if g < S - 1:
+                        recvs.setdefault(((g + 1) % pp, r, "b"), []).append((g + 1, mb))
+                    if g > 0:
+                        sends.setdefault((r, (g - 1) % pp, "b"), []).append((g, mb))
+        assert sends == recvs, (name, pp, M)
+        pos, done_f, done_b, moved = [0] * pp, set(), set(), True
+        while moved:
+            moved = False
+            for r in range(pp):
+                if pos[r] >= len(acts[r]):
+                    continue
+                kind, c, mb = acts[r][pos[r]]
+                g = c * pp + r
+                ready = (g == 0 or (g - 1, mb) in done_f) if kind == "F" else ((g, mb) in done_f and (g == S - 1 or (g + 1, mb) in done_b))
+                if ready:
+                    (done_f if kind == "F" else done_b).add((g, mb))
+                    pos[r] += 1
+                    moved = True
+        assert all(pos[r] == len(acts[r]) for r in range(pp)) and len(done_b) == S * M, (name, pp, M)
