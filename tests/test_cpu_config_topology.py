@@ -177,3 +177,27 @@ def test_runtime_validator_reports_a_working_cpu_path(monkeypatch):
     from torchllmtuner_b200.utils.validate_runtime import collect
     rep = collect()
     assert "train_step_loss" in rep and rep["distributed"]["gloo"] and "extension" in rep
+
+
+def test_compatibility_matrix_entries_reject_before_any_mutation():
+    from types import SimpleNamespace as NS
+
+    from torchllmtuner_b200.parallel.compatibility import ENTRIES, check_compatibility
+    cfg = LLMTunerConfig()
+
+    def topo(**kw):
+        d = dict(tp=1, ep=1, cp_ulysses=1, cp_kv=1, kcp=1, pp=1)
+        d.update(kw)
+        return NS(**d)
+    dense = NS(num_experts=0, num_attention_heads=8, num_key_value_heads=2, model_type="qwen3", tie_word_embeddings=False)
+    moe = NS(num_experts=6, num_attention_heads=8, num_key_value_heads=4, model_type="qwen3_moe", tie_word_embeddings=False,
+             shared_expert_intermediate_size=0)
+    check_compatibility(cfg, topo(), dense)                                   # the plain case passes
+    cases = {"ep_without_experts": (topo(ep=2), dense), "ep_divides_experts": (topo(ep=4), moe),
+             "tp_divides_heads": (topo(tp=4), dense), "ulysses_divides_heads": (topo(cp_ulysses=4), dense),
+             "kcp_needs_delta_attention": (topo(kcp=2), dense)}
+    for name, (t, m) in cases.items():
+        with pytest.raises(UnsupportedCombinationError) as e:
+            check_compatibility(cfg, t, m)
+        assert f"[{name}]" in str(e.value), (name, str(e.value))
+    assert {n for n, _, _ in ENTRIES} >= set(cases)
