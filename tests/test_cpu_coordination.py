@@ -142,7 +142,51 @@ def _case_rank_leaves_between_steps(rank, world):
         return f"timeout after {time.time() - t0:.1f}s: {type(e).__name__}"
 
 
+def _case_vocab_parallel_loss_and_embedding(rank, world):
+    """Vocab-sharded logits: loss, gradient and entropy equal the full-vocabulary statement; the vocab-parallel embedding
+    returns this rank's token shard of the full lookup."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from torchllmtuner_b200.components.loss import LossParallelCrossEntropy, vocab_parallel_entropy
+    from torchllmtuner_b200.models.common import Embedding
+    from torchllmtuner_b200.parallel.tensor_parallel import VocabParallelEmbedding
+    from torchllmtuner_b200.utils.vocabulary import vocab_shard_bounds
+    torch.manual_seed(5)
+    T, V, D = 24, 37, 8                                     # V does not divide evenly
+    logits = torch.randn(T, V, dtype=torch.float64)
+    targets = torch.randint(0, V, (T,))
+    targets[3] = -100
+    lo, hi = vocab_shard_bounds(V, world, rank)
+    shard = logits[:, lo:hi].clone().requires_grad_()
+    loss = LossParallelCrossEntropy.apply(shard, targets, dist.group.WORLD, lo)
+    loss.backward()
+    full = logits.clone().requires_grad_()
+    ref = F.cross_entropy(full, targets, ignore_index=-100, reduction="sum")
+    ref.backward()
+    e1 = abs(float(loss) - float(ref))
+    e2 = float((shard.grad - full.grad[:, lo:hi]).abs().max())
+    ent = vocab_parallel_entropy(logits[:, lo:hi], dist.group.WORLD)
+    p = torch.softmax(logits, -1)
+    e3 = float((ent - (-(p * torch.log(p)).sum(-1))).abs().max())
+    # embedding: same table on every rank, each keeps rows [lo, hi); tokens arrive sequence-sharded
+    table = Embedding(V, D, dtype=torch.float32)
+    with torch.no_grad():
+        table.weight.copy_(torch.arange(V * D, dtype=torch.float32).view(V, D) / 100.0)
+    vpe = VocabParallelEmbedding(table, rank, world, dist.group.WORLD)
+    ids = torch.randint(0, V, (T,))
+    mine = ids[rank * (T // world):(rank + 1) * (T // world)]
+    out = vpe(mine)
+    e4 = float((out - table.weight[mine]).abs().max())
+    return f"{e1:.2e},{e2:.2e},{e3:.2e},{e4:.2e}"
+
+
 # ---------------------------------------------------------------------------------------------- tests
+def test_vocab_parallel_cross_entropy_entropy_and_embedding_match_the_full_vocabulary():
+    for r in _spawn(_case_vocab_parallel_loss_and_embedding, 2):
+        assert r.count(",") == 3, r
+        assert all(float(x) < 1e-5 for x in r.split(",")), r
+
+
 def test_rank_leaving_between_steps_ends_the_next_collective_with_an_error():
     res = _spawn(_case_rank_leaves_between_steps, 2)
     assert res[1] == "left" and res[0].startswith("timeout after"), res
