@@ -48,6 +48,15 @@ def test_ep2_matches_single_rank():
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
 
 
+def test_tp2_moe_matches_single_rank():
+    """MoE block under tensor parallelism: rows gathered in, experts' intermediate dimension sharded, partial sums
+    reduce-scattered out."""
+    ref = run_ranks(1, base_flat(model_name_or_path="qwen3_moe"), arch=MOE)
+    got = run_ranks(2, base_flat(model_name_or_path="qwen3_moe", tensor_parallel_size=2, data_parallel_shard_size=1), arch=MOE)
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
 @pytest.mark.parametrize("flat", [dict(context_parallel_ulysses_size=2), dict(context_parallel_kv_allgather_size=2),
                                   dict(context_parallel_kv_allgather_size=2, context_parallel_load_balancer="headtail")])
 def test_cp2_matches_single_rank(flat):

@@ -34,6 +34,7 @@ MOE = dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128)
     ("cp_ulysses2", dict(context_parallel_ulysses_size=2, data_parallel_shard_size=1), None),
     ("cp_kv2_headtail", dict(context_parallel_kv_allgather_size=2, context_parallel_load_balancer="headtail", data_parallel_shard_size=1), None),
     ("ep2", dict(model_name_or_path="qwen3_moe", expert_parallel_size=2, data_parallel_shard_size=2), MOE),
+    ("tp2_moe", dict(model_name_or_path="qwen3_moe", tensor_parallel_size=2, data_parallel_shard_size=1), MOE),
 ])
 def test_parallel_modes_gpu_match_single_gpu(name, flat, arch):
     _need(2)

@@ -124,6 +124,44 @@ class FusedTPComm:
         return self.rs_finish(token, part, a, w, b_mn, False, residual)
 
 
+    # ------------------------------------------------------------------ row collectives without a GEMM to ride on
+    def all_gather_rows(self, x_shard: torch.Tensor) -> torch.Tensor:
+        """[T/R, D] -> [T, D] by peer loads (the copy kernel of the FSDP path), same slots, flags and epochs as `ag_gemm`."""
+        from .symm import COPY, make_side_job
+        cr, K = x_shard.shape
+        i, e, foff = self._slot(AG)
+        self._view(self.off_chunk[i], cr, K).copy_(x_shard)
+        self.ext.signal_peers([b + foff for b in self.peer_base], self.rank, e)
+        self.ext.wait_flags(self.base + foff, self.world, e, 7500 + i)
+        out = torch.empty(cr * self.world, K, dtype=torch.bfloat16, device=self.device)
+        nbytes = cr * K * 2
+        for k in range(self.world):
+            p = (self.rank + k) % self.world
+            job = dict(kind=COPY, src=[self.peer_base[p] + self.off_chunk[i]], dst=out.data_ptr() + p * nbytes, n=nbytes,
+                       accumulate=False, wait_flags=0, n_wait=0, wait_value=0)
+            self.ext.side_job(make_side_job(self.ext, job), 64)
+        self.ext.signal_peers([b + foff + 4 * self.world for b in self.peer_base], self.rank, e)      # done[rank] everywhere
+        return out
+
+    def reduce_scatter_rows(self, partial: torch.Tensor) -> torch.Tensor:
+        """[T, N] partial sums -> [T/R, N]: every rank publishes its partial, then sums its own chunk over all ranks in
+        fp32 in rank order with peer loads (the reduce kernel of the FSDP path)."""
+        from .symm import REDUCE, make_side_job
+        rows, N = partial.shape
+        cr = rows // self.world
+        i, e, foff = self._slot(RS)
+        self._view(self.off_part[i], rows, N).copy_(partial)
+        self.ext.signal_peers([b + foff for b in self.peer_base], self.rank, e)                       # ready[rank] everywhere
+        self.ext.wait_flags(self.base + foff, self.world, e, 7600 + i)
+        n = cr * N
+        acc = self.acc[:n]
+        job = dict(kind=REDUCE, src=[b + self.off_part[i] + self.rank * n * 2 for b in self.peer_base], dst=acc.data_ptr(), n=n,
+                   accumulate=False, wait_flags=0, n_wait=0, wait_value=0)
+        self.ext.side_job(make_side_job(self.ext, job), 128)
+        self.ext.signal_peers([b + foff + 4 * self.world for b in self.peer_base], self.rank, e)      # done[rank] everywhere
+        return acc.view(cr, N).to(torch.bfloat16)
+
+
 _COMMS: dict = {}
 
 
@@ -199,3 +237,29 @@ class LinearReduceScatter(torch.autograd.Function):
         dx, dy = comm.ag_gemm(dy_shard.contiguous(), w, b_mn=True)             # gather(dy) [T, N] @ W [N, K/R]
         dw = _wgrad(dy, x, w) if ctx.needs_input_grad[2] else None
         return None, (dx if ctx.needs_input_grad[1] else None), dw
+
+
+class PeerAllGatherRows(torch.autograd.Function):
+    """[T/R, D] -> [T, D] over peer memory; backward reduce-scatters the gradient the same way."""
+
+    @staticmethod
+    def forward(ctx, comm: FusedTPComm, x):
+        ctx.comm = comm
+        return comm.all_gather_rows(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return None, ctx.comm.reduce_scatter_rows(g.contiguous())
+
+
+class PeerReduceScatterRows(torch.autograd.Function):
+    """[T, D] partial sums -> [T/R, D] over peer memory; backward all-gathers."""
+
+    @staticmethod
+    def forward(ctx, comm: FusedTPComm, x):
+        ctx.comm = comm
+        return comm.reduce_scatter_rows(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return None, ctx.comm.all_gather_rows(g.contiguous())

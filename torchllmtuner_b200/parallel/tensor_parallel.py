@@ -17,6 +17,7 @@ and, on CUDA with peer access, staged P2P copies driven by the comm warps of the
 """
 from __future__ import annotations
 
+import os
 import re
 
 import torch
@@ -185,6 +186,11 @@ class TPMoeSequenceBoundary(nn.Module):
         self.inner, self.group = inner, group
 
     def forward(self, x):
+        if x.dim() == 2 and os.environ.get("LLMT_PEER_TP_MOE", "0") == "1":
+            comm = _comm_for(self.group, x.shape[0], x.shape[1], x)
+            if comm is not None and x.shape[1] % 8 == 0 and (x.shape[0] * x.shape[1]) % 8 == 0:
+                from .symm_tp import PeerAllGatherRows, PeerReduceScatterRows
+                return PeerReduceScatterRows.apply(comm, self.inner(PeerAllGatherRows.apply(comm, x)))
         return reduce_scatter_along(self.inner(all_gather_along(x, self.group)), self.group)
 
     def __getattr__(self, name):
