@@ -147,3 +147,18 @@ def test_cli_main_runs_a_tiny_job_and_seed_checkpoint(tmp_path, monkeypatch):
     assert os.path.exists(tmp_path / "a" / "checkpoint" / "step-3" / ".metadata")          # the last step is always saved
     assert main(flags + ["--dump_folder", str(tmp_path / "b"), "--create_seed_checkpoint", "true"]) == 0
     assert os.path.exists(tmp_path / "b" / "checkpoint" / "step-0" / ".metadata")
+
+
+def test_aux_loss_gradient_survives_full_activation_checkpointing():
+    """The load-balance loss of MoE blocks must pull on the router under recomputation exactly as it does without it."""
+    def cfg(ac):
+        c = tiny_config(model_name_or_path="qwen3_moe", steps=4, activation_checkpoint_mode=ac, router_aux_loss_coef=0.5)
+        c.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, router_aux_loss_coef=0.5)
+        return c
+    a, b = run(cfg("none")), run(cfg("full"))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5, (a, b)
+    # and the aux term really matters for the trajectory (a coefficient of zero gives different losses after the first update)
+    c0 = tiny_config(model_name_or_path="qwen3_moe", steps=4, activation_checkpoint_mode="full")
+    c0.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
+    z = run(c0)
+    assert max(abs(x - y) for x, y in zip(b[1:], z[1:])) > 1e-6, (b, z)

@@ -444,7 +444,14 @@ class _CheckpointedBlock(torch.autograd.Function):
         xd = x.detach().requires_grad_(True)
         with torch.enable_grad():
             out = ctx.layer(xd, ctx.fctx)
-        torch.autograd.backward(out, dy)
+        # Auxiliary (load-balance) losses of MoE blocks: the value that entered the step's loss came from the first,
+        # graph-free forward, so their gradient is injected here, from the replayed forward (d loss / d aux = 1).
+        aux = [m.aux_loss for m in ctx.layer.modules() if getattr(m, "aux_loss", None) is not None and m.aux_loss.requires_grad]
+        if aux:
+            total_aux = aux[0] if len(aux) == 1 else torch.stack(aux).sum()
+            torch.autograd.backward([out, total_aux], [dy, torch.ones_like(total_aux)])
+        else:
+            torch.autograd.backward(out, dy)
         for u in rt._units(i):
             rt.reduce_grads(u)
             rt.reshard(u)
