@@ -162,3 +162,26 @@ def test_aux_loss_gradient_survives_full_activation_checkpointing():
     c0.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
     z = run(c0)
     assert max(abs(x - y) for x, y in zip(b[1:], z[1:])) > 1e-6, (b, z)
+
+
+def test_region_checkpointing_recomputes_exactly_the_named_blocks():
+    """`region` mode: blocks whose name matches `recompute_regions` run their forward twice per step (once more in
+    backward), the others once; the losses are those of the run without checkpointing."""
+    cfg = tiny_config(steps=2, num_hidden_layers=4, activation_checkpoint_mode="region")
+    cfg.training.region_ac.recompute_regions = [r"layers\.(1|3)$"]
+    tr = Trainer(cfg)
+    calls = {i: 0 for i in range(4)}
+    layers = tr.model.model.layers
+    for i in range(4):
+        layer = layers[i] if not isinstance(layers, torch.nn.ModuleDict) else layers[str(i)]
+        layer.register_forward_hook(lambda m, a_, o, i=i: calls.__setitem__(i, calls[i] + 1))
+    a = []
+    try:
+        for _ in range(2):
+            tr.dataloader.cursor = 0
+            a.append(tr.train_step().loss)
+    finally:
+        tr.close()
+    assert calls == {0: 2, 1: 4, 2: 2, 3: 4}, calls
+    b = run(tiny_config(steps=2, num_hidden_layers=4))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5

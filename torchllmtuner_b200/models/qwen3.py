@@ -268,7 +268,9 @@ class Qwen3ForCausalLM(nn.Module):
         if self.block_runner is not None:
             return self.block_runner(i, layer, x, ctx)
         ac = self.activation_checkpoint
-        use_ac = self.training and torch.is_grad_enabled() and (ac == "full" or (ac == "selective" and i % self.ac_save_every != 0))
+        mask = getattr(self, "ac_block_mask", None)
+        recompute = bool(mask[i]) if mask is not None and i < len(mask) else i % self.ac_save_every != 0
+        use_ac = self.training and torch.is_grad_enabled() and (ac == "full" or (ac == "selective" and recompute))
         if use_ac:
             return checkpoint(layer, x, ctx, use_reentrant=False)
         return layer(x, ctx)

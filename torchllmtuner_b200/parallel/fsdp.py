@@ -359,9 +359,17 @@ class FSDPRuntime:
         for u in self._units(i):
             self.unshard(u, wait=False)
 
+    def _recomputes(self, i: int) -> bool:
+        """Selective modes: the per-block mask of the region mode wins, else every `ac_save_every`-th block keeps its
+        activations."""
+        mask = getattr(self.model, "ac_block_mask", None)
+        if mask is not None and i < len(mask):
+            return bool(mask[i])
+        return i % self.ac_save_every != 0
+
     def run_block(self, i: int, layer: nn.Module, x: torch.Tensor, ctx) -> torch.Tensor:
         grad_mode = self.model.training and torch.is_grad_enabled()
-        ac = grad_mode and (self.ac_mode == "full" or (self.ac_mode == "selective" and i % self.ac_save_every != 0))
+        ac = grad_mode and (self.ac_mode == "full" or (self.ac_mode == "selective" and self._recomputes(i)))
         if ac:
             return _CheckpointedBlock.apply(x, self, i, layer, ctx)
         for u in self._units(i):
