@@ -201,3 +201,30 @@ def test_compatibility_matrix_entries_reject_before_any_mutation():
             check_compatibility(cfg, t, m)
         assert f"[{name}]" in str(e.value), (name, str(e.value))
     assert {n for n, _, _ in ENTRIES} >= set(cases)
+
+
+def test_inert_flags_are_reported_and_every_other_flag_is_read_somewhere():
+    """A flag is either read by the package or listed as inert with a reason; nothing is silently ignored."""
+    import dataclasses
+    import os
+    import re
+
+    import torchllmtuner_b200.config.training_config as tc
+    from torchllmtuner_b200.config.cli_config import PARSER_GROUPS
+    from torchllmtuner_b200.config.inert_fields import INERT_FIELDS, inert_fields_set
+    cfg = LLMTunerConfig()
+    assert inert_fields_set(cfg) == []
+    cfg.apply_flat(dict(norm_backend="other", sharded_expert_parallel=True))
+    assert {n for n, _ in inert_fields_set(cfg)} == {"norm_backend", "sharded_expert_parallel"}
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = ""
+    for d, _, files in os.walk(os.path.join(root, "torchllmtuner_b200")):
+        if "__pycache__" in d:
+            continue
+        for f in files:
+            if f.endswith(".py") and f != "inert_fields.py" and not (d.endswith("config") and f.endswith("_config.py") and f != "llmtuner_config.py"):
+                src += open(os.path.join(d, f)).read()
+    groups = list(PARSER_GROUPS) + [o for o in vars(tc).values() if dataclasses.is_dataclass(o) and isinstance(o, type)]
+    silent = [f"{g.__name__}.{f.name}" for g in dict.fromkeys(groups) for f in dataclasses.fields(g)
+              if f.name not in INERT_FIELDS and not re.search(r"\b" + re.escape(f.name) + r"\b", src)]
+    assert silent == [], silent

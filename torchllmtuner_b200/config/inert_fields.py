@@ -1,0 +1,66 @@
+"""Flags that are accepted so that a command line written for the reference still parses, but that select something this
+platform does not have (another vendor's back end, a tracing compiler, an optional third-party library). Setting one of
+them to a non-default value has no effect; the trainer says so once at start-up instead of staying silent."""
+from __future__ import annotations
+
+import dataclasses
+
+INERT_FIELDS: dict[str, str] = {
+    "norm_backend": "RMSNorm always runs the in-tree sm_100a kernel (CUDA) or the PyTorch statement (CPU)",
+    "attention_backend": "attention always runs the in-tree tcgen05 kernel (CUDA) or the PyTorch statement (CPU)",
+    "linear_attention_backend": "delta-attention mixers use the in-tree PyTorch statement",
+    "router_compute_dtype": "router logits and scores are always fp32",
+    "rotary_init_device": "rotary tables are built on the compute device",
+    "rotary_compute_dtype": "rotary tables are always fp32",
+    "rotary_cache_dtype": "rotary tables are always fp32",
+    "fsdp_cpu_offload_pin_memory": "host-resident optimizer state is always pinned",
+    "fsdp_apply_modules": "sharding units are the decoder blocks plus embedding / head; user patterns are not applied",
+    "enable_fsdp_symm_mem": "the native FSDP runtime always uses its own symmetric arena on CUDA (LLMT_DISABLE_FUSED_COMM=1 turns it off)",
+    "fsdp_symm_mem_scope": "see enable_fsdp_symm_mem",
+    "fsdp_expert_reduce_layout": "expert gradients are reduced in storage order",
+    "fsdp_expert_reduce_workspace_limit_bytes": "see fsdp_expert_reduce_layout",
+    "tp_sequence_modules": "sequence boundaries are placed by the model's TP plan",
+    "context_parallel_strategy": "the strategy follows from which context-parallel degree is > 1",
+    "ep_torchao_pad_multiple": "the torchao dispatcher is not available; segments are padded to 128 rows",
+    "swap_prefetch": "host-resident moments are streamed in fixed slices without a prefetch queue",
+    "swap_memory_fraction": "the slice size comes from swap_max_device_bytes",
+    "swap_max_host_bytes": "pinned host memory for the moments is not capped",
+    "compute_sharding_by_fqn": "Muon owners are balanced automatically",
+    "bucket_configs": "Muon redistribution uses one bucket per matrix",
+    "sharded_expert_parallel": "checkpoints always store global-coordinate pieces, which resume at any EP degree",
+    "sharded_tensor_parallel": "checkpoints always store global-coordinate pieces, which resume at any TP degree",
+    "global_context_rows": "rows are assigned to data-parallel ranks by contiguous slices",
+    "streaming_shuffle_buffer_size": "only used by `datasets.sources.StreamingSource` when a recipe builds one",
+    "mm_pad_token": "multimodal padding uses the tokenizer's pad id",
+    "disable_color_printing": "console output is never coloured",
+    "npu_profiler_level": "no NPU profiler on this platform",
+    "profiler_skip_first_wait": "the profiler schedule has no separate first-cycle wait",
+    "enable_async_tensor_parallel": "TP collectives are fused into the GEMM kernels, there is no compiler pass to enable",
+    "buffer_patterns": "EMA tracks parameters only",
+    "determinism_check": "activation recomputation is bitwise deterministic by construction (same kernels, same order)",
+    "grad_norm_precision": "the gradient norm is always accumulated in fp32 over the fp32 gradient shards",
+    "force_recompute_mm_shapes_by_fqns": "selective checkpointing works on whole blocks",
+}
+
+
+def _walk(obj, prefix=""):
+    if not dataclasses.is_dataclass(obj):
+        return
+    for f in dataclasses.fields(obj):
+        v = getattr(obj, f.name)
+        if dataclasses.is_dataclass(v):
+            yield from _walk(v, prefix + f.name + ".")
+        else:
+            yield f, v
+
+
+def inert_fields_set(config) -> list[tuple[str, str]]:
+    """(field, reason) for every inert field whose value differs from its default."""
+    out = []
+    for f, v in _walk(config):
+        if f.name not in INERT_FIELDS:
+            continue
+        default = f.default if f.default is not dataclasses.MISSING else (f.default_factory() if f.default_factory is not dataclasses.MISSING else None)
+        if v != default:
+            out.append((f.name, INERT_FIELDS[f.name]))
+    return out

@@ -129,6 +129,11 @@ class FSDPRuntime:
         self.param_dtype = param_dtype
         self.reduce_dtype = _dtype(fsdp_config.fsdp_reduce_dtype)
         self.ac_mode, self.ac_save_every = ac_mode, ac_save_every
+        for name in ("fsdp_forward_prefetch_count", "fsdp_backward_prefetch_count"):
+            if getattr(fsdp_config, name, 0) > 1:
+                from ..errors import UnsupportedCombinationError
+                raise UnsupportedCombinationError(f"{name} > 1: the runtime rotates two gather slots, so exactly one unit is "
+                                                  "prefetched ahead of the one that computes (0 and 1 both select that)")
         self.is_cuda = torch.device(device).type == "cuda"
         self.group = topo.get_group("dp_shard_cp")
         self.world = topo.size("dp_shard_cp")

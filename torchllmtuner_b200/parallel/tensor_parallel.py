@@ -274,6 +274,8 @@ def apply_tp(model, topo, tp_config) -> dict:
     group, rank, size = topo.get_group("tp"), topo.coord("tp"), topo.tp
     if group is None:
         raise ConfigError("tensor parallelism needs an initialised process group")
+    if not tp_config.enable_sequence_parallel:
+        raise ConfigError("tensor parallelism is sequence-parallel here: enable_sequence_parallel must stay True")
     plan = resolve_tp_plan(model, tp_config)
     bound = BoundDecoder(model.decoder_structure, model)
     applied = {}
