@@ -122,3 +122,27 @@ def test_hf_disk_source_round_trip(tmp_path):
     ds.save_to_disk(str(tmp_path / "d"))
     src = HuggingFaceDiskSource(str(tmp_path / "d"))
     assert len(src) == 7 and src[3]["text"] == "row 3"
+
+
+def test_huggingface_tokenizer_special_tokens_and_chat_template(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    import json
+
+    from tokenizers import models, pre_tokenizers
+    from torchllmtuner_b200.components.tokenizer.huggingface import HuggingFaceTokenizer
+    vocab = {"<s>": 0, "</s>": 1, "<unk>": 2, "hello": 3, "world": 4, "user": 5, "assistant": 6, ":": 7}
+    tok = tokenizers.Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    d = tmp_path / "tok"
+    d.mkdir()
+    tok.save(str(d / "tokenizer.json"))
+    (d / "tokenizer_config.json").write_text(json.dumps({
+        "bos_token": "<s>", "eos_token": {"content": "</s>"},
+        "chat_template": "{% for m in messages %}{{ m['role'] }} : {{ m['content'] }} {{ eos_token }}{% endfor %}"}))
+    t = HuggingFaceTokenizer(str(d))
+    assert (t.bos_id, t.eos_id, t.pad_id, t.vocab_size) == (0, 1, 1, 8)
+    assert t.encode("hello world", add_bos=True, add_eos=True) == [0, 3, 4, 1]
+    assert t.decode([3, 4]) == "hello world"
+    text = t.apply_chat_template([{"role": "user", "content": "hello"}, {"role": "assistant", "content": "world"}])
+    assert text.replace("</s>", " </s> ").split() == ["user", ":", "hello", "</s>", "assistant", ":", "world", "</s>"]
+    assert t.identity().startswith("hf:") and t.identity() == HuggingFaceTokenizer(str(d)).identity()
