@@ -185,3 +185,17 @@ def test_region_checkpointing_recomputes_exactly_the_named_blocks():
     assert calls == {0: 2, 1: 4, 2: 2, 3: 4}, calls
     b = run(tiny_config(steps=2, num_hidden_layers=4))
     assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
+
+
+def test_tensorboard_sink_receives_logged_steps(tmp_path):
+    import glob
+    import os
+    cfg = tiny_config(steps=2, log_freq=1, dump_folder=str(tmp_path), enable_tensorboard=True)
+    tr = Trainer(cfg)
+    try:
+        tr.train()
+    finally:
+        tr.close()
+    folder = os.path.join(str(tmp_path), cfg.training.metrics_config.save_tb_folder)
+    files = glob.glob(os.path.join(folder, "events.out.tfevents.*")) + glob.glob(os.path.join(folder, "metrics.jsonl"))
+    assert files and os.path.getsize(files[0]) > 0, os.listdir(str(tmp_path))
