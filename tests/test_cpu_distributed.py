@@ -118,3 +118,15 @@ def test_interleaved_schedule_orders_messages_consistently():
                     pos[r] += 1
                     moved = True
         assert all(pos[r] == len(acts[r]) for r in range(pp)) and len(done_b) == S * M, (name, pp, M)
+
+
+@pytest.mark.parametrize("lb", [None, "headtail"])
+def test_hybrid_context_parallel_kv_times_ulysses_matches_single_rank(lb):
+    """cp = cp_kv x cp_ulysses: heads exchanged inside the ulysses axis, keys / values gathered over the other one."""
+    flat = dict(context_parallel_kv_allgather_size=2, context_parallel_ulysses_size=2, data_parallel_shard_size=1)
+    if lb:
+        flat["context_parallel_load_balancer"] = lb
+    ref = run_ranks(1, base_flat())
+    got = run_ranks(4, base_flat(**flat))
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)

@@ -87,6 +87,14 @@ class ContextParallelDriver:
         self.load_balancer = cp_config.context_parallel_load_balancer if topo.cp_kv > 1 else None
         self.group = topo.get_group("cp")
         self.size, self.rank = topo.cp, topo.coord("cp")
+        if self.strategy == "hybrid":
+            # key/value axis outside, ulysses axis inside: heads are exchanged among the ulysses ranks first, which
+            # turns their rows into the rows of the key/value level; keys and values are then gathered over that axis
+            self.group_ul, self.group_kv = topo.get_group("cp_ulysses"), topo.get_group("cp_kv")
+            self.size_kv, self.rank_kv = topo.cp_kv, topo.coord("cp_kv")
+        else:
+            self.group_ul = self.group_kv = self.group
+            self.size_kv, self.rank_kv = self.size, self.rank
         self._mb = None
 
     # ------------------------------------------------------------------ per micro-batch tables
@@ -99,8 +107,8 @@ class ContextParallelDriver:
         if self.strategy == "ulysses":
             mb["meta"] = AttnMeta.build(gcu, causal=True, device=dev)
         else:
-            # local spans of every sequence, in local row order
-            R, r = self.size, self.rank
+            # local spans of every sequence, in local row order (of the key/value level in the hybrid strategy)
+            R, r = self.size_kv, self.rank_kv
             spans = headtail_chunks(S, R, r) if self.load_balancer == "headtail" else [contiguous_chunk(S, R, r)]
             pieces, local = [], 0
             for b in range(B):
@@ -155,16 +163,16 @@ class ContextParallelDriver:
             if B > 1:
                 o = o.index_select(0, inv)
             return cp_all_to_all(o, self.group, False)
-        kg = _AllGatherRowsCP.apply(k, self.group, mb["perm"])
-        vg = _AllGatherRowsCP.apply(v, self.group, mb["perm"])
-        return ops.attention(q, kg, vg, mb["meta"], scale)
+        if self.strategy == "hybrid":
+            q, k, v = (cp_all_to_all(t, self.group_ul, True) for t in (q, k, v))
+        kg = _AllGatherRowsCP.apply(k, self.group_kv, mb["perm"])
+        vg = _AllGatherRowsCP.apply(v, self.group_kv, mb["perm"])
+        o = ops.attention(q, kg, vg, mb["meta"], scale)
+        return cp_all_to_all(o, self.group_ul, False) if self.strategy == "hybrid" else o
 
 
 def apply_cp(model, topo, cp_config) -> ContextParallelDriver:
     if topo.kcp > 1:
         from ..errors import UnsupportedCombinationError
         raise UnsupportedCombinationError("kcp context parallelism applies to delta-attention models only")
-    if topo.cp_ulysses > 1 and topo.cp_kv > 1:
-        from ..errors import UnsupportedCombinationError
-        raise UnsupportedCombinationError("combining the ulysses and kv_allgather axes in one run is not supported yet")
     return ContextParallelDriver(topo, cp_config)

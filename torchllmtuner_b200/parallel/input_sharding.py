@@ -49,7 +49,18 @@ def shard_model_inputs(inputs: dict, parallel_dims) -> dict:
     B, S = inputs["batch"], inputs["seq"]
     rows = torch.arange(B * S)
     if cp > 1:
-        rows = cp_row_index(B, S, cp, int(parallel_dims["cp_rank"]), parallel_dims.get("load_balancer"))
+        kv, ul = int(parallel_dims.get("cp_kv", 1)), int(parallel_dims.get("cp_ulysses", 1))
+        if kv > 1 and ul > 1:
+            # two levels: the key/value axis cuts the sequences (optionally head-tail balanced); the ulysses axis cuts each
+            # rank's rows of that level into contiguous parts, so that its all-to-all restores exactly those rows
+            rows_kv = cp_row_index(B, S, kv, int(parallel_dims["cp_kv_rank"]), parallel_dims.get("load_balancer"))
+            if rows_kv.numel() % ul:
+                raise ConfigError(f"{rows_kv.numel()} rows per key/value rank are not divisible by the ulysses degree {ul}")
+            n = rows_kv.numel() // ul
+            u = int(parallel_dims["cp_ulysses_rank"])
+            rows = rows_kv[u * n:(u + 1) * n]
+        else:
+            rows = cp_row_index(B, S, cp, int(parallel_dims["cp_rank"]), parallel_dims.get("load_balancer"))
         out["cp_rows"] = rows                      # which global rows this rank's queries are
         out["global_cu_seqlens"] = inputs["cu_seqlens"]
         out["global_rows"] = B * S

@@ -28,7 +28,8 @@ class TrainingEngine:
         if t.cp == 1 and t.tp == 1:
             return None
         lb = getattr(self.asm.cp_driver, "load_balancer", None)
-        return {"cp": t.cp, "cp_rank": t.coord("cp"), "tp": t.tp, "tp_rank": t.coord("tp"), "load_balancer": lb}
+        return {"cp": t.cp, "cp_rank": t.coord("cp"), "tp": t.tp, "tp_rank": t.coord("tp"), "load_balancer": lb,
+                "cp_kv": t.cp_kv, "cp_ulysses": t.cp_ulysses, "cp_kv_rank": t.coord("cp_kv"), "cp_ulysses_rank": t.coord("cp_ulysses")}
 
     def forward_backward(self, batch: dict, global_valid_tokens: torch.Tensor, is_last_microbatch: bool = True) -> torch.Tensor:
         """Returns the un-normalised loss sum of this micro-batch (device scalar, detached)."""
