@@ -186,7 +186,7 @@ class TPMoeSequenceBoundary(nn.Module):
         self.inner, self.group = inner, group
 
     def forward(self, x):
-        if x.dim() == 2 and os.environ.get("LLMT_PEER_TP_MOE", "0") == "1":
+        if x.dim() == 2 and os.environ.get("LLMT_PEER_TP_MOE", "1") == "1":
             comm = _comm_for(self.group, x.shape[0], x.shape[1], x)
             if comm is not None and x.shape[1] % 8 == 0 and (x.shape[0] * x.shape[1]) % 8 == 0:
                 from .symm_tp import PeerAllGatherRows, PeerReduceScatterRows
