@@ -199,3 +199,20 @@ def test_tensorboard_sink_receives_logged_steps(tmp_path):
     folder = os.path.join(str(tmp_path), cfg.training.metrics_config.save_tb_folder)
     files = glob.glob(os.path.join(folder, "events.out.tfevents.*")) + glob.glob(os.path.join(folder, "metrics.jsonl"))
     assert files and os.path.getsize(files[0]) > 0, os.listdir(str(tmp_path))
+
+
+def test_validation_preserves_rng_and_training_mode_and_runs_on_schedule():
+    from torchllmtuner_b200.config.training_config import ValidationConfig
+    cfg = tiny_config(steps=4, log_freq=100)
+    cfg.training.validation_config = ValidationConfig(freq=2, steps=2)
+    tr = Trainer(cfg)
+    try:
+        state = torch.get_rng_state()
+        v = tr.validate()
+        assert torch.equal(state, torch.get_rng_state()) and tr.model.training
+        assert 0.0 < v < 20.0
+        tr.validator.history.clear()
+        tr.train()
+        assert [s for s, _ in tr.validator.history] == [1, 2, 4], tr.validator.history
+    finally:
+        tr.close()
