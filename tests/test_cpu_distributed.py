@@ -130,3 +130,10 @@ def test_hybrid_context_parallel_kv_times_ulysses_matches_single_rank(lb):
     got = run_ranks(4, base_flat(**flat))
     _close(ref["loss"], got["loss"], 5e-5)
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
+def test_dist_muon_two_ranks_match_single_rank():
+    """Muon needs whole matrices: owners gather their gradients, orthogonalise, and scatter the updates back."""
+    ref = run_ranks(1, base_flat(optimizer_type="DistMuon", learning_rate=2e-2))
+    got = run_ranks(2, base_flat(optimizer_type="DistMuon", learning_rate=2e-2, data_parallel_shard_size=2))
+    _close(ref["loss"], got["loss"], 2e-3)

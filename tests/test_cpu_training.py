@@ -216,3 +216,21 @@ def test_validation_preserves_rng_and_training_mode_and_runs_on_schedule():
         assert [s for s, _ in tr.validator.history] == [1, 2, 4], tr.validator.history
     finally:
         tr.close()
+
+
+def test_newton_schulz_pushes_singular_values_towards_one_and_lr_modes():
+    from torchllmtuner_b200.components.optimizer.muon import adjusted_lr, newton_schulz
+    torch.manual_seed(0)
+    for shape in [(32, 64), (96, 48)]:
+        g = torch.randn(*shape)
+        x = newton_schulz(g, steps=5).float()
+        sv = torch.linalg.svdvals(x)
+        assert 0.5 < float(sv.min()) and float(sv.max()) < 1.3, (shape, sv.min(), sv.max())   # the quintic's band around 1
+        # same singular vectors as the input: U^T X V is close to diagonal
+        u, _, vt = torch.linalg.svd(g, full_matrices=False)
+        d = u.t() @ x @ vt.t()
+        assert float((d - torch.diag(torch.diagonal(d))).abs().max()) < 0.12
+    assert adjusted_lr(1e-3, (128, 64), "original") == pytest.approx(1e-3 * 2 ** 0.5)
+    assert adjusted_lr(1e-3, (64, 128), "original") == pytest.approx(1e-3)
+    assert adjusted_lr(1e-3, (64, 256), "match_rms_adamw") == pytest.approx(1e-3 * 0.2 * 16)
+    assert adjusted_lr(1e-3, (64, 256), "spectral_unclamped") == pytest.approx(1e-3 * 0.5)
