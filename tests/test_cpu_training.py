@@ -234,3 +234,29 @@ def test_newton_schulz_pushes_singular_values_towards_one_and_lr_modes():
     assert adjusted_lr(1e-3, (64, 128), "original") == pytest.approx(1e-3)
     assert adjusted_lr(1e-3, (64, 256), "match_rms_adamw") == pytest.approx(1e-3 * 0.2 * 16)
     assert adjusted_lr(1e-3, (64, 256), "spectral_unclamped") == pytest.approx(1e-3 * 0.5)
+
+
+def test_regex_param_groups_first_match_wins_and_overrides_apply():
+    from torchllmtuner_b200.config.optimizer_config import ParamGroupConfig
+    cfg = tiny_config(steps=1)
+    cfg.optimizer.param_groups = [ParamGroupConfig(pattern=r"norm", optimizer_kwargs={"learning_rate": 0.0}),
+                                  ParamGroupConfig(pattern=r"layers\.0\.", optimizer_kwargs={"weight_decay": 0.5}),
+                                  ParamGroupConfig(pattern=r"q_proj", optimizer_kwargs={"learning_rate": 1.0})]
+    tr = Trainer(cfg)
+    try:
+        opt = tr.optimizers.optimizers[0]
+        groups = {g["name"]: g for g in opt.param_groups}
+        assert set(groups) == {".*", "norm", r"layers\.0\.", "q_proj"}
+        names = {g["name"]: set(g["param_names"]) for g in opt.param_groups}
+        assert "model.layers.0.input_layernorm.weight" in names["norm"]                     # first match wins over layers.0.
+        assert "model.layers.0.self_attn.q_proj.weight" in names[r"layers\.0\."]            # ... and over q_proj
+        assert "model.layers.1.self_attn.q_proj.weight" in names["q_proj"]
+        assert "model.embed_tokens.weight" in names[".*"]
+        assert groups["norm"]["lr"] == 0.0 and groups[r"layers\.0\."]["weight_decay"] == 0.5
+        before = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+        tr.train_step()
+        after = dict(tr.model.named_parameters())
+        assert torch.equal(before["model.norm.weight"], after["model.norm.weight"])          # lr 0: frozen
+        assert not torch.equal(before["model.layers.1.mlp.up_proj.weight"], after["model.layers.1.mlp.up_proj.weight"])
+    finally:
+        tr.close()
