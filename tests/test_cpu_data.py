@@ -146,3 +146,21 @@ def test_huggingface_tokenizer_special_tokens_and_chat_template(tmp_path):
     text = t.apply_chat_template([{"role": "user", "content": "hello"}, {"role": "assistant", "content": "world"}])
     assert text.replace("</s>", " </s> ").split() == ["user", ":", "hello", "</s>", "assistant", ":", "world", "</s>"]
     assert t.identity().startswith("hf:") and t.identity() == HuggingFaceTokenizer(str(d)).identity()
+
+
+def test_dataset_composition_concat_mix_and_epoch_order():
+    from torchllmtuner_b200.datasets.composition import DatasetConcat, DatasetIterationPolicy, DatasetMix, SingleDataset, epoch_order
+    a = SingleDataset([{"v": i} for i in range(5)], lambda r: r["v"])
+    b = SingleDataset([{"v": 100 + i} for i in range(3)], lambda r: r["v"])
+    cat = DatasetConcat([a, b])
+    assert len(cat) == 8 and [cat.get(i) for i in range(8)] == [0, 1, 2, 3, 4, 100, 101, 102]
+    mix = DatasetMix([a, b], [0.9, 0.1], seed=1)
+    draws = [mix.get(i) for i in range(2000)]
+    assert draws == [mix.get(i) for i in range(2000)]                          # deterministic in the index
+    share_b = sum(d >= 100 for d in draws) / len(draws)
+    assert 0.06 < share_b < 0.14, share_b
+    pol = DatasetIterationPolicy(shuffle=True, seed=3)
+    parts = [epoch_order(10, 0, pol, r, 2) for r in range(2)]
+    assert sorted(parts[0] + parts[1]) == list(range(10)) and not set(parts[0]) & set(parts[1])   # DP shards partition the epoch
+    assert epoch_order(10, 0, pol, 0, 2) != epoch_order(10, 1, pol, 0, 2)                          # reshuffled per epoch
+    assert epoch_order(10, 0, DatasetIterationPolicy(shuffle=False), 1, 2) == [1, 3, 5, 7, 9]
