@@ -106,3 +106,19 @@ def test_checkpoint_key_names(tmp_path):
     assert any(k.startswith("optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg_sq@") for k in keys)
     for k in ("obj.lr_scheduler", "obj.train_state", "obj.format", "obj.optimizer.param_groups", "obj.dataloader.dp0", "obj.rng.rank0"):
         assert k in keys, k
+
+
+def test_resume_at_other_tp_degree(tmp_path):
+    """Saved by two tensor-parallel ranks (column / row shards of every projection, vocab-sharded embedding); resumed by
+    one rank that holds full tensors, and the other way round."""
+    folder = str(tmp_path / "run")
+    ck = dict(dump_folder=folder, enable=True, exclude_from_loading=["dataloader", "rng"])
+    ref = run_ranks(1, base_flat(), steps=4)
+    run_ranks(2, base_flat(tensor_parallel_size=2, data_parallel_shard_size=1, _save_at=2, **ck), steps=2)
+    got = run_ranks(1, base_flat(_load=True, **ck), steps=2)
+    assert max(abs(a - b) for a, b in zip(ref["loss"][2:], got["loss"])) < 5e-5, (ref, got)
+    folder2 = str(tmp_path / "run2")
+    ck2 = dict(dump_folder=folder2, enable=True, exclude_from_loading=["dataloader", "rng"])
+    run_ranks(1, base_flat(_save_at=2, **ck2), steps=2)
+    got2 = run_ranks(2, base_flat(tensor_parallel_size=2, data_parallel_shard_size=1, _load=True, **ck2), steps=2)
+    assert max(abs(a - b) for a, b in zip(ref["loss"][2:], got2["loss"])) < 5e-5, (ref, got2)

@@ -103,6 +103,30 @@ def iter_pieces(rt):
             yield canonical_fqn(fqn), tag, off + lo, off + hi, u, shard_lo
 
 
+def piece_params(rt) -> dict:
+    """canonical fqn -> parameter object (for shapes and cut attributes) of everything this runtime owns."""
+    out = {}
+    for u in rt.units:
+        for p_, s_ in zip(u.params, u.slots):
+            out[canonical_fqn(s_.fqn)] = p_
+    return out
+
+
+_TAG_RE = re.compile(r"^@tp(?P<dim>\d+)\.(?P<r>\d+)of(?P<n>\d+)$")
+
+
+def _global_positions(tag: str, lo: int, hi: int, full_cols: int) -> torch.Tensor:
+    """Flat positions inside the full 2-D tensor of the flat range [lo, hi) of a piece. Untagged pieces are already in
+    full coordinates; a `@tp1.rofn` piece counts inside rank r's column block of width full_cols / n."""
+    idx = torch.arange(lo, hi, dtype=torch.int64)
+    if not tag:
+        return idx
+    m = _TAG_RE.match(tag)
+    r, n = int(m["r"]), int(m["n"])
+    c = full_cols // n
+    return (idx // c) * full_cols + r * c + idx % c
+
+
 def _intersections(need_lo: int, need_hi: int, have: list[tuple[int, int]]):
     for lo, hi in have:
         a, b = max(lo, need_lo), min(hi, need_hi)
@@ -341,20 +365,58 @@ class DistributedCheckpointManager(CheckpointManager):
                 raise ConfigError(f"checkpoint {path} covers {covered} of {ghi - glo} elements of {base}{tag}[{glo}:{ghi}]")
             return True
 
+        have_by_base: dict[str, list[tuple[str, int, int]]] = {}
+        for (base_, tag_), ranges in have.items():
+            for lo_, hi_ in ranges:
+                have_by_base.setdefault(base_, []).append((tag_, lo_, hi_))
+        indexed = []       # (dst view, key, dst positions, src positions): pieces saved under another tensor-parallel cut
+
+        def request_resharded(base, tag, glo, ghi, dst, p) -> bool:
+            """The checkpoint holds this tensor under another cut of dimension 1 (row-parallel weights saved at a
+            different tensor-parallel degree): match element by element through positions in the full tensor."""
+            pieces = have_by_base.get(base)
+            full_shape = tuple(getattr(p, "tp_full_shape", getattr(p, "_meta_shape", p.shape)))
+            if not pieces or len(full_shape) != 2 or getattr(p, "ep_sharded", False):
+                return False
+            if any(t and (_TAG_RE.match(t) is None or int(_TAG_RE.match(t)["dim"]) != 1) for t, _, _ in pieces) or \
+                    (tag and int(_TAG_RE.match(tag)["dim"]) != 1):
+                return False
+            C = full_shape[1]
+            need = _global_positions(tag, glo, ghi, C)
+            covered = 0
+            for t, lo, hi in pieces:
+                src = _global_positions(t, lo, hi, C)
+                # both position lists are sorted: locate the needed positions inside this piece
+                loc = torch.searchsorted(src, need)
+                hit = (loc < src.numel()) & (src[loc.clamp_max(src.numel() - 1)] == need)
+                if hit.any():
+                    key = f"{base}{t}@{lo}:{hi}"
+                    if key not in want:
+                        want[key] = torch.empty(hi - lo, dtype=torch.float32)
+                    indexed.append((dst, key, hit.nonzero().squeeze(1), loc[hit]))
+                    covered += int(hit.sum())
+            if covered != ghi - glo:
+                raise ConfigError(f"checkpoint {path} covers {covered} of {ghi - glo} elements of {base}{tag}[{glo}:{ghi}]")
+            return True
+
         missing = []
         for rt, opt in zip([tr.asm.fsdp], tr.optimizers.optimizers):
+            params = piece_params(rt)
             for fqn, tag, glo, ghi, u, slo in iter_pieces(rt):
                 n = ghi - glo
-                if "model" not in exclude and not request(f"model.{fqn}", tag, glo, ghi, u.master[slo:slo + n]):
+
+                def fetch(base, dst, _fqn=fqn, _tag=tag, _glo=glo, _ghi=ghi):
+                    return request(base, _tag, _glo, _ghi, dst) or request_resharded(base, _tag, _glo, _ghi, dst, params[_fqn])
+                if "model" not in exclude and not fetch(f"model.{fqn}", u.master[slo:slo + n]):
                     missing.append(fqn)
                 if model_only or "optimizer" in exclude:
                     continue
                 st = getattr(opt, "state", {}).get(u.name, {})
                 for k in ("exp_avg", "exp_avg_sq", "momentum_buffer"):
                     if k in st:
-                        request(f"optimizer.state.{fqn}.{k}", tag, glo, ghi, st[k][slo:slo + n])
+                        fetch(f"optimizer.state.{fqn}.{k}", st[k][slo:slo + n])
                 if tr.ema is not None and "ema" not in exclude:
-                    request(f"ema.ema_params.{fqn}", tag, glo, ghi, tr.ema.ema_params[u.name][slo:slo + n])
+                    fetch(f"ema.ema_params.{fqn}", tr.ema.ema_params[u.name][slo:slo + n])
         if missing:
             raise ConfigError(f"checkpoint {path} lacks model tensors: {missing[:5]}{'...' if len(missing) > 5 else ''}")
         buf_dst = {}
@@ -381,6 +443,8 @@ class DistributedCheckpointManager(CheckpointManager):
         with torch.no_grad():
             for dst, key, off, n in copies:
                 dst.copy_(want[key][off:off + n])
+            for dst, key, dpos, spos in indexed:
+                dst[dpos.to(dst.device)] = want[key][spos].to(dst.device, dst.dtype)
             for key, buf in buf_dst.items():
                 buf.copy_(want[key].view_as(buf))
             for rt in [tr.asm.fsdp]:
