@@ -180,7 +180,42 @@ def _case_vocab_parallel_loss_and_embedding(rank, world):
     return f"{e1:.2e},{e2:.2e},{e3:.2e},{e4:.2e}"
 
 
+def _case_unequal_loader_exhaustion(rank, world):
+    """Rank 1's data stream ends one batch early; rank 0's raises. Both ranks must leave `fetch_batch` the same way,
+    before any step collective."""
+    from types import SimpleNamespace as NS
+
+    from torchllmtuner_b200.datasets.contracts import DataloaderExhaustedError
+    from torchllmtuner_b200.trainer.runtime.batch import fetch_batch
+    env = NS(world_size=world, device=torch.device("cpu"))
+    out = []
+    it = iter([{"x": 1}, {"x": 2}] if rank == 0 else [{"x": 1}])
+    for _ in range(2):
+        try:
+            out.append("ready" if fetch_batch(it, env) is not None else "none")
+        except DataloaderExhaustedError:
+            out.append("exhausted")
+
+    def broken():
+        if rank == 0:
+            raise OSError("disk error")
+        yield {"x": 3}
+    try:
+        fetch_batch(broken(), env)
+        out.append("ready")
+    except OSError:
+        out.append("own-error")
+    except RuntimeError as e:
+        out.append("peer-error" if "peer rank failed" in str(e) else "other")
+    return ",".join(out)
+
+
 # ---------------------------------------------------------------------------------------------- tests
+def test_unequal_loader_exhaustion_and_read_errors_are_agreed_on():
+    res = _spawn(_case_unequal_loader_exhaustion, 2)
+    assert res[0] == "ready,exhausted,own-error" and res[1] == "ready,exhausted,peer-error", res
+
+
 def test_vocab_parallel_cross_entropy_entropy_and_embedding_match_the_full_vocabulary():
     for r in _spawn(_case_vocab_parallel_loss_and_embedding, 2):
         assert r.count(",") == 3, r
