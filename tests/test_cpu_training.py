@@ -260,3 +260,32 @@ def test_regex_param_groups_first_match_wins_and_overrides_apply():
         assert not torch.equal(before["model.layers.1.mlp.up_proj.weight"], after["model.layers.1.mlp.up_proj.weight"])
     finally:
         tr.close()
+
+
+def test_accumulation_with_unequal_valid_tokens_equals_one_batch():
+    """Micro-batches with different numbers of valid targets: the loss is the sum of token losses over the whole step
+    divided by the step's valid-token count, so two micro-batches must give the gradients of the joint batch."""
+    one = Trainer(tiny_config(steps=1, global_batch_size=4))
+    two = Trainer(tiny_config(steps=1, global_batch_size=4, gradient_accumulation_steps=2))
+    try:
+        big = one.fetch_batch()
+        big["labels"] = big["labels"].clone()
+        big["labels"][0, 5:] = -100                      # row 0 keeps 5 targets, rows 1-3 keep all
+        big["labels"][3, :20] = -100
+        big["num_valid_tokens"] = int((big["labels"] != -100).sum())
+        halves = []
+        for a in (0, 2):
+            h = {k: (v[a:a + 2].clone() if isinstance(v, torch.Tensor) and v.dim() >= 1 and v.shape[0] == 4 else v) for k, v in big.items()}
+            h["num_valid_tokens"] = int((h["labels"] != -100).sum())
+            halves.append(h)
+        assert halves[0]["num_valid_tokens"] != halves[1]["num_valid_tokens"]
+        r1 = one.train_step(batches=[big])
+        r2 = two.train_step(batches=halves)
+        assert abs(r1.loss - r2.loss) < 1e-5 and abs(r1.grad_norm - r2.grad_norm) < 1e-4, (r1, r2)
+        # Adam's first update is lr * sign-like in every element, so elements whose gradient is ~0 may flip on rounding:
+        # compare in bulk
+        for (n, p), (_, q) in zip(one.model.named_parameters(), two.model.named_parameters()):
+            assert float(((p - q).abs() > 1e-5).float().mean()) < 1e-3, n
+    finally:
+        one.close()
+        two.close()
