@@ -249,3 +249,66 @@ def test_checkpoint_publication_failure_keeps_previous_checkpoint():
         assert r.count(",") == 2, res
         verdict, first, latest = r.split(",")
         assert verdict != "no-raise" and first == latest, res
+
+
+# ---------------------------------------------------------------------------------------------- a rank dies during a save
+def _rank_exit_worker(rank, world, port, folder, out):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      LLMTUNER_DEVICE="cpu")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import datetime
+
+    import torch.distributed as dist
+    from dist_cases import base_flat
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.accelerator.collectives import set_pg_timeouts
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    torch.set_num_threads(1)
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(data_parallel_shard_size=world, dump_folder=folder, enable=True, interval=1000, last_save_model_only=False))
+    tr = Trainer(cfg)
+    for _ in range(2):
+        tr.dataloader.cursor = 0
+        tr.train_step()
+    tr.checkpointer.save(2, force=True)
+    tr.checkpointer.wait()
+    tr.dataloader.cursor = 0
+    tr.train_step()
+    set_pg_timeouts(4, [])
+    import torchllmtuner_b200.components.checkpointer.dcp_manager as dm
+    if rank == 1:
+        real_save = dm.dcp.save
+
+        def dying_save(*a, **k):
+            os._exit(17)                      # the rank vanishes inside the step-3 save, before anything is published
+        dm.dcp.save = dying_save
+    verdict = "saved"
+    try:
+        tr.checkpointer.save(3, force=True)
+        tr.checkpointer.wait()
+    except BaseException as e:  # noqa: BLE001
+        verdict = "error:" + type(e).__name__
+    with open(os.path.join(out, f"{rank}.txt"), "w") as f:
+        f.write(f"{verdict},{tr.checkpointer.latest_step()}")
+    os._exit(0)
+
+
+def test_rank_dying_inside_a_save_leaves_the_previous_checkpoint_and_it_resumes_exactly(tmp_path):
+    import torch.multiprocessing as mp
+    from dist_cases import base_flat, run_ranks
+    folder, out = str(tmp_path / "run"), str(tmp_path / "out")
+    os.makedirs(out)
+    port = 25000 + os.getpid() % 15000
+    ctx = mp.spawn(_rank_exit_worker, args=(2, port, folder, out), nprocs=2, join=False)
+    for p in ctx.processes:
+        p.join(120)
+    assert ctx.processes[1].exitcode == 17
+    verdict, latest = open(os.path.join(out, "0.txt")).read().split(",")
+    assert verdict.startswith("error:") and latest == "2", (verdict, latest)
+    assert not os.path.exists(os.path.join(folder, "checkpoint", "step-3", ".metadata"))
+    # a fresh job resumes from step 2 and reproduces the uninterrupted run
+    ref = run_ranks(2, base_flat(data_parallel_shard_size=2), steps=4)
+    got = run_ranks(2, base_flat(data_parallel_shard_size=2, dump_folder=folder, enable=True, _load=True,
+                                 exclude_from_loading=["dataloader", "rng"]), steps=2)
+    assert max(abs(a - b) for a, b in zip(ref["loss"][2:], got["loss"])) < 1e-6, (ref, got)
