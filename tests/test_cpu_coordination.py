@@ -312,3 +312,57 @@ def test_rank_dying_inside_a_save_leaves_the_previous_checkpoint_and_it_resumes_
     got = run_ranks(2, base_flat(data_parallel_shard_size=2, dump_folder=folder, enable=True, _load=True,
                                  exclude_from_loading=["dataloader", "rng"]), steps=2)
     assert max(abs(a - b) for a, b in zip(ref["loss"][2:], got["loss"])) < 1e-6, (ref, got)
+
+
+# ---------------------------------------------------------------------------------------------- HF export / import under TP
+def _case_hf_round_trip_under_tp(rank, world, folder):
+    """Two tensor-parallel ranks export full Hugging Face tensors (row-parallel weights are scattered back into place),
+    then import them again into freshly, differently initialised shards."""
+    import torch.distributed as dist
+    from dist_cases import base_flat
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.components.checkpointer.hf import load_hf_checkpoint, save_hf_checkpoint
+    flat = base_flat(tensor_parallel_size=2, data_parallel_shard_size=1, dump_folder=folder)
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(flat)
+    tr = Trainer(cfg)
+    tr.train_step()
+    save_hf_checkpoint(tr, os.path.join(folder, "hf"), "float32")
+    want = {u.name: u.master.clone() for u in tr.asm.fsdp.units}
+    tr.close()
+    cfg2 = LLMTunerConfig()
+    cfg2.apply_flat(dict(flat, seed=7))
+    tr2 = Trainer(cfg2)
+    before = max(float((u.master - want[u.name]).abs().max()) for u in tr2.asm.fsdp.units)
+    load_hf_checkpoint(tr2, os.path.join(folder, "hf"))
+    after = max(float((u.master - want[u.name]).abs().max()) for u in tr2.asm.fsdp.units)
+    tr2.close()
+    dist.barrier()
+    return f"{before:.3e},{after:.3e}"
+
+
+def test_hf_export_and_import_under_tensor_parallelism(tmp_path):
+    folder = str(tmp_path / "run")
+    for r in _spawn(_case_hf_round_trip_under_tp, 2, folder):
+        assert r.count(",") == 1, r
+        before, after = (float(x) for x in r.split(","))
+        assert before > 1e-3 and after == 0.0, r
+    # the exported folder holds full tensors: a single rank reads it too
+    import torch
+    from dist_cases import base_flat
+    from safetensors import safe_open
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.components.checkpointer.hf import load_hf_checkpoint
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(dump_folder=folder, seed=11))
+    os.environ["LLMTUNER_DEVICE"] = "cpu"
+    tr = Trainer(cfg)
+    try:
+        load_hf_checkpoint(tr, os.path.join(folder, "hf"))
+        import glob
+        f = safe_open(glob.glob(os.path.join(folder, "hf", "*.safetensors"))[0], "pt")
+        name = "model.layers.0.self_attn.o_proj.weight"
+        assert name in f.keys()
+        assert torch.equal(dict(tr.model.named_parameters())[name].detach().float(), f.get_tensor(name).float())
+    finally:
+        tr.close()

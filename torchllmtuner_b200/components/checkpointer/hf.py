@@ -20,7 +20,7 @@ import torch.distributed as dist
 
 from ...errors import ConfigError
 from ...models.state import get_state_format
-from .dcp_manager import iter_pieces
+from .dcp_manager import _global_positions, iter_pieces
 
 _DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
 
@@ -40,6 +40,10 @@ def read_hf_weight_map(path: str) -> dict[str, str]:
 
 def _param_index(trainer):
     out = {}
+    tp_rank = trainer.env.topo.coord("tp")
+    for p in trainer.model.parameters():
+        if hasattr(p, "tp_shard_dim"):
+            p._tp_rank = tp_rank                  # iter_pieces places a tensor-parallel cut through this
     for u in trainer.asm.fsdp.units:
         for p, s in zip(u.params, u.slots):
             out[s.fqn.replace(".inner.", ".")] = (p, s)
@@ -72,9 +76,18 @@ def load_hf_checkpoint(trainer, path: str) -> None:
     pidx = _param_index(trainer)
     with torch.no_grad():
         for fqn, tag, glo, ghi, u, slo in iter_pieces(trainer.asm.fsdp):
-            if tag:
-                raise ConfigError(f"HF import of {fqn}: parameters cut along a later dimension need tensor_parallel_size 1")
             p, s = pidx[fqn]
+            if tag:
+                # a row-parallel weight (cut on dimension 1): this rank's flat range maps to scattered positions of the
+                # full tensor, which is stored whole under one HF name
+                full_shape = _full_shape(p, s)
+                pieces = fmt.to_hf(fqn, full_shape)
+                if len(full_shape) != 2 or len(pieces) != 1:
+                    raise ConfigError(f"HF import of {fqn}: only 2-D tensors may be cut along dimension 1")
+                pos = _global_positions(tag, glo, ghi, full_shape[1])
+                src = tensor(pieces[0].hf_name).reshape(-1)
+                u.master[slo: slo + (ghi - glo)].copy_(src[pos - pieces[0].native_flat_lo].float())
+                continue
             for piece in fmt.to_hf(fqn, _full_shape(p, s)):
                 a, b = max(glo, piece.native_flat_lo), min(ghi, piece.native_flat_hi)
                 if b <= a:
@@ -98,9 +111,7 @@ def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", ma
     pidx = _param_index(trainer)
     mine: dict[str, list] = {}
     for fqn, tag, glo, ghi, u, slo in iter_pieces(trainer.asm.fsdp):
-        if tag:
-            raise ConfigError(f"HF export of {fqn}: parameters cut along a later dimension need tensor_parallel_size 1")
-        mine.setdefault(fqn, []).append((glo, ghi, u.master[slo:slo + ghi - glo]))
+        mine.setdefault(fqn, []).append((glo, ghi, u.master[slo:slo + ghi - glo], tag))
     # which canonical FQNs exist anywhere, with their full shapes (identical on all ranks except expert slices)
     table = {fqn: _full_shape(*pidx[fqn]) for fqn in pidx}
     if world > 1:
@@ -126,7 +137,7 @@ def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", ma
         numel = 1
         for x in shape:
             numel *= x
-        parts = [(lo, hi, t.detach().to("cpu", torch.float32)) for lo, hi, t in mine.get(fqn, [])]
+        parts = [(lo, hi, t.detach().to("cpu", torch.float32), tag) for lo, hi, t, tag in mine.get(fqn, [])]
         if world > 1:
             gathered = [None] * world if rank == 0 else None
             dist.gather_object(parts, gathered, dst=0)
@@ -135,7 +146,11 @@ def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", ma
             continue
         full = torch.zeros(numel, dtype=torch.float32)
         seen = 0
-        for lo, hi, t in parts:
+        for lo, hi, t, tag in parts:
+            if tag:            # cut on dimension 1: scatter through positions in the full tensor
+                full[_global_positions(tag, lo, hi, shape[1])] = t
+                seen += hi - lo
+                continue
             hi = min(hi, numel)
             if hi > lo:
                 full[lo:hi] = t[:hi - lo]
