@@ -10,7 +10,8 @@ They share one hybrid decoder: every layer has a token mixer and an MLP (dense o
                                              with the aux-loss-free selection bias, hyper-connections (several residual
                                              streams mixed by learned weights)
 Softmax attention and every GEMM run on the sm_100a kernels; the recurrent delta-rule scan is plain PyTorch (chunked
-over documents). The vision towers of the multimodal variants are out of scope of the text decoders registered here.
+over documents). The vision tower, the 3-axis rotary positions and the wrapper that splices image rows into these decoders
+are in `models/vision.py`.
 """
 from __future__ import annotations
 
@@ -209,9 +210,9 @@ class HybridForCausalLM(Qwen3ForCausalLM):
             raise UnsupportedCombinationError(f"{self.config.model_type}: tensor / context parallelism is defined for the Qwen3 family only")
         super().validate_parallel(1, 1, ep)
 
-    def forward(self, tokens, ctx, skip_lm_head=False):
+    def forward(self, tokens, ctx, skip_lm_head=False, inputs_embeds=None):
         n = self.config.hyper_connection_streams
-        x = self.model.embed_tokens(tokens) if self.pp_first else tokens
+        x = inputs_embeds if inputs_embeds is not None else (self.model.embed_tokens(tokens) if self.pp_first else tokens)
         if n > 1:
             x = x.unsqueeze(0).repeat(n, 1, 1)
         for i, layer in enumerate(self.model.layers):

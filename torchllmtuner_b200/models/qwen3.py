@@ -275,10 +275,11 @@ class Qwen3ForCausalLM(nn.Module):
             return checkpoint(layer, x, ctx, use_reentrant=False)
         return layer(x, ctx)
 
-    def forward(self, tokens: torch.Tensor, ctx: ForwardContext, skip_lm_head: bool = False) -> torch.Tensor:
+    def forward(self, tokens: torch.Tensor, ctx: ForwardContext, skip_lm_head: bool = False, inputs_embeds=None) -> torch.Tensor:
         """`tokens` are ids on the first pipeline stage (or without pipeline parallelism) and the previous stage's hidden
-        rows otherwise; a stage that is not the last returns hidden rows."""
-        x = self.model.embed_tokens(tokens) if self.pp_first else tokens
+        rows otherwise; a stage that is not the last returns hidden rows. `inputs_embeds` [T, D] replaces the embedding
+        lookup (multimodal wrappers splice image rows in first)."""
+        x = inputs_embeds if inputs_embeds is not None else (self.model.embed_tokens(tokens) if self.pp_first else tokens)
         layers = self.model.layers
         for i, layer in enumerate(layers.values() if isinstance(layers, nn.ModuleDict) else layers):
             x = self.run_block(getattr(layer, "layer_idx", i), layer, x, ctx)
