@@ -289,3 +289,31 @@ def test_accumulation_with_unequal_valid_tokens_equals_one_batch():
     finally:
         one.close()
         two.close()
+
+
+def test_kernel_status_code_rides_in_the_step_read_and_stops_the_step(monkeypatch):
+    """The status word of the device kernels is read with the step's loss; a non-zero code raises at that step."""
+    from torchllmtuner_b200.errors import KernelStatusError
+    from torchllmtuner_b200.trainer import trainer as trainer_mod
+    from torchllmtuner_b200.trainer.runtime.metrics import build_step_metrics
+
+    class Red:
+        loss_group = None
+    out = build_step_metrics(torch.tensor(6.0), torch.tensor(2.0), torch.tensor(3.0), Red(), torch.tensor([2, 7, 1, 0], dtype=torch.int32))
+    assert out == (2.0, 2.0, 3.0, 2)
+    assert build_step_metrics(torch.tensor(6.0), torch.tensor(2.0), torch.tensor(3.0), Red()) == (2.0, 2.0, 3.0)
+
+    word = torch.zeros(8, dtype=torch.int32)
+    monkeypatch.setattr(trainer_mod, "status_word", lambda device: word)
+
+    def fake_check(where):
+        raise KernelStatusError(where, int(word[0]), "bounded flag wait expired at site 7")
+    monkeypatch.setattr(trainer_mod, "check_status", fake_check)
+    tr = Trainer(tiny_config(steps=3))
+    try:
+        assert tr.train_step().step == 1                              # code 0: nothing happens
+        word[0] = 2
+        with pytest.raises(KernelStatusError, match="training step 2"):
+            tr.train_step()
+    finally:
+        tr.close()

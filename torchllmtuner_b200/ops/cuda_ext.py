@@ -52,6 +52,14 @@ def available() -> bool:
         return False
 
 
+def status_word(device):
+    """The kernels' status word as a device tensor, or None when `device` is not CUDA (nothing can have written one)."""
+    import torch
+    if torch.device(device).type != "cuda":
+        return None
+    return load().status_tensor()
+
+
 def so_path() -> str:
     return _SO
 

@@ -151,15 +151,32 @@ def _align(n: int, a: int = 256) -> int:
 CANARY = 0x5AFEC0DE
 
 
+_ARENAS: list = []      # weak references to every arena that carries a canary, for `damaged_arenas`
+
+
 def write_canary(arena: torch.Tensor, nbytes: int = 256) -> None:
     """Fill the last `nbytes` of a symmetric arena with a known pattern; nothing in the arena's layout uses them."""
+    import weakref
     arena[-nbytes:].view(torch.int32).fill_(CANARY - (1 << 32) if CANARY >= (1 << 31) else CANARY)
+    _ARENAS.append(weakref.ref(arena))
 
 
 def canary_intact(arena: torch.Tensor, nbytes: int = 256) -> bool:
     """Host-side check (synchronises): False means some kernel, local or on a peer, wrote past a buffer of the arena."""
     want = CANARY - (1 << 32) if CANARY >= (1 << 31) else CANARY
     return bool((arena[-nbytes:].view(torch.int32) == want).all().item())
+
+
+def damaged_arenas() -> int:
+    """How many live symmetric arenas have lost their canary words (synchronises; a debugging check)."""
+    bad, live = 0, []
+    for r in _ARENAS:
+        a = r()
+        if a is not None:
+            live.append(r)
+            bad += 0 if canary_intact(a) else 1
+    _ARENAS[:] = live
+    return bad
 
 
 class FusedFSDPComm:

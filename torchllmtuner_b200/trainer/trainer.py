@@ -11,6 +11,8 @@ from ..components.metrics import MetricsProcessor
 from ..config import LLMTunerConfig, resolve_batch_size_per_rank
 from ..datasets import build_dataloader
 from ..datasets.contracts import DataloaderExhaustedError
+from ..errors import KernelStatusError
+from ..ops.cuda_ext import check_status, status_word
 from ..utils import GarbageCollection, get_logger, set_log_ranks
 from ..utils.metric_loggers import build_metric_logger
 from ..utils.nvtx import nvtx_range
@@ -105,7 +107,15 @@ class Trainer:
             self.progress.step = step
             return None
         # one device->host read per step: [loss_sum, grad_norm, valid tokens]
-        loss, gnorm, gtok = build_step_metrics(eng.step_loss, norm, gv, self.reductions)
+        # (the kernels' status code rides in the same read)
+        status = status_word(self.env.device)
+        loss, gnorm, gtok, *code = build_step_metrics(eng.step_loss, norm, gv, self.reductions, status)
+        if code and code[0]:
+            check_status(f"training step {step}")                       # raises KernelStatusError with site and block
+        if status is not None and os.environ.get("LLMT_DEBUG") == "1":
+            from ..parallel.symm import damaged_arenas
+            if damaged_arenas():
+                raise KernelStatusError(f"training step {step}", 5, "a symmetric-memory arena lost its canary words: some kernel wrote past a buffer")
         eng.finish_step(step, loss)
         self.progress.step = step
         self.progress.ntokens_seen += int(gtok)
