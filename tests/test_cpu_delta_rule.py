@@ -1,0 +1,58 @@
+"""Chunk-parallel gated delta rule against its token-by-token statement: values, gradients, documents, strong decay."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from torchllmtuner_b200.models.families import DeltaRuleMixer, HybridConfig, chunked_delta_rule, delta_rule_scan
+from torchllmtuner_b200.models.qwen3 import ForwardContext
+from torchllmtuner_b200.ops.attn_meta import AttnMeta
+
+
+def _inputs(T, H, dk, dv, channels, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    q = F.normalize(torch.randn(T, H, dk, generator=g), dim=-1).requires_grad_()
+    k = F.normalize(torch.randn(T, H, dk, generator=g), dim=-1).requires_grad_()
+    v = torch.randn(T, H, dv, generator=g).requires_grad_()
+    beta = torch.rand(T, H, generator=g).requires_grad_()
+    ld = (-F.softplus(torch.randn(T, H, channels, generator=g) * 3)).requires_grad_()
+    return [q, k, v, beta, ld]
+
+
+@pytest.mark.parametrize("channels,T,chunk", [(1, 37, 8), (8, 37, 8), (1, 64, 16), (8, 50, 16), (8, 16, 16), (1, 5, 64)])
+def test_chunked_form_matches_the_scan(channels, T, chunk):
+    x = _inputs(T, 3, 8, 6, channels)
+    a, b = delta_rule_scan(*x), chunked_delta_rule(*x, chunk)
+    assert torch.allclose(a, b, atol=5e-6)
+    w = torch.randn_like(a)
+    for ga, gb in zip(torch.autograd.grad((a * w).sum(), x), torch.autograd.grad((b * w).sum(), x)):
+        assert torch.allclose(ga, gb, atol=5e-5)
+
+
+def test_strong_decay_stays_finite_and_forgets():
+    T = 40
+    q, k, v, beta, _ = (t.detach() for t in _inputs(T, 2, 4, 4, 4))
+    o = chunked_delta_rule(q, k, v, beta, torch.full((T, 2, 4), -200.0), 16)
+    assert torch.isfinite(o).all()
+    # with the state wiped at every step, o_t = beta_t (k_t . q_t) v_t
+    want = beta.unsqueeze(-1) * (k * q).sum(-1, keepdim=True) * v
+    assert torch.allclose(o, want, atol=1e-6)
+
+
+@pytest.mark.parametrize("channel", [False, True])
+def test_mixer_resets_its_state_at_document_starts(channel):
+    cfg = HybridConfig(vocab_size=32, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=16, delta_heads=2, delta_head_dim=8, delta_channel_decay=channel,
+                       delta_chunk_size=8)
+    torch.manual_seed(0)
+    m = DeltaRuleMixer(cfg)
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.3) if p.dim() > 1 else torch.nn.init.ones_(p)
+    x = torch.randn(30, 32)
+
+    def run(rows, cu):
+        meta = AttnMeta.build(torch.tensor(cu))
+        return m(rows, ForwardContext(None, None, meta))
+    both = run(x, [0, 13, 30])
+    assert torch.allclose(both[:13], run(x[:13], [0, 13]), atol=1e-5)
+    assert torch.allclose(both[13:], run(x[13:], [0, 17]), atol=1e-5)
+    assert not torch.allclose(both[13:], run(x, [0, 30])[13:], atol=1e-3)

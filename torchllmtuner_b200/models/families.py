@@ -9,9 +9,9 @@ They share one hybrid decoder: every layer has a token mixer and an MLP (dense o
   deepseek_v4                                latent attention (low-rank KV with a decoupled rotary key), sigmoid router
                                              with the aux-loss-free selection bias, hyper-connections (several residual
                                              streams mixed by learned weights)
-Softmax attention and every GEMM run on the sm_100a kernels; the recurrent delta-rule scan is plain PyTorch (chunked
-over documents). The vision tower, the 3-axis rotary positions and the wrapper that splices image rows into these decoders
-are in `models/vision.py`.
+Softmax attention and every GEMM run on the sm_100a kernels; the delta rule runs in chunk-parallel form (batched matrix
+products and one triangular solve per layer, a short loop over chunks for the state; per document). The vision tower,
+the 3-axis rotary positions and the wrapper that splices image rows into these decoders are in `models/vision.py`.
 """
 from __future__ import annotations
 
@@ -34,6 +34,7 @@ class HybridConfig(Qwen3Config):
     delta_heads: int = 4
     delta_head_dim: int = 32
     delta_channel_decay: bool = False          # True: KDA (per-channel decay), False: gated delta-net (per-head decay)
+    delta_chunk_size: int = 0                  # tokens per chunk of the chunk-parallel delta rule; 0: 64 (per-head decay) / 16 (KDA)
     attention_output_gate: bool = True
     kv_lora_rank: int = 64                     # latent attention
     qk_rope_dim: int = 32
@@ -49,6 +50,71 @@ def _doc_starts(meta, T: int, device) -> torch.Tensor:
     return s
 
 
+def delta_rule_scan(q, k, v, beta, log_decay):
+    """Token-by-token statement of the gated delta rule, zero initial state (the oracle of `chunked_delta_rule`).
+    q, k [T, H, dk]; v [T, H, dv]; beta [T, H]; log_decay [T, H, dk] or [T, H, 1] (<= 0). Returns [T, H, dv]."""
+    T, H, dk = q.shape
+    S = q.new_zeros(H, dk, v.shape[-1])
+    dec = log_decay.exp().expand(T, H, dk)
+    outs = []
+    for t in range(T):
+        S = S * dec[t].unsqueeze(-1)
+        pred = torch.einsum("hkv,hk->hv", S, k[t])
+        S = S + torch.einsum("hk,hv->hkv", k[t], beta[t].unsqueeze(-1) * (v[t] - pred))
+        outs.append(torch.einsum("hkv,hk->hv", S, q[t]))
+    return torch.stack(outs)
+
+
+def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64):
+    """The same recurrence in chunk-parallel form. Inside a chunk of C tokens that starts from state S0, with the
+    cumulative log decay G_t, the pseudo-values u_t = beta_t (v_t - S'_t^T k_t) solve the triangular system
+        (I + A) U = beta (V - K~ S0),   A[t, i] = beta_t sum_c k_t[c] k_i[c] exp(G_t[c] - G_i[c])   (i < t),
+    with K~_t = exp(G_t) k_t; then O = Q~ S0 + tril(QK) U and S_end = exp(G_C) S0 + (exp(G_C - G) K)^T U.
+    Everything that does not depend on S0 is computed for all chunks at once (batched matrix products and one batched
+    triangular solve); only the [dk, dv] state update runs chunk after chunk. Decay ratios are only ever formed as
+    exp(G_t - G_i) with i <= t, so nothing overflows however strong the decay."""
+    T, H, dk = q.shape
+    dv, C = v.shape[-1], chunk
+    pad = (-T) % C
+    if pad:                                           # padded tokens: beta = 0, k = 0, decay 1 -> no effect on the state
+        z = lambda t: F.pad(t, (0, 0, 0, 0, 0, pad))  # noqa: E731
+        q, k, v, log_decay = z(q), z(k), z(v), z(log_decay)
+        beta = F.pad(beta, (0, 0, 0, pad))
+    N = (T + pad) // C
+    r = lambda t: t.reshape(N, C, H, -1).permute(0, 2, 1, 3)  # noqa: E731  -> [N, H, C, *]
+    q, k, v, beta, G = r(q), r(k), r(v), r(beta.unsqueeze(-1)), r(log_decay).cumsum(2)
+    tri = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+    if G.shape[-1] == 1:                              # one decay per head: the ratio matrix factors out of the products
+        M = (G - G.transpose(2, 3)).clamp(max=0).exp()
+        KK, QK = (k @ k.transpose(2, 3)) * M, (q @ k.transpose(2, 3)) * M
+    else:                                             # a decay per key channel: pairwise ratios, in slabs of chunks
+        KK, QK = [], []
+        slab = max(1, (1 << 25) // (H * C * C * dk))
+        for a in range(0, N, slab):
+            g = G[a:a + slab]
+            E = (g.unsqueeze(3) - g.unsqueeze(2)).clamp(max=0).exp()          # [n, H, t, i, dk]
+            KK.append(torch.einsum("nhtc,nhic,nhtic->nhti", k[a:a + slab], k[a:a + slab], E))
+            QK.append(torch.einsum("nhtc,nhic,nhtic->nhti", q[a:a + slab], k[a:a + slab], E))
+        KK, QK = torch.cat(KK), torch.cat(QK)
+    A = (beta * KK).masked_fill(~tri.tril(-1), 0.0)
+    QK = QK.masked_fill(~tri, 0.0)
+    eG = G.exp()
+    IA = A + torch.eye(C, dtype=q.dtype, device=q.device)
+    W = torch.linalg.solve_triangular(IA, torch.cat((beta * v, beta * eG * k), -1), upper=False)
+    W1, W2 = W[..., :dv], W[..., dv:]
+    Qt = eG * q
+    Kend = (G[:, :, -1:, :] - G).exp() * k
+    dec_end = G[:, :, -1, :].exp().unsqueeze(-1)                              # [N, H, dk | 1, 1]
+    S = q.new_zeros(H, dk, dv)
+    outs = []
+    for n in range(N):
+        U = W1[n] - W2[n] @ S
+        outs.append(Qt[n] @ S + QK[n] @ U)
+        S = dec_end[n] * S + Kend[n].transpose(1, 2) @ U
+    o = torch.stack(outs).permute(0, 2, 1, 3).reshape(N * C, H, dv)
+    return o[:T]
+
+
 class DeltaRuleMixer(nn.Module):
     """Gated delta rule: S_t = a_t * S_{t-1} (I - b_t k_t k_t^T) + b_t k_t v_t^T ; o_t = S_t^T q_t, per head, state reset
     at document starts. `channel_decay` makes a_t a vector over the key dimension (KDA)."""
@@ -57,6 +123,7 @@ class DeltaRuleMixer(nn.Module):
         super().__init__()
         D, H, d = cfg.hidden_size, cfg.delta_heads, cfg.delta_head_dim
         self.H, self.d, self.channel = H, d, cfg.delta_channel_decay
+        self.chunk = cfg.delta_chunk_size or (16 if self.channel else 64)
         self.q_proj, self.k_proj, self.v_proj = (Linear(D, H * d, dtype, device) for _ in range(3))
         self.beta_proj = Linear(D, H, dtype, device)
         self.decay_proj = Linear(D, H * d if self.channel else H, dtype, device)
@@ -70,20 +137,11 @@ class DeltaRuleMixer(nn.Module):
         k = F.normalize(self.k_proj(x).view(T, H, d).float(), dim=-1)
         v = self.v_proj(x).view(T, H, d).float()
         beta = torch.sigmoid(self.beta_proj(x).float())                                   # [T, H]
-        dec = torch.exp(-F.softplus(self.decay_proj(x).float()))                          # in (0, 1)
-        dec = dec.view(T, H, d) if self.channel else dec.view(T, H, 1).expand(T, H, d)
-        starts = _doc_starts(ctx.attn_meta, T, x.device)
-        S = x.new_zeros(H, d, d, dtype=torch.float32)
-        outs = []
-        for t in range(T):
-            if starts[t]:
-                S = torch.zeros_like(S)
-            kt, vt, bt = k[t], v[t], beta[t].unsqueeze(-1)
-            S = S * dec[t].unsqueeze(-1)
-            pred = torch.einsum("hkv,hk->hv", S, kt)
-            S = S + torch.einsum("hk,hv->hkv", kt, bt * (vt - pred))
-            outs.append(torch.einsum("hkv,hk->hv", S, q[t]))
-        o = torch.stack(outs).to(x.dtype)                                                 # [T, H, d]
+        log_decay = -F.softplus(self.decay_proj(x).float()).view(T, H, d if self.channel else 1)
+        cuts = sorted({0, T} | {int(i) for i in _doc_starts(ctx.attn_meta, T, "cpu").nonzero().flatten().tolist()})
+        outs = [chunked_delta_rule(q[a:b], k[a:b], v[a:b], beta[a:b], log_decay[a:b], self.chunk)
+                for a, b in zip(cuts[:-1], cuts[1:])]                                     # the state starts at zero per document
+        o = torch.cat(outs).to(x.dtype)                                                   # [T, H, d]
         o = self.out_norm(o.reshape(T * H, d)).view(T, H * d) * F.silu(self.gate_proj(x))  # gated RMSNorm
         return self.o_proj(o)
 
