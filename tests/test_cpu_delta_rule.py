@@ -56,3 +56,54 @@ def test_mixer_resets_its_state_at_document_starts(channel):
     assert torch.allclose(both[:13], run(x[:13], [0, 13]), atol=1e-5)
     assert torch.allclose(both[13:], run(x[13:], [0, 17]), atol=1e-5)
     assert not torch.allclose(both[13:], run(x, [0, 30])[13:], atol=1e-3)
+
+
+def _kcp_worker(rank, world, store_path, out_path):
+    import torch.distributed as dist
+    from torchllmtuner_b200.parallel.context_parallel import ContextParallelDriver
+    dist.init_process_group("gloo", store=dist.FileStore(store_path, world), rank=rank, world_size=world)
+    try:
+        class Topo:
+            cp_ulysses, cp_kv, cp = 1, 1, world
+            def get_group(self, name): return None
+            def coord(self, name): return rank
+
+        class Cfg:
+            context_parallel_load_balancer = None
+        B, S, H, dk, dv = 2, 24, 2, 4, 4
+        # documents: one crosses the rank boundary, one starts inside a span, one starts exactly at a boundary
+        cu = {2: [0, 5, 24, 36, 48], 3: [0, 5, 24, 32, 48]}[world]
+        res = {}
+        for channels in (1, dk):
+            x = _inputs(B * S, H, dk, dv, channels, seed=3)
+            t = S // world
+            rows = torch.cat([torch.arange(b * S + rank * t, b * S + (rank + 1) * t) for b in range(B)])
+            local = [a.detach()[rows].clone().requires_grad_() for a in x]
+            drv = ContextParallelDriver(Topo(), Cfg())
+            drv._mb = {"B": B, "S": S, "gcu": cu}
+            o = drv.delta_rule(*local, chunk=4)
+            w = torch.randn(B * S, H, dv, generator=torch.Generator().manual_seed(9))
+            (o * w[rows]).sum().backward()
+            res[channels] = (rows, o.detach(), [a.grad for a in local])
+        torch.save(res, f"{out_path}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_parallel_delta_rule_hands_the_state_across_ranks(tmp_path, world):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "o")
+    mp.spawn(_kcp_worker, args=(world, str(tmp_path / "store"), out), nprocs=world, join=True)
+    B, S, H, dk, dv = 2, 24, 2, 4, 4
+    cu = {2: [0, 5, 24, 36, 48], 3: [0, 5, 24, 32, 48]}[world]
+    parts = [torch.load(f"{out}.{r}", weights_only=False) for r in range(world)]
+    for channels in (1, dk):
+        x = _inputs(B * S, H, dk, dv, channels, seed=3)
+        want = torch.cat([delta_rule_scan(*(a[lo:hi] for a in x)) for lo, hi in zip(cu[:-1], cu[1:])])
+        w = torch.randn(B * S, H, dv, generator=torch.Generator().manual_seed(9))
+        grads = torch.autograd.grad((want * w).sum(), x)
+        for rows, o, g in (p[channels] for p in parts):
+            assert torch.allclose(o, want[rows], atol=1e-5)
+            for got, full in zip(g, grads):
+                assert torch.allclose(got, full[rows], atol=1e-4)

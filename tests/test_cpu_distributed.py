@@ -137,3 +137,16 @@ def test_dist_muon_two_ranks_match_single_rank():
     ref = run_ranks(1, base_flat(optimizer_type="DistMuon", learning_rate=2e-2))
     got = run_ranks(2, base_flat(optimizer_type="DistMuon", learning_rate=2e-2, data_parallel_shard_size=2))
     _close(ref["loss"], got["loss"], 2e-3)
+
+
+@pytest.mark.parametrize("family,flat", [("kimi_linear", dict(context_parallel_kcp_size=2)),
+                                         ("qwen3_5", dict(context_parallel_kv_allgather_size=2))])
+def test_delta_attention_families_under_sequence_parallelism(family, flat):
+    """Delta-rule layers hand their recurrent state from rank to rank; the softmax / latent attention layers of the same
+    model gather keys and values over the same axis."""
+    arch = dict(head_dim=16, delta_heads=2, delta_head_dim=8, kv_lora_rank=16, qk_rope_dim=8, delta_chunk_size=8)
+    base = dict(model_name_or_path=family, num_hidden_layers=4)
+    ref = run_ranks(1, base_flat(**base), arch=arch)
+    got = run_ranks(2, base_flat(data_parallel_shard_size=1, **base, **flat), arch=arch)
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)

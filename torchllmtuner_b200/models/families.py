@@ -65,8 +65,11 @@ def delta_rule_scan(q, k, v, beta, log_decay):
     return torch.stack(outs)
 
 
-def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64):
-    """The same recurrence in chunk-parallel form. Inside a chunk of C tokens that starts from state S0, with the
+def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64, initial_state=None, return_state: bool = False):
+    """The same recurrence in chunk-parallel form (`initial_state` [H, dk, dv] instead of zero; `return_state` also
+    returns the state after the last token). The value columns evolve independently of each other, which sequence
+    parallelism uses: extra value columns that start as an identity come back as the segment's transition matrix.
+     Inside a chunk of C tokens that starts from state S0, with the
     cumulative log decay G_t, the pseudo-values u_t = beta_t (v_t - S'_t^T k_t) solve the triangular system
         (I + A) U = beta (V - K~ S0),   A[t, i] = beta_t sum_c k_t[c] k_i[c] exp(G_t[c] - G_i[c])   (i < t),
     with K~_t = exp(G_t) k_t; then O = Q~ S0 + tril(QK) U and S_end = exp(G_C) S0 + (exp(G_C - G) K)^T U.
@@ -105,14 +108,14 @@ def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64):
     Qt = eG * q
     Kend = (G[:, :, -1:, :] - G).exp() * k
     dec_end = G[:, :, -1, :].exp().unsqueeze(-1)                              # [N, H, dk | 1, 1]
-    S = q.new_zeros(H, dk, dv)
+    S = q.new_zeros(H, dk, dv) if initial_state is None else initial_state
     outs = []
     for n in range(N):
         U = W1[n] - W2[n] @ S
         outs.append(Qt[n] @ S + QK[n] @ U)
         S = dec_end[n] * S + Kend[n].transpose(1, 2) @ U
     o = torch.stack(outs).permute(0, 2, 1, 3).reshape(N * C, H, dv)
-    return o[:T]
+    return (o[:T], S) if return_state else o[:T]
 
 
 class DeltaRuleMixer(nn.Module):
@@ -138,10 +141,13 @@ class DeltaRuleMixer(nn.Module):
         v = self.v_proj(x).view(T, H, d).float()
         beta = torch.sigmoid(self.beta_proj(x).float())                                   # [T, H]
         log_decay = -F.softplus(self.decay_proj(x).float()).view(T, H, d if self.channel else 1)
-        cuts = sorted({0, T} | {int(i) for i in _doc_starts(ctx.attn_meta, T, "cpu").nonzero().flatten().tolist()})
-        outs = [chunked_delta_rule(q[a:b], k[a:b], v[a:b], beta[a:b], log_decay[a:b], self.chunk)
-                for a, b in zip(cuts[:-1], cuts[1:])]                                     # the state starts at zero per document
-        o = torch.cat(outs).to(x.dtype)                                                   # [T, H, d]
+        if ctx.cp is not None and ctx.cp.size > 1:
+            o = ctx.cp.delta_rule(q, k, v, beta, log_decay, self.chunk).to(x.dtype)       # state handed from rank to rank
+        else:
+            cuts = sorted({0, T} | {int(i) for i in _doc_starts(ctx.attn_meta, T, "cpu").nonzero().flatten().tolist()})
+            outs = [chunked_delta_rule(q[a:b], k[a:b], v[a:b], beta[a:b], log_decay[a:b], self.chunk)
+                    for a, b in zip(cuts[:-1], cuts[1:])]                                 # the state starts at zero per document
+            o = torch.cat(outs).to(x.dtype)                                               # [T, H, d]
         o = self.out_norm(o.reshape(T * H, d)).view(T, H * d) * F.silu(self.gate_proj(x))  # gated RMSNorm
         return self.o_proj(o)
 
@@ -157,7 +163,8 @@ class GatedAttention(Qwen3Attention):
         q, k, v = self.project_qkv(x)
         q, k = ops.qk_norm_rope(q, k, self.q_norm.weight if self.q_norm is not None else None,
                                 self.k_norm.weight if self.k_norm is not None else None, ctx.cos, ctx.sin, self.eps)
-        o = ops.attention(q, k, v, ctx.attn_meta, self.scale).reshape(x.shape[0], -1)
+        attend = ctx.cp.attention if ctx.cp is not None else ops.attention
+        o = attend(q, k, v, ctx.attn_meta, self.scale).reshape(x.shape[0], -1)
         if self.gate is not None:
             o = o * torch.sigmoid(self.gate(x))
         return self.o_proj(o)
@@ -196,7 +203,8 @@ class LatentAttention(nn.Module):
         kr = self._rope(self.k_rope(x).view(T, 1, self.dr), ctx.cos, ctx.sin).expand(T, H, self.dr)
         q = torch.cat((q[..., :self.dn], self._rope(q[..., self.dn:], ctx.cos, ctx.sin)), -1)
         k = torch.cat((kn, kr), -1)
-        o = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), ctx.attn_meta, self.scale)
+        attend = ctx.cp.attention if ctx.cp is not None else ops.attention
+        o = attend(q.contiguous(), k.contiguous(), v.contiguous(), ctx.attn_meta, self.scale)
         return self.o_proj(o.reshape(T, -1))
 
 
@@ -265,7 +273,9 @@ class HybridForCausalLM(Qwen3ForCausalLM):
     def validate_parallel(self, tp=1, cp_ulysses=1, ep=1):
         from ..errors import UnsupportedCombinationError
         if tp > 1 or cp_ulysses > 1:
-            raise UnsupportedCombinationError(f"{self.config.model_type}: tensor / context parallelism is defined for the Qwen3 family only")
+            raise UnsupportedCombinationError(f"{self.config.model_type}: tensor parallelism and Ulysses context parallelism are defined for the "
+                                              "Qwen3 family only (sequence parallelism of the delta-rule layers hands the state "
+                                              "from rank to rank: context_parallel_kcp_size / context_parallel_kv_allgather_size)")
         super().validate_parallel(1, 1, ep)
 
     def forward(self, tokens, ctx, skip_lm_head=False, inputs_embeds=None):

@@ -103,7 +103,7 @@ class ContextParallelDriver:
         dev = inputs["tokens"].device
         B, S = inputs["batch"], inputs["seq"]
         gcu = inputs.get("global_cu_seqlens", inputs["cu_seqlens"]).tolist()
-        mb = {"B": B, "S": S}
+        mb = {"B": B, "S": S, "gcu": [int(c) for c in gcu]}
         if self.strategy == "ulysses":
             mb["meta"] = AttnMeta.build(gcu, causal=True, device=dev)
         else:
@@ -171,8 +171,68 @@ class ContextParallelDriver:
         return cp_all_to_all(o, self.group_ul, False) if self.strategy == "hybrid" else o
 
 
-def apply_cp(model, topo, cp_config) -> ContextParallelDriver:
-    if topo.kcp > 1:
+    # ------------------------------------------------------------------ delta rule (recurrent state across ranks)
+    def delta_rule(self, q, k, v, beta, log_decay, chunk: int):
+        """Sequence-parallel gated delta rule (reference: llmtuner/parallel/context_parallel/kcp.py:30-335). Every rank
+        owns one contiguous span of each sequence. The recurrence is linear in the state, and its value columns evolve
+        independently, so one pass over the local span with dk extra value columns that start as an identity yields the
+        span's outputs from a zero state, its end state Sigma and its transition matrix Phi (end = Phi start + Sigma).
+        (Phi, Sigma) of all ranks are gathered, every rank folds those of the ranks before it into its incoming state,
+        and adds the incoming state's contribution to the outputs of the document that continues across its left
+        edge. A document that starts inside a span cuts the chain: Phi = 0 for that rank."""
         from ..errors import UnsupportedCombinationError
-        raise UnsupportedCombinationError("kcp context parallelism applies to delta-attention models only")
+        from ..models.families import chunked_delta_rule
+        mb = self._mb
+        if self.strategy != "kv_allgather" or self.load_balancer is not None:
+            raise UnsupportedCombinationError("the delta-rule layers need contiguous sequence spans: use context_parallel_kcp_size or "
+                                              "context_parallel_kv_allgather_size without a load balancer")
+        B, S, R, r = mb["B"], mb["S"], self.size, self.rank
+        gcu = mb["gcu"]
+        t = S // R
+        H, dk, dv = q.shape[1], q.shape[2], v.shape[2]
+        eye = torch.eye(dk, dtype=q.dtype, device=q.device).expand(H, dk, dk)
+        outs, exports, firsts = [], [], []
+        for b in range(B):
+            lo, hi = b * S + r * t, b * S + (r + 1) * t                       # global rows of this local span
+            starts = [c for c in gcu if lo < c < hi]
+            cuts = [lo] + starts + [hi]
+            continues = r > 0 and lo not in gcu                                # a document crosses the left edge
+            seg_out = []
+            for i, (a, e) in enumerate(zip(cuts[:-1], cuts[1:])):
+                sl = slice(b * t + a - lo, b * t + e - lo)
+                last = i == len(cuts) - 2
+                if last:                                                       # the segment whose end state leaves this rank
+                    carry = continues and len(cuts) == 2
+                    vx = torch.cat((v[sl], v.new_zeros(e - a, H, dk)), -1) if carry else v[sl]
+                    s0 = torch.cat((v.new_zeros(H, dk, dv), eye), -1) if carry else None
+                    o, st = chunked_delta_rule(q[sl], k[sl], vx, beta[sl], log_decay[sl], chunk, s0, True)
+                    phi = st[..., dv:] if carry else st.new_zeros(H, dk, dk)
+                    exports.append(torch.cat((st[..., :dv], phi), -1))        # [H, dk, dv + dk]
+                    o = o[..., :dv]
+                else:
+                    o = chunked_delta_rule(q[sl], k[sl], v[sl], beta[sl], log_decay[sl], chunk)
+                seg_out.append(o)
+            firsts.append((slice(b * t, b * t + cuts[1] - lo), continues))
+            outs.append(seg_out)
+        mine = torch.stack(exports).unsqueeze(0)                              # [1, B, H, dk, dv + dk]
+        every = _AllGatherRowsCP.apply(mine, self.group, None)                # [R, B, H, dk, dv + dk]
+        result = []
+        for b in range(B):
+            sl, continues = firsts[b]
+            if continues and r > 0:
+                state = every[0, b, ..., :dv]
+                for p in range(1, r):
+                    state = every[p, b, ..., dv:] @ state + every[p, b, ..., :dv]
+                # contribution of the incoming state to the first segment: the same recurrence without new values
+                corr = chunked_delta_rule(q[sl], k[sl], torch.zeros_like(v[sl]), beta[sl], log_decay[sl], chunk, state)
+                outs[b][0] = outs[b][0] + corr
+            result.extend(outs[b])
+        # every rank keeps the gathered tensor in its graph, so that all of them enter its backward collective
+        result[0] = result[0] + 0.0 * every.sum()
+        return torch.cat(result)
+
+
+def apply_cp(model, topo, cp_config) -> ContextParallelDriver:
+    """`kcp` is the sequence axis of delta-attention models: softmax / latent attention layers gather keys and values
+    over it, delta-rule layers hand their recurrent state from rank to rank (`ContextParallelDriver.delta_rule`)."""
     return ContextParallelDriver(topo, cp_config)
