@@ -378,6 +378,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t o
 // double buffered in TMEM, Q / dO and P^T / dS^T are double buffered in shared memory, so the MMAs of q tile i+1 run
 // while the 128 compute threads turn S^T, dP^T of tile i into P^T, dS^T; dV and dK accumulate in TMEM over the whole walk.
 constexpr int kBwdQ = 64;
+constexpr int kBwdQStages = 3;   // Q / dO stages of the dK/dV kernel
 constexpr int kBwdThreads = 64 + 256;   // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter, one per column half)
 
 template <int HD>
@@ -395,23 +396,25 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + kKVBytes;
-  uint8_t* sQ = sV + kKVBytes;          // 2 stages
-  uint8_t* sdO = sQ + 2 * kQBytes;      // 2 stages
-  uint8_t* sPT = sdO + 2 * kQBytes;     // 2 buffers
+  // Q / dO tiles have three stages: a stage is free again only when the dV / dK products that read it have completed,
+  // and with two stages the reload (a full TMA round trip) sat on the critical path of every iteration.
+  uint8_t* sQ = sV + kKVBytes;              // kBwdQStages stages
+  uint8_t* sdO = sQ + kBwdQStages * kQBytes;
+  uint8_t* sPT = sdO + kBwdQStages * kQBytes;   // 2 buffers
   uint8_t* sdST = sPT + 2 * kPBytes;    // 2 buffers
   float* s_lse = reinterpret_cast<float*>(sdST + 2 * kPBytes);   // [2][64]
   float* s_delta = s_lse + 2 * kBwdQ;                            // [2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * kBwdQ);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;     // [2]
-  uint64_t* qdo_empty = bars + 3;    // [2]
-  uint64_t* s_full = bars + 5;       // [2]
-  uint64_t* s_empty = bars + 7;      // [2]
-  uint64_t* p_full = bars + 9;       // [2]
-  uint64_t* p_empty = bars + 11;     // [2]
-  uint64_t* acc_done = bars + 13;
-  uint64_t* stat_ready = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* qdo_full = bars + 1;     // [kBwdQStages]
+  uint64_t* qdo_empty = bars + 4;    // [kBwdQStages]
+  uint64_t* s_full = bars + 7;       // [2]
+  uint64_t* s_empty = bars + 9;      // [2]
+  uint64_t* p_full = bars + 11;      // [2]
+  uint64_t* p_empty = bars + 13;     // [2]
+  uint64_t* acc_done = bars + 15;
+  uint64_t* stat_ready = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -427,8 +430,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
+    for (int b = 0; b < kBwdQStages; ++b) { mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1); }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&qdo_full[b], 1); mbar_init(&qdo_empty[b], 1);
       mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 256);
       mbar_init(&p_full[b], 256); mbar_init(&p_empty[b], 1);
     }
@@ -452,10 +455,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_3d(sK + hf * 16384, &tmK, kv_full, hf * 64, hk, k0);
         tma_load_3d(sV + hf * 16384, &tmV, kv_full, hf * 64, hk, k0);
       }
-      int armed[2] = {-1, -1};
+      int armed[kBwdQStages] = {-1, -1, -1};
       for (int it = 0; it < n_it; ++it) {
-        const int b = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int b = it % kBwdQStages;
+        const uint32_t ph = (it / kBwdQStages) & 1;
         const int h = hk * g + it / n_qt;
         const int qrow = qbeg + qs + (it % n_qt) * kBwdQ;
         if (!mbar_wait_bounded(&qdo_empty[b], ph ^ 1, abort_flag, status, 2100 + b)) break;
@@ -469,7 +472,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (*abort_flag) {
         for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(kv_full, 0)) break;
-        for (int b = 0; b < 2; ++b)
+        for (int b = 0; b < kBwdQStages; ++b)
           if (armed[b] >= 0)
             for (uint32_t i = 0; i < (1u << 16); ++i) if (mbar_try_wait(&qdo_full[b], (uint32_t)armed[b])) break;
       }
@@ -485,15 +488,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       auto issue_S = [&](int it) -> bool {
         const int b = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait_bounded(&qdo_full[b], ph, abort_flag, status, 2210 + b)) return false;
+        const int qb = it % kBwdQStages;                       // Q / dO stage
+        if (!mbar_wait_bounded(&qdo_full[qb], (it / kBwdQStages) & 1, abort_flag, status, 2210 + qb)) return false;
         if (!mbar_wait_bounded(&s_empty[b], ph ^ 1, abort_flag, status, 2215 + b)) return false;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tST + b * kBwdQ, desc_kmajor_rows(aK, ks, 128), desc_kmajor_rows(aQ + b * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tST + b * kBwdQ, desc_kmajor_rows(aK, ks, 128), desc_kmajor_rows(aQ + qb * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tDPT + b * kBwdQ, desc_kmajor_rows(aV, ks, 128), desc_kmajor_rows(adO + b * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tDPT + b * kBwdQ, desc_kmajor_rows(aV, ks, 128), desc_kmajor_rows(adO + qb * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
         umma_commit(&s_full[b]);
         return true;
       };
@@ -501,16 +505,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t ph = (it >> 1) & 1;
+        const int qb = it % kBwdQStages;
         if (it + 1 < n_it) { if (!issue_S(it + 1)) break; }
         if (!mbar_wait_bounded(&p_full[b], ph, abort_flag, status, 2220 + b)) break;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kBwdQ / 16; ++ks)
-          umma_bf16_ss(tDV, desc_kmajor_rows(aPT + b * kPBytes, ks, 128), desc_mnmajor_rows(adO + b * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
+          umma_bf16_ss(tDV, desc_kmajor_rows(aPT + b * kPBytes, ks, 128), desc_mnmajor_rows(adO + qb * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < kBwdQ / 16; ++ks)
-          umma_bf16_ss(tDK, desc_kmajor_rows(adST + b * kPBytes, ks, 128), desc_mnmajor_rows(aQ + b * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
-        umma_commit(&qdo_empty[b]);
+          umma_bf16_ss(tDK, desc_kmajor_rows(adST + b * kPBytes, ks, 128), desc_mnmajor_rows(aQ + qb * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
+        umma_commit(&qdo_empty[qb]);
         umma_commit(&p_empty[b]);
         if (it == n_it - 1) umma_commit(acc_done);
       }
@@ -930,7 +935,7 @@ extern "C" int llmt_attn_bwd(const void* q, const void* k, const void* v, const 
     return -11;
   CUtensorMap tq64, tdo64;   // 64-row boxes for the dK/dV kernel's q tiles
   if (make_thd_map(&tq64, q, Tq, Hq, HD, q_stride, kBwdQ) || make_thd_map(&tdo64, dout, Tq, Hq, HD, do_stride, kBwdQ)) return -11;
-  const int smem_kv = 2 * 128 * HD * 2 + 4 * kBwdQ * HD * 2 + 4 * 128 * kBwdQ * 2 + 4 * kBwdQ * 4 + 1024 + 256;
+  const int smem_kv = 2 * 128 * HD * 2 + 2 * kBwdQStages * kBwdQ * HD * 2 + 4 * 128 * kBwdQ * 2 + 4 * kBwdQ * 4 + 1024 + 256;
   const int smem_q = 6 * 128 * HD * 2 + 128 * 128 * 2 + 1024 + 256;
   if (HD == 128) {
     static bool cfg = false;

@@ -122,6 +122,9 @@ class DeltaRuleMixer(nn.Module):
     """Gated delta rule: S_t = a_t * S_{t-1} (I - b_t k_t k_t^T) + b_t k_t v_t^T ; o_t = S_t^T q_t, per head, state reset
     at document starts. `channel_decay` makes a_t a vector over the key dimension (KDA)."""
 
+    # tensor parallelism cuts every projection by heads; the output norm (over head_dim) stays replicated
+    tp_cut = {"colwise": ("q_proj", "k_proj", "v_proj", "beta_proj", "decay_proj", "gate_proj"), "rowwise": ("o_proj",), "heads": ("H",)}
+
     def __init__(self, cfg: HybridConfig, dtype=None, device=None):
         super().__init__()
         D, H, d = cfg.hidden_size, cfg.delta_heads, cfg.delta_head_dim
@@ -154,6 +157,8 @@ class DeltaRuleMixer(nn.Module):
 
 class GatedAttention(Qwen3Attention):
     """Softmax attention whose output is multiplied by sigmoid(W_g x) before the output projection."""
+    accepts_sharded_rows = False    # the gate reads the complete rows too
+    tp_cut = {"colwise": ("q_proj", "k_proj", "v_proj", "gate"), "rowwise": ("o_proj",), "heads": ("num_heads", "num_kv_heads")}
 
     def __init__(self, cfg: HybridConfig, dtype=None, device=None):
         super().__init__(cfg, dtype, device)
@@ -173,6 +178,8 @@ class GatedAttention(Qwen3Attention):
 class LatentAttention(nn.Module):
     """Multi-head latent attention: keys and values are up-projected from a shared low-rank latent; a small rotary key
     shared by all heads is concatenated to the per-head non-rotary key."""
+    # tensor parallelism: per-head projections are cut, the latent down-projection, its norm and the rotary key stay whole
+    tp_cut = {"colwise": ("q_proj", "k_up", "v_up"), "rowwise": ("o_proj",), "heads": ("H",)}
 
     def __init__(self, cfg: HybridConfig, dtype=None, device=None):
         super().__init__()
@@ -272,11 +279,17 @@ class HybridForCausalLM(Qwen3ForCausalLM):
 
     def validate_parallel(self, tp=1, cp_ulysses=1, ep=1):
         from ..errors import UnsupportedCombinationError
-        if tp > 1 or cp_ulysses > 1:
-            raise UnsupportedCombinationError(f"{self.config.model_type}: tensor parallelism and Ulysses context parallelism are defined for the "
-                                              "Qwen3 family only (sequence parallelism of the delta-rule layers hands the state "
-                                              "from rank to rank: context_parallel_kcp_size / context_parallel_kv_allgather_size)")
-        super().validate_parallel(1, 1, ep)
+        c = self.config
+        if cp_ulysses > 1:
+            raise UnsupportedCombinationError(f"{c.model_type}: Ulysses context parallelism is defined for the Qwen3 family only (the "
+                                              "delta-rule layers hand their state from rank to rank: context_parallel_kcp_size / "
+                                              "context_parallel_kv_allgather_size)")
+        kinds = {c.mixer_pattern[i % len(c.mixer_pattern)] for i in range(c.num_hidden_layers)}
+        if tp > 1 and kinds & {"delta", "kda"} and c.delta_heads % tp:
+            raise UnsupportedCombinationError(f"tensor_parallel_size {tp} must divide delta_heads {c.delta_heads}")
+        if tp > 1 and "mla" in kinds and c.num_attention_heads % tp:
+            raise UnsupportedCombinationError(f"tensor_parallel_size {tp} must divide num_attention_heads {c.num_attention_heads}")
+        super().validate_parallel(tp if "attention" in kinds else 1, 1, ep)
 
     def forward(self, tokens, ctx, skip_lm_head=False, inputs_embeds=None):
         n = self.config.hyper_connection_streams

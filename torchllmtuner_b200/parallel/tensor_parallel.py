@@ -283,13 +283,22 @@ def apply_tp(model, topo, tp_config) -> dict:
         attn = bound.attention_of(block)
         if getattr(attn, "fused_qkv", False):
             raise UnsupportedCombinationError("fused QKV projection cannot be column-sharded per projection")
-        for name in ("q_proj", "k_proj", "v_proj"):
+        # the mixer names its own cut: projections split by heads (column shards), the output projection (input shard)
+        # and the head counters that shrink with it; the default is the q/k/v/o layout of softmax attention
+        cut = getattr(attn, "tp_cut", None) or {"colwise": ("q_proj", "k_proj", "v_proj"), "rowwise": ("o_proj",),
+                                                 "heads": ("num_heads", "num_kv_heads")}
+        for name in cut["colwise"]:
+            if getattr(attn, name, None) is None:
+                continue
             setattr(attn, name, ColwiseLinearNoGather(getattr(attn, name), rank, size))
             applied[f"layers.{key}.self_attn.{name}"] = "colwise"
-        attn.o_proj = RowParallelLinear(attn.o_proj, rank, size, group)
-        applied[f"layers.{key}.self_attn.o_proj"] = "rowwise"
-        attn.num_heads //= size
-        attn.num_kv_heads //= size
+        for name in cut["rowwise"]:
+            setattr(attn, name, RowParallelLinear(getattr(attn, name), rank, size, group))
+            applied[f"layers.{key}.self_attn.{name}"] = "rowwise"
+        for name in cut["heads"]:
+            if getattr(attn, name) % size:
+                raise UnsupportedCombinationError(f"tensor_parallel_size {size} does not divide {type(attn).__name__}.{name} = {getattr(attn, name)}")
+            setattr(attn, name, getattr(attn, name) // size)
         setattr(block, model.decoder_structure.attention, GatherSequenceFirst(attn, group))
         mlp = bound.mlp_of(block)
         if isinstance(mlp, MoE):
