@@ -150,3 +150,15 @@ def test_delta_attention_families_under_sequence_parallelism(family, flat):
     got = run_ranks(2, base_flat(data_parallel_shard_size=1, **base, **flat), arch=arch)
     _close(ref["loss"], got["loss"], 5e-5)
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
+@pytest.mark.parametrize("family", ["qwen3_5", "kimi_linear", "deepseek_v4"])
+def test_hybrid_families_under_tensor_parallelism(family):
+    """Every mixer names its own cut (delta rule: all projections by heads; latent attention: per-head projections cut,
+    latent down-projection and rotary key whole; gated attention: q/k/v/gate by heads)."""
+    arch = dict(head_dim=16, delta_heads=2, delta_head_dim=8, kv_lora_rank=16, qk_rope_dim=8, delta_chunk_size=8)
+    base = dict(model_name_or_path=family, num_hidden_layers=4)
+    ref = run_ranks(1, base_flat(**base), arch=arch)
+    got = run_ranks(2, base_flat(tensor_parallel_size=2, data_parallel_shard_size=1, **base), arch=arch)
+    _close(ref["loss"], got["loss"], 5e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 5e-4)

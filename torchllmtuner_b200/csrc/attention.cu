@@ -13,6 +13,7 @@
 // the TMEM-resident O), P through shared memory, O += P V.  Backward: a dK/dV kernel per (k tile, kv head) that
 // loops over the query heads of the group and the q tiles, and a dQ kernel per (q tile, head); both recompute
 // S and dP so that no atomics are needed.
+#include <type_traits>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -566,29 +567,38 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();
       mbar_arrive(&s_empty[b]);
       if (!mbar_wait_bounded(&p_empty[b], ph ^ 1, abort_flag, status, 2310 + b)) { ok = false; break; }
-      const float* pl = s_lse + b * kBwdQ;
-      const float* pd = s_delta + b * kBwdQ;
-      {
-        const int c = half;
-        uint32_t wp[16], wd[16];
+      // Most tiles lie wholly below the causal diagonal and inside the document: they skip the per-element visibility
+      // test (the branch is uniform over the CTA). Row statistics come from shared memory four at a time.
+      const bool tile_full = (nk == 128) && (kk0 + 128 <= klen) && (qi0 + kBwdQ <= qlen) && (!causal || kk0 + 127 <= qi0 + off);
+      const float4* pl4 = reinterpret_cast<const float4*>(s_lse + b * kBwdQ + half * 32);
+      const float4* pd4 = reinterpret_cast<const float4*>(s_delta + b * kBwdQ + half * 32);
+      uint32_t wp[16], wd[16];
+      auto softmax_cols = [&](auto masked) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p[2], ds[2];
+        for (int i = 0; i < 32; i += 4) {
+          const float4 l4 = pl4[i >> 2], d4 = pd4[i >> 2];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float p[4], ds[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int qc = c * 32 + i + e;
-            const int qi = qi0 + qc;
-            const bool vis = key_ok && (qi < qlen) && (!causal || key_idx <= qi + off);
-            const float pv = vis ? ex2(__uint_as_float(rs[i + e]) * scale_log2 - pl[qc]) : 0.f;
+          for (int e = 0; e < 4; ++e) {
+            float pv = ex2(__uint_as_float(rs[i + e]) * scale_log2 - lv[e]);
+            if constexpr (decltype(masked)::value) {
+              const int qi = qi0 + half * 32 + i + e;
+              const bool vis = key_ok && (qi < qlen) && (!causal || key_idx <= qi + off);
+              pv = vis ? pv : 0.f;
+            }
             p[e] = pv;
-            ds[e] = pv * (__uint_as_float(rd[i + e]) - pd[qc]);
+            ds[e] = pv * (__uint_as_float(rd[i + e]) - dv[e]);
           }
           wp[i >> 1] = pack_bf16x2(p[0], p[1]);
+          wp[(i >> 1) + 1] = pack_bf16x2(p[2], p[3]);
           wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+          wd[(i >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
         }
-        store_row32_swz(sPT + b * kPBytes, row, c * 32, wp);
-        store_row32_swz(sdST + b * kPBytes, row, c * 32, wd);
-      }
+      };
+      if (tile_full) softmax_cols(std::false_type{}); else softmax_cols(std::true_type{});
+      store_row32_swz(sPT + b * kPBytes, row, half * 32, wp);
+      store_row32_swz(sdST + b * kPBytes, row, half * 32, wd);
       fence_proxy_async_smem();
       mbar_arrive(&p_full[b]);
       if (have_next) {
@@ -677,7 +687,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* dp_full = bars + 11;
   uint64_t* ds_full = bars + 12;
   uint64_t* dq_done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* dp_empty = bars + 14;    // the softmax warps hold dP of the current tile in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -695,6 +706,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&kfull[s], 1); mbar_init(&kempty[s], 1); mbar_init(&vfull[s], 1); mbar_init(&vempty[s], 1);
     }
     mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1); mbar_init(dp_full, 1); mbar_init(ds_full, 256); mbar_init(dq_done, 1);
+    mbar_init(dp_empty, 256);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -772,11 +784,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
         // S of the next tile goes into the other TMEM buffer while the softmax warps are busy with tile j
-        if (j + 1 < n_kv) { if (!issue_S(j + 1)) break; }
+        if (j + 1 < n_kv) {
+          if (!issue_S(j + 1)) break;
+          // dP has one TMEM buffer: the next product starts as soon as the softmax warps have copied this tile's dP
+          // into registers, not when they have finished its math, so it runs under that math
+          if (!mbar_wait_bounded(dp_empty, j & 1, abort_flag, status, 3225)) break;
+          if (!issue_dP(j + 1)) break;
+        }
         if (!mbar_wait_bounded(ds_full, j & 1, abort_flag, status, 3230)) break;
         tc_fence_after();
-        // dP of the next tile first (the softmax warps wait for it), then dQ of this tile
-        if (j + 1 < n_kv) { if (!issue_dP(j + 1)) break; }
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma_bf16_ss(tDQ, desc_kmajor(adS, ks), desc_mnmajor(aK + s * SM::kTile, ks), idDQ, (j | ks) ? 1u : 0u);
@@ -802,24 +818,31 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       const uint32_t tS = (j & 1) ? tS1 : tS0;
       const int kbase = j * 128;
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
-        uint32_t rs[32], rd[32], wd[16];
-        tmem_ld_32x32(tS + lane_off + c * 32, rs);
-        tmem_ld_32x32(tDP + lane_off + c * 32, rd);
-        tmem_wait_ld();
+      uint32_t rs[2][32], rd[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld_32x32(tS + lane_off + (half * 2 + cc) * 32, rs[cc]);
+        tmem_ld_32x32(tDP + lane_off + (half * 2 + cc) * 32, rd[cc]);
+      }
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(dp_empty);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        uint32_t wd[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float ds[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const bool vis = kbase + c * 32 + i + e < row_limit;
-            const float p = vis ? ex2(__uint_as_float(rs[i + e]) * scale_log2 - lse2) : 0.f;
-            ds[e] = p * (__uint_as_float(rd[i + e]) - dl);
+            const float p = vis ? ex2(__uint_as_float(rs[cc][i + e]) * scale_log2 - lse2) : 0.f;
+            ds[e] = p * (__uint_as_float(rd[cc][i + e]) - dl);
           }
           wd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
         }
-        if (j > 0 && c == half * 2) {   // dQ of the previous tile still reads the dS buffer until its MMAs complete
+        if (j > 0 && cc == 0) {   // dQ of the previous tile still reads the dS buffer until its MMAs complete
           if (!mbar_wait_bounded(dq_done, (j - 1) & 1, abort_flag, status, 3310)) { ok = false; break; }
         }
         store_row32_swz(sdS, row, c * 32, wd);
