@@ -82,7 +82,7 @@ def mrope_tables(positions: torch.Tensor, head_dim: int, theta: float, sections=
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim))
     axis = torch.repeat_interleave(torch.arange(3, device=positions.device), torch.tensor(sections, device=positions.device))
     pos = positions.float()[axis]                              # [half, T]: the axis each frequency follows
-    ang = pos.t() * inv[None, :]
+    ang = (pos.t() * inv[None, :]).contiguous()       # the rotary kernel wants dense fp32 tables
     return ang.cos(), ang.sin()
 
 

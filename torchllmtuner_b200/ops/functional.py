@@ -87,6 +87,10 @@ class _Linear(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if _use_cuda(x) and x.dtype == torch.bfloat16:
+        if w.shape[0] % 8 or w.shape[1] % 8:
+            # a TMA row must start on a 16-byte boundary: projections with fewer than 8 (or an odd number of) features,
+            # e.g. one gate value per head, cannot be tiled by the tcgen05 kernel and take the plain library product
+            return ref.linear(x, w)
         return _Linear.apply(x, w)
     return ref.linear(x, w)
 
