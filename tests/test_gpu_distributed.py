@@ -108,3 +108,20 @@ def test_peer_that_never_arrives_becomes_an_error_on_every_rank():
     assert v0.startswith("own:") and "flag" in v0 and "7401" in v0, (v0, v1)
     assert v1.startswith("peer:") and "all-gather of step 7" in v1, (v0, v1)
     assert ok0 and ok1
+
+
+HYBRID = dict(head_dim=64, delta_heads=4, delta_head_dim=64, kv_lora_rank=64, qk_rope_dim=32)
+
+
+@pytest.mark.parametrize("name,flat", [
+    ("kimi_kcp2", dict(model_name_or_path="kimi_linear", context_parallel_kcp_size=2, data_parallel_shard_size=1)),
+    ("qwen3_5_tp2", dict(model_name_or_path="qwen3_5", tensor_parallel_size=2, data_parallel_shard_size=1)),
+    ("kimi_tp2", dict(model_name_or_path="kimi_linear", tensor_parallel_size=2, data_parallel_shard_size=1)),
+])
+def test_hybrid_families_sequence_and_tensor_parallel_on_gpus(name, flat):
+    """Delta-rule state handed across ranks (kcp) and the mixers' own tensor-parallel cuts, on NCCL and the CUDA kernels."""
+    _need(2)
+    base = dict(model_name_or_path=flat["model_name_or_path"], num_hidden_layers=4)
+    ref = run_ranks(1, _flat(**base), arch=HYBRID, device="cuda")
+    got = run_ranks(2, _flat(num_hidden_layers=4, **flat), arch=HYBRID, device="cuda")
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (name, ref, got)
