@@ -77,6 +77,23 @@ __device__ __forceinline__ uint64_t desc_mnmajor_rows(uint32_t base, int ks, int
   return umma_desc_sw128(base + ks * 2048, rows * 128, 1024);
 }
 
+// The MMA warp is one thread, and every instruction it spends between two tcgen05.mma delays the next product. The
+// descriptor's upper word (stride byte offset 1024, version, 128-byte swizzle) never changes, so the loops keep the lower
+// word of each operand (start address and leading byte offset) and add the slice's offset to it: one integer add per
+// operand instead of rebuilding the 64-bit descriptor.
+constexpr uint32_t kDescHi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t desc_pack(uint32_t lo) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+  return d;
+}
+// offset (in 16-byte units) of 16-column slice `ks` of a K-major tile with `rows` rows / of 16-row slice `ks` read MN-major
+__host__ __device__ constexpr uint32_t koff(int ks, int rows) { return (uint32_t)(((ks >> 2) * (rows * 128) + (ks & 3) * 32) >> 4); }
+__host__ __device__ constexpr uint32_t mnoff(int ks) { return (uint32_t)((ks * 2048) >> 4); }
+
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -486,6 +503,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aPT = smem_u32(sPT),
                      adST = smem_u32(sdST);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, status, 2200);
+      const uint32_t loK = desc_lo(aK, 16), loV = desc_lo(aV, 16);
       auto issue_S = [&](int it) -> bool {
         const int b = it & 1;
         const uint32_t ph = (it >> 1) & 1;
@@ -493,12 +511,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait_bounded(&qdo_full[qb], (it / kBwdQStages) & 1, abort_flag, status, 2210 + qb)) return false;
         if (!mbar_wait_bounded(&s_empty[b], ph ^ 1, abort_flag, status, 2215 + b)) return false;
         tc_fence_after();
+        const uint32_t loQ = desc_lo(aQ + qb * kQBytes, 16), lodO = desc_lo(adO + qb * kQBytes, 16);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tST + b * kBwdQ, desc_kmajor_rows(aK, ks, 128), desc_kmajor_rows(aQ + qb * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tST + b * kBwdQ, desc_pack(loK + koff(ks, 128)), desc_pack(loQ + koff(ks, kBwdQ)), idS, ks ? 1u : 0u);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tDPT + b * kBwdQ, desc_kmajor_rows(aV, ks, 128), desc_kmajor_rows(adO + qb * kQBytes, ks, kBwdQ), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tDPT + b * kBwdQ, desc_pack(loV + koff(ks, 128)), desc_pack(lodO + koff(ks, kBwdQ)), idS, ks ? 1u : 0u);
         umma_commit(&s_full[b]);
         return true;
       };
@@ -510,12 +529,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (it + 1 < n_it) { if (!issue_S(it + 1)) break; }
         if (!mbar_wait_bounded(&p_full[b], ph, abort_flag, status, 2220 + b)) break;
         tc_fence_after();
+        const uint32_t loPT = desc_lo(aPT + b * kPBytes, 16), lodST = desc_lo(adST + b * kPBytes, 16);
+        const uint32_t lodOm = desc_lo(adO + qb * kQBytes, kBwdQ * 128), loQm = desc_lo(aQ + qb * kQBytes, kBwdQ * 128);
+        const uint32_t acc0 = it ? 1u : 0u;
 #pragma unroll
         for (int ks = 0; ks < kBwdQ / 16; ++ks)
-          umma_bf16_ss(tDV, desc_kmajor_rows(aPT + b * kPBytes, ks, 128), desc_mnmajor_rows(adO + qb * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
+          umma_bf16_ss(tDV, desc_pack(loPT + koff(ks, 128)), desc_pack(lodOm + mnoff(ks)), idAcc, ks ? 1u : acc0);
 #pragma unroll
         for (int ks = 0; ks < kBwdQ / 16; ++ks)
-          umma_bf16_ss(tDK, desc_kmajor_rows(adST + b * kPBytes, ks, 128), desc_mnmajor_rows(aQ + qb * kQBytes, ks, kBwdQ), idAcc, (it | ks) ? 1u : 0u);
+          umma_bf16_ss(tDK, desc_pack(lodST + koff(ks, 128)), desc_pack(loQm + mnoff(ks)), idAcc, ks ? 1u : acc0);
         umma_commit(&qdo_empty[qb]);
         umma_commit(&p_empty[b]);
         if (it == n_it - 1) umma_commit(acc_done);
@@ -759,13 +781,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t idDQ = umma_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), adS = smem_u32(sdS);
       bool ok = mbar_wait_bounded(qdo_full, 0, abort_flag, status, 3200);
+      const uint32_t loQ = desc_lo(aQ, 16), lodO = desc_lo(adO, 16), lodS = desc_lo(adS, 16);
       auto issue_S = [&](int j) -> bool {
         const int s = j & 1;
         if (!mbar_wait_bounded(&kfull[s], (j >> 1) & 1, abort_flag, status, 3210 + s)) return false;
         tc_fence_after();
+        const uint32_t loKs = desc_lo(aK + s * SM::kTile, 16);
+        const uint32_t tSj = s ? tS1 : tS0;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(s ? tS1 : tS0, desc_kmajor(aQ, ks), desc_kmajor(aK + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tSj, desc_pack(loQ + koff(ks, 128)), desc_pack(loKs + koff(ks, 128)), idS, ks ? 1u : 0u);
         umma_commit(&s_full[s]);
         return true;
       };
@@ -773,9 +798,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int s = j & 1;
         if (!mbar_wait_bounded(&vfull[s], (j >> 1) & 1, abort_flag, status, 3220 + s)) return false;
         tc_fence_after();
+        const uint32_t loVs = desc_lo(aV + s * SM::kTile, 16);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_bf16_ss(tDP, desc_kmajor(adO, ks), desc_kmajor(aV + s * SM::kTile, ks), idS, ks ? 1u : 0u);
+          umma_bf16_ss(tDP, desc_pack(lodO + koff(ks, 128)), desc_pack(loVs + koff(ks, 128)), idS, ks ? 1u : 0u);
         umma_commit(dp_full);
         umma_commit(&vempty[s]);
         return true;
@@ -793,9 +819,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         if (!mbar_wait_bounded(ds_full, j & 1, abort_flag, status, 3230)) break;
         tc_fence_after();
+        const uint32_t loKm = desc_lo(aK + s * SM::kTile, 16384);
+        const uint32_t acc0 = j ? 1u : 0u;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tDQ, desc_kmajor(adS, ks), desc_mnmajor(aK + s * SM::kTile, ks), idDQ, (j | ks) ? 1u : 0u);
+          umma_bf16_ss(tDQ, desc_pack(lodS + koff(ks, 128)), desc_pack(loKm + mnoff(ks)), idDQ, ks ? 1u : acc0);
         umma_commit(&kempty[s]);
         umma_commit(dq_done);
       }
