@@ -202,6 +202,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idS = umma_idesc_bf16(128, kFwdKV, false, false);
       constexpr uint32_t idPV = umma_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+      const uint32_t loVm = desc_lo(aV, kFwdKV * 128);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, status, 1200);
       auto issue_S = [&](int j) -> bool {
         const int s = j & 1;
@@ -238,9 +239,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait_bounded(vfull, j & 1, abort_flag, status, 1240)) break;
         tc_fence_after();
         LLMT_TL(1, j, 3);
+        const uint32_t loP = desc_lo(aP + pb * kPBytes, 16), acc0 = j ? 1u : 0u;
 #pragma unroll
         for (int ks = 0; ks < kFwdKV / 16; ++ks)
-          umma_bf16_ss(tO, desc_kmajor_rows(aP + pb * kPBytes, ks, 128), desc_mnmajor_rows(aV, ks, kFwdKV), idPV, (j | ks) ? 1u : 0u);
+          umma_bf16_ss(tO, desc_pack(loP + koff(ks, 128)), desc_pack(loVm + mnoff(ks)), idPV, ks ? 1u : acc0);
         umma_commit(vempty);
         umma_commit(&pvdone[pb]);
         LLMT_TL(1, j, 4);
