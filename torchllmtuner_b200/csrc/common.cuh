@@ -217,6 +217,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   return d;
 }
 
+// The MMA warp is one thread, and every instruction it spends between two tcgen05.mma delays the next product. The
+// descriptor's upper word (stride byte offset 1024, version, 128-byte swizzle) never changes, so the loops keep the lower
+// word of each operand (start address and leading byte offset) and add the slice's offset to it: one integer add per
+// operand instead of rebuilding the 64-bit descriptor.
+constexpr uint32_t kDescHi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t desc_pack(uint32_t lo) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+  return d;
+}
 // Instruction descriptor: bf16 x bf16 -> fp32, dense. a_mn / b_mn select MN-major operands.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, bool a_mn, bool b_mn) {
   return (1u << 4)                       // D format fp32

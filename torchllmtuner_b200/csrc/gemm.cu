@@ -227,11 +227,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint32_t sb = sa + Cfg::kABytes;
+          const uint32_t la = desc_lo(sa, A_MN ? BK * 128 : 16), lb = desc_lo(sb, B_MN ? BK * 128 : 16);
+          const uint32_t acc0 = kb ? 1u : 0u;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = A_MN ? umma_desc_sw128(sa + k * 2048, BK * 128, 1024) : umma_desc_sw128(sa + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * 2048, BK * 128, 1024) : umma_desc_sw128(sb + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) ? 1u : 0u);
+            const uint64_t da = desc_pack(la + (A_MN ? k * 128 : k * 2));
+            const uint64_t db = desc_pack(lb + (B_MN ? k * 128 : k * 2));
+            umma_bf16_ss(d_tmem, da, db, idesc, k ? 1u : acc0);
           }
           umma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
