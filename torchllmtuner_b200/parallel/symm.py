@@ -193,7 +193,13 @@ class FusedFSDPComm:
             self.queue = None
             return
         padded = {u.padded for u in self.units}
-        assert len(padded) == 1, "block units of one pool must have one size"
+        if len(padded) != 1:
+            # the two gradient slots and the chunk arithmetic assume blocks of one size; models whose blocks differ
+            # (hybrid mixers, a dense first layer before sparse ones) keep the NCCL collectives of the same runtime
+            from ..utils import get_logger
+            get_logger().info(f"fused FSDP collectives are off: decoder blocks have {len(padded)} different sizes")
+            self.queue = None
+            return
         self.padded = padded.pop()
         esz = self.units[0].shard_lowp.element_size()
         self.esz = esz
