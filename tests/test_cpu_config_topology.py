@@ -228,3 +228,33 @@ def test_inert_flags_are_reported_and_every_other_flag_is_read_somewhere():
     silent = [f"{g.__name__}.{f.name}" for g in dict.fromkeys(groups) for f in dataclasses.fields(g)
               if f.name not in INERT_FIELDS and not re.search(r"\b" + re.escape(f.name) + r"\b", src)]
     assert silent == [], silent
+
+
+def _wsd_statement(step, warmup, total, ratio, kind, floor):
+    """The schedule written out independently: phase lengths, then the factor of a 0-indexed step."""
+    warmup = min(warmup, total)
+    decay = min(round(total * ratio), total - warmup)
+    stable = total + 1 - warmup - decay
+    if step < warmup:
+        return (step + 1) / warmup
+    if step < warmup + stable:
+        return 1.0
+    p = (step + 1 - warmup - stable) / decay
+    shape = {"linear": 1 - p, "sqrt": 1 - math.sqrt(p), "cosine": 0.5 * (1 + math.cos(math.pi * p))}[kind]
+    return floor + (1 - floor) * shape
+
+
+@pytest.mark.parametrize("kind", ["linear", "sqrt", "cosine"])
+@pytest.mark.parametrize("floor", [0.0, 0.1])
+@pytest.mark.parametrize("total,warmup,ratio", [(100, 10, 0.29), (100, 0, 0.0), (20, 4, 0.25), (10, 30, 0.5), (50, 30, 0.8), (7, 3, 0.5)])
+def test_wsd_schedule_every_step(kind, floor, total, warmup, ratio):
+    from torchllmtuner_b200.components.optimizer.lr_scheduler import resolve_phases, wsd_factor
+    w, s, d = resolve_phases(total, warmup, ratio)
+    assert w + s + d == total + 1 and w >= 0 and s >= 1 and d >= 0       # phases never overlap, stable never negative
+    for step in range(total):
+        got = wsd_factor(step, warmup=warmup, total=total, decay_ratio=ratio, decay_type=kind, min_lr_factor=floor)
+        assert got == pytest.approx(_wsd_statement(step, warmup, total, ratio, kind, floor), abs=1e-12), step
+        assert got >= min(floor, 1.0 / max(1, w)) - 1e-12
+    if warmup > 0:   # warm-up is not blended with the floor
+        assert wsd_factor(0, warmup=warmup, total=total, decay_ratio=ratio, decay_type=kind, min_lr_factor=floor) == pytest.approx(1 / min(warmup, total))
+    assert round(100 * 0.29) == 29 and resolve_phases(100, 10, 0.29)[2] == 29   # rounded, not truncated

@@ -14,45 +14,9 @@
 // loops over the query heads of the group and the q tiles, and a dQ kernel per (q tile, head); both recompute
 // S and dP so that no atomics are needed.
 #include <type_traits>
-#include "common.cuh"
-#include "kernels.h"
+#include "attn_common.cuh"
 
 namespace llmt {
-
-constexpr int kAttnThreads = 192;
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// 16-column slice `ks` of a K-major tile stored as 64-column halves of [128 rows][128 B].
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int ks) {
-  return umma_desc_sw128(base + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-}
-// 16-row slice `ks` of the same physical tile read as an MN-major operand (rows = reduction index).
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int ks) {
-  return umma_desc_sw128(base + ks * 2048, 16384, 1024);
-}
-// Store 32 consecutive bf16 (packed in 16 words) of row `row`, columns [col0, col0+32) into a swizzled K-major tile.
-__device__ __forceinline__ void store_row32_swz(uint8_t* tile, int row, int col0, const uint32_t* w) {
-  uint8_t* base = tile + (col0 >> 6) * 16384 + row * 128;
-  const int chunk0 = (col0 & 63) >> 3;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint4 v = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-    *reinterpret_cast<uint4*>(base + (((chunk0 + c) ^ (row & 7)) << 4)) = v;
-  }
-}
-
-template <int HD>
-struct AttnSmem {
-  static constexpr int kTile = 128 * HD * 2;   // Q / K / V / dO tile, 128 rows
-  static constexpr int kP = 128 * 128 * 2;     // P / dS tile
-};
 
 // =========================================================================================== forward
 // Forward tiles: 128 query rows x 64 keys. K is double buffered, V single buffered, P goes through shared memory:
@@ -60,26 +24,6 @@ struct AttnSmem {
 // of the other.
 constexpr int kFwdKV = 64;
 
-// Optional timeline of CTA 0 (development aid): role r writes clock64() for step j, point p into g_attn_dbg[(j*8+p)*2+r].
-#ifdef LLMT_ATTN_TIMELINE
-__device__ long long g_attn_dbg[2 * 8 * 256];
-#define LLMT_TL(role, j, p) do { if (blockIdx.x == 0 && (j) < 256) g_attn_dbg[(((j) * 8) + (p)) * 2 + (role)] = clock64(); } while (0)
-#else
-#define LLMT_TL(role, j, p) do { } while (0)
-#endif
-
-// 16-column slice `ks` of a K-major tile with `rows` rows stored as 64-column halves of [rows][128 B].
-__device__ __forceinline__ uint64_t desc_kmajor_rows(uint32_t base, int ks, int rows) {
-  return umma_desc_sw128(base + (ks >> 2) * (rows * 128) + (ks & 3) * 32, 16, 1024);
-}
-// 16-row slice `ks` of a tile with `rows` rows read as an MN-major operand (64-column blocks `rows * 128` B apart).
-__device__ __forceinline__ uint64_t desc_mnmajor_rows(uint32_t base, int ks, int rows) {
-  return umma_desc_sw128(base + ks * 2048, rows * 128, 1024);
-}
-
-// offset (in 16-byte units) of 16-column slice `ks` of a K-major tile with `rows` rows / of 16-row slice `ks` read MN-major
-__host__ __device__ constexpr uint32_t koff(int ks, int rows) { return (uint32_t)(((ks >> 2) * (rows * 128) + (ks & 3) * 32) >> 4); }
-__host__ __device__ constexpr uint32_t mnoff(int ks) { return (uint32_t)((ks * 2048) >> 4); }
 
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 2)
@@ -197,7 +141,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait_bounded(&kfull[s], ph, abort_flag, status, 1210 + s)) return false;
         if (!mbar_wait_bounded(&sempty[s], ph ^ 1, abort_flag, status, 1220 + s)) return false;
         tc_fence_after();
-        LLMT_TL(1, j - 1, 5);
         {
           // descriptors differ only in the start address field: build the two bases once and step the low word
           const uint64_t dq0 = desc_kmajor_rows(aQ, 0, 128), dk0 = desc_kmajor_rows(aK + s * kKVBytes, 0, kFwdKV);
@@ -209,30 +152,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             umma_bf16_ss(d_s, dq0 + offq, dk0 + offk, idS, ks ? 1u : 0u);
           }
         }
-        LLMT_TL(1, j - 1, 6);
         umma_commit(&sfull[s]);
         umma_commit(&kempty[s]);
-        LLMT_TL(1, j - 1, 7);
         return true;
       };
       if (ok) ok = issue_S(0);
       for (int j = 0; j < n_kv && ok; ++j) {
-        LLMT_TL(1, j, 0);
         if (j + 1 < n_kv) { if (!issue_S(j + 1)) break; }
-        LLMT_TL(1, j, 1);
         const int pb = j & 1;
         if (!mbar_wait_bounded(&pfull[pb], (j >> 1) & 1, abort_flag, status, 1230 + pb)) break;
-        LLMT_TL(1, j, 2);
         if (!mbar_wait_bounded(vfull, j & 1, abort_flag, status, 1240)) break;
         tc_fence_after();
-        LLMT_TL(1, j, 3);
         const uint32_t loP = desc_lo(aP + pb * kPBytes, 16), acc0 = j ? 1u : 0u;
 #pragma unroll
         for (int ks = 0; ks < kFwdKV / 16; ++ks)
           umma_bf16_ss(tO, desc_pack(loP + koff(ks, 128)), desc_pack(loVm + mnoff(ks)), idPV, ks ? 1u : acc0);
         umma_commit(vempty);
         umma_commit(&pvdone[pb]);
-        LLMT_TL(1, j, 4);
       }
     }
     __syncwarp();
@@ -245,10 +181,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j & 1;
-      if (threadIdx.x == 64) LLMT_TL(0, j, 0);
       if (!mbar_wait_bounded(&sfull[s], (j >> 1) & 1, abort_flag, status, 1300 + s)) { ok = false; break; }
       tc_fence_after();
-      if (threadIdx.x == 64) LLMT_TL(0, j, 1);
       const uint32_t ts = tS + lane_off + s * kFwdKV;
       const int kbase = j * kFwdKV;
       const bool need_mask = kbase + kFwdKV > (causal ? min(klen, diag0) : klen);
@@ -259,7 +193,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sempty[s]);      // S buffer s may be overwritten by the MMA of tile j + 2
-      if (threadIdx.x == 64) LLMT_TL(0, j, 2);
       // eight independent running maxima keep the dependency chains short
       float mxs[8];
 #pragma unroll
@@ -296,7 +229,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (j > 1) {   // P buffer j & 1 was last read by the PV product of tile j - 2
         if (!mbar_wait_bounded(&pvdone[j & 1], (((j >> 1) & 1) ^ 1), abort_flag, status, 1320)) { ok = false; break; }
       }
-      if (threadIdx.x == 64) LLMT_TL(0, j, 3);
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       float rsum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -316,11 +248,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         store_row32_swz(sP + (j & 1) * kPBytes, row, c * 32, w);
       }
       l += (rsum[0] + rsum[1]) + (rsum[2] + rsum[3]);
-      if (threadIdx.x == 64) LLMT_TL(0, j, 4);
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&pfull[j & 1]);
-      if (threadIdx.x == 64) LLMT_TL(0, j, 5);
     }
     // ---- finalize
     if (ok && n_kv > 0) ok = mbar_wait_bounded(&pvdone[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, status, 1330);
@@ -359,25 +289,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }
-}
-
-// =========================================================================================== backward: delta
-// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h).
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t o_stride, const __nv_bfloat16* __restrict__ d_o,
-                                  int64_t do_stride, float* __restrict__ delta, int T, int H, int HD) {
-  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= (int64_t)T * H) return;
-  const int t = (int)(item / H), h = (int)(item % H), lane = threadIdx.x & 31;
-  const __nv_bfloat16* po = o + (int64_t)t * o_stride + (int64_t)h * HD;
-  const __nv_bfloat16* pd = d_o + (int64_t)t * do_stride + (int64_t)h * HD;
-  float s = 0.f;
-  for (int c = lane * 2; c < HD; c += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + c));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + c));
-    s += a.x * b.x + a.y * b.y;
-  }
-  s = warp_sum(s);
-  if (lane == 0) delta[(int64_t)h * T + t] = s;
 }
 
 // =========================================================================================== backward: dK, dV
@@ -902,32 +813,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-// ------------------------------------------------------------------------------------------- host
-int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                   const uint32_t* box);
-
-// [T, H, HD] tensor with token stride `tok_stride` elements -> 3-D map {HD, H, T}, box {64, 1, rows}.
-static int make_thd_map(CUtensorMap* m, const void* p, int T, int H, int HD, int64_t tok_stride, uint32_t rows = 128) {
-  uint64_t dims[3] = {(uint64_t)HD, (uint64_t)H, (uint64_t)T};
-  uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)tok_stride * 2};
-  uint32_t box[3] = {64, 1, rows};
-  return make_tmap_bf16(m, p, 3, dims, str, box);
-}
-
-template <typename K>
-static int set_smem(K kern, int bytes) {
-  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -2;
-}
-
 }  // namespace llmt
 
 using namespace llmt;
-
-#ifdef LLMT_ATTN_TIMELINE
-extern "C" int llmt_attn_timeline(long long* host_out, int n) {
-  return cudaMemcpyFromSymbol(host_out, g_attn_dbg, sizeof(long long) * (n < 4096 ? n : 4096)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 extern "C" int llmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* tiles, int num_tiles,
                              int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,

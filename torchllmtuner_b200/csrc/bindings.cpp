@@ -495,16 +495,32 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
 // k_tile_passes: the dK/dV kernel runs once per pass; passes after the first accumulate (pieces that share keys).
 std::vector<Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& dout,
                              const Tensor& lse, const Tensor& q_tiles, const std::vector<Tensor>& k_tile_passes, double scale,
-                             bool causal, bool zero_init) {
+                             bool causal, bool zero_init, bool fused) {
   c10::cuda::CUDAGuard guard(q.device());
   check_bf16(dout, "dout");
   TORCH_CHECK(dout.dim() == 3 && dout.stride(2) == 1 && dout.stride(1) == dout.size(2) && o.is_contiguous());
   const int Tq = (int)q.size(0), Hq = (int)q.size(1), HD = (int)q.size(2), Tk = (int)k.size(0), Hkv = (int)k.size(1);
-  Tensor dq = zero_init ? torch::zeros({Tq, Hq, HD}, q.options()) : torch::empty({Tq, Hq, HD}, q.options());
+  Tensor dq = (zero_init && !fused) ? torch::zeros({Tq, Hq, HD}, q.options()) : torch::empty({Tq, Hq, HD}, q.options());
   Tensor dk = zero_init ? torch::zeros({Tk, Hkv, HD}, k.options()) : torch::empty({Tk, Hkv, HD}, k.options());
   Tensor dv = zero_init ? torch::zeros({Tk, Hkv, HD}, v.options()) : torch::empty({Tk, Hkv, HD}, v.options());
   Tensor delta = torch::empty({Hq, Tq}, q.options().dtype(torch::kFloat));
   const int npass = (int)k_tile_passes.size();
+  if (fused) {
+    // one walk per key tile yields dK, dV and that tile's share of dQ, which is summed in an fp32 accumulator
+    Tensor acc = torch::empty({Tq, Hq, HD}, q.options().dtype(torch::kFloat));
+    const int n = npass > 0 ? npass : 1;
+    for (int p = 0; p < n; ++p) {
+      const int* kt = npass > 0 ? k_tile_passes[p].data_ptr<int>() : nullptr;
+      const int nkt = npass > 0 ? (int)k_tile_passes[p].size(0) : 0;
+      check_rc(llmt_attn_bwd_fused(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(),
+                                   delta.data_ptr<float>(), acc.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), kt,
+                                   nkt, Tq, Tk, Hq, Hkv, HD, q.stride(0), k.stride(0), v.stride(0), o.stride(0), dout.stride(0),
+                                   dq.stride(0), dk.stride(0), dv.stride(0), (float)scale, causal, p == 0, p == n - 1,
+                                   status_ptr(), cur_stream()),
+               "llmt_attn_bwd_fused", (p == 0 ? 1 : 0) + (nkt > 0 ? 1 : 0) + (p == n - 1 ? 1 : 0));
+    }
+    return {dq, dk, dv};
+  }
   for (int p = 0; p < (npass > 0 ? npass : 1); ++p) {
     const int* kt = npass > 0 ? k_tile_passes[p].data_ptr<int>() : nullptr;
     const int nkt = npass > 0 ? (int)k_tile_passes[p].size(0) : 0;

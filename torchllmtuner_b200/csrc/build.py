@@ -20,8 +20,8 @@ PKG = os.path.dirname(HERE)
 BUILD = os.path.join(HERE, "build")
 SO_PATH = os.path.join(PKG, "_C.so")
 STAMP = os.path.join(PKG, "_C.stamp")
-CU_SOURCES = ("gemm.cu", "elementwise.cu", "attention.cu", "moe.cu", "comm.cu", "ep_comm.cu", "noalloc.cu")
-HEADERS = ("common.cuh", "comm.cuh", "kernels.h", "noalloc.h")
+CU_SOURCES = ("gemm.cu", "elementwise.cu", "attention.cu", "attention_bwd.cu", "moe.cu", "comm.cu", "ep_comm.cu", "noalloc.cu")
+HEADERS = ("common.cuh", "comm.cuh", "attn_common.cuh", "kernels.h", "noalloc.h")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--use_fast_math", "-Xptxas", "-v"]
 
@@ -80,10 +80,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
     # that report through the status word (the release build keeps only the checks that guard peer memory).
     debug = os.environ.get("LLMT_DEBUG") == "1"
     extra = ["-DLLMT_DEBUG"] if debug else []
+    # LLMT_NVCC_FLAGS: extra nvcc flags (e.g. "-DNAME" for an experiment); they are part of the object cache key.
+    user_flags = os.environ.get("LLMT_NVCC_FLAGS", "").split()
+    extra += user_flags
+    tag = ("." + hashlib.sha256(" ".join(user_flags).encode()).hexdigest()[:8]) if user_flags else ""
 
     def compile_cu(src):
         path = os.path.join(HERE, src)
-        obj = os.path.join(BUILD, f"{os.path.splitext(src)[0]}.{_hash([path] + hdr)}{'.dbg' if debug else ''}.o")
+        obj = os.path.join(BUILD, f"{os.path.splitext(src)[0]}.{_hash([path] + hdr)}{'.dbg' if debug else ''}{tag}.o")
         if not os.path.exists(obj):
             _run([_nvcc(), *NVCC_FLAGS, *extra, "-I", HERE, "-c", path, "-o", obj], log)
         return obj

@@ -366,8 +366,15 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // bf16 tensor map with a 128-byte swizzle. dims/strides are innermost-first; strides in bytes for dims 1..rank-1.
+int make_tmap_typed(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box, int is_f32);
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                    const uint32_t* box) {
+  return make_tmap_typed(out, base, rank, dims, strides_bytes, box, 0);
+}
+// Same for fp32 elements when `is_f32` (inner box of at most 32 elements = one 128-byte swizzle row).
+int make_tmap_typed(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box, int is_f32) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return -1;
   // The encoder is a driver call and needs the primary context bound to the calling thread; a fresh thread (the
@@ -385,7 +392,7 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
     es[i] = 1;
     if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
   }
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
+  CUresult r = enc(out, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (r == CUDA_SUCCESS) ? 0 : (int)r;

@@ -92,6 +92,13 @@ int llmt_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
                   int num_k_tiles, int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride,
                   int64_t v_stride, int64_t o_stride, int64_t do_stride, int64_t dq_stride, int64_t dk_stride,
                   int64_t dv_stride, float scale, int causal, int pass, int* status, cudaStream_t st);
+// Single-kernel backward (attention_bwd.cu): dK, dV and dQ from one walk per key tile; dQ is summed in the fp32
+// accumulator dq_acc [Tq, Hq, HD] (cleared when `first`, cast into dq when `last`).
+int llmt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                        float* delta, float* dq_acc, void* dq, void* dk, void* dv, const int* k_tiles, int num_k_tiles,
+                        int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                        int64_t o_stride, int64_t do_stride, int64_t dq_stride, int64_t dk_stride, int64_t dv_stride,
+                        float scale, int causal, int first, int last, int* status, cudaStream_t st);
 
 #ifdef __cplusplus
 }

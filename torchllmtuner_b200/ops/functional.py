@@ -4,9 +4,8 @@ There is no library fallback on CUDA: if the extension cannot be loaded the call
 """
 from __future__ import annotations
 
-import os
-
 import math
+import os
 
 import torch
 
@@ -211,8 +210,32 @@ class _Attention(torch.autograd.Function):
         if do.stride(2) != 1 or do.stride(1) != do.shape[2]:
             do = do.contiguous()
         m = ctx.meta
-        dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, m.q_tiles, m.k_tile_passes, ctx.scale, m.causal, not m.covers_all_keys)
+        dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, m.q_tiles, m.k_tile_passes, ctx.scale, m.causal, not m.covers_all_keys,
+                                     attention_backward_mode() == "fused")
         return dq, dk, dv, None, None
+
+
+_ATTN_BWD_MODE: str | None = None
+
+
+def set_attention_backward(mode: str | None) -> None:
+    """Choose the attention backward: "fused" (one kernel per key tile, five products, dQ summed in an fp32 accumulator by
+    bulk reduce-adds: fastest, dQ reproducible up to fp32 summation order) or "split" (a dK/dV kernel and a dQ kernel,
+    seven products, bitwise reproducible). `None` returns to the default: the environment variable `LLMT_ATTN_BWD`, else
+    "split" when `torch.use_deterministic_algorithms(True)` is in force, else "fused"."""
+    global _ATTN_BWD_MODE
+    if mode not in (None, "fused", "split"):
+        raise ValueError(f"attention backward mode must be 'fused' or 'split', got {mode!r}")
+    _ATTN_BWD_MODE = mode
+
+
+def attention_backward_mode() -> str:
+    if _ATTN_BWD_MODE is not None:
+        return _ATTN_BWD_MODE
+    env = os.environ.get("LLMT_ATTN_BWD")
+    if env in ("fused", "split"):
+        return env
+    return "split" if torch.are_deterministic_algorithms_enabled() else "fused"
 
 
 def attention(q, k, v, meta: AttnMeta, scale: float | None = None):
