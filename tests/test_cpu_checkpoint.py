@@ -122,3 +122,32 @@ def test_resume_at_other_tp_degree(tmp_path):
     run_ranks(1, base_flat(_save_at=2, **ck2), steps=2)
     got2 = run_ranks(2, base_flat(tensor_parallel_size=2, data_parallel_shard_size=1, _load=True, **ck2), steps=2)
     assert max(abs(a - b) for a, b in zip(ref["loss"][2:], got2["loss"])) < 5e-5, (ref, got2)
+
+
+def test_async_checkpoint_is_published_in_a_later_step_and_adopted_after_a_crash(tmp_path):
+    """A background save is renamed to `step-N` by the per-step hook as soon as it has finished, and a write that finished
+    but was never renamed (the process died first) is adopted by the next load instead of resuming one interval earlier."""
+    import time
+    folder = str(tmp_path / "run")
+    tr = Trainer(_cfg(folder, async_mode="async", interval=2, steps=8))
+    tr.train_step(); r = tr.train_step()
+    tr.checkpointer.save(r.step)                          # step 2, background write
+    final = os.path.join(folder, "checkpoint", "step-2")
+    for _ in range(200):                                  # the hook publishes without another save() or close()
+        tr.checkpointer.maybe_wait_for_staging()
+        if os.path.isdir(final):
+            break
+        time.sleep(0.05)
+    assert os.path.exists(os.path.join(final, ".metadata"))
+    assert tr.checkpointer._async_future is None
+    tr.train_step(); r = tr.train_step()
+    tr.checkpointer.save(r.step)                          # step 4: let the write finish, then "crash" before publication
+    fut, tmp, final4, _ = tr.checkpointer._async_future
+    fut.result()
+    tr.checkpointer._async_future = None                  # the dying process never runs wait()
+    assert os.path.isdir(tmp) and not os.path.isdir(final4)
+    tr2 = Trainer(_cfg(folder, async_mode="async", interval=2, steps=8))
+    assert tr2.checkpointer.load() and tr2.progress.step == 4
+    assert os.path.isdir(final4) and not os.path.isdir(tmp)
+    tr2.close()
+    tr.close()

@@ -48,6 +48,18 @@ def test_ep2_matches_single_rank():
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
 
 
+def test_balance_loss_weight_is_independent_of_dp_and_accumulation():
+    """The load-balance loss is a per-token-stream objective of weight `coef`: two micro-batches accumulated on one rank and
+    the same two micro-batches on two data-parallel ranks give the same loss curve and the same gradient norm."""
+    flat = dict(model_name_or_path="qwen3_moe", router_aux_loss_coef=0.5, learning_rate=1e-2)
+    one = run_ranks(1, base_flat(gradient_accumulation_steps=2, **flat), arch=MOE)
+    two = run_ranks(2, base_flat(data_parallel_shard_size=2, **flat), arch=MOE)
+    _close(one["loss"], two["loss"], 5e-5)
+    _close(one["grad_norm"], two["grad_norm"], 5e-4)
+    off = run_ranks(1, base_flat(gradient_accumulation_steps=2, model_name_or_path="qwen3_moe", learning_rate=1e-2), arch=MOE)
+    assert abs(off["grad_norm"][0] - one["grad_norm"][0]) > 1e-3        # the balance term does reach the gradient
+
+
 def test_tp2_moe_matches_single_rank():
     """MoE block under tensor parallelism: rows gathered in, experts' intermediate dimension sharded, partial sums
     reduce-scattered out."""

@@ -5,11 +5,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _close(out, ref, tol=2e-2):
-    out, ref = out.float(), ref.float()
-    err = (out - ref).abs().max().item()
-    scale = ref.abs().max().item() + 1e-6
-    assert err / scale < tol, f"max err {err} vs scale {scale}"
+from tolerances import GEMM_BF16, GEMM_F32, assert_close
+
+
+def _close(out, ref, name="gemm"):
+    assert_close(out, ref, name=name, **(GEMM_F32 if out.dtype == torch.float32 else GEMM_BF16))
 
 
 SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (200, 136, 72), (1024, 4096, 1024), (64, 64, 64), (136, 520, 200),
@@ -36,6 +36,27 @@ def test_gemm_layouts(M, N, K, layout, out_dtype):
     torch.cuda.synchronize()
     check_status("gemm")
     _close(out, ref)
+
+
+@pytest.mark.parametrize("M,N,K,layout", [(1024, 151936, 4096, "tn"), (8192, 4096, 12288, "tn"), (4096, 12288, 8192, "tt"), (8192, 4096, 4096, "nn")])
+def test_gemm_benchmark_shapes(M, N, K, layout):
+    """Shapes of the Qwen3-8B step: vocabulary head (N = 151,936), down projection (K = 12,288), its weight gradient
+    (reduction over 8192 tokens) and an input gradient."""
+    from torchllmtuner_b200.ops import gemm
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    torch.manual_seed(0)
+    A = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    B = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    if layout == "tn":
+        out = gemm(A, B)
+    elif layout == "nn":
+        out = gemm(A, B.t().contiguous(), b_mn=True)
+    else:
+        out = gemm(A.t().contiguous(), B.t().contiguous(), a_mn=True, b_mn=True)
+    torch.cuda.synchronize()
+    check_status("gemm")
+    for r0 in range(0, M, 1024):       # reference in row blocks to bound the fp32 temporaries
+        _close(out[r0:r0 + 1024], A[r0:r0 + 1024].float() @ B.float().t(), f"rows {r0}")
 
 
 def test_gemm_accumulate_and_strided_out():

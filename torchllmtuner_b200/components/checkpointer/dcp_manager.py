@@ -36,6 +36,7 @@ from .manager import CheckpointManager
 
 FORMAT_VERSION = 2
 _STEP_RE = re.compile(r"^step-(\d+)$")
+_TMP_RE = re.compile(r"^step-(\d+)\.tmp-[0-9a-f]+$")
 _PIECE_RE = re.compile(r"^(?P<base>.+?)(?:@tp(?P<dim>\d+)\.(?P<r>\d+)of(?P<n>\d+))?@(?P<lo>\d+):(?P<hi>\d+)$")
 
 
@@ -273,7 +274,21 @@ class DistributedCheckpointManager(CheckpointManager):
         return max(steps) if steps else -1
 
     def maybe_wait_for_staging(self) -> None:
-        pass        # staging copies are synchronised inside save()
+        """Called once per training step. Staging copies are synchronised inside `save()`; what is left is publication of
+        a background write: as soon as EVERY rank's write has finished (MIN all-reduce of the done flags over the gloo
+        group, so all ranks take the same branch) the folder is renamed to `step-N`. A crash in a later step then resumes
+        from it instead of one interval earlier (reference: the DCP backend publishes when the background save completes,
+        llmtuner/components/checkpointer/backends/distributed_checkpoint.py:328-457)."""
+        if self._async_future is None:
+            return
+        fut = self._async_future[0]
+        done = 1 if fut.done() else 0
+        if dist.is_initialized() and self._gloo is not None:
+            flag = torch.tensor([done], dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self._gloo)
+            done = int(flag.item())
+        if done:
+            self.wait()
 
     def wait(self) -> None:
         if self._async_future is not None:
@@ -297,6 +312,23 @@ class DistributedCheckpointManager(CheckpointManager):
             except OSError:
                 pass
 
+    def _adopt_finished_writes(self) -> None:
+        """A run that died after a background write finished but before its rename leaves `step-N.tmp-<id>` with a
+        `.metadata` file (the coordinator writes it last, after every rank's shards). Such a folder is a complete
+        checkpoint: rank 0 publishes it under its final name unless that step was published already."""
+        if self.rank != 0 or not os.path.isdir(self.root):
+            return
+        for name in sorted(os.listdir(self.root)):
+            m = _TMP_RE.match(name)
+            if not m:
+                continue
+            src, dst = os.path.join(self.root, name), os.path.join(self.root, f"step-{m.group(1)}")
+            if os.path.exists(os.path.join(src, ".metadata")) and not os.path.isdir(dst):
+                try:
+                    os.replace(src, dst)
+                except OSError:
+                    pass
+
     def _existing_steps(self) -> list[int]:
         if not os.path.isdir(self.root):
             return []
@@ -310,6 +342,9 @@ class DistributedCheckpointManager(CheckpointManager):
     # ------------------------------------------------------------------ load
     def _resolve_load_source(self, step: int):
         """An existing step folder of this run wins over `initial_load_path`."""
+        self._adopt_finished_writes()
+        if dist.is_initialized():
+            dist.barrier()
         steps = self._existing_steps()
         if steps:
             s = max(steps) if step == -1 else step

@@ -51,15 +51,32 @@ class MoE(nn.Module):
             with torch.no_grad():
                 self.tokens_per_expert_E.add_(counts)
         if self.aux_loss_coef > 0 and self.training:
-            # DeepSeek-V3 style micro-batch balance loss: E * sum_e f_e * P_e
-            T = x2.shape[0]
-            f = counts / max(1, T * self.top_k) * self.num_experts
-            p = scores.mean(0)
-            self.aux_loss = self.aux_loss_coef * (f.detach() * p).sum()
+            self.aux_loss = self.aux_loss_coef * self.balance_loss_sum(counts, scores)
         out = self.routed(x2, w, idx)
         if self.shared_experts is not None:
             out = out + self.shared_experts(x2)
         return out.reshape(shape)
+
+    def balance_loss_sum(self, counts: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
+        """Micro-batch load-balance loss in its token-sum form, T * L_bal (reference:
+        llmtuner/models/common/moe/auxiliary_loss.py:31-168; DeepSeek-V3 eqs. 17-20).
+
+        f_i = E * counts_i / sum_j counts_j (not differentiable), P_i = sum_t s'_{t,i} with s' the scores L1-normalised
+        per token, value sum_i f_i * P_i. It is a sum over this forward's tokens, so the caller divides it by the global
+        valid-token count exactly like the token loss: the injected weight is then `coef * L_bal` per token stream whatever
+        the data-parallel degree or the number of accumulation steps. Counts and score sums are partial over the ranks that
+        hold pieces of ONE token stream (`self.stream_groups`: the context-parallel group, and the tensor-parallel group
+        when the experts are expert-parallel); they are all-reduced forward with an identity backward. Data-parallel ranks
+        own independent streams and are not reduced."""
+        from ...accelerator.collectives import PartialToInvariantAllReduce
+        probs = scores / scores.sum(-1, keepdim=True).clamp_min(1e-12)
+        p_sum = probs.sum(0)
+        counts = counts.detach().to(p_sum.dtype)
+        for grp in getattr(self, "stream_groups", ()) or ():
+            counts = PartialToInvariantAllReduce.apply(counts, grp)
+            p_sum = PartialToInvariantAllReduce.apply(p_sum, grp)
+        f = counts / counts.sum().clamp_min(1.0) * self.num_experts
+        return (f.detach() * p_sum).sum()
 
     @torch.no_grad()
     def update_expert_bias(self, reduce_fn=None) -> None:

@@ -145,9 +145,6 @@ def apply_ep(model, topo, ep_config) -> dict:
     for n, m in blocks:
         if m.routed.experts.num_experts % topo.ep:
             raise ConfigError(f"{n}: expert_parallel_size {topo.ep} must divide {m.routed.experts.num_experts} experts")
-    if ep_config.router_aux_loss_coef is not None:
-        for _, m in blocks:
-            m.aux_loss_coef = ep_config.router_aux_loss_coef
     for n, m in blocks:
         convert_block(m, topo, ep_config)
     return {n: "ep" for n, _ in blocks}

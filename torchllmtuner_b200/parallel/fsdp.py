@@ -458,11 +458,14 @@ class _CheckpointedBlock(torch.autograd.Function):
         with torch.enable_grad():
             out = ctx.layer(xd, ctx.fctx)
         # Auxiliary (load-balance) losses of MoE blocks: the value that entered the step's loss came from the first,
-        # graph-free forward, so their gradient is injected here, from the replayed forward (d loss / d aux = 1).
+        # graph-free forward, so their gradient is injected here, from the replayed forward. They are token sums, and
+        # d loss / d aux is the step's 1 / global_valid_tokens (`aux_grad_scale`, set by the engine per micro-batch).
         aux = [m.aux_loss for m in ctx.layer.modules() if getattr(m, "aux_loss", None) is not None and m.aux_loss.requires_grad]
         if aux:
             total_aux = aux[0] if len(aux) == 1 else torch.stack(aux).sum()
-            torch.autograd.backward([out, total_aux], [dy, torch.ones_like(total_aux)])
+            scale = getattr(rt, "aux_grad_scale", None)
+            seed = torch.ones_like(total_aux) if scale is None else torch.as_tensor(scale, dtype=total_aux.dtype, device=total_aux.device).reshape(total_aux.shape)
+            torch.autograd.backward([out, total_aux], [dy, seed])
         else:
             torch.autograd.backward(out, dy)
         for u in rt._units(i):

@@ -57,4 +57,23 @@ def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None)
             else:
                 continue
         asm.stages_applied.append(stage)
+    _bind_moe_stream_groups(model, topo, config.parallel.ep_config.router_aux_loss_coef)
     return asm
+
+
+def _bind_moe_stream_groups(model, topo, aux_loss_coef=None) -> None:
+    """Tell every MoE block which process groups split ONE token stream: the context-parallel group always, the
+    tensor-parallel group only when the experts are expert-parallel (the block then sees its sequence-parallel shard; under
+    plain TP the block boundary has already gathered the whole stream and every TP rank holds identical statistics).
+    Balance-loss statistics are summed over these groups (reference: llmtuner/models/common/moe/auxiliary_loss.py:131-140)."""
+    from ..models.moe import moe_blocks
+    groups = []
+    if topo.cp > 1 and topo.get_group("cp") is not None:
+        groups.append(topo.get_group("cp"))
+    if topo.tp > 1 and topo.ep > 1 and topo.get_group("tp") is not None:
+        groups.append(topo.get_group("tp"))
+    for blk in moe_blocks(model):
+        blk.stream_groups = tuple(groups)
+        if aux_loss_coef is not None:            # the `router_aux_loss_coef` flag overrides the architecture's value
+            blk.aux_loss_coef = float(aux_loss_coef)
+            blk.router.need_scores = blk.aux_loss_coef > 0

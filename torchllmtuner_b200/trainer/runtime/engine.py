@@ -35,6 +35,7 @@ class TrainingEngine:
         """Returns the un-normalised loss sum of this micro-batch (device scalar, detached)."""
         m = self.model
         self.rt.is_last_microbatch = is_last_microbatch
+        self.rt.aux_grad_scale = 1.0 / global_valid_tokens
         inputs = m.prepare_inputs(batch, self.device, self.parallel_dims())
         ctx = m.build_context(inputs["positions"], inputs["attn_meta"], self.asm.cp_driver)
         if self.asm.cp_driver is not None:
@@ -46,10 +47,10 @@ class TrainingEngine:
         else:
             logits = m(inputs["tokens"], ctx)
             loss_sum = self.loss_fns.from_logits(logits, inputs["targets"])
-        loss = loss_sum / global_valid_tokens
+        # Load-balance losses are token sums like the CE sum (`MoE.balance_loss_sum`): one division by the global valid-token
+        # count normalises both. Blocks that replay their forward inside backward read the same factor from the runtime.
         aux = collect_aux_loss(m)
-        if aux is not None:
-            loss = loss + aux
+        loss = (loss_sum if aux is None else loss_sum + aux) / global_valid_tokens
         loss.backward()
         self.rt.finish_backward()
         self.step_loss += loss_sum.detach()
