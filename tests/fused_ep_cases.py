@@ -6,7 +6,7 @@ import sys
 import torch
 
 
-def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflow: bool = False):
+def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflow: bool = False, skew: bool = False):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch.distributed as dist
@@ -19,7 +19,7 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflo
     from torchllmtuner_b200.parallel.symm_ep import PeerTokenDispatcher
     E, k, T, D, F = 8 * world, 4, 384, 256, 128
     nccl = AllToAllTokenDispatcher(E, dist.group.WORLD, world, rank)
-    peer = PeerTokenDispatcher(E, dist.group.WORLD, world, rank, fallback=nccl, capacity_factor=1.0 if overflow else 3.0)
+    peer = PeerTokenDispatcher(E, dist.group.WORLD, world, rank, fallback=nccl, capacity_factor=1.0 if overflow else (None if skew else 3.0))
     torch.manual_seed(7)
     experts = GroupedExperts(E // world, D, F, dtype=torch.bfloat16, device=dev)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -36,8 +36,8 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflo
         scores = torch.rand(T, E, generator=g, device=dev)
         if it == 1:
             scores[:, : E // 2] += 0.2           # unbalanced routing that still fits the receive buffers
-        if overflow:
-            scores[:, : E // world] += 10.0      # every copy goes to rank 0: its buffer must overflow
+        if overflow or skew:
+            scores[:, : E // world] += 10.0      # every copy goes to rank 0 (overflows unless the buffers are worst-case sized)
         w0, idx = scores.topk(k, dim=-1)
         w0 = (w0 / w0.sum(-1, keepdim=True)).float()
         dout = (torch.randn(T, D, generator=g, device=dev) * 0.1).bfloat16()
@@ -92,13 +92,13 @@ def _worker(rank: int, world: int, port: int, out_path: str, iters: int, overflo
     dist.destroy_process_group()
 
 
-def run_fused_ep(world: int, iters: int = 4, overflow: bool = False) -> dict:
+def run_fused_ep(world: int, iters: int = 4, overflow: bool = False, skew: bool = False) -> dict:
     import tempfile
 
     import torch.multiprocessing as mp
     out = tempfile.mktemp(suffix=".json")
     port = 22000 + (os.getpid() * 17 + world) % 20000
-    mp.spawn(_worker, args=(world, port, out, iters, overflow), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, out, iters, overflow, skew), nprocs=world, join=True)
     with open(out) as f:
         res = json.load(f)
     os.unlink(out)

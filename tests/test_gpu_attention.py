@@ -5,11 +5,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-from tolerances import ATTENTION, assert_close
+from tolerances import ATTENTION, ATTENTION_GRAD, assert_close
 
 
-def _close(a, b, name="attention"):
-    assert_close(a, b, name=name, **ATTENTION)
+def _close(a, b, name="o"):
+    assert_close(a, b, name=name, **(ATTENTION_GRAD if name.startswith("d") else ATTENTION))
 
 
 def _close_lse(a, b):

@@ -99,6 +99,15 @@ def test_peer_ep_capacity_overflow_is_reported_not_written():
     assert res["overflow_seen"] == 1.0, res
 
 
+def test_peer_ep_default_capacity_takes_every_token_on_one_rank():
+    """Default (worst-case) receive buffers: every copy of every rank routed to rank 0's experts is exchanged without a
+    drop and matches the NCCL all-to-all dispatcher."""
+    _need(2)
+    from fused_ep_cases import run_fused_ep
+    res = run_fused_ep(2, iters=2, skew=True)
+    assert res["out"] < 2e-2 and res["dx"] < 2e-2 and res["dw"] < 2e-2 and res["dparam"] < 3e-2, res
+
+
 def test_peer_that_never_arrives_becomes_an_error_on_every_rank():
     """Failure detection on the device without a fault: a host rank skips its launch, the waiting kernel gives up after
     its poll limit, and both ranks raise through the error-coordination boundary; the symmetric arena is untouched."""

@@ -75,9 +75,11 @@ class ExpertParallelConfig:
     fixed_router: bool = False
     ep_token_dispatcher: str = "alltoall"
     # Receive-buffer size of the peer-memory dispatcher as a multiple of the balanced load (token copies per rank).
-    # A rank can receive at most expert_parallel_size times the balanced load; rows beyond the capacity are dropped
-    # and reported through the kernel status word (the step then raises).
-    ep_capacity_factor: float = 4.0
+    # None (default) sizes the buffers for the worst case, expert_parallel_size times the balanced load (every token of
+    # every rank routed to one rank), so no routing skew can drop a row: at EP=8, 4096 tokens, top-8 and hidden 2048 that is
+    # 1 GiB per buffer. A smaller factor saves memory; rows beyond it are dropped and reported through the kernel status
+    # word (the step then raises).
+    ep_capacity_factor: float | None = None
     ep_torchao_pad_multiple: int = 16
 
     def __post_init__(self):
@@ -88,7 +90,7 @@ class ExpertParallelConfig:
         if self.router_aux_loss_coef is not None and not (self.router_aux_loss_coef >= 0):
             raise ConfigError("router_aux_loss_coef must be >= 0")
         require_integer_at_least("ep_torchao_pad_multiple", self.ep_torchao_pad_multiple, 1)
-        if not (self.ep_capacity_factor >= 1.0):
+        if self.ep_capacity_factor is not None and not (self.ep_capacity_factor >= 1.0):
             raise ConfigError("ep_capacity_factor must be >= 1")
 
 

@@ -133,7 +133,7 @@ def convert_block(moe: MoE, topo, ep_config) -> None:
         # synchronisation); the NCCL dispatcher stays behind it for CPU runs and unsupported shapes.
         from .symm_ep import PeerTokenDispatcher
         moe.routed.dispatcher = PeerTokenDispatcher(E, topo.get_group("ep"), ep, r, fallback=moe.routed.dispatcher,
-                                                        capacity_factor=min(float(ep), float(ep_config.ep_capacity_factor)))
+                                                        capacity_factor=ep_config.ep_capacity_factor)
     if isinstance(moe.routed.dispatcher, DominoTokenDispatcher):
         d = moe.routed.dispatcher
         moe.routed.forward = lambda x, w, i, _d=d, _e=ex: _d.run(_e, x, w, i)

@@ -57,11 +57,19 @@ def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None)
             else:
                 continue
         asm.stages_applied.append(stage)
-    _bind_moe_stream_groups(model, topo, config.parallel.ep_config.router_aux_loss_coef)
+    # tokens one rank feeds to a MoE block per micro-batch: sizes the expert-parallel exchange before the first call
+    try:
+        from ..config.training_config import resolve_batch_size_per_rank
+        rows = resolve_batch_size_per_rank(t.global_batch_size, topo.size("dp"), t.gradient_accumulation_steps)
+        seq_split = topo.cp * (topo.tp if topo.ep > 1 else 1)
+        max_tokens = -(-rows * t.max_seq_len // seq_split)
+    except Exception:
+        max_tokens = 0
+    _bind_moe_stream_groups(model, topo, config.parallel.ep_config.router_aux_loss_coef, max_tokens)
     return asm
 
 
-def _bind_moe_stream_groups(model, topo, aux_loss_coef=None) -> None:
+def _bind_moe_stream_groups(model, topo, aux_loss_coef=None, max_tokens: int = 0) -> None:
     """Tell every MoE block which process groups split ONE token stream: the context-parallel group always, the
     tensor-parallel group only when the experts are expert-parallel (the block then sees its sequence-parallel shard; under
     plain TP the block boundary has already gathered the whole stream and every TP rank holds identical statistics).
@@ -74,6 +82,9 @@ def _bind_moe_stream_groups(model, topo, aux_loss_coef=None) -> None:
         groups.append(topo.get_group("tp"))
     for blk in moe_blocks(model):
         blk.stream_groups = tuple(groups)
+        disp = getattr(blk.routed, "dispatcher", None)
+        if max_tokens and hasattr(disp, "max_copies_hint"):
+            disp.max_copies_hint = max_tokens * blk.top_k
         if aux_loss_coef is not None:            # the `router_aux_loss_coef` flag overrides the architecture's value
             blk.aux_loss_coef = float(aux_loss_coef)
             blk.router.need_scores = blk.aux_loss_coef > 0

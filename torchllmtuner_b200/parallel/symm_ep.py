@@ -11,8 +11,10 @@ No host synchronisation and no NCCL on the data path:
   * backward mirrors it: output gradients are pushed score-scaled (the same kernel also produces the router-weight
     gradients), input gradients are pulled.
 Every rank owns four fixed-capacity row buffers in one symmetric arena (expert inputs, expert outputs and their two
-gradients); `ready` / `free` epoch flags per buffer order producers and consumers. A run that does not fit the capacity
-raises the CapacityOverflow device status instead of writing out of bounds.
+gradients); `ready` / `free` epoch flags per buffer order producers and consumers. The buffers are sized for the worst
+routing skew by default (every copy of every rank lands on one rank), as the reference's exact split sizes are
+(token_dispatch.py:327-395); with a smaller `ep_capacity_factor` a run that does not fit raises the CapacityOverflow device
+status instead of writing out of bounds. Sizes are agreed across the group when the arena is built.
 """
 from __future__ import annotations
 
@@ -21,6 +23,7 @@ import os
 import torch
 import torch.distributed as dist
 
+from ..errors import ConfigError
 from ..models.moe.experts import SEG_ALIGN
 from .symm import canary_intact, write_canary
 
@@ -34,15 +37,28 @@ def _align(n: int, a: int = 256) -> int:
 class PeerExchange:
     """Arena + flags of one EP group, sized for `max_copies` token copies per rank and rows of `hidden` bf16."""
 
-    def __init__(self, group, device, num_experts: int, max_copies: int, hidden: int, capacity_factor: float = 4.0):
+    def __init__(self, group, device, num_experts: int, max_copies: int, hidden: int, capacity_factor: float | None = None):
         import torch.distributed._symmetric_memory as symm_mem
         from ..ops.cuda_ext import load
         self.ext = load()
         self.group, self.device = group, device
         self.R, self.me = dist.get_world_size(group), dist.get_rank(group)
         self.E, self.El, self.D = num_experts, num_experts // self.R, hidden
-        self.max_copies = max_copies
-        cap = int(max_copies * capacity_factor) + self.El * (SEG_ALIGN - 1)
+        # Every offset below is added to PEER base addresses, so the layout has to be the same on every rank: the sizes
+        # are agreed with one MAX all-reduce over the group (ranks may see different token counts on their first call)
+        # and checked for equality.
+        agreed = torch.tensor([max_copies, hidden, num_experts, -hidden, -num_experts], dtype=torch.int64, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=group)
+        mx, hmax, emax, hmin, emin = (int(v) for v in agreed.tolist())
+        if (hmax, emax) != (hidden, num_experts) or (-hmin, -emin) != (hidden, num_experts):
+            raise ConfigError(f"expert-parallel ranks disagree on the exchange shape: hidden {hidden} (group max {hmax}), "
+                              f"experts {num_experts} (group max {emax})")
+        self.max_copies = max_copies = mx
+        # Dropless by default: a rank can receive at most every copy of every rank (R * max_copies rows); each local expert
+        # adds up to SEG_ALIGN - 1 rows of segment padding.
+        factor = float(self.R) if capacity_factor is None else min(float(self.R), float(capacity_factor))
+        self.dropless = factor >= float(self.R)
+        cap = int(max_copies * factor) + self.El * (SEG_ALIGN - 1)
         self.cap = -(-cap // SEG_ALIGN) * SEG_ALIGN
         buf_b = _align(self.cap * hidden * 2)
         tab_b = _align(2 * self.R * self.E * 4)
@@ -182,10 +198,12 @@ class _PeerCombine(torch.autograd.Function):
 class PeerTokenDispatcher:
     """Drop-in for the all-to-all dispatcher (`dispatch` / `combine`) on CUDA bf16; falls back to `fallback` otherwise."""
 
-    def __init__(self, num_experts: int, group, ep_size: int, ep_rank: int, fallback, capacity_factor: float = 4.0):
+    def __init__(self, num_experts: int, group, ep_size: int, ep_rank: int, fallback, capacity_factor: float | None = None,
+                 max_copies_hint: int = 0):
         self.num_experts, self.group, self.ep_size, self.ep_rank = num_experts, group, ep_size, ep_rank
         self.local_experts = num_experts // ep_size
         self.fallback, self.capacity_factor = fallback, capacity_factor
+        self.max_copies_hint = max_copies_hint       # tokens per rank x top-k of the largest micro-batch, when known
         self.exchange: PeerExchange | None = None
 
     def _exchange_for(self, x, indices):
@@ -196,8 +214,16 @@ class PeerTokenDispatcher:
         copies = indices.numel()
         ex = _EXCHANGES.get(id(self.group))
         if ex is None:
-            ex = _EXCHANGES[id(self.group)] = PeerExchange(self.group, x.device, self.num_experts, copies, x.shape[1], self.capacity_factor)
-        return ex if ex.fits(copies, x.shape[1], self.num_experts) else None
+            # collective: every rank of the group reaches its first MoE call in the same step
+            ex = _EXCHANGES[id(self.group)] = PeerExchange(self.group, x.device, self.num_experts, max(copies, self.max_copies_hint),
+                                                           x.shape[1], self.capacity_factor)
+        if not ex.fits(copies, x.shape[1], self.num_experts):
+            # Falling back on this rank alone would leave the others polling flags that never flip, and pushing with a
+            # row count the arena was not sized for would write outside a peer's buffer.
+            raise ConfigError(f"expert-parallel exchange was sized for {ex.max_copies} token copies per rank with hidden {ex.D}; "
+                              f"this call has {copies} copies with hidden {x.shape[1]}. Set the largest micro-batch first "
+                              "(max_seq_len x local batch) or use ep_token_dispatcher=domino / LLMT_DISABLE_FUSED_EP=1")
+        return ex
 
     def dispatch(self, x, indices):
         ex = self._exchange_for(x, indices)
