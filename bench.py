@@ -73,9 +73,27 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    why = ("reference not runnable offline: pip install --no-deps succeeded, but `import llmtuner` needs colorama and grain "
-           "(not in the wheelhouse) and torch>=2.12 APIs (fully_shard(dp_mesh_dims=...), DCP DefaultStager); box has torch 2.11")
-    if int(os.environ.get("RANK", "0")) == 0:
+    """Runs the unmodified reference from `baseline/_ref` through its own CLI entry point. The attempt is real: the
+    reference's trainer module is imported in a child interpreter with `baseline/_ref` first on the path, and the line
+    printed when that fails carries the exception the import actually raised."""
+    import subprocess
+    root = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(root, "baseline", "_ref")
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+    if not os.path.isdir(os.path.join(ref, "llmtuner")):
+        why = "baseline/_ref/llmtuner is absent: the offline install of the reference was not done on this machine"
+    else:
+        probe = ("import sys; sys.path.insert(0, sys.argv[1]); import llmtuner.trainer.cli as c; "
+                 "import torch.distributed.fsdp as f; f.DataParallelMeshDims; print('ok')")
+        r = subprocess.run([sys.executable, "-c", probe, ref], capture_output=True, text=True, timeout=600)
+        if r.returncode == 0 and r.stdout.strip().endswith("ok"):
+            # The reference imports: hand over to its own CLI with the benchmark's configuration.
+            from baseline.reference_cli import run_reference
+            return run_reference(args, ref)
+        last = [ln for ln in (r.stderr or r.stdout).strip().splitlines() if ln.strip()]
+        why = "import of the reference's trainer failed: " + (last[-1].strip() if last else f"exit code {r.returncode}")
+        why = why[:300] + f" (torch {__import__('torch').__version__}; the reference needs torch>=2.12)"
+    if rank0:
         print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 

@@ -128,3 +128,86 @@ def run_absent_peer(world: int = 2):
         res = json.load(f)
     os.unlink(out)
     return res
+
+
+def _vocab_worker(rank: int, world: int, port: int, out_path: str, iters: int):
+    """Vocabulary-parallel head loss and embedding on the fused path against the full-vocabulary fp32 statement."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    from torchllmtuner_b200.models.common import Embedding, Linear
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    from torchllmtuner_b200.parallel import symm_tp
+    from torchllmtuner_b200.parallel.tensor_parallel import VocabParallelEmbedding
+    from torchllmtuner_b200.parallel.vocab_parallel import VocabParallelHead, vocab_parallel_head_loss
+    cr, D, V = 256, 256, 8 * 251 * world - (world - 1)   # chunk = 2008 (a multiple of 8), the last shard has padding rows
+    T = cr * world
+    g = torch.Generator(device=dev).manual_seed(7)    # the same table / head / tokens on every rank
+    full_head = Linear(D, V, torch.bfloat16, dev)
+    table = Embedding(V, D, dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        full_head.weight.copy_((torch.randn(V, D, generator=g, device=dev) * 0.2).bfloat16())
+        table.weight.copy_(torch.randn(V, D, generator=g, device=dev).bfloat16())
+    head = VocabParallelHead(full_head, rank, world, dist.group.WORLD)
+    vpe = VocabParallelEmbedding(table, rank, world, dist.group.WORLD)
+    res = {"loss": 0.0, "dh": 0.0, "dw": 0.0, "emb": 0.0, "demb": 0.0}
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+    for it in range(iters):
+        h = (torch.randn(T, D, generator=g, device=dev) * 0.5).bfloat16()
+        targets = torch.randint(0, V, (T,), generator=g, device=dev)
+        targets[::11] = -100
+        hs = h[rank * cr:(rank + 1) * cr].clone().requires_grad_()
+        head.weight.grad = None
+        loss = vocab_parallel_head_loss(hs, head, targets[rank * cr:(rank + 1) * cr])
+        (loss * 0.01).backward()
+        tot = loss.detach().clone()
+        dist.all_reduce(tot)
+        hf = h.float().requires_grad_()
+        wf = full_head.weight.detach().float().requires_grad_()
+        ref = F.cross_entropy(hf @ wf.t(), targets, ignore_index=-100, reduction="sum")
+        (ref * 0.01).backward()
+        res["loss"] = max(res["loss"], abs(float(tot) - float(ref.detach())) / abs(float(ref.detach())))
+        res["dh"] = max(res["dh"], rel(hs.grad, hf.grad[rank * cr:(rank + 1) * cr]))
+        real = head.end - head.start
+        res["dw"] = max(res["dw"], rel(head.weight.grad[:real], wf.grad[head.start:head.end]))
+        assert float(head.weight.grad[real:].abs().max()) == 0.0 if real < head.chunk else True
+        ids = torch.randint(0, V, (T,), generator=g, device=dev)
+        go = torch.randn(T, D, generator=g, device=dev).bfloat16()
+        vpe.weight.grad = None
+        out = vpe(ids[rank * cr:(rank + 1) * cr])
+        res["emb"] = max(res["emb"], float((out.detach().float() - table.weight[ids[rank * cr:(rank + 1) * cr]].float()).abs().max()))
+        out.backward(go[rank * cr:(rank + 1) * cr])
+        want = torch.zeros(V, D, device=dev).index_add_(0, ids, go.float())
+        res["demb"] = max(res["demb"], rel(vpe.weight.grad[: vpe.end - vpe.start], want[vpe.start:vpe.end]))
+        if it % 2 == rank % 2:
+            torch.cuda._sleep(20_000_000)
+    torch.cuda.synchronize()
+    check_status("vocab-parallel test")
+    stats = next(iter(symm_tp._COMMS.values())).stats if symm_tp._COMMS else {}
+    t = torch.tensor([res[k] for k in sorted(res)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump({**dict(zip(sorted(res), t.tolist())), "stats": stats}, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_vocab_parallel(world: int, iters: int = 3) -> dict:
+    import tempfile
+
+    import torch.multiprocessing as mp
+    out = tempfile.mktemp(suffix=".json")
+    port = 21500 + (os.getpid() * 13 + world) % 20000
+    mp.spawn(_vocab_worker, args=(world, port, out, iters), nprocs=world, join=True)
+    with open(out) as f:
+        res = json.load(f)
+    os.unlink(out)
+    return res

@@ -180,6 +180,54 @@ def _case_vocab_parallel_loss_and_embedding(rank, world):
     return f"{e1:.2e},{e2:.2e},{e3:.2e},{e4:.2e}"
 
 
+def _case_vocab_parallel_head(rank, world):
+    """Sequence-sharded hidden states against a vocabulary-sharded head: the summed loss over the ranks, the hidden-state
+    gradient shard, the head gradient shard and the embedding gradient equal the full-vocabulary statement."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from torchllmtuner_b200.models.common import Embedding, Linear
+    from torchllmtuner_b200.parallel.tensor_parallel import VocabParallelEmbedding
+    from torchllmtuner_b200.parallel.vocab_parallel import VocabParallelHead, vocab_parallel_head_loss
+    torch.manual_seed(11)
+    T, V, D = 16 * world, 37, 8                             # V does not divide evenly: the last shard is padded
+    cr = T // world
+    full_head = Linear(D, V, torch.float64, None)
+    with torch.no_grad():
+        full_head.weight.copy_(torch.randn(V, D, dtype=torch.float64) * 0.3)
+    h = torch.randn(T, D, dtype=torch.float64)
+    targets = torch.randint(0, V, (T,))
+    targets[5] = -100
+    head = VocabParallelHead(full_head, rank, world, dist.group.WORLD)
+    hs = h[rank * cr:(rank + 1) * cr].clone().requires_grad_()
+    loss = vocab_parallel_head_loss(hs, head, targets[rank * cr:(rank + 1) * cr])
+    (loss * 0.25).backward()                                # the same upstream factor on every rank, as in training
+    tot = loss.detach().clone()
+    dist.all_reduce(tot)
+    hf = h.clone().requires_grad_()
+    wf = full_head.weight.detach().clone().requires_grad_()
+    ref = F.cross_entropy(hf @ wf.t(), targets, ignore_index=-100, reduction="sum")
+    (ref * 0.25).backward()
+    e1 = abs(float(tot) - float(ref.detach()))
+    e2 = float((hs.grad - hf.grad[rank * cr:(rank + 1) * cr]).abs().max())
+    real = head.end - head.start
+    e3 = float((head.weight.grad[:real] - wf.grad[head.start:head.end]).abs().max()) if real else 0.0
+    e3 = max(e3, float(head.weight.grad[real:].abs().max()) if real < head.chunk else 0.0)      # padding rows stay zero
+    lg = head.full_logits(hs.detach())
+    e4 = float((lg - (h[rank * cr:(rank + 1) * cr] @ full_head.weight.t())).abs().max())
+    # embedding gradient: owned rows receive the output gradient of every token with that id, from every rank's shard
+    table = Embedding(V, D, dtype=torch.float64)
+    with torch.no_grad():
+        table.weight.copy_(torch.randn(V, D, dtype=torch.float64))
+    vpe = VocabParallelEmbedding(table, rank, world, dist.group.WORLD)
+    ids = torch.randint(0, V, (T,))
+    go = torch.randn(T, D, dtype=torch.float64)
+    out = vpe(ids[rank * cr:(rank + 1) * cr])
+    out.backward(go[rank * cr:(rank + 1) * cr])
+    want = torch.zeros(V, D, dtype=torch.float64).index_add_(0, ids, go)
+    e5 = float((vpe.weight.grad[: vpe.end - vpe.start] - want[vpe.start:vpe.end]).abs().max()) if vpe.end > vpe.start else 0.0
+    return f"{e1:.2e},{e2:.2e},{e3:.2e},{e4:.2e},{e5:.2e}"
+
+
 def _case_unequal_loader_exhaustion(rank, world):
     """Rank 1's data stream ends one batch early; rank 0's raises. Both ranks must leave `fetch_batch` the same way,
     before any step collective."""
@@ -220,6 +268,13 @@ def test_vocab_parallel_cross_entropy_entropy_and_embedding_match_the_full_vocab
     for r in _spawn(_case_vocab_parallel_loss_and_embedding, 2):
         assert r.count(",") == 3, r
         assert all(float(x) < 1e-5 for x in r.split(",")), r
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_vocab_parallel_head_loss_and_gradients_match_the_full_head(world):
+    for r in _spawn(_case_vocab_parallel_head, world):
+        assert r.count(",") == 4, r
+        assert all(float(x) < 2e-5 for x in r.split(",")), r      # the statement computes in fp32
 
 
 def test_rank_leaving_between_steps_ends_the_next_collective_with_an_error():

@@ -55,6 +55,17 @@ def test_fused_tp_gemms_match_nccl_reference(world):
     assert res["stats"]["ag_fused"] > 0 and res["stats"]["rs_fused"] > 0
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_vocab_parallel_head_and_embedding_match_the_full_vocabulary(world):
+    """Vocabulary-sharded head: gather riding on the logits GEMM, one (max, sum-exp, target) exchange per token inside the
+    loss kernel, reduce-scatter riding on the input-gradient GEMM; embedding rows written into the owners' token shards."""
+    _need(world)
+    from fused_tp_cases import run_vocab_parallel
+    res = run_vocab_parallel(world)
+    assert res["loss"] < 2e-3 and res["dh"] < 3e-2 and res["dw"] < 3e-2 and res["emb"] == 0.0 and res["demb"] < 2e-2, res
+    assert res["stats"].get("ag_fused", 0) > 0 and res["stats"].get("rs_fused", 0) > 0, res
+
+
 def test_tp2_model_uses_fused_collectives():
     _need(2)
     flat = _flat(tensor_parallel_size=2, data_parallel_shard_size=1)

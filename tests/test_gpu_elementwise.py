@@ -122,3 +122,47 @@ def test_adamw_and_sqnorm():
     s2 = a.float().pow(2).sum() + b.pow(2).sum()
     assert abs(s1.item() - s2.item()) / s2.item() < 1e-4
     assert torch.equal(ops.sq_norm([a, b]), s1)
+
+
+@pytest.mark.parametrize("rows,V,shards", [(300, 1000, 1), (128, 2007, 3), (64, 18992, 2)])
+def test_vocab_parallel_cross_entropy_kernel_on_one_gpu(rows, V, shards):
+    """`ce_vocab_parallel` with all R vocabulary shards of a row on this one GPU. Launches on one GPU may not wait on one
+    another, so the shards run in two passes over tables that are plain device tensors: the first pass (flags pre-set, no
+    gradient) only publishes every shard's (max, sum-exp, target) triple, the second pass finds all R triples present,
+    combines them and writes the gradient. Loss and gradient must equal the full-vocabulary fp32 statement."""
+    from torchllmtuner_b200.ops.cuda_ext import load
+    from torchllmtuner_b200.ops import reference as ref
+    ext = load()
+    torch.manual_seed(0)
+    full = (torch.randn(rows, V, device="cuda") * 2).bfloat16()
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    labels[::9] = -100
+    chunk = -(-V // shards)
+    chunk = -(-chunk // 8) * 8
+    # one table set per "rank": stats [R][rows] float4, flags [R][rows] uint32
+    stats = [torch.zeros(shards * rows * 4, device="cuda") for _ in range(shards)]
+    flags = [torch.zeros(shards * rows, dtype=torch.int32, device="cuda") for _ in range(shards)]
+    sp, fp = [s.data_ptr() for s in stats], [f.data_ptr() for f in flags]
+    # pass 1: publish every shard's triple (flags pre-set so that nothing waits), pass 2: the real run
+    for f in flags:
+        f.fill_(1)
+    work = []
+    for r in range(shards):
+        lo, hi = r * chunk, min(V, (r + 1) * chunk)
+        buf = torch.zeros(rows, chunk, dtype=torch.bfloat16, device="cuda")
+        buf[:, : hi - lo] = full[:, lo:hi]
+        work.append((lo, hi, buf))
+    for grad_pass in (False, True):
+        losses = []
+        for r, (lo, hi, buf) in enumerate(work):
+            losses.append(ext.ce_vocab_parallel(buf[:, : hi - lo], labels, lo, r, sp, fp, rows, 1, 1.0, -100, grad_pass))
+    torch.cuda.synchronize()
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    check_status("ce_vocab_parallel")
+    lf = full.float().requires_grad_()
+    want = ref.cross_entropy_sum(lf, labels)
+    (g,) = torch.autograd.grad(want, [lf])
+    for l in losses:      # every shard reports the same full-vocabulary row losses
+        assert abs(l.sum().item() - want.item()) / abs(want.item()) < 2e-3
+    got = torch.cat([buf[:, : hi - lo] for lo, hi, buf in work], dim=1)
+    _close(got, g, name="dlogits")

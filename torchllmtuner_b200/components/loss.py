@@ -87,20 +87,25 @@ def mse_loss(pred: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
 
 
 class LossFunctions:
-    """The pair the engine needs: a logits loss and a chunked head loss, both returning sums."""
+    """The pair the engine needs: a logits loss and a chunked head loss, both returning sums. With a vocabulary-parallel
+    head (`head` is then the `VocabParallelHead` module of the model) the loss always takes the hidden-state path."""
 
-    def __init__(self, num_chunks: int = 0, vocab_group=None, vocab_start: int = 0):
+    def __init__(self, num_chunks: int = 0, vocab_group=None, vocab_start: int = 0, head=None):
         self.num_chunks, self.vocab_group, self.vocab_start = num_chunks, vocab_group, vocab_start
+        self.head = head
 
     @property
     def chunked(self) -> bool:
-        return self.num_chunks > 0
+        return self.num_chunks > 0 or self.head is not None
 
     def from_logits(self, logits, targets):
         return cross_entropy_loss(logits, targets, self.vocab_group, self.vocab_start)
 
     def from_hidden(self, hidden, head_weight, targets):
-        return chunked_lm_head_cross_entropy(hidden, head_weight, targets, self.num_chunks)
+        if self.head is not None:
+            from ..parallel.vocab_parallel import vocab_parallel_head_loss
+            return vocab_parallel_head_loss(hidden, self.head, targets, max(1, self.num_chunks))
+        return chunked_lm_head_cross_entropy(hidden, head_weight, targets, max(1, self.num_chunks))
 
 
 def validate_loss_sum(loss: torch.Tensor) -> None:

@@ -49,9 +49,14 @@ class TensorParallelConfig:
     tp_colwise_modules: list[str] = field(default_factory=list)
     tp_rowwise_modules: list[str] = field(default_factory=list)
     tp_sequence_modules: list[str] = field(default_factory=list)
+    # Shard the head over the vocabulary like the embedding (vocabulary-parallel cross-entropy). False keeps the head
+    # replicated with its gradient all-reduced over the TP group, which is the only layout the reference accepts under
+    # sequence-parallel TP.
+    tp_vocab_parallel_head: bool = True
 
     def __post_init__(self):
         require_bool("enable_sequence_parallel", self.enable_sequence_parallel)
+        require_bool("tp_vocab_parallel_head", self.tp_vocab_parallel_head)
         for n in ("tp_colwise_modules", "tp_rowwise_modules", "tp_sequence_modules"):
             require_string_patterns(n, getattr(self, n))
 

@@ -434,6 +434,41 @@ std::vector<Tensor> ce_fwd_bwd(Tensor& logits, const Tensor& labels, double grad
   return {loss, lse};
 }
 
+// Vocabulary-parallel cross-entropy over one shard of the logits [rows, V/R] (in place: the shard becomes its gradient);
+// `stats` / `flags` are every rank's statistics and flag tables in symmetric memory (device addresses).
+Tensor ce_vocab_parallel(Tensor& logits, const Tensor& labels, int64_t vocab_start, int64_t me, const std::vector<int64_t>& stats,
+                         const std::vector<int64_t>& flags, int64_t cap, int64_t epoch, double grad_scale, int64_t ignore_index,
+                         bool write_grad) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_bf16(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0));
+  TORCH_CHECK(stats.size() == flags.size() && stats.size() >= 1 && stats.size() <= 8);
+  const int rows = (int)logits.size(0), V = (int)logits.size(1), R = (int)stats.size();
+  void* sp[8] = {nullptr};
+  void* fp[8] = {nullptr};
+  for (int i = 0; i < R; ++i) { sp[i] = reinterpret_cast<void*>(stats[i]); fp[i] = reinterpret_cast<void*>(flags[i]); }
+  Tensor loss = torch::empty({rows}, logits.options().dtype(torch::kFloat));
+  check_rc(llmt_ce_vocab_parallel(logits.data_ptr(), labels.data_ptr<int64_t>(), loss.data_ptr<float>(), rows, V, logits.stride(0),
+                                  vocab_start, R, (int)me, sp, fp, (int)cap, (uint32_t)epoch, (float)grad_scale, (int)ignore_index,
+                                  write_grad, status_ptr(), cur_stream()),
+           "llmt_ce_vocab_parallel");
+  return loss;
+}
+
+// Table rows of the ids this rank owns, stored into the output shard of the rank that owns each token.
+void vp_embed_scatter(const Tensor& ids, const Tensor& w, int64_t vstart, int64_t vend, const std::vector<int64_t>& out, int64_t chunk) {
+  c10::cuda::CUDAGuard guard(w.device());
+  check_bf16(w, "weight");
+  TORCH_CHECK(w.dim() == 2 && w.is_contiguous() && ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous());
+  TORCH_CHECK(out.size() >= 1 && out.size() <= 8);
+  void* op[8] = {nullptr};
+  for (size_t i = 0; i < out.size(); ++i) op[i] = reinterpret_cast<void*>(out[i]);
+  check_rc(llmt_vp_embed_scatter(ids.data_ptr<int64_t>(), w.data_ptr(), vstart, vend, op, (int)out.size(), (int)ids.numel(), (int)chunk,
+                                 (int)w.size(1), cur_stream()),
+           "llmt_vp_embed_scatter");
+}
+
 void adamw(Tensor& p32, const c10::optional<Tensor>& p16, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1,
            double b2, double eps, double wd, int64_t step, const c10::optional<Tensor>& clip_coef, double grad_scale,
            bool decoupled) {
@@ -641,6 +676,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd", &swiglu_bwd, py::arg("dout"), py::arg("gate"), py::arg("up"), py::arg("dgate_out"), py::arg("dup_out"),
         py::arg("row_limit") = py::none());
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("ce_vocab_parallel", &ce_vocab_parallel);
+  m.def("vp_embed_scatter", &vp_embed_scatter);
   m.def("adamw", &adamw);
   m.def("sqnorm", &sqnorm);
   m.def("sqnorm_scratch_floats", &sqnorm_scratch_floats);

@@ -81,6 +81,13 @@ int llmt_signal_peers(uint32_t* const* peer_flags, int npeers, int slot, uint32_
 int llmt_wait_flags(const uint32_t* flags, int n, uint32_t value, int site, uint32_t max_polls, int* status,
                     cudaStream_t st);
 
+// ---- vocabulary-parallel loss and embedding over peer memory (vocab_parallel.cu) ----
+int llmt_ce_vocab_parallel(void* logits, const int64_t* labels, float* row_loss, int rows, int Vr, int64_t ld,
+                           int64_t vocab_start, int R, int me, void* const* stats, void* const* flags, int cap, uint32_t epoch,
+                           float grad_scale, int ignore_index, int write_grad, int* status, cudaStream_t st);
+int llmt_vp_embed_scatter(const int64_t* ids, const void* w, int64_t vstart, int64_t vend, void* const* out, int R, int T,
+                          int chunk, int D, cudaStream_t st);
+
 // ---- attention (attention.cu) ----
 // q [Tq, Hq, HD], k/v [Tk, Hkv, HD] bf16 with token strides in elements; varlen via cu_seqlens (device int32).
 // tiles: device int32 [num_tiles][4] = {q_row_begin, q_row_end, k_row_begin, k_causal_end_for_first_row}; see attention.cu.

@@ -7,9 +7,10 @@ Outside the GEMMs every activation is sequence-sharded `[T/tp, D]`. A block gath
 attention projections and once in front of gate/up (one gather feeds q, k and v; one feeds gate and up), runs
 column-sharded GEMMs on full rows and local heads, and reduce-scatters the row-parallel outputs (o_proj, down_proj)
 back to `[T/tp, D]`. MoE blocks gather in, run experts whose intermediate dimension is sharded, and reduce-scatter
-out. The embedding is vocab-parallel (ids gathered, masked local lookup, reduce-scatter of the partial rows); the
-head stays replicated and its gradient, like that of every other replicated parameter (norms, q/k norms, router),
-is summed over the TP group before the data-parallel reduction.
+out. The embedding and the head are vocabulary-parallel (`parallel/vocab_parallel.py`: every id's row is written straight
+into the owner's token shard; the loss exchanges three scalars per token); the gradients of the parameters that stay
+replicated (norms, q/k norms, router, and the head when `tp_vocab_parallel_head` is off) are summed over the TP group
+before the data-parallel reduction.
 
 Two implementations of the row collectives sit behind the same autograd functions: torch.distributed (NCCL / gloo)
 and, on CUDA with peer access, staged P2P copies driven by the comm warps of the consuming / producing GEMM
@@ -220,13 +221,16 @@ class VocabParallelEmbedding(nn.Module):
         self.group, self.rank, self.size = group, rank, size
 
     def forward(self, ids_local: torch.Tensor) -> torch.Tensor:
+        from .vocab_parallel import _EmbedScatter, vocab_exchange
         R = self.size
         ids = torch.empty(ids_local.shape[0] * R, dtype=ids_local.dtype, device=ids_local.device)
         dist.all_gather_into_tensor(ids, ids_local.contiguous(), group=self.group)
-        mine = (ids >= self.start) & (ids < self.end)
-        rows = torch.nn.functional.embedding((ids - self.start).clamp(0, self.chunk - 1), self.weight)
-        rows = rows * mine.to(rows.dtype).unsqueeze(-1)
-        return reduce_scatter_along(rows, self.group)
+        ex = None
+        w = self.weight
+        if w.is_cuda and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and ids.shape[0] % R == 0 and \
+                os.environ.get("LLMT_DISABLE_FUSED_TP") != "1":
+            ex = vocab_exchange(self.group, w.device, ids.shape[0], w.shape[1])
+        return _EmbedScatter.apply(w, ids, self, ex)
 
 
 # ---------------------------------------------------------------------------------------------- plan + apply
@@ -325,6 +329,14 @@ def apply_tp(model, topo, tp_config) -> dict:
         parent = getattr(parent, part)
     setattr(parent, emb_path[-1], VocabParallelEmbedding(bound.embedding, rank, size, group))
     applied["embedding"] = "vocab"
+    if getattr(tp_config, "tp_vocab_parallel_head", True):
+        from .vocab_parallel import VocabParallelHead
+        head_path = model.decoder_structure.head.split(".")
+        parent = model
+        for part in head_path[:-1]:
+            parent = getattr(parent, part)
+        setattr(parent, head_path[-1], VocabParallelHead(getattr(parent, head_path[-1]), rank, size, group))
+        applied["head"] = "vocab"
     for _, p in model.named_parameters():
         if not hasattr(p, "tp_shard_dim"):
             p.tp_replicated = True

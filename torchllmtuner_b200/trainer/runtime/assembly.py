@@ -49,7 +49,18 @@ def prepare_parallel_model(config, env):
 
 
 def build_loss_functions(config, env, asm) -> LossFunctions:
-    return LossFunctions(num_chunks=config.training.chunked_loss_num_chunks)
+    """Under tensor parallelism the head is vocabulary-sharded (unless `tp_vocab_parallel_head` is off): the loss service
+    then owns the sharded head module and exchanges per-token statistics over the TP group."""
+    from ...parallel.vocab_parallel import VocabParallelHead
+    head = None
+    model = asm.model
+    if env.topo.tp > 1:
+        cand = model
+        for part in model.decoder_structure.head.split("."):
+            cand = getattr(cand, part)
+        if isinstance(cand, VocabParallelHead):
+            head = cand
+    return LossFunctions(num_chunks=config.training.chunked_loss_num_chunks, head=head)
 
 
 def build_optimizer_stack(config, env, asm):
