@@ -70,9 +70,18 @@ class Model(nn.Module):
 
 
 def run_stock(args) -> int:
+    if getattr(args, "tp", 1) > 1 and args.model == "qwen3_8b" and getattr(args, "ep", 1) == 1:
+        from baseline.stock_parallel import run_stock_tp
+        return run_stock_tp(args)
+    if getattr(args, "ep", 1) > 1 and args.model == "qwen3_30b_a3b" and getattr(args, "tp", 1) == 1:
+        from baseline.stock_parallel import run_stock_ep
+        return run_stock_ep(args)
     if getattr(args, "tp", 1) > 1 or getattr(args, "ep", 1) > 1 or getattr(args, "cp_ulysses", 1) > 1 or getattr(args, "cp_kv", 1) > 1 \
             or args.model != "qwen3_8b":
-        print(json.dumps({"impl": "stock", "unavailable": "the stock-PyTorch arm covers the dense FSDP configuration only"}))
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "stock", "unavailable": "the stock-PyTorch arms cover dense FSDP, TP + SP over all ranks and "
+                              "EP over all ranks; the reference itself rejects context parallelism for Qwen models "
+                              "(llmtuner/parallel/context_parallel/plan.py:27-34)"}))
         return 0
     import torch.distributed as dist
     from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard

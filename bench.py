@@ -109,6 +109,8 @@ def build_config(args, world: int):
                 fsdp_implementation=args.fsdp_impl, deterministic=False, gradient_accumulation_steps=args.accum)
     if args.qkv == "fused":
         flat["qkv_projection"] = "fused"
+    if args.dataset != "random":
+        flat["dataset"] = args.dataset
     if args.tp > 1:
         flat["tensor_parallel_size"] = args.tp
     if args.ep > 1:
@@ -153,6 +155,8 @@ def main() -> int:
     ap.add_argument("--cp-kv", type=int, default=1)
     ap.add_argument("--global-batch", type=int, default=0, help="sequences per step over the whole job (default: one per data-parallel rank)")
     ap.add_argument("--accum", type=int, default=1, help="gradient accumulation steps")
+    ap.add_argument("--dataset", default="random", choices=["random", "random_packed"],
+                    help="random: one document per row; random_packed: rows packed from documents of log-uniform length 512..32768")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -228,7 +232,7 @@ def main() -> int:
     mem = torch.cuda.max_memory_allocated() / 2 ** 30
     out = {"metric": f"training tokens/sec/box (device-timed, max over ranks), {args.model} {par} bf16 seq {args.seq}", "value": value,
            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_dev / args.steps,
-           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens" + (" packed from documents of log-uniform length 512..32768" if args.dataset == "random_packed" else "") + ", random-init weights",
            "config": {"model": args.model + (f"[layers={args.layers}]" if args.layers else ""), "global_batch": cfg.training.global_batch_size,
                       "seq_len": args.seq, "parallelism": par, "activation_checkpointing": args.ac,
                       "loss": f"chunked x{args.loss_chunks}", "l2": "inputs (16 GB of weights per step) larger than the 126 MB L2",

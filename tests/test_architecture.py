@@ -14,7 +14,7 @@ ALLOWED = {
     "csrc": {"errors"},
     "accelerator": {"errors", "utils", "ops"},                              # the capability registry probes the extension
     "ops": {"errors", "csrc", "utils", "parallel", "models"},          # ops.gemm asks the comm queue; kernel_bench builds an expert stack
-    "models": {"errors", "ops", "utils", "parallel", "config"},
+    "models": {"errors", "ops", "utils", "parallel", "config", "accelerator"},   # L4 sits on the L1 collectives (balance-loss sums)
     "memory": {"errors", "ops", "utils"},
     "datasets": {"errors", "utils", "config", "components"},
     "components": {"errors", "ops", "utils", "accelerator", "config", "models", "parallel", "datasets"},

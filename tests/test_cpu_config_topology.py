@@ -211,9 +211,16 @@ def test_inert_flags_are_reported_and_every_other_flag_is_read_somewhere():
 
     import torchllmtuner_b200.config.training_config as tc
     from torchllmtuner_b200.config.cli_config import PARSER_GROUPS
-    from torchllmtuner_b200.config.inert_fields import INERT_FIELDS, inert_fields_set
+    from torchllmtuner_b200.config.inert_fields import INERT_FIELDS, UNSUPPORTED_FIELDS, check_unsupported_fields, inert_fields_set
+    from torchllmtuner_b200.errors import UnsupportedCombinationError
     cfg = LLMTunerConfig()
     assert inert_fields_set(cfg) == []
+    check_unsupported_fields(cfg)
+    for flat in (dict(grad_norm_precision="parameter"), dict(fsdp_expert_reduce_layout="split")):
+        bad = LLMTunerConfig()
+        bad.apply_flat(flat)
+        with pytest.raises(UnsupportedCombinationError):          # semantics-changing flags raise instead of being ignored
+            check_unsupported_fields(bad)
     cfg.apply_flat(dict(norm_backend="other", sharded_expert_parallel=True))
     assert {n for n, _ in inert_fields_set(cfg)} == {"norm_backend", "sharded_expert_parallel"}
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -226,7 +233,7 @@ def test_inert_flags_are_reported_and_every_other_flag_is_read_somewhere():
                 src += open(os.path.join(d, f)).read()
     groups = list(PARSER_GROUPS) + [o for o in vars(tc).values() if dataclasses.is_dataclass(o) and isinstance(o, type)]
     silent = [f"{g.__name__}.{f.name}" for g in dict.fromkeys(groups) for f in dataclasses.fields(g)
-              if f.name not in INERT_FIELDS and not re.search(r"\b" + re.escape(f.name) + r"\b", src)]
+              if f.name not in INERT_FIELDS and f.name not in UNSUPPORTED_FIELDS and not re.search(r"\b" + re.escape(f.name) + r"\b", src)]
     assert silent == [], silent
 
 
@@ -258,3 +265,19 @@ def test_wsd_schedule_every_step(kind, floor, total, warmup, ratio):
     if warmup > 0:   # warm-up is not blended with the floor
         assert wsd_factor(0, warmup=warmup, total=total, decay_ratio=ratio, decay_type=kind, min_lr_factor=floor) == pytest.approx(1 / min(warmup, total))
     assert round(100 * 0.29) == 29 and resolve_phases(100, 10, 0.29)[2] == 29   # rounded, not truncated
+
+
+def test_module_pattern_grammar():
+    from torchllmtuner_b200.parallel.module_patterns import compile_module_pattern, module_name_matches, resolve_module_patterns
+    names = [f"model.layers.{i}.{m}" for i in range(12) for m in ("mlp", "mlp.gate_proj", "self_attn")] + ["model.norm", "lm_head"]
+    assert resolve_module_patterns(names, ["model.layers.{0-3}.mlp"]) == {f"model.layers.{i}.mlp" for i in range(4)}
+    assert resolve_module_patterns(names, ["model.layers.{*}.self_attn"]) == {f"model.layers.{i}.self_attn" for i in range(12)}
+    assert module_name_matches("model.layers.10.mlp.gate_proj", "model.layers.1?.mlp.*")
+    assert not module_name_matches("model.layers.1.mlp", "model.layers.{10-11}.mlp")       # a range is a number, not a prefix
+    assert not module_name_matches("model.layers.x.mlp", "model.layers.{*}.mlp")
+    assert module_name_matches("lm_head", "lm_head") and not module_name_matches("lm_head2", "lm_head")    # whole-name match
+    with pytest.raises(ValueError):
+        resolve_module_patterns(names, ["model.layer.{0-3}.mlp"], "test")                  # a typo selects nothing: refused
+    for bad in ("a.{3-1}", "a.{x}", "a.{1-", "a.}"):
+        with pytest.raises(ValueError):
+            compile_module_pattern(bad)

@@ -38,6 +38,34 @@ def test_tp2_dp2_matches_single_rank():
     _close(ref["loss"], got["loss"], 5e-5)
 
 
+def test_fsdp_ignored_modules_are_reduced_and_stepped():
+    """Parameters named by `fsdp_ignored_modules` stay whole on every rank; their gradient is summed over the data ranks
+    and the optimizer steps them, so the curve equals the fully sharded one (and differs from a run that froze them)."""
+    ref = run_ranks(1, base_flat())
+    got = run_ranks(2, base_flat(data_parallel_shard_size=2, fsdp_ignored_modules=["layers\\.1\\.mlp", "norm"]))
+    _close(ref["loss"], got["loss"], 2e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 2e-4)
+
+
+def test_fsdp_pattern_units_match_single_rank():
+    """`fsdp_apply_modules`: selected modules become sharding units of their own (two same-size projections of one block
+    included); the curve is unchanged, with and without activation checkpointing."""
+    ref = run_ranks(1, base_flat())
+    pats = ["model.layers.{0-1}.mlp.gate_proj", "model.layers.{0-1}.mlp.up_proj", "model.layers.*.self_attn"]
+    for ac in ("none", "full"):
+        got = run_ranks(2, base_flat(data_parallel_shard_size=2, fsdp_apply_modules=pats, activation_checkpoint_mode=ac))
+        _close(ref["loss"], got["loss"], 2e-5)
+        _close(ref["grad_norm"], got["grad_norm"], 2e-4)
+
+
+def test_single_rank_accumulation_matches_one_large_batch():
+    """One shard rank with gradient accumulation accumulates in fp32: four micro-batches equal one batch of four rows."""
+    ref = run_ranks(1, base_flat())
+    got = run_ranks(1, base_flat(gradient_accumulation_steps=4))
+    _close(ref["loss"], got["loss"], 2e-5)
+    _close(ref["grad_norm"], got["grad_norm"], 2e-4)
+
+
 MOE = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
 
 

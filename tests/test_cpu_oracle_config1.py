@@ -1,4 +1,4 @@
-"""BASELINE configuration 1: tiny Qwen3 dense on CPU, single process, fp32, 20 AdamW steps on uniform random tokens from
+"""The CPU oracle configuration: tiny Qwen3 dense on CPU, single process, fp32, 20 AdamW steps on uniform random tokens from
 seed 0. The oracle is an independent plain-PyTorch statement of the same architecture (`baseline/stock_arm.py::Model`,
 library `nn.Linear` / `F.scaled_dot_product_attention` / `nn.RMSNorm`), started from the same weights and fed the same
 batches; thresholds are the reference's acceptance numbers (per-step loss absolute error <= 0.02, relative <= 0.005)."""

@@ -317,3 +317,31 @@ def test_kernel_status_code_rides_in_the_step_read_and_stops_the_step(monkeypatc
             tr.train_step()
     finally:
         tr.close()
+
+
+def test_per_op_selective_checkpointing_matches_no_checkpointing():
+    """selective / policy "op": attention and every other linear keep their outputs, the rest is replayed. The curve is the
+    one without checkpointing, the frame keeps strictly less than a whole block, and a forced-recompute weight shape changes
+    what is kept without changing the result."""
+    from torchllmtuner_b200.ops import functional as F
+    kept = []
+    orig = F.SelectiveReplay.put
+
+    def spy(self, value):
+        orig(self, value)
+        kept.append(self.kept_bytes)
+    F.SelectiveReplay.put = spy
+    try:
+        base = run(tiny_config(steps=3, activation_checkpoint_mode="none"))
+        sel = run(tiny_config(steps=3, activation_checkpoint_mode="selective"))
+        n_default = len(kept)
+        forced = run(tiny_config(steps=3, activation_checkpoint_mode="selective", force_recompute_mm_shapes_by_fqns=["mlp.gate_proj"]))
+        n_forced = len(kept) - n_default
+        blk = run(tiny_config(steps=3, activation_checkpoint_mode="selective", selective_ac_policy="block"))
+    finally:
+        F.SelectiveReplay.put = orig
+    for other in (sel, forced, blk):
+        assert max(abs(a - b) for a, b in zip(base, other)) < 1e-5, (base, other)
+    assert n_default > 0 and 0 < n_forced < n_default          # gate/up share a shape: both leave the kept set
+    with pytest.raises(ValueError):
+        run(tiny_config(steps=1, activation_checkpoint_mode="selective", force_recompute_mm_shapes_by_fqns=["no_such_module"]))

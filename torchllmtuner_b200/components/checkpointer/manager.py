@@ -1,4 +1,5 @@
-"""Checkpoint manager placeholder wired into the trainer; the full implementation lives in `dcp_manager.py`."""
+"""The checkpoint manager interface and its disabled form: the object a trainer holds when `checkpoint.enable` is off.
+Every call is a no-op; `dcp_manager.DistributedCheckpointManager` overrides them when checkpointing is on."""
 from __future__ import annotations
 
 

@@ -74,11 +74,14 @@ class GradientClipper:
 
     @torch.no_grad()
     def __call__(self) -> torch.Tensor:
-        dense, expert, tp_rep = [], [], []
+        dense, expert, tp_rep, whole = [], [], [], []
         tp = self.topo.tp > 1
         for rt in self.runtimes:
             for u in rt.units:
                 if not u.has_grad:
+                    continue
+                if getattr(u, "is_replicated", False):
+                    whole.append(u.grad_shard)      # identical on every data rank: counted once, after the group sums
                     continue
                 (expert if u.is_expert else dense).append(u.grad_shard)
                 if tp:
@@ -105,6 +108,8 @@ class GradientClipper:
         elif self.topo.size("dp_shard_cp") > 1:
             self._reduce(sq_e, "dp_shard_cp")
         total = (sq_d + sq_e).reshape(1)
+        if whole:
+            total = total + ops.sq_norm(whole).reshape(1).to(self.device)
         if self.device.type == "cuda":
             from ...ops.cuda_ext import load
             load().clip_coef(total, self.max_norm, self.coef, self.norm, self.finite)

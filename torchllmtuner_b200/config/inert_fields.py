@@ -14,11 +14,9 @@ INERT_FIELDS: dict[str, str] = {
     "rotary_compute_dtype": "rotary tables are always fp32",
     "rotary_cache_dtype": "rotary tables are always fp32",
     "fsdp_cpu_offload_pin_memory": "host-resident optimizer state is always pinned",
-    "fsdp_apply_modules": "sharding units are the decoder blocks plus embedding / head; user patterns are not applied",
     "enable_fsdp_symm_mem": "the native FSDP runtime always uses its own symmetric arena on CUDA (LLMT_DISABLE_FUSED_COMM=1 turns it off)",
     "fsdp_symm_mem_scope": "see enable_fsdp_symm_mem",
-    "fsdp_expert_reduce_layout": "expert gradients are reduced in storage order",
-    "fsdp_expert_reduce_workspace_limit_bytes": "see fsdp_expert_reduce_layout",
+    "fsdp_expert_reduce_workspace_limit_bytes": "expert gradients are reduced in storage order, without a workspace",
     "tp_sequence_modules": "sequence boundaries are placed by the model's TP plan",
     "context_parallel_strategy": "the strategy follows from which context-parallel degree is > 1",
     "ep_torchao_pad_multiple": "the torchao dispatcher is not available; segments are padded to 128 rows",
@@ -38,8 +36,15 @@ INERT_FIELDS: dict[str, str] = {
     "enable_async_tensor_parallel": "TP collectives are fused into the GEMM kernels, there is no compiler pass to enable",
     "buffer_patterns": "EMA tracks parameters only",
     "determinism_check": "activation recomputation is bitwise deterministic by construction (same kernels, same order)",
-    "grad_norm_precision": "the gradient norm is always accumulated in fp32 over the fp32 gradient shards",
-    "force_recompute_mm_shapes_by_fqns": "selective checkpointing works on whole blocks",
+}
+
+# Flags whose non-default value would CHANGE what is trained or how gradients are formed, and that this platform does not
+# implement: setting one raises instead of being ignored. Value: (accepted default values, reason).
+UNSUPPORTED_FIELDS: dict[str, tuple[tuple, str]] = {
+    "grad_norm_precision": (("float32",), "the gradient norm is accumulated in fp32 over the fp32 gradient shards; a norm "
+                                           "taken in the parameter dtype is not implemented"),
+    "fsdp_expert_reduce_layout": (("storage",), "expert gradients are reduced in storage order; the split gate / up / down "
+                                                 "reduce layout is not implemented"),
 }
 
 
@@ -52,6 +57,15 @@ def _walk(obj, prefix=""):
             yield from _walk(v, prefix + f.name + ".")
         else:
             yield f, v
+
+
+def check_unsupported_fields(config) -> None:
+    """Raises `UnsupportedCombinationError` for the first semantics-changing flag set to a value this platform lacks."""
+    from ..errors import UnsupportedCombinationError
+    for f, v in _walk(config):
+        rule = UNSUPPORTED_FIELDS.get(f.name)
+        if rule is not None and v not in rule[0] and v not in (None, [], ()):
+            raise UnsupportedCombinationError(f"--{f.name}={v!r} is not supported: {rule[1]}")
 
 
 def inert_fields_set(config) -> list[tuple[str, str]]:

@@ -28,7 +28,14 @@ class SelectiveACConfig:
     preserve_rng_state: bool = True
     determinism_check: str = "default"
     debug: bool = False
-    save_every_nth_block: int = 2   # selective mode: every n-th block keeps its activations
+    # "op": every block is checkpointed with the per-op policy (attention and every other linear keep their outputs, the
+    # rest is recomputed; linears named by force_recompute_mm_shapes_by_fqns are always recomputed). "block": every
+    # `save_every_nth_block`-th block keeps all its activations and the others recompute everything.
+    selective_ac_policy: str = "op"
+    save_every_nth_block: int = 2
+
+    def __post_init__(self):
+        require_choice("selective_ac_policy", self.selective_ac_policy, ("op", "block"))
 
 
 @dataclass

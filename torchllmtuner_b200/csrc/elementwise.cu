@@ -540,9 +540,11 @@ __global__ void clip_coef_kernel(const float* __restrict__ total_sq, float max_n
   if (finite != nullptr) finite[0] = isfinite(n) ? 1 : 0;
 }
 
+int sm_count();   // gemm.cu: SMs of the current device
+
 static inline int grid_for(int64_t n, int threads, int per_sm = 8) {
   int64_t b = (n + threads - 1) / threads;
-  const int64_t cap = (int64_t)148 * per_sm;
+  const int64_t cap = (int64_t)sm_count() * per_sm;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
@@ -557,7 +559,7 @@ extern "C" int llmt_rmsnorm_fwd(const void* x, const void* res, const void* w, v
   if (T <= 0) return 0;
   if (D % 8 || D > 8 * kRowThreads * 4) return -10;
   const int nv = (D + 8 * kRowThreads - 1) / (8 * kRowThreads);
-  const int grid = T < 148 * 8 ? T : 148 * 8;
+  const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
   auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)res; auto W = (const __nv_bfloat16*)w;
   auto Y = (__nv_bfloat16*)y; auto S = (__nv_bfloat16*)sum_out;
   if (nv == 1) rmsnorm_fwd_kernel<1><<<grid, kRowThreads, 0, st>>>(X, R, W, Y, S, rstd, T, D, eps);
@@ -567,7 +569,11 @@ extern "C" int llmt_rmsnorm_fwd(const void* x, const void* res, const void* w, v
 }
 
 // dw_partial: fp32 scratch of llmt_rmsnorm_bwd_partials(T) * D floats.
-extern "C" int llmt_rmsnorm_bwd_partials(int T) { return T < 148 * 2 ? (T < 1 ? 1 : T) : 148 * 2; }
+// Two row blocks per SM, at most 296 (the allocation-free entry point in noalloc.cu sizes its scratch for that bound).
+extern "C" int llmt_rmsnorm_bwd_partials(int T) {
+  const int cap = sm_count() * 2 < 296 ? sm_count() * 2 : 296;
+  return T < cap ? (T < 1 ? 1 : T) : cap;
+}
 extern "C" int llmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                                 float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, int T, int D,
                                 cudaStream_t st) {
@@ -603,7 +609,8 @@ extern "C" int llmt_qk_norm_rope_fwd(const void* x, int64_t tok_stride, const vo
 extern "C" int llmt_qk_norm_rope_bwd_partials(int T, int H) {
   const int64_t items = (int64_t)T * H;
   const int64_t b = (items + 7) / 8;
-  return (int)(b < 1 ? 1 : (b > 148 * 4 ? 148 * 4 : b));
+  const int64_t cap = (int64_t)sm_count() * 4;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 extern "C" int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, const void* x, int64_t tok_stride, const void* w,
                                      const float* cosb, const float* sinb, const float* rstd, void* dx,
@@ -669,7 +676,7 @@ extern "C" int llmt_adamw(float* p32, void* p16, const void* g, int g_is_bf16, f
 }
 
 // scratch must hold llmt_sqnorm_scratch_floats() floats.
-extern "C" int llmt_sqnorm_scratch_floats() { return 148 * 8; }
+extern "C" int llmt_sqnorm_scratch_floats() { return sm_count() * 8; }
 extern "C" int llmt_sqnorm(const void* x, int is_bf16, int64_t n, float* scratch, float* out, int accumulate,
                            cudaStream_t st) {
   if (n <= 0) {

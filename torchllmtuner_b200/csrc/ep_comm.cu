@@ -18,6 +18,8 @@
 
 namespace llmt {
 
+int sm_count();   // gemm.cu: SMs of the current device
+
 constexpr int kEpMaxExperts = 1024;
 
 struct EpPeers {
@@ -293,6 +295,6 @@ extern "C" int llmt_ep_clone_rows(const void* src, void* dst, const int* seg_off
                                   cudaStream_t st) {
   if (G <= 0) return 0;
   if (D % 8) return -10;
-  ep_clone_rows_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, seg_offsets, totals, G, D, zero_pad);
+  ep_clone_rows_kernel<<<sm_count() * 4, 256, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, seg_offsets, totals, G, D, zero_pad);
   LLMT_CHECK_LAUNCH();
 }

@@ -35,6 +35,67 @@ def _2d(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
 
 
+# ----------------------------------------------------------------------------------------------- per-op checkpointing
+class SelectiveReplay:
+    """Per-op activation checkpointing of one block frame (reference policy: llmtuner/memory/activation_checkpoint.py:203-256).
+
+    The block's first forward runs without a graph in `record` mode and its replay inside backward in `replay` mode. Ops
+    the policy keeps store their output while recording and hand it back while replaying, so the replay only rebuilds the
+    autograd node (inputs saved, nothing computed); every other op is recomputed. Policy: attention is kept; linears are
+    kept except every second one (counted in call order, restarted per frame so that record and replay agree); a linear
+    whose weight shape is in `recompute_mm_shapes` is always recomputed and not counted."""
+
+    def __init__(self, recompute_mm_shapes=()):
+        self.recompute_mm_shapes = {tuple(s) for s in recompute_mm_shapes}
+        self.store: list = []
+        self.mode = "record"
+        self.mm_count = 0
+        self.cursor = 0
+        self.kept_bytes = 0
+
+    def begin(self, mode: str) -> None:
+        self.mode, self.mm_count, self.cursor = mode, 0, 0
+
+    def keeps_linear(self, w: torch.Tensor) -> bool:
+        if tuple(w.shape) in self.recompute_mm_shapes:
+            return False
+        self.mm_count += 1
+        return self.mm_count % 2 == 1
+
+    def put(self, value) -> None:
+        self.store.append(value)
+        for t in (value if isinstance(value, tuple) else (value,)):
+            self.kept_bytes += t.numel() * t.element_size()
+
+    def take(self):
+        v = self.store[self.cursor]
+        self.cursor += 1
+        return v
+
+
+_SAC: SelectiveReplay | None = None
+
+
+class sac_frame:
+    """Context manager that makes `frame` the active per-op checkpoint frame in `mode` ("record" / "replay")."""
+
+    def __init__(self, frame: SelectiveReplay | None, mode: str):
+        self.frame, self.mode = frame, mode
+
+    def __enter__(self):
+        global _SAC
+        self.prev = _SAC
+        _SAC = self.frame
+        if self.frame is not None:
+            self.frame.begin(self.mode)
+        return self.frame
+
+    def __exit__(self, *exc):
+        global _SAC
+        _SAC = self.prev
+        return False
+
+
 # ----------------------------------------------------------------------------------------------- GEMM
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=False, max_ctas=0):
     """out[M,N] (+)= op(a) @ op(b)^T-style product on the tcgen05 kernel.
@@ -60,10 +121,12 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=F
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, y_kept=None):
         x2 = _2d(x)
         ctx.save_for_backward(x2, w)
         ctx.xshape = x.shape
+        if y_kept is not None:              # replay of a kept op: only the graph node is rebuilt
+            return y_kept.view(*x.shape[:-1], w.shape[0])
         return gemm(x2, w).reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -81,17 +144,37 @@ class _Linear(torch.autograd.Function):
                 dw = None
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)        # dy^T [N,M] @ x [M,K]
-        return dx, dw
+        return dx, dw, None
+
+
+class _KeptLinear(torch.autograd.Function):
+    """Replay of a kept linear off the kernel path (CPU, odd shapes): returns the kept output, backward is the linear's."""
+
+    @staticmethod
+    def forward(ctx, x, w, y_kept):
+        ctx.save_for_backward(x, w)
+        return y_kept.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
+        return (dy2 @ w.to(dy2.dtype)).reshape(x.shape), (dy2.t() @ x2).to(w.dtype), None
 
 
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    if _use_cuda(x) and x.dtype == torch.bfloat16:
-        if w.shape[0] % 8 or w.shape[1] % 8:
-            # a TMA row must start on a 16-byte boundary: projections with fewer than 8 (or an odd number of) features,
-            # e.g. one gate value per head, cannot be tiled by the tcgen05 kernel and take the plain library product
-            return ref.linear(x, w)
-        return _Linear.apply(x, w)
-    return ref.linear(x, w)
+    # a TMA row must start on a 16-byte boundary: projections with fewer than 8 (or an odd number of) features, e.g. one
+    # gate value per head, cannot be tiled by the tcgen05 kernel and take the plain library product
+    kernel = _use_cuda(x) and x.dtype == torch.bfloat16 and not (w.shape[0] % 8 or w.shape[1] % 8)
+    frame = _SAC
+    if frame is not None and frame.keeps_linear(w):
+        if frame.mode == "record":
+            y = _Linear.apply(x, w) if kernel else ref.linear(x, w)
+            frame.put(y.detach())
+            return y
+        kept = frame.take()
+        return _Linear.apply(x, w, kept) if kernel else _KeptLinear.apply(x, w, kept)
+    return _Linear.apply(x, w) if kernel else ref.linear(x, w)
 
 
 # ----------------------------------------------------------------------------------------------- RMSNorm
@@ -198,21 +281,22 @@ def swiglu(gate, up, row_limit=None):
 # ----------------------------------------------------------------------------------------------- attention
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, meta: AttnMeta, scale):
-        o, lse = _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
+    def forward(ctx, q, k, v, meta: AttnMeta, scale, kept=None):
+        o, lse = kept if kept is not None else _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.meta, ctx.scale = meta, scale
-        return o
+        ctx.mark_non_differentiable(lse)
+        return o, lse
 
     @staticmethod
-    def backward(ctx, do):
+    def backward(ctx, do, _dlse=None):
         q, k, v, o, lse = ctx.saved_tensors
         if do.stride(2) != 1 or do.stride(1) != do.shape[2]:
             do = do.contiguous()
         m = ctx.meta
         dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, m.q_tiles, m.k_tile_passes, ctx.scale, m.causal, not m.covers_all_keys,
                                      attention_backward_mode() == "fused")
-        return dq, dk, dv, None, None
+        return dq, dk, dv, None, None, None
 
 
 _ATTN_BWD_MODE: str | None = None
@@ -245,7 +329,14 @@ def attention(q, k, v, meta: AttnMeta, scale: float | None = None):
     if _use_cuda(q) and q.dtype == torch.bfloat16:
         if meta.q_tiles is None:
             raise ValueError("AttnMeta was built without device tables; pass device= to AttnMeta.build")
-        return _Attention.apply(q, k, v, meta, scale)
+        frame = _SAC
+        if frame is None:
+            return _Attention.apply(q, k, v, meta, scale)[0]
+        if frame.mode == "record":                       # attention is always kept by the per-op policy
+            o, lse = _Attention.apply(q, k, v, meta, scale)
+            frame.put((o.detach(), lse.detach()))
+            return o
+        return _Attention.apply(q, k, v, meta, scale, frame.take())[0]
     out, _ = ref.attention_pieces(q, k, v, meta.pieces, meta.causal, scale)
     return out
 

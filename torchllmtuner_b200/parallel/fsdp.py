@@ -129,6 +129,8 @@ class FSDPRuntime:
         self.param_dtype = param_dtype
         self.reduce_dtype = _dtype(fsdp_config.fsdp_reduce_dtype)
         self.ac_mode, self.ac_save_every = ac_mode, ac_save_every
+        self.grad_accum_steps = 1          # set by apply_fsdp from the training configuration
+        self.named_units: dict = {}
         for name in ("fsdp_forward_prefetch_count", "fsdp_backward_prefetch_count"):
             if getattr(fsdp_config, name, 0) > 1:
                 from ..errors import UnsupportedCombinationError
@@ -153,7 +155,11 @@ class FSDPRuntime:
         self._slot_owner: dict = {}
 
     # ------------------------------------------------------------------ construction
-    def add_unit(self, name, named_params, *, expert: bool = False) -> FlatUnit | None:
+    def add_unit(self, name, named_params, *, expert: bool = False, replicated: bool = False,
+                 block_index: int | None = None) -> FlatUnit | None:
+        """`replicated`: the unit is not sharded at all (every rank keeps the whole flat buffer and steps it); its gradient is
+        summed over the data ranks (`dp_cp`) before the optimizer, which is how parameters excluded from FSDP by
+        `fsdp_ignored_modules` are kept in step (reference: llmtuner/trainer/runtime/gradients.py:50-83)."""
         named_params = [(n, p) for n, p in named_params if id(p) not in self.unit_of_param]
         seen, uniq = set(), []
         for n, p in named_params:
@@ -162,19 +168,29 @@ class FSDPRuntime:
                 uniq.append((n, p))
         if not uniq:
             return None
-        if expert and self.topo.ep > 1:
+        if replicated:
+            group, world, rank = None, 1, 0
+        elif expert and self.topo.ep > 1:
             group, world, rank = self.topo.get_group("efsdp"), self.topo.efsdp, self.topo.coord("efsdp")
         else:
             group, world, rank = self.group, self.world, self.rank
         u = FlatUnit(name, uniq, group=group, rank=rank, world=world, device=self.device, param_dtype=self.param_dtype,
                      reduce_dtype=self.reduce_dtype, replicate_group=self.replicate_group, is_expert=expert)
+        u.replicated_group = self.topo.get_group("dp_cp") if replicated else None
+        u.is_replicated = replicated
+        # Gather / gradient buffers rotate between two slots by block parity. Units of one block that have the same size
+        # (two selected projections, say) would land in the same buffer, so each gets its own lane of the pool.
+        u.slot_index = (block_index % 2) if block_index is not None else 0
+        twins = [v for v in self.units if getattr(v, "block_index", None) == block_index and block_index is not None
+                 and v.padded == u.padded and v.is_expert == u.is_expert]
+        u.block_index, u.lane = block_index, len(twins)
         self.units.append(u)
         for _, p in uniq:
             self.unit_of_param[id(p)] = u
         return u
 
     def _pool(self, table, unit: FlatUnit, count: int, dtype) -> list[torch.Tensor]:
-        key = (unit.padded, dtype, unit.is_expert)
+        key = (unit.padded, dtype, unit.is_expert, getattr(unit, "lane", 0))
         bufs = table.setdefault(key, [])
         while len(bufs) < count:
             bufs.append(torch.zeros(unit.padded, dtype=dtype, device=self.device))
@@ -208,7 +224,10 @@ class FSDPRuntime:
             u.gathered = u.world == 1 or persistent
             u.needs_param_sync = u.world > 1 and persistent     # persistent full copies are refreshed after each step
             if u.world == 1:
-                gbuf = torch.zeros(u.padded, dtype=u.param_dtype, device=self.device)
+                # one shard rank: the flat buffer itself accumulates over micro-batches, so with gradient accumulation (or
+                # a cross-rank sum for a replicated unit) it is fp32 like the sharded path's reduce buffer
+                wide = self.grad_accum_steps > 1 or getattr(u, "is_replicated", False)
+                gbuf = torch.zeros(u.padded, dtype=torch.float32 if wide else u.param_dtype, device=self.device)
                 u.grad_shard = gbuf
             else:
                 gpool = self._pool(self._grad_bufs, u, 2, u.param_dtype) if not persistent else [torch.zeros(u.padded, dtype=u.param_dtype, device=self.device)]
@@ -217,8 +236,7 @@ class FSDPRuntime:
             u.bind_grad(gbuf, use_main)
 
     def _unit_slot(self, u: FlatUnit) -> int:
-        m = re.search(r"(\d+)", u.name)
-        return (int(m.group(1)) % 2) if m else 0
+        return getattr(u, "slot_index", 0)
 
     # ------------------------------------------------------------------ collectives (NCCL / gloo arm)
     def _on_comm(self):
@@ -232,7 +250,7 @@ class FSDPRuntime:
             return
         if not u.gathered:
             if not getattr(u, "persistent", False):
-                key = (u.padded, u.is_expert, self._unit_slot(u))
+                key = (u.padded, u.is_expert, self._unit_slot(u), getattr(u, "lane", 0))
                 prev = self._slot_owner.get(key)
                 if prev is not None and prev is not u:
                     prev.gathered = False
@@ -304,7 +322,7 @@ class FSDPRuntime:
                 p.main_grad_initialized = False      # the flat buffer is reused by the next unit of this slot
 
     def _gslot_key(self, u: FlatUnit):
-        return (u.padded, u.is_expert, self._unit_slot(u), getattr(u, "persistent", False) and u.name)
+        return (u.padded, u.is_expert, self._unit_slot(u), getattr(u, "lane", 0), getattr(u, "persistent", False) and u.name)
 
     def before_block_backward(self, i: int) -> None:
         """The gradient slot about to be written may still be read by an earlier reduce-scatter."""
@@ -340,8 +358,12 @@ class FSDPRuntime:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         if self.replicate_group is not None and self.is_last_microbatch:
             for u in self.units:
-                if u.has_grad:
+                if u.has_grad and not getattr(u, "is_replicated", False):
                     dist.all_reduce(u.grad_shard, group=self.replicate_group)
+        if self.is_last_microbatch:
+            for u in self.units:
+                if getattr(u, "replicated_group", None) is not None and u.has_grad:
+                    dist.all_reduce(u.grad_shard, group=u.replicated_group)
 
     def post_optimizer(self) -> None:
         """After the optimizer rewrote the shards: zero gradient state, refresh persistent full copies."""
@@ -374,9 +396,10 @@ class FSDPRuntime:
 
     def run_block(self, i: int, layer: nn.Module, x: torch.Tensor, ctx) -> torch.Tensor:
         grad_mode = self.model.training and torch.is_grad_enabled()
-        ac = grad_mode and (self.ac_mode == "full" or (self.ac_mode == "selective" and self._recomputes(i)))
+        per_op = self.ac_mode == "selective" and getattr(self.model, "ac_per_op", False)
+        ac = grad_mode and (self.ac_mode == "full" or per_op or (self.ac_mode == "selective" and self._recomputes(i)))
         if ac:
-            return _CheckpointedBlock.apply(x, self, i, layer, ctx)
+            return _CheckpointedBlock.apply(x, self, i, layer, ctx, per_op)
         for u in self._units(i):
             self.unshard(u)
         self._prefetch(i + 1)
@@ -390,7 +413,6 @@ class FSDPRuntime:
                 self.reshard(u)
         return out
 
-    named_units: dict = {}
 
 
 class _PreBackward(torch.autograd.Function):
@@ -434,12 +456,15 @@ class _CheckpointedBlock(torch.autograd.Function):
     reduce-scatter."""
 
     @staticmethod
-    def forward(ctx, x, rt: FSDPRuntime, i: int, layer, fctx):
+    def forward(ctx, x, rt: FSDPRuntime, i: int, layer, fctx, per_op: bool = False):
+        from ..ops.functional import SelectiveReplay, sac_frame
         ctx.rt, ctx.i, ctx.layer, ctx.fctx = rt, i, layer, fctx
+        # per-op policy: attention and every other linear keep their outputs, the replay only rebuilds their graph nodes
+        ctx.frame = SelectiveReplay(getattr(rt.model, "ac_recompute_mm_shapes", ())) if per_op else None
         for u in rt._units(i):
             rt.unshard(u)
         rt._prefetch(i + 1)
-        with torch.no_grad():
+        with torch.no_grad(), sac_frame(ctx.frame, "record"):
             out = layer(x, fctx)
         for u in rt._units(i):
             rt.reshard(u)
@@ -455,8 +480,11 @@ class _CheckpointedBlock(torch.autograd.Function):
         rt._prefetch(i - 1)
         rt.before_block_backward(i)
         xd = x.detach().requires_grad_(True)
-        with torch.enable_grad():
+        from ..ops.functional import sac_frame
+        with torch.enable_grad(), sac_frame(ctx.frame, "replay"):
             out = ctx.layer(xd, ctx.fctx)
+        if ctx.frame is not None:
+            ctx.frame.store.clear()
         # Auxiliary (load-balance) losses of MoE blocks: the value that entered the step's loss came from the first,
         # graph-free forward, so their gradient is injected here, from the replayed forward. They are token sums, and
         # d loss / d aux is the step's 1 / global_valid_tokens (`aux_grad_scale`, set by the engine per micro-batch).
@@ -471,7 +499,7 @@ class _CheckpointedBlock(torch.autograd.Function):
         for u in rt._units(i):
             rt.reduce_grads(u)
             rt.reshard(u)
-        return xd.grad, None, None, None, None
+        return xd.grad, None, None, None, None, None
 
 
 def _materialize_meta_params(model: nn.Module, device, dtype) -> set[int]:
@@ -494,7 +522,7 @@ def _materialize_meta_params(model: nn.Module, device, dtype) -> set[int]:
 
 # ---------------------------------------------------------------------------------------------- stage entry
 def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_mode="none", ac_save_every=2,
-               init_fn=None) -> FSDPRuntime:
+               init_fn=None, grad_accum_steps: int = 1) -> FSDPRuntime:
     """Build the units in forward order (embedding, blocks, [experts], norm + head), bind buffers, install the
     block runner. Works for any shard degree, including 1 (then gather/reduce are no-ops and the same flat
     buffers serve the fused optimizer)."""
@@ -506,6 +534,7 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
     bound = BoundDecoder(structure, model)
     rt = FSDPRuntime(model, topo, fsdp_config, device=device, param_dtype=param_dtype, ac_mode=ac_mode,
                      ac_save_every=ac_save_every)
+    rt.grad_accum_steps = max(1, int(grad_accum_steps))
     ignored = [re.compile(p) for p in fsdp_config.fsdp_ignored_modules]
     skip = lambda fqn: any(r.search(fqn) for r in ignored)  # noqa: E731
     prefix_of = {id(m): n for n, m in model.named_modules()}
@@ -514,6 +543,40 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
         base = prefix_of[id(mod)]
         return [(f"{base}.{n}" if base else n, p) for n, p in mod.named_parameters() if not skip(f"{base}.{n}")]
 
+    # User-selected units (`fsdp_apply_modules`): every selected module becomes a unit of its own, made of the parameters
+    # whose innermost selected ancestor it is. A unit gathers and reduces with the block it lives in, so a selection has
+    # to sit inside a decoder block or beside the blocks (embedding, norm, head), not around several blocks.
+    own_unit_of: dict[int, str] = {}
+    if fsdp_config.fsdp_apply_modules:
+        from ..errors import UnsupportedCombinationError
+        from .module_patterns import resolve_module_patterns
+        names = [n for n, _ in model.named_modules() if n]
+        try:
+            chosen = resolve_module_patterns(names, fsdp_config.fsdp_apply_modules, "fsdp_apply_modules")
+        except ValueError as e:
+            raise ConfigError(str(e)) from None
+        block_names = {prefix_of[id(b)] for _, b in bound.block_items()}
+        for c in chosen:
+            if any(b != c and b.startswith(c + ".") for b in block_names):
+                raise UnsupportedCombinationError(f"fsdp_apply_modules selects {c!r}, which contains whole decoder blocks: a "
+                                                  "sharding unit is gathered with one block and cannot span several")
+        for mod_name in sorted(chosen, key=len):            # innermost selection wins: longer names overwrite shorter ones
+            mod = model.get_submodule(mod_name)
+            for _, p in mod.named_parameters():
+                own_unit_of[id(p)] = mod_name
+
+    def split_selected(pairs):
+        """(parameters left to the default unit, [(selected module name, its parameters)] in first-appearance order)"""
+        rest, groups = [], {}
+        for n, p in pairs:
+            key = own_unit_of.get(id(p))
+            if key is None or key in block_names_default:
+                rest.append((n, p))
+            else:
+                groups.setdefault(key, []).append((n, p))
+        return rest, list(groups.items())
+
+    block_names_default = {prefix_of[id(b)] for _, b in bound.block_items()}      # selecting a block itself is the default
     tied = bound.tied_embeddings()
     named_units = {}
     if tied:
@@ -526,11 +589,16 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
         units = []
         exp = [(n, p) for n, p in named(block) if getattr(p, "is_expert", False)]
         dense = [(n, p) for n, p in named(block) if not getattr(p, "is_expert", False)]
-        u = rt.add_unit(f"block{i}", dense)
+        dense, selected = split_selected(dense)
+        u = rt.add_unit(f"block{i}", dense, block_index=i)
         if u is not None:
             units.append(u)
+        for mod_name, pairs in selected:
+            us = rt.add_unit(f"block{i}.{mod_name}", pairs, block_index=i)
+            if us is not None:
+                units.append(us)
         if exp:
-            ue = rt.add_unit(f"block{i}.experts", exp, expert=True)
+            ue = rt.add_unit(f"block{i}.experts", exp, expert=True, block_index=i)
             if ue is not None:
                 units.append(ue)
         rt.block_units[i] = units
@@ -539,6 +607,15 @@ def apply_fsdp(model: nn.Module, topo, fsdp_config, *, device, param_dtype, ac_m
     rest = [(n, p) for n, p in model.named_parameters() if id(p) not in rt.unit_of_param and not skip(n)]
     if rest:
         named_units["rest"] = rt.add_unit("rest", rest)
+    # Parameters excluded from sharding stay whole on every rank: one replicated unit, gradient summed over the data ranks,
+    # stepped by the optimizer like any other unit.
+    kept = [(n, p) for n, p in model.named_parameters() if id(p) not in rt.unit_of_param and skip(n)]
+    if kept:
+        if any(getattr(p, "is_expert", False) for _, p in kept):
+            from ..errors import UnsupportedCombinationError
+            raise UnsupportedCombinationError("fsdp_ignored_modules may not name expert parameters: their gradient lives on "
+                                              "the expert-parallel mesh, not on the data ranks")
+        named_units["ignored"] = rt.add_unit("ignored", kept, replicated=True)
     rt.named_units = {k: v for k, v in named_units.items() if v is not None}
     rt.finalize(init_fn=init_fn, needs_init=needs_init)
     from .symm import enable_fused_fsdp

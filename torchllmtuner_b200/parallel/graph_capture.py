@@ -14,16 +14,22 @@ from ..errors import LLMTunerError
 
 
 class SDCGuard(torch.nn.Module):
-    """Silent-data-corruption guard: raises when a block returns non-finite values."""
+    """Silent-data-corruption guard: records, on the device, the first block whose output is not finite. Nothing is read
+    back inside the forward pass (no host synchronisation per block); `check_sdc(model)` reads the one flag word, once
+    per step, and raises."""
 
-    def __init__(self, inner):
+    def __init__(self, inner, index: int, flag: torch.Tensor):
         super().__init__()
-        self.inner = inner
+        self.inner, self.index, self.flag = inner, index, flag
 
     def forward(self, *a, **k):
         out = self.inner(*a, **k)
-        if not torch.isfinite(out.float().sum()):
-            raise LLMTunerError(f"non-finite output of {type(self.inner).__name__}")
+        with torch.no_grad():
+            bad = ~torch.isfinite(out.detach().float().sum())
+            if self.flag.device != out.device:
+                self.flag.data = self.flag.data.to(out.device)
+            # flag holds 0 (healthy) or 1 + index of the first bad block
+            self.flag.copy_(torch.where((self.flag == 0) & bad, torch.full_like(self.flag, self.index + 1), self.flag))
         return out
 
     def __getattr__(self, name):
@@ -31,6 +37,17 @@ class SDCGuard(torch.nn.Module):
             return super().__getattr__(name)
         except AttributeError:
             return getattr(super().__getattr__("inner"), name)
+
+
+def check_sdc(model) -> None:
+    """One device-to-host read of the guard's flag word; raises `LLMTunerError` naming the first non-finite block."""
+    flag = getattr(model, "_sdc_flag", None)
+    if flag is None:
+        return
+    v = int(flag.item())
+    if v:
+        flag.zero_()
+        raise LLMTunerError(f"non-finite output of decoder block {v - 1} (silent-data-corruption guard)")
 
 
 class GraphedInference(torch.nn.Module):
@@ -67,10 +84,12 @@ class GraphedInference(torch.nn.Module):
 
 def apply_compile(model, compile_config) -> None:
     layers = model.model.layers
+    if compile_config.enable_sdc:
+        model._sdc_flag = torch.zeros((), dtype=torch.int32)
     for i in range(len(layers)):
         blk = layers[i]
         if compile_config.enable_sdc:
-            blk = SDCGuard(blk)
+            blk = SDCGuard(blk, i, model._sdc_flag)
         if compile_config.per_block and compile_config.backend == "cudagraph":
             blk = GraphedInference(blk)
         layers[i] = blk

@@ -53,7 +53,8 @@ def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None)
                 from .fsdp import apply_fsdp
                 asm.fsdp = apply_fsdp(model, topo, config.parallel.fsdp_config, device=device, param_dtype=param_dtype,
                                       ac_mode=getattr(model, "activation_checkpoint", "none"),
-                                      ac_save_every=getattr(model, "ac_save_every", 2), init_fn=init_fn)
+                                      ac_save_every=getattr(model, "ac_save_every", 2), init_fn=init_fn,
+                                      grad_accum_steps=t.gradient_accumulation_steps)
             else:
                 continue
         asm.stages_applied.append(stage)

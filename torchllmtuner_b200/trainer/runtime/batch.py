@@ -43,8 +43,3 @@ def global_valid_tokens(batches, device, reductions) -> torch.Tensor:
     if reductions.dp_group is not None:
         dist.all_reduce(gv, group=reductions.dp_group)
     return gv.reshape(())
-
-
-def move_batch_to_device(batch: dict, device, non_blocking: bool = True) -> dict:
-    """Tensors go to the device (pinned host tensors asynchronously); `cu_seqlens` and plain Python values stay."""
-    return {k: (v.to(device, non_blocking=non_blocking) if isinstance(v, torch.Tensor) and k != "cu_seqlens" else v) for k, v in batch.items()}

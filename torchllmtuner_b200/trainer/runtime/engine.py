@@ -94,4 +94,6 @@ class TrainingEngine:
         return norm
 
     def finish_step(self, step: int, loss_value: float | None = None) -> None:
+        from ...parallel.graph_capture import check_sdc
+        check_sdc(self.model)
         check_step_condition(self.clipper, loss_value)

@@ -1,16 +1,10 @@
-"""Gradient services between backward and the optimizer (reference: llmtuner/trainer/runtime/gradients.py:70-372):
-summing the gradients of parameters that tensor-parallel ranks hold in full, the clip coefficient, and the finite
-verdict that raises on every rank before any parameter changes."""
+"""Gradient services between backward and the optimizer (reference: llmtuner/trainer/runtime/gradients.py:70-372).
+The sums themselves live with the sharding runtime, which owns the flat gradient buffers: tensor-parallel-replicated
+parameters in `parallel/fsdp.py::reduce_grads`, parameters excluded from sharding in `wait_reductions`, the clip coefficient
+in `components/optimizer/container.py::GradientClipper`. What is left here is the finite verdict that raises on every rank."""
 from __future__ import annotations
 
 from ...components.optimizer import check_finite
-from ...parallel.tensor_parallel import allreduce_replicated_tp_grads
-
-
-def reduce_replicated_gradients(params, topo) -> None:
-    """Norm weights, q/k norms, routers and a replicated head see only their rank's tokens under TP + SP."""
-    if topo.tp > 1:
-        allreduce_replicated_tp_grads(params, topo.get_group("tp"))
 
 
 def check_step_condition(clipper, loss_value: float | None = None) -> None:

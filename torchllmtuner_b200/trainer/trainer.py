@@ -36,7 +36,8 @@ class Trainer:
         t = cfg.training
         set_log_ranks(t.metrics_config.log_ranks)
         self.logger = get_logger("trainer")
-        from ..config.inert_fields import inert_fields_set
+        from ..config.inert_fields import check_unsupported_fields, inert_fields_set
+        check_unsupported_fields(cfg)
         for name, why in inert_fields_set(cfg):
             self.logger.warning(f"--{name} is accepted for command-line compatibility and has no effect here: {why}")
         self.env = env = build_runtime_environment(cfg)
