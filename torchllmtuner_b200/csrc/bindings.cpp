@@ -510,7 +510,9 @@ void clip_coef(const Tensor& total_sq, double max_norm, Tensor& coef, Tensor& no
            "llmt_clip_coef");
 }
 
-std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tiles, double scale, bool causal) {
+// pair: two query heads of a key/value group per CTA (attention_fwd_pair.cu); needs an even group size.
+std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tiles, double scale, bool causal,
+                             bool pair) {
   c10::cuda::CUDAGuard guard(q.device());
   check_bf16(q, "q"); check_bf16(k, "k"); check_bf16(v, "v");
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3);
@@ -520,6 +522,13 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   const int Tq = (int)q.size(0), Hq = (int)q.size(1), HD = (int)q.size(2), Tk = (int)k.size(0), Hkv = (int)k.size(1);
   Tensor o = torch::empty({Tq, Hq, HD}, q.options());
   Tensor lse = torch::empty({Hq, Tq}, q.options().dtype(torch::kFloat));
+  if (pair && Hkv > 0 && Hq % Hkv == 0 && ((Hq / Hkv) % 2) == 0) {
+    check_rc(llmt_attn_fwd_pair(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), tiles.data_ptr<int>(),
+                                (int)tiles.size(0), Tq, Tk, Hq, Hkv, HD, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
+                                (float)scale, causal, status_ptr(), cur_stream()),
+             "llmt_attn_fwd_pair");
+    return {o, lse};
+  }
   check_rc(llmt_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), tiles.data_ptr<int>(),
                          (int)tiles.size(0), Tq, Tk, Hq, Hkv, HD, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
                          (float)scale, causal, status_ptr(), cur_stream()),
@@ -682,7 +691,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sqnorm", &sqnorm);
   m.def("sqnorm_scratch_floats", &sqnorm_scratch_floats);
   m.def("clip_coef", &clip_coef);
-  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("tiles"), py::arg("scale"), py::arg("causal"),
+        py::arg("pair") = false);
   m.def("attn_bwd", &attn_bwd);
   m.def("read_status", &read_status, py::arg("clear") = true);
   m.def("status_tensor", &status_tensor);

@@ -20,7 +20,7 @@ PKG = os.path.dirname(HERE)
 BUILD = os.path.join(HERE, "build")
 SO_PATH = os.path.join(PKG, "_C.so")
 STAMP = os.path.join(PKG, "_C.stamp")
-CU_SOURCES = ("gemm.cu", "elementwise.cu", "attention.cu", "attention_bwd.cu", "moe.cu", "comm.cu", "ep_comm.cu", "vocab_parallel.cu", "noalloc.cu")
+CU_SOURCES = ("gemm.cu", "elementwise.cu", "attention.cu", "attention_fwd_pair.cu", "attention_bwd.cu", "moe.cu", "comm.cu", "ep_comm.cu", "vocab_parallel.cu", "noalloc.cu")
 HEADERS = ("common.cuh", "comm.cuh", "attn_common.cuh", "kernels.h", "noalloc.h")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--use_fast_math", "-Xptxas", "-v"]

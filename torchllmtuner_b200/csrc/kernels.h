@@ -94,6 +94,10 @@ int llmt_vp_embed_scatter(const int64_t* ids, const void* w, int64_t vstart, int
 int llmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* tiles, int num_tiles,
                   int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
                   int64_t o_stride, float scale, int causal, int* status, cudaStream_t st);
+// Same contract; one CTA per (q tile, pair of query heads of one key/value group). Needs an even group size.
+int llmt_attn_fwd_pair(const void* q, const void* k, const void* v, void* o, float* lse, const int* tiles, int num_tiles,
+                       int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                       int64_t o_stride, float scale, int causal, int* status, cudaStream_t st);
 int llmt_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                   float* delta, void* dq, void* dk, void* dv, const int* q_tiles, int num_q_tiles, const int* k_tiles,
                   int num_k_tiles, int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride,

@@ -282,7 +282,7 @@ def swiglu(gate, up, row_limit=None):
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, meta: AttnMeta, scale, kept=None):
-        o, lse = kept if kept is not None else _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
+        o, lse = kept if kept is not None else _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal, attention_forward_mode() == "pair")
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.meta, ctx.scale = meta, scale
         ctx.mark_non_differentiable(lse)
@@ -297,6 +297,12 @@ class _Attention(torch.autograd.Function):
         dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, m.q_tiles, m.k_tile_passes, ctx.scale, m.causal, not m.covers_all_keys,
                                      attention_backward_mode() == "fused")
         return dq, dk, dv, None, None, None
+
+
+def attention_forward_mode() -> str:
+    """"single" (default): one head per CTA. "pair" (`LLMT_ATTN_FWD=pair`): one CTA serves two query heads of a key/value
+    group, K/V tiles are loaded once for both and P stays in tensor memory; needs an even group size."""
+    return "pair" if os.environ.get("LLMT_ATTN_FWD") == "pair" else "single"
 
 
 _ATTN_BWD_MODE: str | None = None
@@ -345,7 +351,7 @@ def attention_with_lse(q, k, v, meta: AttnMeta, scale: float | None = None):
     """Forward only, returns (out, lse [Hq, Tq]); used by context-parallel merges."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _use_cuda(q) and q.dtype == torch.bfloat16:
-        o, lse = _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal)
+        o, lse = _ext().attn_fwd(q, k, v, meta.q_tiles, scale, meta.causal, attention_forward_mode() == "pair")
         return o, lse
     return ref.attention_pieces(q, k, v, meta.pieces, meta.causal, scale)
 

@@ -232,6 +232,29 @@ class ContextParallelDriver:
         return torch.cat(result)
 
 
+def build_cp_plan(model, topo, cp_config):
+    """Which attention modules will run under context parallelism, and along which axes. Ulysses exchanges heads, so its
+    degree has to divide the key/value heads left after tensor parallelism; checked here, before any stage runs."""
+    from ..models.contracts import BoundDecoder
+    from .plan import ParallelPlan, PlanTarget
+    from ..errors import UnsupportedCombinationError
+    bound = BoundDecoder(model.decoder_structure, model)
+    st = model.decoder_structure
+    targets = []
+    for key, block in bound.block_items():
+        attn = bound.attention_of(block)
+        if topo.cp_ulysses > 1:
+            for name in ("num_heads", "num_kv_heads"):
+                h = getattr(attn, name, None)
+                if h is not None and (h // max(1, topo.tp)) % topo.cp_ulysses:
+                    raise UnsupportedCombinationError(f"context_parallel_ulysses_size {topo.cp_ulysses} does not divide "
+                                                      f"{type(attn).__name__}.{name} = {h} (after tensor parallelism {topo.tp})")
+        targets.append(PlanTarget(f"{st.blocks}.{key}.{st.attention}", "attention", "context", attn))
+    axes = "+".join(n for n, d in (("kv_allgather", topo.cp_kv), ("ulysses", topo.cp_ulysses), ("kcp", getattr(topo, "kcp", 1))) if d > 1)
+    return ParallelPlan("cp", topo.cp, axes or "none", tuple(targets), binds=("modules",),
+                        notes=(f"load balancer: {cp_config.context_parallel_load_balancer}",))
+
+
 def apply_cp(model, topo, cp_config) -> ContextParallelDriver:
     """`kcp` is the sequence axis of delta-attention models: softmax / latent attention layers gather keys and values
     over it, delta-rule layers hand their recurrent state from rank to rank (`ContextParallelDriver.delta_rule`)."""

@@ -139,6 +139,24 @@ def convert_block(moe: MoE, topo, ep_config) -> None:
         moe.routed.forward = lambda x, w, i, _d=d, _e=ex: _d.run(_e, x, w, i)
 
 
+def build_ep_plan(model, topo, ep_config):
+    """Resolve every MoE block against the untouched model: the degree must divide the experts of each block, the
+    dispatcher must exist. Binds the block objects only: tensor parallelism, which runs first, re-creates the expert
+    parameters (intermediate dimension cut) of the very blocks this plan names."""
+    from .plan import ParallelPlan, PlanTarget
+    targets = []
+    for n, m in model.named_modules():
+        if isinstance(m, MoE):
+            E = m.routed.experts.num_experts
+            if E % topo.ep:
+                raise ConfigError(f"{n}: expert_parallel_size {topo.ep} must divide {E} experts")
+            targets.append(PlanTarget(n, "moe", "ep", m))
+    if not targets:
+        raise ConfigError("expert_parallel_size > 1 but the model has no MoE block")
+    return ParallelPlan("ep", topo.ep, ep_config.ep_token_dispatcher, tuple(targets), binds=("modules",),
+                        notes=(f"{targets[0].module.routed.experts.num_experts // topo.ep} experts per rank",))
+
+
 def apply_ep(model, topo, ep_config) -> dict:
     """Plan every block first (so a bad block raises before any mutation), then install."""
     blocks = [(n, m) for n, m in model.named_modules() if isinstance(m, MoE)]

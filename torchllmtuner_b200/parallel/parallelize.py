@@ -20,6 +20,8 @@ class ParallelAssembly:
     ep_plan: dict = field(default_factory=dict)
     cp_driver: object = None
     stages_applied: list[str] = field(default_factory=list)
+    plans: dict = field(default_factory=dict)          # stage -> ParallelPlan, resolved before any mutation
+    execution: object = None                            # ExecutionLayout
 
 
 def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None) -> ParallelAssembly:
@@ -29,8 +31,24 @@ def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None)
         model.validate_parallel(tp=topo.tp, cp_ulysses=topo.cp_ulysses, ep=topo.ep)
     asm = ParallelAssembly(model, topo)
     t = config.training
+    # Resolve first, execute second: every stage's plan is computed against the untouched model (metadata only), so a
+    # configuration error of a late stage surfaces before an early stage has rewritten anything.
+    with synchronize_local_errors("parallelize:resolve"):
+        if topo.tp > 1:
+            from .tensor_parallel import build_tp_plan
+            asm.plans["tp"] = build_tp_plan(model, topo, config.parallel.tp_config)
+        if getattr(arch, "num_experts", 0) > 0 and topo.ep > 1:
+            from .expert_parallel import build_ep_plan
+            asm.plans["ep"] = build_ep_plan(model, topo, config.parallel.ep_config)
+        if topo.cp > 1:
+            from .context_parallel import build_cp_plan
+            asm.plans["cp"] = build_cp_plan(model, topo, config.parallel.cp_config)
+        from .execution import resolve_execution_layout
+        asm.execution = resolve_execution_layout(config, topo, model, asm.plans)
     for stage in STAGE_ORDER:
         with synchronize_local_errors(f"parallelize:{stage}"):
+            if stage in asm.plans:
+                asm.plans[stage].validate_binding(model)      # the model may not have changed under the plan's targets
             if stage == "tp" and topo.tp > 1:
                 from .tensor_parallel import apply_tp
                 asm.tp_plan = apply_tp(model, topo, config.parallel.tp_config)

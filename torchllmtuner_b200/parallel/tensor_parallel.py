@@ -270,6 +270,53 @@ def _shard_experts(experts, rank: int, size: int) -> None:
     experts.inter = s
 
 
+def build_tp_plan(model, topo, tp_config):
+    """Resolve, without touching the model, what `apply_tp` will do: every projection with its cut, every MoE block, the
+    embedding and the head. Configuration errors (a head count the degree does not divide, tied embeddings, a fused QKV
+    projection, sequence parallelism switched off) surface here, before any stage has mutated anything."""
+    from ..models.contracts import BoundDecoder
+    from ..models.moe import MoE
+    from .plan import ParallelPlan, PlanTarget
+    size = topo.tp
+    if not tp_config.enable_sequence_parallel:
+        raise ConfigError("tensor parallelism is sequence-parallel here: enable_sequence_parallel must stay True")
+    bound = BoundDecoder(model.decoder_structure, model)
+    st = model.decoder_structure
+    targets = []
+    for key, block in bound.block_items():
+        base = f"{st.blocks}.{key}"
+        attn = bound.attention_of(block)
+        if getattr(attn, "fused_qkv", False):
+            raise UnsupportedCombinationError("fused QKV projection cannot be column-sharded per projection")
+        cut = getattr(attn, "tp_cut", None) or {"colwise": ("q_proj", "k_proj", "v_proj"), "rowwise": ("o_proj",),
+                                                 "heads": ("num_heads", "num_kv_heads")}
+        for name in cut["heads"]:
+            if getattr(attn, name) % size:
+                raise UnsupportedCombinationError(f"tensor_parallel_size {size} does not divide {type(attn).__name__}.{name} = {getattr(attn, name)}")
+        targets.append(PlanTarget(f"{base}.{st.attention}", "attention", "sequence-gather", attn))
+        for name in cut["colwise"]:
+            if getattr(attn, name, None) is not None:
+                targets.append(PlanTarget(f"{base}.{st.attention}.{name}", "dense", "colwise", getattr(attn, name)))
+        for name in cut["rowwise"]:
+            targets.append(PlanTarget(f"{base}.{st.attention}.{name}", "dense", "rowwise", getattr(attn, name)))
+        mlp = bound.mlp_of(block)
+        if isinstance(mlp, MoE):
+            F_ = mlp.routed.experts.w1_EFD.shape[1]
+            if F_ % size:
+                raise UnsupportedCombinationError(f"tensor_parallel_size {size} does not divide moe_intermediate_size {F_}")
+            targets.append(PlanTarget(f"{base}.{st.mlp}", "moe", "expert-intermediate", mlp))
+        else:
+            for name, lay in (("gate_proj", "colwise"), ("up_proj", "colwise"), ("down_proj", "rowwise")):
+                targets.append(PlanTarget(f"{base}.{st.mlp}.{name}", "dense", lay, getattr(mlp, name)))
+    if bound.tied_embeddings():
+        raise UnsupportedCombinationError("tied embeddings with tensor parallelism are not supported (embedding and head are cut separately)")
+    targets.append(PlanTarget(st.embedding, "vocab", "vocab", bound.embedding))
+    head_layout = "vocab" if getattr(tp_config, "tp_vocab_parallel_head", True) else "replicated"
+    targets.append(PlanTarget(st.head, "head", head_layout, bound.head))
+    impl = "peer-memory" if os.environ.get("LLMT_DISABLE_FUSED_TP") != "1" else "torch.distributed"
+    return ParallelPlan("tp", size, impl, tuple(targets), binds=("modules", "parameters", "forwards"))
+
+
 def apply_tp(model, topo, tp_config) -> dict:
     """Swap the planned linears for their sharded forms, install the sequence boundaries and the vocab-parallel
     embedding, and mark every parameter that stays replicated so that its gradient is summed over the TP group."""

@@ -49,18 +49,22 @@ def prepare_parallel_model(config, env):
 
 
 def build_loss_functions(config, env, asm) -> LossFunctions:
-    """Under tensor parallelism the head is vocabulary-sharded (unless `tp_vocab_parallel_head` is off): the loss service
-    then owns the sharded head module and exchanges per-token statistics over the TP group."""
+    """The loss service follows the resolved execution layout: hidden-state path with the layout's chunk count, and, when
+    the head is vocabulary-sharded over the tensor-parallel group, the sharded head module whose loss kernel exchanges
+    per-token statistics over that group."""
     from ...parallel.vocab_parallel import VocabParallelHead
+    layout = asm.execution
     head = None
-    model = asm.model
-    if env.topo.tp > 1:
-        cand = model
-        for part in model.decoder_structure.head.split("."):
+    if layout is not None and layout.vocabulary_sharded:
+        cand = asm.model
+        for part in asm.model.decoder_structure.head.split("."):
             cand = getattr(cand, part)
-        if isinstance(cand, VocabParallelHead):
-            head = cand
-    return LossFunctions(num_chunks=config.training.chunked_loss_num_chunks, head=head)
+        if not isinstance(cand, VocabParallelHead):
+            raise RuntimeError("execution layout says the head is vocabulary-sharded but the tensor-parallel stage left "
+                               f"{type(cand).__name__} in place")
+        head = cand
+    chunks = layout.loss_chunks if layout is not None and layout.output_kind == "hidden" else config.training.chunked_loss_num_chunks
+    return LossFunctions(num_chunks=chunks, head=head)
 
 
 def build_optimizer_stack(config, env, asm):

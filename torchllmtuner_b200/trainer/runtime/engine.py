@@ -7,6 +7,7 @@ import torch.distributed as dist
 
 from ...components.loss import LossFunctions
 from .gradients import check_step_condition
+from ...models.execution import capabilities_of, validate_prepared_model_inputs, validate_training_output
 from ...models.moe import collect_aux_loss, moe_blocks
 
 
@@ -16,6 +17,8 @@ class TrainingEngine:
         self.optimizers, self.lr_schedulers, self.ema, self.clipper = optimizers, lr_schedulers, ema, clipper
         self.topo, self.device = topo, device
         self.rt = assembly.fsdp
+        self.caps = capabilities_of(model)
+        self.caps.require("hidden" if loss_fns.chunked else "logits")
         self.step_loss = torch.zeros((), dtype=torch.float32, device=device)
 
     # ------------------------------------------------------------------ step phases
@@ -36,16 +39,18 @@ class TrainingEngine:
         m = self.model
         self.rt.is_last_microbatch = is_last_microbatch
         self.rt.aux_grad_scale = 1.0 / global_valid_tokens
-        inputs = m.prepare_inputs(batch, self.device, self.parallel_dims())
+        inputs = validate_prepared_model_inputs(m.prepare_inputs(batch, self.device, self.parallel_dims()))
         ctx = m.build_context(inputs["positions"], inputs["attn_meta"], self.asm.cp_driver)
         if self.asm.cp_driver is not None:
             self.asm.cp_driver.begin_microbatch(inputs)
         self.rt.before_forward()
         if self.loss_fns.chunked:
             h = m(inputs["tokens"], ctx, skip_lm_head=True)
+            validate_training_output(h, inputs["targets"], output_width=self.caps.width("hidden"))
             loss_sum = self.loss_fns.from_hidden(h, m.lm_head.weight, inputs["targets"])
         else:
             logits = m(inputs["tokens"], ctx)
+            validate_training_output(logits, inputs["targets"], output_width=self.caps.width("logits"))
             loss_sum = self.loss_fns.from_logits(logits, inputs["targets"])
         # Load-balance losses are token sums like the CE sum (`MoE.balance_loss_sum`): one division by the global valid-token
         # count normalises both. Blocks that replay their forward inside backward read the same factor from the runtime.
