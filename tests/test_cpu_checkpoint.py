@@ -90,8 +90,8 @@ def test_resume_at_other_dp_and_ep_degree(tmp_path):
 
 
 def test_checkpoint_key_names(tmp_path):
-    """Keys follow the reference's flattened names: `model.<fqn>`, `optimizer.state.<fqn>.<moment>`, `ema.ema_params.<fqn>`,
-    plus lr scheduler, train state, data loader and RNG entries."""
+    """Keys follow the reference's flattened names: bare `<fqn>` for model tensors (whole N-D tensors),
+    `optimizer.state.<fqn>.<moment>`, `ema.ema_params.<fqn>`, plus lr scheduler, train state, data loader and RNG entries."""
     import torch.distributed.checkpoint as dcp
     folder = str(tmp_path / "run")
     cfg = _cfg(folder)
@@ -100,10 +100,16 @@ def test_checkpoint_key_names(tmp_path):
     tr.checkpointer.save(1, force=True)
     tr.checkpointer.wait()
     tr.close()
-    keys = set(dcp.FileSystemReader(os.path.join(folder, "checkpoint", "step-1")).read_metadata().state_dict_metadata.keys())
-    assert any(k.startswith("model.model.layers.0.self_attn.q_proj.weight@") for k in keys), sorted(keys)[:20]
-    assert any(k.startswith("optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg@") for k in keys)
-    assert any(k.startswith("optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg_sq@") for k in keys)
+    md = dcp.FileSystemReader(os.path.join(folder, "checkpoint", "step-1")).read_metadata().state_dict_metadata
+    keys = set(md.keys())
+    assert "model.layers.0.self_attn.q_proj.weight" in keys, sorted(keys)[:20]
+    assert "optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg" in keys
+    assert "optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg_sq" in keys
+    assert len(md["model.layers.0.self_attn.q_proj.weight"].size) == 2          # a whole matrix, not a flat piece
+    # any DCP reader gets the whole tensor without this framework's code
+    want = {"model.layers.0.self_attn.q_proj.weight": torch.zeros(tuple(md["model.layers.0.self_attn.q_proj.weight"].size))}
+    dcp.load(want, checkpoint_id=os.path.join(folder, "checkpoint", "step-1"), no_dist=True)
+    assert want["model.layers.0.self_attn.q_proj.weight"].abs().sum() > 0
     for k in ("obj.lr_scheduler", "obj.train_state", "obj.format", "obj.optimizer.param_groups", "obj.dataloader.dp0", "obj.rng.rank0"):
         assert k in keys, k
 
@@ -151,3 +157,117 @@ def test_async_checkpoint_is_published_in_a_later_step_and_adopted_after_a_crash
     assert os.path.isdir(final4) and not os.path.isdir(tmp)
     tr2.close()
     tr.close()
+
+
+def test_reference_key_layout_round_trip(tmp_path):
+    """A checkpoint of this framework is exported to the reference's key layout (whole tensors under the names of the
+    reference's modules, packed experts as gate_up_proj / down_proj, optimizer flattened per parameter name), read back
+    into a native folder, and a fresh trainer that resumes from that folder continues bit for bit."""
+    import torch.distributed.checkpoint as dcp
+    from torchllmtuner_b200.components.checkpointer.reference_layout import (export_reference_layout, import_reference_layout,
+                                                                             native_shapes)
+    folder = str(tmp_path / "run")
+
+    def cfg_of(f):
+        cfg = _cfg(f, model_name_or_path="qwen3_moe", exclude_from_loading=["dataloader", "rng"])
+        cfg.model.arch_overrides = dict(MOE)
+        return cfg
+    tr = Trainer(cfg_of(folder))
+    for _ in range(2):
+        tr.train_step()
+    tr.checkpointer.save(2, force=True)
+    tr.checkpointer.wait()
+    shapes = native_shapes(tr.model)
+    E, F, D = shapes["model.layers.0.mlp.routed.experts.w1_EFD"]
+    w1 = dict(tr.model.named_parameters())["model.layers.0.mlp.routed.experts.w1_EFD"]
+    masters = [u.master.clone() for u in tr.asm.fsdp.units]
+    moments = {n: {k: v.clone() for k, v in st.items() if torch.is_tensor(v)} for n, st in tr.optimizers.optimizers[0].state.items()}
+    batches = [tr.train_step().loss for _ in range(2)]
+    tr.close()
+
+    ref_dir = str(tmp_path / "reference_layout")
+    info = export_reference_layout(os.path.join(folder, "checkpoint", "step-2"), ref_dir)
+    keys = set(info["keys"])
+    for k in ("model.layers.0.self_attn.q_proj.weight", "model.layers.0.mlp.experts.gate_up_proj", "model.layers.0.mlp.experts.down_proj",
+              "model.layers.0.mlp.gate.weight", "optimizer.state.model.layers.0.self_attn.q_proj.weight.exp_avg",
+              "optimizer.state.model.layers.0.mlp.experts.gate_up_proj.exp_avg_sq", "optimizer.state.model.embed_tokens.weight.step",
+              "optimizer.param_groups.model.layers.0.self_attn.q_proj.weight.lr",
+              "optimizer.param_groups.model.norm.weight.weight_decay", "lr_scheduler.last_epoch", "train_state.step"):
+        assert k in keys, (k, sorted(keys)[:40])
+    md = dcp.FileSystemReader(ref_dir).read_metadata().state_dict_metadata
+    assert tuple(md["model.layers.0.mlp.experts.gate_up_proj"].size) == (E, 2 * F, D)
+    assert tuple(md["optimizer.state.model.layers.0.mlp.experts.down_proj.exp_avg"].size) == (E, D, F)
+    # gate rows then up rows of each expert
+    want = {"model.layers.0.mlp.experts.gate_up_proj": torch.empty(E, 2 * F, D)}
+    dcp.load(want, checkpoint_id=ref_dir, no_dist=True)
+    del w1
+
+    folder2 = str(tmp_path / "run2")
+    back = import_reference_layout(ref_dir, os.path.join(folder2, "checkpoint", "step-2"), shapes, state_format="qwen3")
+    assert back["step"] == 2
+    tr2 = Trainer(cfg_of(folder2))
+    assert tr2.checkpointer.load()
+    assert tr2.progress.step == 2
+    for a, u in zip(masters, tr2.asm.fsdp.units):
+        assert torch.equal(a[:u.numel], u.master[:u.numel])
+    for n, st in tr2.optimizers.optimizers[0].state.items():
+        for k, v in st.items():
+            if torch.is_tensor(v) and k in moments[n]:
+                assert torch.equal(v, moments[n][k]), (n, k)
+    tr2.close()
+
+
+def test_flat_range_boxes_tile_the_range_exactly():
+    """A flat range of a row-major tensor is at most 2N-1 boxes whose concatenation, in order, is the range."""
+    import random
+    from torchllmtuner_b200.components.checkpointer.boxes import boxes_of_slice, flat_range_boxes
+    rnd = random.Random(0)
+    for shape in [(7,), (5, 4), (3, 4, 5), (2, 3, 2, 4), (6, 1, 3)]:
+        n = 1
+        for s in shape:
+            n *= s
+        ref = torch.arange(n).view(shape)
+        for _ in range(100):
+            lo = rnd.randint(0, n)
+            hi = rnd.randint(lo, n)
+            bx = flat_range_boxes(lo, hi, shape)
+            assert len(bx) <= max(1, 2 * len(shape) - 1)
+            pos = lo
+            for off, size, start in bx:
+                v = ref[tuple(slice(o, o + s) for o, s in zip(off, size))].reshape(-1)
+                assert start == pos - lo and torch.equal(v, torch.arange(pos, pos + v.numel()))
+                pos += v.numel()
+            assert pos == hi
+    # a column cut places the boxes at the rank's columns; padding rows of a vocabulary cut are clipped
+    b = boxes_of_slice("w", 0, 6, (3, 2), (3, 8), (0, 4))
+    assert [(x.offsets, x.sizes) for x in b] == [((0, 4), (3, 2))]
+    b = boxes_of_slice("emb", 0, 12, (4, 3), (6, 3), (4, 0))          # rank 1 of a vocabulary of 6 padded to 8
+    assert [(x.offsets, x.sizes, x.numel) for x in b] == [((4, 0), (2, 3), 6)]
+
+
+def test_format_2_pieces_are_still_read(tmp_path):
+    """A folder in the previous format (flat pieces keyed `model.<fqn>@lo:hi`) resumes: the loader migrates on read."""
+    import torch.distributed.checkpoint as dcp
+    from torchllmtuner_b200.components.checkpointer.dcp_manager import _pack, iter_pieces
+    folder = str(tmp_path / "run")
+    tr = Trainer(_cfg(folder))
+    tr.train_step()
+    state = {}
+    for fqn, tag, glo, ghi, u, slo in iter_pieces(tr.asm.fsdp):
+        mid = glo + (ghi - glo) // 2                       # two pieces per tensor, as two ranks would have written
+        for a, b in ((glo, mid), (mid, ghi)):
+            if b > a:
+                state[f"model.{fqn}{tag}@{a}:{b}"] = u.master[slo + a - glo: slo + b - glo].clone()
+    state["obj.format"] = _pack({"version": 2})
+    state["obj.train_state"] = _pack(tr.progress.state_dict())
+    os.makedirs(os.path.join(folder, "checkpoint"), exist_ok=True)
+    dcp.save(state, checkpoint_id=os.path.join(folder, "checkpoint", "step-1"), no_dist=True)
+    masters = [u.master.clone() for u in tr.asm.fsdp.units]
+    tr.close()
+    tr2 = Trainer(_cfg(folder, exclude_from_loading=["optimizer", "lr_scheduler", "dataloader", "rng"]))
+    for u in tr2.asm.fsdp.units:
+        u.master.zero_()
+    assert tr2.checkpointer.load()
+    for a, u in zip(masters, tr2.asm.fsdp.units):
+        assert torch.equal(a[:u.numel], u.master[:u.numel])
+    tr2.close()

@@ -142,3 +142,98 @@ def test_model_execution_contracts():
         ModelExecutionCapabilities(True, False, 64)
     with pytest.raises(ValueError):
         ModelExecutionCapabilities(True, False).require("hidden")
+
+
+# ------------------------------------------------------------------------------------------ model part layout
+def _tied():
+    import torch.nn as nn
+
+    class Tied(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(8, 4)
+            self.body = nn.Sequential(nn.Linear(4, 4, bias=False))
+            self.head = nn.Linear(4, 8, bias=False)
+            self.head.weight = self.embed.weight
+    return Tied()
+
+
+def test_layout_names_aliases_and_owner():
+    from torchllmtuner_b200.parallel.assembly import ModelPartLayout
+    m = _tied()
+    lay = ModelPartLayout()
+    lay.refresh(m)
+    assert list(lay.bindings) == ["embed.weight", "body.0.weight", "head.weight"]
+    assert lay.aliases[m.embed.weight] == ("embed.weight", "head.weight")
+    assert lay.owner_names[m.embed.weight] == "embed.weight"          # first registration names the state
+    assert lay.validate(m)["head.weight"] == "head.weight"
+
+
+def test_layout_refresh_accepts_materialisation_and_rejects_split_alias():
+    import torch
+    import torch.nn as nn
+    from torchllmtuner_b200.parallel.assembly import LayoutError, ModelPartLayout
+    m = _tied()
+    lay = ModelPartLayout()
+    lay.refresh(m)
+    snap = lay.snapshot()
+    # a whole-model materialisation swaps every object and keeps the sharing
+    new = nn.Parameter(torch.zeros(8, 4))
+    old = m.embed.weight
+    m.embed.weight = new
+    m.head.weight = new
+    lay.refresh(m)
+    assert lay.replaced[id(old)] is new and lay.validate(m)
+    with pytest.raises(LayoutError, match="ownership changed"):
+        snap.validate(lay, consumer="optimizer")
+    # replacing one path of a shared parameter splits the alias
+    m.head.weight = nn.Parameter(torch.zeros(8, 4))
+    with pytest.raises(LayoutError, match="split"):
+        lay.refresh(m)
+
+
+def test_layout_rejects_wrapper_name_collision_and_stale_model():
+    import torch.nn as nn
+    from torchllmtuner_b200.parallel.assembly import LayoutError, ModelPartLayout, validate_layouts, capture_layouts
+
+    class Wrap(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.inner = nn.Linear(2, 2, bias=False)
+            self.weight = nn.Parameter(self.inner.weight.detach().clone())      # collapses onto inner.weight -> "weight"
+    lay = ModelPartLayout()
+    lay.refresh(Wrap())
+    with pytest.raises(LayoutError, match="collapse"):
+        lay.state_names
+    m = _tied()
+    lay = ModelPartLayout()
+    lay.refresh(m)
+    m.extra = nn.Linear(2, 2)
+    with pytest.raises(LayoutError, match="stale"):
+        lay.validate(m)
+    a, b = _tied(), _tied()
+    with pytest.raises(LayoutError, match="claimed by model parts"):
+        validate_layouts([a, b], capture_layouts([a, b]))
+
+
+def test_trainer_layout_binds_optimizer_and_checkpointer(tmp_path):
+    import torch
+    from dist_cases import base_flat
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.parallel.assembly import LayoutError
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(dump_folder=str(tmp_path), enable=True, interval=1, steps=2))
+    tr = Trainer(cfg)
+    lay = tr.asm.layout
+    assert lay is not None and tr.optimizers.layout_snapshot is not None
+    names = set(lay.state_names.values())
+    assert "model.layers.0.self_attn.q_proj.weight" in names and not any(".inner." in n for n in names)
+    tr.train_step()
+    tr.checkpointer.save(1, force=True)
+    tr.checkpointer.wait()
+    # a parameter swapped behind the optimizer's back: the next save refuses instead of writing state under a stale name
+    blk = next(m for n, m in tr.model.named_modules() if n.endswith("self_attn.q_proj"))
+    blk.weight = torch.nn.Parameter(blk.weight.detach().clone())
+    with pytest.raises(LayoutError):
+        tr.checkpointer.save(2, force=True)
+    tr.close()

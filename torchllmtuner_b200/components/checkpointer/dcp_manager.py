@@ -3,13 +3,13 @@ backends/distributed_checkpoint.py:102-899, core/format_state.py, core/random_st
 
 State categories, in order: format, model, optimizer, lr_scheduler, [ema], train_state, dataloader, rng.
 
-Tensor state lives in flat shards (see parallel/fsdp.py). It is written as 1-D pieces whose keys carry *global*
-coordinates of the full parameter, `model.<fqn>@<lo>:<hi>`, `optimizer.state.<fqn>.exp_avg@<lo>:<hi>`, so the layout on
-disk is independent of the data-parallel, expert-parallel and (for dim-0 cuts: column-parallel linears, vocab
-embedding, experts) tensor-parallel degree of the run that wrote it: a reader asks DCP's metadata which pieces exist and
-loads the ones that intersect what it owns. Expert tensors therefore appear as pieces of the FULL `(E, ...)` tensors and a
-run resumes at any EP degree. Parameters cut along a later dimension (row-parallel linears, TP-sharded experts) are
-keyed in local coordinates with their cut, `...@tp<dim>.<rank>of<size>@<lo>:<hi>`, and resume at the same TP degree.
+Tensor state lives in flat shards (see parallel/fsdp.py). On disk every parameter is ONE N-D tensor under its
+wrapper-free name (`model.layers.0.self_attn.q_proj.weight`), its moments under `optimizer.state.<fqn>.exp_avg` /
+`.exp_avg_sq` / `.momentum_buffer`, its average under `ema.ema_params.<fqn>`: the key layout of the reference. Each rank
+contributes the rectangular boxes that make up the flat range it owns (components/checkpointer/boxes.py), placed inside
+the global tensor by its tensor-, expert- or vocabulary-parallel cut, so the files are independent of every parallel
+degree of the run that wrote them and a reader loads exactly the boxes it owns. Format 2 of this framework (1-D pieces
+keyed `model.<fqn>@<lo>:<hi>`) is still read: `_load_pieces` is the migration path.
 
 Publication is atomic: a save writes into `step-N.tmp-<id>/` and renames it to `step-N/` after DCP has written its
 `.metadata`; `load` only considers folders that contain `.metadata`. A purge thread keeps the newest K resumable
@@ -18,6 +18,7 @@ background thread over a gloo group.
 """
 from __future__ import annotations
 
+import dataclasses
 import io
 import os
 import queue
@@ -34,7 +35,9 @@ import torch.distributed.checkpoint as dcp
 from ...errors import ConfigError
 from .manager import CheckpointManager
 
-FORMAT_VERSION = 2
+FORMAT_VERSION = 3
+READABLE_VERSIONS = (2, 3)
+_CATEGORIES = ("optimizer", "ema", "obj")
 _STEP_RE = re.compile(r"^step-(\d+)$")
 _TMP_RE = re.compile(r"^step-(\d+)\.tmp-[0-9a-f]+$")
 _PIECE_RE = re.compile(r"^(?P<base>.+?)(?:@tp(?P<dim>\d+)\.(?P<r>\d+)of(?P<n>\d+))?@(?P<lo>\d+):(?P<hi>\d+)$")
@@ -49,7 +52,23 @@ def _pack(obj) -> torch.Tensor:
 
 
 def _unpack(t: torch.Tensor):
-    return torch.load(io.BytesIO(t.numpy().tobytes()), weights_only=False)
+    """Only plain containers, numbers, strings and tensors come back: a checkpoint cannot make the reader run code."""
+    return torch.load(io.BytesIO(t.numpy().tobytes()), weights_only=True)
+
+
+def validate_step_counter(value, *, key: str) -> int:
+    """An optimizer step counter read from a checkpoint must be one finite, non-negative whole number (plain or a
+    one-element tensor); anything else would silently corrupt bias correction
+    (reference: llmtuner/components/optimizer/state_dict.py:237-265)."""
+    if isinstance(value, torch.Tensor):
+        if value.numel() != 1:
+            raise ConfigError(f"{key}: step counter must hold exactly one value, got {value.numel()}")
+        value = value.item()
+    if isinstance(value, bool) or not isinstance(value, (int, float)):
+        raise ConfigError(f"{key}: step counter must be a number, got {type(value).__name__}")
+    if value != value or value in (float("inf"), float("-inf")) or value < 0 or float(value) != int(value):
+        raise ConfigError(f"{key}: step counter must be a finite non-negative integer, got {value!r}")
+    return int(value)
 
 
 def canonical_fqn(fqn: str) -> str:
@@ -113,6 +132,38 @@ def piece_params(rt) -> dict:
     return out
 
 
+def cut_geometry(p):
+    """(local shape, global shape, offsets of the local tensor inside the global one) from the cut attributes that the
+    tensor-, expert- and vocabulary-parallel stages leave on a parameter."""
+    local = tuple(int(x) for x in getattr(p, "_meta_shape", p.shape))
+    glob = list(local)
+    off = [0] * len(local)
+    d = getattr(p, "tp_shard_dim", None)
+    if hasattr(p, "tp_full_shape") and (d is not None or getattr(p, "tp_vocab", False)):
+        fs = tuple(int(x) for x in p.tp_full_shape)
+        d = 0 if d is None else d
+        r = getattr(p, "_tp_rank", None)
+        if r is None:
+            raise ConfigError("tensor-parallel cut without a recorded rank")
+        glob[d] = fs[d]
+        off[d] = r * local[d]
+    if getattr(p, "ep_sharded", False):
+        glob[0] = int(p.ep_full_experts)
+        off[0] = int(p.ep_rank) * local[0]
+    return local, tuple(glob), tuple(off)
+
+
+def iter_boxes(rt):
+    """Yield (fqn, Box list, unit, shard_lo) for every parameter range this rank owns; box names are the bare fqn."""
+    from .boxes import boxes_of_slice
+    params = piece_params(rt)
+    for u in rt.units:
+        for fqn, _shape, lo, hi, shard_lo in u.shard_slices():
+            name = canonical_fqn(fqn)
+            local, glob, off = cut_geometry(params[name])
+            yield name, boxes_of_slice(name, lo, hi, local, glob, off), u, shard_lo
+
+
 _TAG_RE = re.compile(r"^@tp(?P<dim>\d+)\.(?P<r>\d+)of(?P<n>\d+)$")
 
 
@@ -162,27 +213,48 @@ class DistributedCheckpointManager(CheckpointManager):
                 p._tp_rank = topo.coord("tp")
 
     # ------------------------------------------------------------------ state assembly
-    def _tensor_state(self, model_only: bool = False) -> dict[str, torch.Tensor]:
+    def _tensor_state(self, model_only: bool = False):
+        """({key: view or tensor}, {key: Box}): box views of this rank's shards plus whole buffers from their owner."""
         tr = self.trainer
         out: dict[str, torch.Tensor] = {}
+        table: dict = {}
+
+        def add(name, boxes, flat, slo):
+            for b in boxes:
+                key = f"{name}#box{len(table)}"
+                table[key] = b if b.name == name else dataclasses.replace(b, name=name)
+                out[key] = flat[slo + b.start: slo + b.start + b.numel].view(b.sizes)
         for rt, opt in zip([tr.asm.fsdp], tr.optimizers.optimizers):
             moments = getattr(opt, "state", {})
-            for fqn, tag, glo, ghi, u, slo in iter_pieces(rt):
-                n = ghi - glo
-                suffix = f"{tag}@{glo}:{ghi}"
-                out[f"model.{fqn}{suffix}"] = u.master[slo:slo + n]
+            for fqn, boxes, u, slo in iter_boxes(rt):
+                if fqn.split(".")[0] in _CATEGORIES:
+                    raise ConfigError(f"parameter {fqn} is named like a checkpoint state category")
+                add(fqn, boxes, u.master, slo)
                 if model_only:
                     continue
                 st = moments.get(u.name)
                 if st is not None:
                     for k in ("exp_avg", "exp_avg_sq", "momentum_buffer"):
                         if k in st:
-                            out[f"optimizer.state.{fqn}.{k}{suffix}"] = st[k][slo:slo + n]
+                            add(f"optimizer.state.{fqn}.{k}", boxes, st[k], slo)
                 if tr.ema is not None:
-                    out[f"ema.ema_params.{fqn}{suffix}"] = tr.ema.ema_params[u.name][slo:slo + n]
+                    add(f"ema.ema_params.{fqn}", boxes, tr.ema.ema_params[u.name], slo)
         for name, buf in tr.model.named_buffers():
             if buf is not None and self._owns_replicated():
-                out[f"model.{canonical_fqn(name)}@0:{buf.numel()}"] = buf.detach().reshape(-1)
+                out[canonical_fqn(name)] = buf.detach()
+        return out, table
+
+    def _full_shapes(self) -> dict[str, list[int]]:
+        """canonical fqn -> shape of the whole (unsharded, all experts) parameter; what a converter needs to turn the
+        flat pieces back into tensors."""
+        out = {}
+        for fqn, p in piece_params(self.trainer.asm.fsdp).items():
+            shape = list(getattr(p, "_meta_shape", p.shape))
+            if hasattr(p, "tp_full_shape") and not getattr(p, "ep_sharded", False):
+                shape = list(p.tp_full_shape)
+            if getattr(p, "ep_sharded", False):
+                shape[0] = p.ep_full_experts
+            out[fqn] = [int(x) for x in shape]
         return out
 
     def _owns_replicated(self) -> bool:
@@ -195,10 +267,11 @@ class DistributedCheckpointManager(CheckpointManager):
         obj = {}
         if self.rank == 0:
             obj["format"] = {"version": FORMAT_VERSION, "topology": t.snapshot(), "model": type(tr.model).__name__,
-                             "arch": {k: v for k, v in vars(tr.model.config).items() if isinstance(v, (int, float, str, bool, list))}}
+                             "arch": {k: v for k, v in vars(tr.model.config).items() if isinstance(v, (int, float, str, bool, list))},
+                             "state_format": getattr(tr.model, "state_format", "native"), "shapes": self._full_shapes()}
             obj["optimizer.step"] = [getattr(o, "step_count", 0) for o in tr.optimizers.optimizers]
-            obj["optimizer.param_groups"] = [[{k: v for k, v in g.items() if k != "param_names"} for g in o.param_groups]
-                                             for o in tr.optimizers.optimizers]
+            obj["optimizer.param_groups"] = [[dict(g, param_names=[canonical_fqn(n) for n in g.get("param_names", [])])
+                                              for g in o.param_groups] for o in tr.optimizers.optimizers]
             obj["lr_scheduler"] = tr.lr_schedulers.state_dict()
             obj["train_state"] = tr.progress.state_dict()
             if tr.ema is not None:
@@ -219,10 +292,24 @@ class DistributedCheckpointManager(CheckpointManager):
             return True
         return step % self.cfg.interval == 0
 
+    def _check_layout(self, what: str) -> None:
+        """Optimizer and EMA state are keyed by parameter names: refuse to write or read them when the model's parameters
+        are no longer the ones those consumers were built against."""
+        tr = self.trainer
+        layout = getattr(getattr(tr, "asm", None), "layout", None)
+        if layout is None:
+            return
+        layout.validate(tr.model)
+        for consumer, obj in (("optimizer", getattr(tr, "optimizers", None)), ("ema", getattr(tr, "ema", None))):
+            snap = getattr(obj, "layout_snapshot", None)
+            if snap is not None:
+                snap.validate(layout, consumer=f"checkpoint {what}: {consumer}")
+
     def save(self, step: int, last_step: bool = False, force: bool = False) -> None:
         if not (force or self._should_save(step, last_step)):
             return
         self.wait()
+        self._check_layout("save")
         model_only = last_step and self.cfg.last_save_model_only and not force and step != 0
         if last_step and self.cfg.last_save_in_hf:
             from .hf import save_hf_checkpoint
@@ -235,10 +322,11 @@ class DistributedCheckpointManager(CheckpointManager):
             save_id = ids[0]
         final = os.path.join(self.root, "model-export" if model_only and False else f"step-{step}")
         tmp = f"{final}.tmp-{save_id}"
-        state = self._tensor_state(model_only=model_only)
+        from .boxes import BoxSavePlanner
+        state, table = self._tensor_state(model_only=model_only)
         state.update(self._object_state())
         if self.cfg.async_mode == "disabled":
-            dcp.save(state, checkpoint_id=tmp)
+            dcp.save(state, checkpoint_id=tmp, planner=BoxSavePlanner(table))
             self._publish(tmp, final, step)
         else:
             pin = self.cfg.async_mode == "async_with_pinned_mem" and torch.cuda.is_available()
@@ -252,7 +340,7 @@ class DistributedCheckpointManager(CheckpointManager):
                     staged[k] = v
             if torch.cuda.is_available():
                 torch.cuda.synchronize()
-            fut = dcp.async_save(staged, checkpoint_id=tmp, process_group=self._gloo)
+            fut = dcp.async_save(staged, checkpoint_id=tmp, process_group=self._gloo, planner=BoxSavePlanner(table))
             self._async_future = (fut, tmp, final, step)
 
     def _publish(self, tmp: str, final: str, step: int) -> None:
@@ -372,9 +460,96 @@ class DistributedCheckpointManager(CheckpointManager):
         return True
 
     def _load_dcp(self, path: str, model_only: bool) -> None:
-        tr = self.trainer
+        self._check_layout("load")
         reader = dcp.FileSystemReader(path)
         meta = reader.read_metadata()
+        if any(_PIECE_RE.match(k) for k in meta.state_dict_metadata):
+            self._load_pieces(path, model_only, reader, meta)       # written by format 2
+        else:
+            self._load_boxes(path, model_only, reader, meta)
+
+    def _object_wants(self, meta, model_only: bool, exclude) -> dict:
+        obj_keys = ["format"]
+        if not model_only:
+            t = self.trainer.env.topo
+            obj_keys += ["optimizer.step", "lr_scheduler", "train_state", "ema.num_updates", f"dataloader.dp{t.coord('dp')}",
+                         f"rng.rank{self.rank}"]
+        want = {}
+        for k in obj_keys:
+            md = meta.state_dict_metadata.get(f"obj.{k}")
+            if md is not None and k.split(".")[0] not in exclude:
+                want[f"obj.{k}"] = torch.empty(md.size, dtype=torch.uint8)
+        return want
+
+    def _load_boxes(self, path: str, model_only: bool, reader, meta) -> None:
+        from .boxes import BoxLoadPlanner
+        tr = self.trainer
+        exclude = set(self.cfg.exclude_from_loading)
+        want: dict[str, torch.Tensor] = {}
+        table: dict = {}
+        staged = []                  # (device view, host tensor): DCP reads into host memory, one copy to the device follows
+
+        def add(name, boxes, flat, slo):
+            for b in boxes:
+                key = f"{name}#box{len(table)}"
+                table[key] = dataclasses.replace(b, name=name)
+                dst = flat[slo + b.start: slo + b.start + b.numel].view(b.sizes)
+                if dst.device.type != "cpu":
+                    host = torch.empty(b.sizes, dtype=dst.dtype)
+                    staged.append((dst, host, key))
+                    dst = host
+                want[key] = dst
+        required = set()
+        for rt, opt in zip([tr.asm.fsdp], tr.optimizers.optimizers):
+            for fqn, boxes, u, slo in iter_boxes(rt):
+                if "model" not in exclude:
+                    add(fqn, boxes, u.master, slo)
+                    required.add(fqn)
+                if model_only or "optimizer" in exclude:
+                    continue
+                st = getattr(opt, "state", {}).get(u.name, {})
+                for k in ("exp_avg", "exp_avg_sq", "momentum_buffer"):
+                    if k in st:
+                        add(f"optimizer.state.{fqn}.{k}", boxes, st[k], slo)
+                if tr.ema is not None and "ema" not in exclude:
+                    add(f"ema.ema_params.{fqn}", boxes, tr.ema.ema_params[u.name], slo)
+        buf_dst = {}
+        for name, buf in tr.model.named_buffers():
+            key = canonical_fqn(name)
+            md = meta.state_dict_metadata.get(key)
+            if md is not None and "model" not in exclude and tuple(md.size) == tuple(buf.shape):
+                want[key] = torch.empty(buf.shape, dtype=buf.dtype)
+                buf_dst[key] = buf
+        obj_want = self._object_wants(meta, model_only, exclude)
+        want.update(obj_want)
+        planner = BoxLoadPlanner(table)
+        dcp.load(want, checkpoint_id=path, storage_reader=reader, planner=planner, no_dist=True)
+        lacking = sorted(required & planner.missing)
+        if lacking:
+            raise ConfigError(f"checkpoint {path} lacks model tensors: {lacking[:5]}{'...' if len(lacking) > 5 else ''}")
+        with torch.no_grad():
+            for dst, host, key in staged:
+                if table[key].name not in planner.missing:
+                    dst.copy_(host)
+            for key, buf in buf_dst.items():
+                buf.copy_(want[key])
+        self._after_tensor_load()
+        self._restore_objects({k[4:]: _unpack(v) for k, v in obj_want.items()}, model_only)
+
+    def _after_tensor_load(self) -> None:
+        with torch.no_grad():
+            for rt in [self.trainer.asm.fsdp]:
+                for u in rt.units:
+                    if u.separate_master:
+                        u.shard_lowp.copy_(u.master)
+                    if u.world > 1:
+                        u.gathered = False
+                        if getattr(u, "persistent", False):
+                            rt.unshard(u)
+
+    def _load_pieces(self, path: str, model_only: bool, reader, meta) -> None:
+        """Format 2: 1-D pieces in global flat coordinates, `model.<fqn>@<lo>:<hi>`."""
+        tr = self.trainer
         have: dict[tuple[str, str], list[tuple[int, int]]] = {}
         for key in meta.state_dict_metadata:
             m = _PIECE_RE.match(key)
@@ -490,14 +665,21 @@ class DistributedCheckpointManager(CheckpointManager):
                         u.gathered = False
                         if getattr(u, "persistent", False):
                             rt.unshard(u)
+        self._restore_objects(want, model_only)
+
+    def _restore_objects(self, want: dict, model_only: bool) -> None:
+        tr = self.trainer
         fmt = want.get("format")
-        if isinstance(fmt, dict) and fmt.get("version") != FORMAT_VERSION:
-            raise ConfigError(f"checkpoint format version {fmt.get('version')} != {FORMAT_VERSION}")
+        if isinstance(fmt, dict) and fmt.get("version") not in READABLE_VERSIONS:
+            raise ConfigError(f"checkpoint format version {fmt.get('version')} is not one of {READABLE_VERSIONS}")
         if model_only:
             return
         if "optimizer.step" in want:
-            for o, s in zip(tr.optimizers.optimizers, want["optimizer.step"]):
-                o.step_count = int(s)
+            steps = want["optimizer.step"]
+            if not isinstance(steps, (list, tuple)) or len(steps) != len(tr.optimizers.optimizers):
+                raise ConfigError(f"checkpoint records {steps!r} optimizer step counters for {len(tr.optimizers.optimizers)} optimizers")
+            for o, s in zip(tr.optimizers.optimizers, steps):
+                o.step_count = validate_step_counter(s, key="optimizer.step")
         if isinstance(want.get("lr_scheduler"), dict):
             tr.lr_schedulers.load_state_dict(want["lr_scheduler"])
         if isinstance(want.get("train_state"), dict):

@@ -61,7 +61,7 @@ def _full_shape(p, s):
 
 def load_hf_checkpoint(trainer, path: str) -> None:
     from safetensors import safe_open
-    fmt = get_state_format(getattr(trainer, "state_format", "qwen3"))
+    fmt = get_state_format(getattr(trainer.model, "state_format", "qwen3"))
     wmap = read_hf_weight_map(path)
     handles: dict[str, object] = {}
 
@@ -106,7 +106,7 @@ def load_hf_checkpoint(trainer, path: str) -> None:
 def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", max_shard_bytes: int = 5 << 30) -> None:
     from safetensors.torch import save_file
     rank, world = trainer.env.rank, trainer.env.world_size
-    fmt = get_state_format(getattr(trainer, "state_format", "qwen3"))
+    fmt = get_state_format(getattr(trainer.model, "state_format", "qwen3"))
     dt = _DT[export_dtype]
     pidx = _param_index(trainer)
     mine: dict[str, list] = {}

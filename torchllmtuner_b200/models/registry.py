@@ -67,7 +67,9 @@ def build_registered_model(model_config, dtype=None, device=None):
         overrides = {k: v for k, v in hf.items() if not isinstance(v, (dict,))}
         overrides["num_experts"] = hf.get("num_experts", 0) or 0
     spec = get_model_spec(key)
-    return spec.builder(model_config, dtype=dtype, device=device, **overrides)
+    model = spec.builder(model_config, dtype=dtype, device=device, **overrides)
+    model.state_format = spec.state_format           # read by the HF and reference-layout converters
+    return model
 
 
 _loaded = False

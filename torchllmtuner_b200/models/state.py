@@ -17,8 +17,27 @@ class HFPiece:
     native_flat_hi: int
 
 
+@dataclass
+class RefPiece:
+    """`n` consecutive elements of the flattened native tensor, starting at `native_lo`, are elements
+    `ref_lo .. ref_lo + n` of the flattened tensor `name` (whole shape `shape`) of the reference's own model classes."""
+    name: str
+    shape: tuple
+    ref_lo: int
+    native_lo: int
+    n: int
+
+
 class ModelStateFormat:
     name = "native"
+
+    def to_reference(self, fqn: str, shape) -> list[RefPiece]:
+        """Names and layouts of the reference's native modules (its distributed checkpoints are keyed by them). The
+        default covers tensors that `to_hf` maps one to one."""
+        pieces = self.to_hf(fqn, shape)
+        if len(pieces) != 1:
+            raise NotImplementedError(f"{self.name}: no reference layout for {fqn}")
+        return [RefPiece(pieces[0].hf_name, tuple(shape), 0, pieces[0].native_flat_lo, pieces[0].native_flat_hi - pieces[0].native_flat_lo)]
 
     def to_hf(self, fqn: str, shape) -> list[HFPiece]:
         n = 1
@@ -46,6 +65,20 @@ class Qwen3StateFormat(ModelStateFormat):
         if m:
             return [HFPiece(f"{m.group(1)}.gate.weight", 0, shape[0] * shape[1])]
         return super().to_hf(fqn, shape)
+
+    def to_reference(self, fqn, shape):
+        # packed experts of the reference (llmtuner/models/qwen/qwen3/model.py:312): gate_up_proj (E, 2F, D) holds the gate
+        # rows then the up rows of each expert, down_proj (E, D, F)
+        m = self._EXP.match(fqn)
+        if m:
+            E, a, b = shape
+            which = m.group(2)
+            if which == "w2_EDF":
+                return [RefPiece(f"{m.group(1)}.experts.down_proj", (E, a, b), 0, 0, E * a * b)]
+            half = a * b
+            off = 0 if which == "w1_EFD" else half
+            return [RefPiece(f"{m.group(1)}.experts.gate_up_proj", (E, 2 * a, b), e * 2 * half + off, e * half, half) for e in range(E)]
+        return super().to_reference(fqn, shape)
 
     def hf_config(self, arch) -> dict:
         moe = arch.num_experts > 0

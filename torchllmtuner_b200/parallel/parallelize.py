@@ -22,6 +22,7 @@ class ParallelAssembly:
     stages_applied: list[str] = field(default_factory=list)
     plans: dict = field(default_factory=dict)          # stage -> ParallelPlan, resolved before any mutation
     execution: object = None                            # ExecutionLayout
+    layout: object = None                               # ModelPartLayout of the assembled model
 
 
 def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None) -> ParallelAssembly:
@@ -85,6 +86,12 @@ def parallelize_model(model, config, topo, *, device, param_dtype, init_fn=None)
     except Exception:
         max_tokens = 0
     _bind_moe_stream_groups(model, topo, config.parallel.ep_config.router_aux_loss_coef, max_tokens)
+    # The record optimizer, EMA and checkpointer bind to: final parameter objects under wrapper-free names.
+    from .assembly import ModelPartLayout
+    with synchronize_local_errors("parallelize:layout"):
+        asm.layout = ModelPartLayout(execution=asm.execution, topology=topo.snapshot())
+        asm.layout.refresh(model)
+        asm.layout.validate(model)
     return asm
 
 

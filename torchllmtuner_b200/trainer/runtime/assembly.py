@@ -45,6 +45,9 @@ def prepare_parallel_model(config, env):
         for name, buf in list(m._buffers.items()):
             if buf is not None and buf.device != env.device:
                 m._buffers[name] = buf.to(env.device)
+    if asm.layout is not None:         # materialisation may have swapped parameter objects: paths, order and sharing must survive
+        asm.layout.refresh(model)
+        asm.layout.validate(model)
     return model, asm
 
 
@@ -72,6 +75,12 @@ def build_optimizer_stack(config, env, asm):
     lr = build_lr_scheduler(optimizers, config.optimizer.lr_scheduler_config, config.training.steps)
     ema = EMA([asm.fsdp], config.training.ema_config, config.training.steps) if config.training.ema_config is not None else None
     clipper = GradientClipper([asm.fsdp], env.topo, config.training.max_norm, env.device)
+    if asm.layout is not None:
+        # the state consumers remember the layout they were built against; the checkpointer checks it before every save/load
+        asm.layout.validate(asm.model)
+        optimizers.layout_snapshot = asm.layout.snapshot()
+        if ema is not None:
+            ema.layout_snapshot = optimizers.layout_snapshot
     return optimizers, lr, ema, clipper
 
 
