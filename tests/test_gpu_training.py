@@ -52,3 +52,42 @@ def test_host_resident_optimizer_state_keeps_the_losses():
     ref, _ = _run(_cfg())
     got, _ = _run(_cfg(fsdp_cpu_offload=True))
     assert max(abs(a - b) for a, b in zip(ref, got)) < 1e-3, (ref, got)
+
+
+def _repeat_two_batches(tr, steps):
+    """Random tokens carry nothing to learn unless they repeat: alternate between the first two batches of the stream."""
+    out = []
+    for i in range(steps):
+        if i % 2 == 0:
+            tr.dataloader.cursor = 0
+        out.append(tr.train_step().loss)
+    return out
+
+
+def test_twenty_step_loss_curve_follows_the_fp32_oracle(tmp_path, monkeypatch):
+    """The same model, weights and token stream trained twice through the public Trainer: once on the host in fp32 with
+    the plain PyTorch statements of every op (the oracle), once on the GPU with the bf16 kernels. The weights travel
+    through a checkpoint, so both runs start from identical parameters. The curves must track each other step by step;
+    a kernel whose gradient is subtly wrong shows up as a drift that grows over the twenty steps."""
+    steps = 20
+    folder = str(tmp_path / "oracle")
+    kw = dict(dump_folder=folder, enable=True, interval=1000, steps=steps, learning_rate=3e-3, warmup_steps=2,
+              hidden_size=256, intermediate_size=512, max_seq_len=512, global_batch_size=4)
+    monkeypatch.setenv("LLMTUNER_DEVICE", "cpu")
+    tr = Trainer(_cfg(**kw))
+    assert next(tr.model.parameters()).device.type == "cpu"
+    tr.checkpointer.save(0, force=True)
+    tr.checkpointer.wait()
+    oracle = _repeat_two_batches(tr, steps)
+    tr.close()
+    monkeypatch.delenv("LLMTUNER_DEVICE")
+    tr = Trainer(_cfg(exclude_from_loading=["rng"], **kw))
+    assert next(tr.model.parameters()).device.type == "cuda"
+    assert tr.checkpointer.load(0)
+    got = _repeat_two_batches(tr, steps)
+    tr.close()
+    assert abs(got[0] - oracle[0]) < 0.02, (got[0], oracle[0])                     # same weights, same batch: forward only
+    worst = max(abs(a - b) for a, b in zip(got, oracle))
+    assert worst < 0.15, list(zip(got, oracle))
+    assert oracle[0] - oracle[-1] > 0.5 and got[0] - got[-1] > 0.5, (oracle, got)   # both actually learn
+    assert abs((got[0] - got[-1]) - (oracle[0] - oracle[-1])) < 0.15

@@ -6,9 +6,7 @@ They share one hybrid decoder: every layer has a token mixer and an MLP (dense o
                                              softmax attention with an output gate; gated RMSNorm on the mixer output
   kimi_linear / kimi_k3                      KDA (delta rule with per-channel decay) layers with an MLA (latent
                                              attention) layer every 4th; sigmoid router with shared experts
-  deepseek_v4                                latent attention (low-rank KV with a decoupled rotary key), sigmoid router
-                                             with the aux-loss-free selection bias, hyper-connections (several residual
-                                             streams mixed by learned weights)
+(DeepSeek-V4 has its own module, `models/deepseek_v4.py`.)
 Softmax attention and every GEMM run on the sm_100a kernels; the delta rule runs in chunk-parallel form (batched matrix
 products and one triangular solve per layer, a short loop over chunks for the state; per document). The vision tower,
 the 3-axis rotary positions and the wrapper that splices image rows into these decoders are in `models/vision.py`.
@@ -329,9 +327,6 @@ FAMILIES = {
     "kimi_k3": dict(model_type="kimi_k3", mixer_pattern=["kda", "kda", "kda", "mla"], delta_channel_decay=True, num_experts=8,
                     num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64, router_score_fn="sigmoid",
                     mlp_only_layers=[0]),
-    "deepseek_v4": dict(model_type="deepseek_v4", mixer_pattern=["mla"], num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
-                        shared_expert_intermediate_size=64, router_score_fn="sigmoid", router_bias_update_coeff=1e-3,
-                        hyper_connection_streams=2, mlp_only_layers=[0]),
 }
 
 

@@ -110,14 +110,23 @@ class _CombineRows(torch.autograd.Function):
 
 
 class GroupedExperts(nn.Module):
-    def __init__(self, num_experts: int, hidden: int, inter: int, dtype=None, device=None, implementation: str = "native"):
+    def __init__(self, num_experts: int, hidden: int, inter: int, dtype=None, device=None, implementation: str = "native",
+                 swiglu_limit: float | None = None):
         super().__init__()
         self.num_experts, self.hidden, self.inter, self.implementation = num_experts, hidden, inter, implementation
+        # asymmetric clamp before the gated activation: gate <= limit, |up| <= limit
+        # (reference: llmtuner/models/deepseek/deepseek_v4/modeling.py:164-169)
+        self.swiglu_limit = swiglu_limit
         self.w1_EFD = nn.Parameter(torch.empty(num_experts, inter, hidden, dtype=dtype, device=device))
         self.w3_EFD = nn.Parameter(torch.empty(num_experts, inter, hidden, dtype=dtype, device=device))
         self.w2_EDF = nn.Parameter(torch.empty(num_experts, hidden, inter, dtype=dtype, device=device))
         for p in (self.w1_EFD, self.w3_EFD, self.w2_EDF):
             p.is_expert = True
+
+    def _clamp(self, g, u):
+        if self.swiglu_limit is None:
+            return g, u
+        return g.clamp(max=self.swiglu_limit), u.clamp(min=-self.swiglu_limit, max=self.swiglu_limit)
 
     def forward(self, rows: torch.Tensor, seg_offsets: torch.Tensor) -> torch.Tensor:
         """rows: padded expert-major rows [R, D]; returns [R, D]."""
@@ -129,11 +138,10 @@ class GroupedExperts(nn.Module):
             for e in range(self.w1_EFD.shape[0]):
                 s, t = seg[e], seg[e + 1]
                 if t > s:
-                    h = ops.swiglu(ops.linear(rows[s:t], self.w1_EFD[e]), ops.linear(rows[s:t], self.w3_EFD[e]))
+                    h = ops.swiglu(*self._clamp(ops.linear(rows[s:t], self.w1_EFD[e]), ops.linear(rows[s:t], self.w3_EFD[e])))
                     out[s:t] = ops.linear(h, self.w2_EDF[e])
             return out
-        g = grouped_linear(rows, self.w1_EFD, seg_offsets)
-        u = grouped_linear(rows, self.w3_EFD, seg_offsets)
+        g, u = self._clamp(grouped_linear(rows, self.w1_EFD, seg_offsets), grouped_linear(rows, self.w3_EFD, seg_offsets))
         # rows past the last segment of a statically sized receive buffer hold nothing: the kernels skip them
         limit = seg_offsets[-1:] if rows.is_cuda and seg_offsets.dtype == torch.int32 else None
         return grouped_linear(ops.swiglu(g, u, limit), self.w2_EDF, seg_offsets)

@@ -10,7 +10,7 @@ import torch
 import torch.nn as nn
 
 from .experts import GroupedExperts, RoutedExperts
-from .routing import QuantileBalancedTopKRouter, TokenChoiceTopKRouter
+from .routing import HashRouter, QuantileBalancedTopKRouter, TokenChoiceTopKRouter
 
 
 class MoE(nn.Module):
@@ -18,13 +18,18 @@ class MoE(nn.Module):
                  score_fn: str = "softmax", norm_topk_prob: bool = True, route_scale: float = 1.0,
                  bias_update_coeff: float = 0.0, aux_loss_coef: float = 0.0, quantile_balancing: bool = False,
                  fixed_router: bool = False, experts_implementation: str = "native", dtype=None, device=None,
-                 shared_mlp_factory=None):
+                 shared_mlp_factory=None, swiglu_limit: float | None = None, hash_vocab_size: int = 0):
         super().__init__()
-        rcls = QuantileBalancedTopKRouter if quantile_balancing else TokenChoiceTopKRouter
-        self.router = rcls(hidden, num_experts, top_k, score_fn, norm_topk_prob, route_scale, fixed=fixed_router, dtype=dtype,
-                           device=device)
+        if hash_vocab_size:
+            self.router = HashRouter(hidden, num_experts, top_k, hash_vocab_size, score_fn, norm_topk_prob, route_scale, dtype=dtype,
+                                     device=device)
+        else:
+            rcls = QuantileBalancedTopKRouter if quantile_balancing else TokenChoiceTopKRouter
+            self.router = rcls(hidden, num_experts, top_k, score_fn, norm_topk_prob, route_scale, fixed=fixed_router, dtype=dtype,
+                               device=device)
+        self.hash_routed = bool(hash_vocab_size)
         self.routed = RoutedExperts(GroupedExperts(num_experts, hidden, moe_inter, dtype=dtype, device=device,
-                                                   implementation=experts_implementation))
+                                                   implementation=experts_implementation, swiglu_limit=swiglu_limit))
         self.shared_experts = shared_mlp_factory(shared_inter) if (shared_inter and shared_mlp_factory) else None
         self.num_experts, self.top_k = num_experts, top_k
         self.bias_update_coeff, self.aux_loss_coef = bias_update_coeff, aux_loss_coef
@@ -42,11 +47,11 @@ class MoE(nn.Module):
     def experts(self):
         return self.routed.experts
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, token_ids: torch.Tensor | None = None) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         bias = self.expert_bias_E if self.bias_update_coeff > 0 else None
-        w, idx, counts, scores = self.router(x2, bias)
+        w, idx, counts, scores = self.router(x2, bias, token_ids=token_ids) if self.hash_routed else self.router(x2, bias)
         if self.training and torch.is_grad_enabled():
             with torch.no_grad():
                 self.tokens_per_expert_E.add_(counts)

@@ -108,6 +108,36 @@ class TokenChoiceTopKRouter(nn.Module):
         return w, idx, counts, scores
 
 
+class HashRouter(TokenChoiceTopKRouter):
+    """Experts come from a persistent token-id table `tid2eid` [vocab, k] instead of a top-k; the learned projection
+    still scores them, so the combine weights (and the projection's gradient) are those of the looked-up experts
+    (reference: llmtuner/models/deepseek/deepseek_v4/routing.py:60-85). The caller passes the token ids of the rows."""
+
+    def __init__(self, hidden: int, num_experts: int, top_k: int, vocab_size: int, score_fn: str = "sqrtsoftplus",
+                 norm_topk_prob: bool = True, route_scale: float = 1.0, dtype=None, device=None):
+        super().__init__(hidden, num_experts, top_k, score_fn, norm_topk_prob, route_scale, dtype=dtype, device=device)
+        self.register_buffer("tid2eid", torch.zeros(vocab_size, top_k, dtype=torch.int64, device=device), persistent=True)
+
+    @torch.no_grad()
+    def fill_table(self, seed: int = 0) -> None:
+        """A fixed pseudo-random table with k distinct experts per token id (pre-trained checkpoints bring their own)."""
+        g = torch.Generator().manual_seed(seed)
+        V, k = self.tid2eid.shape
+        self.tid2eid.copy_(torch.rand(V, self.num_experts, generator=g).topk(k, dim=-1).indices.to(self.tid2eid.device))
+
+    def forward(self, x: torch.Tensor, expert_bias=None, token_ids: torch.Tensor | None = None):
+        if token_ids is None:
+            raise ValueError("a hash-routed block needs the token ids of its rows")
+        scores = ref.router_scores(self.gate(x), self.score_fn)
+        idx = self.tid2eid[token_ids.reshape(-1)]
+        w = scores.gather(-1, idx)
+        if self.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        counts = torch.zeros(self.num_experts, dtype=torch.float32, device=x.device)
+        counts.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x.device))
+        return w * self.route_scale, idx, counts, scores
+
+
 class QuantileBalancer(nn.Module):
     """Running per-expert logit quantiles from a 1000-bin histogram (reference: routing.py:491)."""
 

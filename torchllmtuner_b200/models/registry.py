@@ -88,8 +88,8 @@ def _ensure_builtins() -> None:
         state_format="qwen3", description="Qwen3-8B architecture")
     reg("qwen3_30b_a3b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_30B_A3B, **(mc.arch_overrides or {}), **kw}),
         state_format="qwen3", description="Qwen3-30B-A3B architecture")
-    try:
-        from . import families
-        families.register_all(reg)
-    except ImportError:
-        pass
+    from . import deepseek_v4, families
+    families.register_all(reg)
+    reg("deepseek_v4", deepseek_v4.build_deepseek_v4, state_format="deepseek_v4", supports={"fsdp", "ep", "ac"},
+        description="DeepSeek-V4 decoder: hyper-connections, shared-KV sliding/compressed attention with an indexer, hash and "
+                    "biased top-k routers")

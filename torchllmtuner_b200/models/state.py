@@ -95,7 +95,54 @@ class Qwen3StateFormat(ModelStateFormat):
         return cfg
 
 
-_FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat()}
+class DeepseekV4StateFormat(Qwen3StateFormat):
+    """Native names follow the reference's module tree except inside the MoE block: the router projection is
+    `mlp.gate.weight`, the hash table `mlp.gate.tid2eid`, the indexer's head weights sit under `indexer.scorer`
+    (reference: llmtuner/models/deepseek/deepseek_v4/modeling.py:219-247, indexer.py:18-60). Experts: one tensor per
+    expert and projection in HF files, packed `gate_up_proj` / `down_proj` in the reference's own checkpoints."""
+    name = "deepseek_v4"
+    _RENAMES = ((re.compile(r"^(model\.layers\.\d+\.mlp)\.router\.gate\.weight$"), r"\1.gate.weight"),
+                (re.compile(r"^(model\.layers\.\d+\.self_attn\.compressor\.indexer)\.weights_proj\.weight$"), r"\1.scorer.weights_proj.weight"))
+    BUFFER_RENAMES = {"mlp.router.tid2eid": "mlp.gate.tid2eid", "mlp.expert_bias_E": "mlp.gate.e_score_correction_bias"}
+
+    def _rename(self, fqn: str) -> str:
+        for rx, to in self._RENAMES:
+            if rx.match(fqn):
+                return rx.sub(to, fqn)
+        return fqn
+
+    def to_hf(self, fqn, shape):
+        if self._EXP.match(fqn):
+            return super().to_hf(fqn, shape)
+        n = 1
+        for x in shape:
+            n *= x
+        return [HFPiece(self._rename(fqn), 0, n)]
+
+    def to_reference(self, fqn, shape):
+        if self._EXP.match(fqn):
+            return super().to_reference(fqn, shape)
+        n = 1
+        for x in shape:
+            n *= x
+        return [RefPiece(self._rename(fqn), tuple(shape), 0, 0, n)]
+
+    def hf_config(self, arch) -> dict:
+        keep = ("vocab_size", "hidden_size", "num_hidden_layers", "num_attention_heads", "head_dim", "q_lora_rank", "o_lora_rank",
+                "o_groups", "qk_rope_head_dim", "swiglu_limit", "rms_norm_eps", "sliding_window", "layer_types", "mlp_layer_types",
+                "compress_rates", "index_head_dim", "index_n_heads", "index_topk", "hc_mult", "hc_eps", "hc_sinkhorn_iters",
+                "num_experts_per_tok", "scoring_func", "routed_scaling_factor", "tie_word_embeddings", "max_position_embeddings")
+        cfg = {k: getattr(arch, k) for k in keep}
+        cfg.update(architectures=["DeepseekV4ForCausalLM"], model_type="deepseek_v4", n_routed_experts=arch.num_experts,
+                   intermediate_size=arch.moe_intermediate_size, n_shared_experts=1, hidden_act="silu", torch_dtype="bfloat16",
+                   rope_parameters={"main": {"rope_type": "default", "rope_theta": arch.rope_theta,
+                                             "partial_rotary_factor": arch.qk_rope_head_dim / arch.head_dim},
+                                    "compress": {"rope_type": "default", "rope_theta": arch.compress_rope_theta,
+                                                 "partial_rotary_factor": arch.qk_rope_head_dim / arch.head_dim}})
+        return cfg
+
+
+_FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat()}
 
 
 def get_state_format(name: str) -> ModelStateFormat:

@@ -113,7 +113,7 @@ class ModelPartLayout:
         if self.execution is not None and hasattr(self.execution, "validate_model"):
             self.execution.validate_model(model)
         if self.execution is not None and self.topology is not None:
-            degree = {"cp": int(self.topology.get("cp_kv", 1)) * int(self.topology.get("cp_ulysses", 1)),
+            degree = {"cp": int(self.topology.get("cp_kv", 1)) * int(self.topology.get("cp_ulysses", 1)) * int(self.topology.get("kcp", 1)),
                       "tp": int(self.topology.get("tp", 1))}
             axes = tuple(a for a in ("cp", "tp") if degree[a] > 1)
             declared = tuple(getattr(self.execution, "sequence_shard_axes", axes))
