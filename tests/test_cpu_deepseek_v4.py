@@ -229,3 +229,12 @@ def test_trains_through_the_trainer_and_round_trips_its_checkpoint_names(tmp_pat
               "model.layers.2.self_attn.compressor.position_bias", "model.layers.0.attn_hc.fn", "model.hc_head.hc_fn", "model.layers.0.self_attn.sinks",
               "model.layers.0.self_attn.o_a_proj.weight"):
         assert k in keys, (k, sorted(keys)[:30])
+
+
+def test_two_fsdp_ranks_match_one():
+    """The stream-collapsing head belongs to no decoder block; its shard must be gathered again after every step."""
+    from dist_cases import base_flat, run_ranks
+    base = dict(model_name_or_path="deepseek_v4", num_hidden_layers=3, max_seq_len=64)
+    ref = run_ranks(1, base_flat(**base), steps=4)
+    got = run_ranks(2, base_flat(data_parallel_shard_size=2, **base), steps=4)
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 5e-5, (ref, got)

@@ -4,8 +4,9 @@
 They share one hybrid decoder: every layer has a token mixer and an MLP (dense or the shared MoE block).
   qwen3_5 / qwen3_5_moe / qwen3_5_moe_text   3 of 4 layers use a gated delta-net linear attention, every 4th layer a
                                              softmax attention with an output gate; gated RMSNorm on the mixer output
-  kimi_linear / kimi_k3                      KDA (delta rule with per-channel decay) layers with an MLA (latent
+  hybrid_kda_mla                             KDA (delta rule with per-channel decay) layers with an MLA (latent
                                              attention) layer every 4th; sigmoid router with shared experts
+(Kimi-Linear / Kimi-K3 have their own module, `models/kimi_k3.py`.)
 (DeepSeek-V4 has its own module, `models/deepseek_v4.py`.)
 Softmax attention and every GEMM run on the sm_100a kernels; the delta rule runs in chunk-parallel form (batched matrix
 products and one triangular solve per layer, a short loop over chunks for the state; per document). The vision tower,
@@ -321,12 +322,11 @@ FAMILIES = {
                         num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64),
     "qwen3_5_moe_text": dict(model_type="qwen3_5_moe_text", mixer_pattern=["delta", "delta", "delta", "attention"], num_experts=8,
                              num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64),
-    "kimi_linear": dict(model_type="kimi_linear", mixer_pattern=["kda", "kda", "kda", "mla"], delta_channel_decay=True, num_experts=8,
-                        num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64, router_score_fn="sigmoid",
-                        mlp_only_layers=[0]),
-    "kimi_k3": dict(model_type="kimi_k3", mixer_pattern=["kda", "kda", "kda", "mla"], delta_channel_decay=True, num_experts=8,
-                    num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64, router_score_fn="sigmoid",
-                    mlp_only_layers=[0]),
+    # KDA layers with a latent-attention layer every 4th, on the generic hybrid decoder: the carrier of the tensor-parallel
+    # cuts of these mixers (the faithful Kimi decoder is models/kimi_k3.py and, like the reference's, declares no TP plan)
+    "hybrid_kda_mla": dict(model_type="hybrid_kda_mla", mixer_pattern=["kda", "kda", "kda", "mla"], delta_channel_decay=True, num_experts=8,
+                           num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64, router_score_fn="sigmoid",
+                           mlp_only_layers=[0]),
 }
 
 

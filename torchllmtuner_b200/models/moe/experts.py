@@ -111,8 +111,10 @@ class _CombineRows(torch.autograd.Function):
 
 class GroupedExperts(nn.Module):
     def __init__(self, num_experts: int, hidden: int, inter: int, dtype=None, device=None, implementation: str = "native",
-                 swiglu_limit: float | None = None):
+                 swiglu_limit: float | None = None, glu_fn=None):
         super().__init__()
+        # `glu_fn(gate, up) -> hidden` replaces silu(gate) * up (Kimi's bounded SituGLU); None keeps the fused kernel
+        self.glu_fn = glu_fn
         self.num_experts, self.hidden, self.inter, self.implementation = num_experts, hidden, inter, implementation
         # asymmetric clamp before the gated activation: gate <= limit, |up| <= limit
         # (reference: llmtuner/models/deepseek/deepseek_v4/modeling.py:164-169)
@@ -138,13 +140,15 @@ class GroupedExperts(nn.Module):
             for e in range(self.w1_EFD.shape[0]):
                 s, t = seg[e], seg[e + 1]
                 if t > s:
-                    h = ops.swiglu(*self._clamp(ops.linear(rows[s:t], self.w1_EFD[e]), ops.linear(rows[s:t], self.w3_EFD[e])))
+                    g_, u_ = self._clamp(ops.linear(rows[s:t], self.w1_EFD[e]), ops.linear(rows[s:t], self.w3_EFD[e]))
+                    h = ops.swiglu(g_, u_) if self.glu_fn is None else self.glu_fn(g_, u_)
                     out[s:t] = ops.linear(h, self.w2_EDF[e])
             return out
         g, u = self._clamp(grouped_linear(rows, self.w1_EFD, seg_offsets), grouped_linear(rows, self.w3_EFD, seg_offsets))
         # rows past the last segment of a statically sized receive buffer hold nothing: the kernels skip them
         limit = seg_offsets[-1:] if rows.is_cuda and seg_offsets.dtype == torch.int32 else None
-        return grouped_linear(ops.swiglu(g, u, limit), self.w2_EDF, seg_offsets)
+        h = ops.swiglu(g, u, limit) if self.glu_fn is None else self.glu_fn(g, u)
+        return grouped_linear(h, self.w2_EDF, seg_offsets)
 
 
 class LocalTokenDispatcher:

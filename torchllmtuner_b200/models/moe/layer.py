@@ -14,22 +14,27 @@ from .routing import HashRouter, QuantileBalancedTopKRouter, TokenChoiceTopKRout
 
 
 class MoE(nn.Module):
+    always_bias = False     # True: the selection bias is applied even when it is not being updated (loaded from a checkpoint)
+
     def __init__(self, hidden: int, num_experts: int, top_k: int, moe_inter: int, *, shared_inter: int = 0,
                  score_fn: str = "softmax", norm_topk_prob: bool = True, route_scale: float = 1.0,
                  bias_update_coeff: float = 0.0, aux_loss_coef: float = 0.0, quantile_balancing: bool = False,
                  fixed_router: bool = False, experts_implementation: str = "native", dtype=None, device=None,
-                 shared_mlp_factory=None, swiglu_limit: float | None = None, hash_vocab_size: int = 0):
+                 shared_mlp_factory=None, swiglu_limit: float | None = None, hash_vocab_size: int = 0, num_groups: int = 1,
+                 topk_groups: int = 1, expert_width: int | None = None, glu_fn=None):
         super().__init__()
         if hash_vocab_size:
             self.router = HashRouter(hidden, num_experts, top_k, hash_vocab_size, score_fn, norm_topk_prob, route_scale, dtype=dtype,
                                      device=device)
         else:
             rcls = QuantileBalancedTopKRouter if quantile_balancing else TokenChoiceTopKRouter
+            kw = {} if quantile_balancing else dict(num_groups=num_groups, topk_groups=topk_groups)
             self.router = rcls(hidden, num_experts, top_k, score_fn, norm_topk_prob, route_scale, fixed=fixed_router, dtype=dtype,
-                               device=device)
+                               device=device, **kw)
         self.hash_routed = bool(hash_vocab_size)
-        self.routed = RoutedExperts(GroupedExperts(num_experts, hidden, moe_inter, dtype=dtype, device=device,
-                                                   implementation=experts_implementation, swiglu_limit=swiglu_limit))
+        # `expert_width`: the experts work in a narrower latent space; the block projects into and out of it
+        self.routed = RoutedExperts(GroupedExperts(num_experts, expert_width or hidden, moe_inter, dtype=dtype, device=device,
+                                                   implementation=experts_implementation, swiglu_limit=swiglu_limit, glu_fn=glu_fn))
         self.shared_experts = shared_mlp_factory(shared_inter) if (shared_inter and shared_mlp_factory) else None
         self.num_experts, self.top_k = num_experts, top_k
         self.bias_update_coeff, self.aux_loss_coef = bias_update_coeff, aux_loss_coef
@@ -50,17 +55,24 @@ class MoE(nn.Module):
     def forward(self, x: torch.Tensor, token_ids: torch.Tensor | None = None) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
-        bias = self.expert_bias_E if self.bias_update_coeff > 0 else None
+        bias = self.expert_bias_E if (self.bias_update_coeff > 0 or self.always_bias) else None
         w, idx, counts, scores = self.router(x2, bias, token_ids=token_ids) if self.hash_routed else self.router(x2, bias)
         if self.training and torch.is_grad_enabled():
             with torch.no_grad():
                 self.tokens_per_expert_E.add_(counts)
         if self.aux_loss_coef > 0 and self.training:
             self.aux_loss = self.aux_loss_coef * self.balance_loss_sum(counts, scores)
-        out = self.routed(x2, w, idx)
+        out = self.routed_output(self.routed(self.routed_input(x2), w, idx))
         if self.shared_experts is not None:
             out = out + self.shared_experts(x2)
         return out.reshape(shape)
+
+    def routed_input(self, x2: torch.Tensor) -> torch.Tensor:
+        """What the routed experts consume; the router and the shared expert always see the block's input."""
+        return x2
+
+    def routed_output(self, y: torch.Tensor) -> torch.Tensor:
+        return y
 
     def balance_loss_sum(self, counts: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
         """Micro-batch load-balance loss in its token-sum form, T * L_bal (reference:

@@ -88,8 +88,12 @@ def _ensure_builtins() -> None:
         state_format="qwen3", description="Qwen3-8B architecture")
     reg("qwen3_30b_a3b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_30B_A3B, **(mc.arch_overrides or {}), **kw}),
         state_format="qwen3", description="Qwen3-30B-A3B architecture")
-    from . import deepseek_v4, families
+    from . import deepseek_v4, families, kimi_k3
     families.register_all(reg)
+    reg("kimi_linear", kimi_k3.build_kimi(kimi_k3.KIMI_LINEAR_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "cp", "ac"},
+        description="Kimi-Linear decoder: KDA with short convolutions, latent attention without rotary, grouped sigmoid router")
+    reg("kimi_k3", kimi_k3.build_kimi(kimi_k3.KIMI_K3_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "cp", "ac"},
+        description="Kimi-K3 text decoder: Kimi-Linear plus attention residuals, SituGLU and latent-space experts")
     reg("deepseek_v4", deepseek_v4.build_deepseek_v4, state_format="deepseek_v4", supports={"fsdp", "ep", "ac"},
         description="DeepSeek-V4 decoder: hyper-connections, shared-KV sliding/compressed attention with an indexer, hash and "
                     "biased top-k routers")

@@ -142,7 +142,58 @@ class DeepseekV4StateFormat(Qwen3StateFormat):
         return cfg
 
 
-_FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat()}
+class KimiStateFormat(ModelStateFormat):
+    """Kimi checkpoints name the sparse block `block_sparse_moe` and keep one module per expert with projections `w1`
+    (gate), `w3` (up), `w2` (down); the reference's own module tree is the same, so its distributed checkpoints use these
+    names too (reference: llmtuner/models/kimi/kimi_k3/model.py:102-110, mlp.py:47-61, checkpoint.py:27-342)."""
+    name = "kimi"
+    _EXP = re.compile(r"^(model\.layers\.\d+)\.mlp\.routed\.experts\.(w1_EFD|w3_EFD|w2_EDF)$")
+    _SPARSE = re.compile(r"^(model\.layers\.\d+)\.mlp\.(router\.gate\.weight|shared_experts\..+|routed_expert_(?:down_proj|up_proj|norm)\.weight)$")
+    _PROJ = {"w1_EFD": "w1", "w3_EFD": "w3", "w2_EDF": "w2"}
+    BUFFER_RENAMES = {"mlp.expert_bias_E": "block_sparse_moe.gate.e_score_correction_bias"}
+
+    def to_hf(self, fqn, shape):
+        m = self._EXP.match(fqn)
+        if m:
+            per = shape[1] * shape[2]
+            return [HFPiece(f"{m.group(1)}.block_sparse_moe.experts.{e}.{self._PROJ[m.group(2)]}.weight", e * per, (e + 1) * per)
+                    for e in range(shape[0])]
+        m = self._SPARSE.match(fqn)
+        n = 1
+        for x in shape:
+            n *= x
+        if m:
+            tail = "gate.weight" if m.group(2) == "router.gate.weight" else m.group(2)
+            return [HFPiece(f"{m.group(1)}.block_sparse_moe.{tail}", 0, n)]
+        return [HFPiece(fqn, 0, n)]
+
+    def to_reference(self, fqn, shape):
+        m = self._EXP.match(fqn)
+        if m:
+            per = shape[1] * shape[2]
+            return [RefPiece(p.hf_name, tuple(shape[1:]), 0, p.native_flat_lo, per) for p in self.to_hf(fqn, shape)]
+        p = self.to_hf(fqn, shape)[0]
+        return [RefPiece(p.hf_name, tuple(shape), 0, 0, p.native_flat_hi)]
+
+    def hf_config(self, arch) -> dict:
+        keep = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads",
+                "rms_norm_eps", "q_lora_rank", "kv_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim", "mla_use_output_gate",
+                "first_k_dense_replace", "moe_layer_freq", "num_experts", "num_shared_experts", "num_expert_group", "topk_group",
+                "moe_renormalize", "routed_scaling_factor", "moe_router_activation_func", "moe_intermediate_size",
+                "routed_expert_hidden_size", "latent_moe_use_norm", "hidden_act", "activation_situ_beta", "activation_situ_linear_beta",
+                "attn_res_block_size", "tie_word_embeddings")
+        cfg = {k: getattr(arch, k) for k in keep}
+        n = arch.num_hidden_layers
+        cfg.update(architectures=["KimiLinearForCausalLM"], model_type="kimi_linear", num_experts_per_token=arch.num_experts_per_tok,
+                   mla_use_nope=True, torch_dtype="bfloat16",
+                   linear_attn_config={"kda_layers": list(arch.kda_layers), "full_attn_layers": [i + 1 for i in range(n) if (i + 1) not in arch.kda_layers],
+                                       "num_heads": arch.linear_heads, "head_dim": arch.linear_head_dim,
+                                       "short_conv_kernel_size": arch.short_conv_kernel_size, "use_full_rank_gate": arch.use_full_rank_gate,
+                                       "gate_lower_bound": arch.gate_lower_bound})
+        return cfg
+
+
+_FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat(), "kimi": KimiStateFormat()}
 
 
 def get_state_format(name: str) -> ModelStateFormat:

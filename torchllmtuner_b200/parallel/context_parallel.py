@@ -172,6 +172,25 @@ class ContextParallelDriver:
 
 
     # ------------------------------------------------------------------ delta rule (recurrent state across ranks)
+    def prev_rows(self, x: torch.Tensor, n: int) -> torch.Tensor:
+        """x [B*t, C]: this rank's contiguous span of each of the B sequences. Returns [B, n, C]: the last n rows of the
+        span before it (zeros on the first rank): the history a causal convolution of width n + 1 needs at the left
+        edge (reference: llmtuner/models/kimi/kimi_k3/delta_attention.py:237-262 hands the same rows to its convolution
+        kernel through the context-parallel context). Every rank keeps the gather in its graph."""
+        from ..errors import UnsupportedCombinationError
+        if self.strategy != "kv_allgather" or self.load_balancer is not None:
+            raise UnsupportedCombinationError("convolution history needs contiguous sequence spans: use context_parallel_kcp_size or "
+                                              "context_parallel_kv_allgather_size without a load balancer")
+        B = self._mb["B"]
+        t = x.shape[0] // B
+        if t < n:
+            raise UnsupportedCombinationError(f"a local span of {t} rows is shorter than the convolution history of {n}")
+        tail = x.view(B, t, -1)[:, t - n:].contiguous().unsqueeze(0)
+        every = _AllGatherRowsCP.apply(tail, self.group, None)                # [R, B, n, C]
+        if self.rank == 0:
+            return every[0] * 0.0
+        return every[self.rank - 1] + 0.0 * every[self.rank].sum()
+
     def delta_rule(self, q, k, v, beta, log_decay, chunk: int):
         """Sequence-parallel gated delta rule (reference: llmtuner/parallel/context_parallel/kcp.py:30-335). Every rank
         owns one contiguous span of each sequence. The recurrence is linear in the state, and its value columns evolve

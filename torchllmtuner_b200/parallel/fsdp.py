@@ -202,7 +202,9 @@ class FSDPRuntime:
         full buffer, unit by unit, so the peak is one unit."""
         use_main = self.is_cuda and self.param_dtype == torch.bfloat16
         for u in self.units:
-            persistent = u.world == 1 or not self.reshard_after_forward or u.name in ("embedding", "root", "head")
+            # units that no decoder block owns (embedding, head, leftovers such as a stream-collapsing head) are not part of
+            # the per-block gather schedule: their full copy stays resident and is refreshed after every optimizer step
+            persistent = u.world == 1 or not self.reshard_after_forward or getattr(u, "block_index", None) is None
             if u.world == 1:
                 full = u.shard_lowp
             elif persistent:
