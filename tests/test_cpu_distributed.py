@@ -179,8 +179,8 @@ def test_dist_muon_two_ranks_match_single_rank():
     _close(ref["loss"], got["loss"], 2e-3)
 
 
-@pytest.mark.parametrize("family,flat", [("kimi_linear", dict(context_parallel_kcp_size=2)), ("hybrid_kda_mla", dict(context_parallel_kcp_size=2)),
-                                         ("qwen3_5", dict(context_parallel_kv_allgather_size=2))])
+@pytest.mark.parametrize("family,flat", [("hybrid_kda_mla", dict(context_parallel_kcp_size=2)),
+                                         ("hybrid_gdn", dict(context_parallel_kv_allgather_size=2))])
 def test_delta_attention_families_under_sequence_parallelism(family, flat):
     """Delta-rule layers hand their recurrent state from rank to rank; the softmax / latent attention layers of the same
     model gather keys and values over the same axis."""
@@ -192,7 +192,7 @@ def test_delta_attention_families_under_sequence_parallelism(family, flat):
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
 
 
-@pytest.mark.parametrize("family", ["qwen3_5", "hybrid_kda_mla"])
+@pytest.mark.parametrize("family", ["hybrid_gdn", "hybrid_kda_mla"])
 def test_hybrid_families_under_tensor_parallelism(family):
     """Every mixer names its own cut (delta rule: all projections by heads; latent attention: per-head projections cut,
     latent down-projection and rotary key whole; gated attention: q/k/v/gate by heads)."""

@@ -94,7 +94,7 @@ def test_registry_lists_every_family():
     from torchllmtuner_b200.models import registered_models
     have = set(registered_models())
     assert {"qwen3", "qwen3_moe", "qwen3_8b", "qwen3_30b_a3b", "qwen3_5", "qwen3_5_moe", "qwen3_5_moe_text", "deepseek_v4",
-            "kimi_linear", "kimi_k3", "hybrid_kda_mla"} <= have
+            "kimi_linear", "kimi_k3", "hybrid_kda_mla", "hybrid_gdn", "hybrid_gdn_moe"} <= have
 
 
 def test_fsdp_cpu_offload_keeps_moments_on_the_host_and_trains():

@@ -134,8 +134,8 @@ HYBRID = dict(head_dim=64, delta_heads=4, delta_head_dim=64, kv_lora_rank=64, qk
 
 
 @pytest.mark.parametrize("name,flat", [
-    ("kimi_kcp2", dict(model_name_or_path="kimi_linear", context_parallel_kcp_size=2, data_parallel_shard_size=1)),
-    ("qwen3_5_tp2", dict(model_name_or_path="qwen3_5", tensor_parallel_size=2, data_parallel_shard_size=1)),
+    ("kda_mla_kcp2", dict(model_name_or_path="hybrid_kda_mla", context_parallel_kcp_size=2, data_parallel_shard_size=1)),
+    ("gdn_tp2", dict(model_name_or_path="hybrid_gdn", tensor_parallel_size=2, data_parallel_shard_size=1)),
     ("kda_mla_tp2", dict(model_name_or_path="hybrid_kda_mla", tensor_parallel_size=2, data_parallel_shard_size=1)),
 ])
 def test_hybrid_families_sequence_and_tensor_parallel_on_gpus(name, flat):

@@ -54,7 +54,7 @@ def test_vision_language_wrapper_runs_forward_and_backward():
     check_status("vision-language wrapper")
 
 
-@pytest.mark.parametrize("family", ["qwen3_5", "kimi_linear", "deepseek_v4"])
+@pytest.mark.parametrize("family", ["qwen3_5", "kimi_linear", "kimi_k3", "deepseek_v4", "hybrid_gdn", "hybrid_kda_mla"])
 def test_delta_attention_and_latent_attention_families_train(family):
     from torchllmtuner_b200 import LLMTunerConfig, Trainer
     cfg = LLMTunerConfig()

@@ -77,22 +77,23 @@ def load_hf_checkpoint(trainer, path: str) -> None:
     with torch.no_grad():
         for fqn, tag, glo, ghi, u, slo in iter_pieces(trainer.asm.fsdp):
             p, s = pidx[fqn]
+            full_shape = _full_shape(p, s)
+            pieces = fmt.hf_pieces(fqn, full_shape)
             if tag:
                 # a row-parallel weight (cut on dimension 1): this rank's flat range maps to scattered positions of the
                 # full tensor, which is stored whole under one HF name
-                full_shape = _full_shape(p, s)
-                pieces = fmt.to_hf(fqn, full_shape)
                 if len(full_shape) != 2 or len(pieces) != 1:
                     raise ConfigError(f"HF import of {fqn}: only 2-D tensors may be cut along dimension 1")
                 pos = _global_positions(tag, glo, ghi, full_shape[1])
-                src = tensor(pieces[0].hf_name).reshape(-1)
-                u.master[slo: slo + (ghi - glo)].copy_(src[pos - pieces[0].native_flat_lo].float())
+                src = tensor(pieces[0].name).reshape(-1)
+                u.master[slo: slo + (ghi - glo)].copy_(src[pos - pieces[0].native_lo + pieces[0].ref_lo].float())
                 continue
-            for piece in fmt.to_hf(fqn, _full_shape(p, s)):
-                a, b = max(glo, piece.native_flat_lo), min(ghi, piece.native_flat_hi)
+            for piece in pieces:
+                a, b = max(glo, piece.native_lo), min(ghi, piece.native_lo + piece.n)
                 if b <= a:
                     continue
-                src = tensor(piece.hf_name).reshape(-1)[a - piece.native_flat_lo:b - piece.native_flat_lo]
+                off = piece.ref_lo - piece.native_lo
+                src = tensor(piece.name).reshape(-1)[a + off:b + off]
                 u.master[slo + (a - glo): slo + (b - glo)].copy_(src.float())
         for u in trainer.asm.fsdp.units:
             if u.separate_master:
@@ -123,6 +124,7 @@ def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", ma
     if rank == 0:
         os.makedirs(stage, exist_ok=True)
     shard, shard_bytes, shard_files, weight_map = {}, 0, [], {}
+    partial: dict[str, tuple] = {}
 
     def flush():
         nonlocal shard, shard_bytes
@@ -157,16 +159,31 @@ def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", ma
                 seen += hi - lo
         if seen < numel:
             raise ConfigError(f"export of {fqn}: gathered {seen} of {numel} elements")
-        for piece in fmt.to_hf(fqn, shape):
-            t = full[piece.native_flat_lo:piece.native_flat_hi].to(dt)
-            pshape = shape[1:] if len(fmt.to_hf(fqn, shape)) > 1 else shape
-            t = t.view(*pshape).contiguous()
+        for piece in fmt.hf_pieces(fqn, shape):
+            numel_hf = 1
+            for x in piece.shape:
+                numel_hf *= x
+            if piece.n == numel_hf:
+                t = full[piece.native_lo:piece.native_lo + piece.n].to(dt).view(*piece.shape).contiguous()
+            else:                        # an HF tensor filled from several native tensors: hold it until it is complete
+                buf, filled = partial.get(piece.name, (None, 0))
+                if buf is None:
+                    buf = torch.zeros(numel_hf, dtype=dt)
+                buf[piece.ref_lo:piece.ref_lo + piece.n] = full[piece.native_lo:piece.native_lo + piece.n].to(dt)
+                filled += piece.n
+                if filled < numel_hf:
+                    partial[piece.name] = (buf, filled)
+                    continue
+                partial.pop(piece.name, None)
+                t = buf.view(*piece.shape)
             nbytes = t.numel() * t.element_size()
             if shard_bytes + nbytes > max_shard_bytes:
                 flush()
-            shard[piece.hf_name] = t
+            shard[piece.name] = t
             shard_bytes += nbytes
     if rank == 0:
+        if partial:
+            raise ConfigError(f"HF export: tensors left incomplete: {sorted(partial)[:5]}")
         flush()
         total = len(shard_files)
         for i, (name, keys) in enumerate(shard_files):

@@ -2,8 +2,9 @@
 (reference: llmtuner/models/qwen/qwen3_5*, llmtuner/models/deepseek/deepseek_v4/*, llmtuner/models/kimi/kimi_k3/*).
 
 They share one hybrid decoder: every layer has a token mixer and an MLP (dense or the shared MoE block).
-  qwen3_5 / qwen3_5_moe / qwen3_5_moe_text   3 of 4 layers use a gated delta-net linear attention, every 4th layer a
+  hybrid_gdn / hybrid_gdn_moe                3 of 4 layers use a gated delta-net linear attention, every 4th layer a
                                              softmax attention with an output gate; gated RMSNorm on the mixer output
+(Qwen3.5 has its own module, `models/qwen3_5.py`.)
   hybrid_kda_mla                             KDA (delta rule with per-channel decay) layers with an MLA (latent
                                              attention) layer every 4th; sigmoid router with shared experts
 (Kimi-Linear / Kimi-K3 have their own module, `models/kimi_k3.py`.)
@@ -317,11 +318,11 @@ def _builder(defaults: dict):
 
 
 FAMILIES = {
-    "qwen3_5": dict(model_type="qwen3_5", mixer_pattern=["delta", "delta", "delta", "attention"]),
-    "qwen3_5_moe": dict(model_type="qwen3_5_moe", mixer_pattern=["delta", "delta", "delta", "attention"], num_experts=8,
-                        num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64),
-    "qwen3_5_moe_text": dict(model_type="qwen3_5_moe_text", mixer_pattern=["delta", "delta", "delta", "attention"], num_experts=8,
-                             num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64),
+    # gated delta-net layers with a gated softmax attention every 4th, on the generic hybrid decoder: the carrier of the
+    # tensor-parallel cuts of these mixers (the faithful Qwen3.5 decoder is models/qwen3_5.py)
+    "hybrid_gdn": dict(model_type="hybrid_gdn", mixer_pattern=["delta", "delta", "delta", "attention"]),
+    "hybrid_gdn_moe": dict(model_type="hybrid_gdn_moe", mixer_pattern=["delta", "delta", "delta", "attention"], num_experts=8,
+                           num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64),
     # KDA layers with a latent-attention layer every 4th, on the generic hybrid decoder: the carrier of the tensor-parallel
     # cuts of these mixers (the faithful Kimi decoder is models/kimi_k3.py and, like the reference's, declares no TP plan)
     "hybrid_kda_mla": dict(model_type="hybrid_kda_mla", mixer_pattern=["kda", "kda", "kda", "mla"], delta_channel_decay=True, num_experts=8,

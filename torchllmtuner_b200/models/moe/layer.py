@@ -21,7 +21,7 @@ class MoE(nn.Module):
                  bias_update_coeff: float = 0.0, aux_loss_coef: float = 0.0, quantile_balancing: bool = False,
                  fixed_router: bool = False, experts_implementation: str = "native", dtype=None, device=None,
                  shared_mlp_factory=None, swiglu_limit: float | None = None, hash_vocab_size: int = 0, num_groups: int = 1,
-                 topk_groups: int = 1, expert_width: int | None = None, glu_fn=None):
+                 topk_groups: int = 1, expert_width: int | None = None, glu_fn=None, shared_gate: bool = False):
         super().__init__()
         if hash_vocab_size:
             self.router = HashRouter(hidden, num_experts, top_k, hash_vocab_size, score_fn, norm_topk_prob, route_scale, dtype=dtype,
@@ -36,6 +36,11 @@ class MoE(nn.Module):
         self.routed = RoutedExperts(GroupedExperts(num_experts, expert_width or hidden, moe_inter, dtype=dtype, device=device,
                                                    implementation=experts_implementation, swiglu_limit=swiglu_limit, glu_fn=glu_fn))
         self.shared_experts = shared_mlp_factory(shared_inter) if (shared_inter and shared_mlp_factory) else None
+        # Qwen3.5: the shared expert's output is scaled per token by sigmoid(w_g . x)
+        self.shared_expert_gate = None
+        if shared_gate and self.shared_experts is not None:
+            from ..common import Linear
+            self.shared_expert_gate = Linear(hidden, 1, dtype, device)
         self.num_experts, self.top_k = num_experts, top_k
         self.bias_update_coeff, self.aux_loss_coef = bias_update_coeff, aux_loss_coef
         self.register_buffer("expert_bias_E", torch.zeros(num_experts, dtype=torch.float32, device=device), persistent=True)
@@ -64,7 +69,10 @@ class MoE(nn.Module):
             self.aux_loss = self.aux_loss_coef * self.balance_loss_sum(counts, scores)
         out = self.routed_output(self.routed(self.routed_input(x2), w, idx))
         if self.shared_experts is not None:
-            out = out + self.shared_experts(x2)
+            sh = self.shared_experts(x2)
+            if self.shared_expert_gate is not None:
+                sh = sh * torch.sigmoid(self.shared_expert_gate(x2))
+            out = out + sh
         return out.reshape(shape)
 
     def routed_input(self, x2: torch.Tensor) -> torch.Tensor:

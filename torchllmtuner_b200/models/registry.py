@@ -88,8 +88,11 @@ def _ensure_builtins() -> None:
         state_format="qwen3", description="Qwen3-8B architecture")
     reg("qwen3_30b_a3b", lambda mc, dtype=None, device=None, **kw: qwen3.build_qwen3(mc, dtype, device, **{**qwen3.QWEN3_30B_A3B, **(mc.arch_overrides or {}), **kw}),
         state_format="qwen3", description="Qwen3-30B-A3B architecture")
-    from . import deepseek_v4, families, kimi_k3
+    from . import deepseek_v4, families, kimi_k3, qwen3_5
     families.register_all(reg)
+    for name, defaults in (("qwen3_5", qwen3_5.QWEN3_5_DENSE), ("qwen3_5_moe", qwen3_5.QWEN3_5_MOE), ("qwen3_5_moe_text", qwen3_5.QWEN3_5_MOE)):
+        reg(name, qwen3_5.build_qwen3_5(defaults), state_format="qwen3_5", supports={"fsdp", "ep", "cp", "ac"},
+            description="Qwen3.5 text decoder: gated delta-net layers with a gated full attention every 4th, zero-centred norms")
     reg("kimi_linear", kimi_k3.build_kimi(kimi_k3.KIMI_LINEAR_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "cp", "ac"},
         description="Kimi-Linear decoder: KDA with short convolutions, latent attention without rotary, grouped sigmoid router")
     reg("kimi_k3", kimi_k3.build_kimi(kimi_k3.KIMI_K3_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "cp", "ac"},

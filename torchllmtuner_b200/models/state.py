@@ -45,6 +45,14 @@ class ModelStateFormat:
             n *= s
         return [HFPiece(fqn, 0, n)]
 
+    def hf_pieces(self, fqn: str, shape) -> list[RefPiece]:
+        """The general form of `to_hf`, used by the safetensors import / export: several native tensors may fill one HF
+        tensor (packed gate/up experts). The default restates `to_hf`: one HF tensor per piece, and when a native tensor
+        splits into several (per-expert files) each takes the native shape without its leading dimension."""
+        pieces = self.to_hf(fqn, shape)
+        pshape = tuple(shape[1:]) if len(pieces) > 1 else tuple(shape)
+        return [RefPiece(p.hf_name, pshape, 0, p.native_flat_lo, p.native_flat_hi - p.native_flat_lo) for p in pieces]
+
     def hf_config(self, arch) -> dict:
         return dict(vars(arch))
 
@@ -142,6 +150,58 @@ class DeepseekV4StateFormat(Qwen3StateFormat):
         return cfg
 
 
+class Qwen35StateFormat(ModelStateFormat):
+    """Qwen3.5: the delta-net mixer is `linear_attn` in published files, the router `mlp.gate`, the shared expert
+    `mlp.shared_expert`, experts packed as `mlp.experts.gate_up_proj` (E, 2F, D: gate rows then up rows of each expert) and
+    `mlp.experts.down_proj` (reference: llmtuner/models/qwen/qwen3_5_moe/model.py:217-275, gated_delta.py:34-72)."""
+    name = "qwen3_5"
+    _LINEAR = re.compile(r"^(model\.layers\.\d+)\.self_attn\.((?:in_proj_(?:qkv|z|b|a)|conv1d|norm|out_proj)\.weight|dt_bias|A_log)$")
+    _EXP = re.compile(r"^(model\.layers\.\d+\.mlp)\.routed\.experts\.(w1_EFD|w3_EFD|w2_EDF)$")
+    _ROUTER = re.compile(r"^(model\.layers\.\d+\.mlp)\.router\.gate\.weight$")
+    _SHARED = re.compile(r"^(model\.layers\.\d+\.mlp)\.shared_experts\.(.+)$")
+
+    def hf_pieces(self, fqn, shape):
+        n = 1
+        for x in shape:
+            n *= x
+        m = self._EXP.match(fqn)
+        if m:
+            E, a, b = shape
+            if m.group(2) == "w2_EDF":
+                return [RefPiece(f"{m.group(1)}.experts.down_proj", (E, a, b), 0, 0, n)]
+            half = a * b
+            off = 0 if m.group(2) == "w1_EFD" else half
+            return [RefPiece(f"{m.group(1)}.experts.gate_up_proj", (E, 2 * a, b), e * 2 * half + off, e * half, half) for e in range(E)]
+        for rx, fmt in ((self._LINEAR, "{0}.linear_attn.{1}"), (self._ROUTER, "{0}.gate.weight"), (self._SHARED, "{0}.shared_expert.{1}")):
+            m = rx.match(fqn)
+            if m:
+                return [RefPiece(fmt.format(*m.groups()), tuple(shape), 0, 0, n)]
+        return [RefPiece(fqn, tuple(shape), 0, 0, n)]
+
+    to_reference = hf_pieces
+
+    def to_hf(self, fqn, shape):
+        if self._EXP.match(fqn) and not fqn.endswith("w2_EDF"):
+            raise NotImplementedError("packed gate/up experts: use hf_pieces")
+        return [HFPiece(p.name, p.native_lo, p.native_lo + p.n) for p in self.hf_pieces(fqn, shape)]
+
+    def hf_config(self, arch) -> dict:
+        moe = arch.num_experts > 0
+        keep = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim",
+                "rms_norm_eps", "layer_types", "full_attention_interval", "linear_num_value_heads", "linear_num_key_heads",
+                "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel_dim", "attn_output_gate", "tie_word_embeddings",
+                "max_position_embeddings")
+        cfg = {k: getattr(arch, k) for k in keep}
+        cfg.update(architectures=["Qwen3_5MoeForCausalLM" if moe else "Qwen3_5ForCausalLM"], model_type="qwen3_5_moe_text" if moe else "qwen3_5_text",
+                   hidden_act="silu", torch_dtype="bfloat16",
+                   rope_parameters={"rope_type": "default", "rope_theta": arch.rope_theta, "partial_rotary_factor": arch.partial_rotary_factor,
+                                    "mrope_section": list(arch.mrope_section), "mrope_interleaved": True})
+        if moe:
+            cfg.update(num_experts=arch.num_experts, num_experts_per_tok=arch.num_experts_per_tok, moe_intermediate_size=arch.moe_intermediate_size,
+                       shared_expert_intermediate_size=arch.shared_expert_intermediate_size, norm_topk_prob=arch.norm_topk_prob)
+        return cfg
+
+
 class KimiStateFormat(ModelStateFormat):
     """Kimi checkpoints name the sparse block `block_sparse_moe` and keep one module per expert with projections `w1`
     (gate), `w3` (up), `w2` (down); the reference's own module tree is the same, so its distributed checkpoints use these
@@ -193,7 +253,8 @@ class KimiStateFormat(ModelStateFormat):
         return cfg
 
 
-_FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat(), "kimi": KimiStateFormat()}
+_FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat(), "kimi": KimiStateFormat(),
+            "qwen3_5": Qwen35StateFormat()}
 
 
 def get_state_format(name: str) -> ModelStateFormat:

@@ -26,7 +26,7 @@ ENTRIES = (
      "tensor_parallel_size must divide the query and key/value head counts"),
     ("ulysses_divides_heads", lambda c: c.topo.cp_ulysses > 1 and ((c.model_config.num_key_value_heads // max(1, c.topo.tp)) % c.topo.cp_ulysses),
      "ulysses degree must divide the per-rank key/value head count"),
-    ("kcp_needs_delta_attention", lambda c: c.topo.kcp > 1 and getattr(c.model_config, "model_type", "") not in ("kimi_linear", "kimi_k3"),
+    ("kcp_needs_delta_attention", lambda c: c.topo.kcp > 1 and getattr(c.model_config, "model_type", "") not in ("kimi_linear", "kimi_k3", "hybrid_kda_mla"),
      "context_parallel_kcp_size > 1 is defined for delta-attention models only"),
     ("ptrr_backstop", lambda c: c.config.parallel.cp_config.context_parallel_load_balancer == "ptrr", "ptrr load balancing is not supported"),
     ("headtail_needs_kv_allgather", lambda c: c.config.parallel.cp_config.context_parallel_load_balancer == "headtail" and c.topo.cp_ulysses > 1 and c.topo.cp_kv == 1,
