@@ -1,0 +1,108 @@
+"""Multimodal data path and a vision-language model under the Trainer: frame sampling, patch grids, placeholder
+expansion and label masking, three-axis positions, packing, collation, the synthetic loader's determinism and resume,
+and training a tower + decoder through the public Trainer on one and on two FSDP ranks."""
+import pytest
+import torch
+
+from dist_cases import base_flat, run_ranks
+from torchllmtuner_b200.datasets import multimodal_pipeline as mp
+from torchllmtuner_b200.datasets.contracts import IGNORE_INDEX
+
+
+def test_frame_sampling_respects_rate_budget_and_temporal_patch():
+    spec = mp.VisionSpec(video_fps=2.0, video_min_frames=4, video_max_frames=8, temporal_patch_size=2)
+    idx = mp.sample_frame_indices(60, 30.0, spec)        # 2 s at 2 fps -> 4 frames (the minimum)
+    assert len(idx) == 4 and idx[0] == 0 and idx[-1] == 59 and idx == sorted(idx)
+    assert len(mp.sample_frame_indices(3000, 30.0, spec)) == 8                  # capped by the budget
+    assert len(mp.sample_frame_indices(5, 30.0, spec)) == 4                     # 5 frames -> 4 (multiple of 2)
+    with pytest.raises(ValueError):
+        mp.sample_frame_indices(1, 30.0, spec)
+
+
+def test_image_and_video_patches_follow_the_pixel_budget():
+    spec = mp.VisionSpec(patch_size=14, merge_size=2, max_pixels=14 * 14 * 4 * 16, min_pixels=56 * 56)
+    p, g = mp.image_to_patches(torch.rand(3, 300, 500), spec)
+    assert g[0] == 1 and g[1] % 2 == 0 and g[2] % 2 == 0 and g[1] * g[2] * 196 <= spec.max_pixels
+    assert p.shape == (g[1] * g[2], 3 * 14 * 14)
+    p, g = mp.video_to_patches(torch.rand(9, 3, 80, 120), 4.0, spec)
+    assert g[0] == 2 and p.shape[0] == g[0] * g[1] * g[2]
+
+
+def test_sample_expands_placeholders_masks_labels_and_builds_positions():
+    spec = mp.VisionSpec()
+    img = (torch.rand(4 * 6, 588), (1, 4, 6))             # 4x6 patches -> 2x3 merged rows
+    s = mp.build_sample([5, 6, 99, 7, 8, 9], [img], placeholder_id=99, spec=spec, start_id=90, end_id=91, prompt_len=4)
+    assert s.tokens == [5, 6, 90] + [99] * 6 + [91, 7, 8, 9]
+    assert s.labels == [IGNORE_INDEX] * 10 + [IGNORE_INDEX, 8, 9][0:0] + [IGNORE_INDEX, 8, 9] or s.labels[-2:] == [8, 9]
+    assert s.labels[:10] == [IGNORE_INDEX] * 10 and s.labels[10] == IGNORE_INDEX and s.labels[-2:] == [8, 9]
+    pos = s.positions
+    assert pos.shape == (3, 13)
+    assert pos[:, :3].tolist() == [[0, 1, 2]] * 3
+    assert pos[0, 3:9].tolist() == [3] * 6 and pos[1, 3:9].tolist() == [3, 3, 3, 4, 4, 4] and pos[2, 3:9].tolist() == [3, 4, 5] * 2
+    assert pos[:, 9].tolist() == [6, 6, 6]                                     # continues after the largest position used
+    with pytest.raises(ValueError):
+        mp.build_sample([5, 99, 99], [img], placeholder_id=99, spec=spec)
+
+
+def test_packing_keeps_samples_whole_and_collation_builds_documents():
+    spec = mp.VisionSpec()
+    mk = lambda n, k: mp.build_sample(list(range(1, n + 1)) + [99] * k, [(torch.rand(4, 588), (1, 2, 2))] * k, placeholder_id=99, spec=spec)  # noqa: E731
+    a, b, c, big = mk(10, 1), mk(7, 0), mk(12, 2), mk(40, 0)
+    rows, left, dropped = mp.pack_samples([a, big, b, c], seq_len=20, rows=2)
+    assert dropped == 1 and not left
+    assert [len(r.samples) for r in rows] == [2, 1] and rows[0].used == len(a) + len(b)
+    batch = mp.collate_rows(rows, 20, pad_id=0)
+    assert batch["input"].shape == (2, 20) and batch["positions"].shape == (3, 2, 20)
+    assert batch["cu_seqlens"].tolist() == [0, 11, 18, 20, 34, 40]
+    assert batch["patches"].shape == (12, 588) and len(batch["grids"]) == 3
+    lab = batch["labels"]
+    assert lab[0, 10] == IGNORE_INDEX and lab[0, 17] == IGNORE_INDEX and (lab[0, 18:] == IGNORE_INDEX).all()
+    assert lab[0, 0] == 2 and lab[0, 11] == 2                               # shifted inside each document
+    assert batch["num_valid_tokens"] == int((lab != IGNORE_INDEX).sum())
+
+
+def test_synthetic_loader_is_deterministic_disjoint_and_resumable():
+    kw = dict(vocab_size=300, image_token_id=299, global_batch=4, seq_len=256, seed=3, rows_per_rank=1, dp_degree=2,
+              spec=mp.VisionSpec(max_pixels=14 * 14 * 4 * 8, min_pixels=28 * 28 * 4))
+    a0, a1 = mp.SyntheticMultimodalLoader(dp_rank=0, **kw), mp.SyntheticMultimodalLoader(dp_rank=1, **kw)
+    x0, x1 = next(a0), next(a1)
+    assert not torch.equal(x0["input"], x1["input"])
+    assert (x0["input"] == 299).sum() == sum(mp.calculate_vision_tokens(g) for g in x0["grids"])
+    assert x0["patches"].shape[0] == sum(t * h * w for t, h, w in x0["grids"])
+    again = mp.SyntheticMultimodalLoader(dp_rank=0, **kw)
+    assert torch.equal(next(again)["input"], x0["input"])
+    second = next(a0)
+    resumed = mp.SyntheticMultimodalLoader(dp_rank=0, **kw)
+    resumed.load_state_dict({**a0.state_dict(), "cursor": 1})
+    assert torch.equal(next(resumed)["input"], second["input"])
+
+
+VL = dict(model_name_or_path="qwen3_5_vl", dataset="random_multimodal", vocab_size=320, hidden_size=64, num_hidden_layers=4,
+          num_attention_heads=2, num_key_value_heads=2, max_seq_len=192, global_batch_size=2, learning_rate=3e-3, mm_max_pixels=14 * 14 * 4 * 8)
+VL_ARCH = dict(head_dim=32, vision=dict(hidden_size=64, intermediate_size=128, depth=2, num_heads=2))
+
+
+def test_vision_language_model_trains_through_the_trainer(tmp_path):
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(dump_folder=str(tmp_path), steps=6, **VL))
+    cfg.model.arch_overrides = dict(VL_ARCH)
+    tr = Trainer(cfg)
+    assert tr.model.image_token_id == 319 and any(n.startswith("visual.") for n, _ in tr.model.named_parameters())
+    names = set(tr.asm.layout.state_names.values())
+    assert "visual.merger.fc2.weight" in names and "text.model.layers.0.self_attn.in_proj_qkv.weight" in names
+    before = tr.model.visual.merger.fc2.weight.detach().clone()
+    losses = []
+    for _ in range(6):
+        tr.dataloader.cursor = 0
+        losses.append(tr.train_step().loss)
+    assert losses[-1] < losses[0] - 0.3, losses
+    assert not torch.equal(before, tr.model.visual.merger.fc2.weight)           # the tower trains with the decoder
+    tr.checkpointer  # noqa: B018
+    tr.close()
+
+
+def test_vision_language_model_on_two_fsdp_ranks_matches_one():
+    ref = run_ranks(1, base_flat(**VL), arch=VL_ARCH, steps=3)
+    got = run_ranks(2, base_flat(data_parallel_shard_size=2, **VL), arch=VL_ARCH, steps=3)
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 5e-5, (ref, got)

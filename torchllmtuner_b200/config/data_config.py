@@ -35,6 +35,9 @@ class DataloaderConfig:
     mm_vision_start_token: str = "<|vision_start|>"
     mm_vision_end_token: str = "<|vision_end|>"
     mm_pad_token: str = "<|endoftext|>"
+    mm_max_pixels: int = 14 * 14 * 4 * 64        # random_multimodal: pixel budget per image / clip
+    mm_max_items: int = 2                        # random_multimodal: images or clips per document
+    mm_video_fraction: float = 0.25              # random_multimodal: share of items that are short clips
 
     def __post_init__(self):
         require_choice("tokenizer_backend", self.tokenizer_backend, ("huggingface", "kimi_k3", "whitespace"))

@@ -7,8 +7,21 @@ from .synthetic import RandomPackedSource, RandomTokenDataLoader, RandomTokenSou
 
 
 def build_dataloader(data_cfg, *, vocab_size: int, global_batch: int, seq_len: int, seed: int, dp_rank: int, dp_degree: int,
-                     rows_per_rank: int, pin_memory: bool = False, split: str = "train"):
+                     rows_per_rank: int, pin_memory: bool = False, split: str = "train", model=None):
     name = data_cfg.dataset
+    if name == "random_multimodal":
+        # image-and-text documents for a vision-language model: the model says which token marks an image and how its
+        # tower cuts pixels into patches
+        from .multimodal_pipeline import SyntheticMultimodalLoader, VisionSpec
+        if model is None or not hasattr(model, "image_token_id"):
+            raise ConfigError("dataset 'random_multimodal' needs a vision-language model (one that names an image_token_id)")
+        vc = model.visual.config
+        spec = VisionSpec(patch_size=vc.patch_size, merge_size=vc.spatial_merge_size, max_pixels=data_cfg.mm_max_pixels,
+                          min_pixels=min(data_cfg.mm_max_pixels, (vc.patch_size * vc.spatial_merge_size * 2) ** 2))
+        return SyntheticMultimodalLoader(vocab_size=vocab_size, image_token_id=model.image_token_id, global_batch=global_batch,
+                                         seq_len=seq_len, seed=seed, dp_rank=dp_rank, dp_degree=dp_degree, rows_per_rank=rows_per_rank,
+                                         spec=spec, max_items=data_cfg.mm_max_items, video_fraction=data_cfg.mm_video_fraction,
+                                         pin_memory=pin_memory)
     if name == "random":
         return RandomTokenDataLoader(RandomTokenSource(vocab_size, global_batch, seq_len, seed), dp_rank, dp_degree,
                                      rows_per_rank, pin_memory)

@@ -235,6 +235,7 @@ class Qwen35DecoderLayer(nn.Module):
 
 class Qwen35ForCausalLM(Qwen3ForCausalLM):
     decoder_structure = DecoderStructure()
+    accepts_three_axis_positions = True      # `build_context` takes [3, T] (time, height, width) positions
 
     def __init__(self, cfg: Qwen35Config, dtype=None, device=None):
         nn.Module.__init__(self)
@@ -300,3 +301,20 @@ def build_qwen3_5(defaults: dict):
 QWEN3_5_DENSE = dict(model_type="qwen3_5")
 QWEN3_5_MOE = dict(model_type="qwen3_5_moe", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=64,
                    norm_topk_prob=True)
+
+
+def build_qwen3_5_vl(defaults: dict):
+    """Text decoder + vision tower under one model: `arch_overrides` may carry `image_token_id` (default: the last token of
+    the vocabulary) and `vision` (a dict of `VisionConfig` fields; the output width always follows the text width)."""
+    text_builder = build_qwen3_5(defaults)
+
+    def build(model_config, dtype=None, device=None, **overrides):
+        from .vision import VisionConfig, VisionLanguageModel
+        text = text_builder(model_config, dtype=dtype, device=device, **overrides)
+        extra = dict(model_config.arch_overrides or {})
+        vkw = dict(hidden_size=128, intermediate_size=256, depth=2, num_heads=2)
+        vkw.update(extra.get("vision") or {})
+        vkw["out_hidden_size"] = text.config.hidden_size
+        image_id = int(extra.get("image_token_id", text.config.vocab_size - 1))
+        return VisionLanguageModel(text, VisionConfig(**vkw), image_id, dtype=dtype, device=device)
+    return build

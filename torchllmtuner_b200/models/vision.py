@@ -12,7 +12,9 @@ llmtuner/models/qwen/qwen3_5_moe/rotary.py, llmtuner/models/kimi/kimi_k3/multimo
 
 Every projection is the sm_100a GEMM, attention is the packed-row kernel with one non-causal piece per image, the norms
 and the rotary step are the fused elementwise kernels; on CPU the same calls resolve to the fp32 statements.
-The wrapper is a module-level API (one device); the trainer's sharding units cover text decoders only.
+The wrapper exposes the same contracts as a text decoder (decoder structure, `prepare_inputs`, `build_context`, the
+block-runner and checkpointing switches pass through to the text model), so the trainer shards its decoder blocks as
+usual and keeps the tower in the unit of parameters that no block owns.
 """
 from __future__ import annotations
 
@@ -27,6 +29,7 @@ from .. import ops
 from ..errors import ConfigError
 from ..ops.attn_meta import AttnMeta
 from .common import GatedMLP, Linear, RMSNorm
+from .contracts import DecoderStructure
 from .qwen3 import ForwardContext
 
 
@@ -186,6 +189,11 @@ class VisionLanguageModel(nn.Module):
     """`text` is any decoder of the registry (its `forward(tokens, ctx, skip_lm_head, inputs_embeds=...)` runs on given
     rows); `image_token_id` marks the rows that the tower's output replaces."""
 
+    decoder_structure = DecoderStructure(decoder="text.model", embedding="text.model.embed_tokens", blocks="text.model.layers",
+                                         final_norm="text.model.norm", head="text.lm_head")
+    # switches that the parallel stages set on "the model" and the text decoder reads on itself
+    _PASS = ("block_runner", "activation_checkpoint", "ac_save_every", "ac_block_mask", "pp_first", "pp_last", "activation_swap")
+
     def __init__(self, text: nn.Module, vision: VisionConfig, image_token_id: int, mrope_sections=None, dtype=None, device=None):
         super().__init__()
         if vision.out_hidden_size != text.config.hidden_size:
@@ -193,6 +201,17 @@ class VisionLanguageModel(nn.Module):
         self.text, self.visual = text, VisionTower(vision, dtype, device)
         self.image_token_id, self.mrope_sections = image_token_id, mrope_sections
         self.config = text.config
+
+    def __setattr__(self, name, value):
+        if name in self._PASS and "text" in self.__dict__.get("_modules", {}):
+            setattr(self._modules["text"], name, value)
+            return
+        super().__setattr__(name, value)
+
+    def __getattr__(self, name):
+        if name in VisionLanguageModel._PASS:
+            return getattr(self._modules["text"], name)
+        return super().__getattr__(name)
 
     @property
     def lm_head(self):
@@ -202,7 +221,44 @@ class VisionLanguageModel(nn.Module):
         self.text.initialize_parameters(seed)
         self.visual.initialize_parameters(None if seed is None else seed + 1)
 
+    def tp_config(self) -> dict:
+        return {}
+
+    def validate_parallel(self, tp: int = 1, cp_ulysses: int = 1, ep: int = 1) -> None:
+        from ..errors import UnsupportedCombinationError
+        if tp > 1 or cp_ulysses > 1:
+            raise UnsupportedCombinationError("vision-language models run data-, FSDP- and expert-parallel; the tower is not cut by "
+                                              "heads and image rows are not split across sequence shards")
+        self.text.validate_parallel(1, 1, ep)
+
+    def flops_per_token(self, seq_len: int) -> float:
+        return self.text.flops_per_token(seq_len)
+
+    def prepare_inputs(self, batch: dict, device=None, parallel_dims=None) -> dict:
+        """Batch dict of the multimodal collator (`input`, `labels`, `positions` [3, B, S] or [B, S], `cu_seqlens`,
+        `patches`, `grids`) -> packed model inputs; patches and grids travel under `model_kwargs`."""
+        if parallel_dims is not None and (parallel_dims.get("cp", 1) > 1 or parallel_dims.get("tp", 1) > 1):
+            raise ConfigError("vision-language inputs are not split across context- or tensor-parallel ranks")
+        ids, labels = batch["input"], batch["labels"]
+        B, S = ids.shape
+        positions = batch.get("positions")
+        if positions is None:
+            positions = torch.arange(S, dtype=torch.int64).repeat(B, 1)
+        positions = positions.reshape(3, -1) if positions.dim() == 3 else positions.reshape(-1)
+        cu = batch.get("cu_seqlens")
+        if cu is None:
+            cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32)
+        dev = device if device is not None else next(self.parameters()).device
+        patches = batch.get("patches")
+        out = {"tokens": ids.reshape(-1).to(dev, non_blocking=True), "targets": labels.reshape(-1).to(dev, non_blocking=True),
+               "positions": positions.to(dev, non_blocking=True), "cu_seqlens": cu, "batch": B, "seq": S,
+               "attn_meta": AttnMeta.build(cu, causal=True, device=dev),
+               "model_kwargs": {"patches": None if patches is None else patches.to(dev, non_blocking=True), "grids": batch.get("grids")}}
+        return out
+
     def build_context(self, positions: torch.Tensor, attn_meta: AttnMeta, cp=None) -> ForwardContext:
+        if getattr(self.text, "accepts_three_axis_positions", False):
+            return self.text.build_context(positions, attn_meta, cp)
         cos, sin = mrope_tables(positions, self.config.head_dim, self.config.rope_theta, self.mrope_sections)
         return ForwardContext(cos, sin, attn_meta, cp)
 

@@ -44,12 +44,13 @@ class TrainingEngine:
         if self.asm.cp_driver is not None:
             self.asm.cp_driver.begin_microbatch(inputs)
         self.rt.before_forward()
+        extra = inputs.get("model_kwargs") or {}          # what a wrapper model needs beside the tokens (image patches, grids)
         if self.loss_fns.chunked:
-            h = m(inputs["tokens"], ctx, skip_lm_head=True)
+            h = m(inputs["tokens"], ctx, skip_lm_head=True, **extra)
             validate_training_output(h, inputs["targets"], output_width=self.caps.width("hidden"))
             loss_sum = self.loss_fns.from_hidden(h, m.lm_head.weight, inputs["targets"])
         else:
-            logits = m(inputs["tokens"], ctx)
+            logits = m(inputs["tokens"], ctx, **extra)
             validate_training_output(logits, inputs["targets"], output_width=self.caps.width("logits"))
             loss_sum = self.loss_fns.from_logits(logits, inputs["targets"])
         # Load-balance losses are token sums like the CE sum (`MoE.balance_loss_sum`): one division by the global valid-token
@@ -69,7 +70,7 @@ class TrainingEngine:
         inputs = m.prepare_inputs(batch, self.device, self.parallel_dims())
         ctx = m.build_context(inputs["positions"], inputs["attn_meta"], self.asm.cp_driver)
         self.rt.before_forward()
-        h = m(inputs["tokens"], ctx, skip_lm_head=True)
+        h = m(inputs["tokens"], ctx, skip_lm_head=True, **(inputs.get("model_kwargs") or {}))
         loss = self.loss_fns.from_hidden(h, m.lm_head.weight, inputs["targets"]) if self.loss_fns.chunked else \
             self.loss_fns.from_logits(m.lm_head(h), inputs["targets"])
         m.train(was)

@@ -53,7 +53,7 @@ class Trainer:
         arch = self.model.config
         self.dataloader = build_dataloader(t.dataloader_config, vocab_size=arch.vocab_size, global_batch=t.global_batch_size,
                                            seq_len=t.max_seq_len, seed=t.seed, dp_rank=self.dp_rank, dp_degree=self.dp_degree,
-                                           rows_per_rank=self.rows_per_rank, pin_memory=env.device.type == "cuda")
+                                           rows_per_rank=self.rows_per_rank, pin_memory=env.device.type == "cuda", model=self.model)
         self.data_iterator = iter(self.dataloader)
         self.progress = TrainingProgress()
         self.num_params = sum(u.numel for u in self.asm.fsdp.units)
