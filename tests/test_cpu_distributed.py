@@ -202,3 +202,28 @@ def test_hybrid_families_under_tensor_parallelism(family):
     got = run_ranks(2, base_flat(tensor_parallel_size=2, data_parallel_shard_size=1, **base), arch=arch)
     _close(ref["loss"], got["loss"], 5e-5)
     _close(ref["grad_norm"], got["grad_norm"], 5e-4)
+
+
+def test_dist_muon_plan_balances_work_and_prefers_the_storing_rank():
+    from torchllmtuner_b200.components.optimizer.muon import MuonJob, ns_cost, plan_owners
+    jobs = [MuonJob("a", 0, 1, 64, 64, (64, 64)), MuonJob("b", 4096, 1, 64, 64, (64, 64)), MuonJob("c", 8192, 1, 64, 256, (64, 256)),
+            MuonJob("d", 24576, 1, 32, 32, (32, 32)), MuonJob("e", 25600, 1, 32, 32, (32, 32))]
+    owners, loads = plan_owners(jobs, 2, 13312, 5)
+    assert owners[2] == 1                                   # the largest job goes first; the tie goes to the rank storing more of it
+    assert owners[0] == owners[1] == 0                      # the two mid-size matrices balance it on the other rank
+    assert max(loads) - min(loads) <= ns_cost(64, 64, 1, 5)
+    again, carried = plan_owners(jobs[:1], 2, 13312, 5, loads)
+    assert again == [loads.index(min(loads))] and sum(carried) == sum(loads) + ns_cost(64, 64, 1, 5)
+
+
+def test_dist_muon_orthogonalises_expert_matrices_and_fused_qkv_row_blocks():
+    """Packed expert tensors are Muon matrices too (one per expert, runs of experts placed as jobs); with a fused QKV
+    projection the query, key and value rows are orthogonalised separately. Two ranks reproduce one."""
+    moe = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
+    base = dict(model_name_or_path="qwen3_moe", optimizer_type="DistMuon", learning_rate=2e-2, qkv_projection="fused")
+    ref = run_ranks(1, base_flat(**base), arch=moe)
+    got = run_ranks(2, base_flat(data_parallel_shard_size=2, **base), arch=moe)
+    ep = run_ranks(2, base_flat(data_parallel_shard_size=2, expert_parallel_size=2, **base), arch=moe)
+    _close(ref["loss"], got["loss"], 2e-3)
+    _close(ref["loss"], ep["loss"], 2e-3)
+    assert ref["loss"][-1] < ref["loss"][0]

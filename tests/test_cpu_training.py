@@ -345,3 +345,34 @@ def test_per_op_selective_checkpointing_matches_no_checkpointing():
     assert n_default > 0 and 0 < n_forced < n_default          # gate/up share a shape: both leave the kept set
     with pytest.raises(ValueError):
         run(tiny_config(steps=1, activation_checkpoint_mode="selective", force_recompute_mm_shapes_by_fqns=["no_such_module"]))
+
+
+def test_ema_firing_count_decay_and_buffer_tracking(tmp_path):
+    """Firing n = (step - start_step) / every + step_bias, derived from the step; decay 2^(-1 / (hl * n)); a MoE block's
+    selection bias is averaged when `buffer_patterns` names it, travels in the checkpoint, and a replaced buffer is an
+    error rather than a frozen average."""
+    from torchllmtuner_b200.config.training_config import EMAConfig
+    cfg = tiny_config(model_name_or_path="qwen3_moe", steps=8, dump_folder=str(tmp_path), enable=True, interval=100)
+    cfg.model.arch_overrides = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, router_bias_update_coeff=1e-2)
+    cfg.training.ema_config = EMAConfig(half_life_fraction=0.5, start_step=1, update_every_n_steps=2, step_bias=3, buffer_patterns=[r"expert_bias_E$"])
+    tr = Trainer(cfg)
+    ema = tr.ema
+    assert [ema.firing(s) for s in range(7)] == [0, 0, 0, 4, 0, 5, 0]
+    assert abs(ema.decay_at(4) - 2.0 ** (-1.0 / (0.5 * 4))) < 1e-12
+    assert sorted(ema.ema_buffers) == ["model.layers.0.mlp.expert_bias_E", "model.layers.1.mlp.expert_bias_E"]
+    for _ in range(3):
+        tr.train_step()
+    name = "model.layers.0.mlp.expert_bias_E"
+    live = dict(tr.model.named_buffers())[name]
+    assert live.abs().sum() > 0 and ema.ema_buffers[name].abs().sum() > 0 and not torch.equal(ema.ema_buffers[name], live)
+    tr.checkpointer.save(3, force=True)
+    tr.checkpointer.wait()
+    kept = ema.ema_buffers[name].clone()
+    ema.ema_buffers[name].zero_()
+    assert tr.checkpointer.load(3)
+    assert torch.equal(ema.ema_buffers[name], kept)
+    blk = tr.model.model.layers[0].mlp
+    blk.register_buffer("expert_bias_E", blk.expert_bias_E.clone())
+    with pytest.raises(RuntimeError, match="identity"):
+        ema.step(5)
+    tr.close()

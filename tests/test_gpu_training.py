@@ -54,6 +54,26 @@ def test_host_resident_optimizer_state_keeps_the_losses():
     assert max(abs(a - b) for a, b in zip(ref, got)) < 1e-3, (ref, got)
 
 
+def test_host_resident_moments_stream_through_two_device_slots_in_many_slices():
+    """A 1 MiB slice budget cuts every unit into many slices: uploads, kernels and downloads of neighbouring slices
+    overlap on three streams, the device holds two slices of moments, and the numbers do not change."""
+    ref, _ = _run(_cfg())
+    cfg = _cfg(optimizer_type="AdamWSwap", swap_max_device_bytes=1 << 20)
+    tr = Trainer(cfg)
+    try:
+        got = []
+        for _ in range(cfg.training.steps):
+            tr.dataloader.cursor = 0
+            got.append(tr.train_step().loss)
+        stager = tr.optimizers.optimizers[0].stager
+        assert stager is not None and stager.stats["slices"] > 3 * 8, stager.stats
+        assert stager.stats["device_bytes"] == 2 * 2 * (1 << 20)
+        assert stager.stats["uploaded_bytes"] == stager.stats["downloaded_bytes"] > 0
+    finally:
+        tr.close()
+    assert max(abs(a - b) for a, b in zip(ref, got)) < 1e-3, (ref, got)
+
+
 def _repeat_two_batches(tr, steps):
     """Random tokens carry nothing to learn unless they repeat: alternate between the first two batches of the stream."""
     out = []

@@ -242,6 +242,9 @@ class DistributedCheckpointManager(CheckpointManager):
         for name, buf in tr.model.named_buffers():
             if buf is not None and self._owns_replicated():
                 out[canonical_fqn(name)] = buf.detach()
+        if tr.ema is not None and not model_only and self._owns_replicated():
+            for name, avg in tr.ema.ema_buffers.items():          # averaged buffers sit beside the averaged parameters
+                out[f"ema.ema_params.{name}"] = avg
         return out, table
 
     def _full_shapes(self) -> dict[str, list[int]]:
@@ -520,6 +523,14 @@ class DistributedCheckpointManager(CheckpointManager):
             if md is not None and "model" not in exclude and tuple(md.size) == tuple(buf.shape):
                 want[key] = torch.empty(buf.shape, dtype=buf.dtype)
                 buf_dst[key] = buf
+        ema_buf_dst = {}
+        if tr.ema is not None and not model_only and "ema" not in exclude:
+            for name, avg in tr.ema.ema_buffers.items():
+                key = f"ema.ema_params.{name}"
+                md = meta.state_dict_metadata.get(key)
+                if md is not None and tuple(md.size) == tuple(avg.shape):
+                    want[key] = torch.empty(avg.shape, dtype=avg.dtype)
+                    ema_buf_dst[key] = avg
         obj_want = self._object_wants(meta, model_only, exclude)
         want.update(obj_want)
         planner = BoxLoadPlanner(table)
@@ -533,6 +544,8 @@ class DistributedCheckpointManager(CheckpointManager):
                     dst.copy_(host)
             for key, buf in buf_dst.items():
                 buf.copy_(want[key])
+            for key, avg in ema_buf_dst.items():
+                avg.copy_(want[key])
         self._after_tensor_load()
         self._restore_objects({k[4:]: _unpack(v) for k, v in obj_want.items()}, model_only)
 

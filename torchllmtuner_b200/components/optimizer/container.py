@@ -32,6 +32,22 @@ class OptimizersContainer:
         return [g for o in self.optimizers for g in o.param_groups]
 
 
+def fused_qkv_row_blocks(model):
+    """A fused QKV projection is three matrices stacked by rows (query, key, value heads in the ratio H : Hkv : Hkv,
+    also after a tensor-parallel cut by heads): Muon orthogonalises them separately."""
+    cfg = getattr(model, "config", None)
+    if cfg is None or getattr(cfg, "qkv_projection", "separate") != "fused":
+        return None
+    H, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+
+    def blocks(fqn: str, shape):
+        if not fqn.endswith("qkv_proj.weight") or shape[0] % (H + 2 * Hkv):
+            return None
+        unit = shape[0] // (H + 2 * Hkv)
+        return [H * unit, Hkv * unit, Hkv * unit]
+    return blocks
+
+
 def build_optimizers(runtimes, opt_cfg, host_state: bool = False) -> OptimizersContainer:
     """`host_state` (set by `fsdp_cpu_offload`) keeps the Adam moments in pinned host memory like AdamWSwap does: on a
     180 GB device the optimizer state is the part worth offloading; parameters and gradients stay resident."""
@@ -47,7 +63,7 @@ def build_optimizers(runtimes, opt_cfg, host_state: bool = False) -> OptimizersC
         elif t == "DistMuon":
             from .muon import DistMuon
             outs.append(DistMuon(rt, lr=opt_cfg.learning_rate, weight_decay=opt_cfg.weight_decay, betas=opt_cfg.betas,
-                                 eps=opt_cfg.eps, param_group_rules=opt_cfg.param_groups))
+                                 eps=opt_cfg.eps, param_group_rules=opt_cfg.param_groups, row_blocks=fused_qkv_row_blocks(rt.model)))
         else:
             raise ConfigError(f"unknown optimizer_type {t!r}")
     return OptimizersContainer(outs)
@@ -122,40 +138,93 @@ class GradientClipper:
 
 
 class EMA:
-    """Exponential moving average of the fp32 master shards: avg.lerp_(param, 1 - decay) with
-    decay = 2^(-1 / (half_life_fraction * num_updates)) unless given (reference: ema.py:152-410)."""
+    """Exponential moving average of the fp32 master shards and, optionally, of selected module buffers
+    (reference: llmtuner/components/optimizer/ema.py:43-410).
 
-    def __init__(self, runtimes, cfg, total_steps: int):
+    The training engine calls `step(current_step)` after the optimizer. An update fires when
+    `elapsed = current_step - start_step` is positive and a multiple of `update_every_n_steps`. The firing count
+    `n = elapsed / update_every_n_steps + step_bias` is DERIVED from the step, never stored, so a resumed run continues
+    with the right decay although only the averages are checkpointed. With `decay=None` the decay of firing n is
+    2^(-1 / (half_life_fraction * n)): the half-life is a fixed fraction of the updates done so far.
+
+    `buffer_patterns` (regular expressions searched in wrapper-free buffer names, all aliases considered) add buffers
+    such as a MoE block's selection bias to the average; each buffer is tracked once, under its first name, BY IDENTITY:
+    replacing a tracked buffer after construction is an error at the next step rather than a silently frozen average."""
+
+    def __init__(self, runtimes, cfg, total_steps: int, model=None):
+        import re
         self.cfg = cfg
         self.units = [u for rt in runtimes for u in rt.units]
-        n_updates = max(1, (total_steps - cfg.start_step) // cfg.update_every_n_steps)
-        self.decay = cfg.decay if cfg.decay is not None else 2.0 ** (-1.0 / max(1e-9, cfg.half_life_fraction * n_updates))
+        self.decay = cfg.decay
         self.ema_params = {u.name: u.master.detach().clone() for u in self.units}
         self.num_updates = 0
+        self.buffers: dict[str, torch.Tensor] = {}          # first wrapper-free name -> the live buffer
+        self.ema_buffers: dict[str, torch.Tensor] = {}
+        self._model = model
+        patterns = [re.compile(p) for p in (cfg.buffer_patterns or [])]
+        if patterns and model is not None:
+            first: dict[int, str] = {}
+            for path, buf in model.named_buffers(remove_duplicate=False):
+                name = path.replace(".inner.", ".")
+                first.setdefault(id(buf), name)
+                if any(p.search(name) for p in patterns) and first[id(buf)] not in self.buffers:
+                    self.buffers[first[id(buf)]] = buf
+            for name, buf in self.buffers.items():
+                if not buf.dtype.is_floating_point:
+                    raise ConfigError(f"EMA buffer {name} has dtype {buf.dtype}; only floating-point buffers can be averaged")
+                self.ema_buffers[name] = buf.detach().clone().float()
+        if patterns and not self.buffers:
+            import logging
+            logging.getLogger("torchllmtuner_b200").warning("EMA buffer_patterns %s matched no buffer: nothing but parameters is "
+                                                            "averaged; check the patterns", list(cfg.buffer_patterns))
+
+    def firing(self, step: int) -> int:
+        """0 when `step` does not fire, else the firing count n (with `step_bias` added)."""
+        if isinstance(step, bool) or not isinstance(step, int) or step < 0:
+            raise ValueError("EMA current_step must be a non-negative integer")
+        c = self.cfg
+        elapsed = step - c.start_step
+        if elapsed <= 0 or elapsed % c.update_every_n_steps:
+            return 0
+        return elapsed // c.update_every_n_steps + c.step_bias
+
+    def decay_at(self, n: int) -> float:
+        return self.decay if self.decay is not None else 2.0 ** (-1.0 / (self.cfg.half_life_fraction * n))
 
     @torch.no_grad()
     def step(self, step: int) -> None:
-        c = self.cfg
-        if step < c.start_step or (step - c.start_step) % c.update_every_n_steps:
+        n = self.firing(step)
+        if n <= 0:
             return
-        self.num_updates += 1
-        d = self.decay
-        if c.step_bias:
-            d = min(d, (1 + self.num_updates) / (c.step_bias + self.num_updates))
+        self.num_updates = n
+        d = self.decay_at(n)
         avgs = [self.ema_params[u.name] for u in self.units]
         torch._foreach_lerp_(avgs, [u.master for u in self.units], 1.0 - d)
+        if self.buffers:
+            live = {id(b) for b in self._model.buffers()} if self._model is not None else None
+            for name, buf in self.buffers.items():
+                if live is not None and id(buf) not in live:
+                    raise RuntimeError(f"EMA tracks the buffer {name} by identity and it is no longer registered in the model: "
+                                       "build the EMA after the model is final")
+                self.ema_buffers[name].lerp_(buf.detach().float(), 1.0 - d)
 
     def reset(self) -> None:
         for u in self.units:
             self.ema_params[u.name].copy_(u.master)
+        for name, buf in self.buffers.items():
+            self.ema_buffers[name].copy_(buf.detach().float())
         self.num_updates = 0
 
     def state_dict(self):
-        return {"ema_params": self.ema_params, "num_updates": self.num_updates}
+        return {"ema_params": self.ema_params, "ema_buffers": self.ema_buffers, "num_updates": self.num_updates}
 
     def load_state_dict(self, sd):
         for k, v in sd["ema_params"].items():
             self.ema_params[k].copy_(v)
+        for k, v in (sd.get("ema_buffers") or {}).items():
+            if k not in self.ema_buffers:
+                raise ConfigError(f"EMA state names the buffer {k}, which this run does not track")
+            self.ema_buffers[k].copy_(v)
         self.num_updates = int(sd.get("num_updates", 0))
 
 

@@ -17,6 +17,65 @@ import torch
 from ... import ops
 
 
+class StagedSlices:
+    """Streams host-resident optimizer state through the device in bounded slices (reference:
+    llmtuner/components/optimizer/adamw_swap.py:71-650). Two device slots rotate; three streams work at once:
+        upload    slice i+1: pinned host -> slot (waits until the slot's previous download is done)
+        compute   slice i:   the update kernel on the slot (waits for its upload)
+        download  slice i-1: slot -> pinned host (waits for its compute)
+    so that the PCIe copies in both directions hide behind the kernel, and the device never holds more than two slices
+    of moments. Without a CUDA device the slices run one after the other on the host tensors themselves."""
+
+    def __init__(self, device: torch.device, slice_elems: int, arrays: int = 2):
+        self.device, self.slice = device, slice_elems
+        self.cuda = device.type == "cuda"
+        self.stats = {"slices": 0, "uploaded_bytes": 0, "downloaded_bytes": 0, "device_bytes": 0}
+        if self.cuda:
+            self.slots = [[torch.empty(slice_elems, dtype=torch.float32, device=device) for _ in range(arrays)] for _ in range(2)]
+            self.up, self.down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+            self.uploaded = [torch.cuda.Event() for _ in range(2)]
+            self.computed = [torch.cuda.Event() for _ in range(2)]
+            self.drained = [torch.cuda.Event() for _ in range(2)]
+            self.stats["device_bytes"] = 2 * arrays * slice_elems * 4
+            self._n = 0
+
+    def run(self, host_arrays: list[torch.Tensor], lo: int, hi: int, kernel) -> None:
+        """`kernel(a, b, device_views)` updates elements [a, b) given views of the host arrays' slices on the device."""
+        if not self.cuda:
+            for a in range(lo, hi, self.slice):
+                b = min(hi, a + self.slice)
+                kernel(a, b, [h[a:b] for h in host_arrays])
+                self.stats["slices"] += 1
+            return
+        main = torch.cuda.current_stream(self.device)
+        for a in range(lo, hi, self.slice):
+            b = min(hi, a + self.slice)
+            s = self._n % 2
+            self._n += 1
+            views = [slot[:b - a] for slot in self.slots[s]]
+            with torch.cuda.stream(self.up):
+                self.up.wait_event(self.drained[s])              # the slot's last download (two slices ago) has left it
+                for v, h in zip(views, host_arrays):
+                    v.copy_(h[a:b], non_blocking=True)
+                self.uploaded[s].record(self.up)
+            main.wait_event(self.uploaded[s])
+            kernel(a, b, views)
+            self.computed[s].record(main)
+            with torch.cuda.stream(self.down):
+                self.down.wait_event(self.computed[s])
+                for v, h in zip(views, host_arrays):
+                    h[a:b].copy_(v, non_blocking=True)
+                self.drained[s].record(self.down)
+            self.stats["slices"] += 1
+            self.stats["uploaded_bytes"] += (b - a) * 4 * len(host_arrays)
+            self.stats["downloaded_bytes"] += (b - a) * 4 * len(host_arrays)
+
+    def finish(self) -> None:
+        """The host arrays are complete once the download stream is idle (called at the end of a step)."""
+        if self.cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self.down)
+
+
 class ShardedAdamW:
     def __init__(self, units, *, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
                  decoupled: bool = True, param_group_rules=None, host_moments: bool = False, swap_slice_bytes: int = 1 << 28):
@@ -42,6 +101,10 @@ class ShardedAdamW:
                 m, v = m.pin_memory(), v.pin_memory()
             self.state[u.name] = {"exp_avg": m, "exp_avg_sq": v}
             self._runs[u.name] = self._build_runs(u)
+        self.stager = None
+        if host_moments and self.units:
+            biggest = max(u.shard_numel for u in self.units)
+            self.stager = StagedSlices(self.units[0].master.device, min(self.swap_slice, biggest))
 
     def _group_index(self, fqn: str) -> int:
         for i, (pat, _) in enumerate(self.rules):
@@ -91,13 +154,11 @@ class ShardedAdamW:
                     ops.adamw_step_(u.master[lo:hi], u.grad_shard[lo:hi], st["exp_avg"][lo:hi], st["exp_avg_sq"][lo:hi],
                                     p_lowp=None if lowp is None else lowp[lo:hi], **kw)
                 else:
-                    for a in range(lo, hi, self.swap_slice):
-                        b = min(hi, a + self.swap_slice)
-                        m = st["exp_avg"][a:b].to(u.master.device, non_blocking=True)
-                        v = st["exp_avg_sq"][a:b].to(u.master.device, non_blocking=True)
-                        ops.adamw_step_(u.master[a:b], u.grad_shard[a:b], m, v, p_lowp=None if lowp is None else lowp[a:b], **kw)
-                        st["exp_avg"][a:b].copy_(m, non_blocking=True)
-                        st["exp_avg_sq"][a:b].copy_(v, non_blocking=True)
+                    def update(a, b, mv, _u=u, _lowp=lowp, _kw=kw):
+                        ops.adamw_step_(_u.master[a:b], _u.grad_shard[a:b], mv[0], mv[1], p_lowp=None if _lowp is None else _lowp[a:b], **_kw)
+                    self.stager.run([st["exp_avg"], st["exp_avg_sq"]], lo, hi, update)
+        if self.stager is not None:
+            self.stager.finish()
 
     # ------------------------------------------------------------------ checkpoint state keyed by parameter FQN
     def state_dict_shards(self):

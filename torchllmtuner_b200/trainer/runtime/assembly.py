@@ -73,7 +73,7 @@ def build_loss_functions(config, env, asm) -> LossFunctions:
 def build_optimizer_stack(config, env, asm):
     optimizers = build_optimizers([asm.fsdp], config.optimizer, host_state=config.parallel.fsdp_config.fsdp_cpu_offload)
     lr = build_lr_scheduler(optimizers, config.optimizer.lr_scheduler_config, config.training.steps)
-    ema = EMA([asm.fsdp], config.training.ema_config, config.training.steps) if config.training.ema_config is not None else None
+    ema = EMA([asm.fsdp], config.training.ema_config, config.training.steps, model=asm.model) if config.training.ema_config is not None else None
     clipper = GradientClipper([asm.fsdp], env.topo, config.training.max_norm, env.device)
     if asm.layout is not None:
         # the state consumers remember the layout they were built against; the checkpointer checks it before every save/load
