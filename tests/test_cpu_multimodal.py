@@ -106,3 +106,55 @@ def test_vision_language_model_on_two_fsdp_ranks_matches_one():
     ref = run_ranks(1, base_flat(**VL), arch=VL_ARCH, steps=3)
     got = run_ranks(2, base_flat(data_parallel_shard_size=2, **VL), arch=VL_ARCH, steps=3)
     assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 5e-5, (ref, got)
+
+
+# ------------------------------------------------------------------------------------------ MoonViT (Kimi-K3's tower)
+def test_moonvit_pieces_match_their_restatements():
+    import torch.nn.functional as F
+    from torchllmtuner_b200.models import moonvit as mv
+    cfg = mv.MoonViTConfig(hidden_size=32, intermediate_size=64, depth=1, num_heads=2, out_hidden_size=24, pos_emb_height=4, pos_emb_width=4)
+    tower = mv.MoonViTTower(cfg, dtype=torch.float32)
+    tower.initialize_parameters(seed=2)
+    grids = [(1, 4, 4), (2, 2, 6)]
+    # position table: the learned table as is at its own size, bicubic elsewhere, plus the frame code for clips
+    tab = tower.position_table(grids, torch.float32)
+    assert torch.equal(tab[:16], tower.pos_emb.flatten(0, 1))
+    want = F.interpolate(tower.pos_emb.permute(2, 0, 1)[None], size=(2, 6), mode="bicubic")[0].permute(1, 2, 0).flatten(0, 1)
+    code = mv.time_code(32, 4)
+    assert torch.allclose(tab[16:28], want + code[0]) and torch.allclose(tab[28:40], want + code[1])
+    assert torch.allclose(code[1, :16], torch.sin(1.0 / 10000 ** (torch.arange(16) / 16.0)))
+    # rotary pairs: even pairs turn with the column, odd pairs with the row; equal to a complex multiplication
+    ang = mv.grid_pair_angles([(1, 2, 3)], 8, 10000.0)
+    f = 1.0 / (10000.0 ** (torch.arange(0, 8, 4) / 8))
+    assert torch.allclose(ang[4], torch.stack((1 * f, 1 * f), -1).flatten())          # patch (row 1, col 1)
+    assert torch.allclose(ang[2], torch.stack((2 * f, 0 * f), -1).flatten())          # patch (row 0, col 2)
+    x = torch.randn(6, 2, 8)
+    z = torch.view_as_complex(x.view(6, 2, 4, 2).contiguous()) * torch.polar(torch.ones(6, 4), ang)[:, None, :]
+    assert torch.allclose(mv.rotate_pairs(x, ang), torch.view_as_real(z).flatten(-2), atol=1e-6)
+    # merger: mean over frames, then 2 x 2 neighbourhoods in row-major order of the merged grid
+    h = torch.randn(16 + 24, 32)
+    merged = tower.merge(h, grids)
+    assert merged.shape == (4 + 3, 4, 32)
+    clip = h[16:].view(2, 2, 6, 32).mean(0)
+    assert torch.allclose(merged[4 + 1], torch.stack((clip[0, 2], clip[0, 3], clip[1, 2], clip[1, 3])))
+    out = tower(torch.rand(40, cfg.patch_dim), grids)
+    assert out.shape == (7, 24) and torch.isfinite(out).all()
+
+
+def test_kimi_k3_with_moonvit_trains_through_the_trainer(tmp_path):
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(dump_folder=str(tmp_path), steps=5, model_name_or_path="kimi_k3_vl", dataset="random_multimodal", vocab_size=320,
+                             hidden_size=64, num_hidden_layers=4, num_attention_heads=2, num_key_value_heads=2, max_seq_len=160,
+                             global_batch_size=2, learning_rate=3e-3, mm_max_pixels=14 * 14 * 4 * 8, mm_video_fraction=0.5))
+    cfg.model.arch_overrides = dict(linear_heads=2, linear_head_dim=16, vision=dict(hidden_size=32, intermediate_size=64, depth=1, num_heads=2))
+    tr = Trainer(cfg)
+    batch = next(iter(tr.dataloader))
+    tr.dataloader.cursor = 0
+    assert (batch["input"] == tr.model.image_token_id).sum() == sum((gh // 2) * (gw // 2) for _, gh, gw in batch["grids"])   # time-pooled
+    losses = []
+    for _ in range(5):
+        tr.dataloader.cursor = 0
+        losses.append(tr.train_step().loss)
+    assert losses[-1] < losses[0] - 0.2, losses
+    tr.close()

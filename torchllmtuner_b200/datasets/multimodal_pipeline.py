@@ -37,10 +37,18 @@ class VisionSpec:
     video_fps: float = 2.0
     video_min_frames: int = 4
     video_max_frames: int = 32
+    temporal_pool: bool = False        # the tower averages a clip's frames: rows per item do not grow with the frame count
 
     @property
     def factor(self) -> int:
         return self.patch_size * self.merge_size
+
+    def rows_of(self, grid) -> int:
+        t, gh, gw = grid
+        return calculate_vision_tokens((1 if self.temporal_pool else t, gh, gw), self.merge_size)
+
+    def position_grid(self, grid):
+        return (1, grid[1], grid[2]) if self.temporal_pool else tuple(grid)
 
 
 # --------------------------------------------------------------------------------------------------- items
@@ -102,7 +110,7 @@ def build_sample(ids: list[int], items: list[tuple[torch.Tensor, tuple[int, int,
     tokens, labels, gi = [], [], 0
     for i, t in enumerate(ids):
         if t == placeholder_id:
-            n = calculate_vision_tokens(grids[gi], spec.merge_size)
+            n = spec.rows_of(grids[gi])
             gi += 1
             block = ([start_id] if start_id is not None else []) + [placeholder_id] * n + ([end_id] if end_id is not None else [])
             tokens += block
@@ -110,7 +118,7 @@ def build_sample(ids: list[int], items: list[tuple[torch.Tensor, tuple[int, int,
         else:
             tokens.append(t)
             labels.append(IGNORE_INDEX if i < prompt_len else t)
-    positions = build_mrope_positions(tokens, placeholder_id, grids, spec.merge_size)
+    positions = build_mrope_positions(tokens, placeholder_id, [spec.position_grid(g) for g in grids], spec.merge_size)
     patches = torch.cat([p for p, _ in items]) if items else torch.zeros(0, 0)
     return MultimodalSample(tokens, labels, positions, patches, grids)
 

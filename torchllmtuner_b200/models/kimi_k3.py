@@ -360,6 +360,7 @@ class KimiDecoderLayer(nn.Module):
 
 class KimiForCausalLM(Qwen3ForCausalLM):
     decoder_structure = DecoderStructure()
+    positions_are_document_indices = True      # no rotary anywhere: positions only tell where documents restart
 
     def __init__(self, cfg: KimiConfig, dtype=None, device=None):
         nn.Module.__init__(self)
@@ -438,3 +439,20 @@ KIMI_LINEAR_DEFAULTS = dict(model_type="kimi_linear", num_experts=8, num_experts
                             first_k_dense_replace=1, router_bias_update_coeff=1e-3)
 KIMI_K3_DEFAULTS = dict(KIMI_LINEAR_DEFAULTS, model_type="kimi_k3", attn_res_block_size=2, hidden_act="situ", activation_situ_beta=4.0,
                         routed_expert_hidden_size=32, mla_use_output_gate=True, num_expert_group=4, topk_group=2)
+
+
+def build_kimi_vl(defaults: dict):
+    """Kimi-K3 with its vision tower (MoonViT): `arch_overrides` may carry `image_token_id` (default: the last token) and
+    `vision` (fields of `MoonViTConfig`; the output width follows the text width). Text positions stay one-dimensional."""
+    text_builder = build_kimi(defaults)
+
+    def build(model_config, dtype=None, device=None, **overrides):
+        from .moonvit import MoonViTConfig, MoonViTTower
+        from .vision import VisionLanguageModel
+        text = text_builder(model_config, dtype=dtype, device=device, **overrides)
+        extra = dict(model_config.arch_overrides or {})
+        vkw = dict(extra.get("vision") or {})
+        vkw["out_hidden_size"] = text.config.hidden_size
+        image_id = int(extra.get("image_token_id", text.config.vocab_size - 1))
+        return VisionLanguageModel(text, MoonViTConfig(**vkw), image_id, dtype=dtype, device=device, tower=MoonViTTower)
+    return build

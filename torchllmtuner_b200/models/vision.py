@@ -194,11 +194,13 @@ class VisionLanguageModel(nn.Module):
     # switches that the parallel stages set on "the model" and the text decoder reads on itself
     _PASS = ("block_runner", "activation_checkpoint", "ac_save_every", "ac_block_mask", "pp_first", "pp_last", "activation_swap")
 
-    def __init__(self, text: nn.Module, vision: VisionConfig, image_token_id: int, mrope_sections=None, dtype=None, device=None):
+    def __init__(self, text: nn.Module, vision, image_token_id: int, mrope_sections=None, dtype=None, device=None, tower=None):
+        """`tower`: the tower class for `vision` (default: the Qwen-style `VisionTower`; `models/moonvit.py::MoonViTTower`
+        for Kimi)."""
         super().__init__()
         if vision.out_hidden_size != text.config.hidden_size:
             raise ConfigError(f"vision out_hidden_size {vision.out_hidden_size} != text hidden_size {text.config.hidden_size}")
-        self.text, self.visual = text, VisionTower(vision, dtype, device)
+        self.text, self.visual = text, (tower or VisionTower)(vision, dtype, device)
         self.image_token_id, self.mrope_sections = image_token_id, mrope_sections
         self.config = text.config
 
@@ -257,8 +259,11 @@ class VisionLanguageModel(nn.Module):
         return out
 
     def build_context(self, positions: torch.Tensor, attn_meta: AttnMeta, cp=None) -> ForwardContext:
-        if getattr(self.text, "accepts_three_axis_positions", False):
+        if getattr(self.text, "accepts_three_axis_positions", False) or positions.dim() == 1:
             return self.text.build_context(positions, attn_meta, cp)
+        if getattr(self.text, "positions_are_document_indices", False):      # no rotary in the text model: only restarts matter
+            doc = torch.cat([torch.arange(int(p[1]), device=positions.device) for p in attn_meta.pieces])
+            return self.text.build_context(doc, attn_meta, cp)
         cos, sin = mrope_tables(positions, self.config.head_dim, self.config.rope_theta, self.mrope_sections)
         return ForwardContext(cos, sin, attn_meta, cp)
 
