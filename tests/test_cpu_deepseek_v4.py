@@ -238,3 +238,28 @@ def test_two_fsdp_ranks_match_one():
     ref = run_ranks(1, base_flat(**base), steps=4)
     got = run_ranks(2, base_flat(data_parallel_shard_size=2, **base), steps=4)
     assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 5e-5, (ref, got)
+
+
+def test_sequence_parallel_ranks_reproduce_one_rank(tmp_path):
+    """Two ranks each hold half of every sequence: the shared key/value head and the compressor inputs are gathered, every
+    rank pools all windows, queries stay local. First Adam moments (0.1 x gradient) and losses agree with one rank."""
+    import os
+    import torch.distributed.checkpoint as dcp
+    from dist_cases import base_flat, run_ranks
+    base = dict(model_name_or_path="deepseek_v4", num_hidden_layers=3, max_seq_len=64, enable=True)
+    one, two = str(tmp_path / "one"), str(tmp_path / "two")
+    ref = run_ranks(1, base_flat(dump_folder=one, _save_at=1, **base), steps=3)
+    got = run_ranks(2, base_flat(dump_folder=two, _save_at=1, data_parallel_shard_size=1, context_parallel_kv_allgather_size=2, **base), steps=3)
+    assert abs(ref["loss"][0] - got["loss"][0]) < 1e-5, (ref, got)
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 1e-4, (ref, got)
+
+    def moments(folder):
+        path = os.path.join(folder, "checkpoint", "step-1")
+        md = dcp.FileSystemReader(path).read_metadata().state_dict_metadata
+        want = {k: torch.empty(tuple(v.size), dtype=v.properties.dtype) for k, v in md.items() if k.endswith(".exp_avg")}
+        dcp.load(want, checkpoint_id=path, no_dist=True)
+        return want
+    a, b = moments(one), moments(two)
+    scale = max(t.abs().max().item() for t in a.values())
+    for k in a:
+        assert (a[k] - b[k]).abs().max().item() <= 1e-4 * a[k].abs().max().item() + 1e-7 * scale, k

@@ -17,8 +17,12 @@ What makes the family:
     "hash_moe" layers, experts looked up in a token-id table; clamped SwiGLU; one shared expert.
 
 Rows are packed `[T, D]`, streams `[T, n, D]`; documents come from `AttnMeta.pieces`, so windows, entries and positions
-restart at every document. The window/entry attention is evaluated densely in query chunks (fp32 softmax); every
-projection is a `Linear` of this framework and therefore a tcgen05 GEMM on the device.
+restart at every document. Sequence parallelism (reference: llmtuner/parallel/context_parallel/compressor_attention.py:39-371,
+compression_windows.py exchanges windows and runs a Ulysses exchange over the query heads) takes another route here: the
+key/value stream is ONE head and the compressor inputs are a few head-widths per token, so they are gathered over the
+sequence ranks (a few MB at 128k tokens) and every rank pools all windows itself; queries, the H-head products and
+the hyper-connection streams stay local to the rank's span. The window/entry attention is evaluated densely in query
+chunks (fp32 softmax); every projection is a `Linear` of this framework and therefore a tcgen05 GEMM on the device.
 """
 from __future__ import annotations
 
@@ -149,9 +153,37 @@ class V4Context(ForwardContext):
     token_ids: torch.Tensor | None = None    # set by the model's forward for hash-routed blocks
 
 
+def _cp(ctx):
+    cp = getattr(ctx, "cp", None)
+    return cp if cp is not None and getattr(cp, "size", 1) > 1 else None
+
+
 def _docs(ctx) -> list[tuple[int, int]]:
-    """(first row, length) of every document of the packed batch."""
-    return [(int(p[0]), int(p[1])) for p in ctx.attn_meta.pieces]
+    """(first row, length) of every document of the batch, in the row numbering of the gathered (whole-sequence) tensors:
+    the local rows without sequence parallelism, the global rows with it."""
+    cp = _cp(ctx)
+    if cp is None:
+        return [(int(p[0]), int(p[1])) for p in ctx.attn_meta.pieces]
+    gcu = cp._mb["gcu"]
+    return [(gcu[i], gcu[i + 1] - gcu[i]) for i in range(len(gcu) - 1)]
+
+
+def _views(ctx) -> list[tuple[int, int, int, int]]:
+    """What this rank's queries see: (first local query row, count, position of that row inside its document, index of the
+    document in `_docs`). Without sequence parallelism every document is one view that starts at position 0."""
+    cp = _cp(ctx)
+    if cp is None:
+        return [(int(p[0]), int(p[1]), 0, i) for i, p in enumerate(ctx.attn_meta.pieces)]
+    import bisect
+    gcu = cp._mb["gcu"]
+    return [(int(q0), int(n), int(off), bisect.bisect_right(gcu, int(k0)) - 1) for q0, n, k0, _klen, off in cp._mb["meta"].pieces]
+
+
+def _whole(ctx, t: torch.Tensor) -> torch.Tensor:
+    """Per-token tensors that every rank needs for the whole sequence (one shared key/value head, compressor inputs) are
+    small: under sequence parallelism they are gathered, and every rank pools the windows redundantly."""
+    cp = _cp(ctx)
+    return t if cp is None else cp.gather_rows(t)
 
 
 # --------------------------------------------------------------------------------------------------- compressors
@@ -170,8 +202,8 @@ class _WindowPool(nn.Module):
         self.rope_dim, self.theta = cfg.qk_rope_head_dim, cfg.compress_rope_theta
 
     def pool(self, x: torch.Tensor, ctx) -> list[torch.Tensor]:
-        """Per document: entries [W, width] (W = complete windows of that document, possibly 0)."""
-        kv_all, gate_all = self.kv_proj(x), self.gate_proj(x)
+        """Per document of `_docs`: entries [W, width] (W = complete windows of that document, possibly 0)."""
+        kv_all, gate_all = _whole(ctx, self.kv_proj(x)), _whole(ctx, self.gate_proj(x))
         out = []
         d, r = self.width, self.rate
         for q0, L in _docs(ctx):
@@ -209,7 +241,7 @@ class Indexer(_WindowPool):
 
     @torch.no_grad()
     def select(self, x: torch.Tensor, q_residual: torch.Tensor, ctx) -> list[torch.Tensor]:
-        """Per document: [L, min(topk, W)] entry indices, -1 where fewer entries are visible."""
+        """Per view of `_views`: [L, min(topk, W)] entry indices, -1 where fewer entries are visible."""
         if q_residual.shape != (x.shape[0], self.q_b_proj.weight.shape[1]):
             raise ValueError("indexer: q_residual does not match the rows")
         keys = self.pool(x, ctx)
@@ -217,7 +249,8 @@ class Indexer(_WindowPool):
         q = rotate_trailing_pairs(self.q_b_proj(q_residual).view(x.shape[0], self.heads, self.width), cos, sin)
         hw = self.weights_proj(x).float() * self.head_scale
         out = []
-        for (q0, L), k in zip(_docs(ctx), keys):
+        for q0, L, _first, doc in _views(ctx):
+            k = keys[doc]
             W = k.shape[0]
             if W == 0:
                 out.append(torch.full((L, 0), -1, dtype=torch.int64, device=x.device))
@@ -236,9 +269,11 @@ class HCACompressor(_WindowPool):
         super().__init__(cfg, cfg.compress_rates["heavily_compressed_attention"], cfg.head_dim, False, dtype, device)
 
     def forward(self, x, q_residual, ctx):
-        """Per document: (entries [W, d], bias [L, W]: 0 where the entry's window is complete at the query, else -inf)."""
+        """Per view: (entries [W, d], bias [L, W]: 0 where the entry's window is complete at the query, else -inf)."""
         out = []
-        for (q0, L), e in zip(_docs(ctx), self.pool(x, ctx)):
+        pooled = self.pool(x, ctx)
+        for q0, L, _first, doc in _views(ctx):
+            e = pooled[doc]
             thr = (ctx.positions[q0:q0 + L] + 1) // self.rate
             hidden = torch.arange(e.shape[0], device=x.device)[None, :] >= thr[:, None]
             out.append((e, torch.zeros(L, e.shape[0], device=x.device).masked_fill(hidden, float("-inf"))))
@@ -252,7 +287,9 @@ class CSACompressor(_WindowPool):
 
     def forward(self, x, q_residual, ctx):
         out = []
-        for (q0, L), e, sel in zip(_docs(ctx), self.pool(x, ctx), self.indexer.select(x, q_residual, ctx)):
+        pooled = self.pool(x, ctx)
+        for (q0, L, _first, doc), sel in zip(_views(ctx), self.indexer.select(x, q_residual, ctx)):
+            e = pooled[doc]
             W = e.shape[0]
             bias = torch.full((L, W + 1), float("-inf"), device=x.device)
             bias.scatter_(1, torch.where(sel >= 0, sel, torch.full_like(sel, W)), 0.0)      # invalid picks go to a spare slot
@@ -282,21 +319,22 @@ class V4Attention(nn.Module):
         if self.compressor is not None:
             self.compressor = self.compressor(cfg, dtype, device)
 
-    def _attend(self, q, kv, entries, bias, chunk: int = 1024):
-        """One document. q [L, H, d], kv [L, d] (keys = values, one head), entries [W, d] with additive bias [L, W].
-        Query i sees rows (i - window, i] and the entries its bias admits; a per-head sink logit joins the softmax and
-        is dropped afterwards."""
+    def _attend(self, q, kv, entries, bias, first: int = 0, chunk: int = 1024):
+        """One view. q [L, H, d]: queries at positions first .. first + L of their document; kv [first + L, d]: the
+        document's shared keys = values up to the last query; entries [W, d] with additive bias [L, W]. The query at
+        position p sees rows (p - window, p] and the entries its bias admits; a per-head sink logit joins the softmax
+        and is dropped afterwards."""
         L, H, d = q.shape
         W = entries.shape[0]
         sink = self.sinks.float().view(1, H, 1)
         outs = []
         for c0 in range(0, L, chunk):
             c1 = min(L, c0 + chunk)
-            k0 = max(0, c0 - self.window + 1)
-            keys = kv[k0:c1]
+            k0 = max(0, first + c0 - self.window + 1)
+            keys = kv[k0:first + c1]
             s = torch.einsum("lhd,kd->lhk", q[c0:c1], keys).float() * self.scale
-            qi = torch.arange(c0, c1, device=q.device)[:, None]
-            kj = torch.arange(k0, c1, device=q.device)[None, :]
+            qi = torch.arange(first + c0, first + c1, device=q.device)[:, None]
+            kj = torch.arange(k0, first + c1, device=q.device)[None, :]
             s = s.masked_fill(((kj > qi) | (kj <= qi - self.window))[:, None, :], float("-inf"))
             parts = [s]
             if W:
@@ -317,15 +355,17 @@ class V4Attention(nn.Module):
         q_res = self.q_a_norm(self.q_a_proj(x))
         q = unweighted_rms_norm(self.q_b_proj(q_res).view(T, self.H, self.d), self.eps)
         q = rotate_trailing_pairs(q, cos, sin)
-        kv = rotate_trailing_pairs(self.kv_norm(self.kv_proj(x)), cos, sin)
+        kv = _whole(ctx, rotate_trailing_pairs(self.kv_norm(self.kv_proj(x)), cos, sin))
         comp = self.compressor(x, q_res, ctx) if self.compressor is not None else None
+        docs = _docs(ctx)
         outs = []
-        for i, (q0, L) in enumerate(_docs(ctx)):
+        for i, (q0, L, first, doc) in enumerate(_views(ctx)):
             if comp is None:
                 e, b = kv.new_zeros(0, self.d), None
             else:
                 e, b = comp[i]
-            outs.append(self._attend(q[q0:q0 + L], kv[q0:q0 + L], e, b))
+            g0 = docs[doc][0]
+            outs.append(self._attend(q[q0:q0 + L], kv[g0:g0 + first + L], e, b, first))
         o = torch.cat(outs, 0) if len(outs) > 1 else outs[0]
         o = rotate_trailing_pairs(o, cos, -sin)            # values carried the rotation of their own position: undo the query's
         g = self.o_a_proj(o.reshape(T, self.groups, -1)).reshape(T, -1)
@@ -463,19 +503,20 @@ class DeepseekV4ForCausalLM(Qwen3ForCausalLM):
     def validate_parallel(self, tp: int = 1, cp_ulysses: int = 1, ep: int = 1) -> None:
         from ..errors import UnsupportedCombinationError
         if tp > 1 or cp_ulysses > 1:
-            raise UnsupportedCombinationError("deepseek_v4: one shared key/value head and window compression leave nothing to cut "
-                                              "by heads; use data, expert and pipeline-free FSDP parallelism")
+            raise UnsupportedCombinationError("deepseek_v4: no tensor-parallel plan and no Ulysses exchange; use data, expert, FSDP and "
+                                              "key/value-gathering sequence parallelism")
         if self.config.num_experts % ep:
             raise UnsupportedCombinationError(f"expert_parallel_size {ep} must divide num_experts {self.config.num_experts}")
 
     def build_context(self, positions: torch.Tensor, attn_meta, cp=None) -> V4Context:
-        if cp is not None:
+        if cp is not None and getattr(cp, "size", 1) > 1 and (cp.strategy != "kv_allgather" or cp.load_balancer is not None):
             from ..errors import UnsupportedCombinationError
-            raise UnsupportedCombinationError("deepseek_v4: context parallelism needs the window exchange of the compressors")
+            raise UnsupportedCombinationError("deepseek_v4: sequence parallelism gathers the shared key/value head and the compressor "
+                                              "inputs over contiguous spans: use context_parallel_kv_allgather_size without a load balancer")
         c = self.config
         rope = {"main": rope_tables_interleaved(positions, c.qk_rope_head_dim, c.rope_theta),
                 "compress": rope_tables_interleaved(positions, c.qk_rope_head_dim, c.compress_rope_theta)}
-        return V4Context(rope["main"][0], rope["main"][1], attn_meta, None, positions=positions, rope=rope)
+        return V4Context(rope["main"][0], rope["main"][1], attn_meta, cp, positions=positions, rope=rope)
 
     def checkpoint_configuration(self) -> dict:
         """What a reader of a checkpoint must agree on before the tensors mean anything."""

@@ -102,6 +102,6 @@ def _ensure_builtins() -> None:
         description="Kimi-Linear decoder: KDA with short convolutions, latent attention without rotary, grouped sigmoid router")
     reg("kimi_k3", kimi_k3.build_kimi(kimi_k3.KIMI_K3_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "cp", "ac"},
         description="Kimi-K3 text decoder: Kimi-Linear plus attention residuals, SituGLU and latent-space experts")
-    reg("deepseek_v4", deepseek_v4.build_deepseek_v4, state_format="deepseek_v4", supports={"fsdp", "ep", "ac"},
+    reg("deepseek_v4", deepseek_v4.build_deepseek_v4, state_format="deepseek_v4", supports={"fsdp", "ep", "cp", "ac"},
         description="DeepSeek-V4 decoder: hyper-connections, shared-KV sliding/compressed attention with an indexer, hash and "
                     "biased top-k routers")

@@ -191,6 +191,15 @@ class ContextParallelDriver:
             return every[0] * 0.0
         return every[self.rank - 1] + 0.0 * every[self.rank].sum()
 
+    def gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's rows [B*t, ...] -> every rank's rows in global order [B*S, ...] (differentiable: the backward is a
+        reduce-scatter). For small per-token tensors that every rank needs whole: a shared single-head key/value stream,
+        the inputs of window compressors."""
+        from ..errors import UnsupportedCombinationError
+        if self.strategy != "kv_allgather":
+            raise UnsupportedCombinationError("gathering rows over the sequence axis needs context_parallel_kv_allgather_size (or kcp)")
+        return _AllGatherRowsCP.apply(x, self.group_kv, self._mb["perm"])
+
     def delta_rule(self, q, k, v, beta, log_decay, chunk: int):
         """Sequence-parallel gated delta rule (reference: llmtuner/parallel/context_parallel/kcp.py:30-335). Every rank
         owns one contiguous span of each sequence. The recurrence is linear in the state, and its value columns evolve
