@@ -20,13 +20,13 @@ INERT_FIELDS: dict[str, str] = {
     "tp_sequence_modules": "sequence boundaries are placed by the model's TP plan",
     "context_parallel_strategy": "the strategy follows from which context-parallel degree is > 1",
     "ep_torchao_pad_multiple": "the torchao dispatcher is not available; segments are padded to 128 rows",
-    "swap_prefetch": "host-resident moments are streamed in fixed slices without a prefetch queue",
+    "swap_prefetch": "host-resident moments are streamed through two device slots: the upload of the next slice always overlaps the current update",
     "swap_memory_fraction": "the slice size comes from swap_max_device_bytes",
     "swap_max_host_bytes": "pinned host memory for the moments is not capped",
-    "compute_sharding_by_fqn": "Muon owners are balanced automatically",
-    "bucket_configs": "Muon redistribution uses one bucket per matrix",
-    "sharded_expert_parallel": "checkpoints always store global-coordinate pieces, which resume at any EP degree",
-    "sharded_tensor_parallel": "checkpoints always store global-coordinate pieces, which resume at any TP degree",
+    "compute_sharding_by_fqn": "Muon jobs are placed by cost (longest first on the least loaded rank, ties to the storing rank)",
+    "bucket_configs": "Muon redistribution is one all-to-all per sharding unit each way",
+    "sharded_expert_parallel": "checkpoints always hold whole tensors written as boxes, which resume at any EP degree",
+    "sharded_tensor_parallel": "checkpoints always hold whole tensors written as boxes, which resume at any TP degree",
     "global_context_rows": "rows are assigned to data-parallel ranks by contiguous slices",
     "streaming_shuffle_buffer_size": "only used by `datasets.sources.StreamingSource` when a recipe builds one",
     "mm_pad_token": "multimodal padding uses the tokenizer's pad id",
@@ -34,7 +34,6 @@ INERT_FIELDS: dict[str, str] = {
     "npu_profiler_level": "no NPU profiler on this platform",
     "profiler_skip_first_wait": "the profiler schedule has no separate first-cycle wait",
     "enable_async_tensor_parallel": "TP collectives are fused into the GEMM kernels, there is no compiler pass to enable",
-    "buffer_patterns": "EMA tracks parameters only",
     "determinism_check": "activation recomputation is bitwise deterministic by construction (same kernels, same order)",
 }
 
