@@ -200,8 +200,11 @@ def main() -> int:
         b = next(tr.data_iterator)
         return [{k: (v.to(dev) if isinstance(v, torch.Tensor) and k != "cu_seqlens" else v) for k, v in b.items()}]
 
+    # the same call the training loop makes (`Trainer._run_training`): with `overlap_optimizer_step` (default on) the update
+    # of a single-shard-rank run goes to its own stream and the next forward waits unit by unit
+    ov = bool(cfg.training.overlap_optimizer_step)
     for _ in range(warm):
-        tr.train_step()
+        tr.train_step(overlap_optimizer=ov)
     check_status("bench warm-up")
     pre = [device_batch() for _ in range(args.steps)]
     it = iter(pre)
@@ -209,7 +212,7 @@ def main() -> int:
     if sampler:
         sampler.start()
     n0 = ext.launch_count()
-    ms_dev = timed(lambda: tr.train_step(batches=next(it), read_stats=False), args.steps)
+    ms_dev = timed(lambda: tr.train_step(batches=next(it), read_stats=False, overlap_optimizer=ov), args.steps)
     launches = ext.launch_count() - n0
     fused = getattr(getattr(tr.asm, "fsdp", None), "fused", None)
     qs = dict(fused.queue.stats) if fused is not None and fused.queue is not None else None
@@ -220,7 +223,7 @@ def main() -> int:
     h2d = sum(v.numel() * v.element_size() for k, v in probe.items() if isinstance(v, torch.Tensor) and k != "cu_seqlens")
     d2h = 4 * 4                       # one read per step: loss sum, gradient norm, valid tokens, kernel status code
     results = []
-    ms_e2e = timed(lambda: results.append(tr.train_step()), args.steps)
+    ms_e2e = timed(lambda: results.append(tr.train_step(overlap_optimizer=ov)), args.steps)
     check_status("bench")
     tokens_per_step = cfg.training.global_batch_size * args.seq
     par = "+".join(p for p in (f"fsdp{tr.env.topo.dp_shard}" if tr.env.topo.dp_shard > 1 or world == 1 else "", f"tp{args.tp}" if args.tp > 1 else "",
@@ -234,7 +237,7 @@ def main() -> int:
            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_dev / args.steps,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens" + (" packed from documents of log-uniform length 512..32768" if args.dataset == "random_packed" else "") + ", random-init weights",
            "config": {"model": args.model + (f"[layers={args.layers}]" if args.layers else ""), "global_batch": cfg.training.global_batch_size,
-                      "seq_len": args.seq, "parallelism": par, "activation_checkpointing": args.ac,
+                      "seq_len": args.seq, "parallelism": par, "activation_checkpointing": args.ac, "optimizer_overlap": ov,
                       "loss": f"chunked x{args.loss_chunks}", "l2": "inputs (16 GB of weights per step) larger than the 126 MB L2",
                       "fsdp_implementation": args.fsdp_impl},
            "clocks": clocks, "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d,

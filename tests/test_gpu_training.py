@@ -111,3 +111,26 @@ def test_twenty_step_loss_curve_follows_the_fp32_oracle(tmp_path, monkeypatch):
     assert worst < 0.15, list(zip(got, oracle))
     assert oracle[0] - oracle[-1] > 0.5 and got[0] - got[-1] > 0.5, (oracle, got)   # both actually learn
     assert abs((got[0] - got[-1]) - (oracle[0] - oracle[-1])) < 0.15
+
+
+def test_optimizer_update_under_the_next_forward_changes_nothing():
+    """With `overlap_optimizer=True` the AdamW kernels run on their own stream in the order the next forward needs the
+    units and the forward waits unit by unit. Same arithmetic, same order per element: the losses are identical, and
+    after `sync_optimizer()` so are the parameters."""
+    cfg = _cfg(steps=5, num_hidden_layers=4)
+    tr = Trainer(cfg)
+    ref = [tr.train_step().loss for _ in range(5)]
+    ref_master = [u.master.clone() for u in tr.asm.fsdp.units]
+    tr.close()
+    tr = Trainer(_cfg(steps=5, num_hidden_layers=4))
+    got = [tr.train_step(overlap_optimizer=True).loss for _ in range(5)]
+    assert any(getattr(u, "updated_event", None) is not None for u in tr.asm.fsdp.units)     # the last update is still pending or just done
+    tr.asm.fsdp.sync_optimizer()
+    assert all(getattr(u, "updated_event", None) is None for u in tr.asm.fsdp.units)
+    torch.cuda.synchronize()
+    try:
+        assert got == ref, (got, ref)
+        for a, u in zip(ref_master, tr.asm.fsdp.units):
+            assert torch.equal(a, u.master)
+    finally:
+        tr.close()

@@ -299,6 +299,9 @@ class DistributedCheckpointManager(CheckpointManager):
         """Optimizer and EMA state are keyed by parameter names: refuse to write or read them when the model's parameters
         are no longer the ones those consumers were built against."""
         tr = self.trainer
+        rt = getattr(getattr(tr, "asm", None), "fsdp", None)
+        if rt is not None and hasattr(rt, "sync_optimizer"):
+            rt.sync_optimizer()                   # a parameter update may still be running on the optimizer's stream
         layout = getattr(getattr(tr, "asm", None), "layout", None)
         if layout is None:
             return

@@ -39,6 +39,8 @@ def read_hf_weight_map(path: str) -> dict[str, str]:
 
 
 def _param_index(trainer):
+    if hasattr(trainer.asm.fsdp, "sync_optimizer"):
+        trainer.asm.fsdp.sync_optimizer()
     out = {}
     tp_rank = trainer.env.topo.coord("tp")
     for p in trainer.model.parameters():

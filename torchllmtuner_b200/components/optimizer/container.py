@@ -19,9 +19,13 @@ class OptimizersContainer:
     def __init__(self, optimizers):
         self.optimizers = list(optimizers)
 
-    def step(self, clip_coef=None) -> None:
+    def step(self, clip_coef=None, overlap: bool = False) -> None:
+        """`overlap`: let optimizers that can (sharded AdamW on one shard rank) run their update under the next forward."""
         for o in self.optimizers:
-            o.step(clip_coef)
+            if overlap and isinstance(o, ShardedAdamW):
+                o.step(clip_coef, overlap=True)
+            else:
+                o.step(clip_coef)
 
     def zero_grad(self) -> None:
         for o in self.optimizers:

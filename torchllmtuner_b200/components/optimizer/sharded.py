@@ -138,27 +138,55 @@ class ShardedAdamW:
         for u in self.units:
             u.has_grad = False
 
+    def overlap_order(self):
+        """Units in the order the next forward needs them: everything outside the blocks except the head first, the
+        blocks in order, the head (needed after the last block) last."""
+        first = [u for u in self.units if getattr(u, "block_index", None) is None and u.name != "head"]
+        blocks = [u for u in self.units if getattr(u, "block_index", None) is not None]
+        last = [u for u in self.units if getattr(u, "block_index", None) is None and u.name == "head"]
+        return first + blocks + last
+
     @torch.no_grad()
-    def step(self, clip_coef: torch.Tensor | None = None) -> None:
+    def step(self, clip_coef: torch.Tensor | None = None, overlap: bool = False) -> None:
+        """`overlap=True` (single shard rank, device-resident moments, CUDA): the update kernels go to a second stream in
+        the order the next forward needs the units and record one event per unit; the forward waits per unit
+        (`FSDPRuntime.wait_param_update`), so the memory-bound update of later layers runs under the GEMMs of earlier
+        ones. The arithmetic and its order per element are unchanged."""
         self.step_count += 1
+        overlap = (overlap and not self.host_moments and all(u.world == 1 for u in self.units)
+                   and self.units and self.units[0].master.is_cuda)
+        if overlap:
+            if getattr(self, "_side", None) is None:
+                self._side = torch.cuda.Stream(self.units[0].master.device)
+            self._side.wait_stream(torch.cuda.current_stream())          # gradients and the clip coefficient are ready
+            with torch.cuda.stream(self._side):
+                for u in self.overlap_order():
+                    self._step_unit(u, clip_coef)
+                    ev = torch.cuda.Event()
+                    ev.record(self._side)
+                    u.updated_event = ev
+            return
         for u in self.units:
-            if not u.has_grad:
-                continue
-            st = self.state[u.name]
-            lowp = u.shard_lowp if u.separate_master else None
-            for lo, hi, gi in self._runs[u.name]:
-                g = self.param_groups[gi]
-                kw = dict(lr=g["lr"], beta1=g["betas"][0], beta2=g["betas"][1], eps=g["eps"], weight_decay=g["weight_decay"],
-                          step=self.step_count, decoupled=self.decoupled, clip_coef=clip_coef)
-                if not self.host_moments:
-                    ops.adamw_step_(u.master[lo:hi], u.grad_shard[lo:hi], st["exp_avg"][lo:hi], st["exp_avg_sq"][lo:hi],
-                                    p_lowp=None if lowp is None else lowp[lo:hi], **kw)
-                else:
-                    def update(a, b, mv, _u=u, _lowp=lowp, _kw=kw):
-                        ops.adamw_step_(_u.master[a:b], _u.grad_shard[a:b], mv[0], mv[1], p_lowp=None if _lowp is None else _lowp[a:b], **_kw)
-                    self.stager.run([st["exp_avg"], st["exp_avg_sq"]], lo, hi, update)
+            self._step_unit(u, clip_coef)
         if self.stager is not None:
             self.stager.finish()
+
+    def _step_unit(self, u, clip_coef) -> None:
+        if not u.has_grad:
+            return
+        st = self.state[u.name]
+        lowp = u.shard_lowp if u.separate_master else None
+        for lo, hi, gi in self._runs[u.name]:
+            g = self.param_groups[gi]
+            kw = dict(lr=g["lr"], beta1=g["betas"][0], beta2=g["betas"][1], eps=g["eps"], weight_decay=g["weight_decay"],
+                      step=self.step_count, decoupled=self.decoupled, clip_coef=clip_coef)
+            if not self.host_moments:
+                ops.adamw_step_(u.master[lo:hi], u.grad_shard[lo:hi], st["exp_avg"][lo:hi], st["exp_avg_sq"][lo:hi],
+                                p_lowp=None if lowp is None else lowp[lo:hi], **kw)
+            else:
+                def update(a, b, mv, _u=u, _lowp=lowp, _kw=kw):
+                    ops.adamw_step_(_u.master[a:b], _u.grad_shard[a:b], mv[0], mv[1], p_lowp=None if _lowp is None else _lowp[a:b], **_kw)
+                self.stager.run([st["exp_avg"], st["exp_avg_sq"]], lo, hi, update)
 
     # ------------------------------------------------------------------ checkpoint state keyed by parameter FQN
     def state_dict_shards(self):

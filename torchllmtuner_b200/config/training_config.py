@@ -111,6 +111,7 @@ class TrainingConfig:
     grad_norm_precision: str = "float32"
     gc_freq: int = 50
     gradient_accumulation_steps: int = 1
+    overlap_optimizer_step: bool = True          # the training loop lets the parameter update run under the next forward (one shard rank)
     chunked_loss_num_chunks: int = 0
     dump_folder: str = "./outputs"
     checkpoint_config: CheckpointConfig = field(default_factory=CheckpointConfig)

@@ -341,6 +341,9 @@ class FSDPRuntime:
 
     def before_forward(self) -> None:
         """Wait for the refresh of persistently gathered units (embedding, head) issued after the last step."""
+        for u in self.units:               # whatever the forward touches before its first block; the head is waited for later
+            if id(u) not in self._block_owned() and u.name != "head":
+                self.wait_param_update(u)
         for u in self.units:
             if getattr(u, "persistent", False) and u.world > 1:
                 self.unshard(u)
@@ -396,7 +399,34 @@ class FSDPRuntime:
             return bool(mask[i])
         return i % self.ac_save_every != 0
 
+    # ------------------------------------------------------------------ optimizer updates that overlap the next forward
+    def wait_param_update(self, u: FlatUnit) -> None:
+        """The optimizer may still be rewriting this unit on its own stream (see `ShardedAdamW.step`): the first use of the
+        unit's parameters in the next forward waits for exactly that unit's update."""
+        ev = getattr(u, "updated_event", None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            u.updated_event = None
+
+    def sync_optimizer(self) -> None:
+        """Everything that reads masters, moments or parameters outside the forward path (EMA, checkpoints, exports, a
+        caller inspecting the model) first lets every pending update finish."""
+        for u in self.units:
+            self.wait_param_update(u)
+
+    def _block_owned(self) -> set:
+        owned = getattr(self, "_owned_ids", None)
+        if owned is None:
+            owned = self._owned_ids = {id(u) for us in self.block_units.values() for u in us}
+        return owned
+
     def run_block(self, i: int, layer: nn.Module, x: torch.Tensor, ctx) -> torch.Tensor:
+        for u in self._units(i):
+            self.wait_param_update(u)
+        if self.block_units and i == max(self.block_units):       # head, final norm: updated last, needed after the last block
+            for u in self.units:
+                if id(u) not in self._block_owned():
+                    self.wait_param_update(u)
         grad_mode = self.model.training and torch.is_grad_enabled()
         per_op = self.ac_mode == "selective" and getattr(self.model, "ac_per_op", False)
         ac = grad_mode and (self.ac_mode == "full" or per_op or (self.ac_mode == "selective" and self._recomputes(i)))

@@ -88,15 +88,20 @@ class TrainingEngine:
             b.tokens_per_expert_E.copy_(c)
             b.update_expert_bias()
 
-    def optimizer_step(self, step: int) -> torch.Tensor:
+    def optimizer_step(self, step: int, overlap: bool = False) -> torch.Tensor:
+        """`overlap=True`: the parameter update may still be running on the optimizer's stream when this returns; the next
+        forward waits unit by unit, every other reader calls `rt.sync_optimizer()` first."""
         self.rt.wait_reductions()
         norm = self.clipper()
         self._update_moe_bias()
-        self.optimizers.step(self.clipper.coef)
+        self.optimizers.step(self.clipper.coef, overlap=overlap)
         self.rt.post_optimizer()
         self.lr_schedulers.step()
         if self.ema is not None:
+            self.rt.sync_optimizer()
             self.ema.step(step)
+        elif not overlap:
+            self.rt.sync_optimizer()
         return norm
 
     def finish_step(self, step: int, loss_value: float | None = None) -> None:

@@ -88,9 +88,12 @@ class Trainer:
         """Read one micro-batch; all data-parallel ranks agree on (ready / exhausted / error)."""
         return fetch_batch(self.data_iterator, self.env)
 
-    def train_step(self, batches=None, read_stats: bool = True) -> StepResult | None:
+    def train_step(self, batches=None, read_stats: bool = True, overlap_optimizer: bool = False) -> StepResult | None:
         """One optimizer step. `batches` overrides the data loader (a list of trainer batches, which may already
-        live on the device); `read_stats=False` skips the single device->host read and returns None."""
+        live on the device); `read_stats=False` skips the single device->host read and returns None.
+        `overlap_optimizer=True` (what the training loop passes when `overlap_optimizer_step` is set) lets the parameter
+        update run on its own stream under the next step's forward; callers that look at parameters or optimizer state
+        between steps leave it off, or call `self.asm.fsdp.sync_optimizer()` first."""
         t = self.config.training
         eng = self.engine
         eng.begin_step()
@@ -103,7 +106,7 @@ class Trainer:
                 eng.forward_backward(b, gv, is_last_microbatch=(i == len(batches) - 1))
         step = self.progress.step + 1
         with nvtx_range("optimizer_step"):
-            norm = eng.optimizer_step(step)
+            norm = eng.optimizer_step(step, overlap=overlap_optimizer)
         if not read_stats:
             self.progress.step = step
             return None
@@ -139,7 +142,7 @@ class Trainer:
             while self.progress.step < t.steps:
                 self.observer.begin_step()
                 try:
-                    res = self.train_step()
+                    res = self.train_step(overlap_optimizer=t.overlap_optimizer_step)
                 except DataloaderExhaustedError:
                     self.logger.info("data exhausted; stopping")
                     break
