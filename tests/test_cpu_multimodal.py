@@ -158,3 +158,78 @@ def test_kimi_k3_with_moonvit_trains_through_the_trainer(tmp_path):
         losses.append(tr.train_step().loss)
     assert losses[-1] < losses[0] - 0.2, losses
     tr.close()
+
+
+# ------------------------------------------------------------------------------------------ local-file recipes
+def _fixtures(tmp_path):
+    """Three record shapes over PNG files, a whitespace vocabulary that knows the placeholder tokens."""
+    import json
+    from PIL import Image
+    import numpy as np
+    from torchllmtuner_b200.components.tokenizer.whitespace import WhitespaceTokenizer
+    rng = np.random.default_rng(0)
+    for i in range(6):
+        Image.fromarray(rng.integers(0, 255, (40 + 8 * i, 72 - 4 * i, 3), dtype=np.uint8)).save(tmp_path / f"im{i}.png")
+    words = [f"w{i}" for i in range(40)]
+    specials = ["<|image_pad|>", "<|video_pad|>", "<|vision_start|>", "<|vision_end|>", "<|endoftext|>"]
+    WhitespaceTokenizer(specials + words).save(str(tmp_path / "vocab.json"))
+    text = lambda n, a=0: " ".join(words[(a + j) % 40] for j in range(n))  # noqa: E731
+    with open(tmp_path / "captions.jsonl", "w") as f:
+        for i in range(6):
+            f.write(json.dumps({"image": f"im{i}.png", "caption": text(6 + i, i)}) + "\n")
+    with open(tmp_path / "interleaved.jsonl", "w") as f:
+        for i in range(4):
+            f.write(json.dumps({"texts": [text(5, i), None, text(7, i + 3), None], "images": [None, f"im{i}.png", None, f"im{i + 1}.png"]}) + "\n")
+    with open(tmp_path / "mixed.jsonl", "w") as f:
+        f.write(json.dumps({"text": f"{text(4)} <|image_pad|> {text(5, 9)} <|video_pad|> {text(3, 20)}", "images": ["im0.png"],
+                            "videos": [["im2.png"] * 4]}) + "\n")
+        f.write(json.dumps({"text": text(12, 5)}) + "\n")
+    return tmp_path
+
+
+def test_local_recipes_build_samples_from_files(tmp_path):
+    from torchllmtuner_b200.components.tokenizer.huggingface import MultimodalTokenizer
+    from torchllmtuner_b200.components.tokenizer.whitespace import WhitespaceTokenizer
+    from torchllmtuner_b200.config.data_config import DataloaderConfig as DataConfig
+    from torchllmtuner_b200.datasets.multimodal_recipes import MultimodalProcessor, load_image
+    from torchllmtuner_b200.datasets.sources import IndexedJsonlSource
+    root = _fixtures(tmp_path)
+    tok = MultimodalTokenizer(WhitespaceTokenizer.from_file(str(root / "vocab.json")), DataConfig())
+    assert load_image(str(root / "im0.png")).shape == (3, 40, 72)
+    spec = mp.VisionSpec(max_pixels=14 * 14 * 4 * 8, min_pixels=28 * 28 * 4)
+    cap = MultimodalProcessor(tok, "local_captions", spec, root=str(root))(IndexedJsonlSource(str(root / "captions.jsonl"))[0])
+    n_img = mp.calculate_vision_tokens(cap.grids[0])
+    assert cap.tokens[0] == tok.vision_start_id and cap.tokens[1:1 + n_img] == [tok.image_id] * n_img and cap.tokens[1 + n_img] == tok.vision_end_id
+    assert cap.labels[:n_img + 2] == [IGNORE_INDEX] * (n_img + 2) and cap.labels[n_img + 2] == cap.tokens[n_img + 2]
+    inter = MultimodalProcessor(tok, "local_interleaved", spec, root=str(root))(IndexedJsonlSource(str(root / "interleaved.jsonl"))[1])
+    assert len(inter.grids) == 2 and inter.patches.shape[0] == sum(t * h * w for t, h, w in inter.grids)
+    mixed_src = IndexedJsonlSource(str(root / "mixed.jsonl"))
+    proc = MultimodalProcessor(tok, "local_multimodal", spec, root=str(root))
+    mixed = proc(mixed_src[0])
+    assert [g[0] for g in mixed.grids] == [1, 2]                        # an image, then a clip of 4 frames = 2 temporal steps
+    assert proc(mixed_src[1]).grids == [] and proc(mixed_src[1]).patches.numel() == 0
+    with pytest.raises(Exception, match="placeholder"):
+        proc({"text": "w1 w2", "images": ["im0.png"]})
+
+
+def test_vision_language_model_trains_on_local_image_files(tmp_path):
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    root = _fixtures(tmp_path)
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(dump_folder=str(tmp_path / "run"), steps=4, model_name_or_path="qwen3_5_vl", dataset="local_captions",
+                             dataset_path=str(root / "captions.jsonl"), tokenizer_backend="whitespace", tokenizer_path=str(root / "vocab.json"),
+                             vocab_size=64, hidden_size=64, num_hidden_layers=4, num_attention_heads=2, num_key_value_heads=2, max_seq_len=96,
+                             global_batch_size=2, learning_rate=3e-3, mm_max_pixels=14 * 14 * 4 * 8, shuffle=False))
+    cfg.model.arch_overrides = dict(head_dim=32, image_token_id=6, vision=dict(hidden_size=64, intermediate_size=128, depth=1, num_heads=2))
+    tr = Trainer(cfg)
+    first = next(iter(tr.dataloader))
+    assert first["patches"] is not None and (first["input"] == 6).sum() > 0
+    state = tr.dataloader.state_dict()
+    second = next(tr.dataloader)
+    tr.dataloader.load_state_dict(state)
+    assert torch.equal(next(tr.dataloader)["input"], second["input"])          # resumable
+    tr.dataloader.load_state_dict({**state, "delivered": 0})
+    tr.data_iterator = iter(tr.dataloader)
+    losses = [tr.train_step().loss for _ in range(3)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0] + 0.5
+    tr.close()

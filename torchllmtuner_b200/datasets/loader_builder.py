@@ -29,6 +29,10 @@ def build_dataloader(data_cfg, *, vocab_size: int, global_batch: int, seq_len: i
     if name == "random_packed":
         src = RandomPackedSource(vocab_size, global_batch, seq_len, seed, data_cfg.packed_min_doc_len, data_cfg.packed_max_doc_len)
         return RandomTokenDataLoader(src, dp_rank, dp_degree, rows_per_rank, pin_memory)
+    if name in ("local_captions", "local_interleaved", "local_multimodal"):
+        from .multimodal_recipes import build_multimodal_dataloader
+        return build_multimodal_dataloader(data_cfg, model=model, vocab_size=vocab_size, seq_len=seq_len, seed=seed, dp_rank=dp_rank,
+                                           dp_degree=dp_degree, rows_per_rank=rows_per_rank, pin_memory=pin_memory, split=split)
     try:
         from .text import build_text_dataloader
     except ImportError as e:  # pragma: no cover
