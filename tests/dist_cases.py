@@ -49,6 +49,10 @@ def train_case(flat: dict, arch: dict | None, out_path: str, steps: int = 3, rep
                     extra["tp_fused"] = dict(c.stats)
             except Exception:
                 pass
+            fused = getattr(tr.asm.fsdp, "fused", None)
+            if fused is not None and fused.queue is not None:
+                extra["fsdp_fused_units"] = len(fused.units)
+                extra["fsdp_block_units"] = sum(len(us) for us in tr.asm.fsdp.block_units.values())
             json.dump({"loss": losses, "grad_norm": norms, **extra}, f)
     tr.close()
     import torch.distributed as dist

@@ -26,6 +26,18 @@ def test_fsdp2_gpu_matches_single_gpu():
         assert max(abs(a - b) / max(a, 1e-6) for a, b in zip(ref["grad_norm"], got["grad_norm"])) < 5e-2, (impl, ref, got)
 
 
+def test_fsdp2_with_blocks_of_different_sizes_fuses_the_common_size():
+    """Kimi-Linear blocks come in three sizes (dense first layer, KDA + sparse, latent attention + sparse). The most common
+    size rides the peer-memory collectives, the odd units take NCCL in the same runtime; two GPUs reproduce one."""
+    _need(2)
+    arch = dict(linear_heads=4, linear_head_dim=64, kda_chunk_size=16, qk_nope_head_dim=32, qk_rope_head_dim=32, v_head_dim=64, kv_lora_rank=64)
+    base = dict(model_name_or_path="kimi_linear", num_hidden_layers=6)
+    ref = run_ranks(1, _flat(**base), arch=arch, device="cuda")
+    got = run_ranks(2, _flat(data_parallel_shard_size=2, **base), arch=arch, device="cuda")
+    assert got.get("fsdp_fused_units", 0) >= 3 and got["fsdp_fused_units"] < got["fsdp_block_units"], got
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (ref, got)
+
+
 MOE = dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128)
 
 

@@ -134,3 +134,45 @@ def test_optimizer_update_under_the_next_forward_changes_nothing():
             assert torch.equal(a, u.master)
     finally:
         tr.close()
+
+
+def test_checkpoint_resume_is_bit_exact_on_the_gpu(tmp_path):
+    """Saved from device shards as boxes of whole tensors (through pinned staging, asynchronously), resumed into a fresh
+    trainer: the next steps repeat bit for bit. The save follows an overlapped optimizer update, so it must wait for it."""
+    import os
+    import shutil
+    kw = dict(dump_folder=str(tmp_path), enable=True, interval=2, steps=4, last_save_model_only=False, async_mode="async_with_pinned_mem",
+              exclude_from_loading=[])
+    tr = Trainer(_cfg(**kw))
+    ref = []
+    for _ in range(4):
+        r = tr.train_step(overlap_optimizer=True)
+        ref.append(r.loss)
+        tr.checkpointer.save(r.step)
+    tr.close()
+    assert os.path.exists(os.path.join(str(tmp_path), "checkpoint", "step-2", ".metadata"))
+    shutil.rmtree(os.path.join(str(tmp_path), "checkpoint", "step-4"))
+    tr2 = Trainer(_cfg(**kw))
+    assert tr2.checkpointer.load() and tr2.progress.step == 2
+    got = [tr2.train_step().loss for _ in range(2)]
+    tr2.close()
+    assert got == ref[2:], (got, ref)
+
+
+def test_vision_language_model_trains_on_the_gpu(tmp_path):
+    """Tower (tcgen05 GEMMs, the non-causal attention kernel) + Qwen3.5 decoder under the Trainer on synthetic image-text rows."""
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(dict(model_name_or_path="qwen3_5_vl", dataset="random_multimodal", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                        num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, global_batch_size=2, max_seq_len=512, steps=4, seed=0,
+                        dump_folder=str(tmp_path), deterministic=False, learning_rate=2e-3, mm_max_pixels=14 * 14 * 4 * 16))
+    cfg.model.arch_overrides = dict(head_dim=64, linear_key_head_dim=64, linear_value_head_dim=64,
+                                    vision=dict(hidden_size=128, intermediate_size=256, depth=2, num_heads=2))
+    tr = Trainer(cfg)
+    try:
+        losses = []
+        for _ in range(4):
+            tr.dataloader.cursor = 0
+            losses.append(tr.train_step().loss)
+    finally:
+        tr.close()
+    assert losses[-1] < losses[0] - 0.3, losses

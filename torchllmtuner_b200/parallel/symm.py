@@ -188,19 +188,25 @@ class FusedFSDPComm:
         self.rt, self.ext = rt, load()
         self.world, self.rank, self.group = rt.world, rt.rank, rt.group
         self.units = [u for us in rt.block_units.values() for u in us if not u.is_expert and u.world == rt.world and not getattr(u, "persistent", False)]
-        self._ids = {id(u) for u in self.units}
         if not self.units:
+            self._ids = set()
             self.queue = None
             return
-        padded = {u.padded for u in self.units}
-        if len(padded) != 1:
-            # the two gradient slots and the chunk arithmetic assume blocks of one size; models whose blocks differ
-            # (hybrid mixers, a dense first layer before sparse ones) keep the NCCL collectives of the same runtime
+        # The two gradient slots and the chunk arithmetic assume units of one size. Where decoder blocks differ (hybrid
+        # mixers, a dense first layer before sparse ones) the most common size takes the peer-memory path and the odd
+        # units keep the NCCL collectives of the same runtime (`supports(u)` is the switch, unit by unit).
+        sizes: dict[int, int] = {}
+        for u in self.units:
+            sizes[u.padded] = sizes.get(u.padded, 0) + 1
+        common = max(sizes, key=lambda k: (sizes[k], k))
+        if len(sizes) > 1:
             from ..utils import get_logger
-            get_logger().info(f"fused FSDP collectives are off: decoder blocks have {len(padded)} different sizes")
-            self.queue = None
-            return
-        self.padded = padded.pop()
+            odd = sum(n for k, n in sizes.items() if k != common)
+            get_logger().info(f"fused FSDP collectives cover {sizes[common]} of {len(self.units)} block units (one size); {odd} "
+                              f"units of {len(sizes) - 1} other sizes use NCCL")
+        self.units = [u for u in self.units if u.padded == common]
+        self._ids = {id(u) for u in self.units}
+        self.padded = common
         esz = self.units[0].shard_lowp.element_size()
         self.esz = esz
         off, self.shard_off = 0, {}
