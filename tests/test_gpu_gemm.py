@@ -149,3 +149,28 @@ def test_bounded_wait_expires_into_status_word():
     ext.gemm(a, b, out, False, False, False, 0)
     check_status("after recovery")
     assert torch.allclose(out.float(), a.float() @ b.float().t(), atol=0.5, rtol=5e-2)
+
+
+def test_projections_of_the_same_rows_sum_their_input_gradient_in_the_epilogue():
+    """`ops.linears(x, W0, W1, W2)`: the same outputs as three `ops.linear` calls; dx is accumulated by the second and third
+    GEMM's epilogue instead of by elementwise additions, so it may differ from the separate form by one bf16 rounding."""
+    from torchllmtuner_b200 import ops
+    torch.manual_seed(0)
+    x = (torch.randn(1024, 512, device="cuda") * 0.5).bfloat16().requires_grad_()
+    ws = [(torch.randn(n, 512, device="cuda") * 0.05).bfloat16().requires_grad_() for n in (512, 128, 256)]
+    gs = [torch.randn(1024, n, device="cuda").bfloat16() for n in (512, 128, 256)]
+    ys = ops.linears(x, *ws)
+    torch.autograd.backward(ys, gs)
+    got = [x.grad.clone()] + [w.grad.clone() for w in ws]
+    x.grad = None
+    for w in ws:
+        w.grad = None
+    ys2 = [ops.linear(x, w) for w in ws]
+    for a, b in zip(ys, ys2):
+        assert torch.equal(a, b)
+    torch.autograd.backward(ys2, gs)
+    ref_dx = sum(g.float() @ w.float() for g, w in zip(gs, ws))
+    assert (got[0].float() - ref_dx).abs().max() <= 0.02 * ref_dx.abs().max()
+    assert (got[0].float() - x.grad.float()).abs().max() <= 0.02 * ref_dx.abs().max()
+    for a, w in zip(got[1:], ws):
+        assert torch.equal(a, w.grad)

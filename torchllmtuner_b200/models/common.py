@@ -59,7 +59,8 @@ class GatedMLP(nn.Module):
         if hasattr(x, "linears"):
             g, u = x.linears(self.gate_proj.weight, self.up_proj.weight)
             return self.down_proj(ops.swiglu(g, u))
-        return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
+        g, u = ops.linears(x, self.gate_proj.weight, self.up_proj.weight)
+        return self.down_proj(ops.swiglu(g, u))
 
 
 class Embedding(nn.Module):

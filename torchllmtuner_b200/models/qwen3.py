@@ -126,7 +126,8 @@ class Qwen3Attention(nn.Module):
             qkv = self.qkv_proj(x)
             nq, nk = self.num_heads * d, self.num_kv_heads * d
             return (qkv[:, :nq].view(T, -1, d), qkv[:, nq:nq + nk].view(T, -1, d), qkv[:, nq + nk:].view(T, -1, d))
-        return (self.q_proj(x).view(T, -1, d), self.k_proj(x).view(T, -1, d), self.v_proj(x).view(T, -1, d))
+        q, k, v = ops.linears(x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
+        return q.view(T, -1, d), k.view(T, -1, d), v.view(T, -1, d)
 
     def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
         q, k, v = self.project_qkv(x)

@@ -162,6 +162,55 @@ class _KeptLinear(torch.autograd.Function):
         return (dy2 @ w.to(dy2.dtype)).reshape(x.shape), (dy2.t() @ x2).to(w.dtype), None
 
 
+class _MultiLinear(torch.autograd.Function):
+    """y_i = x W_i^T for several weights that read the same rows (q / k / v, gate / up). The input gradient is summed by the
+    GEMM epilogues themselves (dx = dy_0 W_0, then dx += dy_i W_i with the accumulating epilogue) instead of by one
+    elementwise addition per extra consumer, which autograd would otherwise insert."""
+
+    @staticmethod
+    def forward(ctx, x, *ws):
+        x2 = _2d(x)
+        ctx.save_for_backward(x2, *ws)
+        ctx.xshape = x.shape
+        return tuple(gemm(x2, w).reshape(*x.shape[:-1], w.shape[0]) for w in ws)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *ws = ctx.saved_tensors
+        dx = None
+        if ctx.needs_input_grad[0]:
+            for dy, w in zip(dys, ws):
+                if dy is None:
+                    continue
+                if dx is None:
+                    dx = gemm(_2d(dy), w, b_mn=True)
+                else:
+                    gemm(_2d(dy), w, b_mn=True, out=dx, accumulate=True)
+            dx = None if dx is None else dx.reshape(ctx.xshape)
+        dws = []
+        for i, (dy, w) in enumerate(zip(dys, ws)):
+            if dy is None or not ctx.needs_input_grad[1 + i]:
+                dws.append(None)
+                continue
+            main = getattr(w, "main_grad", None)
+            if main is not None:
+                gemm(_2d(dy), x2, a_mn=True, b_mn=True, out=main, accumulate=getattr(w, "main_grad_initialized", False))
+                w.main_grad_initialized = True
+                dws.append(None)
+            else:
+                dws.append(gemm(_2d(dy), x2, a_mn=True, b_mn=True, out_dtype=w.dtype))
+        return (dx, *dws)
+
+
+def linears(x: torch.Tensor, *ws: torch.Tensor):
+    """Several bias-free projections of the same rows; one autograd node on the kernel path, plain `linear` calls elsewhere
+    (CPU, odd shapes, and under per-op checkpointing, whose keep / replay bookkeeping is per projection)."""
+    if (_SAC is None and _use_cuda(x) and x.dtype == torch.bfloat16 and len(ws) > 1
+            and not any(w.shape[0] % 8 or w.shape[1] % 8 for w in ws)):
+        return _MultiLinear.apply(x, *ws)
+    return tuple(linear(x, w) for w in ws)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     # a TMA row must start on a 16-byte boundary: projections with fewer than 8 (or an odd number of) features, e.g. one
     # gate value per head, cannot be tiled by the tcgen05 kernel and take the plain library product
