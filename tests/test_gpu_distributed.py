@@ -157,3 +157,29 @@ def test_hybrid_families_sequence_and_tensor_parallel_on_gpus(name, flat):
     ref = run_ranks(1, _flat(**base), arch=HYBRID, device="cuda")
     got = run_ranks(2, _flat(num_hidden_layers=4, **flat), arch=HYBRID, device="cuda")
     assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 4e-2, (name, ref, got)
+
+
+FAITHFUL = dict(head_dim=64, linear_heads=4, linear_head_dim=64, kda_chunk_size=16, qk_nope_head_dim=32, qk_rope_head_dim=32, v_head_dim=64,
+                kv_lora_rank=64, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=64, linear_value_head_dim=64,
+                linear_chunk_size=32)
+
+
+@pytest.mark.parametrize("name,flat", [
+    ("kimi_linear_kcp2", dict(model_name_or_path="kimi_linear", context_parallel_kcp_size=2, data_parallel_shard_size=1)),
+    ("kimi_k3_kcp2", dict(model_name_or_path="kimi_k3", context_parallel_kcp_size=2, data_parallel_shard_size=1)),
+    ("qwen3_5_moe_kv2", dict(model_name_or_path="qwen3_5_moe", context_parallel_kv_allgather_size=2, data_parallel_shard_size=1)),
+    ("deepseek_v4_kv2", dict(model_name_or_path="deepseek_v4", context_parallel_kv_allgather_size=2, data_parallel_shard_size=1)),
+    ("deepseek_v4_ep2", dict(model_name_or_path="deepseek_v4", expert_parallel_size=2, data_parallel_shard_size=2)),
+])
+def test_model_families_sequence_and_expert_parallel_on_gpus(name, flat):
+    """The families' own sequence-parallel paths on NCCL and the CUDA kernels: convolution history and recurrent state
+    handed across ranks (Kimi, Qwen3.5), the gathered shared key/value head and compressor inputs (DeepSeek-V4), and
+    hash-routed plus biased top-k experts under expert parallelism."""
+    _need(2)
+    arch = {k: v for k, v in FAITHFUL.items() if v is not None}
+    if flat["model_name_or_path"] == "deepseek_v4":
+        arch = dict(head_dim=64, qk_rope_head_dim=16, index_head_dim=32, q_lora_rank=64, o_lora_rank=32, sliding_window=32)
+    base = dict(model_name_or_path=flat["model_name_or_path"], num_hidden_layers=4)
+    ref = run_ranks(1, _flat(**base), arch=arch, device="cuda")
+    got = run_ranks(2, _flat(num_hidden_layers=4, **flat), arch=arch, device="cuda")
+    assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 5e-2, (name, ref, got)

@@ -344,8 +344,8 @@ class FSDPRuntime:
         for u in self.units:               # whatever the forward touches before its first block; the head is waited for later
             if id(u) not in self._block_owned() and u.name != "head":
                 self.wait_param_update(u)
-        for u in self.units:
-            if getattr(u, "persistent", False) and u.world > 1:
+        for u in self.units:                # the head's refresh keeps running under the forward; the last block waits for it
+            if getattr(u, "persistent", False) and u.world > 1 and not (u.name == "head" and self.block_units):
                 self.unshard(u)
 
     def finish_backward(self) -> None:
@@ -427,6 +427,8 @@ class FSDPRuntime:
             for u in self.units:
                 if id(u) not in self._block_owned():
                     self.wait_param_update(u)
+                    if u.name == "head" and getattr(u, "persistent", False) and u.world > 1:
+                        self.unshard(u)
         grad_mode = self.model.training and torch.is_grad_enabled()
         per_op = self.ac_mode == "selective" and getattr(self.model, "ac_per_op", False)
         ac = grad_mode and (self.ac_mode == "full" or per_op or (self.ac_mode == "selective" and self._recomputes(i)))
