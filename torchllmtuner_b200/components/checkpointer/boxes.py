@@ -20,7 +20,7 @@ from dataclasses import dataclass
 
 import torch
 from torch.distributed.checkpoint.default_planner import DefaultLoadPlanner, DefaultSavePlanner
-from torch.distributed.checkpoint.metadata import (BytesStorageMetadata, ChunkStorageMetadata, MetadataIndex, TensorProperties,
+from torch.distributed.checkpoint.metadata import (ChunkStorageMetadata, MetadataIndex, TensorProperties,
                                                    TensorStorageMetadata)
 from torch.distributed.checkpoint.planner import LoadPlan, SavePlan, TensorWriteData, WriteItem, WriteItemType
 from torch.distributed.checkpoint.planner_helpers import _create_read_items, _create_write_items, create_read_items_for_chunk_list

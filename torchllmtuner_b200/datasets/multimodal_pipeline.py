@@ -17,7 +17,6 @@ by its step cursor, which makes the whole path testable and benchmarkable offlin
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 
 import torch
