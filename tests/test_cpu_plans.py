@@ -237,3 +237,40 @@ def test_trainer_layout_binds_optimizer_and_checkpointer(tmp_path):
     with pytest.raises(LayoutError):
         tr.checkpointer.save(2, force=True)
     tr.close()
+
+
+def test_replacement_map_composes_events_by_identity():
+    import gc
+    import torch
+    import torch.nn as nn
+    from torchllmtuner_b200.parallel.replacements import ReplacementMap
+    rm = ReplacementMap()
+    a, b, c, d = (nn.Parameter(torch.zeros(2)) for _ in range(4))          # equal values: only identity may tell them apart
+    rm.record(parameters={a: (b,)})
+    rm.record(parameters={b: (c, d)})
+    assert rm.parameters(a) == (c, d) and rm.parameters(b) == (c, d) and rm.parameters(c) == (c,)
+    rm.record(parameters={c: ()})                                           # removal
+    assert rm.parameters(a) == (d,)
+    m0, m1, m2 = nn.Linear(2, 2), nn.Linear(2, 2), nn.Linear(2, 2)
+    rm.record(modules={m0: m1})
+    rm.record(modules={m1: m2})
+    assert rm.module(m0) is m2 and rm.module(m2) is m2
+    with pytest.raises(TypeError):
+        rm.record(parameters={a: b})
+    n = len(rm._params)
+    del a
+    gc.collect()
+    assert len(rm._params) == n - 1                                         # sources are held weakly
+
+
+def test_heads_must_divide_by_the_axes_that_cut_them():
+    from torchllmtuner_b200.errors import UnsupportedCombinationError
+    from torchllmtuner_b200.models.qwen3 import Qwen3Config, Qwen3ForCausalLM
+    from torchllmtuner_b200.parallel.attention_heads import head_counts, require_heads_divisible_by
+    m = Qwen3ForCausalLM(Qwen3Config(num_attention_heads=8, num_key_value_heads=2, hidden_size=64), device="meta")
+    assert head_counts(m) == [("num_attention_heads", 8), ("num_key_value_heads", 2)]
+    require_heads_divisible_by(m, size=2, axis="tp", why="whole heads per rank")
+    with pytest.raises(UnsupportedCombinationError, match=r"num_key_value_heads \(2\) must be divisible by tp \(4\): whole heads"):
+        require_heads_divisible_by(m, size=4, axis="tp", why="whole heads per rank")
+    with pytest.raises(UnsupportedCombinationError, match="Ulysses"):
+        m.validate_parallel(tp=2, cp_ulysses=2)

@@ -223,12 +223,12 @@ class Qwen3ForCausalLM(nn.Module):
 
     def validate_parallel(self, tp: int = 1, cp_ulysses: int = 1, ep: int = 1) -> None:
         from ..errors import UnsupportedCombinationError
+        from ..parallel.attention_heads import require_heads_divisible_by
         c = self.config
-        if c.num_key_value_heads % tp or c.num_attention_heads % tp:
-            raise UnsupportedCombinationError(f"tensor_parallel_size {tp} must divide the head counts "
-                                              f"({c.num_attention_heads} q / {c.num_key_value_heads} kv)")
-        if (c.num_attention_heads // tp) % cp_ulysses or (c.num_key_value_heads // tp) % cp_ulysses:
-            raise UnsupportedCombinationError(f"ulysses degree {cp_ulysses} must divide the per-rank head counts")
+        require_heads_divisible_by(self, size=tp, axis="tensor_parallel_size",
+                                   why="every tensor-parallel rank owns whole query and key/value heads")
+        require_heads_divisible_by(self, size=tp * cp_ulysses, axis="tensor_parallel_size * context_parallel_ulysses_size",
+                                   why="the Ulysses exchange hands each rank whole heads of its tensor-parallel share")
         if c.num_experts and c.num_experts % ep:
             raise UnsupportedCombinationError(f"expert_parallel_size {ep} must divide num_experts {c.num_experts}")
 

@@ -26,6 +26,7 @@ from typing import Mapping, Sequence
 import torch.nn as nn
 
 from ..errors import LLMTunerError
+from .replacements import ReplacementMap
 
 
 class LayoutError(LLMTunerError):
@@ -58,6 +59,7 @@ class ModelPartLayout:
     topology: Mapping | None = None
     bindings: dict[str, nn.Parameter] = field(default_factory=dict)
     replaced: dict[int, nn.Parameter] = field(default_factory=dict)     # id(old parameter) -> its replacement
+    replacements: ReplacementMap = field(default_factory=ReplacementMap)   # composed over every refresh
     _captured: bool = field(default=False, repr=False)
 
     # ------------------------------------------------------------------ capture / refresh
@@ -78,6 +80,8 @@ class ModelPartLayout:
                     raise LayoutError(f"layout refresh: two distinct parameters were merged at {path!r}")
                 if new is not old:
                     self.replaced[id(old)] = new
+            self.replacements.record(parameters={old: (new,) for old, new in ((o, forward[id(o)]) for o in dict.fromkeys(self.bindings.values()))
+                                                 if new is not old})
         self.bindings = current
         self._captured = True
 
@@ -126,6 +130,9 @@ class ModelPartLayout:
         for new in self.replaced.values():
             if id(new) not in live:
                 raise LayoutError("model layout is stale: a recorded replacement parameter is no longer registered")
+        for _src, targets in self.replacements.parameter_targets():
+            if any(id(t) not in live for t in targets):
+                raise LayoutError("model layout is stale: a parameter that replaced an earlier one is no longer registered")
         return self.state_names
 
     def snapshot(self) -> LayoutSnapshot:
