@@ -64,6 +64,26 @@ def test_qk_norm_rope(T, Hq, Hkv, d, with_norm):
         _close(a, b, "reduced" if n in ("dqw", "dkw") else None, n)
 
 
+def test_qk_norm_weight_gradient_is_the_same_bits_on_every_call():
+    """The per-block partial sums of the norm-weight gradient are combined in a fixed order (no atomic adds), so repeated
+    calls on the same inputs agree bit for bit: what the reproducible training mode relies on."""
+    from torchllmtuner_b200 import ops
+    torch.manual_seed(1)
+    T, Hq, Hkv, d = 4096, 8, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * d, device="cuda").bfloat16().requires_grad_()
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    cos, sin = ops.rope_tables(torch.arange(T, device="cuda"), d, 1e6)
+    gq, gk = torch.randn(T, Hq, d, device="cuda").bfloat16(), torch.randn(T, Hkv, d, device="cuda").bfloat16()
+    seen = []
+    for _ in range(8):
+        q, k = ops.qk_norm_rope(qkv[:, :Hq * d].view(T, Hq, d), qkv[:, Hq * d:(Hq + Hkv) * d].view(T, Hkv, d), qw, kw, cos, sin, 1e-6)
+        seen.append(torch.autograd.grad([q, k], [qw, kw, qkv], [gq, gk]))
+    for other in seen[1:]:
+        for a, b in zip(seen[0], other):
+            assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("T,F", [(256, 768), (1000, 12288), (3, 64)])
 def test_swiglu(T, F):
     from torchllmtuner_b200 import ops

@@ -116,7 +116,17 @@ def test_twenty_step_loss_curve_follows_the_fp32_oracle(tmp_path, monkeypatch):
 def test_optimizer_update_under_the_next_forward_changes_nothing():
     """With `overlap_optimizer=True` the AdamW kernels run on their own stream in the order the next forward needs the
     units and the forward waits unit by unit. Same arithmetic, same order per element: the losses are identical, and
-    after `sync_optimizer()` so are the parameters."""
+    after `sync_optimizer()` so are the parameters. (The attention backward runs in its bitwise-reproducible two-kernel
+    mode here: the one-kernel mode sums dQ with reduce-adds whose order differs from run to run in the last bit.)"""
+    from torchllmtuner_b200.ops import functional as F
+    F.set_attention_backward("split")
+    try:
+        _overlap_case()
+    finally:
+        F.set_attention_backward(None)
+
+
+def _overlap_case():
     cfg = _cfg(steps=5, num_hidden_layers=4)
     tr = Trainer(cfg)
     ref = [tr.train_step().loss for _ in range(5)]
@@ -138,7 +148,17 @@ def test_optimizer_update_under_the_next_forward_changes_nothing():
 
 def test_checkpoint_resume_is_bit_exact_on_the_gpu(tmp_path):
     """Saved from device shards as boxes of whole tensors (through pinned staging, asynchronously), resumed into a fresh
-    trainer: the next steps repeat bit for bit. The save follows an overlapped optimizer update, so it must wait for it."""
+    trainer: the next steps repeat bit for bit. The save follows an overlapped optimizer update, so it must wait for it.
+    (Bit for bit needs the reproducible two-kernel attention backward, see the test above.)"""
+    from torchllmtuner_b200.ops import functional as F
+    F.set_attention_backward("split")
+    try:
+        _resume_case(tmp_path)
+    finally:
+        F.set_attention_backward(None)
+
+
+def _resume_case(tmp_path):
     import os
     import shutil
     kw = dict(dump_folder=str(tmp_path), enable=True, interval=2, steps=4, last_save_model_only=False, async_mode="async_with_pinned_mem",

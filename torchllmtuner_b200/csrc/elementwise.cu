@@ -261,9 +261,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
                                                                __nv_bfloat16* __restrict__ dx, int64_t dx_tok_stride,
                                                                float* __restrict__ dw_partial, int T, int H) {
   constexpr int HD = 64 * P, HALF = HD / 2, G = 8 * P, IPW = 32 / G;
-  __shared__ float sdw[HD];
-  for (int i = threadIdx.x; i < HD; i += blockDim.x) sdw[i] = 0.f;
-  __syncthreads();
+  // weight-gradient partials of the block's 256 / G thread groups, summed in a fixed order at the end (an atomic add into
+  // one row would make the last bit depend on the order in which the groups arrive)
+  constexpr int kGroups = 256 / G;
+  __shared__ float sparts[kGroups * HD];
   const int lane = threadIdx.x & 31, g = lane % G;
   const int wpb = blockDim.x >> 5;
   const int64_t total = (int64_t)T * H;
@@ -327,13 +328,19 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
     }
   }
   if (w != nullptr && dw_partial != nullptr) {
+    float* mine = sparts + (threadIdx.x / G) * HD;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      atomicAdd(&sdw[4 * g + j], dwa[j]);
-      atomicAdd(&sdw[HALF + 4 * g + j], dwb[j]);
+      mine[4 * g + j] = dwa[j];
+      mine[HALF + 4 * g + j] = dwb[j];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < HD; i += blockDim.x) dw_partial[(int64_t)blockIdx.x * HD + i] = sdw[i];
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+      float acc = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < kGroups; ++c) acc += sparts[c * HD + i];
+      dw_partial[(int64_t)blockIdx.x * HD + i] = acc;
+    }
   }
 }
 
