@@ -16,6 +16,7 @@ degree, along any cut dimension, and any DCP reader (the reference's included) s
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 
 import torch
@@ -25,9 +26,34 @@ from torch.distributed.checkpoint.metadata import (ChunkStorageMetadata, Metadat
 from torch.distributed.checkpoint.planner import LoadPlan, SavePlan, TensorWriteData, WriteItem, WriteItemType
 from torch.distributed.checkpoint.planner_helpers import _create_read_items, _create_write_items, create_read_items_for_chunk_list
 
-from ...errors import ConfigError
+from ...errors import ConfigError, LLMTunerError
 
 BOX_SEP = "#box"
+
+
+class CheckpointIOError(LLMTunerError, RuntimeError):
+    """A distributed-checkpoint save or load failed on at least one rank."""
+
+
+@contextlib.contextmanager
+def dcp_errors(what: str):
+    """torch's `CheckpointException` derives from `BaseException`, so it slips past every `except Exception` between the
+    checkpointer and the training loop's cleanup. Inside this block it is turned into this framework's errors: a
+    `ConfigError` raised by a planner comes out as itself, anything else as `CheckpointIOError` naming the ranks."""
+    from torch.distributed.checkpoint.api import CheckpointException
+    try:
+        yield
+    except CheckpointException as e:
+        failures = getattr(e, "failures", {}) or {}
+        for rank in sorted(failures):
+            cause = failures[rank]
+            cause = cause[0] if isinstance(cause, tuple) else cause
+            if isinstance(cause, LLMTunerError):
+                raise cause from None
+        ranks = sorted(failures)
+        first = failures[ranks[0]] if ranks else e
+        first = first[0] if isinstance(first, tuple) else first
+        raise CheckpointIOError(f"{what} failed on ranks {ranks}: {type(first).__name__}: {first}") from None
 
 
 def _prod(xs) -> int:

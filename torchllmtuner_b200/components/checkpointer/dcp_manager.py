@@ -328,11 +328,12 @@ class DistributedCheckpointManager(CheckpointManager):
             save_id = ids[0]
         final = os.path.join(self.root, "model-export" if model_only and False else f"step-{step}")
         tmp = f"{final}.tmp-{save_id}"
-        from .boxes import BoxSavePlanner
+        from .boxes import BoxSavePlanner, dcp_errors
         state, table = self._tensor_state(model_only=model_only)
         state.update(self._object_state())
         if self.cfg.async_mode == "disabled":
-            dcp.save(state, checkpoint_id=tmp, planner=BoxSavePlanner(table))
+            with dcp_errors(f"saving {tmp}"):
+                dcp.save(state, checkpoint_id=tmp, planner=BoxSavePlanner(table))
             self._publish(tmp, final, step)
         else:
             pin = self.cfg.async_mode == "async_with_pinned_mem" and torch.cuda.is_available()
@@ -386,9 +387,11 @@ class DistributedCheckpointManager(CheckpointManager):
 
     def wait(self) -> None:
         if self._async_future is not None:
+            from .boxes import dcp_errors
             fut, tmp, final, step = self._async_future
-            fut.result()
-            self._async_future = None
+            self._async_future = None                         # a failed write is reported once, not at every later step
+            with dcp_errors(f"saving {tmp}"):
+                fut.result()
             self._publish(tmp, final, step)
 
     # ------------------------------------------------------------------ purge
@@ -488,7 +491,7 @@ class DistributedCheckpointManager(CheckpointManager):
         return want
 
     def _load_boxes(self, path: str, model_only: bool, reader, meta) -> None:
-        from .boxes import BoxLoadPlanner
+        from .boxes import BoxLoadPlanner, dcp_errors
         tr = self.trainer
         exclude = set(self.cfg.exclude_from_loading)
         want: dict[str, torch.Tensor] = {}
@@ -537,7 +540,8 @@ class DistributedCheckpointManager(CheckpointManager):
         obj_want = self._object_wants(meta, model_only, exclude)
         want.update(obj_want)
         planner = BoxLoadPlanner(table)
-        dcp.load(want, checkpoint_id=path, storage_reader=reader, planner=planner, no_dist=True)
+        with dcp_errors(f"loading {path}"):
+            dcp.load(want, checkpoint_id=path, storage_reader=reader, planner=planner, no_dist=True)
         lacking = sorted(required & planner.missing)
         if lacking:
             raise ConfigError(f"checkpoint {path} lacks model tensors: {lacking[:5]}{'...' if len(lacking) > 5 else ''}")
@@ -662,7 +666,9 @@ class DistributedCheckpointManager(CheckpointManager):
             if md is not None and k.split(".")[0] not in exclude:
                 want[f"obj.{k}"] = torch.empty(md.size, dtype=torch.uint8)
                 objs[k] = None
-        dcp.load(want, checkpoint_id=path, storage_reader=reader, no_dist=True)
+        from .boxes import dcp_errors
+        with dcp_errors(f"loading {path}"):
+            dcp.load(want, checkpoint_id=path, storage_reader=reader, no_dist=True)
         for k in objs:
             objs[k] = _unpack(want.pop(f"obj.{k}"))
         want.update(objs)

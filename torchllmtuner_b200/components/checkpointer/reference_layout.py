@@ -28,6 +28,7 @@ import torch.distributed.checkpoint as dcp
 
 from ...errors import ConfigError
 from ...models.state import get_state_format
+from .boxes import dcp_errors
 from .dcp_manager import _PIECE_RE, _global_positions, _pack, _unpack, FORMAT_VERSION
 
 _MOMENTS = ("exp_avg", "exp_avg_sq", "momentum_buffer")
@@ -96,6 +97,7 @@ class _PieceReader:
         return out
 
 
+@dcp_errors("exporting a checkpoint to the reference layout")
 def export_reference_layout(step_dir: str, out_dir: str, state_format: str | None = None) -> dict:
     """Returns {"tensors": count, "keys": sorted list of the keys written}."""
     src = _PieceReader(step_dir)
@@ -161,6 +163,7 @@ def export_reference_layout(step_dir: str, out_dir: str, state_format: str | Non
     return {"tensors": len(ref_shape), "keys": keys}
 
 
+@dcp_errors("importing a reference-layout checkpoint")
 def import_reference_layout(ref_dir: str, step_dir: str, shapes: dict[str, list[int]], state_format: str = "native",
                             model_only: bool = False) -> dict:
     """`shapes`: canonical native fqn -> whole shape of the model that will load the result (`native_shapes(model)` gives
