@@ -271,3 +271,56 @@ def test_format_2_pieces_are_still_read(tmp_path):
     for a, u in zip(masters, tr2.asm.fsdp.units):
         assert torch.equal(a[:u.numel], u.master[:u.numel])
     tr2.close()
+
+
+def test_checkpoints_on_an_fsspec_store(tmp_path):
+    """The same save / publish / purge / resume cycle against a URI: the in-memory fsspec filesystem stands in for an
+    object store. A second run then starts from that store through `initial_load_path` while writing locally."""
+    import fsspec
+    uri = f"memory://ckpt-{os.getpid()}/run"
+
+    def cfg_of(**flat):
+        c = _cfg(str(tmp_path / "unused"), interval=1, keep_latest_k=2, **flat)
+        c.training.checkpoint_config.folder = uri
+        return c
+    tr = Trainer(cfg_of())
+    ref = []
+    for _ in range(4):
+        r = tr.train_step()
+        ref.append(r.loss)
+        tr.checkpointer.save(r.step)
+    tr.close()
+    fs = fsspec.filesystem("memory")
+    names = sorted(os.path.basename(p) for p in fs.ls(uri[len("memory://"):], detail=False))
+    assert names == ["step-3", "step-4"], names                      # purged to the latest two, no temporary folder left
+    assert not os.path.exists(str(tmp_path / "unused" / "checkpoint"))
+    fs.rm(uri[len("memory://"):] + "/step-4", recursive=True)
+    tr2 = Trainer(cfg_of())
+    assert tr2.checkpointer.load() and tr2.progress.step == 3
+    got = tr2.train_step().loss
+    tr2.close()
+    assert got == ref[3]
+    # a local run seeded from the store
+    c3 = _cfg(str(tmp_path / "local"), initial_load_path=uri + "/step-3", initial_load_model_only=False)
+    tr3 = Trainer(c3)
+    assert tr3.checkpointer.load() and tr3.progress.step == 3
+    assert tr3.train_step().loss == ref[3]
+    tr3.close()
+    fs.rm(uri[len("memory://"):], recursive=True)
+
+
+def test_storage_path_rules():
+    from torchllmtuner_b200.components.checkpointer.storage import FsspecStorage, LocalStorage, is_remote, storage_for
+    assert is_remote("gs://bucket/run") and is_remote("memory://x") and not is_remote("/abs/run") and not is_remote("C:\\run")
+    assert isinstance(storage_for("./out"), LocalStorage) and isinstance(storage_for("s3://b/k"), FsspecStorage)
+    st = FsspecStorage()
+    assert st.join("./outputs", "gs://bucket/ck") == "gs://bucket/ck"          # a URI restarts the path
+    assert st.join("gs://bucket/run", "checkpoint", "step-3") == "gs://bucket/run/checkpoint/step-3"
+    assert LocalStorage().join("/a", "b", "c") == os.path.join("/a", "b", "c")
+    st.makedirs("memory://rules/a/a")
+    with __import__("fsspec").open("memory://rules/a/a/f", "wb") as f:
+        f.write(b"x")
+    assert st.listdir("memory://rules/a") == ["a"] and st.listdir("memory://rules/a/a") == ["f"]
+    st.rmtree("memory://rules/a")
+    st.rmtree("memory://rules/a")                                              # missing is fine
+    assert not st.exists("memory://rules/a/a/f")

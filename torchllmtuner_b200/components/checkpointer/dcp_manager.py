@@ -23,7 +23,6 @@ import io
 import os
 import queue
 import re
-import shutil
 import threading
 import time
 import uuid
@@ -34,6 +33,7 @@ import torch.distributed.checkpoint as dcp
 
 from ...errors import ConfigError
 from .manager import CheckpointManager
+from .storage import is_remote, storage_for
 
 FORMAT_VERSION = 3
 READABLE_VERSIONS = (2, 3)
@@ -192,7 +192,8 @@ class DistributedCheckpointManager(CheckpointManager):
     def __init__(self, config, trainer):
         self.cfg = config.training.checkpoint_config
         self.config, self.trainer = config, trainer
-        self.root = os.path.join(config.training.dump_folder, self.cfg.folder)
+        self.store = storage_for(self.cfg.folder if is_remote(self.cfg.folder) else config.training.dump_folder)
+        self.root = self.store.join(config.training.dump_folder, self.cfg.folder)     # a URI in `folder` stands alone
         self.rank = trainer.env.rank
         self.world = trainer.env.world_size
         self._stamp_tp_ranks()
@@ -319,21 +320,21 @@ class DistributedCheckpointManager(CheckpointManager):
         model_only = last_step and self.cfg.last_save_model_only and not force and step != 0
         if last_step and self.cfg.last_save_in_hf:
             from .hf import save_hf_checkpoint
-            save_hf_checkpoint(self.trainer, os.path.join(self.root, "model-export"), self.cfg.export_dtype)
+            save_hf_checkpoint(self.trainer, self.store.join(self.root, "model-export"), self.cfg.export_dtype)
             return
         save_id = uuid.uuid4().hex[:8]
         if dist.is_initialized():
             ids = [save_id]
             dist.broadcast_object_list(ids, src=0)
             save_id = ids[0]
-        final = os.path.join(self.root, "model-export" if model_only and False else f"step-{step}")
+        final = self.store.join(self.root, f"step-{step}")
         tmp = f"{final}.tmp-{save_id}"
         from .boxes import BoxSavePlanner, dcp_errors
         state, table = self._tensor_state(model_only=model_only)
         state.update(self._object_state())
         if self.cfg.async_mode == "disabled":
             with dcp_errors(f"saving {tmp}"):
-                dcp.save(state, checkpoint_id=tmp, planner=BoxSavePlanner(table))
+                dcp.save(state, storage_writer=self.store.writer(tmp), planner=BoxSavePlanner(table))
             self._publish(tmp, final, step)
         else:
             pin = self.cfg.async_mode == "async_with_pinned_mem" and torch.cuda.is_available()
@@ -347,7 +348,7 @@ class DistributedCheckpointManager(CheckpointManager):
                     staged[k] = v
             if torch.cuda.is_available():
                 torch.cuda.synchronize()
-            fut = dcp.async_save(staged, checkpoint_id=tmp, process_group=self._gloo, planner=BoxSavePlanner(table))
+            fut = dcp.async_save(staged, storage_writer=self.store.writer(tmp), process_group=self._gloo, planner=BoxSavePlanner(table))
             self._async_future = (fut, tmp, final, step)
 
     def _publish(self, tmp: str, final: str, step: int) -> None:
@@ -358,9 +359,9 @@ class DistributedCheckpointManager(CheckpointManager):
             dist.barrier()
         with synchronize_local_errors("checkpoint-publish"):
             if self.rank == 0:
-                if os.path.isdir(final):
-                    shutil.rmtree(final)
-                os.replace(tmp, final)
+                if self.store.isdir(final):
+                    self.store.rmtree(final)
+                self.store.rename(tmp, final)
                 self._purge_q.put(step)
 
     def latest_step(self) -> int:
@@ -405,34 +406,36 @@ class DistributedCheckpointManager(CheckpointManager):
                 exempt = self.cfg.purge_exempt or (lambda s: False)
                 for s in steps[:-self.cfg.keep_latest_k]:
                     if not exempt(s):
-                        shutil.rmtree(os.path.join(self.root, f"step-{s}"), ignore_errors=True)
-            except OSError:
+                        self.store.rmtree(self.store.join(self.root, f"step-{s}"))
+            except Exception:                # purging is best effort on every store; the next publication retries
                 pass
 
     def _adopt_finished_writes(self) -> None:
         """A run that died after a background write finished but before its rename leaves `step-N.tmp-<id>` with a
         `.metadata` file (the coordinator writes it last, after every rank's shards). Such a folder is a complete
         checkpoint: rank 0 publishes it under its final name unless that step was published already."""
-        if self.rank != 0 or not os.path.isdir(self.root):
+        st = self.store
+        if self.rank != 0 or not st.isdir(self.root):
             return
-        for name in sorted(os.listdir(self.root)):
+        for name in sorted(st.listdir(self.root)):
             m = _TMP_RE.match(name)
             if not m:
                 continue
-            src, dst = os.path.join(self.root, name), os.path.join(self.root, f"step-{m.group(1)}")
-            if os.path.exists(os.path.join(src, ".metadata")) and not os.path.isdir(dst):
+            src, dst = st.join(self.root, name), st.join(self.root, f"step-{m.group(1)}")
+            if st.exists(st.join(src, ".metadata")) and not st.isdir(dst):
                 try:
-                    os.replace(src, dst)
+                    st.rename(src, dst)
                 except OSError:
                     pass
 
     def _existing_steps(self) -> list[int]:
-        if not os.path.isdir(self.root):
+        st = self.store
+        if not st.isdir(self.root):
             return []
         out = []
-        for name in os.listdir(self.root):
+        for name in st.listdir(self.root):
             m = _STEP_RE.match(name)
-            if m and os.path.exists(os.path.join(self.root, name, ".metadata")):
+            if m and st.exists(st.join(self.root, name, ".metadata")):
                 out.append(int(m.group(1)))
         return out
 
@@ -447,7 +450,7 @@ class DistributedCheckpointManager(CheckpointManager):
             s = max(steps) if step == -1 else step
             if s not in steps:
                 raise ConfigError(f"checkpoint step {s} not found under {self.root} (have {sorted(steps)})")
-            return os.path.join(self.root, f"step-{s}"), False, False
+            return self.store.join(self.root, f"step-{s}"), False, False
         if self.cfg.initial_load_path:
             return self.cfg.initial_load_path, self.cfg.initial_load_model_only, self.cfg.initial_load_in_hf
         return None, False, False
@@ -470,7 +473,7 @@ class DistributedCheckpointManager(CheckpointManager):
 
     def _load_dcp(self, path: str, model_only: bool) -> None:
         self._check_layout("load")
-        reader = dcp.FileSystemReader(path)
+        reader = storage_for(path).reader(path)           # `initial_load_path` may live on another store than this run
         meta = reader.read_metadata()
         if any(_PIECE_RE.match(k) for k in meta.state_dict_metadata):
             self._load_pieces(path, model_only, reader, meta)       # written by format 2

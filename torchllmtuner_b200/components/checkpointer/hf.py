@@ -18,7 +18,7 @@ import uuid
 import torch
 import torch.distributed as dist
 
-from ...errors import ConfigError
+from ...errors import ConfigError, UnsupportedCombinationError
 from ...models.state import get_state_format
 from .dcp_manager import _global_positions, iter_pieces
 
@@ -108,6 +108,9 @@ def load_hf_checkpoint(trainer, path: str) -> None:
 
 def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", max_shard_bytes: int = 5 << 30) -> None:
     from safetensors.torch import save_file
+    from .storage import is_remote
+    if is_remote(out_dir):
+        raise UnsupportedCombinationError(f"safetensors export writes local files; {out_dir} is a URI (export locally, then copy)")
     rank, world = trainer.env.rank, trainer.env.world_size
     fmt = get_state_format(getattr(trainer.model, "state_format", "qwen3"))
     dt = _DT[export_dtype]
