@@ -127,3 +127,33 @@ def test_a_planner_error_reaches_the_caller_as_this_frameworks_error(tmp_path):
     with pytest.raises(CheckpointIOError, match="ranks"):
         with dcp_errors("loading"):
             dcp.load({"w": torch.zeros(3, 4)}, checkpoint_id=path, no_dist=True)      # torch's own size check
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_backward_from_lse_matches_autograd(causal):
+    """The chunked backward that serves head sizes with a forward kernel only: same gradients as autograd through the
+    plain statement, for grouped heads, several documents, a chunk size that cuts documents, and offset diagonals."""
+    import torch
+    from torchllmtuner_b200.ops import reference as ref
+    torch.manual_seed(0)
+    Hq, Hkv, d = 4, 2, 16
+    pieces = [(0, 37, 0, 37, 0), (37, 20, 37, 50, 30), (57, 9, 87, 9, 0)]       # the middle piece: 20 queries at the end of 50 keys
+    q = torch.randn(66, Hq, d, dtype=torch.float64, requires_grad=True)
+    k = torch.randn(96, Hkv, d, dtype=torch.float64, requires_grad=True)
+    v = torch.randn(96, Hkv, d, dtype=torch.float64, requires_grad=True)
+
+    def plain(q, k, v):                      # float64 statement (attention_pieces computes in fp32)
+        outs = []
+        for (q0, n, k0, m, off) in pieces:
+            s = torch.einsum("qhd,khd->hqk", q[q0:q0 + n], k[k0:k0 + m].repeat_interleave(Hq // Hkv, 1)) * 0.3
+            if causal:
+                s = s.masked_fill(torch.arange(m)[None, :] > torch.arange(n)[:, None] + off, float("-inf"))
+            outs.append((torch.einsum("hqk,khd->qhd", s.softmax(-1), v[k0:k0 + m].repeat_interleave(Hq // Hkv, 1)), s.logsumexp(-1)))
+        return torch.cat([o for o, _ in outs]), torch.cat([l for _, l in outs], 1)
+    o, lse = plain(q, k, v)
+    go = torch.randn_like(o)
+    want = torch.autograd.grad(o, [q, k, v], go)
+    for chunk in (7, 512):
+        got = ref.attention_backward_rows(q.detach(), k.detach(), v.detach(), o.detach(), go, lse.detach(), pieces, causal, 0.3, q_chunk=chunk)
+        for a, b, n in zip(got, want, "qkv"):
+            assert torch.allclose(a, b, rtol=1e-5, atol=1e-5), (n, chunk, (a - b).abs().max())    # softmax algebra is fp32

@@ -148,3 +148,62 @@ def test_attention_backward_modes_agree_on_dk_dv():
     assert torch.equal(res["fused"][2], res["split"][2])
     _close(res["fused"][0], res["split"][0].float(), "dq fused vs split")
     _close(res["fused"][1], res["split"][1].float(), "dk fused vs split")
+
+
+@pytest.mark.parametrize("cu,Hq,Hkv,causal", [([0, 128], 2, 1, True), ([0, 77, 300, 301, 900], 8, 2, True),
+                                                ([0, 200, 520], 2, 2, False), ([0, 1024, 2048], 8, 2, True)])
+def test_attention_head_size_256(cu, Hq, Hkv, causal):
+    """Head size 256: forward kernel (a 16-slice K loop for S, one N=256 product for P V, 384 TMEM columns), backward
+    rebuilt per chunk of query rows from the saved log-sum-exp."""
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    d = 256
+    torch.manual_seed(0)
+    T = cu[-1]
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * d, device="cuda").bfloat16().requires_grad_()
+    q = qkv[:, :Hq * d].view(T, Hq, d)
+    k = qkv[:, Hq * d:(Hq + Hkv) * d].view(T, Hkv, d)
+    v = qkv[:, (Hq + Hkv) * d:].view(T, Hkv, d)
+    meta = ops.AttnMeta.build(cu, causal=causal, device="cuda")
+    o = ops.attention(q, k, v, meta)
+    torch.cuda.synchronize()
+    check_status("attn_fwd")
+    go = torch.randn_like(o)
+    (g1,) = torch.autograd.grad(o, [qkv], go)
+    qf = qkv.detach().float().requires_grad_()
+    q2 = qf[:, :Hq * d].view(T, Hq, d)
+    k2 = qf[:, Hq * d:(Hq + Hkv) * d].view(T, Hkv, d)
+    v2 = qf[:, (Hq + Hkv) * d:].view(T, Hkv, d)
+    o2, lse2 = ref.attention(q2, k2, v2, torch.tensor(cu, dtype=torch.int32), causal)
+    (g2,) = torch.autograd.grad(o2, [qf], go.float())
+    _close(o, o2, "o")
+    _close(g1[:, :Hq * d], g2[:, :Hq * d], "dq")
+    _close(g1[:, Hq * d:(Hq + Hkv) * d], g2[:, Hq * d:(Hq + Hkv) * d], "dk")
+    _close(g1[:, (Hq + Hkv) * d:], g2[:, (Hq + Hkv) * d:], "dv")
+    _, lse3 = ops.attention_with_lse(q.detach(), k.detach(), v.detach(), meta)
+    _close_lse(lse3, lse2.to(lse3.device))
+
+
+@pytest.mark.parametrize("causal,diag", [(True, 100), (True, -3), (False, 0)])
+def test_attention_rows_kernels_match_the_tensor_expressions(causal, diag):
+    """The one-pass P and dS kernels of the row-chunked backward against the same algebra in fp32 tensor expressions,
+    with an odd column count, rows that see no key (lse = -inf) and a diagonal that starts before column 0."""
+    from torchllmtuner_b200.ops import reference as ref
+    from torchllmtuner_b200.ops.cuda_ext import load
+    ext = load()
+    torch.manual_seed(0)
+    B, g, n, C = 3, 2, 37, 301
+    s = torch.randn(B, g * n, C, device="cuda") * 3
+    lse = torch.logsumexp(s * 0.25, -1) + 0.5
+    if causal and diag < 0:
+        lse[:, :3] = float("-inf")
+        lse[:, n:n + 3] = float("-inf")
+    p = ext.attn_rows_probs(s.clone(), lse.contiguous(), n, diag, 0.25, causal)
+    want = ref._rows_probs(s.clone(), lse, n, diag, 0.25, causal, torch.float32)
+    assert p.dtype == torch.bfloat16 and torch.isfinite(p.float()).all()
+    assert_close(p.float(), want, rtol=2 ** -7, atol_rms=1e-3, name="p")
+    dp = torch.randn(B, g * n, C, device="cuda") * 4
+    dl = torch.randn(B, g * n, device="cuda")
+    ds = ext.attn_rows_ds(dp.clone(), p, dl)
+    assert_close(ds.float(), (dp - dl.unsqueeze(-1)) * p.float(), rtol=2 ** -7, atol_rms=1e-3, name="ds")

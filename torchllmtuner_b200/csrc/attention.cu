@@ -20,8 +20,10 @@ namespace llmt {
 
 // =========================================================================================== forward
 // Forward tiles: 128 query rows x 64 keys. K is double buffered, V single buffered, P goes through shared memory:
-// 96 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and the softmax of one overlaps the MMAs
-// of the other.
+// 96 KB of shared memory and 256 TMEM columns per CTA at head size 128, so two CTAs share an SM and the softmax of one
+// overlaps the MMAs of the other. Head size 256 (a K loop of 16 slices for S, one N=256 product for P V) takes 192 KB and
+// 128 + 256 = 384 columns, allocated as 512: one CTA per SM, which shared memory already enforces, so the allocation
+// never waits on a co-resident CTA of this kernel.
 constexpr int kFwdKV = 64;
 
 
@@ -35,6 +37,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int kQBytes = 128 * HD * 2;
   constexpr int kKVBytes = kFwdKV * HD * 2;
   constexpr int kPBytes = 128 * kFwdKV * 2;
+  constexpr uint32_t kTmemCols = HD > 128 ? 512u : 256u;
   // The launch asks for exactly the bytes used (two CTAs must fit in one SM), so the dynamic shared memory base has to be
   // 1024-byte aligned already; the kernel refuses to run otherwise instead of overrunning its allocation.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -81,7 +84,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -287,7 +290,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -821,14 +824,19 @@ extern "C" int llmt_attn_fwd(const void* q, const void* k, const void* v, void* 
                              int Tq, int Tk, int Hq, int Hkv, int HD, int64_t q_stride, int64_t k_stride, int64_t v_stride,
                              int64_t o_stride, float scale, int causal, int* status, cudaStream_t st) {
   if (num_tiles <= 0 || Hq <= 0) return 0;
-  if ((HD != 64 && HD != 128) || Hq % Hkv || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (o_stride & 7)) return -10;
+  if ((HD != 64 && HD != 128 && HD != 256) || Hq % Hkv || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (o_stride & 7)) return -10;
   CUtensorMap tq, tk, tv;
   if (make_thd_map(&tq, q, Tq, Hq, HD, q_stride) || make_thd_map(&tk, k, Tk, Hkv, HD, k_stride, kFwdKV) ||
       make_thd_map(&tv, v, Tk, Hkv, HD, v_stride, kFwdKV))
     return -11;
   const int smem = 128 * HD * 2 + 3 * kFwdKV * HD * 2 + 2 * 128 * kFwdKV * 2 + 256;   // exact: no alignment slack, see the kernel
   const float sl2 = scale * kLog2e;
-  if (HD == 128) {
+  if (HD == 256) {
+    static bool cfg = false;
+    if (!cfg) { if (set_smem(attn_fwd_kernel<256>, smem)) return -2; cfg = true; }
+    attn_fwd_kernel<256><<<num_tiles * Hq, kAttnThreads, smem, st>>>(tq, tk, tv, (__nv_bfloat16*)o, lse, tiles, Hq, Hkv, Tq,
+                                                                     o_stride, sl2, causal, status);
+  } else if (HD == 128) {
     static bool cfg = false;
     if (!cfg) { if (set_smem(attn_fwd_kernel<128>, smem)) return -2; cfg = true; }
     attn_fwd_kernel<128><<<num_tiles * Hq, kAttnThreads, smem, st>>>(tq, tk, tv, (__nv_bfloat16*)o, lse, tiles, Hq, Hkv, Tq,

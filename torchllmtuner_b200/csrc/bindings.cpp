@@ -392,6 +392,30 @@ static const int* limit_ptr(const c10::optional<Tensor>& row_limit) {
   return row_limit->data_ptr<int>();
 }
 
+// s fp32 [B, R, C] contiguous, lse fp32 with B * R elements -> P bf16 [B, R, C]; row r is query (r % n) of its chunk.
+Tensor attn_rows_probs(const Tensor& s, const Tensor& lse, int64_t n, int64_t diag, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(s.device());
+  TORCH_CHECK(s.is_cuda() && s.scalar_type() == at::kFloat && s.is_contiguous() && s.dim() == 3, "s must be a contiguous fp32 [B, R, C]");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == s.size(0) * s.size(1));
+  TORCH_CHECK(n > 0 && s.size(1) % n == 0, "rows per batch must be a multiple of the chunk length");
+  Tensor p = torch::empty(s.sizes(), s.options().dtype(at::kBFloat16));
+  check_rc(llmt_attn_rows_probs(s.data_ptr<float>(), lse.data_ptr<float>(), p.data_ptr(), s.size(0) * s.size(1), (int)s.size(2), (int)n,
+                                (int)diag, (float)scale, causal ? 1 : 0, cur_stream()),
+           "llmt_attn_rows_probs");
+  return p;
+}
+Tensor attn_rows_ds(const Tensor& dp, const Tensor& p, const Tensor& delta) {
+  c10::cuda::CUDAGuard guard(dp.device());
+  TORCH_CHECK(dp.is_cuda() && dp.scalar_type() == at::kFloat && dp.is_contiguous() && dp.dim() == 3);
+  TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kBFloat16 && p.is_contiguous() && p.sizes() == dp.sizes());
+  TORCH_CHECK(delta.is_cuda() && delta.scalar_type() == at::kFloat && delta.is_contiguous() && delta.numel() == dp.size(0) * dp.size(1));
+  Tensor ds = torch::empty(dp.sizes(), p.options());
+  check_rc(llmt_attn_rows_ds(dp.data_ptr<float>(), p.data_ptr(), delta.data_ptr<float>(), ds.data_ptr(), dp.size(0) * dp.size(1),
+                             (int)dp.size(2), cur_stream()),
+           "llmt_attn_rows_ds");
+  return ds;
+}
+
 // row_limit (optional int32 device scalar): rows at or beyond it are neither read nor written.
 Tensor swiglu_fwd(const Tensor& gate, const Tensor& up, const c10::optional<Tensor>& row_limit) {
   c10::cuda::CUDAGuard guard(gate.device());
@@ -522,7 +546,7 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   const int Tq = (int)q.size(0), Hq = (int)q.size(1), HD = (int)q.size(2), Tk = (int)k.size(0), Hkv = (int)k.size(1);
   Tensor o = torch::empty({Tq, Hq, HD}, q.options());
   Tensor lse = torch::empty({Hq, Tq}, q.options().dtype(torch::kFloat));
-  if (pair && Hkv > 0 && Hq % Hkv == 0 && ((Hq / Hkv) % 2) == 0) {
+  if (pair && HD <= 128 && Hkv > 0 && Hq % Hkv == 0 && ((Hq / Hkv) % 2) == 0) {
     check_rc(llmt_attn_fwd_pair(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), tiles.data_ptr<int>(),
                                 (int)tiles.size(0), Tq, Tk, Hq, Hkv, HD, q.stride(0), k.stride(0), v.stride(0), o.stride(0),
                                 (float)scale, causal, status_ptr(), cur_stream()),
@@ -681,6 +705,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("attn_rows_probs", &attn_rows_probs);
+  m.def("attn_rows_ds", &attn_rows_ds);
   m.def("swiglu_fwd", &swiglu_fwd, py::arg("gate"), py::arg("up"), py::arg("row_limit") = py::none());
   m.def("swiglu_bwd", &swiglu_bwd, py::arg("dout"), py::arg("gate"), py::arg("up"), py::arg("dgate_out"), py::arg("dup_out"),
         py::arg("row_limit") = py::none());

@@ -344,6 +344,36 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
   }
 }
 
+// ------------------------------------------------------------------------------------------ attention backward by rows
+// The two elementwise steps of the attention backward that rebuilds probabilities per block of query rows (head sizes with
+// a forward kernel only): S [rows, C] fp32 from a batched product -> P = exp(S * scale - lse[row]) in bf16 with the causal
+// limit applied, and dS = (dP - delta[row]) * P in bf16. One read of the fp32 block and one bf16 write each, where the
+// same algebra as tensor expressions takes eight passes. Row r of the block is query (r % n) of the chunk; it sees columns
+// [0, (r % n) + diag + 1).
+__global__ void attn_rows_probs_kernel(const float* __restrict__ s, const float* __restrict__ lse, __nv_bfloat16* __restrict__ p,
+                                       int64_t rows, int C, int n, int diag, float scale_log2, int causal) {
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float l = lse[row];
+    const float l2 = isinf(l) ? 0.f : l * 1.4426950408889634f;    // a row that sees no key: every column is beyond its limit
+    const int i = (int)(row % n);
+    const int lim = causal ? min(C, i + diag + 1) : C;
+    const float* sr = s + row * (int64_t)C;
+    __nv_bfloat16* pr = p + row * (int64_t)C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+      pr[c] = __float2bfloat16_rn(c < lim ? exp2f(sr[c] * scale_log2 - l2) : 0.f);
+  }
+}
+__global__ void attn_rows_ds_kernel(const float* __restrict__ dp, const __nv_bfloat16* __restrict__ p, const float* __restrict__ delta,
+                                    __nv_bfloat16* __restrict__ ds, int64_t rows, int C) {
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float dl = delta[row];
+    const float* dr = dp + row * (int64_t)C;
+    const __nv_bfloat16* pr = p + row * (int64_t)C;
+    __nv_bfloat16* or_ = ds + row * (int64_t)C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) or_[c] = __float2bfloat16_rn((dr[c] - dl) * __bfloat162float(pr[c]));
+  }
+}
+
 // ------------------------------------------------------------------------------------------ SwiGLU
 // Rows of `gate` and `up` may be strided (views into one [T, 2F] buffer); out/dgate/dup likewise.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
@@ -636,6 +666,22 @@ extern "C" int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, cons
   else return -10;
   if (w != nullptr && dw_partial != nullptr)
     colsum_kernel<<<(HD + 255) / 256, 256, 0, st>>>(dw_partial, dw_f32, (__nv_bfloat16*)dw_bf16, grid, HD, accumulate);
+  LLMT_CHECK_LAUNCH();
+}
+
+extern "C" int llmt_attn_rows_probs(const float* s, const float* lse, void* p, int64_t rows, int C, int n, int diag, float scale,
+                                    int causal, cudaStream_t st) {
+  if (rows <= 0 || C <= 0) return 0;
+  if (n <= 0) return -10;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  attn_rows_probs_kernel<<<(int)(rows < cap ? rows : cap), 256, 0, st>>>(s, lse, (__nv_bfloat16*)p, rows, C, n, diag,
+                                                                          scale * 1.4426950408889634f, causal);
+  LLMT_CHECK_LAUNCH();
+}
+extern "C" int llmt_attn_rows_ds(const float* dp, const void* p, const float* delta, void* ds, int64_t rows, int C, cudaStream_t st) {
+  if (rows <= 0 || C <= 0) return 0;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  attn_rows_ds_kernel<<<(int)(rows < cap ? rows : cap), 256, 0, st>>>(dp, (const __nv_bfloat16*)p, delta, (__nv_bfloat16*)ds, rows, C);
   LLMT_CHECK_LAUNCH();
 }
 

@@ -40,6 +40,9 @@ int llmt_qk_norm_rope_bwd(const void* dy, int64_t dy_tok_stride, const void* x, 
                           const float* cosb, const float* sinb, const float* rstd, void* dx, int64_t dx_tok_stride,
                           float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, int T, int H, int HD,
                           cudaStream_t st);
+int llmt_attn_rows_probs(const float* s, const float* lse, void* p, int64_t rows, int C, int n, int diag, float scale,
+                         int causal, cudaStream_t st);
+int llmt_attn_rows_ds(const float* dp, const void* p, const float* delta, void* ds, int64_t rows, int C, cudaStream_t st);
 int llmt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t T, int F, int64_t ld_in, int64_t ld_out,
                     const int* row_limit, cudaStream_t st);
 int llmt_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int64_t T, int F,

@@ -274,7 +274,7 @@ class KimiLatentAttention(nn.Module):
         kv = self.kv_b_proj(self.kv_a_layernorm(ckv[:, :self.rank])).view(T, H, self.dn + self.dv)
         k = torch.cat((kv[..., :self.dn], ckv[:, None, self.rank:].expand(T, H, self.dr)), -1)      # no rotary: positions come from the KDA layers
         v = kv[..., self.dn:]
-        if ctx.cp is not None or (self.dv == self.dq and (not x.is_cuda or self.dq in (64, 128))):
+        if ctx.cp is not None or (self.dv == self.dq and (not x.is_cuda or self.dq in ops.DEVICE_ATTENTION_HEAD_DIMS)):
             attend = ctx.cp.attention if ctx.cp is not None else ops.attention
             vv = v if self.dv == self.dq else F.pad(v, (0, self.dq - self.dv))
             o = attend(q.contiguous(), k.contiguous(), vv.contiguous(), ctx.attn_meta, self.scale)[..., :self.dv]

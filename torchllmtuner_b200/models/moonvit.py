@@ -117,7 +117,7 @@ class MoonViTBlock(nn.Module):
         N = x.shape[0]
         q, k, v = self.wqkv(self.norm0(x)).view(N, 3, self.heads, self.head_dim).unbind(1)
         q, k = rotate_pairs(q, ang), rotate_pairs(k, ang)
-        if not x.is_cuda or self.head_dim in (64, 128):
+        if not x.is_cuda or self.head_dim in ops.DEVICE_ATTENTION_HEAD_DIMS:
             o = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), meta, self.scale)
         else:
             o = ref.attention_pieces(q, k, v, meta.pieces, False, self.scale)[0]

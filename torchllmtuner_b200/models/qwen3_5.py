@@ -131,7 +131,7 @@ def attend(q, k, v, ctx, scale):
     """The sm_100a kernel where it has a variant for the head size, the plain statement otherwise."""
     if ctx.cp is not None:
         return ctx.cp.attention(q, k, v, ctx.attn_meta, scale)
-    if not q.is_cuda or q.shape[-1] in (64, 128):
+    if not q.is_cuda or q.shape[-1] in ops.DEVICE_ATTENTION_HEAD_DIMS:
         return ops.attention(q, k, v, ctx.attn_meta, scale)
     return ref.attention_pieces(q, k, v, ctx.attn_meta.pieces, True, scale)[0]
 

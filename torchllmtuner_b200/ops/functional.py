@@ -328,6 +328,9 @@ def swiglu(gate, up, row_limit=None):
 
 
 # ----------------------------------------------------------------------------------------------- attention
+DEVICE_ATTENTION_HEAD_DIMS = (64, 128, 256)     # 256: forward kernel, backward rebuilt per chunk of rows from the LSE
+
+
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, meta: AttnMeta, scale, kept=None):
@@ -343,6 +346,11 @@ class _Attention(torch.autograd.Function):
         if do.stride(2) != 1 or do.stride(1) != do.shape[2]:
             do = do.contiguous()
         m = ctx.meta
+        if q.shape[-1] not in (64, 128):      # forward kernel only at this head size: rebuild P per chunk of rows from the LSE
+            ext = _ext()
+            dq, dk, dv = ref.attention_backward_rows(q, k, v, o, do, lse, m.pieces, m.causal, ctx.scale,
+                                                     probs_fn=ext.attn_rows_probs, ds_fn=ext.attn_rows_ds)
+            return dq, dk, dv, None, None, None
         dq, dk, dv = _ext().attn_bwd(q, k, v, o, do, lse, m.q_tiles, m.k_tile_passes, ctx.scale, m.causal, not m.covers_all_keys,
                                      attention_backward_mode() == "fused")
         return dq, dk, dv, None, None, None

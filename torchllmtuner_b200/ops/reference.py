@@ -103,6 +103,71 @@ def attention_pieces(q, k, v, pieces, causal: bool = True, scale: float | None =
     return out.to(q.dtype), lses
 
 
+def _bmm_fp32(a, b):
+    """Batched product with an fp32 result: 16-bit inputs on the device keep the tensor cores' fp32 accumulator instead of
+    rounding the result to 16 bits first."""
+    if a.is_cuda and a.dtype in (torch.bfloat16, torch.float16):
+        return torch.bmm(a, b, out_dtype=torch.float32)
+    return torch.bmm(a, b).float()
+
+
+def _rows_probs(s, l, n, diag, scale, causal, dtype):
+    """P = exp(S * scale - lse) with the causal limit, as tensor expressions (in place on `s`)."""
+    l = torch.where(torch.isinf(l), torch.zeros_like(l), l).unsqueeze(-1)       # rows that see no key; masked below
+    p = s.mul_(scale).sub_(l).exp_()
+    if causal:
+        C = p.shape[-1]
+        kd = max(0, diag + 1)                                                    # columns below kd are visible to every row
+        if kd < C:
+            hidden = torch.arange(kd, C, device=p.device)[None, :] > (torch.arange(n, device=p.device) + diag)[:, None]
+            p[:, :, kd:].masked_fill_(hidden.repeat(p.shape[1] // n, 1)[None], 0.0)
+    return p.to(dtype)
+
+
+def _rows_ds(dp, p, dl):
+    return dp.sub_(dl.unsqueeze(-1)).mul_(p).to(p.dtype)
+
+
+def attention_backward_rows(q, k, v, o, do, lse, pieces, causal: bool = True, scale: float | None = None, q_chunk: int = 512,
+                            probs_fn=None, ds_fn=None):
+    """Gradients of `attention_pieces` from its saved output and log-sum-exp, without the [Tq, Tk] probabilities ever
+    existing at once: per piece and per chunk of query rows, P = exp(S - lse) is rebuilt, then dV += P^T dO,
+    dS = P * (dO V^T - rowsum(dO * O)), dQ = dS K, dK += dS^T Q. The products run in the inputs' dtype (tensor cores
+    for bf16) with fp32 results, the key/value accumulators are fp32. Query heads of one key/value group are stacked
+    along the row axis, so no head is ever repeated in memory. This is the backward of the head sizes for which the
+    device has a forward kernel only; there `probs_fn(s, lse_rows, n, diag, scale, causal)` and `ds_fn(dp, p, delta_rows)`
+    are one-pass kernels, here they default to tensor expressions. Returns (dq, dk, dv) in the inputs' dtype."""
+    Tq, Hq, d = q.shape
+    Tk, Hkv = k.shape[0], k.shape[1]
+    g = Hq // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    probs_fn = probs_fn or (lambda s, l, n, diag, sc, ca: _rows_probs(s, l, n, diag, sc, ca, q.dtype))
+    ds_fn = ds_fn or _rows_ds
+    dq = torch.zeros(Tq, Hq, d, dtype=q.dtype, device=q.device)
+    dk = torch.zeros(Tk, Hkv, d, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(Tk, Hkv, d, dtype=torch.float32, device=q.device)
+    delta = (o.float() * do.float()).sum(-1)                                    # [Tq, Hq]
+    for (q0, qlen, k0, klen, off) in pieces:
+        for a in range(0, qlen, q_chunk):
+            n = min(q_chunk, qlen - a)
+            kend = min(klen, a + n + off) if causal else klen                    # keys the chunk's last row sees
+            if kend <= 0:
+                continue
+            rows = slice(q0 + a, q0 + a + n)
+            keys = slice(k0, k0 + kend)
+            qg = q[rows].transpose(0, 1).reshape(Hkv, g * n, d)                 # heads of a group stacked along rows
+            dog = do[rows].transpose(0, 1).reshape(Hkv, g * n, d).to(q.dtype)
+            ki, vi = k[keys].transpose(0, 1), v[keys].transpose(0, 1)           # [Hkv, kend, d]
+            l = lse[:, rows].reshape(Hkv, g * n).contiguous()
+            dl = delta[rows].transpose(0, 1).reshape(Hkv, g * n).contiguous()
+            p = probs_fn(_bmm_fp32(qg, ki.transpose(1, 2)), l, n, a + off, scale, causal)       # [Hkv, g*n, kend]
+            dv[keys] += _bmm_fp32(p.transpose(1, 2), dog).transpose(0, 1)
+            ds = ds_fn(_bmm_fp32(dog, vi.transpose(1, 2)), p, dl)                # the softmax scale goes on the outputs
+            dq[rows] = _bmm_fp32(ds, ki).mul_(scale).reshape(Hq, n, d).transpose(0, 1).to(q.dtype)
+            dk[keys] += _bmm_fp32(ds.transpose(1, 2), qg).mul_(scale).transpose(0, 1)
+    return dq, dk.to(k.dtype), dv.to(v.dtype)
+
+
 def attention(q, k, v, cu_seqlens=None, causal: bool = True, scale: float | None = None, k_cu_seqlens=None, q_offsets=None):
     """Packed-row attention from cumulative document cuts (see `attention_pieces`)."""
     Tq = q.shape[0]

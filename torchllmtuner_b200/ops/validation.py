@@ -36,7 +36,7 @@ def require_last_dim_contiguous(x: torch.Tensor, name: str, multiple: int = 8) -
 
 
 def validate_attention_inputs(q, k, v) -> None:
-    """q [T, Hq, d], k / v [S, Hkv, d]; Hq a multiple of Hkv; d in {64, 128}."""
+    """q [T, Hq, d], k / v [S, Hkv, d]; Hq a multiple of Hkv; on the device d in {64, 128, 256}."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         require_tensor(t, n, dims=3)
     require_same_device(("q", q), ("k", k), ("v", v))
