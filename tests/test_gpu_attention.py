@@ -207,3 +207,30 @@ def test_attention_rows_kernels_match_the_tensor_expressions(causal, diag):
     dl = torch.randn(B, g * n, device="cuda")
     ds = ext.attn_rows_ds(dp.clone(), p, dl)
     assert_close(ds.float(), (dp - dl.unsqueeze(-1)) * p.float(), rtol=2 ** -7, atol_rms=1e-3, name="ds")
+
+
+@pytest.mark.parametrize("d,dv,causal", [(72, 72, False), (192, 128, True), (40, 64, True)])
+def test_attention_pads_widths_without_a_kernel_variant(d, dv, causal):
+    """Head widths between the kernel variants (a vision tower's 72, latent attention's 192 keys / 128 values) run zero-padded
+    to the next variant; outputs and gradients equal the fp32 statement at the true widths."""
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.ops import reference as ref
+    torch.manual_seed(0)
+    cu, Hq, Hkv = [0, 150, 400], 4, 2
+    T = cu[-1]
+    q = torch.randn(T, Hq, d, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(T, Hkv, d, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(T, Hkv, dv, device="cuda").bfloat16().requires_grad_()
+    meta = ops.AttnMeta.build(cu, causal=causal, device="cuda")
+    scale = d ** -0.5
+    o = ops.attention(q, k, v, meta, scale)
+    assert o.shape == (T, Hq, dv)
+    go = torch.randn_like(o)
+    g1 = torch.autograd.grad(o, [q, k, v], go)
+    q2, k2, v2 = (t.detach().float().requires_grad_() for t in (q, k, v))
+    o2, _ = ref.attention_pieces(q2, k2, v2, meta.pieces, causal, scale)
+    g2 = torch.autograd.grad(o2, [q2, k2, v2], go.float())
+    _close(o, o2, "o")
+    for a, b, n in zip(g1, g2, ("dq", "dk", "dv")):
+        assert a.shape == b.shape
+        _close(a, b, n)

@@ -30,7 +30,6 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
-from ..ops import reference as ref
 from .common import Embedding, GatedMLP, Linear, RMSNorm
 from .contracts import DecoderStructure
 from .families import chunked_delta_rule
@@ -274,13 +273,11 @@ class KimiLatentAttention(nn.Module):
         kv = self.kv_b_proj(self.kv_a_layernorm(ckv[:, :self.rank])).view(T, H, self.dn + self.dv)
         k = torch.cat((kv[..., :self.dn], ckv[:, None, self.rank:].expand(T, H, self.dr)), -1)      # no rotary: positions come from the KDA layers
         v = kv[..., self.dn:]
-        if ctx.cp is not None or (self.dv == self.dq and (not x.is_cuda or self.dq in ops.DEVICE_ATTENTION_HEAD_DIMS)):
-            attend = ctx.cp.attention if ctx.cp is not None else ops.attention
+        if ctx.cp is not None:                    # the exchange moves q, k and v as one head-sharded block: one width
             vv = v if self.dv == self.dq else F.pad(v, (0, self.dq - self.dv))
-            o = attend(q.contiguous(), k.contiguous(), vv.contiguous(), ctx.attn_meta, self.scale)[..., :self.dv]
-        else:
-            o, _ = ref.attention_pieces(q, k, F.pad(v, (0, self.dq - self.dv)), ctx.attn_meta.pieces, True, self.scale)
-            o = o[..., :self.dv]
+            o = ctx.cp.attention(q.contiguous(), k.contiguous(), vv.contiguous(), ctx.attn_meta, self.scale)[..., :self.dv]
+        else:                                     # widths without a kernel variant (192 / 128 here) are padded inside
+            o = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), ctx.attn_meta, self.scale)
         o = o.reshape(T, H * self.dv)
         if self.g_proj is not None:
             o = o * torch.sigmoid(self.g_proj(x))

@@ -24,7 +24,6 @@ import torch.nn.functional as F
 
 from .. import ops
 from ..errors import ConfigError
-from ..ops import reference as ref
 from ..ops.attn_meta import AttnMeta
 
 
@@ -117,10 +116,7 @@ class MoonViTBlock(nn.Module):
         N = x.shape[0]
         q, k, v = self.wqkv(self.norm0(x)).view(N, 3, self.heads, self.head_dim).unbind(1)
         q, k = rotate_pairs(q, ang), rotate_pairs(k, ang)
-        if not x.is_cuda or self.head_dim in ops.DEVICE_ATTENTION_HEAD_DIMS:
-            o = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), meta, self.scale)
-        else:
-            o = ref.attention_pieces(q, k, v, meta.pieces, False, self.scale)[0]
+        o = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), meta, self.scale)   # width 72 runs padded to 128
         x = x + self.wo(o.reshape(N, -1))
         return x + self.fc1(F.gelu(self.fc0(self.norm1(x))))
 

@@ -24,7 +24,6 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
-from ..ops import reference as ref
 from .common import Embedding, GatedMLP, Linear
 from .contracts import DecoderStructure
 from .families import chunked_delta_rule
@@ -128,12 +127,9 @@ def rotate_leading(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> tor
 
 
 def attend(q, k, v, ctx, scale):
-    """The sm_100a kernel where it has a variant for the head size, the plain statement otherwise."""
     if ctx.cp is not None:
         return ctx.cp.attention(q, k, v, ctx.attn_meta, scale)
-    if not q.is_cuda or q.shape[-1] in ops.DEVICE_ATTENTION_HEAD_DIMS:
-        return ops.attention(q, k, v, ctx.attn_meta, scale)
-    return ref.attention_pieces(q, k, v, ctx.attn_meta.pieces, True, scale)[0]
+    return ops.attention(q, k, v, ctx.attn_meta, scale)
 
 
 # --------------------------------------------------------------------------------------------------- mixers

@@ -10,6 +10,7 @@ import os
 import torch
 
 from . import reference as ref
+from ..errors import UnsupportedCombinationError
 from .validation import validate_attention_inputs, validate_rms_norm_inputs
 from .attn_meta import AttnMeta
 from .cuda_ext import load as _ext
@@ -385,11 +386,27 @@ def attention_backward_mode() -> str:
     return "split" if torch.are_deterministic_algorithms_enabled() else "fused"
 
 
+def device_head_dim(d: int) -> int | None:
+    """The head size the device kernels run a head of width `d` at (the next supported size), None beyond the largest."""
+    return next((s for s in DEVICE_ATTENTION_HEAD_DIMS if s >= d), None)
+
+
 def attention(q, k, v, meta: AttnMeta, scale: float | None = None):
-    """Packed-row GQA attention; documents and masks come from `meta`. q [Tq,Hq,d], k/v [Tk,Hkv,d] -> [Tq,Hq,d]."""
+    """Packed-row GQA attention; documents and masks come from `meta`. q [Tq,Hq,d], k [Tk,Hkv,d], v [Tk,Hkv,dv]
+    -> [Tq,Hq,dv]. On the device a head width the kernels have no variant for (72, 192, a value width that differs from
+    the key width) is zero-padded to the next one they have: the padded columns add nothing to Q K^T and their outputs are
+    cut away again, so only the products grow."""
     validate_attention_inputs(q, k, v)
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if _use_cuda(q) and q.dtype == torch.bfloat16:
+        d, dv = q.shape[-1], v.shape[-1]
+        run = device_head_dim(max(d, dv))
+        if run is None:
+            raise UnsupportedCombinationError(f"attention head width {max(d, dv)} exceeds the device kernels' largest ({DEVICE_ATTENTION_HEAD_DIMS[-1]})")
+        if d != run or dv != run:
+            pad = torch.nn.functional.pad
+            out = attention(pad(q, (0, run - d)), pad(k, (0, run - d)), pad(v, (0, run - dv)), meta, scale)
+            return out[..., :dv]
         if meta.q_tiles is None:
             raise ValueError("AttnMeta was built without device tables; pass device= to AttnMeta.build")
         frame = _SAC

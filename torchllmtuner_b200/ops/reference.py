@@ -64,11 +64,12 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 def attention_pieces(q, k, v, pieces, causal: bool = True, scale: float | None = None):
     """GQA attention over explicit pieces (q0, qlen, k0, klen, off): query i of a piece sees keys
-    [0, min(klen, i + off + 1)) of that piece when causal. q [Tq, Hq, d], k/v [Tk, Hkv, d].
-    Returns (out [Tq, Hq, d], lse [Hq, Tq] fp32)."""
+    [0, min(klen, i + off + 1)) of that piece when causal. q [Tq, Hq, d], k [Tk, Hkv, d], v [Tk, Hkv, dv].
+    Returns (out [Tq, Hq, dv], lse [Hq, Tq] fp32)."""
     Tq, Hq, d = q.shape
     g = Hq // k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    d = v.shape[-1]                                        # the output takes the values' width
     outs = torch.zeros(Tq, Hq, d, dtype=torch.float32, device=q.device)
     lses = torch.full((Hq, Tq), float("-inf"), dtype=torch.float32, device=q.device)
     rows_o, rows_i = [], []

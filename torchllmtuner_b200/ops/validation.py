@@ -36,12 +36,12 @@ def require_last_dim_contiguous(x: torch.Tensor, name: str, multiple: int = 8) -
 
 
 def validate_attention_inputs(q, k, v) -> None:
-    """q [T, Hq, d], k / v [S, Hkv, d]; Hq a multiple of Hkv; on the device d in {64, 128, 256}."""
+    """q [T, Hq, d], k [S, Hkv, d], v [S, Hkv, dv]; Hq a multiple of Hkv; on the device d and dv at most 256."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         require_tensor(t, n, dims=3)
     require_same_device(("q", q), ("k", k), ("v", v))
-    if k.shape != v.shape:
-        raise ConfigError(f"k {tuple(k.shape)} and v {tuple(v.shape)} must have the same shape")
+    if k.shape[:2] != v.shape[:2]:
+        raise ConfigError(f"k {tuple(k.shape)} and v {tuple(v.shape)} must agree in rows and heads")
     if q.shape[2] != k.shape[2] or q.shape[1] % k.shape[1]:
         raise ConfigError(f"q {tuple(q.shape)} is not compatible with k {tuple(k.shape)} (head_dim equal, Hq % Hkv == 0)")
 
