@@ -18,7 +18,8 @@ def _inputs(T, H, dk, dv, channels, seed=0):
     return [q, k, v, beta, ld]
 
 
-@pytest.mark.parametrize("channels,T,chunk", [(1, 37, 8), (8, 37, 8), (1, 64, 16), (8, 50, 16), (8, 16, 16), (1, 5, 64)])
+@pytest.mark.parametrize("channels,T,chunk", [(1, 37, 8), (8, 37, 8), (1, 64, 16), (8, 50, 16), (8, 16, 16), (1, 5, 64),
+                                              (1, 150, 8), (8, 200, 16), (8, 128, 8), (1, 72, 8)])      # the last four: more chunks than the loop form takes
 def test_chunked_form_matches_the_scan(channels, T, chunk):
     x = _inputs(T, 3, 8, 6, channels)
     a, b = delta_rule_scan(*x), chunked_delta_rule(*x, chunk)
@@ -107,3 +108,37 @@ def test_sequence_parallel_delta_rule_hands_the_state_across_ranks(tmp_path, wor
             assert torch.allclose(o, want[rows], atol=1e-5)
             for got, full in zip(g, grads):
                 assert torch.allclose(got, full[rows], atol=1e-4)
+
+
+@pytest.mark.parametrize("N", [1, 2, 9, 10, 16, 23])
+def test_affine_scan_matches_the_step_by_step_recurrence(N):
+    from torchllmtuner_b200.models.families import affine_scan
+    torch.manual_seed(N)
+    A = (torch.randn(N, 2, 5, 5, dtype=torch.float64) * 0.4).requires_grad_()
+    B = torch.randn(N, 2, 5, 3, dtype=torch.float64, requires_grad=True)
+    S0 = torch.randn(2, 5, 3, dtype=torch.float64, requires_grad=True)
+
+    def plain(A, B, S):
+        out = []
+        for n in range(N):
+            out.append(S)
+            S = A[n] @ S + B[n]
+        return torch.stack(out), S
+    got, want = affine_scan(A, B, S0), plain(A, B, S0)
+    assert torch.allclose(got[0], want[0], atol=1e-12) and torch.allclose(got[1], want[1], atol=1e-12)
+    w0, w1 = torch.randn_like(want[0]), torch.randn_like(want[1])
+    for ga, gb in zip(torch.autograd.grad((got[0] * w0).sum() + (got[1] * w1).sum(), [A, B, S0]),
+                      torch.autograd.grad((want[0] * w0).sum() + (want[1] * w1).sum(), [A, B, S0])):
+        assert torch.allclose(ga, gb, atol=1e-11)
+
+
+def test_long_sequences_carry_and_return_state_like_short_ones():
+    """The scan form (many chunks) and the loop form (few chunks) agree when a sequence is processed in two halves with
+    the state handed over, for both decay forms."""
+    for channels in (1, 8):
+        q, k, v, beta, ld = (t.detach() for t in _inputs(160, 2, 8, 6, channels, seed=3))
+        whole, s_whole = chunked_delta_rule(q, k, v, beta, ld, 8, None, True)                       # 20 chunks: scan form
+        a, s_a = chunked_delta_rule(q[:40], k[:40], v[:40], beta[:40], ld[:40], 8, None, True)       # 5 chunks: loop form
+        b, s_b = chunked_delta_rule(q[40:], k[40:], v[40:], beta[40:], ld[40:], 8, s_a, True)        # 15 chunks: scan form from a state
+        assert torch.allclose(torch.cat((a, b)), whole, atol=2e-5) and torch.allclose(s_b, s_whole, atol=2e-5)
+        assert torch.allclose(whole, delta_rule_scan(q, k, v, beta, ld), atol=2e-5)

@@ -95,27 +95,73 @@ def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64, initial_state=
         slab = max(1, (1 << 25) // (H * C * C * dk))
         for a in range(0, N, slab):
             g = G[a:a + slab]
-            E = (g.unsqueeze(3) - g.unsqueeze(2)).clamp(max=0).exp()          # [n, H, t, i, dk]
-            KK.append(torch.einsum("nhtc,nhic,nhtic->nhti", k[a:a + slab], k[a:a + slab], E))
-            QK.append(torch.einsum("nhtc,nhic,nhtic->nhti", q[a:a + slab], k[a:a + slab], E))
+            Ek = (g.unsqueeze(3) - g.unsqueeze(2)).clamp(max=0).exp() * k[a:a + slab].unsqueeze(2)      # [n, H, t, i, dk]
+            # k_t and q_t against the same decayed keys: one batched [2, dk] x [dk, C] product per (chunk, head, t)
+            both = torch.stack((k[a:a + slab], q[a:a + slab]), 3) @ Ek.transpose(-1, -2)                # [n, H, t, 2, i]
+            KK.append(both[..., 0, :])
+            QK.append(both[..., 1, :])
         KK, QK = torch.cat(KK), torch.cat(QK)
     A = (beta * KK).masked_fill(~tri.tril(-1), 0.0)
     QK = QK.masked_fill(~tri, 0.0)
     eG = G.exp()
     IA = A + torch.eye(C, dtype=q.dtype, device=q.device)
     W = torch.linalg.solve_triangular(IA, torch.cat((beta * v, beta * eG * k), -1), upper=False)
-    W1, W2 = W[..., :dv], W[..., dv:]
+    W1, W2 = W.split((dv, W.shape[-1] - dv), -1)
     Qt = eG * q
     Kend = (G[:, :, -1:, :] - G).exp() * k
     dec_end = G[:, :, -1, :].exp().unsqueeze(-1)                              # [N, H, dk | 1, 1]
     S = q.new_zeros(H, dk, dv) if initial_state is None else initial_state
-    outs = []
-    for n in range(N):
-        U = W1[n] - W2[n] @ S
-        outs.append(Qt[n] @ S + QK[n] @ U)
-        S = dec_end[n] * S + Kend[n].transpose(1, 2) @ U
-    o = torch.stack(outs).permute(0, 2, 1, 3).reshape(N * C, H, dv)
+    if N <= SEQUENTIAL_CHUNKS:
+        outs = []
+        for n in range(N):
+            U = W1[n] - W2[n] @ S
+            outs.append(Qt[n] @ S + QK[n] @ U)
+            S = dec_end[n] * S + Kend[n].transpose(1, 2) @ U
+        o = torch.stack(outs)
+    else:
+        # The state update is affine in the state: S_{n+1} = A_n S_n + B_n with A_n = diag(decay_n) - Kend_n^T W2_n and
+        # B_n = Kend_n^T W1_n, both known for every chunk at once. A two-level scan over those maps leaves about
+        # 2 sqrt(N) dependent steps instead of N, and every output product becomes one batched product over all chunks.
+        KendT = Kend.transpose(2, 3)
+        A = (-KendT) @ W2
+        A.diagonal(dim1=-2, dim2=-1).add_(dec_end.squeeze(-1).expand(N, H, dk))
+        S_all, S = affine_scan(A, KendT @ W1, S)
+        U = W1 - W2 @ S_all
+        o = Qt @ S_all + QK @ U
+    o = o.permute(0, 2, 1, 3).reshape(N * C, H, dv)
     return (o[:T], S) if return_state else o[:T]
+
+
+SEQUENTIAL_CHUNKS = 8       # up to this many chunks the plain chunk-after-chunk loop is the cheaper form
+
+
+def affine_scan(A, B, S0):
+    """States of S_{n+1} = A_n S_n + B_n for n = 0..N-1. A [N, H, a, a], B [N, H, a, b], S0 [H, a, b].
+    Returns (the state each step starts from [N, H, a, b], the state after the last step [H, a, b]).
+    Two levels: the N steps are cut into groups of about sqrt(N); inside all groups at once the prefix maps
+    (P_j, Q_j) with S_{g, j} = P_j S_g + Q_j are built step by step (batched over groups), then the group-start states
+    follow group after group, then every state comes from one batched product. Steps that pad the last group are the
+    identity map."""
+    N, H, a, _ = A.shape
+    R = max(1, int(math.isqrt(N)))
+    M = -(-N // R)
+    if M * R != N:
+        eye = torch.eye(a, dtype=A.dtype, device=A.device).expand(M * R - N, H, a, a)
+        A = torch.cat((A, eye))
+        B = torch.cat((B, B.new_zeros(M * R - N, *B.shape[1:])))
+    # unbind, not indexing: the backward of an index is a zero-filled tensor of the whole size per step
+    Aj, Bj = A.view(M, R, *A.shape[1:]).unbind(1), B.view(M, R, *B.shape[1:]).unbind(1)
+    P, Q = [Aj[0]], [Bj[0]]                                       # the maps after 1, 2, ... R steps of a group
+    for j in range(1, R):
+        P.append(Aj[j] @ P[-1])
+        Q.append(Aj[j] @ Q[-1] + Bj[j])
+    starts = [S0]
+    for Pg, Qg in zip(P[-1].unbind(0), Q[-1].unbind(0)):
+        starts.append(Pg @ starts[-1] + Qg)
+    Sg = torch.stack(starts[:-1]).unsqueeze(1)                    # [M, 1, H, a, b]
+    inner = torch.stack(P[:-1], 1) @ Sg + torch.stack(Q[:-1], 1) if R > 1 else None      # after 1 .. R-1 steps
+    S_all = Sg if inner is None else torch.cat((Sg, inner), 1)
+    return S_all.reshape(M * R, *S_all.shape[2:])[:N], starts[-1]
 
 
 class DeltaRuleMixer(nn.Module):

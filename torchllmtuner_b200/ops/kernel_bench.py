@@ -47,12 +47,13 @@ def main() -> None:
     from .. import ops
     from .cuda_ext import check_status
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "attention", "attention_bwd", "rmsnorm", "swiglu", "ce", "adamw", "qk_norm_rope", "grouped_gemm", "router"])
+    ap.add_argument("--op", required=True, choices=["gemm", "attention", "attention_bwd", "rmsnorm", "swiglu", "ce", "adamw", "qk_norm_rope", "grouped_gemm", "router", "delta_rule"])
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--layout", default="tn", choices=["tn", "nn", "tt"])
     ap.add_argument("--seq", type=int, default=8192); ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--rows", type=int, default=8192); ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--chunk", type=int, default=64); ap.add_argument("--channel-decay", action="store_true"); ap.add_argument("--loop", action="store_true")
     ap.add_argument("--iters", type=int, default=10); ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--peak-tflops", type=float, default=None); ap.add_argument("--peak-gbs", type=float, default=None)
     a = ap.parse_args()
@@ -84,6 +85,23 @@ def main() -> None:
             ms = timeit(lambda: torch.autograd.grad(o, [q, k, v], go, retain_graph=True), a.iters, a.warmup)
         tf = fl / ms / 1e9
         out.update(seq=S, heads=[H, Hk], head_dim=d, ms=ms, tflops_causal=tf, frac_of_peak=tf / ptf)
+    elif a.op == "delta_rule":
+        # gated delta rule, forward + backward in fp32: --heads, --head-dim, --chunk; --channel-decay for a decay per key channel;
+        # --loop forces the chunk-after-chunk form the scan form replaces
+        import torch.nn.functional as F
+        from ..models import families as fam
+        S, H, d = a.seq, a.heads, a.head_dim
+        g = torch.Generator(device=dev).manual_seed(0)
+        x = [F.normalize(torch.randn(S, H, d, generator=g, device=dev), dim=-1).requires_grad_() for _ in range(2)]
+        x += [torch.randn(S, H, d, generator=g, device=dev).requires_grad_(), torch.rand(S, H, generator=g, device=dev).requires_grad_(),
+              (-F.softplus(torch.randn(S, H, d if a.channel_decay else 1, generator=g, device=dev))).requires_grad_()]
+        if a.loop:
+            fam.SEQUENTIAL_CHUNKS = 1 << 30
+
+        def step():
+            torch.autograd.grad(fam.chunked_delta_rule(*x, a.chunk).square().sum(), x)
+        ms = timeit(step, a.iters, a.warmup)
+        out.update(seq=S, heads=H, head_dim=d, chunk=a.chunk, channel_decay=a.channel_decay, form="loop" if a.loop else "scan", ms_fwd_bwd=ms)
     elif a.op == "rmsnorm":
         x = torch.randn(a.rows, a.cols, device=dev).bfloat16(); w = torch.ones(a.cols, device=dev).bfloat16()
         ms = timeit(lambda: ops.rms_norm(x, w, 1e-6), a.iters, a.warmup)
