@@ -142,3 +142,16 @@ def test_long_sequences_carry_and_return_state_like_short_ones():
         b, s_b = chunked_delta_rule(q[40:], k[40:], v[40:], beta[40:], ld[40:], 8, s_a, True)        # 15 chunks: scan form from a state
         assert torch.allclose(torch.cat((a, b)), whole, atol=2e-5) and torch.allclose(s_b, s_whole, atol=2e-5)
         assert torch.allclose(whole, delta_rule_scan(q, k, v, beta, ld), atol=2e-5)
+
+
+def test_scan_blocks_carry_the_state(monkeypatch):
+    """With a tiny block budget the scan runs as several blocks of chunks; values and gradients do not change."""
+    from torchllmtuner_b200.models import families as fam
+    x = _inputs(200, 2, 8, 6, 8, seed=5)
+    want = chunked_delta_rule(*x, 8)
+    gw = torch.autograd.grad(want.square().sum(), x)
+    monkeypatch.setattr(fam, "SCAN_BLOCK_BYTES", 1)            # -> blocks of SEQUENTIAL_CHUNKS + 1 = 9 chunks, 25 chunks in all
+    got = chunked_delta_rule(*x, 8)
+    assert torch.allclose(got, want, atol=1e-6)
+    for a, b in zip(torch.autograd.grad(got.square().sum(), x), gw):
+        assert torch.allclose(a, b, atol=1e-5)

@@ -122,17 +122,22 @@ def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64, initial_state=
         # The state update is affine in the state: S_{n+1} = A_n S_n + B_n with A_n = diag(decay_n) - Kend_n^T W2_n and
         # B_n = Kend_n^T W1_n, both known for every chunk at once. A two-level scan over those maps leaves about
         # 2 sqrt(N) dependent steps instead of N, and every output product becomes one batched product over all chunks.
-        KendT = Kend.transpose(2, 3)
-        A = (-KendT) @ W2
-        A.diagonal(dim1=-2, dim2=-1).add_(dec_end.squeeze(-1).expand(N, H, dk))
-        S_all, S = affine_scan(A, KendT @ W1, S)
-        U = W1 - W2 @ S_all
-        o = Qt @ S_all + QK @ U
+        # Blocks of chunks bound the [chunks, H, dk, dk] maps (and what autograd keeps of them); the state carries over.
+        blk = max(SEQUENTIAL_CHUNKS + 1, SCAN_BLOCK_BYTES // (H * dk * dk * q.element_size()))
+        outs = []
+        for w1, w2, qt, qk, kend, dec in zip(*(t.split(blk) for t in (W1, W2, Qt, QK, Kend, dec_end))):
+            kendT = kend.transpose(2, 3)
+            A = (-kendT) @ w2
+            A.diagonal(dim1=-2, dim2=-1).add_(dec.squeeze(-1).expand(A.shape[0], H, dk))
+            S_all, S = affine_scan(A, kendT @ w1, S)
+            outs.append(qt @ S_all + qk @ (w1 - w2 @ S_all))
+        o = torch.cat(outs) if len(outs) > 1 else outs[0]
     o = o.permute(0, 2, 1, 3).reshape(N * C, H, dv)
     return (o[:T], S) if return_state else o[:T]
 
 
 SEQUENTIAL_CHUNKS = 8       # up to this many chunks the plain chunk-after-chunk loop is the cheaper form
+SCAN_BLOCK_BYTES = 1 << 29  # size of the state-transition maps of one scan block
 
 
 def affine_scan(A, B, S0):
