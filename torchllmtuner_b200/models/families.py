@@ -105,7 +105,10 @@ def chunked_delta_rule(q, k, v, beta, log_decay, chunk: int = 64, initial_state=
     QK = QK.masked_fill(~tri, 0.0)
     eG = G.exp()
     IA = A + torch.eye(C, dtype=q.dtype, device=q.device)
-    W = torch.linalg.solve_triangular(IA, torch.cat((beta * v, beta * eG * k), -1), upper=False)
+    # (I + A)^-1 by forward substitution against the identity (C columns), then one product with the dv + dk right-hand
+    # sides: the substitution is the slow part on the device and this way it runs on a quarter of the columns
+    inv = torch.linalg.solve_triangular(IA, torch.eye(C, dtype=q.dtype, device=q.device).expand_as(IA), upper=False)
+    W = inv @ torch.cat((beta * v, beta * eG * k), -1)
     W1, W2 = W.split((dv, W.shape[-1] - dv), -1)
     Qt = eG * q
     Kend = (G[:, :, -1:, :] - G).exp() * k
