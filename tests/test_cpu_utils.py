@@ -1,0 +1,240 @@
+"""Small services on their own: FLOP accounting, aligned garbage collection, tensor trees, corpus identity, collation,
+input sharding for context and tensor parallelism, the non-finite guard, capability probes, meta materialisation,
+metric loggers, dispatch timing, progress state."""
+import gc
+import json
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+from torchllmtuner_b200.errors import ConfigError, EnvironmentUnsupportedError, LLMTunerError
+
+
+def test_flops_per_token_formula():
+    from torchllmtuner_b200.utils.flops import generic_flops_per_token
+    D, L, H, Hkv, d, F, V, S = 64, 3, 4, 2, 16, 128, 1000, 256
+    attn = 2 * (D * H * d + 2 * D * Hkv * d + H * d * D)
+    want = 3 * (L * (attn + 6 * D * F) + 2 * V * D) + L * 6 * H * 2 * d * S
+    got = generic_flops_per_token(hidden_size=D, num_layers=L, num_heads=H, num_kv_heads=Hkv, head_dim=d, intermediate_size=F,
+                                  vocab_size=V, seq_len=S)
+    assert got == want
+    # experts replace the dense MLP only on the layers the mask names
+    moe = 2 * (D * 8 + 2 * 3 * D * 32 + 3 * D * 16)
+    got = generic_flops_per_token(hidden_size=D, num_layers=L, num_heads=H, num_kv_heads=Hkv, head_dim=d, intermediate_size=F,
+                                  vocab_size=V, seq_len=S, num_experts=8, top_k=2, moe_intermediate_size=32,
+                                  shared_intermediate_size=16, moe_layer_mask=[False, True, True])
+    assert got == 3 * (L * attn + 6 * D * F + 2 * moe + 2 * V * D) + L * 6 * H * 2 * d * S
+
+
+def test_peak_flops_table_and_measured_override(monkeypatch):
+    from torchllmtuner_b200.utils import monitoring
+    assert monitoring.get_peak_flops("NVIDIA B200") == 2.25e15 and monitoring.get_peak_flops("NVIDIA H100 PCIe") == 756e12
+    assert monitoring.get_peak_flops("some other device") == 0.0
+    monkeypatch.setenv("LLMT_MEASURED_PEAK_TFLOPS", "1400")
+    assert monitoring.get_measured_peak_flops() == 1.4e15
+
+
+def test_garbage_collection_runs_on_its_own_schedule_and_restores_the_setting():
+    from torchllmtuner_b200.utils.garbage_collection import GarbageCollection
+    assert gc.isenabled()
+    with GarbageCollection(gc_freq=3) as g:
+        assert not gc.isenabled()
+        seen = []
+        for step in range(1, 10):
+            g.last_pause_s = -1.0
+            g.run(step)
+            if g.last_pause_s >= 0:
+                seen.append(step)
+        assert seen == [3, 6, 9]
+    assert gc.isenabled()
+    with pytest.raises(ValueError):
+        GarbageCollection(gc_freq=0)
+
+
+def test_tensor_trees():
+    from torchllmtuner_b200.accelerator.tensor_tree import clone_local_tensor, get_tensor_tree_device, move_tensor_tree
+    tree = {"a": [torch.ones(2), ("x", torch.zeros(1))], "b": 3}
+    assert get_tensor_tree_device(tree) == torch.device("cpu") and get_tensor_tree_device({"n": [1, "s"]}) is None
+    moved = move_tensor_tree(tree, "cpu")
+    assert moved["b"] == 3 and isinstance(moved["a"][1], tuple) and torch.equal(moved["a"][0], tree["a"][0])
+    p = nn.Parameter(torch.ones(3))
+    c = clone_local_tensor(p)
+    assert not c.requires_grad and c.data_ptr() != p.data_ptr()
+
+
+def test_corpus_identity_follows_data_and_settings(tmp_path):
+    from types import SimpleNamespace as NS
+    from torchllmtuner_b200.datasets.corpus_identity import corpus_data_identity
+    f = tmp_path / "a.jsonl"
+    f.write_text('{"text": "one"}\n')
+    cfg = NS(data_identity="", dataset="local_text", packing="greedy", num_packing_bins=4, max_num_documents=0, prompt_field="p",
+             response_field="r", text_field="text", messages_field="m", chat_template=None)
+    a = corpus_data_identity(cfg, "tok-1", [str(f)])
+    assert a == corpus_data_identity(cfg, "tok-1", [str(f)]) and len(a) == 24
+    assert a != corpus_data_identity(cfg, "tok-2", [str(f)])
+    cfg2 = NS(**{**vars(cfg), "packing": "none"})
+    assert a != corpus_data_identity(cfg2, "tok-1", [str(f)])
+    f.write_text('{"text": "two!"}\n')
+    assert a != corpus_data_identity(cfg, "tok-1", [str(f)])
+    assert corpus_data_identity(NS(**{**vars(cfg), "data_identity": "pinned"}), "tok-9") == "pinned"
+
+
+def test_text_collator_builds_global_document_cuts():
+    from types import SimpleNamespace as NS
+    from torchllmtuner_b200.datasets.collators import TextCollator
+    from torchllmtuner_b200.datasets.contracts import IGNORE_INDEX
+    rows = [NS(tokens=[1, 2, 3, 4], labels=[2, 3, IGNORE_INDEX, 9], positions=[0, 1, 0, 1], cuts=[0, 2, 4]),
+            NS(tokens=[5, 6, 7, 8], labels=[6, 7, 8, IGNORE_INDEX], positions=[0, 1, 2, 3], cuts=[0, 4])]
+    b = TextCollator(4)(rows)
+    assert b["input"].shape == (2, 4) and b["cu_seqlens"].tolist() == [0, 2, 4, 8] and b["num_valid_tokens"] == 6
+    assert b["positions"][0].tolist() == [0, 1, 0, 1]
+
+
+def test_input_sharding_covers_every_row_exactly_once():
+    from torchllmtuner_b200.parallel.input_sharding import (contiguous_chunk, cp_row_index, headtail_chunks,
+                                                            shard_model_inputs)
+    assert headtail_chunks(16, 2, 0) == [(0, 4), (12, 16)] and headtail_chunks(16, 2, 1) == [(4, 8), (8, 12)]
+    with pytest.raises(ConfigError):
+        headtail_chunks(10, 2, 0)
+    with pytest.raises(ConfigError):
+        contiguous_chunk(10, 3, 0)
+    for lb in (None, "headtail"):
+        rows = torch.cat([cp_row_index(2, 16, 4, r, lb) for r in range(4)])
+        assert sorted(rows.tolist()) == list(range(32))
+    B, S = 2, 16
+    inputs = {"batch": B, "seq": S, "tokens": torch.arange(B * S), "targets": torch.arange(B * S) + 1,
+              "positions": torch.arange(S).repeat(B), "cu_seqlens": torch.tensor([0, 16, 32], dtype=torch.int32)}
+    assert shard_model_inputs(inputs, None) is inputs and shard_model_inputs(inputs, {"cp": 1, "tp": 1}) is inputs
+    # CP 2 (head-tail) x TP 2: four ranks tile the tokens; positions stay whole per CP rank
+    seen = []
+    for c in range(2):
+        for t in range(2):
+            out = shard_model_inputs(inputs, {"cp": 2, "cp_rank": c, "tp": 2, "tp_rank": t, "load_balancer": "headtail"})
+            assert out["positions"].numel() == 16 and out["tokens"].numel() == 8 and out["global_rows"] == 32
+            assert torch.equal(out["targets"], out["tokens"] + 1)
+            assert torch.equal(out["cp_rows"][out["tp_span"][0]:out["tp_span"][1]], out["tokens"])
+            seen += out["tokens"].tolist()
+    assert sorted(seen) == list(range(32))
+    # two-level CP: key/value axis 2 x ulysses 2
+    seen = []
+    for kv in range(2):
+        for u in range(2):
+            out = shard_model_inputs(inputs, {"cp": 4, "cp_kv": 2, "cp_ulysses": 2, "cp_kv_rank": kv, "cp_ulysses_rank": u,
+                                              "cp_rank": kv * 2 + u, "tp": 1, "load_balancer": "headtail"})
+            seen += out["tokens"].tolist()
+    assert sorted(seen) == list(range(32))
+
+
+def test_non_finite_guard_names_the_first_bad_block_without_reading_back_in_forward():
+    from torchllmtuner_b200.parallel.graph_capture import SDCGuard, check_sdc
+
+    class Scale(nn.Module):
+        def __init__(self, s):
+            super().__init__()
+            self.s, self.width = s, 7
+
+        def forward(self, x):
+            return x * self.s
+    model = nn.Sequential()
+    model._sdc_flag = torch.zeros((), dtype=torch.int32)
+    for i, s in enumerate([1.0, float("inf"), float("nan")]):
+        model.append(SDCGuard(Scale(s), i, model._sdc_flag))
+    assert model[0].width == 7                                # attributes of the wrapped block stay reachable
+    model[0](torch.ones(3))
+    check_sdc(model)                                           # healthy: nothing raised
+    model(torch.ones(3))
+    with pytest.raises(LLMTunerError, match="block 1"):
+        check_sdc(model)
+    check_sdc(model)                                           # the flag was cleared by the report
+    check_sdc(nn.Linear(2, 2))                                 # a model without the guard
+
+
+def test_capability_probes():
+    from torchllmtuner_b200.accelerator import capabilities as cap
+    rep = cap.report()
+    assert set(rep) == set(cap.CAPABILITIES) and rep["dcp"] and rep["yaml"]
+    assert rep["cuda"] == torch.cuda.is_available()
+    with pytest.raises(KeyError):
+        cap.has("warp_drive")
+    if not rep["cuda"]:
+        with pytest.raises(EnvironmentUnsupportedError, match="needs a device"):
+            cap.require("cuda", "needs a device")
+
+
+def test_meta_materialisation_keeps_ties_marks_and_buffer_persistence():
+    from torchllmtuner_b200.memory.materialization import materialize_meta_model
+
+    class Tied(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(10, 4)
+            self.head = nn.Linear(4, 10, bias=False)
+            self.head.weight = self.embed.weight
+            self.frozen = nn.Parameter(torch.empty(3), requires_grad=False)
+            self.register_buffer("table", torch.empty(5), persistent=False)
+            self.other = nn.Module()
+            self.other.register_buffer("table", self.table)
+    with torch.device("meta"):
+        m = Tied()
+    m.embed.weight.tp_shard_dim = 0
+    assert materialize_meta_model(m, "cpu") == 3
+    assert m.head.weight is m.embed.weight and not m.embed.weight.is_meta and m.embed.weight.tp_shard_dim == 0
+    assert not m.frozen.requires_grad and m.table is m.other.table and float(m.table.abs().sum()) == 0.0
+    assert "table" not in m.state_dict() and len(list(m.parameters())) == 2
+    assert materialize_meta_model(m, "cpu") == 0
+
+
+def test_metric_loggers(tmp_path):
+    from types import SimpleNamespace as NS
+    from torchllmtuner_b200.utils.metric_loggers import JsonlLogger, LoggerContainer, build_metric_logger
+    path = tmp_path / "m" / "metrics.jsonl"
+    lg = LoggerContainer([JsonlLogger(str(path))])
+    lg.log({"loss": 1.5, "tps": 10}, 3)
+    lg.log({"loss": 1.25}, 4)
+    lg.close()
+    lines = [json.loads(x) for x in path.read_text().splitlines()]
+    assert [x["step"] for x in lines] == [3, 4] and lines[0]["loss"] == 1.5
+    cfg = NS(log_ranks=[0], save_for_all_ranks=False, enable_tensorboard=False, enable_wandb=False, save_tb_folder="tb", tag=None)
+    assert build_metric_logger(cfg, str(tmp_path), rank=1).loggers == []
+    assert build_metric_logger(cfg, str(tmp_path), rank=0).loggers == []
+    cfg.enable_tensorboard, cfg.save_for_all_ranks = True, True
+    c = build_metric_logger(cfg, str(tmp_path), rank=1)
+    assert len(c.loggers) == 1
+    c.log({"loss": 2.0}, 1)
+    c.close()
+    assert os.path.isdir(tmp_path / "tb" / "rank_1")
+
+
+def test_dispatch_timer_percentiles_on_the_host():
+    from torchllmtuner_b200.trainer.runtime.observer import DispatchTimer
+    t = DispatchTimer("cpu")
+    for _ in range(5):
+        with t.span("dispatch"):
+            pass
+    with t.span("combine"):
+        pass
+    out = t.collect()
+    assert {"moe/dispatch_p50(ms)", "moe/dispatch_p90(ms)", "moe/dispatch_total(ms)", "moe/combine_p50(ms)"} <= set(out)
+    assert out["moe/dispatch_p50(ms)"] <= out["moe/dispatch_p90(ms)"] <= out["moe/dispatch_total(ms)"]
+    assert t.collect() == {}
+
+
+def test_progress_state_round_trip():
+    from torchllmtuner_b200.trainer.runtime.results import StepResult, TrainingProgress
+    p = TrainingProgress(step=7, ntokens_seen=1234)
+    q = TrainingProgress()
+    q.load_state_dict(json.loads(json.dumps(p.state_dict())))
+    assert q == p
+    r = StepResult(step=1, loss=2.0, grad_norm=0.5, lr=1e-3, global_tokens=64, step_seconds=0.1)
+    assert r.extra == {} and r.max_loss is None
+
+
+def test_nvtx_ranges_are_free_when_disabled():
+    from torchllmtuner_b200.utils import nvtx
+    nvtx.enable(True)                      # without a device this stays off
+    assert nvtx._ENABLED == torch.cuda.is_available()
+    nvtx.enable(False)
+    with nvtx.nvtx_range("step"):
+        pass

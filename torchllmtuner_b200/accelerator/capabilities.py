@@ -18,8 +18,9 @@ def _probe(name: str) -> bool:
         from ..ops.cuda_ext import available
         return available()
     if name == "symm_mem":
+        import importlib                       # an `import torch.x` statement here would make `torch` local to the function
         try:
-            import torch.distributed._symmetric_memory  # noqa: F401
+            importlib.import_module("torch.distributed._symmetric_memory")
             return torch.cuda.is_available()
         except ImportError:
             return False
@@ -28,8 +29,9 @@ def _probe(name: str) -> bool:
             return False
         return all(torch.cuda.can_device_access_peer(0, i) for i in range(1, torch.cuda.device_count()))
     if name == "dcp":
+        import importlib
         try:
-            import torch.distributed.checkpoint  # noqa: F401
+            importlib.import_module("torch.distributed.checkpoint")
             return True
         except ImportError:
             return False
