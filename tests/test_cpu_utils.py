@@ -238,3 +238,78 @@ def test_nvtx_ranges_are_free_when_disabled():
     nvtx.enable(False)
     with nvtx.nvtx_range("step"):
         pass
+
+
+# ---------------------------------------------------------------------------------------------- config groups on their own
+def test_parallel_config_rules():
+    from torchllmtuner_b200.config.parallel_config import (ContextParallelConfig, ExpertParallelConfig, FSDPConfig, ParallelConfig,
+                                                           TensorParallelConfig)
+    p = ParallelConfig(tensor_parallel_size=2, context_parallel_ulysses_size=2)
+    assert p.cp_size == 2 and p.derive_dp(8) == (1, 2)
+    assert ParallelConfig(data_parallel_replicate_size=2, data_parallel_shard_size=2).derive_dp(4) == (2, 2)
+    with pytest.raises(ConfigError, match="not divisible"):
+        ParallelConfig(tensor_parallel_size=3).derive_dp(8)
+    with pytest.raises(ConfigError, match="!= world size"):
+        ParallelConfig(data_parallel_shard_size=3).derive_dp(8)
+    with pytest.raises(ConfigError):
+        ParallelConfig(tensor_parallel_size=0)
+    with pytest.raises(ConfigError, match="sequence-parallel"):
+        ParallelConfig(tensor_parallel_size=2, tp_config=TensorParallelConfig(enable_sequence_parallel=False))
+    with pytest.raises(ConfigError):
+        FSDPConfig(fsdp_reduce_dtype="float16")
+    with pytest.raises(ConfigError, match="cpu_offload"):
+        FSDPConfig(fsdp_cpu_offload=True, enable_fsdp_symm_mem=True)
+    with pytest.raises(ConfigError):
+        FSDPConfig(fsdp_ignored_modules=[""])
+    with pytest.raises(ConfigError, match="ptrr"):
+        ContextParallelConfig(context_parallel_load_balancer="ptrr")
+    with pytest.raises(ConfigError):
+        ContextParallelConfig(context_parallel_strategy="ring")
+    with pytest.raises(ConfigError, match=">= 1"):
+        ExpertParallelConfig(ep_capacity_factor=0.5)
+    with pytest.raises(ConfigError, match=">= 0"):
+        ExpertParallelConfig(router_aux_loss_coef=-1.0)
+    with pytest.raises(ConfigError, match="registered gap"):
+        ExpertParallelConfig(ep_token_dispatcher="mc2")
+
+
+def test_model_and_observability_config_rules():
+    from torchllmtuner_b200.config.model_config import ModelConfig
+    from torchllmtuner_b200.config.observability_config import MetricsConfig, ProfilerConfig
+    assert ModelConfig(compute_dtype="bfloat16").compute_dtype == "bfloat16"
+    for bad in (dict(initialization_device="tpu"), dict(hidden_size=0), dict(qkv_projection="packed"),
+                dict(experts_implementation="triton"), dict(compute_dtype="int8")):
+        with pytest.raises(ConfigError):
+            ModelConfig(**bad)
+    assert MetricsConfig(log_ranks=("0", 3)).log_ranks == [0, 3]
+    with pytest.raises(ConfigError):
+        MetricsConfig(log_freq=0)
+    ProfilerConfig(enable_profiling=True, profile_freq=4, profiler_active=1, profiler_warmup=3)
+    with pytest.raises(ConfigError, match="profile_freq"):
+        ProfilerConfig(enable_profiling=True, profile_freq=3, profiler_active=1, profiler_warmup=3)
+    with pytest.raises(ConfigError, match="Ascend"):
+        ProfilerConfig(npu_profiler_level="level1")
+
+
+def test_rank_aware_logging(monkeypatch, tmp_path):
+    import logging
+    from torchllmtuner_b200.utils import logging as L
+    flt = L._RankFilter()
+    rec = lambda lvl: logging.LogRecord("x", lvl, __file__, 1, "m", None, None)  # noqa: E731
+    monkeypatch.setenv("RANK", "3")
+    L.set_log_ranks([0])
+    assert not flt.filter(rec(logging.INFO)) and flt.filter(rec(logging.ERROR))      # every rank prints errors
+    L.set_log_ranks([0, 3])
+    assert flt.filter(rec(logging.INFO))
+    L.set_log_ranks([0])
+    monkeypatch.setenv("RANK", "0")
+    log = L.get_logger("torchllmtuner_b200.trainer", log_file=str(tmp_path / "logs" / "run.log"))
+    assert log.name == "torchllmtuner_b200.trainer"
+    log.info("hello from the test")
+    for h in logging.getLogger("torchllmtuner_b200").handlers:
+        h.flush()
+    assert "hello from the test" in (tmp_path / "logs" / "run.log").read_text()
+    root = logging.getLogger("torchllmtuner_b200")
+    for h in [h for h in root.handlers if isinstance(h, logging.FileHandler)]:
+        root.removeHandler(h)
+        h.close()
