@@ -28,8 +28,12 @@ def _exchange_worker(rank, world, port, out):
 
 
 def test_variable_size_exchange_without_native_all_to_all(tmp_path):
+    import socket
     out = str(tmp_path / "res")
-    mp.spawn(_exchange_worker, args=(3, 29831, out), nprocs=3, join=True)
+    with socket.socket() as sk:                       # a port nobody holds right now
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    mp.spawn(_exchange_worker, args=(3, port, out), nprocs=3, join=True)
     assert open(out).read() == "ok"
 
 

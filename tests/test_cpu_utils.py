@@ -303,13 +303,18 @@ def test_rank_aware_logging(monkeypatch, tmp_path):
     assert flt.filter(rec(logging.INFO))
     L.set_log_ranks([0])
     monkeypatch.setenv("RANK", "0")
+    root = logging.getLogger("torchllmtuner_b200")
+    earlier = [h for h in root.handlers if isinstance(h, logging.FileHandler)]      # one file per process: set any aside
+    for h in earlier:
+        root.removeHandler(h)
     log = L.get_logger("torchllmtuner_b200.trainer", log_file=str(tmp_path / "logs" / "run.log"))
     assert log.name == "torchllmtuner_b200.trainer"
     log.info("hello from the test")
     for h in logging.getLogger("torchllmtuner_b200").handlers:
         h.flush()
     assert "hello from the test" in (tmp_path / "logs" / "run.log").read_text()
-    root = logging.getLogger("torchllmtuner_b200")
     for h in [h for h in root.handlers if isinstance(h, logging.FileHandler)]:
         root.removeHandler(h)
         h.close()
+    for h in earlier:
+        root.addHandler(h)
