@@ -40,7 +40,9 @@ def test_concat_then_split_positions_cuts_and_border_labels():
     rows = list(concat_then_split([_seq(5), _seq(7, 100), _seq(3, 200)], seq_len=8, pad_id=0))
     assert [len(r.tokens) for r in rows] == [8, 8]
     assert rows[0].cuts == [0, 5, 8] and rows[0].positions == [0, 1, 2, 3, 4, 0, 1, 2]
-    assert rows[0].labels[4] == IGNORE_INDEX and rows[0].labels[7] == IGNORE_INDEX       # nothing predicted across borders
+    assert rows[0].labels[4] == IGNORE_INDEX                 # nothing predicted across a document border
+    assert rows[0].labels[7] == 103 and rows[1].tokens[0] == 103   # a document cut by the row end still predicts its next token
+    assert rows[1].labels[3] == IGNORE_INDEX                 # ... and its true end is a border
     assert rows[1].cuts[-1] == 8 and rows[1].tokens[-1] == 0 and rows[1].labels[-1] == IGNORE_INDEX
     capped = list(concat_then_split([_seq(2), _seq(2, 10), _seq(2, 20)], seq_len=8, max_num_documents=2))
     assert len(capped) == 2 and capped[0].cuts[:3] == [0, 2, 4]

@@ -2,7 +2,8 @@
 
   concat_then_split   documents are concatenated into a token stream and cut every `seq_len` tokens; a document that
                       crosses a cut is split (its continuation restarts positions at 0 and is a document of its own for
-                      the attention mask); `max_num_documents` caps the documents per row (the row is then padded).
+                      the attention mask; the last token before the cut still predicts the first one after it);
+                      `max_num_documents` caps the documents per row (the row is then padded).
   first_fit           documents (truncated to seq_len) go into the first of `num_bins` open rows with room; a row is
                       emitted when no open row fits the next document; rows are padded.
 Each packed row carries tokens, shifted labels (no loss across document borders or on padding), per-document positions
@@ -27,7 +28,10 @@ class PackedRow:
     def add(self, seq: TextSequence, start: int, n: int) -> None:
         self.tokens += seq.tokens[start:start + n]
         lab = seq.labels[start:start + n]
-        lab[-1:] = [IGNORE_INDEX] if start + n < len(seq.tokens) or True else lab[-1:]   # nothing is predicted across a border
+        if start + n >= len(seq.tokens):
+            lab[-1:] = [IGNORE_INDEX]          # nothing is predicted across a document border
+        # a document cut by the end of the row keeps its last target: the token that opens its continuation in the next
+        # row (reference: llmtuner/datasets/packing/iterators.py:178, labels are sliced as they are)
         self.labels += lab
         self.positions += list(range(n))
         self.cuts.append(len(self.tokens))
