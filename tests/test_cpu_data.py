@@ -166,3 +166,26 @@ def test_dataset_composition_concat_mix_and_epoch_order():
     assert sorted(parts[0] + parts[1]) == list(range(10)) and not set(parts[0]) & set(parts[1])   # DP shards partition the epoch
     assert epoch_order(10, 0, pol, 0, 2) != epoch_order(10, 1, pol, 0, 2)                          # reshuffled per epoch
     assert epoch_order(10, 0, DatasetIterationPolicy(shuffle=False), 1, 2) == [1, 3, 5, 7, 9]
+
+
+def test_prefetch_thread_ends_when_the_cursor_is_restored_or_the_loader_closed(tmp_path):
+    import time
+    texts = [" ".join(f"w{(i * 7 + j) % 50}" for j in range(20)) for i in range(40)]
+    data = tmp_path / "corpus.jsonl"
+    data.write_text("\n".join(json.dumps({"text": t}) for t in texts))
+    vocab = tmp_path / "vocab.json"
+    WhitespaceTokenizer.from_texts(texts).save(str(vocab))
+    cfg = DataloaderConfig(dataset="local_jsonl", dataset_path=str(data), tokenizer_path=str(vocab), tokenizer_backend="whitespace",
+                           num_prefetch_batches=2)
+    dl = build_dataloader(cfg, vocab_size=1000, global_batch=2, seq_len=16, seed=0, dp_rank=0, dp_degree=1, rows_per_rank=2)
+    first = [next(dl) for _ in range(3)]
+    t1 = dl._thread
+    time.sleep(0.1)
+    assert t1 is not None and t1.is_alive()                  # blocked on the full queue
+    sd = dl.state_dict()
+    dl.load_state_dict({**sd, "delivered": 1})
+    assert not t1.is_alive()
+    assert torch.equal(next(dl)["input"], first[1]["input"])  # the stream restarts at the restored cursor
+    t2 = dl._thread
+    dl.close()
+    assert not t2.is_alive() and dl._thread is None

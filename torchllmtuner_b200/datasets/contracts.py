@@ -34,6 +34,9 @@ class BaseDataLoader(Stateful):
     def __next__(self) -> dict:
         raise NotImplementedError
 
+    def close(self) -> None:
+        """Ends background work (prefetch threads); the trainer calls it on shutdown."""
+
 
 @dataclass
 class Batch:

@@ -33,6 +33,7 @@ class TextDataLoader(BaseDataLoader):
         self._q: queue.Queue | None = None
         self._thread = None
         self._gen = None
+        self._stop = None
 
     # ------------------------------------------------------------------ stream
     def _sequences(self):
@@ -64,17 +65,39 @@ class TextDataLoader(BaseDataLoader):
         if self.prefetch <= 0:
             self._gen = gen
             return
-        self._q = queue.Queue(maxsize=self.prefetch)
+        q, stop = queue.Queue(maxsize=self.prefetch), threading.Event()
+        self._q, self._stop = q, stop
+
+        def offer(item) -> bool:                 # a full queue must not hold the thread after the loader moved on
+            while not stop.is_set():
+                try:
+                    q.put(item, timeout=0.2)
+                    return True
+                except queue.Full:
+                    continue
+            return False
 
         def work():
             try:
                 for b in gen:
-                    self._q.put(b)
-                self._q.put(StopIteration)
+                    if not offer(b):
+                        return
+                offer(StopIteration)
             except Exception as e:  # noqa: BLE001
-                self._q.put(e)
+                offer(e)
         self._thread = threading.Thread(target=work, daemon=True)
         self._thread.start()
+
+    def _halt(self) -> None:
+        """Ends the prefetch thread of the current stream (a restored cursor or a closed loader starts a new one)."""
+        if getattr(self, "_stop", None) is not None:
+            self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        self._q = self._gen = self._thread = None
+
+    def close(self) -> None:
+        self._halt()
 
     def __iter__(self):
         return self
@@ -106,7 +129,7 @@ class TextDataLoader(BaseDataLoader):
         if int(sd["rows"]) != self.rows or int(sd["seq_len"]) != self.seq_len:
             raise ConfigError("batch layout changed since the data cursor was saved")
         self.delivered = int(sd["delivered"])
-        self._q = self._gen = None
+        self._halt()
 
 
 def build_text_dataloader(data_cfg, *, vocab_size, seq_len, seed, dp_rank, dp_degree, rows_per_rank, pin_memory=False, split="train"):

@@ -176,7 +176,7 @@ class Trainer:
         if self.closed:
             return
         self.closed = True
-        for name in ("checkpointer", "profiler", "metrics"):
+        for name in ("checkpointer", "profiler", "metrics", "dataloader"):
             obj = getattr(self, name, None)
             if obj is not None and hasattr(obj, "close"):
                 try:
