@@ -192,10 +192,10 @@ def test_metric_loggers(tmp_path):
     path = tmp_path / "m" / "metrics.jsonl"
     lg = LoggerContainer([JsonlLogger(str(path))])
     lg.log({"loss": 1.5, "tps": 10}, 3)
-    lg.log({"loss": 1.25}, 4)
+    lg.log({"loss": torch.tensor(1.25), "note": "warm-up", "skipped": None, "ok": True}, 4)       # only numbers are written
     lg.close()
     lines = [json.loads(x) for x in path.read_text().splitlines()]
-    assert [x["step"] for x in lines] == [3, 4] and lines[0]["loss"] == 1.5
+    assert [x["step"] for x in lines] == [3, 4] and lines[0]["loss"] == 1.5 and lines[1] == {"step": 4, "loss": 1.25}
     cfg = NS(log_ranks=[0], save_for_all_ranks=False, enable_tensorboard=False, enable_wandb=False, save_tb_folder="tb", tag=None)
     assert build_metric_logger(cfg, str(tmp_path), rank=1).loggers == []
     assert build_metric_logger(cfg, str(tmp_path), rank=0).loggers == []

@@ -6,6 +6,19 @@ import json
 import os
 
 
+def _scalars(metrics: dict) -> dict:
+    """Only numbers reach a sink: a step may carry notes (a string, None) beside its measurements."""
+    out = {}
+    for k, v in metrics.items():
+        if isinstance(v, bool) or v is None:
+            continue
+        try:
+            out[k] = float(v)
+        except (TypeError, ValueError):
+            continue
+    return out
+
+
 class BaseLogger:
     def log(self, metrics: dict, step: int) -> None:  # pragma: no cover - interface
         pass
@@ -22,7 +35,7 @@ class JsonlLogger(BaseLogger):
         self._f = open(path, "a")
 
     def log(self, metrics, step):
-        self._f.write(json.dumps({"step": step, **{k: float(v) for k, v in metrics.items()}}) + "\n")
+        self._f.write(json.dumps({"step": step, **_scalars(metrics)}) + "\n")
         self._f.flush()
 
     def close(self):
@@ -36,7 +49,7 @@ class TensorBoardLogger(BaseLogger):
         self.writer = SummaryWriter(log_dir, max_queue=1000)
 
     def log(self, metrics, step):
-        for k, v in metrics.items():
+        for k, v in _scalars(metrics).items():
             self.writer.add_scalar(k if self.tag is None else f"{self.tag}/{k}", v, step)
 
     def close(self):
@@ -50,7 +63,7 @@ class WandBLogger(BaseLogger):
         wandb.init(project=os.environ.get("WANDB_PROJECT", "torchllmtuner_b200"), dir=log_dir, config=config)
 
     def log(self, metrics, step):
-        self.wandb.log({(k if self.tag is None else f"{self.tag}/{k}"): v for k, v in metrics.items()}, step=step)
+        self.wandb.log({(k if self.tag is None else f"{self.tag}/{k}"): v for k, v in _scalars(metrics).items()}, step=step)
 
     def close(self):
         self.wandb.finish()
