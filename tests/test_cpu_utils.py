@@ -318,3 +318,34 @@ def test_rank_aware_logging(monkeypatch, tmp_path):
         h.close()
     for h in earlier:
         root.addHandler(h)
+
+
+def test_graph_replay_follows_the_forward_context():
+    """A replayed block must read the CURRENT call's context. The capture backend is replaced by one that re-runs the
+    captured closure (which only sees the static buffers), so stale buffers would show."""
+    from dataclasses import dataclass
+    from torchllmtuner_b200.ops.attn_meta import AttnMeta
+    from torchllmtuner_b200.parallel.graph_capture import GraphedInference, context_leaves
+    from torchllmtuner_b200.models.qwen3 import ForwardContext
+
+    class Block(nn.Module):
+        def forward(self, x, ctx):
+            return x * ctx.cos.sum() + len(ctx.attn_meta.pieces)
+
+    def fake_capture(fn):
+        out = fn()
+        def replay():
+            out.copy_(fn())
+        return out, replay
+    g = GraphedInference(Block(), capture=fake_capture).eval()
+    ctx = lambda c, cu: ForwardContext(torch.full((4,), float(c)), torch.zeros(4), AttnMeta.build(torch.tensor(cu)))  # noqa: E731
+    x = torch.ones(3)
+    with torch.no_grad():
+        assert g(x, ctx(1, [0, 8])).tolist() == [5.0] * 3 and g.captures == 1
+        assert g(x * 2, ctx(2, [0, 8])).tolist() == [17.0] * 3 and g.captures == 1       # same layout: tensors copied, replayed
+        assert g(x, ctx(1, [0, 3, 8])).tolist() == [6.0] * 3 and g.captures == 2         # other documents: captured anew
+        assert g(torch.ones(5), ctx(1, [0, 3, 8])).shape == (5,) and g.captures == 3     # other input shape
+    y = g(x.requires_grad_(), ctx(3, [0, 8]))                                           # with gradients: the plain block
+    assert y.requires_grad and g.captures == 3
+    t, c = context_leaves(ctx(1, [0, 4, 8]))
+    assert len(t) >= 2 and (0, 4, 0, 4, 0) in [tuple(p) for p in AttnMeta.build(torch.tensor([0, 4, 8])).pieces] and "pieces" in c

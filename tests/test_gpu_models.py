@@ -71,3 +71,31 @@ def test_delta_attention_and_latent_attention_families_train(family):
     finally:
         tr.close()
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_graphed_block_replays_with_the_current_context():
+    """A decoder block captured in a CUDA graph: a later call with other positions (same document layout) replays the graph
+    on ITS rotary tables; another document layout is captured anew. Every output equals the plain block's."""
+    from torchllmtuner_b200.models.qwen3 import Qwen3Config, Qwen3ForCausalLM
+    from torchllmtuner_b200.ops.attn_meta import AttnMeta
+    from torchllmtuner_b200.ops.cuda_ext import check_status
+    from torchllmtuner_b200.parallel.graph_capture import GraphedInference
+    dev = torch.device("cuda")
+    cfg = Qwen3Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=1, num_attention_heads=2,
+                      num_key_value_heads=1, head_dim=128, tie_word_embeddings=False)
+    m = Qwen3ForCausalLM(cfg, dtype=torch.bfloat16, device=dev)
+    m.initialize_parameters(0)
+    m.eval()
+    blk = m.model.layers[0]
+    g = GraphedInference(blk).eval()
+    torch.manual_seed(0)
+    with torch.no_grad():
+        for n, (off, cu) in enumerate([(0, [0, 256]), (7, [0, 256]), (0, [0, 100, 256]), (3, [0, 100, 256])]):
+            x = torch.randn(256, 256, device=dev).bfloat16()
+            ctx = m.build_context(torch.arange(256, device=dev) + off, AttnMeta.build(torch.tensor(cu), device=dev))
+            want = blk(x, ctx)
+            got = g(x, ctx)
+            assert torch.equal(got, want), n
+    assert g.captures == 2
+    torch.cuda.synchronize()
+    check_status("graphed block")

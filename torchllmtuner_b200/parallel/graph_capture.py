@@ -50,29 +50,86 @@ def check_sdc(model) -> None:
         raise LLMTunerError(f"non-finite output of decoder block {v - 1} (silent-data-corruption guard)")
 
 
-class GraphedInference(torch.nn.Module):
-    """Replays a captured forward for evaluation-mode calls with a fixed input shape."""
+def context_leaves(obj, max_depth: int = 6):
+    """(tensors, constants) reachable from a forward context, in a fixed order. A captured graph reads the tensors by
+    address and has the constants (document pieces, flags, sizes) baked into its launch parameters, so a later call may
+    replay the graph only if its constants are equal and its tensors fit the captured ones."""
+    tensors, consts = [], []
 
-    def __init__(self, inner):
+    def rec(o, depth):
+        if isinstance(o, torch.Tensor):
+            tensors.append(o)
+        elif depth >= max_depth:
+            consts.append(("deep", id(o)))
+        elif isinstance(o, (list, tuple)):
+            consts.append((type(o).__name__, len(o)))
+            for x in o:
+                rec(x, depth + 1)
+        elif isinstance(o, dict):
+            consts.append(("dict", tuple(o)))
+            for k in o:
+                rec(o[k], depth + 1)
+        elif isinstance(o, (int, float, str, bool, type(None))):
+            consts.append(o)
+        elif hasattr(o, "__dict__") and type(o).__module__.startswith(__name__.split(".")[0]):
+            consts.append(type(o).__qualname__)
+            for k in sorted(vars(o)):
+                consts.append(k)
+                rec(vars(o)[k], depth + 1)
+        else:
+            consts.append(("object", id(o)))          # anything else must be the very same object
+    rec(obj, 0)
+    return tensors, consts
+
+
+def _cuda_graph_capture(fn):
+    """Warm up on a side stream, capture `fn()` in a CUDA graph; returns (its output, a replay function)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fn()
+    return out, graph.replay
+
+
+class GraphedInference(torch.nn.Module):
+    """Replays a captured forward for evaluation-mode calls. The graph is tied to the input's shape AND to the forward
+    context it was captured with: a call whose context has the same constants (same documents, same flags) and tensors of
+    the same shapes copies them into the captured ones and replays; any other context is captured anew (a packed
+    validation set with a different document layout per batch therefore gains nothing, and loses nothing but the
+    capture). `capture` is the backend, replaceable for tests without a device."""
+
+    def __init__(self, inner, capture=_cuda_graph_capture):
         super().__init__()
-        self.inner, self.graph, self.static_in, self.static_out = inner, None, None, None
+        self.inner, self.capture = inner, capture
+        self.replay, self.static_in, self.static_out, self.static_tensors, self.static_consts = None, None, None, [], []
+        self.captures = 0
+
+    def _fits(self, x, tensors, consts) -> bool:
+        return (self.replay is not None and self.static_in.shape == x.shape and consts == self.static_consts
+                and len(tensors) == len(self.static_tensors)
+                and all(a.shape == b.shape and a.dtype == b.dtype and a.device == b.device for a, b in zip(tensors, self.static_tensors)))
 
     def forward(self, x, ctx):
-        if self.training or torch.is_grad_enabled() or not x.is_cuda:
+        if self.training or torch.is_grad_enabled() or (self.capture is _cuda_graph_capture and not x.is_cuda):
             return self.inner(x, ctx)
-        if self.graph is None or self.static_in.shape != x.shape:
+        tensors, consts = context_leaves(ctx)
+        if not self._fits(x, tensors, consts):
             self.static_in = x.clone()
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                for _ in range(2):
-                    self.inner(self.static_in, ctx)
-            torch.cuda.current_stream().wait_stream(s)
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self.static_out = self.inner(self.static_in, ctx)
+            self.static_tensors, self.static_consts = tensors, consts      # the captured context stays alive with the graph
+            static_ctx = ctx
+            self.static_out, self.replay = self.capture(lambda: self.inner(self.static_in, static_ctx))
+            self.captures += 1
+        else:
+            for mine, new in zip(self.static_tensors, tensors):
+                if mine is not new:
+                    mine.copy_(new)
         self.static_in.copy_(x)
-        self.graph.replay()
+        self.replay()
         return self.static_out.clone()
 
     def __getattr__(self, name):
