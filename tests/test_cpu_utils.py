@@ -349,3 +349,27 @@ def test_graph_replay_follows_the_forward_context():
     assert y.requires_grad and g.captures == 3
     t, c = context_leaves(ctx(1, [0, 4, 8]))
     assert len(t) >= 2 and (0, 4, 0, 4, 0) in [tuple(p) for p in AttnMeta.build(torch.tensor([0, 4, 8])).pieces] and "pieces" in c
+
+
+def test_loss_helpers_on_one_rank():
+    from torchllmtuner_b200.components.loss import (chunked_lm_head_cross_entropy, compute_logprobs, cross_entropy_loss, mse_loss,
+                                                    vocab_parallel_entropy)
+    from torchllmtuner_b200.ops import IGNORE_INDEX
+    torch.manual_seed(0)
+    logits = torch.randn(6, 11)
+    tgt = torch.tensor([1, 4, IGNORE_INDEX, 10, 0, IGNORE_INDEX])
+    keep = tgt != IGNORE_INDEX
+    want = torch.nn.functional.cross_entropy(logits[keep], tgt[keep], reduction="sum")
+    assert torch.allclose(cross_entropy_loss(logits, tgt), want, atol=1e-5)                       # a SUM over valid tokens
+    lp = compute_logprobs(logits, tgt)
+    assert torch.allclose(-lp.sum(), want, atol=1e-5) and float(lp[2]) == 0.0
+    p = logits.softmax(-1)
+    assert torch.allclose(vocab_parallel_entropy(logits), -(p * p.log()).sum(-1), atol=1e-5)
+    assert float(mse_loss(torch.ones(2, 3), torch.zeros(2, 3))) == 6.0
+    h, w = torch.randn(6, 5, requires_grad=True), torch.randn(11, 5, requires_grad=True)
+    full = cross_entropy_loss(h @ w.t(), tgt)
+    gh, gw = torch.autograd.grad(full, [h, w])
+    for chunks in (1, 3, 8):
+        loss = chunked_lm_head_cross_entropy(h, w, tgt, chunks)
+        a, b = torch.autograd.grad(loss, [h, w])
+        assert torch.allclose(loss, full, atol=1e-5) and torch.allclose(a, gh, atol=1e-5) and torch.allclose(b, gw, atol=1e-5)
