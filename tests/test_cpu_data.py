@@ -148,6 +148,12 @@ def test_huggingface_tokenizer_special_tokens_and_chat_template(tmp_path):
     text = t.apply_chat_template([{"role": "user", "content": "hello"}, {"role": "assistant", "content": "world"}])
     assert text.replace("</s>", " </s> ").split() == ["user", ":", "hello", "</s>", "assistant", ":", "world", "</s>"]
     assert t.identity().startswith("hf:") and t.identity() == HuggingFaceTokenizer(str(d)).identity()
+    # what published templates rely on: raise_exception, loop controls, tojson that keeps unicode
+    t.chat_template = ("{% for m in messages %}{% if m['role'] == 'tool' %}{{ raise_exception('tool turns need a call') }}{% endif %}"
+                       "{% if m['role'] == 'system' %}{% continue %}{% endif %}{{ m['content'] | tojson }}{% endfor %}")
+    assert t.apply_chat_template([{"role": "system", "content": "x"}, {"role": "user", "content": "h\u00e9"}]) == '"h\u00e9"'
+    with pytest.raises(Exception, match="tool turns need a call"):
+        t.apply_chat_template([{"role": "tool", "content": "x"}])
 
 
 def test_dataset_composition_concat_mix_and_epoch_order():

@@ -62,7 +62,15 @@ class HuggingFaceTokenizer(BaseTokenizer):
         if not self.chat_template:
             return super().apply_chat_template(messages, add_generation_prompt, **kw)
         import jinja2
-        env = jinja2.Environment(trim_blocks=True, lstrip_blocks=True)
+        from jinja2.sandbox import ImmutableSandboxedEnvironment
+
+        def raise_exception(message):                     # templates call this for malformed conversations
+            raise ConfigError(f"chat template: {message}")
+        # the environment published templates are written for: sandboxed, loop controls, `tojson` that keeps unicode
+        env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, extensions=["jinja2.ext.loopcontrols"])
+        env.globals["raise_exception"] = raise_exception
+        env.filters["tojson"] = lambda v, indent=None: json.dumps(v, ensure_ascii=False, indent=indent)
+        del jinja2
         return env.from_string(self.chat_template).render(messages=messages, add_generation_prompt=add_generation_prompt,
                                                           bos_token=self.bos_token or "", eos_token=self.eos_token or "", **kw)
 
