@@ -5,6 +5,7 @@ import shutil
 import pytest
 import torch
 
+from caps import skip_without
 from dist_cases import base_flat, run_ranks
 from torchllmtuner_b200 import LLMTunerConfig, Trainer
 
@@ -53,6 +54,7 @@ def test_keep_latest_k_and_atomic_publication(tmp_path):
     tr2.close()
 
 
+@skip_without("safetensors")
 def test_hf_export_import_round_trip(tmp_path):
     from torchllmtuner_b200.components.checkpointer.hf import load_hf_checkpoint, save_hf_checkpoint
     folder = str(tmp_path / "run")
@@ -273,6 +275,7 @@ def test_format_2_pieces_are_still_read(tmp_path):
     tr2.close()
 
 
+@skip_without("fsspec")
 def test_checkpoints_on_an_fsspec_store(tmp_path):
     """The same save / publish / purge / resume cycle against a URI: the in-memory fsspec filesystem stands in for an
     object store. A second run then starts from that store through `initial_load_path` while writing locally."""
@@ -309,6 +312,7 @@ def test_checkpoints_on_an_fsspec_store(tmp_path):
     fs.rm(uri[len("memory://"):], recursive=True)
 
 
+@skip_without("fsspec")
 def test_storage_path_rules():
     from torchllmtuner_b200.components.checkpointer.storage import FsspecStorage, LocalStorage, is_remote, storage_for
     assert is_remote("gs://bucket/run") and is_remote("memory://x") and not is_remote("/abs/run") and not is_remote("C:\\run")

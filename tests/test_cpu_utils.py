@@ -151,6 +151,16 @@ def test_non_finite_guard_names_the_first_bad_block_without_reading_back_in_forw
     check_sdc(nn.Linear(2, 2))                                 # a model without the guard
 
 
+def test_capability_gates_for_tests():
+    import caps
+    assert caps.available("yaml") and caps.available("dcp") and not caps.missing("yaml")
+    assert caps.available("cuda") == torch.cuda.is_available()
+    mark = caps.skip_without("yaml", "dcp")
+    assert mark.args == (False,) and "missing" in mark.kwargs["reason"]
+    with pytest.raises(KeyError):
+        caps.available("warp_drive")
+
+
 def test_capability_probes():
     from torchllmtuner_b200.accelerator import capabilities as cap
     rep = cap.report()
