@@ -161,3 +161,22 @@ def test_attention_backward_from_lse_matches_autograd(causal):
         got = ref.attention_backward_rows(q.detach(), k.detach(), v.detach(), o.detach(), go, lse.detach(), pieces, causal, 0.3, q_chunk=chunk)
         for a, b, n in zip(got, want, "qkv"):
             assert torch.allclose(a, b, rtol=1e-5, atol=1e-5), (n, chunk, (a - b).abs().max())    # softmax algebra is fp32
+
+
+def test_attention_accepts_values_narrower_than_keys():
+    """Latent attention has 192-wide keys and 128-wide values; the op's contract is q/k [.., d], v [.., dv] -> [.., dv]."""
+    import torch
+    from torchllmtuner_b200 import ops
+    from torchllmtuner_b200.errors import ConfigError
+    torch.manual_seed(0)
+    q, k, v = torch.randn(10, 4, 8), torch.randn(10, 2, 8), torch.randn(10, 2, 6)
+    meta = ops.AttnMeta.build(torch.tensor([0, 4, 10]))
+    o = ops.attention(q, k, v, meta, 0.3)
+    assert o.shape == (10, 4, 6)
+    s = torch.einsum("qhd,khd->hqk", q[:4], k[:4].repeat_interleave(2, 1)) * 0.3
+    s = s.masked_fill(torch.arange(4)[None, :] > torch.arange(4)[:, None], float("-inf"))
+    want = torch.einsum("hqk,khd->qhd", s.softmax(-1), v[:4].repeat_interleave(2, 1))
+    assert torch.allclose(o[:4], want, atol=1e-5)
+    assert ops.functional.device_head_dim(72) == 128 and ops.functional.device_head_dim(192) == 256 and ops.functional.device_head_dim(300) is None
+    with pytest.raises(ConfigError):
+        ops.attention(q, k, torch.randn(9, 2, 6), meta, 0.3)          # rows must agree
