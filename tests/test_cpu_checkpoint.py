@@ -328,3 +328,63 @@ def test_storage_path_rules():
     st.rmtree("memory://rules/a")
     st.rmtree("memory://rules/a")                                              # missing is fine
     assert not st.exists("memory://rules/a/a/f")
+
+
+@pytest.mark.parametrize("name", ["qwen3", "qwen3_moe", "qwen3_5", "qwen3_5_moe", "kimi_linear", "kimi_k3", "deepseek_v4"])
+def test_a_config_json_written_by_the_export_builds_the_same_architecture(name, tmp_path):
+    """`model_name_or_path=<folder>`: every family's exported config.json maps back to its registered builder and to the
+    same architecture (parameter names and shapes), through the state format's `arch_from_hf`."""
+    import json
+    from torchllmtuner_b200.config.model_config import ModelConfig
+    from torchllmtuner_b200.models.registry import build_registered_model
+    from torchllmtuner_b200.models.state import get_state_format
+    mc = ModelConfig(model_name_or_path=name, vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
+                     num_attention_heads=4, num_key_value_heads=2)
+    with torch.device("meta"):
+        m0 = build_registered_model(mc)
+    (tmp_path / "config.json").write_text(json.dumps(get_state_format(m0.state_format).hf_config(m0.config)))
+    with torch.device("meta"):
+        m1 = build_registered_model(ModelConfig(model_name_or_path=str(tmp_path)))
+    assert m1.state_format == m0.state_format and type(m1) is type(m0)
+    assert {n: tuple(p.shape) for n, p in m1.named_parameters()} == {n: tuple(p.shape) for n, p in m0.named_parameters()}
+    import dataclasses
+    a, b = dataclasses.asdict(m0.config), dataclasses.asdict(m1.config)
+    assert {k for k in a if a[k] != b[k]} <= {"model_type", "intermediate_size"}      # labels; V4 has no dense MLP width
+
+
+@skip_without("safetensors")
+def test_an_exported_folder_is_a_model_name_and_an_initial_checkpoint(tmp_path):
+    """Export a Kimi-K3 run as Hugging Face files; a new run names that folder as its model and its initial checkpoint and
+    starts from the same weights."""
+    from torchllmtuner_b200.components.checkpointer.hf import save_hf_checkpoint
+    cfg = _cfg(str(tmp_path / "run"), model_name_or_path="kimi_k3", num_hidden_layers=4)
+    cfg.model.arch_overrides = dict(head_dim=16, linear_heads=2, linear_head_dim=8)
+    tr = Trainer(cfg)
+    tr.train_step()
+    out = str(tmp_path / "hf")
+    save_hf_checkpoint(tr, out, "float32")
+    cfg2 = _cfg(str(tmp_path / "run2"), model_name_or_path=out, initial_load_path=out, initial_load_in_hf=True)
+    tr2 = Trainer(cfg2)
+    assert tr2.checkpointer.load()
+    a = {u.name: u.master[:u.numel].clone() for u in tr.asm.fsdp.units}
+    b = {u.name: u.master[:u.numel].clone() for u in tr2.asm.fsdp.units}
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    tr.close()
+    tr2.close()
+    # the preflight agrees, and notices a tensor that went missing or changed shape
+    import json
+    from safetensors.torch import load_file, save_file
+    from torchllmtuner_b200.components.checkpointer import hf_preflight
+    rep = hf_preflight.preflight(out)
+    assert rep["ok"] and rep["registered_model"] == "kimi_linear" and rep["missing_count"] == rep["unused_count"] == 0
+    assert hf_preflight.main([out]) == 0
+    wm = json.load(open(os.path.join(out, "model.safetensors.index.json")))["weight_map"]
+    victim = "model.layers.0.self_attn.A_log"
+    path = os.path.join(out, wm[victim])
+    tensors = load_file(path)
+    tensors[victim] = tensors[victim][:-1].clone()
+    dropped = next(k for k in tensors if k.endswith("q_conv1d.weight"))
+    del tensors[dropped]
+    save_file(tensors, path)
+    rep = hf_preflight.preflight(out)
+    assert not rep["ok"] and victim in rep["shape_mismatches"] and dropped in rep["missing"] and hf_preflight.main([out, "--json"]) == 1

@@ -1,0 +1,67 @@
+"""Folders as Hugging Face `transformers` writes them (`save_pretrained`): the preflight accepts them, a run names the
+folder as its model and initial checkpoint, and the loaded model reproduces the library model's logits. This pins what a
+config.json of today's library looks like: `rope_theta` nested in `rope_parameters`, `num_local_experts` for the expert
+count, a `dtype` key."""
+import pytest
+import torch
+
+from caps import require_env
+
+require_env("transformers", "safetensors")
+
+from dist_cases import base_flat  # noqa: E402
+from torchllmtuner_b200 import LLMTunerConfig, Trainer  # noqa: E402
+from torchllmtuner_b200.components.checkpointer import hf_preflight  # noqa: E402
+from torchllmtuner_b200.ops import AttnMeta  # noqa: E402
+
+DENSE = dict(vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+             head_dim=16, tie_word_embeddings=False)
+
+
+def _case(kind):
+    import transformers as T
+    if kind == "dense":
+        return T.Qwen3ForCausalLM, T.Qwen3Config(**DENSE)
+    return T.Qwen3MoeForCausalLM, T.Qwen3MoeConfig(**DENSE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24,
+                                                   norm_topk_prob=(kind == "moe_renormalised"))
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe", "moe_renormalised"])
+def test_qwen3_folder_from_save_pretrained(kind, tmp_path):
+    torch.manual_seed(0)
+    cls, hf_cfg = _case(kind)
+    hf_cfg._attn_implementation = "eager"
+    theirs = cls(hf_cfg).eval()
+    folder = str(tmp_path / "hf")
+    theirs.save_pretrained(folder, safe_serialization=True)
+    rep = hf_preflight.preflight(folder)
+    assert rep["ok"] and rep["registered_model"] == "qwen3_moe" and rep["expected_tensors"] == rep["stored_tensors"], rep
+    assert rep["parameters"] == sum(p.numel() for p in theirs.parameters())
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(model_name_or_path=folder, dump_folder=str(tmp_path / "run"), enable=True, initial_load_path=folder,
+                             initial_load_in_hf=True))
+    tr = Trainer(cfg)
+    assert tr.checkpointer.load()
+    assert tr.model.config.rope_theta == 10000.0                      # the library's default, not this framework's
+    S = 23
+    tok = torch.randint(0, 96, (S,))
+    with torch.no_grad():
+        ctx = tr.model.build_context(torch.arange(S), AttnMeta.build(torch.tensor([0, S], dtype=torch.int32), causal=True))
+        got = tr.model(tok, ctx)
+        want = theirs(input_ids=tok[None]).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=1e-5), (got - want).abs().max()
+
+
+def test_preflight_names_an_unknown_model_type(tmp_path):
+    (tmp_path / "config.json").write_text('{"model_type": "gpt_oss"}')
+    rep = hf_preflight.preflight(str(tmp_path))
+    assert not rep["ok"] and "no registered model" in rep["error"] and hf_preflight.main([str(tmp_path)]) == 1
+
+
+def test_preflight_without_weights_reports_what_it_would_need(tmp_path):
+    import json
+    _, hf_cfg = _case("moe")
+    (tmp_path / "config.json").write_text(json.dumps(hf_cfg.to_dict()))
+    rep = hf_preflight.preflight(str(tmp_path))
+    assert not rep["ok"] and "no readable weights" in rep["error"] and rep["expected_tensors"] > 0 and rep["registered_model"] == "qwen3_moe"

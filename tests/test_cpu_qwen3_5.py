@@ -134,3 +134,30 @@ def test_sequence_parallel_matches_one_rank():
     got = run_ranks(2, base_flat(data_parallel_shard_size=1, context_parallel_kv_allgather_size=2, **base), arch=arch)
     assert max(abs(a - b) for a, b in zip(ref["loss"], got["loss"])) < 5e-5, (ref, got)
     assert max(abs(a - b) for a, b in zip(ref["grad_norm"], got["grad_norm"])) < 5e-4, (ref, got)
+
+
+def test_a_folder_written_by_save_pretrained_loads_and_gives_the_same_logits(tmp_path):
+    """Files as transformers writes them (text decoder under `model.language_model.`, one tensor per expert and
+    projection): the preflight accepts the folder, a run names it as model and initial checkpoint, and the loaded model
+    reproduces the Hugging Face model's logits."""
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.components.checkpointer import hf_preflight
+    theirs = _theirs(_ours())
+    folder = str(tmp_path / "hf")
+    theirs.save_pretrained(folder, safe_serialization=True)
+    rep = hf_preflight.preflight(folder)
+    assert rep["ok"] and rep["registered_model"] == "qwen3_5_moe" and rep["expected_tensors"] == rep["stored_tensors"], rep
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(model_name_or_path=folder, dump_folder=str(tmp_path / "run"), enable=True, initial_load_path=folder,
+                             initial_load_in_hf=True))
+    cfg.model.arch_overrides = dict(linear_chunk_size=8)
+    tr = Trainer(cfg)
+    assert tr.checkpointer.load()
+    S = 29
+    tok = torch.randint(0, 96, (S,))
+    with torch.no_grad():
+        ctx = tr.model.build_context(torch.arange(S), AttnMeta.build(torch.tensor([0, S], dtype=torch.int32), causal=True))
+        got = tr.model(tok, ctx)
+        want = theirs(input_ids=tok[None]).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()

@@ -38,6 +38,14 @@ def read_hf_weight_map(path: str) -> dict[str, str]:
     raise ConfigError(f"{path} holds neither model.safetensors.index.json nor model.safetensors")
 
 
+def resolve_hf_name(fmt, name: str, stored) -> str | None:
+    """The key of `stored` (a weight map or any container of names) that holds the tensor `name`: itself, else the first
+    of the state format's aliases that is there."""
+    if name in stored:
+        return name
+    return next((a for a in fmt.hf_aliases(name) if a in stored), None)
+
+
 def _param_index(trainer):
     if hasattr(trainer.asm.fsdp, "sync_optimizer"):
         trainer.asm.fsdp.sync_optimizer()
@@ -68,9 +76,10 @@ def load_hf_checkpoint(trainer, path: str) -> None:
     handles: dict[str, object] = {}
 
     def tensor(name):
-        fn = wmap.get(name)
-        if fn is None:
+        stored = resolve_hf_name(fmt, name, wmap)
+        if stored is None:
             raise ConfigError(f"HF checkpoint {path} lacks tensor {name}")
+        fn, name = wmap[stored], stored
         if fn not in handles:
             handles[fn] = safe_open(os.path.join(path, fn), "pt")
         return handles[fn].get_tensor(name)
@@ -80,7 +89,8 @@ def load_hf_checkpoint(trainer, path: str) -> None:
         for fqn, tag, glo, ghi, u, slo in iter_pieces(trainer.asm.fsdp):
             p, s = pidx[fqn]
             full_shape = _full_shape(p, s)
-            pieces = fmt.hf_pieces(fqn, full_shape)
+            variants = fmt.hf_piece_variants(fqn, full_shape)
+            pieces = next((v for v in variants if all(resolve_hf_name(fmt, pc.name, wmap) is not None for pc in v)), variants[0])
             if tag:
                 # a row-parallel weight (cut on dimension 1): this rank's flat range maps to scattered positions of the
                 # full tensor, which is stored whole under one HF name

@@ -60,12 +60,14 @@ def build_registered_model(model_config, dtype=None, device=None):
     if key not in _MODELS and os.path.isdir(key):
         with open(os.path.join(key, "config.json")) as f:
             hf = json.load(f)
+        from .state import registered_for_hf_model_type
         mt = hf.get("model_type", "")
-        key = {"qwen3": "qwen3_moe", "qwen3_moe": "qwen3_moe"}.get(mt)
+        key, fmt = registered_for_hf_model_type(mt)
         if key is None:
             raise ConfigError(f"Hugging Face model_type {mt!r} has no registered model")
-        overrides = {k: v for k, v in hf.items() if not isinstance(v, (dict,))}
-        overrides["num_experts"] = hf.get("num_experts", 0) or 0
+        overrides = fmt.arch_from_hf(hf)
+        for k in ("dtype", "device", "model_config"):          # config.json keys that are not architecture (`dtype` is in every
+            overrides.pop(k, None)                              # file transformers writes) must not collide with the builder's own
     spec = get_model_spec(key)
     model = spec.builder(model_config, dtype=dtype, device=device, **overrides)
     model.state_format = spec.state_format           # read by the HF and reference-layout converters

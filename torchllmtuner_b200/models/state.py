@@ -56,9 +56,36 @@ class ModelStateFormat:
     def hf_config(self, arch) -> dict:
         return dict(vars(arch))
 
+    # `model_name_or_path=<folder>`: which registered model a config.json's `model_type` builds, and the architecture
+    # fields it carries (the inverse of `hf_config`; fields a builder does not know are ignored by it)
+    hf_model_types: dict = {}
+
+    def arch_from_hf(self, hf: dict) -> dict:
+        out = {k: v for k, v in hf.items() if not isinstance(v, dict)}
+        rope = hf.get("rope_parameters")               # transformers 5 nests what used to be the top-level `rope_theta`
+        if isinstance(rope, dict) and "rope_theta" in rope:
+            out.setdefault("rope_theta", rope["rope_theta"])
+        return out
+
+    def hf_aliases(self, name: str) -> list[str]:
+        """Other names under which published files may store the tensor `name` (tried in order when `name` is absent)."""
+        return []
+
+    def hf_piece_variants(self, fqn: str, shape) -> list[list[RefPiece]]:
+        """Layouts in which published files may hold the native tensor `fqn`; the first is what the export writes. The
+        importer takes the first one whose tensors are all there."""
+        return [self.hf_pieces(fqn, shape)]
+
 
 class Qwen3StateFormat(ModelStateFormat):
     name = "qwen3"
+    hf_model_types = {"qwen3": "qwen3_moe", "qwen3_moe": "qwen3_moe"}
+
+    def arch_from_hf(self, hf: dict) -> dict:
+        out = ModelStateFormat.arch_from_hf(self, hf)
+        # a dense config.json has neither key; published files say `num_experts`, transformers 5 writes `num_local_experts`
+        out["num_experts"] = hf.get("num_experts", hf.get("num_local_experts", 0)) or 0
+        return out
     _EXP = re.compile(r"^(model\.layers\.\d+\.mlp)\.routed\.experts\.(w1_EFD|w3_EFD|w2_EDF)$")
     _ROUTER = re.compile(r"^(model\.layers\.\d+\.mlp)\.router\.gate\.weight$")
     _PROJ = {"w1_EFD": "gate_proj", "w3_EFD": "up_proj", "w2_EDF": "down_proj"}
@@ -109,6 +136,20 @@ class DeepseekV4StateFormat(Qwen3StateFormat):
     (reference: llmtuner/models/deepseek/deepseek_v4/modeling.py:219-247, indexer.py:18-60). Experts: one tensor per
     expert and projection in HF files, packed `gate_up_proj` / `down_proj` in the reference's own checkpoints."""
     name = "deepseek_v4"
+    hf_model_types = {"deepseek_v4": "deepseek_v4"}
+
+    def arch_from_hf(self, hf: dict) -> dict:
+        out = ModelStateFormat.arch_from_hf(self, hf)
+        out["num_experts"] = hf.get("n_routed_experts", hf.get("num_experts", 0))
+        if "moe_intermediate_size" not in hf and "intermediate_size" in hf:      # published files call the expert width this
+            out["moe_intermediate_size"] = hf["intermediate_size"]
+        rope = hf.get("rope_parameters") or {}
+        if "main" in rope:
+            out["rope_theta"] = rope["main"].get("rope_theta", out.get("rope_theta"))
+        if "compress" in rope:
+            out["compress_rope_theta"] = rope["compress"].get("rope_theta", out.get("compress_rope_theta"))
+        return {k: v for k, v in out.items() if v is not None}
+
     _RENAMES = ((re.compile(r"^(model\.layers\.\d+\.mlp)\.router\.gate\.weight$"), r"\1.gate.weight"),
                 (re.compile(r"^(model\.layers\.\d+\.self_attn\.compressor\.indexer)\.weights_proj\.weight$"), r"\1.scorer.weights_proj.weight"))
     BUFFER_RENAMES = {"mlp.router.tid2eid": "mlp.gate.tid2eid", "mlp.expert_bias_E": "mlp.gate.e_score_correction_bias"}
@@ -155,6 +196,23 @@ class Qwen35StateFormat(ModelStateFormat):
     `mlp.shared_expert`, experts packed as `mlp.experts.gate_up_proj` (E, 2F, D: gate rows then up rows of each expert) and
     `mlp.experts.down_proj` (reference: llmtuner/models/qwen/qwen3_5_moe/model.py:217-275, gated_delta.py:34-72)."""
     name = "qwen3_5"
+    hf_model_types = {"qwen3_5_text": "qwen3_5", "qwen3_5_moe_text": "qwen3_5_moe", "qwen3_5": "qwen3_5", "qwen3_5_moe": "qwen3_5_moe"}
+
+    def arch_from_hf(self, hf: dict) -> dict:
+        hf = hf.get("text_config") or hf                      # the vision-language config nests the decoder's
+        out = ModelStateFormat.arch_from_hf(self, hf)
+        rope = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+        for k in ("rope_theta", "partial_rotary_factor", "mrope_section"):
+            if k in rope:
+                out[k] = rope[k]
+        out["num_experts"] = hf.get("num_experts", hf.get("num_local_experts", 0)) or 0
+        out.pop("model_type", None)                           # the registered builder names it
+        return out
+
+    def hf_aliases(self, name: str) -> list[str]:
+        # transformers writes the text decoder under the vision-language model's tree, also for text-only checkpoints
+        return ["model.language_model." + name[len("model."):]] if name.startswith("model.") else []
+
     _LINEAR = re.compile(r"^(model\.layers\.\d+)\.self_attn\.((?:in_proj_(?:qkv|z|b|a)|conv1d|norm|out_proj)\.weight|dt_bias|A_log)$")
     _EXP = re.compile(r"^(model\.layers\.\d+\.mlp)\.routed\.experts\.(w1_EFD|w3_EFD|w2_EDF)$")
     _ROUTER = re.compile(r"^(model\.layers\.\d+\.mlp)\.router\.gate\.weight$")
@@ -179,6 +237,18 @@ class Qwen35StateFormat(ModelStateFormat):
         return [RefPiece(fqn, tuple(shape), 0, 0, n)]
 
     to_reference = hf_pieces
+
+    _PROJ = {"w1_EFD": "gate_proj", "w3_EFD": "up_proj", "w2_EDF": "down_proj"}
+
+    def hf_piece_variants(self, fqn, shape):
+        """Packed experts are what the module tree holds; files written by `save_pretrained` carry one tensor per expert
+        and projection (`experts.<e>.gate_proj.weight`), as Qwen3-MoE files do."""
+        m = self._EXP.match(fqn)
+        if not m:
+            return [self.hf_pieces(fqn, shape)]
+        E, a, b = shape
+        each = [RefPiece(f"{m.group(1)}.experts.{e}.{self._PROJ[m.group(2)]}.weight", (a, b), 0, e * a * b, a * b) for e in range(E)]
+        return [self.hf_pieces(fqn, shape), each]
 
     def to_hf(self, fqn, shape):
         if self._EXP.match(fqn) and not fqn.endswith("w2_EDF"):
@@ -207,6 +277,22 @@ class KimiStateFormat(ModelStateFormat):
     (gate), `w3` (up), `w2` (down); the reference's own module tree is the same, so its distributed checkpoints use these
     names too (reference: llmtuner/models/kimi/kimi_k3/model.py:102-110, mlp.py:47-61, checkpoint.py:27-342)."""
     name = "kimi"
+    hf_model_types = {"kimi_linear": "kimi_linear", "kimi_k3": "kimi_k3"}
+
+    def arch_from_hf(self, hf: dict) -> dict:
+        hf = hf.get("text_config") or hf
+        out = ModelStateFormat.arch_from_hf(self, hf)
+        if "num_experts_per_token" in hf:
+            out["num_experts_per_tok"] = hf["num_experts_per_token"]
+        lin = hf.get("linear_attn_config") or {}
+        for theirs, ours in (("kda_layers", "kda_layers"), ("num_heads", "linear_heads"), ("head_dim", "linear_head_dim"),
+                             ("short_conv_kernel_size", "short_conv_kernel_size"), ("use_full_rank_gate", "use_full_rank_gate"),
+                             ("gate_lower_bound", "gate_lower_bound")):
+            if theirs in lin:
+                out[ours] = lin[theirs]
+        out.pop("model_type", None)
+        return out
+
     _EXP = re.compile(r"^(model\.layers\.\d+)\.mlp\.routed\.experts\.(w1_EFD|w3_EFD|w2_EDF)$")
     _SPARSE = re.compile(r"^(model\.layers\.\d+)\.mlp\.(router\.gate\.weight|shared_experts\..+|routed_expert_(?:down_proj|up_proj|norm)\.weight)$")
     _PROJ = {"w1_EFD": "w1", "w3_EFD": "w3", "w2_EDF": "w2"}
@@ -255,6 +341,15 @@ class KimiStateFormat(ModelStateFormat):
 
 _FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat(), "kimi": KimiStateFormat(),
             "qwen3_5": Qwen35StateFormat()}
+
+
+def registered_for_hf_model_type(model_type: str):
+    """(registry key, state format) that builds a config.json of this `model_type`, or (None, None)."""
+    for fmt in _FORMATS.values():
+        key = fmt.hf_model_types.get(model_type)
+        if key is not None:
+            return key, fmt
+    return None, None
 
 
 def get_state_format(name: str) -> ModelStateFormat:
