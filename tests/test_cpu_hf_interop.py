@@ -65,3 +65,32 @@ def test_preflight_without_weights_reports_what_it_would_need(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(hf_cfg.to_dict()))
     rep = hf_preflight.preflight(str(tmp_path))
     assert not rep["ok"] and "no readable weights" in rep["error"] and rep["expected_tensors"] > 0 and rep["registered_model"] == "qwen3_moe"
+
+
+@pytest.mark.parametrize("name,arch", [("qwen3", dict(head_dim=16)),
+                                       ("qwen3_moe", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, head_dim=16)),
+                                       ("qwen3_5_moe", dict(head_dim=16, linear_chunk_size=8))])
+def test_the_library_loads_this_frameworks_export(name, arch, tmp_path):
+    """The other direction: `save_hf_checkpoint` output goes through `from_pretrained` and gives this model's logits."""
+    import transformers as T
+    from torchllmtuner_b200.components.checkpointer.hf import save_hf_checkpoint
+    if name == "qwen3_5_moe":
+        cls = pytest.importorskip("transformers.models.qwen3_5_moe.modeling_qwen3_5_moe").Qwen3_5MoeForCausalLM
+    else:
+        cls = T.Qwen3ForCausalLM if name == "qwen3" else T.Qwen3MoeForCausalLM
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(model_name_or_path=name, num_hidden_layers=4, dump_folder=str(tmp_path / "run")))
+    cfg.model.arch_overrides = arch
+    tr = Trainer(cfg)
+    tr.train_step()
+    out = str(tmp_path / "hf")
+    save_hf_checkpoint(tr, out, "float32")
+    theirs = cls.from_pretrained(out, attn_implementation="eager", dtype=torch.float32).eval()
+    S = 19
+    tok = torch.randint(0, 100, (S,))
+    with torch.no_grad():
+        ctx = tr.model.build_context(torch.arange(S), AttnMeta.build(torch.tensor([0, S], dtype=torch.int32), causal=True))
+        got = tr.model(tok, ctx)
+        want = theirs(input_ids=tok[None], use_cache=False).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=1e-5), (got - want).abs().max()
