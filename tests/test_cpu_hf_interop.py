@@ -69,6 +69,7 @@ def test_preflight_without_weights_reports_what_it_would_need(tmp_path):
 
 @pytest.mark.parametrize("name,arch", [("qwen3", dict(head_dim=16)),
                                        ("qwen3_moe", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, head_dim=16)),
+                                       ("qwen3_5", dict(head_dim=16, linear_chunk_size=8)),
                                        ("qwen3_5_moe", dict(head_dim=16, linear_chunk_size=8))])
 def test_the_library_loads_this_frameworks_export(name, arch, tmp_path):
     """The other direction: `save_hf_checkpoint` output goes through `from_pretrained` and gives this model's logits."""
@@ -76,6 +77,8 @@ def test_the_library_loads_this_frameworks_export(name, arch, tmp_path):
     from torchllmtuner_b200.components.checkpointer.hf import save_hf_checkpoint
     if name == "qwen3_5_moe":
         cls = pytest.importorskip("transformers.models.qwen3_5_moe.modeling_qwen3_5_moe").Qwen3_5MoeForCausalLM
+    elif name == "qwen3_5":
+        cls = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5").Qwen3_5ForCausalLM
     else:
         cls = T.Qwen3ForCausalLM if name == "qwen3" else T.Qwen3MoeForCausalLM
     cfg = LLMTunerConfig()
@@ -94,3 +97,8 @@ def test_the_library_loads_this_frameworks_export(name, arch, tmp_path):
         want = theirs(input_ids=tok[None], use_cache=False).logits[0]
     tr.close()
     assert torch.allclose(got.float(), want, atol=1e-5), (got - want).abs().max()
+    # and back: what the library writes from that model passes the preflight
+    back = str(tmp_path / "back")
+    theirs.save_pretrained(back, safe_serialization=True)
+    rep = hf_preflight.preflight(back)
+    assert rep["ok"] and rep["expected_tensors"] == rep["stored_tensors"], rep
