@@ -102,3 +102,18 @@ def test_the_library_loads_this_frameworks_export(name, arch, tmp_path):
     theirs.save_pretrained(back, safe_serialization=True)
     rep = hf_preflight.preflight(back)
     assert rep["ok"] and rep["expected_tensors"] == rep["stored_tensors"], rep
+
+
+@pytest.mark.parametrize("change,word", [(dict(attention_bias=True), "attention_bias"), (dict(hidden_act="gelu"), "hidden_act"),
+                                         (dict(rope_parameters={"rope_type": "yarn", "rope_theta": 1e4, "factor": 4.0}), "yarn")])
+def test_a_config_that_asks_for_something_unbuilt_is_refused(change, word, tmp_path):
+    import json
+    from torchllmtuner_b200.config.model_config import ModelConfig
+    from torchllmtuner_b200.errors import UnsupportedCombinationError
+    from torchllmtuner_b200.models.registry import build_registered_model
+    hf = dict(model_type="qwen3", **DENSE)
+    hf.update(change)
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    with pytest.raises(UnsupportedCombinationError, match=word):
+        with torch.device("meta"):
+            build_registered_model(ModelConfig(model_name_or_path=str(tmp_path)))

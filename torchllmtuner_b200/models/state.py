@@ -28,6 +28,20 @@ class RefPiece:
     n: int
 
 
+def refuse_unsupported_hf_settings(hf: dict, accepted: dict) -> None:
+    """A config.json may switch on something this framework's model of the family does not have (a bias on the attention
+    projections, a sliding window, a scaled rotary embedding). Building the model anyway would load the weights it knows
+    and silently compute something else, so such a folder is refused, naming the setting."""
+    from ..errors import UnsupportedCombinationError
+    for key, ok in accepted.items():
+        if key in hf and hf[key] is not None and hf[key] not in ok:
+            raise UnsupportedCombinationError(f"config.json sets {key}={hf[key]!r}; this framework's model supports {key} in {list(ok)}")
+    rope = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+    kind = rope.get("rope_type", rope.get("type", "default")) if isinstance(rope, dict) else "default"
+    if kind not in ("default", None):
+        raise UnsupportedCombinationError(f"config.json asks for a {kind!r} rotary embedding; only the default one is built")
+
+
 class ModelStateFormat:
     name = "native"
 
@@ -85,6 +99,8 @@ class Qwen3StateFormat(ModelStateFormat):
         out = ModelStateFormat.arch_from_hf(self, hf)
         # a dense config.json has neither key; published files say `num_experts`, transformers 5 writes `num_local_experts`
         out["num_experts"] = hf.get("num_experts", hf.get("num_local_experts", 0)) or 0
+        refuse_unsupported_hf_settings(hf, {"attention_bias": (False,), "use_sliding_window": (False,), "hidden_act": ("silu",),
+                                            "attention_dropout": (0, 0.0)})
         return out
     _EXP = re.compile(r"^(model\.layers\.\d+\.mlp)\.routed\.experts\.(w1_EFD|w3_EFD|w2_EDF)$")
     _ROUTER = re.compile(r"^(model\.layers\.\d+\.mlp)\.router\.gate\.weight$")
