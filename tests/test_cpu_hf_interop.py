@@ -117,3 +117,29 @@ def test_a_config_that_asks_for_something_unbuilt_is_refused(change, word, tmp_p
     with pytest.raises(UnsupportedCombinationError, match=word):
         with torch.device("meta"):
             build_registered_model(ModelConfig(model_name_or_path=str(tmp_path)))
+
+
+def test_published_style_config_files_build_the_registered_architectures(tmp_path):
+    """config.json as the Qwen3-8B and Qwen3-30B-A3B repositories carry it (top-level `rope_theta`, `num_experts`, null
+    `rope_scaling`): the same parameter names and shapes as the registry's own entries."""
+    import json
+    from torchllmtuner_b200.config.model_config import ModelConfig
+    from torchllmtuner_b200.models.registry import build_registered_model
+    common = {"attention_bias": False, "attention_dropout": 0.0, "head_dim": 128, "hidden_act": "silu", "max_position_embeddings": 40960,
+              "rms_norm_eps": 1e-06, "rope_scaling": None, "rope_theta": 1000000, "sliding_window": None, "tie_word_embeddings": False,
+              "torch_dtype": "bfloat16", "use_cache": True, "use_sliding_window": False, "vocab_size": 151936}
+    dense = dict(common, architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, intermediate_size=12288,
+                 num_attention_heads=32, num_hidden_layers=36, num_key_value_heads=8, max_window_layers=36)
+    moe = dict(common, architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", hidden_size=2048, intermediate_size=6144,
+               moe_intermediate_size=768, norm_topk_prob=True, num_attention_heads=32, num_experts=128, num_experts_per_tok=8,
+               num_hidden_layers=48, num_key_value_heads=4, decoder_sparse_step=1, mlp_only_layers=[], output_router_logits=False,
+               router_aux_loss_coef=0.001)
+    for hf, preset, params in ((dense, "qwen3_8b", 8190735360), (moe, "qwen3_30b_a3b", 30532122624)):
+        d = tmp_path / preset
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(hf))
+        with torch.device("meta"):
+            a = build_registered_model(ModelConfig(model_name_or_path=str(d)))
+            b = build_registered_model(ModelConfig(model_name_or_path=preset))
+        assert sum(p.numel() for p in a.parameters()) == params and a.config.rope_theta == 1000000
+        assert {n: tuple(p.shape) for n, p in a.named_parameters()} == {n: tuple(p.shape) for n, p in b.named_parameters()}
