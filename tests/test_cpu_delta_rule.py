@@ -155,3 +155,27 @@ def test_scan_blocks_carry_the_state(monkeypatch):
     assert torch.allclose(got, want, atol=1e-6)
     for a, b in zip(torch.autograd.grad(got.square().sum(), x), gw):
         assert torch.allclose(a, b, atol=1e-5)
+
+
+@pytest.mark.parametrize("channels", [1, 8])
+def test_against_the_flash_linear_attention_reference_recurrences(channels):
+    """An independent statement of both recurrences: the plain-PyTorch references of the `fla` package (the library the
+    reference framework calls for these mixers). One decay per head is its gated delta rule, one per key channel its KDA.
+    The long sequence takes the scan form, the short one the loop form; an initial state and the final state agree too."""
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        naive_kda = pytest.importorskip("fla.ops.kda.naive").naive_recurrent_kda
+        naive_gdn = pytest.importorskip("fla.ops.gated_delta_rule.naive").naive_recurrent_gated_delta_rule
+    for T, chunk in ((150, 8), (40, 16)):
+        q, k, v, beta, ld = (t.detach() for t in _inputs(T, 3, 8, 6, channels, seed=T))
+        s0 = torch.randn(3, 8, 6) * 0.3
+        got, s_got = chunked_delta_rule(q, k, v, beta, ld, chunk, s0, True)
+        if channels == 1:
+            want, s_want = naive_gdn(q[None], k[None], v[None], beta[None], ld[None, ..., 0], scale=1.0, initial_state=s0[None],
+                                     output_final_state=True)
+        else:
+            want, s_want = naive_kda(q[None], k[None], v[None], ld[None], beta[None], scale=1.0, initial_state=s0[None],
+                                     output_final_state=True)
+        assert torch.allclose(got, want[0].float(), atol=2e-5), (got - want[0]).abs().max()
+        assert torch.allclose(s_got, s_want[0].float(), atol=2e-5)
