@@ -260,3 +260,25 @@ def test_hf_export_uses_the_published_names_and_imports_back(tmp_path):
     for a, u in zip(before, tr.asm.fsdp.units):
         assert torch.equal(a[:u.numel], u.master[:u.numel])
     tr.close()
+
+
+@pytest.mark.parametrize("lower", [None, -5.0, -2.0])
+def test_decay_gate_forms_match_the_flash_linear_attention_references(lower):
+    """log decay = -exp(A_log) * softplus(f(x) + dt_bias), or lower_bound * sigmoid(exp(A_log) * (f(x) + dt_bias)): the
+    module's two forms against the plain-PyTorch gate references of the `fla` package."""
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        gate = pytest.importorskip("fla.ops.kda.gate")
+    cfg = _cfg(gate_lower_bound=lower)
+    torch.manual_seed(1)
+    m = km.KimiDeltaAttention(cfg)
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.5)
+    x = torch.randn(13, cfg.hidden_size)
+    raw = m.f_b_proj(m.f_a_proj(x)).float().view(1, 13, m.H, m.d)
+    if lower is None:
+        want = gate.naive_kda_gate(raw, m.A_log, m.dt_bias)
+    else:
+        want = gate.naive_kda_lowerbound_gate(raw, m.A_log, m.dt_bias, lower_bound=lower)
+    assert torch.allclose(m.log_decay(x), want[0], atol=1e-6)
