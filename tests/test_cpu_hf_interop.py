@@ -143,3 +143,28 @@ def test_published_style_config_files_build_the_registered_architectures(tmp_pat
             b = build_registered_model(ModelConfig(model_name_or_path=preset))
         assert sum(p.numel() for p in a.parameters()) == params and a.config.rope_theta == 1000000
         assert {n: tuple(p.shape) for n, p in a.named_parameters()} == {n: tuple(p.shape) for n, p in b.named_parameters()}
+
+
+def test_grouped_biased_sigmoid_routing_matches_the_librarys_deepseek_v3_router():
+    """Group-limited top-k with the aux-loss-free bias (sigmoid scores, groups ranked by their two best biased scores,
+    weights from the unbiased scores, renormalised and scaled): same experts and weights as `DeepseekV3MoE`."""
+    import transformers as T
+    from transformers.models.deepseek_v3 import modeling_deepseek_v3 as m
+    from torchllmtuner_b200.models.moe.routing import TokenChoiceTopKRouter
+    torch.manual_seed(0)
+    cfg = T.DeepseekV3Config(hidden_size=32, n_routed_experts=16, num_experts_per_tok=4, n_group=4, topk_group=2, norm_topk_prob=True,
+                             routed_scaling_factor=2.5, moe_intermediate_size=8, n_shared_experts=1, num_hidden_layers=1,
+                             intermediate_size=16, vocab_size=32, num_attention_heads=2)
+    moe = m.DeepseekV3MoE(cfg)
+    with torch.no_grad():
+        torch.nn.init.normal_(moe.gate.weight, std=1.0)
+        moe.gate.e_score_correction_bias.copy_(torch.randn(16) * 0.2)
+        x = torch.randn(40, 32)
+        idx_hf, w_hf = moe.route_tokens_to_experts(moe.gate(x))
+        ours = TokenChoiceTopKRouter(32, 16, 4, score_fn="sigmoid", norm_topk_prob=True, route_scale=2.5, num_groups=4, topk_groups=2)
+        ours.gate.weight.copy_(moe.gate.weight)
+        w, idx, counts, _ = ours(x, expert_bias=moe.gate.e_score_correction_bias)
+    a = {(t, int(e)): float(v) for t in range(40) for e, v in zip(idx_hf[t], w_hf[t])}
+    b = {(t, int(e)): float(v) for t in range(40) for e, v in zip(idx[t], w[t])}
+    assert a.keys() == b.keys() and max(abs(a[k] - b[k]) for k in a) < 1e-6
+    assert float(counts.sum()) == 40 * 4
