@@ -168,3 +168,37 @@ def test_grouped_biased_sigmoid_routing_matches_the_librarys_deepseek_v3_router(
     b = {(t, int(e)): float(v) for t in range(40) for e, v in zip(idx[t], w[t])}
     assert a.keys() == b.keys() and max(abs(a[k] - b[k]) for k in a) < 1e-6
     assert float(counts.sum()) == 40 * 4
+
+
+def test_latent_attention_matches_the_librarys_multi_head_latent_attention():
+    """Low-rank queries, one compressed key/value row per token with a shared positional part, per-head expansion: Kimi's
+    latent attention against `DeepseekV3Attention` with the rotation switched off (cos = 1, sin = 0; this family carries
+    positions in its delta-rule layers)."""
+    import transformers as T
+    from transformers.models.deepseek_v3 import modeling_deepseek_v3 as m
+    from torchllmtuner_b200.models import kimi_k3 as km
+    torch.manual_seed(0)
+    D, H, dn, dr, dv, ql, kvl, S = 64, 4, 16, 8, 12, 24, 20, 21
+    cfg = T.DeepseekV3Config(hidden_size=D, num_attention_heads=H, num_key_value_heads=H, qk_nope_head_dim=dn, qk_rope_head_dim=dr,
+                             v_head_dim=dv, q_lora_rank=ql, kv_lora_rank=kvl, num_hidden_layers=1, vocab_size=32, intermediate_size=32,
+                             n_routed_experts=4, moe_intermediate_size=8, attention_bias=False, rms_norm_eps=1e-6)
+    cfg._attn_implementation = "eager"
+    theirs = m.DeepseekV3Attention(cfg, layer_idx=0).eval()
+    kc = km.KimiConfig(vocab_size=32, hidden_size=D, intermediate_size=32, num_hidden_layers=4, num_attention_heads=H, num_key_value_heads=H,
+                       head_dim=16, q_lora_rank=ql, kv_lora_rank=kvl, qk_nope_head_dim=dn, qk_rope_head_dim=dr, v_head_dim=dv,
+                       mla_use_output_gate=False, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=8, linear_heads=2,
+                       linear_head_dim=8)
+    ours = km.KimiLatentAttention(kc).eval()
+    with torch.no_grad():
+        for p in theirs.parameters():
+            torch.nn.init.normal_(p, std=0.3) if p.dim() > 1 else torch.nn.init.normal_(p, mean=1.0, std=0.2)
+        for n in ("q_a_proj", "q_b_proj", "kv_a_proj_with_mqa", "kv_b_proj", "o_proj"):
+            getattr(ours, n).weight.copy_(getattr(theirs, n).weight)
+        ours.q_a_layernorm.weight.copy_(theirs.q_a_layernorm.weight)
+        ours.kv_a_layernorm.weight.copy_(theirs.kv_a_layernorm.weight)
+        x = torch.randn(S, D)
+        mask = torch.full((S, S), float("-inf")).triu(1)[None, None]
+        want = theirs(x[None], position_embeddings=(torch.ones(1, S, dr), torch.zeros(1, S, dr)), attention_mask=mask)[0][0]
+        ctx = km.KimiContext(None, None, AttnMeta.build(torch.tensor([0, S], dtype=torch.int32)), None, torch.arange(S))
+        got = ours(x, ctx)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-5), (got - want).abs().max()
