@@ -202,3 +202,105 @@ def test_latent_attention_matches_the_librarys_multi_head_latent_attention():
         ctx = km.KimiContext(None, None, AttnMeta.build(torch.tensor([0, S], dtype=torch.int32)), None, torch.arange(S))
         got = ours(x, ctx)
     assert torch.allclose(got, want, atol=1e-4, rtol=1e-5), (got - want).abs().max()
+
+
+VIT = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, num_position_embeddings=64, patch_size=4, temporal_patch_size=2,
+           in_channels=3, spatial_merge_size=2)
+
+
+def test_vision_tower_matches_the_librarys_qwen3_5_vision_model():
+    """Same parameter names and shapes (a plain `load_state_dict`), same output rows for images and a two-frame video in
+    the processors' merge-block order; patches given row-major (this framework's data pipeline) land on the same rows."""
+    hf = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5")
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5VisionConfig
+    from torchllmtuner_b200.models.qwen_vit import QwenViTConfig, QwenViTTower, merge_block_order
+    torch.manual_seed(0)
+    hcfg = Qwen3_5VisionConfig(**VIT, out_hidden_size=48)
+    hcfg._attn_implementation = "eager"
+    theirs = hf.Qwen3_5VisionModel(hcfg).eval()
+    with torch.no_grad():
+        for p in theirs.parameters():
+            torch.nn.init.normal_(p, std=0.2)
+    ours = QwenViTTower(QwenViTConfig(**VIT, out_hidden_size=48, patch_order="merge_blocks")).eval()
+    ours.load_state_dict(theirs.state_dict())
+    grids = [(1, 4, 6), (2, 2, 4), (1, 8, 8)]
+    N = sum(t * h * w for t, h, w in grids)
+    x = torch.randn(N, 3 * 2 * 4 * 4)
+    with torch.no_grad():
+        want = theirs(x, grid_thw=torch.tensor(grids)).pooler_output
+        got = ours(x, grids)
+        assert got.shape == want.shape == (N // 4, 48) and torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+        ours.config.patch_order = "row_major"
+        inv = torch.empty(N, dtype=torch.long)
+        inv[merge_block_order(grids, 2)] = torch.arange(N)
+        assert torch.equal(ours(x[inv], grids), got)
+        # an image row without the temporal axis is the frame repeated over it
+        one = torch.randn(16, 3 * 4 * 4)
+        both = one.view(16, 3, 1, 16).expand(16, 3, 2, 16).reshape(16, -1)
+        assert torch.allclose(ours(one, [(1, 4, 4)]), ours(both, [(1, 4, 4)]), atol=1e-6)
+
+
+def test_vision_language_folder_in_the_published_layout_loads(tmp_path):
+    """Tensors named as the library's vision-language model holds them (`model.language_model.*`, `model.visual.*`,
+    `lm_head.weight`): the `_vl` model with the published tower imports them, and its tower and text decoder compute what
+    the library's do."""
+    hf = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5")
+    from safetensors.torch import save_file
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5Config
+    from torchllmtuner_b200.components.checkpointer.hf import load_hf_checkpoint
+    torch.manual_seed(0)
+    txt = dict(vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=32, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=24,
+               linear_conv_kernel_dim=4, rms_norm_eps=1e-6,
+               rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5, "mrope_section": [4, 2, 2],
+                                "mrope_interleaved": True})
+    cfg = Qwen3_5Config(text_config=txt, vision_config=dict(VIT, out_hidden_size=64), image_token_id=90, video_token_id=91,
+                        vision_start_token_id=92, vision_end_token_id=93, tie_word_embeddings=False)
+    cfg._attn_implementation = "eager"
+    cfg.text_config._attn_implementation = "eager"
+    cfg.vision_config._attn_implementation = "eager"
+    theirs = hf.Qwen3_5ForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n, p in theirs.named_parameters():
+            if "visual" in n:
+                torch.nn.init.normal_(p, std=0.2)
+    folder = tmp_path / "hf"
+    folder.mkdir()
+    save_file({k: v.contiguous() for k, v in theirs.state_dict().items()}, str(folder / "model.safetensors"))
+    c = LLMTunerConfig()
+    c.apply_flat(base_flat(model_name_or_path="qwen3_5_vl", vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                           num_attention_heads=4, num_key_value_heads=2, dump_folder=str(tmp_path / "run")))
+    c.model.arch_overrides = dict(head_dim=32, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+                                  linear_value_head_dim=24, linear_conv_kernel_dim=4, rope_theta=10000.0, partial_rotary_factor=0.5,
+                                  mrope_section=[4, 2, 2], linear_chunk_size=8, image_token_id=90, vision_tower="qwen3_5",
+                                  vision=dict(VIT, patch_order="merge_blocks"))
+    tr = Trainer(c)
+    assert tr.model.state_format == "qwen3_5_vl"
+    load_hf_checkpoint(tr, str(folder))
+    grids = [(1, 4, 4), (1, 2, 6)]
+    patches = torch.randn(sum(t * h * w for t, h, w in grids), 3 * 2 * 4 * 4)
+    S = 17
+    tok = torch.randint(0, 80, (S,))
+    with torch.no_grad():
+        rows = tr.model.visual(patches, grids)
+        want_rows = theirs.model.visual(patches, grid_thw=torch.tensor(grids)).pooler_output
+        assert torch.allclose(rows.float(), want_rows, atol=1e-5), (rows - want_rows).abs().max()
+        ctx = tr.model.build_context(torch.arange(S), AttnMeta.build(torch.tensor([0, S], dtype=torch.int32), causal=True))
+        got = tr.model(tok, ctx)
+        want = theirs(input_ids=tok[None], use_cache=False).logits[0]
+        assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()
+        # two images between words: placeholders, three-axis positions and the merged rows land where the library puts them
+        from torchllmtuner_b200.datasets.multimodal import build_mrope_positions, insert_vision_placeholders
+        words = torch.randint(0, 80, (20,)).tolist()
+        ids = insert_vision_placeholders(words[:5] + [92, 90, 93] + words[5:12] + [92, 90, 93] + words[12:], 90, grids)
+        pos = build_mrope_positions(ids, 90, grids)
+        ids_t = torch.tensor(ids)
+        kinds = (ids_t[None] == 90).int()
+        their_pos = theirs.model.get_rope_index(ids_t[None], mm_token_type_ids=kinds, image_grid_thw=torch.tensor(grids))[0]
+        assert torch.equal(their_pos[:, 0], pos)
+        ctx = tr.model.build_context(pos, AttnMeta.build(torch.tensor([0, len(ids)], dtype=torch.int32), causal=True))
+        got = tr.model(ids_t, ctx, patches=patches, grids=grids)
+        want = theirs(input_ids=ids_t[None], pixel_values=patches, image_grid_thw=torch.tensor(grids), mm_token_type_ids=kinds,
+                      use_cache=False).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()

@@ -301,16 +301,22 @@ QWEN3_5_MOE = dict(model_type="qwen3_5_moe", num_experts=8, num_experts_per_tok=
 
 def build_qwen3_5_vl(defaults: dict):
     """Text decoder + vision tower under one model: `arch_overrides` may carry `image_token_id` (default: the last token of
-    the vocabulary) and `vision` (a dict of `VisionConfig` fields; the output width always follows the text width)."""
+    the vocabulary), `vision` (a dict of the tower's config fields; the output width always follows the text width) and
+    `vision_tower`: "generic" (default, `models/vision.py`) or "qwen3_5" (the published tower, `models/qwen_vit.py`)."""
     text_builder = build_qwen3_5(defaults)
 
     def build(model_config, dtype=None, device=None, **overrides):
         from .vision import VisionConfig, VisionLanguageModel
         text = text_builder(model_config, dtype=dtype, device=device, **overrides)
         extra = dict(model_config.arch_overrides or {})
+        image_id = int(extra.get("image_token_id", text.config.vocab_size - 1))
+        if extra.get("vision_tower", "generic") == "qwen3_5":        # the published tower, weight for weight (models/qwen_vit.py)
+            from .qwen_vit import QwenViTConfig, QwenViTTower
+            vkw = dict(extra.get("vision") or {})
+            vkw["out_hidden_size"] = text.config.hidden_size
+            return VisionLanguageModel(text, QwenViTConfig(**vkw), image_id, dtype=dtype, device=device, tower=QwenViTTower)
         vkw = dict(hidden_size=128, intermediate_size=256, depth=2, num_heads=2)
         vkw.update(extra.get("vision") or {})
         vkw["out_hidden_size"] = text.config.hidden_size
-        image_id = int(extra.get("image_token_id", text.config.vocab_size - 1))
         return VisionLanguageModel(text, VisionConfig(**vkw), image_id, dtype=dtype, device=device)
     return build

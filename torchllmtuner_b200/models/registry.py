@@ -98,7 +98,7 @@ def _ensure_builtins() -> None:
     reg("kimi_k3_vl", kimi_k3.build_kimi_vl(kimi_k3.KIMI_K3_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "ac"},
         description="Kimi-K3 with the MoonViT tower: learned interpolated position table, time-pooled patch merger")
     for name, defaults in (("qwen3_5_vl", qwen3_5.QWEN3_5_DENSE), ("qwen3_5_moe_vl", qwen3_5.QWEN3_5_MOE)):
-        reg(name, qwen3_5.build_qwen3_5_vl(defaults), state_format="qwen3_5", supports={"fsdp", "ep", "ac"},
+        reg(name, qwen3_5.build_qwen3_5_vl(defaults), state_format="qwen3_5_vl", supports={"fsdp", "ep", "ac"},
             description="Qwen3.5 vision-language model: vision tower with patch merger feeding image rows into the text decoder")
     reg("kimi_linear", kimi_k3.build_kimi(kimi_k3.KIMI_LINEAR_DEFAULTS), state_format="kimi", supports={"fsdp", "ep", "cp", "ac"},
         description="Kimi-Linear decoder: KDA with short convolutions, latent attention without rotary, grouped sigmoid router")

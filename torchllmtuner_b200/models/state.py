@@ -259,12 +259,15 @@ class Qwen35StateFormat(ModelStateFormat):
     def hf_piece_variants(self, fqn, shape):
         """Packed experts are what the module tree holds; files written by `save_pretrained` carry one tensor per expert
         and projection (`experts.<e>.gate_proj.weight`), as Qwen3-MoE files do."""
+        each = self._per_expert(fqn, shape)
+        return [self.hf_pieces(fqn, shape)] + ([each] if each else [])
+
+    def _per_expert(self, fqn, shape):
         m = self._EXP.match(fqn)
         if not m:
-            return [self.hf_pieces(fqn, shape)]
+            return None
         E, a, b = shape
-        each = [RefPiece(f"{m.group(1)}.experts.{e}.{self._PROJ[m.group(2)]}.weight", (a, b), 0, e * a * b, a * b) for e in range(E)]
-        return [self.hf_pieces(fqn, shape), each]
+        return [RefPiece(f"{m.group(1)}.experts.{e}.{self._PROJ[m.group(2)]}.weight", (a, b), 0, e * a * b, a * b) for e in range(E)]
 
     def to_hf(self, fqn, shape):
         if self._EXP.match(fqn) and not fqn.endswith("w2_EDF"):
@@ -286,6 +289,48 @@ class Qwen35StateFormat(ModelStateFormat):
             cfg.update(num_experts=arch.num_experts, num_experts_per_tok=arch.num_experts_per_tok, moe_intermediate_size=arch.moe_intermediate_size,
                        shared_expert_intermediate_size=arch.shared_expert_intermediate_size, norm_topk_prob=arch.norm_topk_prob)
         return cfg
+
+
+class Qwen35VLStateFormat(Qwen35StateFormat):
+    """The vision-language model: the text decoder's tensors (`text.` here) sit under `model.language_model.` in
+    published files, the tower's (`visual.`) under `model.visual.`; `lm_head.weight` stays at the top. With the
+    `models/qwen_vit.py` tower the names and shapes below `visual.` are the published ones."""
+    name = "qwen3_5_vl"
+    hf_model_types: dict = {}        # a vision-language folder builds the text decoder unless the run names a `_vl` model
+
+    @staticmethod
+    def _place(piece: RefPiece) -> RefPiece:
+        name = piece.name
+        if name.startswith("model."):
+            name = "model.language_model." + name[len("model."):]
+        return RefPiece(name, piece.shape, piece.ref_lo, piece.native_lo, piece.n)
+
+    def hf_piece_variants(self, fqn, shape):
+        if fqn.startswith("text."):
+            inner = fqn[len("text."):]
+            variants = [Qwen35StateFormat.hf_pieces(self, inner, shape)]
+            each = self._per_expert(inner, shape)
+            return [[self._place(p) for p in v] for v in variants + ([each] if each else [])]
+        n = 1
+        for x in shape:
+            n *= x
+        if fqn.startswith("visual."):
+            return [[RefPiece("model." + fqn, tuple(shape), 0, 0, n)]]
+        return [[RefPiece(fqn, tuple(shape), 0, 0, n)]]
+
+    def hf_pieces(self, fqn, shape):
+        return self.hf_piece_variants(fqn, shape)[0]
+
+    to_reference = hf_pieces
+
+    def hf_aliases(self, name: str) -> list[str]:
+        return []
+
+    def hf_config(self, arch) -> dict:
+        text = Qwen35StateFormat.hf_config(self, arch)
+        return {"architectures": ["Qwen3_5MoeForConditionalGeneration" if arch.num_experts > 0 else "Qwen3_5ForConditionalGeneration"],
+                "model_type": "qwen3_5_moe" if arch.num_experts > 0 else "qwen3_5", "text_config": text,
+                "tie_word_embeddings": arch.tie_word_embeddings, "torch_dtype": "bfloat16"}
 
 
 class KimiStateFormat(ModelStateFormat):
@@ -356,7 +401,7 @@ class KimiStateFormat(ModelStateFormat):
 
 
 _FORMATS = {"native": ModelStateFormat(), "qwen3": Qwen3StateFormat(), "deepseek_v4": DeepseekV4StateFormat(), "kimi": KimiStateFormat(),
-            "qwen3_5": Qwen35StateFormat()}
+            "qwen3_5": Qwen35StateFormat(), "qwen3_5_vl": Qwen35VLStateFormat()}
 
 
 def registered_for_hf_model_type(model_type: str):
