@@ -304,3 +304,34 @@ def test_vision_language_folder_in_the_published_layout_loads(tmp_path):
                       use_cache=False).logits[0]
     tr.close()
     assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()
+
+
+def test_the_library_loads_a_vision_language_export(tmp_path):
+    """`save_hf_checkpoint` of the `_vl` model with the published tower: `from_pretrained` builds the library's
+    vision-language model from the written config.json and tensors, and a forward with an image gives this model's logits."""
+    hf = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5")
+    from torchllmtuner_b200.components.checkpointer.hf import save_hf_checkpoint
+    from torchllmtuner_b200.datasets.multimodal import build_mrope_positions, insert_vision_placeholders
+    c = LLMTunerConfig()
+    c.apply_flat(base_flat(model_name_or_path="qwen3_5_vl", vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                           num_attention_heads=4, num_key_value_heads=2, dump_folder=str(tmp_path / "run")))
+    c.model.arch_overrides = dict(head_dim=32, linear_chunk_size=8, image_token_id=90, vision_tower="qwen3_5",
+                                  vision=dict(VIT, patch_order="merge_blocks"))
+    tr = Trainer(c)
+    out = str(tmp_path / "hf")
+    save_hf_checkpoint(tr, out, "float32")
+    theirs = hf.Qwen3_5ForConditionalGeneration.from_pretrained(out, attn_implementation="eager", dtype=torch.float32).eval()
+    grids = [(1, 4, 4)]
+    torch.manual_seed(1)
+    patches = torch.randn(16, 3 * 2 * 4 * 4)
+    words = torch.randint(0, 80, (12,)).tolist()
+    ids = insert_vision_placeholders(words[:5] + [90] + words[5:], 90, grids)
+    pos = build_mrope_positions(ids, 90, grids)
+    ids_t = torch.tensor(ids)
+    with torch.no_grad():
+        ctx = tr.model.build_context(pos, AttnMeta.build(torch.tensor([0, len(ids)], dtype=torch.int32), causal=True))
+        got = tr.model(ids_t, ctx, patches=patches, grids=grids)
+        want = theirs(input_ids=ids_t[None], pixel_values=patches, image_grid_thw=torch.tensor(grids),
+                      mm_token_type_ids=(ids_t[None] == 90).int(), use_cache=False).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()

@@ -207,7 +207,7 @@ def save_hf_checkpoint(trainer, out_dir: str, export_dtype: str = "bfloat16", ma
             for k in keys:
                 weight_map[k] = final
         with open(os.path.join(stage, "config.json"), "w") as f:
-            json.dump(fmt.hf_config(trainer.model.config), f, indent=1)
+            json.dump(fmt.hf_config_of(trainer.model), f, indent=1)
         with open(os.path.join(stage, "model.safetensors.index.json.tmp"), "w") as f:
             json.dump({"metadata": {"format": "pt"}, "weight_map": weight_map}, f, indent=1)
         os.replace(os.path.join(stage, "model.safetensors.index.json.tmp"), os.path.join(stage, "model.safetensors.index.json"))

@@ -70,6 +70,10 @@ class ModelStateFormat:
     def hf_config(self, arch) -> dict:
         return dict(vars(arch))
 
+    def hf_config_of(self, model) -> dict:
+        """config.json for `model`; formats whose file describes more than the decoder's architecture override this."""
+        return self.hf_config(model.config)
+
     # `model_name_or_path=<folder>`: which registered model a config.json's `model_type` builds, and the architecture
     # fields it carries (the inverse of `hf_config`; fields a builder does not know are ignored by it)
     hf_model_types: dict = {}
@@ -331,6 +335,18 @@ class Qwen35VLStateFormat(Qwen35StateFormat):
         return {"architectures": ["Qwen3_5MoeForConditionalGeneration" if arch.num_experts > 0 else "Qwen3_5ForConditionalGeneration"],
                 "model_type": "qwen3_5_moe" if arch.num_experts > 0 else "qwen3_5", "text_config": text,
                 "tie_word_embeddings": arch.tie_word_embeddings, "torch_dtype": "bfloat16"}
+
+    def hf_config_of(self, model) -> dict:
+        """Adds what only the whole model knows: the placeholder token and, for the published tower, its geometry."""
+        cfg = self.hf_config(model.config)
+        cfg["image_token_id"] = int(model.image_token_id)
+        v = getattr(getattr(model, "visual", None), "config", None)
+        if v is not None and hasattr(v, "num_position_embeddings"):
+            cfg["vision_config"] = {k: getattr(v, k) for k in ("depth", "hidden_size", "intermediate_size", "num_heads", "in_channels", "patch_size",
+                                                              "spatial_merge_size", "temporal_patch_size", "out_hidden_size",
+                                                              "num_position_embeddings")}
+            cfg["vision_config"].update(model_type=cfg["model_type"], hidden_act="gelu_pytorch_tanh")
+        return cfg
 
 
 class KimiStateFormat(ModelStateFormat):
