@@ -321,6 +321,10 @@ def test_the_library_loads_a_vision_language_export(tmp_path):
     out = str(tmp_path / "hf")
     save_hf_checkpoint(tr, out, "float32")
     theirs = hf.Qwen3_5ForConditionalGeneration.from_pretrained(out, attn_implementation="eager", dtype=torch.float32).eval()
+    rep = hf_preflight.preflight(out, vision=True)           # every tensor of the folder, the tower's included
+    assert rep["ok"] and rep["registered_model"] == "qwen3_5_vl" and rep["unused_count"] == 0 and rep["expected_tensors"] == rep["stored_tensors"], rep
+    text_only = hf_preflight.preflight(out)                  # as a text decoder: the tower's tensors are simply not read
+    assert text_only["ok"] and text_only["registered_model"] == "qwen3_5" and text_only["unused_count"] > 0
     grids = [(1, 4, 4)]
     torch.manual_seed(1)
     patches = torch.randn(16, 3 * 2 * 4 * 4)

@@ -4,7 +4,7 @@ inspector, examples/inspect_hf_experts.py:1-70; this tool answers the question a
 `--model_name_or_path <folder> --initial_load_path <folder> --initial_load_in_hf true` find every tensor it needs, in the
 shape it needs?).
 
-    python -m torchllmtuner_b200.components.checkpointer.hf_preflight <folder> [--json]
+    python -m torchllmtuner_b200.components.checkpointer.hf_preflight <folder> [--json] [--vision]
 
 It reads `config.json`, names the registered model and state format that build it, builds that model on the meta
 device, lists the tensor names and shapes the importer will ask for (the state format's `hf_pieces`), and compares them
@@ -50,21 +50,38 @@ def stored_tensors(folder: str) -> dict[str, tuple[int, ...]]:
     return out
 
 
-def preflight(folder: str) -> dict:
+_TOWER_FIELDS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_channels", "patch_size", "spatial_merge_size",
+                 "temporal_patch_size", "num_position_embeddings")
+
+
+def preflight(folder: str, vision: bool = False) -> dict:
+    """`vision=True`: a folder whose config.json carries a `vision_config` is checked as the vision-language model (the
+    `_vl` entry of its family with the published tower) instead of as its text decoder alone."""
     import torch
     from ...config.model_config import ModelConfig
-    from ...models.registry import build_registered_model
-    from ...models.state import registered_for_hf_model_type
+    from ...models.registry import build_registered_model, registered_models
+    from ...models.state import get_state_format, registered_for_hf_model_type
     with open(os.path.join(folder, "config.json")) as f:
         hf = json.load(f)
     key, fmt = registered_for_hf_model_type(hf.get("model_type", ""))
+    model_config = ModelConfig(model_name_or_path=folder)
+    if vision and key is not None and isinstance(hf.get("vision_config"), dict) and key + "_vl" in registered_models():
+        key = key + "_vl"
+        arch = fmt.arch_from_hf(hf)
+        arch.update(vision_tower="qwen3_5", image_token_id=hf.get("image_token_id", 0),
+                    vision=dict({k: hf["vision_config"][k] for k in _TOWER_FIELDS if k in hf["vision_config"]}, patch_order="merge_blocks"))
+        for k in ("dtype", "device", "model_config"):
+            arch.pop(k, None)
+        model_config = ModelConfig(model_name_or_path=key, arch_overrides=arch)
     report = {"folder": folder, "model_type": hf.get("model_type"), "registered_model": key,
               "state_format": getattr(fmt, "name", None), "ok": False}
     if key is None:
         report["error"] = f"model_type {hf.get('model_type')!r} has no registered model"
         return report
     with torch.device("meta"):
-        model = build_registered_model(ModelConfig(model_name_or_path=folder))
+        model = build_registered_model(model_config)
+    fmt = get_state_format(model.state_format)
+    report.update(registered_model=key, state_format=fmt.name)
     report["parameters"] = sum(p.numel() for p in model.parameters())
     try:
         have = stored_tensors(folder)
@@ -88,8 +105,9 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="hf_preflight", description="check a Hugging Face folder against this framework's importer")
     ap.add_argument("folder")
     ap.add_argument("--json", action="store_true", help="print the whole report as JSON")
+    ap.add_argument("--vision", action="store_true", help="check the vision tower's tensors too (folders with a vision_config)")
     a = ap.parse_args(argv)
-    rep = preflight(a.folder)
+    rep = preflight(a.folder, vision=a.vision)
     if a.json:
         print(json.dumps(rep, indent=1))
     else:
