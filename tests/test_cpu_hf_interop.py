@@ -267,16 +267,15 @@ def test_vision_language_folder_in_the_published_layout_loads(tmp_path):
     folder = tmp_path / "hf"
     folder.mkdir()
     save_file({k: v.contiguous() for k, v in theirs.state_dict().items()}, str(folder / "model.safetensors"))
-    c = LLMTunerConfig()
-    c.apply_flat(base_flat(model_name_or_path="qwen3_5_vl", vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
-                           num_attention_heads=4, num_key_value_heads=2, dump_folder=str(tmp_path / "run")))
-    c.model.arch_overrides = dict(head_dim=32, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
-                                  linear_value_head_dim=24, linear_conv_kernel_dim=4, rope_theta=10000.0, partial_rotary_factor=0.5,
-                                  mrope_section=[4, 2, 2], linear_chunk_size=8, image_token_id=90, vision_tower="qwen3_5",
-                                  vision=dict(VIT, patch_order="merge_blocks"))
+    import json
+    (folder / "config.json").write_text(json.dumps(cfg.to_dict()))
+    c = LLMTunerConfig()      # the folder names the model; asking for the tower turns it into the vision-language entry
+    c.apply_flat(base_flat(model_name_or_path=str(folder), dump_folder=str(tmp_path / "run"), enable=True, initial_load_path=str(folder),
+                           initial_load_in_hf=True))
+    c.model.arch_overrides = dict(vision_tower="qwen3_5", vision=dict(patch_order="merge_blocks"), linear_chunk_size=8)
     tr = Trainer(c)
-    assert tr.model.state_format == "qwen3_5_vl"
-    load_hf_checkpoint(tr, str(folder))
+    assert tr.model.state_format == "qwen3_5_vl" and tr.model.image_token_id == 90 and tr.model.visual.config.hidden_size == 32
+    assert tr.checkpointer.load()
     grids = [(1, 4, 4), (1, 2, 6)]
     patches = torch.randn(sum(t * h * w for t, h, w in grids), 3 * 2 * 4 * 4)
     S = 17

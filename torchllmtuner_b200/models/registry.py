@@ -52,8 +52,14 @@ def resolve_state_format(name: str):
     return get_state_format(get_model_spec(name).state_format)
 
 
+_TOWER_FIELDS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_channels", "patch_size", "spatial_merge_size",
+                 "temporal_patch_size", "num_position_embeddings")
+
+
 def build_registered_model(model_config, dtype=None, device=None):
-    """`model_name_or_path` is a registry key or a Hugging Face folder whose config.json names the architecture."""
+    """`model_name_or_path` is a registry key or a Hugging Face folder whose config.json names the architecture. A folder
+    with a `vision_config` builds the text decoder, or, when `arch_overrides` names a `vision_tower`, the family's
+    vision-language model with the folder's tower geometry and placeholder token."""
     _ensure_builtins()
     key = model_config.model_name_or_path
     overrides = {}
@@ -68,6 +74,15 @@ def build_registered_model(model_config, dtype=None, device=None):
         overrides = fmt.arch_from_hf(hf)
         for k in ("dtype", "device", "model_config"):          # config.json keys that are not architecture (`dtype` is in every
             overrides.pop(k, None)                              # file transformers writes) must not collide with the builder's own
+        asked = dict(model_config.arch_overrides or {})
+        if asked.get("vision_tower") and isinstance(hf.get("vision_config"), dict) and key + "_vl" in _MODELS:
+            # a vision-language folder, and the run wants the tower: the family's `_vl` entry with the folder's tower geometry
+            import dataclasses
+            tower = {k: v for k, v in hf["vision_config"].items() if k in _TOWER_FIELDS}
+            tower.update(asked.get("vision") or {})
+            asked.update(vision=tower, image_token_id=asked.get("image_token_id", hf.get("image_token_id")))
+            model_config = dataclasses.replace(model_config, arch_overrides=asked)
+            key = key + "_vl"
     spec = get_model_spec(key)
     model = spec.builder(model_config, dtype=dtype, device=device, **overrides)
     model.state_format = spec.state_format           # read by the HF and reference-layout converters
