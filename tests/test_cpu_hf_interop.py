@@ -247,7 +247,6 @@ def test_vision_language_folder_in_the_published_layout_loads(tmp_path):
     hf = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5")
     from safetensors.torch import save_file
     from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5Config
-    from torchllmtuner_b200.components.checkpointer.hf import load_hf_checkpoint
     torch.manual_seed(0)
     txt = dict(vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
                head_dim=32, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=24,
@@ -329,6 +328,56 @@ def test_the_library_loads_a_vision_language_export(tmp_path):
     patches = torch.randn(16, 3 * 2 * 4 * 4)
     words = torch.randint(0, 80, (12,)).tolist()
     ids = insert_vision_placeholders(words[:5] + [90] + words[5:], 90, grids)
+    pos = build_mrope_positions(ids, 90, grids)
+    ids_t = torch.tensor(ids)
+    with torch.no_grad():
+        ctx = tr.model.build_context(pos, AttnMeta.build(torch.tensor([0, len(ids)], dtype=torch.int32), causal=True))
+        got = tr.model(ids_t, ctx, patches=patches, grids=grids)
+        want = theirs(input_ids=ids_t[None], pixel_values=patches, image_grid_thw=torch.tensor(grids),
+                      mm_token_type_ids=(ids_t[None] == 90).int(), use_cache=False).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()
+
+
+def test_moe_vision_language_folder_builds_loads_and_matches(tmp_path):
+    """Qwen3.5-MoE with its tower, tensors as the library's model holds them (packed experts under
+    `model.language_model.`): preflight with the tower, build from the folder, load, and a forward with an image."""
+    hf = pytest.importorskip("transformers.models.qwen3_5_moe.modeling_qwen3_5_moe")
+    import json
+    from safetensors.torch import save_file
+    from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeConfig
+    from torchllmtuner_b200.datasets.multimodal import build_mrope_positions, insert_vision_placeholders
+    torch.manual_seed(0)
+    txt = dict(vocab_size=96, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32, num_experts=4,
+               num_experts_per_tok=2, moe_intermediate_size=24, shared_expert_intermediate_size=40, linear_num_value_heads=4,
+               linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=24, linear_conv_kernel_dim=4, rms_norm_eps=1e-6,
+               rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5, "mrope_section": [4, 2, 2],
+                                "mrope_interleaved": True})
+    cfg = Qwen3_5MoeConfig(text_config=txt, vision_config=dict(VIT, out_hidden_size=64), image_token_id=90, video_token_id=91,
+                           vision_start_token_id=92, vision_end_token_id=93, tie_word_embeddings=False)
+    for part in (cfg, cfg.text_config, cfg.vision_config):
+        part._attn_implementation = "eager"
+    theirs = hf.Qwen3_5MoeForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n, p in theirs.named_parameters():
+            if "visual" in n:
+                torch.nn.init.normal_(p, std=0.2)
+    folder = tmp_path / "hf"
+    folder.mkdir()
+    save_file({k: v.contiguous() for k, v in theirs.state_dict().items()}, str(folder / "model.safetensors"))
+    (folder / "config.json").write_text(json.dumps(cfg.to_dict()))
+    rep = hf_preflight.preflight(str(folder), vision=True)
+    assert rep["ok"] and rep["registered_model"] == "qwen3_5_moe_vl" and rep["unused_count"] == 0, rep
+    c = LLMTunerConfig()
+    c.apply_flat(base_flat(model_name_or_path=str(folder), dump_folder=str(tmp_path / "run"), enable=True, initial_load_path=str(folder),
+                           initial_load_in_hf=True))
+    c.model.arch_overrides = dict(vision_tower="qwen3_5", vision=dict(patch_order="merge_blocks"), linear_chunk_size=8)
+    tr = Trainer(c)
+    assert tr.checkpointer.load() and tr.model.config.num_experts == 4
+    grids = [(1, 4, 4)]
+    patches = torch.randn(16, 96)
+    words = torch.randint(0, 80, (14,)).tolist()
+    ids = insert_vision_placeholders(words[:6] + [90] + words[6:], 90, grids)
     pos = build_mrope_positions(ids, 90, grids)
     ids_t = torch.tensor(ids)
     with torch.no_grad():
