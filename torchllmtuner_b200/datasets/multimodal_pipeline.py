@@ -37,6 +37,10 @@ class VisionSpec:
     video_min_frames: int = 4
     video_max_frames: int = 32
     temporal_pool: bool = False        # the tower averages a clip's frames: rows per item do not grow with the frame count
+    # The tower's patch embedding has a temporal axis (`models/qwen_vit.py`): every row carries channels x
+    # temporal_patch_size x patch x patch values, the frames of a temporal step side by side (an image repeats its one
+    # frame), instead of one frame-sized patch per step with the step's frames averaged.
+    full_temporal: bool = False
 
     @property
     def factor(self) -> int:
@@ -56,7 +60,17 @@ def image_to_patches(img: torch.Tensor, spec: VisionSpec):
     c, h, w = img.shape
     nh, nw = smart_resize(h, w, factor=spec.factor, min_pixels=spec.min_pixels, max_pixels=spec.max_pixels)
     img = F.interpolate(img[None], size=(nh, nw), mode="bilinear", align_corners=False)[0]
-    return vision_to_patches(img, spec.patch_size), (1, nh // spec.patch_size, nw // spec.patch_size)
+    rows = vision_to_patches(img, spec.patch_size)
+    if spec.full_temporal:
+        rows = temporal_rows([rows] * spec.temporal_patch_size, c)
+    return rows, (1, nh // spec.patch_size, nw // spec.patch_size)
+
+
+def temporal_rows(frames_rows: list[torch.Tensor], channels: int) -> torch.Tensor:
+    """Per-frame patch rows [N, C*p*p] of one temporal step -> [N, C * len(frames) * p*p], laid out channel-major then
+    frame, the order of a [C, temporal, patch, patch] convolution kernel."""
+    n = frames_rows[0].shape[0]
+    return torch.stack([r.view(n, channels, -1) for r in frames_rows], 2).reshape(n, -1)
 
 
 def sample_frame_indices(num_frames: int, source_fps: float, spec: VisionSpec) -> list[int]:
@@ -74,16 +88,20 @@ def sample_frame_indices(num_frames: int, source_fps: float, spec: VisionSpec) -
 
 def video_to_patches(frames: torch.Tensor, source_fps: float, spec: VisionSpec):
     """frames [F, C, H, W] -> (patches [t*gh*gw, C*p*p], (t, gh, gw)). Each temporal step averages its
-    `temporal_patch_size` frames (the tower's patch embedding sees one frame-sized patch per step); the pixel budget is
-    shared by the steps."""
+    `temporal_patch_size` frames (the tower's patch embedding sees one frame-sized patch per step), or with
+    `spec.full_temporal` keeps them side by side in rows of C*temporal_patch_size*p*p values; the pixel budget is shared by
+    the steps."""
     idx = sample_frame_indices(frames.shape[0], source_fps, spec)
     clip = frames[idx]
     t = len(idx) // spec.temporal_patch_size
     _, c, h, w = clip.shape
     nh, nw = smart_resize(h, w, factor=spec.factor, min_pixels=spec.min_pixels, max_pixels=max(spec.min_pixels, spec.max_pixels // t))
     clip = F.interpolate(clip, size=(nh, nw), mode="bilinear", align_corners=False)
-    steps = clip.view(t, spec.temporal_patch_size, c, nh, nw).mean(1)
-    patches = torch.cat([vision_to_patches(s, spec.patch_size) for s in steps])
+    steps = clip.view(t, spec.temporal_patch_size, c, nh, nw)
+    if spec.full_temporal:
+        patches = torch.cat([temporal_rows([vision_to_patches(f, spec.patch_size) for f in step], c) for step in steps])
+    else:
+        patches = torch.cat([vision_to_patches(s, spec.patch_size) for s in steps.mean(1)])
     return patches, (t, nh // spec.patch_size, nw // spec.patch_size)
 
 

@@ -181,7 +181,8 @@ def build_multimodal_dataloader(data_cfg, *, model, vocab_size: int, seq_len: in
     vc = model.visual.config
     spec = VisionSpec(patch_size=vc.patch_size, merge_size=vc.spatial_merge_size, max_pixels=data_cfg.mm_max_pixels,
                       min_pixels=min(data_cfg.mm_max_pixels, (vc.patch_size * vc.spatial_merge_size * 2) ** 2),
-                      temporal_pool=getattr(vc, "temporal_pool", False), video_max_frames=2 * getattr(vc, "pos_emb_time", 16))
+                      temporal_pool=getattr(vc, "temporal_pool", False), video_max_frames=2 * getattr(vc, "pos_emb_time", 16),
+                      temporal_patch_size=getattr(vc, "temporal_patch_size", 2), full_temporal=hasattr(vc, "full_patch_dim"))
     src = IndexedJsonlSource(data_cfg.dataset_path)
     root = os.path.dirname(src.paths[0]) if getattr(src, "paths", None) else ""
     proc = MultimodalProcessor(tok, data_cfg.dataset, spec, root=root, image_token=data_cfg.mm_image_token, video_token=data_cfg.mm_video_token)
