@@ -387,3 +387,33 @@ def test_moe_vision_language_folder_builds_loads_and_matches(tmp_path):
                       mm_token_type_ids=(ids_t[None] == 90).int(), use_cache=False).logits[0]
     tr.close()
     assert torch.allclose(got.float(), want, atol=2e-4, rtol=1e-4), (got - want).abs().max()
+
+
+def test_packed_documents_match_the_library_run_with_a_block_diagonal_mask(tmp_path):
+    """Three documents packed into one row: document cut points and per-document positions here, an explicit
+    block-diagonal causal mask and the same position ids in the library."""
+    import transformers as T
+    torch.manual_seed(0)
+    hf_cfg = T.Qwen3MoeConfig(**DENSE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24, norm_topk_prob=True)
+    hf_cfg._attn_implementation = "eager"
+    theirs = T.Qwen3MoeForCausalLM(hf_cfg).eval()
+    folder = str(tmp_path / "hf")
+    theirs.save_pretrained(folder, safe_serialization=True)
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(model_name_or_path=folder, dump_folder=str(tmp_path / "run"), enable=True, initial_load_path=folder,
+                             initial_load_in_hf=True))
+    tr = Trainer(cfg)
+    assert tr.checkpointer.load()
+    lens = [7, 12, 5]
+    S = sum(lens)
+    tok = torch.randint(0, 96, (S,))
+    pos = torch.cat([torch.arange(n) for n in lens])
+    doc = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens))
+    allowed = (doc[:, None] == doc[None, :]) & (torch.arange(S)[None, :] <= torch.arange(S)[:, None])
+    mask = torch.zeros(S, S).masked_fill(~allowed, float("-inf"))[None, None]
+    with torch.no_grad():
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        got = tr.model(tok, tr.model.build_context(pos, AttnMeta.build(cu, causal=True)))
+        want = theirs(input_ids=tok[None], position_ids=pos[None], attention_mask=mask, use_cache=False).logits[0]
+    tr.close()
+    assert torch.allclose(got.float(), want, atol=1e-5), (got - want).abs().max()
