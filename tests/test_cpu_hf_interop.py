@@ -417,3 +417,30 @@ def test_packed_documents_match_the_library_run_with_a_block_diagonal_mask(tmp_p
         want = theirs(input_ids=tok[None], position_ids=pos[None], attention_mask=mask, use_cache=False).logits[0]
     tr.close()
     assert torch.allclose(got.float(), want, atol=1e-5), (got - want).abs().max()
+
+
+def test_a_training_step_has_the_librarys_loss_and_gradient_norm(tmp_path):
+    """One optimizer step over two accumulated micro-batches through the Trainer (flat gradient buffers, sum / global
+    token count, norm for clipping) against `loss.backward()` of the library's model on the same rows."""
+    import transformers as T
+    torch.manual_seed(0)
+    hf_cfg = T.Qwen3MoeConfig(**DENSE, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24, norm_topk_prob=True,
+                              router_aux_loss_coef=0.0)
+    hf_cfg._attn_implementation = "eager"
+    theirs = T.Qwen3MoeForCausalLM(hf_cfg).train()
+    folder = str(tmp_path / "hf")
+    theirs.save_pretrained(folder, safe_serialization=True)
+    cfg = LLMTunerConfig()
+    cfg.apply_flat(base_flat(model_name_or_path=folder, dump_folder=str(tmp_path / "run"), enable=True, initial_load_path=folder,
+                             initial_load_in_hf=True, gradient_accumulation_steps=2, global_batch_size=4))
+    tr = Trainer(cfg)
+    assert tr.checkpointer.load()
+    it = iter(tr.dataloader)
+    rows = torch.cat([next(it)["input"] for _ in range(2)])
+    tr.dataloader.cursor = 0
+    step = tr.train_step()
+    tr.close()
+    out = theirs(input_ids=rows, labels=rows)
+    out.loss.backward()
+    norm = torch.sqrt(sum(p.grad.float().square().sum() for p in theirs.parameters() if p.grad is not None))
+    assert abs(step.loss - out.loss.item()) < 1e-5 and abs(step.grad_norm - norm.item()) < 1e-5 * max(1.0, norm.item())
