@@ -439,8 +439,19 @@ def test_a_training_step_has_the_librarys_loss_and_gradient_norm(tmp_path):
     rows = torch.cat([next(it)["input"] for _ in range(2)])
     tr.dataloader.cursor = 0
     step = tr.train_step()
+    ours_after = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
     tr.close()
     out = theirs(input_ids=rows, labels=rows)
     out.loss.backward()
     norm = torch.sqrt(sum(p.grad.float().square().sum() for p in theirs.parameters() if p.grad is not None))
     assert abs(step.loss - out.loss.item()) < 1e-5 and abs(step.grad_norm - norm.item()) < 1e-5 * max(1.0, norm.item())
+    # the update: clip to max_norm, AdamW with the step's learning rate (decoupled weight decay on every tensor, like here)
+    t, o = cfg.training, cfg.optimizer
+    before = theirs.lm_head.weight.detach().clone()
+    torch.nn.utils.clip_grad_norm_(theirs.parameters(), t.max_norm)
+    torch.optim.AdamW(theirs.parameters(), lr=step.lr, betas=tuple(o.betas), eps=o.eps, weight_decay=o.weight_decay).step()
+    moved = (theirs.lm_head.weight - before).abs().max().item()
+    assert moved > 0 and norm.item() > t.max_norm                                     # the clip was active
+    for name in ("lm_head.weight", "model.layers.1.self_attn.q_proj.weight", "model.norm.weight"):
+        want = dict(theirs.named_parameters())[name]
+        assert torch.allclose(ours_after[name], want, atol=moved * 1e-3), (name, (ours_after[name] - want).abs().max(), moved)
